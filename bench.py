@@ -1,0 +1,210 @@
+#!/usr/bin/env python
+"""Headline benchmark: examples/sec of CTR-scale online FTRL-proximal (L1-LR) on N B200s.
+
+Config (the CTR-scale FTRL configuration of the baseline): hashed uint64 keys over a 2^30-key
+space drawn Zipf(1.1), 12 feature groups x ~8 binary features (~96-100 nnz/row), minibatches of
+100,000 rows per GPU (weak scaling: every GPU streams its own minibatches), labels
+Bernoulli(sigmoid(X.w* - 3.2)), per-key fp32 state, alpha=0.1 beta=1 lambda1=1 lambda2=0.1.
+A step = one minibatch per GPU through the pull-fused SpMV and the push-fused FTRL update.
+
+  python bench.py --gpus 1 --steps 20 --warmup 5
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+      --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
+
+``value`` is device-timed (CUDA events, max over ranks) on minibatches resident on the device
+(a ring of distinct minibatches larger than L2); ``e2e`` times the public streaming API
+(`FTRLTrainer.train`) including the pinned host->device copy of every minibatch and the
+device->host read of every step's loss.  ``--impl nccl`` runs the unfused NCCL baseline of the
+same algorithm; ``--impl reference`` reports why the CPU/ZeroMQ reference cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+REFERENCE_UNAVAILABLE = ("reference is a CPU-only C++/ZeroMQ program with a make build and no Python package: "
+                         "pip install of /root/reference fails (no setup.py/pyproject.toml) and its build needs "
+                         "zeromq, gflags, glog, protobuf+protoc, snappy, eigen3, tcmalloc, none present offline")
+
+CLOCK_QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+               "clocks_event_reasons.sw_power_cap")
+
+
+class ClockSampler:
+    """Samples this rank's GPU clocks with nvidia-smi while the timed region runs."""
+
+    def __init__(self, device):
+        import torch
+
+        self.proc, self.path = None, f"/tmp/psb_clocks_{os.getpid()}.csv"
+        try:
+            uuid = str(torch.cuda.get_device_properties(device).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.cmd = ["nvidia-smi", "-i", uuid, f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits",
+                        "-lms", "100"]
+        except Exception:
+            self.cmd = None
+
+    def start(self):
+        if self.cmd:
+            try:
+                self.proc = subprocess.Popen(self.cmd, stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            except Exception:
+                self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 7:
+                    continue
+                try:
+                    sm.append(float(f[0])); mx.append(float(f[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, f[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def run_ftrl(args) -> dict:
+    import torch
+
+    from parameter_server_b200.data.synthetic import ctr_minibatch
+    from parameter_server_b200.models.ftrl import DeviceMinibatch, FTRLEngine, FTRLHyper
+    from parameter_server_b200.models.ftrl_trainer import FTRLTrainer, HostMinibatch
+    from parameter_server_b200.parallel.peer import PeerGroup
+
+    group = PeerGroup.from_env()
+    dev, rank, world = group.device, group.rank, group.world
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    rows, ring = args.rows, args.ring
+    batches = []
+    for i in range(ring):
+        off, keys, y = ctr_minibatch(rows, seed=1000 * rank + i + 1, device=dev)
+        batches.append(DeviceMinibatch(off, keys, y))
+    max_nnz = max(b.nnz for b in batches)
+    eng = FTRLEngine(group, FTRLHyper(alpha=0.1, beta=1.0, lambda1=1.0, lambda2=0.1),
+                     table_capacity=1 << args.table_log2, max_rows=rows, max_nnz=max_nnz,
+                     local_capacity=1 << args.local_log2, timeout_s=args.timeout_s,
+                     impl="nccl" if args.impl == "nccl" else "fused")
+    # ---------------------------------------------------------------- device-resident timing
+    for i in range(args.warmup):
+        eng.step(batches[i % ring])
+    eng.read_stats()
+    eng.check_status()
+    group.barrier()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    launches0 = eng.kernel_launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        eng.step(batches[(args.warmup + i) % ring])
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = group.all_reduce_max(e0.elapsed_time(e1))
+    group.barrier()
+    launches = eng.kernel_launches - launches0
+    st = eng.read_stats()
+    eng.check_status()
+    # ---------------------------------------------------------------- end to end (public API)
+    host = [HostMinibatch(b.offsets.cpu(), b.keys.cpu(), b.y.cpu()).pin() for b in batches]
+    trainer = FTRLTrainer(eng)
+    trainer.train(host[i % ring] for i in range(max(3, args.warmup)))
+    group.barrier()
+    trainer.h2d_bytes = trainer.d2h_bytes = 0
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    losses = trainer.train(host[i % ring] for i in range(args.steps))
+    t1.record()
+    torch.cuda.synchronize(dev)
+    e2e_ms = group.all_reduce_max(t0.elapsed_time(t1))
+    clocks = sampler.stop()
+    group.barrier()
+    ex_per_step = rows * world
+    return {
+        "metric": "examples/sec (online FTRL-proximal L1-LR, CTR-scale stream)",
+        "value": ex_per_step * args.steps / (ms / 1e3),
+        "unit": "examples/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32", "data": "synthetic",
+        "impl": "nccl-baseline" if args.impl == "nccl" else "fused",
+        "config": {"model": "FTRL-proximal logistic regression, 2^30 hashed uint64 keys Zipf(1.1), ~96 nnz/row, "
+                            "alpha=0.1 beta=1 lambda1=1 lambda2=0.1, per-key fp32 (w,z,pos,neg)",
+                   "global_batch": ex_per_step, "seq_len": None, "nnz_per_row": max_nnz / rows,
+                   "parallelism": f"dp{world} x key-range shards {world} (worker+server per GPU)",
+                   "l2_policy": f"inputs larger than L2: ring of {ring} distinct minibatches "
+                                f"({batches[0].nbytes() >> 20} MiB each) plus {max_nnz * 4 >> 20} MiB slot map per step",
+                   "mean_logloss_last": st["loss_sum"] / max(st["rows"], 1), "nnz_w": st["nnz_w"],
+                   "unique_keys_per_step": st["unique_keys"] / max(args.steps, 1)},
+        "e2e": {"value": ex_per_step * args.steps / (e2e_ms / 1e3), "unit": "examples/s",
+                "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": trainer.h2d_bytes // args.steps, "d2h_bytes_per_step": trainer.d2h_bytes // args.steps,
+                "mean_logloss_last": losses[-1] if losses else None},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }, rank
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "fused", "nccl", "reference"])
+    ap.add_argument("--rows", type=int, default=100000, help="minibatch rows per GPU")
+    ap.add_argument("--ring", type=int, default=4, help="distinct minibatches per GPU")
+    ap.add_argument("--table-log2", type=int, default=26, help="log2 slots of each GPU's shard table")
+    ap.add_argument("--local-log2", type=int, default=22, help="log2 slots of the per-minibatch dedup table")
+    ap.add_argument("--timeout-s", type=float, default=5.0, help="limit of in-kernel cross-GPU waits")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+    result, rank = run_ftrl(args)
+    if rank == 0:
+        print(json.dumps(result))
+    try:
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,559 @@
+// Online FTRL-proximal on key-range sharded device hash tables: the two fused
+// communication+compute kernels of the product path, plus the same phases as
+// stand-alone kernels for the unfused NCCL baseline.
+//
+// One rank = one GPU = worker r (streams minibatches) + server r (owns the keys
+// of [sep[r], sep[r+1]) in an open-addressing table {key -> w, z, pos, neg}).
+//
+//   ftrl_pull_spmv  : de-duplicate the minibatch's keys into an L2-resident local
+//                     table, gather each unique key's weight straight from the
+//                     owner shard's table with peer loads over NVLink, then run
+//                     the CSR SpMV X·w, the logistic loss and the per-row
+//                     coefficient −y/(1+e^{y·Xw}) — one cooperative kernel.
+//   ftrl_push_update: Xᵀ·coef and the pos/neg row counts per unique key, routed by
+//                     key range into the owner's per-sender inbox with peer
+//                     stores, a release flag per (sender, owner), and — on
+//                     arrival of all senders — the owner-side FTRL update applied
+//                     sender by sender, then an "applied" notification to every
+//                     peer — one cooperative kernel.
+//
+// The arithmetic is the reference's server rule FTRLModel::setValue
+// (src/linear_method/ftrl_model.h:81-112), the worker gradient of LogitLoss
+// (src/linear_method/loss.h:73-88) and FTRL::countKeys
+// (src/linear_method/ftrl.cc:154-174); the message flow replaces
+// SharedParameter::push/pull (src/parameter/shared_parameter.h:14-26,90-149).
+// The schedule is bulk-synchronous (one legal serialisation of the reference's
+// eventual-consistency execution): pull(e) sees every update of step e-1.
+#include "psb_common.cuh"
+
+namespace psb {
+
+struct ShardState {  // 16 B, one per table slot
+  float w;
+  float z;
+  uint32_t pos;  // rule 0: #positive rows seen; rule 1: bit pattern of Σg² (float)
+  uint32_t neg;
+};
+
+struct FtrlHyper {
+  float alpha, beta, l1, l2;
+  int rule;  // 0 = count-based ‖g‖ estimate (reference), 1 = Σ g² (McMahan et al.)
+  int pad;
+};
+
+struct FtrlPeers {
+  KeySeps seps;
+  int rank;
+  int max_probe;
+  uint64_t tab_mask;                       // table capacity − 1 (same on all ranks)
+  uint64_t* tab_keys[PSB_MAX_RANKS];
+  ShardState* tab_state[PSB_MAX_RANKS];
+  uint64_t* in_keys[PSB_MAX_RANKS];        // owner o: [sender][in_cap]
+  float* in_g[PSB_MAX_RANKS];
+  uint64_t* in_cnt[PSB_MAX_RANKS];         // pos<<32 | neg
+  uint64_t* in_flag[PSB_MAX_RANKS];        // owner o: [sender] = epoch<<32 | count
+  uint64_t* applied[PSB_MAX_RANKS];        // rank r: [owner] = epoch<<32
+  uint64_t timeout_ns;
+  uint32_t in_cap;
+  uint32_t pad;
+};
+
+struct Minibatch {
+  const int64_t* offsets;  // rows+1
+  const uint64_t* keys;    // nnz global keys
+  const float* vals;       // nnz values or nullptr (binary features)
+  const float* y;          // rows, ±1
+  int64_t nnz;
+  int rows;
+  int pad;
+};
+
+struct LocalSlot {  // 16 B payload of one local dedup-table slot
+  float w;                  // pulled weight
+  float g;                  // gradient accumulator
+  unsigned long long cnt;   // pos<<32 | neg rows containing the key
+};
+
+struct LocalScratch {
+  uint64_t* lt_keys;   // per-minibatch dedup table (all kEmptyKey between steps)
+  LocalSlot* lt_val;   // payload per slot (one 16-byte sector: w, g, counts)
+  uint64_t lt_mask;
+  uint32_t* slot_of;   // nnz: local slot of each non-zero
+  float* coef;         // rows: −y/(1+e^{y·Xw})
+  float* xw;           // rows: X·w (predictions)
+  uint32_t* send_cnt;  // [PSB_MAX_RANKS] cursors, zero between steps
+  uint32_t* recv_cnt;  // [PSB_MAX_RANKS]
+  double* stats;       // [0] Σloss [1] rows [2] ‖w‖₁ [3] ‖w‖₂² [4] nnz(w) [5] unique keys [6] table entries
+  uint32_t* status;    // StatusCode etc.
+};
+
+constexpr uint32_t kBadSlot = 0xFFFFFFFFu;
+
+__device__ __forceinline__ uint64_t shard_hash(uint64_t key) { return mix64(key) >> 20; }
+
+// ------------------------------------------------------------------ phases
+__device__ __forceinline__ void phase_localize(const Minibatch& M, const LocalScratch& L, int max_probe,
+                                               size_t gtid, size_t gsz) {
+  for (int64_t e = (int64_t)gtid; e < M.nnz; e += (int64_t)gsz) {
+    const uint64_t key = M.keys[e];
+    uint64_t slot = table_find_or_insert(L.lt_keys, L.lt_mask, mix64(key), key, max_probe);
+    if (slot == ~0ull) {
+      set_status(L.status, kLocalTableFull, 0, 0);
+      slot = kBadSlot;
+    }
+    L.slot_of[e] = (uint32_t)slot;
+  }
+}
+
+// weight of `key` in owner's table (peer memory), 0 when absent
+__device__ __forceinline__ float probe_weight(const uint64_t* tkeys, const ShardState* tstate,
+                                              uint64_t mask, uint64_t key, int max_probe) {
+  uint64_t slot = shard_hash(key) & mask;
+  for (int i = 0; i < max_probe; ++i) {
+    const uint64_t k = ld_relaxed_sys_u64(tkeys + slot);
+    if (k == key) return ld_relaxed_sys_f32(&tstate[slot].w);
+    if (k == kEmptyKey) return 0.f;
+    slot = (slot + 1) & mask;
+  }
+  return 0.f;
+}
+
+__device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScratch& L, size_t gtid,
+                                             size_t gsz) {
+  uint32_t uniq = 0;
+  for (uint64_t s = gtid; s <= L.lt_mask; s += gsz) {
+    const uint64_t key = __ldcg(L.lt_keys + s);
+    if (key != kEmptyKey) {
+      const int o = route_owner(P.seps, key);
+      LocalSlot v;
+      v.w = probe_weight(P.tab_keys[o], P.tab_state[o], P.tab_mask, key, P.max_probe);
+      v.g = 0.f;
+      v.cnt = 0ull;
+      *reinterpret_cast<float4*>(L.lt_val + s) = *reinterpret_cast<float4*>(&v);
+      ++uniq;
+    }
+  }
+  uniq = __reduce_add_sync(0xffffffffu, uniq);
+  if ((threadIdx.x & 31) == 0 && uniq) atomicAdd(&L.stats[5], (double)uniq);
+}
+
+__device__ __forceinline__ void phase_spmv_loss(const Minibatch& M, const LocalScratch& L, size_t gwarp,
+                                                size_t nwarps, int lane) {
+  double loss = 0.0;
+  for (int64_t row = (int64_t)gwarp; row < M.rows; row += (int64_t)nwarps) {
+    const int64_t b = M.offsets[row], e = M.offsets[row + 1];
+    float s = 0.f;
+    for (int64_t i = b + lane; i < e; i += 32) {
+      const uint32_t sl = L.slot_of[i];
+      if (sl != kBadSlot) {
+        const float w = __ldcg(&L.lt_val[sl].w);
+        s += M.vals ? w * M.vals[i] : w;
+      }
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+      const float y = M.y[row];
+      const float m = y * s;
+      loss += (double)log1pexp(-m);
+      L.coef[row] = -y / (1.f + __expf(m));
+      L.xw[row] = s;
+    }
+  }
+  if (lane == 0 && loss != 0.0) atomicAdd(&L.stats[0], loss);
+}
+
+__device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratch& L, size_t gwarp,
+                                           size_t nwarps, int lane) {
+  for (int64_t row = (int64_t)gwarp; row < M.rows; row += (int64_t)nwarps) {
+    const int64_t b = M.offsets[row], e = M.offsets[row + 1];
+    const float c = L.coef[row];
+    const unsigned long long inc = M.y[row] > 0.f ? (1ull << 32) : 1ull;
+    for (int64_t i = b + lane; i < e; i += 32) {
+      const uint32_t sl = L.slot_of[i];
+      if (sl != kBadSlot) {
+        atomicAdd(&L.lt_val[sl].g, M.vals ? c * M.vals[i] : c);
+        atomicAdd(&L.lt_val[sl].cnt, inc);
+      }
+    }
+  }
+}
+
+// Scan the local table, append every unique key's record to its owner's inbox
+// (segment of this sender) and empty the table for the next minibatch.
+__device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const LocalScratch& L, size_t gwarp,
+                                                 size_t nwarps, int lane) {
+  const uint64_t n = L.lt_mask + 1;
+  for (uint64_t s0 = gwarp * 32; s0 < n; s0 += nwarps * 32) {
+    const uint64_t s = s0 + lane;
+    const uint64_t key = s < n ? __ldcg(L.lt_keys + s) : kEmptyKey;
+    const bool occ = key != kEmptyKey;
+    const int o = occ ? route_owner(P.seps, key) : -1;
+    if (__ballot_sync(0xffffffffu, occ) == 0u) continue;
+    float g = 0.f;
+    uint64_t c = 0;
+    if (occ) {
+      g = __ldcg(&L.lt_val[s].g);
+      c = __ldcg(&L.lt_val[s].cnt);
+      L.lt_keys[s] = kEmptyKey;
+    }
+    for (int t = 0; t < P.seps.world; ++t) {
+      const unsigned m = __ballot_sync(0xffffffffu, o == t);
+      if (m == 0u) continue;
+      const int leader = __ffs(m) - 1;
+      uint32_t base = 0;
+      if (lane == leader) base = atomicAdd(L.send_cnt + t, (uint32_t)__popc(m));
+      base = __shfl_sync(0xffffffffu, base, leader);
+      if (o == t) {
+        const uint32_t idx = base + __popc(m & ((1u << lane) - 1u));
+        if (idx < P.in_cap) {
+          const size_t at = (size_t)P.rank * P.in_cap + idx;
+          P.in_keys[t][at] = key;
+          P.in_g[t][at] = g;
+          P.in_cnt[t][at] = c;
+        } else {
+          set_status(L.status, kInboxOverflow, (uint32_t)t, idx);
+        }
+      }
+    }
+  }
+  __threadfence_system();
+}
+
+__device__ __forceinline__ float ftrl_sqrt_n(float pos, float neg) {
+  const float all = pos + neg;
+  return all == 0.f ? 0.f : sqrtf(pos * neg / all);
+}
+
+// The reference's per-key server update (src/linear_method/ftrl_model.h:88-110).
+__device__ __forceinline__ void ftrl_update(ShardState& e, float g, uint32_t dpos, uint32_t dneg,
+                                            const FtrlHyper& h, float& dn1, float& dn2, int& dnnz) {
+  float sqrt_n, sqrt_n_new;
+  if (h.rule == 0) {
+    sqrt_n = ftrl_sqrt_n((float)e.pos, (float)e.neg);
+    e.pos += dpos;
+    e.neg += dneg;
+    sqrt_n_new = ftrl_sqrt_n((float)e.pos, (float)e.neg);
+  } else {
+    float n = __uint_as_float(e.pos);
+    sqrt_n = sqrtf(n);
+    n += g * g;
+    sqrt_n_new = sqrtf(n);
+    e.pos = __float_as_uint(n);
+    e.neg += dpos + dneg;
+  }
+  const float sigma = (sqrt_n_new - sqrt_n) / h.alpha;
+  e.z += g - sigma * e.w;
+  const float l2 = h.l2 + (h.beta + sqrt_n_new) / h.alpha;
+  const float w_old = e.w;
+  const float az = fabsf(e.z) - h.l1;
+  const float w = az > 0.f ? -copysignf(az, e.z) / l2 : 0.f;
+  e.w = w;
+  dn1 += fabsf(w) - fabsf(w_old);
+  dn2 += w * w - w_old * w_old;
+  dnnz += (w != 0.f && w_old == 0.f) - (w == 0.f && w_old != 0.f);
+}
+
+__device__ __forceinline__ void phase_apply(uint64_t* tkeys, ShardState* tstate, uint64_t mask, int max_probe,
+                                            const uint64_t* rk, const float* rg, const uint64_t* rc,
+                                            uint32_t n, const FtrlHyper& h, double* stats, uint32_t* status,
+                                            size_t gtid, size_t gsz) {
+  float dn1 = 0.f, dn2 = 0.f;
+  int dnnz = 0, dins = 0;
+  for (size_t i = gtid; i < n; i += gsz) {
+    const uint64_t key = __ldcg(rk + i);
+    if (key == kEmptyKey) continue;
+    const float g = __ldcg(rg + i);
+    const uint64_t c = __ldcg(rc + i);
+    uint64_t slot = shard_hash(key) & mask;
+    bool found = false;
+    for (int p = 0; p < max_probe; ++p) {
+      const uint64_t cur = tkeys[slot];
+      if (cur == key) { found = true; break; }
+      if (cur == kEmptyKey) {
+        const unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long*>(tkeys + slot),
+                                                  (unsigned long long)kEmptyKey, (unsigned long long)key);
+        if (prev == kEmptyKey) { found = true; ++dins; break; }
+        if (prev == key) { found = true; break; }
+      }
+      slot = (slot + 1) & mask;
+    }
+    if (!found) {
+      set_status(status, kShardTableFull, 0, 0);
+      continue;
+    }
+    float4 raw = *reinterpret_cast<float4*>(tstate + slot);
+    ShardState e;
+    e.w = raw.x; e.z = raw.y; e.pos = __float_as_uint(raw.z); e.neg = __float_as_uint(raw.w);
+    ftrl_update(e, g, (uint32_t)(c >> 32), (uint32_t)c, h, dn1, dn2, dnnz);
+    raw.x = e.w; raw.y = e.z; raw.z = __uint_as_float(e.pos); raw.w = __uint_as_float(e.neg);
+    *reinterpret_cast<float4*>(tstate + slot) = raw;
+  }
+  dn1 = warp_sum(dn1);
+  dn2 = warp_sum(dn2);
+  dnnz = __reduce_add_sync(0xffffffffu, dnnz);
+  dins = __reduce_add_sync(0xffffffffu, dins);
+  if ((threadIdx.x & 31) == 0) {
+    if (dn1 != 0.f) atomicAdd(stats + 2, (double)dn1);
+    if (dn2 != 0.f) atomicAdd(stats + 3, (double)dn2);
+    if (dnnz != 0) atomicAdd(stats + 4, (double)dnnz);
+    if (dins != 0) atomicAdd(stats + 6, (double)dins);
+  }
+}
+
+// ------------------------------------------------------------ fused kernels
+__global__ void __launch_bounds__(256)
+ftrl_pull_spmv_kernel(FtrlPeers P, Minibatch M, LocalScratch L, uint32_t epoch) {
+  cg::grid_group grid = cg::this_grid();
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t gsz = (size_t)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+
+  // every owner must have applied step epoch-1 before its table is read
+  if (blockIdx.x == 0 && threadIdx.x < P.seps.world) {
+    bool ok;
+    wait_epoch_ge(P.applied[P.rank] + threadIdx.x, epoch - 1, P.timeout_ns, &ok);
+    if (!ok) set_status(L.status, kWaitTimeout, threadIdx.x, 1);
+  }
+  if (gtid == 0) L.stats[1] += (double)M.rows;
+  phase_localize(M, L, P.max_probe, gtid, gsz);
+  grid.sync();
+  phase_gather(P, L, gtid, gsz);
+  grid.sync();
+  phase_spmv_loss(M, L, gtid >> 5, gsz >> 5, lane);
+}
+
+__global__ void __launch_bounds__(256)
+ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, uint32_t epoch) {
+  cg::grid_group grid = cg::this_grid();
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t gsz = (size_t)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const int world = P.seps.world;
+
+  phase_grad(M, L, gtid >> 5, gsz >> 5, lane);
+  grid.sync();
+  phase_route_send(P, L, gtid >> 5, gsz >> 5, lane);
+  grid.sync();
+  // publish this sender's record count to every owner, then wait for all senders
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    const int t = threadIdx.x;
+    uint32_t cnt = L.send_cnt[t];
+    if (cnt > P.in_cap) cnt = P.in_cap;
+    L.send_cnt[t] = 0;
+    __threadfence_system();
+    st_release_sys_u64(P.in_flag[t] + P.rank, ((uint64_t)epoch << 32) | cnt);
+    bool ok;
+    const uint64_t v = wait_epoch_ge(P.in_flag[P.rank] + t, epoch, P.timeout_ns, &ok);
+    L.recv_cnt[t] = ok ? (uint32_t)v : 0u;
+    if (!ok) set_status(L.status, kWaitTimeout, t, 2);
+  }
+  grid.sync();
+  // apply sender by sender (the reference applies each worker's push separately)
+  for (int s = 0; s < world; ++s) {
+    const uint32_t n = __ldcg(L.recv_cnt + s);
+    const size_t off = (size_t)s * P.in_cap;
+    phase_apply(P.tab_keys[P.rank], P.tab_state[P.rank], P.tab_mask, P.max_probe,
+                P.in_keys[P.rank] + off, P.in_g[P.rank] + off, P.in_cnt[P.rank] + off, n, H, L.stats,
+                L.status, gtid, gsz);
+    grid.sync();
+  }
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys_u64(P.applied[threadIdx.x] + P.rank, (uint64_t)epoch << 32);
+  }
+}
+
+// ------------------------------------------------- stand-alone phase kernels
+__global__ void k_localize(Minibatch M, LocalScratch L, int max_probe) {
+  phase_localize(M, L, max_probe, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+}
+__global__ void k_spmv_loss(Minibatch M, LocalScratch L) {
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gtid == 0) L.stats[1] += (double)M.rows;
+  phase_spmv_loss(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31);
+}
+__global__ void k_grad(Minibatch M, LocalScratch L) {
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  phase_grad(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31);
+}
+// count unique keys per owner (pass 1 of packing for all_to_all_v)
+__global__ void k_count_owner(KeySeps seps, LocalScratch L, uint32_t* counts) {
+  const size_t gsz = (size_t)gridDim.x * blockDim.x;
+  uint32_t c[PSB_MAX_RANKS] = {0};
+  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += gsz) {
+    const uint64_t key = L.lt_keys[s];
+    if (key != kEmptyKey) {
+      const int o = route_owner(seps, key);
+#pragma unroll
+      for (int t = 0; t < PSB_MAX_RANKS; ++t) c[t] += (o == t);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < PSB_MAX_RANKS; ++t) {
+    const uint32_t v = __reduce_add_sync(0xffffffffu, c[t]);
+    if ((threadIdx.x & 31) == 0 && v) atomicAdd(counts + t, v);
+  }
+}
+// pass 2: write (key, slot) grouped by owner; cursors[] start at the segment bases
+__global__ void k_pack_keys(KeySeps seps, LocalScratch L, uint32_t* cursors, uint64_t* out_keys,
+                            uint32_t* out_slot) {
+  const size_t gsz = (size_t)gridDim.x * blockDim.x;
+  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += gsz) {
+    const uint64_t key = L.lt_keys[s];
+    if (key != kEmptyKey) {
+      const uint32_t at = atomicAdd(cursors + route_owner(seps, key), 1u);
+      out_keys[at] = key;
+      out_slot[at] = (uint32_t)s;
+    }
+  }
+}
+// owner side of an unfused pull: w for each requested key (0 when absent)
+__global__ void k_lookup(const uint64_t* tkeys, const ShardState* tstate, uint64_t mask, int max_probe,
+                         const uint64_t* keys, uint32_t n, float* out_w) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out_w[i] = probe_weight(tkeys, tstate, mask, keys[i], max_probe);
+}
+__global__ void k_scatter_w(const uint32_t* slots, const float* w, uint32_t n, LocalScratch L) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t s = slots[i];
+    LocalSlot v;
+    v.w = w[i];
+    v.g = 0.f;
+    v.cnt = 0ull;
+    L.lt_val[s] = v;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) L.stats[5] += (double)n;
+}
+__global__ void k_pack_push(const uint32_t* slots, uint32_t n, LocalScratch L, float* out_g, uint64_t* out_cnt) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t s = slots[i];
+    out_g[i] = L.lt_val[s].g;
+    out_cnt[i] = L.lt_val[s].cnt;
+    L.lt_keys[s] = kEmptyKey;
+  }
+}
+__global__ void k_apply(uint64_t* tkeys, ShardState* tstate, uint64_t mask, int max_probe, const uint64_t* rk,
+                        const float* rg, const uint64_t* rc, uint32_t n, FtrlHyper h, double* stats,
+                        uint32_t* status) {
+  phase_apply(tkeys, tstate, mask, max_probe, rk, rg, rc, n, h, stats, status,
+              (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+}
+__global__ void k_clear_local(LocalScratch L) {
+  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += (size_t)gridDim.x * blockDim.x)
+    L.lt_keys[s] = kEmptyKey;
+}
+// dump the non-zero weights of a shard: out_keys/out_w sized by capacity, *count receives the number
+__global__ void k_dump_nonzero(const uint64_t* tkeys, const ShardState* tstate, uint64_t mask, uint64_t* out_keys,
+                               float* out_w, unsigned long long* count) {
+  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= mask; s += (size_t)gridDim.x * blockDim.x) {
+    const uint64_t k = tkeys[s];
+    if (k != kEmptyKey && tstate[s].w != 0.f) {
+      const unsigned long long at = atomicAdd(count, 1ull);
+      out_keys[at] = k;
+      out_w[at] = tstate[s].w;
+    }
+  }
+}
+
+}  // namespace psb
+
+// ------------------------------------------------------------------ C ABI
+using namespace psb;
+
+namespace {
+int g_coop_blocks_pull[16] = {0}, g_coop_blocks_push[16] = {0};
+
+template <typename K>
+int coop_grid(K kernel, int* cache) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) dev = 0;
+  if (cache[dev] == 0) {
+    int per_sm = 0, sms = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (per_sm > 4) per_sm = 4;
+    cache[dev] = per_sm * sms;
+  }
+  return cache[dev];
+}
+inline int flat_grid(size_t n, int cap = 148 * 8) {
+  size_t b = (n + 255) / 256;
+  if (b < 1) b = 1;
+  if (b > (size_t)cap) b = cap;
+  return (int)b;
+}
+}  // namespace
+
+extern "C" {
+
+int psb_ftrl_pull_spmv(const FtrlPeers* P, const Minibatch* M, const LocalScratch* L, uint32_t epoch,
+                       cudaStream_t stream) {
+  const int grid = coop_grid(ftrl_pull_spmv_kernel, g_coop_blocks_pull);
+  if (grid <= 0) return (int)cudaErrorLaunchFailure;
+  FtrlPeers p = *P; Minibatch m = *M; LocalScratch l = *L;
+  void* args[] = {&p, &m, &l, &epoch};
+  return (int)cudaLaunchCooperativeKernel((void*)ftrl_pull_spmv_kernel, dim3(grid), dim3(256), args, 0, stream);
+}
+
+int psb_ftrl_push_update(const FtrlPeers* P, const Minibatch* M, const LocalScratch* L, const FtrlHyper* H,
+                         uint32_t epoch, cudaStream_t stream) {
+  const int grid = coop_grid(ftrl_push_update_kernel, g_coop_blocks_push);
+  if (grid <= 0) return (int)cudaErrorLaunchFailure;
+  FtrlPeers p = *P; Minibatch m = *M; LocalScratch l = *L; FtrlHyper h = *H;
+  void* args[] = {&p, &m, &l, &h, &epoch};
+  return (int)cudaLaunchCooperativeKernel((void*)ftrl_push_update_kernel, dim3(grid), dim3(256), args, 0, stream);
+}
+
+int psb_ftrl_localize(const Minibatch* M, const LocalScratch* L, int max_probe, cudaStream_t s) {
+  k_localize<<<flat_grid(M->nnz), 256, 0, s>>>(*M, *L, max_probe);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_spmv_loss(const Minibatch* M, const LocalScratch* L, cudaStream_t s) {
+  k_spmv_loss<<<flat_grid((size_t)M->rows * 32), 256, 0, s>>>(*M, *L);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_grad(const Minibatch* M, const LocalScratch* L, cudaStream_t s) {
+  k_grad<<<flat_grid((size_t)M->rows * 32), 256, 0, s>>>(*M, *L);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_count_owner(const KeySeps* seps, const LocalScratch* L, uint32_t* counts, cudaStream_t s) {
+  k_count_owner<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*seps, *L, counts);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_pack_keys(const KeySeps* seps, const LocalScratch* L, uint32_t* cursors, uint64_t* out_keys,
+                       uint32_t* out_slot, cudaStream_t s) {
+  k_pack_keys<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*seps, *L, cursors, out_keys, out_slot);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_lookup(const uint64_t* tkeys, const void* tstate, uint64_t mask, int max_probe, const uint64_t* keys,
+                    uint32_t n, float* out_w, cudaStream_t s) {
+  k_lookup<<<flat_grid(n), 256, 0, s>>>(tkeys, (const ShardState*)tstate, mask, max_probe, keys, n, out_w);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_scatter_w(const uint32_t* slots, const float* w, uint32_t n, const LocalScratch* L, cudaStream_t s) {
+  k_scatter_w<<<flat_grid(n), 256, 0, s>>>(slots, w, n, *L);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_pack_push(const uint32_t* slots, uint32_t n, const LocalScratch* L, float* out_g, uint64_t* out_cnt,
+                       cudaStream_t s) {
+  k_pack_push<<<flat_grid(n), 256, 0, s>>>(slots, n, *L, out_g, out_cnt);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_apply(uint64_t* tkeys, void* tstate, uint64_t mask, int max_probe, const uint64_t* rk, const float* rg,
+                   const uint64_t* rc, uint32_t n, const FtrlHyper* h, double* stats, uint32_t* status,
+                   cudaStream_t s) {
+  k_apply<<<flat_grid(n), 256, 0, s>>>(tkeys, (ShardState*)tstate, mask, max_probe, rk, rg, rc, n, *h, stats, status);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_clear_local(const LocalScratch* L, cudaStream_t s) {
+  k_clear_local<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*L);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_dump_nonzero(const uint64_t* tkeys, const void* tstate, uint64_t mask, uint64_t* out_keys, float* out_w,
+                          unsigned long long* count, cudaStream_t s) {
+  k_dump_nonzero<<<flat_grid(mask + 1), 256, 0, s>>>(tkeys, (const ShardState*)tstate, mask, out_keys, out_w, count);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

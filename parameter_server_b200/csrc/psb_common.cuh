@@ -1,0 +1,149 @@
+// Shared device-side primitives for the sm_100a kernels of this library:
+// system-scope loads/stores used on peer (NVLink) memory, bounded flag waits,
+// the 64-bit mixer used by every hash table, warp helpers and the status word.
+//
+// Conventions
+//  * A "rank" is one GPU that hosts worker r and server (key-range shard) r.
+//  * Cross-GPU waits never spin forever: they give up after `timeout_ns`
+//    (and an iteration cap), record {code, peer, phase} in the status word and
+//    let the kernel run to its end so that the context stays usable.
+//  * kEmptyKey (2^64-1) is never a valid key; the reference's key space
+//    Range::all() = [0, 2^64-1) excludes it as well (src/base/range.h:75-78).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
+#define PSB_MAX_RANKS 8
+#define PSB_WARP 32
+
+namespace psb {
+
+constexpr uint64_t kEmptyKey = 0xFFFFFFFFFFFFFFFFull;
+
+// status word layout (uint32_t[8], owned by the caller, zeroed by the caller)
+enum StatusCode : uint32_t {
+  kOk = 0,
+  kWaitTimeout = 1,      // a bounded cross-GPU wait ran out
+  kLocalTableFull = 2,   // per-minibatch dedup table overflow
+  kShardTableFull = 3,   // owner hash table probe limit reached
+  kInboxOverflow = 4,    // more records for one owner than the inbox holds
+  kBadIndex = 5,         // an index failed its bounds check and was skipped
+};
+
+__device__ __forceinline__ void set_status(uint32_t* status, uint32_t code, uint32_t a, uint32_t b) {
+  if (atomicCAS(&status[0], 0u, code) == 0u) {
+    status[1] = a;
+    status[2] = b;
+  }
+}
+
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {
+  x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
+  x ^= x >> 27; x *= 0x94d049bb133111ebull;
+  x ^= x >> 31;
+  return x;
+}
+
+// ---- system-scope memory operations (peer memory over NVLink / NVSwitch) ----
+__device__ __forceinline__ uint64_t ld_relaxed_sys_u64(const uint64_t* p) {
+  uint64_t v; asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
+  uint32_t v; asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
+  float v; asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ uint64_t ld_acquire_sys_u64(const uint64_t* p) {
+  uint64_t v; asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ void st_release_sys_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_f32(float* p, float v) {
+  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" :: "l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_sys_f32(float* p, float v) {
+  asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" :: "l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
+}
+
+// Wait until (*flag >> 32) >= want_epoch, at most timeout_ns. Returns the flag
+// value on success; on timeout sets *ok=false and returns the last value seen.
+__device__ __forceinline__ uint64_t wait_epoch_ge(const uint64_t* flag, uint32_t want_epoch,
+                                                  uint64_t timeout_ns, bool* ok) {
+  const uint64_t t0 = globaltimer_ns();
+  const uint64_t max_iters = timeout_ns / 32 + 1024;
+  uint64_t v = 0;
+  for (uint64_t it = 0; it < max_iters; ++it) {
+    v = ld_acquire_sys_u64(flag);
+    if ((uint32_t)(v >> 32) >= want_epoch) { *ok = true; return v; }
+    if ((it & 63) == 63 && globaltimer_ns() - t0 > timeout_ns) break;
+    __nanosleep(40);
+  }
+  *ok = false;
+  return v;
+}
+
+// ---- key-range routing (≤ 8 separators, kept in kernel-parameter space) ----
+struct KeySeps {
+  uint64_t sep[PSB_MAX_RANKS + 1];  // owner s holds keys in [sep[s], sep[s+1])
+  int world;
+};
+__device__ __forceinline__ int route_owner(const KeySeps& s, uint64_t key) {
+  int o = 0;
+#pragma unroll
+  for (int i = 1; i < PSB_MAX_RANKS; ++i) o += (i < s.world && key >= s.sep[i]) ? 1 : 0;
+  return o;
+}
+
+// ---- warp helpers ----
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- open-addressing u64 set/map probes ----
+// insert-or-find in a local (same GPU) table; returns slot or ~0ull when the
+// probe limit is hit.
+__device__ __forceinline__ uint64_t table_find_or_insert(uint64_t* keys, uint64_t mask, uint64_t h,
+                                                        uint64_t key, int max_probe) {
+  uint64_t slot = h & mask;
+  for (int i = 0; i < max_probe; ++i) {
+    uint64_t cur = keys[slot];
+    if (cur == key) return slot;
+    if (cur == kEmptyKey) {
+      unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long*>(keys + slot),
+                                          (unsigned long long)kEmptyKey, (unsigned long long)key);
+      if (prev == kEmptyKey || prev == key) return slot;
+    }
+    slot = (slot + 1) & mask;
+  }
+  return ~0ull;
+}
+
+// numerically safe log(1+exp(x))
+__device__ __forceinline__ float log1pexp(float x) {
+  return x > 0.f ? x + log1pf(__expf(-x)) : log1pf(__expf(x));
+}
+
+}  // namespace psb

@@ -1,0 +1,113 @@
+"""Streaming driver for online FTRL: host-resident minibatches → device steps → per-step loss.
+
+This is the user-facing loop of the FTRL app (the reference's reader thread + bounded
+``data_buf_`` + minibatch loop, src/linear_method/ftrl.cc:74-151).  Minibatches live in pinned
+host memory; each is uploaded with ``cudaMemcpyAsync`` on a side stream into one of two device
+staging buffers while the previous step computes, and each step's loss sum is read back to the
+host (device→host copy into pinned memory) one step behind the compute stream.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Iterable, Iterator, List, Optional
+
+import torch
+
+from .ftrl import DeviceMinibatch, FTRLEngine
+
+
+@dataclass
+class HostMinibatch:
+    """CSR minibatch in (preferably pinned) host memory; keys are uint64 bit patterns in int64."""
+    offsets: torch.Tensor
+    keys: torch.Tensor
+    y: torch.Tensor
+    vals: Optional[torch.Tensor] = None
+
+    def pin(self) -> "HostMinibatch":
+        f = lambda t: None if t is None else (t if t.is_pinned() else t.pin_memory())
+        return HostMinibatch(f(self.offsets), f(self.keys), f(self.y), f(self.vals))
+
+    def nbytes(self) -> int:
+        n = self.offsets.numel() * 8 + self.keys.numel() * 8 + self.y.numel() * 4
+        return n + (self.vals.numel() * 4 if self.vals is not None else 0)
+
+
+class _Staging:
+    def __init__(self, eng: FTRLEngine, with_vals: bool):
+        d = eng.dev
+        self.offsets = torch.empty((eng.max_rows + 1,), dtype=torch.int64, device=d)
+        self.keys = torch.empty((eng.max_nnz,), dtype=torch.int64, device=d)
+        self.y = torch.empty((eng.max_rows,), dtype=torch.float32, device=d)
+        self.vals = torch.empty((eng.max_nnz,), dtype=torch.float32, device=d) if with_vals else None
+        self.ready = torch.cuda.Event()
+        self.free = torch.cuda.Event()
+
+    def upload(self, hb: HostMinibatch) -> DeviceMinibatch:
+        r, n = hb.y.numel(), hb.keys.numel()
+        self.offsets[: r + 1].copy_(hb.offsets, non_blocking=True)
+        self.keys[:n].copy_(hb.keys, non_blocking=True)
+        self.y[:r].copy_(hb.y, non_blocking=True)
+        v = None
+        if hb.vals is not None:
+            self.vals[:n].copy_(hb.vals, non_blocking=True)
+            v = self.vals[:n]
+        return DeviceMinibatch(self.offsets[: r + 1], self.keys[:n], self.y[:r], v)
+
+
+class FTRLTrainer:
+    """Double-buffered host→device streaming around :class:`FTRLEngine`."""
+
+    def __init__(self, engine: FTRLEngine, with_vals: bool = False, depth: int = 2):
+        self.eng = engine
+        self.copy_stream = torch.cuda.Stream(device=engine.dev)
+        self.stages = [_Staging(engine, with_vals) for _ in range(depth)]
+        self.loss_host = torch.zeros((depth, 2), dtype=torch.float64).pin_memory()
+        self.loss_events = [torch.cuda.Event() for _ in range(depth)]
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def train(self, batches: Iterable[HostMinibatch]) -> List[float]:
+        """Run one step per minibatch; returns the mean logistic loss of every step."""
+        eng, depth = self.eng, len(self.stages)
+        compute = torch.cuda.current_stream(eng.dev)
+        it: Iterator[HostMinibatch] = iter(batches)
+        losses: List[float] = []
+        pending: List[int] = []
+
+        def upload(i: int, hb: HostMinibatch) -> DeviceMinibatch:
+            st = self.stages[i % depth]
+            with torch.cuda.stream(self.copy_stream):
+                self.copy_stream.wait_event(st.free)   # the step that last used this buffer is done
+                mb = st.upload(hb)
+                st.ready.record(self.copy_stream)
+            self.h2d_bytes += hb.nbytes()
+            return mb
+
+        def collect(j: int) -> None:
+            self.loss_events[j % depth].synchronize()
+            s, r = self.loss_host[j % depth].tolist()
+            losses.append(s / max(r, 1.0))
+
+        nxt = next(it, None)
+        i = 0
+        cur = upload(0, nxt) if nxt is not None else None
+        while cur is not None:
+            nxt = next(it, None)
+            nxt_dev = upload(i + 1, nxt) if nxt is not None else None
+            st = self.stages[i % depth]
+            compute.wait_event(st.ready)
+            if len(pending) >= depth:
+                collect(pending.pop(0))
+            eng.stats[0:2].zero_()
+            eng.step(cur)
+            st.free.record(compute)
+            self.loss_host[i % depth].copy_(eng.stats[0:2], non_blocking=True)
+            self.loss_events[i % depth].record(compute)
+            self.d2h_bytes += 16
+            pending.append(i)
+            cur, i = nxt_dev, i + 1
+        for j in pending:
+            collect(j)
+        eng.check_status()
+        return losses

@@ -1,0 +1,87 @@
+"""ctypes binding of ``libpsb_kernels.so`` (the sm_100a kernels, C ABI).
+
+The library is built in-tree by :mod:`parameter_server_b200.utils.build`; it is
+loaded lazily so that CPU-only code paths (config parsing, the host runtime, the
+fp64 oracle) import without CUDA.  On a machine with a GPU a missing library is
+an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+from ..utils import build as _build
+
+MAX_RANKS = 8
+EMPTY_KEY = 0xFFFFFFFFFFFFFFFF
+
+_lib = None
+_lock = threading.Lock()
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "bounded cross-GPU wait timed out",
+    2: "per-minibatch dedup table full",
+    3: "shard hash table full (probe limit)",
+    4: "inbox overflow",
+    5: "index out of bounds (skipped)",
+}
+
+
+class KeySeps(C.Structure):
+    _fields_ = [("sep", C.c_uint64 * (MAX_RANKS + 1)), ("world", C.c_int)]
+
+
+class FtrlHyper(C.Structure):
+    _fields_ = [("alpha", C.c_float), ("beta", C.c_float), ("l1", C.c_float), ("l2", C.c_float),
+                ("rule", C.c_int), ("pad", C.c_int)]
+
+
+_P8 = C.c_void_p * MAX_RANKS
+
+
+class FtrlPeers(C.Structure):
+    _fields_ = [("seps", KeySeps), ("rank", C.c_int), ("max_probe", C.c_int), ("tab_mask", C.c_uint64),
+                ("tab_keys", _P8), ("tab_state", _P8), ("in_keys", _P8), ("in_g", _P8), ("in_cnt", _P8),
+                ("in_flag", _P8), ("applied", _P8), ("timeout_ns", C.c_uint64), ("in_cap", C.c_uint32),
+                ("pad", C.c_uint32)]
+
+
+class Minibatch(C.Structure):
+    _fields_ = [("offsets", C.c_void_p), ("keys", C.c_void_p), ("vals", C.c_void_p), ("y", C.c_void_p),
+                ("nnz", C.c_int64), ("rows", C.c_int), ("pad", C.c_int)]
+
+
+class LocalScratch(C.Structure):
+    _fields_ = [("lt_keys", C.c_void_p), ("lt_val", C.c_void_p),
+                ("lt_mask", C.c_uint64), ("slot_of", C.c_void_p), ("coef", C.c_void_p), ("xw", C.c_void_p),
+                ("send_cnt", C.c_void_p), ("recv_cnt", C.c_void_p), ("stats", C.c_void_p),
+                ("status", C.c_void_p)]
+
+
+def lib() -> C.CDLL:
+    """Load (building first if needed) the kernel library."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = _build.kernels_lib_path()
+                if not path.exists():
+                    _build.build_kernels()
+                _lib = C.CDLL(str(path))
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what}: CUDA error {code}")
+
+
+def stream_ptr() -> C.c_void_p:
+    import torch
+
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())

@@ -1,0 +1,140 @@
+"""In-tree build of the native libraries.
+
+Two shared objects are produced next to the sources, under ``parameter_server_b200/lib``:
+
+* ``libpsb_kernels.so`` — every CUDA kernel, compiled for sm_100a only
+  (``-gencode arch=compute_100a,code=sm_100a``), exported through a C ABI and
+  loaded with ctypes.  No torch headers are involved, so a full rebuild takes
+  seconds and nvcc cross-compiles on a machine without a GPU.
+* ``_psb_host*.so`` — the host runtime (control-plane van, executor, parsers,
+  slot reader, ...) as a pybind11 module compiled with g++.
+
+Objects are rebuilt only when a source or header is newer than the object.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent.parent
+CSRC = PKG / "csrc"
+HOST = PKG / "csrc" / "host"
+LIB = PKG / "lib"
+OBJ = LIB / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wall", "-Wno-sign-compare"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _newer(src_paths, target: Path) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(p.stat().st_mtime > t for p in src_paths)
+
+
+def _run(cmd, log: Path | None = None):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if log is not None:
+        log.write_text(" ".join(map(str, cmd)) + "\n" + r.stdout + r.stderr)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("build failed: " + " ".join(map(str, cmd)))
+    return r
+
+
+def kernels_lib_path() -> Path:
+    return LIB / "libpsb_kernels.so"
+
+
+def host_lib_path() -> Path:
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return LIB / ("_psb_host" + suffix)
+
+
+def extra_include_dirs() -> list[str]:
+    """CUTLASS/CuTe header trees vendored inside site-packages (used by the GEMM kernels)."""
+    out = []
+    for p in sys.path:
+        cand = Path(p) / "flashinfer" / "data" / "cutlass" / "include"
+        if cand.is_dir():
+            out.append(str(cand))
+            break
+    return out
+
+
+def build_kernels(force: bool = False, verbose: bool = False) -> Path:
+    LIB.mkdir(exist_ok=True)
+    OBJ.mkdir(exist_ok=True)
+    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    sources = sorted(CSRC.glob("*.cu"))
+    nvcc = _nvcc()
+    jobs = []
+    for src in sources:
+        obj = OBJ / (src.stem + ".o")
+        if force or _newer([src] + headers, obj):
+            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC)]
+            cmd += ["-c", str(src), "-o", str(obj)]
+            jobs.append((cmd, OBJ / (src.stem + ".log")))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for r in ex.map(lambda j: _run(*j), jobs):
+                if verbose:
+                    sys.stderr.write(r.stderr)
+    objs = [OBJ / (s.stem + ".o") for s in sources]
+    out = kernels_lib_path()
+    if force or jobs or _newer(objs, out):
+        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-lcudart", "-lcuda"])
+    return out
+
+
+def build_host(force: bool = False) -> Path | None:
+    if not HOST.is_dir():
+        return None
+    sources = sorted(HOST.glob("*.cc"))
+    if not sources:
+        return None
+    import pybind11
+
+    LIB.mkdir(exist_ok=True)
+    OBJ.mkdir(exist_ok=True)
+    headers = list(HOST.glob("*.h"))
+    inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(HOST)]
+    jobs = []
+    for src in sources:
+        obj = OBJ / ("host_" + src.stem + ".o")
+        if force or _newer([src] + headers, obj):
+            jobs.append(([os.environ.get("CXX", "g++"), *CXX_FLAGS, *inc, "-c", str(src), "-o", str(obj)], None))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(lambda j: _run(*j), jobs))
+    objs = [OBJ / ("host_" + s.stem + ".o") for s in sources]
+    out = host_lib_path()
+    if force or jobs or _newer(objs, out):
+        _run([os.environ.get("CXX", "g++"), "-shared", "-o", str(out), *map(str, objs), "-pthread", "-lz"])
+    return out
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    k = build_kernels(force=force, verbose=verbose)
+    h = build_host(force=force)
+    return k, h
+
+
+if __name__ == "__main__":
+    print(build_all(force="--force" in sys.argv, verbose=True))

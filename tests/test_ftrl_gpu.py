@@ -1,0 +1,102 @@
+"""FTRL fused kernels on one GPU against the fp64 CPU restatement of the reference."""
+import numpy as np
+import pytest
+import torch
+
+from baseline.cpu_ref.ftrl_ref import FTRLRef
+from parameter_server_b200.data.synthetic import ctr_minibatch
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(impl="fused", rule="count", **kw):
+    from parameter_server_b200.models.ftrl import FTRLEngine, FTRLHyper
+    from parameter_server_b200.parallel.peer import PeerGroup
+
+    hyper = FTRLHyper(alpha=0.02, beta=1.0, lambda1=0.05, lambda2=0.1, rule=rule)
+    args = dict(table_capacity=1 << 16, max_rows=4096, max_nnz=1 << 19, local_capacity=1 << 16)
+    args.update(kw)
+    return FTRLEngine(PeerGroup.single(torch.device("cuda", 0)), hyper, impl=impl, **args), hyper
+
+
+def _batches(n, rows=700, log2=13):
+    return [ctr_minibatch(rows, seed=100 + i, device="cuda", key_space_log2=log2, bias=-0.5, wstar_frac=0.2,
+                          wstar_std=1.0) for i in range(n)]
+
+
+@pytest.mark.parametrize("impl,rule", [("fused", "count"), ("fused", "sumsq"), ("nccl", "count")])
+def test_ftrl_matches_oracle(impl, rule):
+    from parameter_server_b200.models.ftrl import DeviceMinibatch
+
+    eng, hy = _engine(impl, rule)
+    ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2, rule)
+    for off, keys, y in _batches(6):
+        eng.step(DeviceMinibatch(off, keys, y))
+        st = eng.read_stats()
+        eng.check_status()
+        loss = ref.step([(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64), y.cpu().numpy().astype(np.float64))])
+        assert st["rows"] == y.numel()
+        assert st["loss_sum"] == pytest.approx(loss, rel=2e-4)
+    k, w = eng.dump_model()
+    rk, rw = ref.nonzero()
+    assert len(rk) > 50
+    assert np.array_equal(k, rk)
+    np.testing.assert_allclose(w, rw, rtol=2e-3, atol=2e-5)
+    st = eng.read_stats(reset=False)
+    assert st["nnz_w"] == ref.nnz
+    assert st["norm1"] == pytest.approx(ref.norm1, rel=1e-3)
+    assert st["table_entries"] == len(ref.model)
+    assert eng.penalty(st) == pytest.approx(ref.objv(), rel=1e-3)
+
+
+def test_ftrl_valued_features_and_predict():
+    from parameter_server_b200.models.ftrl import DeviceMinibatch
+
+    eng, hy = _engine()
+    ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for off, keys, y in _batches(4, rows=300, log2=10):
+        vals = torch.rand(keys.numel(), generator=g, device="cuda") + 0.5
+        eng.step(DeviceMinibatch(off, keys, y, vals))
+        ref.step([(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64), y.cpu().numpy().astype(np.float64),
+                   vals.cpu().numpy())])
+    off, keys, y = _batches(1, rows=200, log2=10)[0]
+    xw = eng.predict(DeviceMinibatch(off, keys, y)).cpu().numpy()
+    _, _, _, _, _, rxw = ref.worker_gradient(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64),
+                                             y.cpu().numpy().astype(np.float64))
+    np.testing.assert_allclose(xw, rxw, rtol=2e-3, atol=2e-4)
+    # predict leaves training state untouched: one more step still matches
+    eng.step(DeviceMinibatch(off, keys, y))
+    ref.step([(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64), y.cpu().numpy().astype(np.float64))])
+    k, w = eng.dump_model()
+    rk, rw = ref.nonzero()
+    assert np.array_equal(k, rk)
+    np.testing.assert_allclose(w, rw, rtol=2e-3, atol=2e-5)
+    eng.check_status()
+
+
+def test_ftrl_reports_local_table_overflow():
+    from parameter_server_b200.models.ftrl import DeviceMinibatch
+
+    eng, _ = _engine(local_capacity=256, max_probe=64)
+    off, keys, y = _batches(1, rows=200)[0]
+    eng.step(DeviceMinibatch(off, keys, y))
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="dedup table full"):
+        eng.check_status()
+
+
+def test_model_text_dump(tmp_path):
+    from parameter_server_b200.models.ftrl import DeviceMinibatch
+    from parameter_server_b200.utils.modelio import read_model_text
+
+    eng, _ = _engine()
+    for off, keys, y in _batches(3):
+        eng.step(DeviceMinibatch(off, keys, y))
+    path = eng.save_model(str(tmp_path / "ftrl"))
+    assert path.endswith("_S0")
+    k, w = eng.dump_model()
+    m = read_model_text(path)
+    assert len(m) == len(k)
+    for kk, ww in zip(k[:50], w[:50]):
+        assert m[int(kk)] == pytest.approx(float(ww), rel=1e-5)
