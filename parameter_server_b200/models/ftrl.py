@@ -179,8 +179,12 @@ class FTRLEngine:
         """
         M, s = self._mb(mb), N.stream_ptr()
         saved = self.stats.clone()
-        N.check(self._lib.psb_ftrl_pull_spmv(C.byref(self._P), C.byref(M), C.byref(self._L),
-                                             C.c_uint32(self.epoch + 1), s), "ftrl_pull_spmv")
+        if self.impl == "nccl":
+            self.group.barrier()   # every owner's last apply kernel has finished
+            self._pull_nccl(M)
+        else:
+            N.check(self._lib.psb_ftrl_pull_spmv(C.byref(self._P), C.byref(M), C.byref(self._L),
+                                                 C.c_uint32(self.epoch + 1), s), "ftrl_pull_spmv")
         N.check(self._lib.psb_ftrl_clear_local(C.byref(self._L), s), "clear_local")
         self.kernel_launches += 2
         out = self.xw[: mb.rows].clone()
@@ -189,10 +193,16 @@ class FTRLEngine:
 
     # ------------------------------------------------------- NCCL-only baseline
     def _step_nccl(self, mb: DeviceMinibatch) -> None:
+        self.epoch += 1
+        M = self._mb(mb)
+        ctx = self._pull_nccl(M)
+        self._push_nccl(M, *ctx)
+
+    def _pull_nccl(self, M):
+        """Unfused pull: localize, pack unique keys by owner, all_to_all keys, lookup, all_to_all weights, SpMV."""
         import torch.distributed as dist
 
-        self.epoch += 1
-        lib, L, M, s = self._lib, self._L, self._mb(mb), N.stream_ptr()
+        lib, L, s = self._lib, self._L, N.stream_ptr()
         W = self.group.world
         N.check(lib.psb_ftrl_localize(C.byref(M), C.byref(L), self._P.max_probe, s), "localize")
         self._counts.zero_()
@@ -230,13 +240,22 @@ class FTRLEngine:
         if total:
             N.check(lib.psb_ftrl_scatter_w(N.ptr(self._u_slot), N.ptr(uw), C.c_uint32(total), C.byref(L), s), "scatter_w")
         N.check(lib.psb_ftrl_spmv_loss(C.byref(M), C.byref(L), s), "spmv_loss")
+        self.kernel_launches += 2
+        return counts, in_counts, rkeys
+
+    def _push_nccl(self, M, counts, in_counts, rkeys) -> None:
+        """Unfused push: gradient, pack by owner, all_to_all (g, counts), owner update sender by sender."""
+        import torch.distributed as dist
+
+        lib, L, s = self._lib, self._L, N.stream_ptr()
+        W, total, nr = self.group.world, sum(counts), rkeys.numel()
         N.check(lib.psb_ftrl_grad(C.byref(M), C.byref(L), s), "grad")
         ug = torch.empty((total,), dtype=torch.float32, device=self.dev)
         uc = torch.empty((total,), dtype=torch.int64, device=self.dev)
         if total:
             N.check(lib.psb_ftrl_pack_push(N.ptr(self._u_slot), C.c_uint32(total), C.byref(L), N.ptr(ug), N.ptr(uc), s),
                     "pack_push")
-        self.kernel_launches += 4
+        self.kernel_launches += 2
         if W > 1:
             rg = torch.empty((nr,), dtype=torch.float32, device=self.dev)
             rc = torch.empty((nr,), dtype=torch.int64, device=self.dev)
@@ -244,7 +263,6 @@ class FTRLEngine:
             dist.all_to_all_single(rc, uc, in_counts, counts, group=self.group.group)
         else:
             rg, rc = ug, uc
-        # apply sender by sender, like the fused path
         off = 0
         for n in in_counts:
             if n:
