@@ -112,7 +112,7 @@ def run_ftrl(args) -> dict:
         off, keys, y = ctr_minibatch(rows, seed=1000 * rank + i + 1, device=dev)
         batches.append(DeviceMinibatch(off, keys, y))
     max_nnz = max(b.nnz for b in batches)
-    eng = FTRLEngine(group, FTRLHyper(alpha=0.1, beta=1.0, lambda1=1.0, lambda2=0.1),
+    eng = FTRLEngine(group, FTRLHyper(alpha=0.1, beta=1.0, lambda1=1.0, lambda2=0.1, rule=args.rule),
                      table_capacity=1 << args.table_log2, max_rows=rows, max_nnz=max_nnz,
                      local_capacity=1 << args.local_log2, timeout_s=args.timeout_s,
                      impl="nccl" if args.impl == "nccl" else "fused")
@@ -137,20 +137,26 @@ def run_ftrl(args) -> dict:
     st = eng.read_stats()
     eng.check_status()
     # ---------------------------------------------------------------- end to end (public API)
-    host = [HostMinibatch(b.offsets.cpu(), b.keys.cpu(), b.y.cpu()).pin() for b in batches]
-    trainer = FTRLTrainer(eng)
-    trainer.train(host[i % ring] for i in range(max(3, args.warmup)))
-    group.barrier()
-    trainer.h2d_bytes = trainer.d2h_bytes = 0
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    losses = trainer.train(host[i % ring] for i in range(args.steps))
-    t1.record()
-    torch.cuda.synchronize(dev)
-    e2e_ms = group.all_reduce_max(t0.elapsed_time(t1))
+    ex_per_step = rows * world
+    e2e = None
+    if not args.no_e2e:
+        host = [HostMinibatch(b.offsets.cpu(), b.keys.cpu(), b.y.cpu()).pin() for b in batches]
+        trainer = FTRLTrainer(eng)
+        trainer.train(host[i % ring] for i in range(max(3, args.warmup)))
+        group.barrier()
+        trainer.h2d_bytes = trainer.d2h_bytes = 0
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        losses = trainer.train(host[i % ring] for i in range(args.steps))
+        t1.record()
+        torch.cuda.synchronize(dev)
+        e2e_ms = group.all_reduce_max(t0.elapsed_time(t1))
+        e2e = {"value": ex_per_step * args.steps / (e2e_ms / 1e3), "unit": "examples/s",
+               "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": trainer.h2d_bytes // args.steps,
+               "d2h_bytes_per_step": trainer.d2h_bytes // args.steps,
+               "mean_logloss_last": losses[-1] if losses else None}
     clocks = sampler.stop()
     group.barrier()
-    ex_per_step = rows * world
     return {
         "metric": "examples/sec (online FTRL-proximal L1-LR, CTR-scale stream)",
         "value": ex_per_step * args.steps / (ms / 1e3),
@@ -161,17 +167,14 @@ def run_ftrl(args) -> dict:
         "dtype": "fp32", "data": "synthetic",
         "impl": "nccl-baseline" if args.impl == "nccl" else "fused",
         "config": {"model": "FTRL-proximal logistic regression, 2^30 hashed uint64 keys Zipf(1.1), ~96 nnz/row, "
-                            "alpha=0.1 beta=1 lambda1=1 lambda2=0.1, per-key fp32 (w,z,pos,neg)",
+                            "alpha=0.1 beta=1 lambda1=1 lambda2=0.1, per-key fp32 state, rule=" + args.rule,
                    "global_batch": ex_per_step, "seq_len": None, "nnz_per_row": max_nnz / rows,
                    "parallelism": f"dp{world} x key-range shards {world} (worker+server per GPU)",
                    "l2_policy": f"inputs larger than L2: ring of {ring} distinct minibatches "
                                 f"({batches[0].nbytes() >> 20} MiB each) plus {max_nnz * 4 >> 20} MiB slot map per step",
                    "mean_logloss_last": st["loss_sum"] / max(st["rows"], 1), "nnz_w": st["nnz_w"],
                    "unique_keys_per_step": st["unique_keys"] / max(args.steps, 1)},
-        "e2e": {"value": ex_per_step * args.steps / (e2e_ms / 1e3), "unit": "examples/s",
-                "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": trainer.h2d_bytes // args.steps, "d2h_bytes_per_step": trainer.d2h_bytes // args.steps,
-                "mean_logloss_last": losses[-1] if losses else None},
+        "e2e": e2e,
         "gpu_launches": launches,
         "clocks": clocks,
     }, rank
@@ -187,6 +190,9 @@ def main() -> None:
     ap.add_argument("--ring", type=int, default=4, help="distinct minibatches per GPU")
     ap.add_argument("--table-log2", type=int, default=26, help="log2 slots of each GPU's shard table")
     ap.add_argument("--local-log2", type=int, default=22, help="log2 slots of the per-minibatch dedup table")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host-streaming) measurement")
+    ap.add_argument("--rule", default="sumsq", choices=["count", "sumsq"],
+                    help="per-key learning-rate statistic: reference count-based estimate or sum of g^2")
     ap.add_argument("--timeout-s", type=float, default=5.0, help="limit of in-kernel cross-GPU waits")
     args = ap.parse_args()
     if args.impl == "reference":
