@@ -24,16 +24,27 @@
 // SharedParameter::push/pull (src/parameter/shared_parameter.h:14-26,90-149).
 // The schedule is bulk-synchronous (one legal serialisation of the reference's
 // eventual-consistency execution): pull(e) sees every update of step e-1.
+#include <cstddef>
+
 #include "psb_common.cuh"
 
 namespace psb {
 
-struct ShardState {  // 16 B, one per table slot
+struct ShardState {  // 16 B of per-key state
   float w;
   float z;
   uint32_t pos;  // rule 0: #positive rows seen; rule 1: bit pattern of Σg² (float)
   uint32_t neg;
 };
+
+// One slot of an owner's table: key and state share one 32-byte sector, so a pull probe
+// is one sector read and an update is one read-modify-write of the same sector.
+struct __align__(32) ShardSlot {
+  ShardState st;     // offset 0: accessed as one 16-byte vector
+  uint64_t key;      // offset 16: kEmptyKey when free
+  uint64_t reserved;
+};
+static_assert(sizeof(ShardSlot) == 32 && offsetof(ShardSlot, key) == 16, "ShardSlot layout");
 
 struct FtrlHyper {
   float alpha, beta, l1, l2;
@@ -46,8 +57,7 @@ struct FtrlPeers {
   int rank;
   int max_probe;
   uint64_t tab_mask;                       // table capacity − 1 (same on all ranks)
-  uint64_t* tab_keys[PSB_MAX_RANKS];
-  ShardState* tab_state[PSB_MAX_RANKS];
+  ShardSlot* tab[PSB_MAX_RANKS];
   uint64_t* in_keys[PSB_MAX_RANKS];        // owner o: [sender][in_cap]
   float* in_g[PSB_MAX_RANKS];
   uint64_t* in_cnt[PSB_MAX_RANKS];         // pos<<32 | neg
@@ -68,11 +78,17 @@ struct Minibatch {
   int pad;
 };
 
-struct LocalSlot {  // 16 B payload of one local dedup-table slot
-  float w;                  // pulled weight
-  float g;                  // gradient accumulator
-  unsigned long long cnt;   // pos<<32 | neg rows containing the key
+struct __align__(16) LocalSlot {  // 16 B payload of one local dedup-table slot
+  float w;    // pulled weight
+  float g;    // gradient accumulator
+  float pos;  // #positive rows containing the key (exact in fp32: a minibatch has < 2^24 rows)
+  float neg;  // #negative rows containing the key
 };
+
+// One 16-byte vector reduction per non-zero instead of separate atomics on g and counts.
+__device__ __forceinline__ void red_add_slot(LocalSlot* p, float g, float pos, float neg) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(0.f), "f"(g), "f"(pos), "f"(neg) : "memory");
+}
 
 struct LocalScratch {
   uint64_t* lt_keys;   // per-minibatch dedup table (all kEmptyKey between steps)
@@ -106,12 +122,11 @@ __device__ __forceinline__ void phase_localize(const Minibatch& M, const LocalSc
 }
 
 // weight of `key` in owner's table (peer memory), 0 when absent
-__device__ __forceinline__ float probe_weight(const uint64_t* tkeys, const ShardState* tstate,
-                                              uint64_t mask, uint64_t key, int max_probe) {
+__device__ __forceinline__ float probe_weight(const ShardSlot* tab, uint64_t mask, uint64_t key, int max_probe) {
   uint64_t slot = shard_hash(key) & mask;
   for (int i = 0; i < max_probe; ++i) {
-    const uint64_t k = ld_relaxed_sys_u64(tkeys + slot);
-    if (k == key) return ld_relaxed_sys_f32(&tstate[slot].w);
+    const uint64_t k = ld_relaxed_sys_u64(&tab[slot].key);
+    if (k == key) return ld_relaxed_sys_f32(&tab[slot].st.w);
     if (k == kEmptyKey) return 0.f;
     slot = (slot + 1) & mask;
   }
@@ -126,9 +141,10 @@ __device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScra
     if (key != kEmptyKey) {
       const int o = route_owner(P.seps, key);
       LocalSlot v;
-      v.w = probe_weight(P.tab_keys[o], P.tab_state[o], P.tab_mask, key, P.max_probe);
+      v.w = probe_weight(P.tab[o], P.tab_mask, key, P.max_probe);
       v.g = 0.f;
-      v.cnt = 0ull;
+      v.pos = 0.f;
+      v.neg = 0.f;
       *reinterpret_cast<float4*>(L.lt_val + s) = *reinterpret_cast<float4*>(&v);
       ++uniq;
     }
@@ -146,7 +162,7 @@ __device__ __forceinline__ void phase_spmv_loss(const Minibatch& M, const LocalS
     for (int64_t i = b + lane; i < e; i += 32) {
       const uint32_t sl = L.slot_of[i];
       if (sl != kBadSlot) {
-        const float w = __ldcg(&L.lt_val[sl].w);
+        const float w = L.lt_val[sl].w;
         s += M.vals ? w * M.vals[i] : w;
       }
     }
@@ -162,59 +178,116 @@ __device__ __forceinline__ void phase_spmv_loss(const Minibatch& M, const LocalS
   if (lane == 0 && loss != 0.0) atomicAdd(&L.stats[0], loss);
 }
 
+// Block-local cache of gradient accumulators for frequently hit slots.  Under Zipf
+// popularity a few keys receive a large share of all non-zeros; accumulating them in
+// shared memory and flushing once per block removes the same-address serialisation of
+// global atomics.  Entries are claimed first come, first served; a slot that finds its
+// cache line taken by another slot falls back to the global atomic.
+constexpr int kHotEntries = 1024;
+struct HotCache {
+  uint32_t slot[kHotEntries];
+  float g[kHotEntries];
+  unsigned long long cnt[kHotEntries];
+};
+
 __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratch& L, size_t gwarp,
-                                           size_t nwarps, int lane) {
+                                           size_t nwarps, int lane, HotCache* hc) {
+  for (int i = threadIdx.x; i < kHotEntries; i += blockDim.x) {
+    hc->slot[i] = kBadSlot;
+    hc->g[i] = 0.f;
+    hc->cnt[i] = 0ull;
+  }
+  __syncthreads();
   for (int64_t row = (int64_t)gwarp; row < M.rows; row += (int64_t)nwarps) {
     const int64_t b = M.offsets[row], e = M.offsets[row + 1];
     const float c = L.coef[row];
-    const unsigned long long inc = M.y[row] > 0.f ? (1ull << 32) : 1ull;
+    const bool is_pos = M.y[row] > 0.f;
+    const unsigned long long inc = is_pos ? (1ull << 32) : 1ull;
     for (int64_t i = b + lane; i < e; i += 32) {
       const uint32_t sl = L.slot_of[i];
-      if (sl != kBadSlot) {
-        atomicAdd(&L.lt_val[sl].g, M.vals ? c * M.vals[i] : c);
-        atomicAdd(&L.lt_val[sl].cnt, inc);
+      if (sl == kBadSlot) continue;
+      const float gv = M.vals ? c * M.vals[i] : c;
+      const int h = (int)((sl * 2654435761u) >> 22);  // top 10 bits
+      uint32_t cur = hc->slot[h];
+      if (cur == kBadSlot) {
+        const uint32_t prev = atomicCAS(&hc->slot[h], kBadSlot, sl);
+        cur = prev == kBadSlot ? sl : prev;
       }
+      if (cur == sl) {
+        atomicAdd(&hc->g[h], gv);
+        atomicAdd(&hc->cnt[h], inc);
+      } else {
+        red_add_slot(L.lt_val + sl, gv, is_pos ? 1.f : 0.f, is_pos ? 0.f : 1.f);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kHotEntries; i += blockDim.x) {
+    const uint32_t sl = hc->slot[i];
+    if (sl != kBadSlot) {
+      const unsigned long long c = hc->cnt[i];
+      red_add_slot(L.lt_val + sl, hc->g[i], (float)(uint32_t)(c >> 32), (float)(uint32_t)c);
     }
   }
 }
 
 // Scan the local table, append every unique key's record to its owner's inbox
-// (segment of this sender) and empty the table for the next minibatch.
-__device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const LocalScratch& L, size_t gwarp,
-                                                 size_t nwarps, int lane) {
+// (segment of this sender) and empty the table for the next minibatch.  A block
+// handles chunks of kSendChunk slots: positions inside the chunk come from
+// shared-memory counters, so there is one global cursor update per owner and chunk.
+constexpr int kSendItems = 4;
+__device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const LocalScratch& L, uint32_t* s_cnt,
+                                                 uint32_t* s_base) {
   const uint64_t n = L.lt_mask + 1;
-  for (uint64_t s0 = gwarp * 32; s0 < n; s0 += nwarps * 32) {
-    const uint64_t s = s0 + lane;
-    const uint64_t key = s < n ? __ldcg(L.lt_keys + s) : kEmptyKey;
-    const bool occ = key != kEmptyKey;
-    const int o = occ ? route_owner(P.seps, key) : -1;
-    if (__ballot_sync(0xffffffffu, occ) == 0u) continue;
-    float g = 0.f;
-    uint64_t c = 0;
-    if (occ) {
-      g = __ldcg(&L.lt_val[s].g);
-      c = __ldcg(&L.lt_val[s].cnt);
-      L.lt_keys[s] = kEmptyKey;
+  const uint64_t chunk = (uint64_t)blockDim.x * kSendItems;
+  const int lane = threadIdx.x & 31;
+  const int world = P.seps.world;
+  for (uint64_t c0 = (uint64_t)blockIdx.x * chunk; c0 < n; c0 += (uint64_t)gridDim.x * chunk) {
+    if (threadIdx.x < PSB_MAX_RANKS) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    uint64_t key[kSendItems];
+    uint32_t pos[kSendItems];
+    int own[kSendItems];
+#pragma unroll
+    for (int k = 0; k < kSendItems; ++k) {
+      const uint64_t s = c0 + (uint64_t)k * blockDim.x + threadIdx.x;
+      key[k] = s < n ? __ldcg(L.lt_keys + s) : kEmptyKey;
+      own[k] = key[k] != kEmptyKey ? route_owner(P.seps, key[k]) : -1;
+      pos[k] = 0;
     }
-    for (int t = 0; t < P.seps.world; ++t) {
-      const unsigned m = __ballot_sync(0xffffffffu, o == t);
-      if (m == 0u) continue;
-      const int leader = __ffs(m) - 1;
-      uint32_t base = 0;
-      if (lane == leader) base = atomicAdd(L.send_cnt + t, (uint32_t)__popc(m));
-      base = __shfl_sync(0xffffffffu, base, leader);
-      if (o == t) {
-        const uint32_t idx = base + __popc(m & ((1u << lane) - 1u));
-        if (idx < P.in_cap) {
-          const size_t at = (size_t)P.rank * P.in_cap + idx;
-          P.in_keys[t][at] = key;
-          P.in_g[t][at] = g;
-          P.in_cnt[t][at] = c;
-        } else {
-          set_status(L.status, kInboxOverflow, (uint32_t)t, idx);
-        }
+#pragma unroll
+    for (int k = 0; k < kSendItems; ++k) {
+      for (int t = 0; t < world; ++t) {
+        const unsigned m = __ballot_sync(0xffffffffu, own[k] == t);
+        if (m == 0u) continue;
+        const int leader = __ffs(m) - 1;
+        uint32_t base = 0;
+        if (lane == leader) base = atomicAdd(&s_cnt[t], (uint32_t)__popc(m));
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (own[k] == t) pos[k] = base + __popc(m & ((1u << lane) - 1u));
       }
     }
+    __syncthreads();
+    if (threadIdx.x < world) s_base[threadIdx.x] = s_cnt[threadIdx.x] ? atomicAdd(L.send_cnt + threadIdx.x, s_cnt[threadIdx.x]) : 0u;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kSendItems; ++k) {
+      if (own[k] < 0) continue;
+      const uint64_t s = c0 + (uint64_t)k * blockDim.x + threadIdx.x;
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(L.lt_val + s));
+      L.lt_keys[s] = kEmptyKey;
+      const int t = own[k];
+      const uint32_t idx = s_base[t] + pos[k];
+      if (idx < P.in_cap) {
+        const size_t at = (size_t)P.rank * P.in_cap + idx;
+        P.in_keys[t][at] = key[k];
+        P.in_g[t][at] = v.y;
+        P.in_cnt[t][at] = ((uint64_t)(uint32_t)v.z << 32) | (uint64_t)(uint32_t)v.w;
+      } else {
+        set_status(L.status, kInboxOverflow, (uint32_t)t, idx);
+      }
+    }
+    __syncthreads();
   }
   __threadfence_system();
 }
@@ -253,7 +326,7 @@ __device__ __forceinline__ void ftrl_update(ShardState& e, float g, uint32_t dpo
   dnnz += (w != 0.f && w_old == 0.f) - (w == 0.f && w_old != 0.f);
 }
 
-__device__ __forceinline__ void phase_apply(uint64_t* tkeys, ShardState* tstate, uint64_t mask, int max_probe,
+__device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, int max_probe,
                                             const uint64_t* rk, const float* rg, const uint64_t* rc,
                                             uint32_t n, const FtrlHyper& h, double* stats, uint32_t* status,
                                             size_t gtid, size_t gsz) {
@@ -267,10 +340,10 @@ __device__ __forceinline__ void phase_apply(uint64_t* tkeys, ShardState* tstate,
     uint64_t slot = shard_hash(key) & mask;
     bool found = false;
     for (int p = 0; p < max_probe; ++p) {
-      const uint64_t cur = tkeys[slot];
+      const uint64_t cur = tab[slot].key;
       if (cur == key) { found = true; break; }
       if (cur == kEmptyKey) {
-        const unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long*>(tkeys + slot),
+        const unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long*>(&tab[slot].key),
                                                   (unsigned long long)kEmptyKey, (unsigned long long)key);
         if (prev == kEmptyKey) { found = true; ++dins; break; }
         if (prev == key) { found = true; break; }
@@ -281,12 +354,12 @@ __device__ __forceinline__ void phase_apply(uint64_t* tkeys, ShardState* tstate,
       set_status(status, kShardTableFull, 0, 0);
       continue;
     }
-    float4 raw = *reinterpret_cast<float4*>(tstate + slot);
+    float4 raw = *reinterpret_cast<float4*>(&tab[slot].st);
     ShardState e;
     e.w = raw.x; e.z = raw.y; e.pos = __float_as_uint(raw.z); e.neg = __float_as_uint(raw.w);
     ftrl_update(e, g, (uint32_t)(c >> 32), (uint32_t)c, h, dn1, dn2, dnnz);
     raw.x = e.w; raw.y = e.z; raw.z = __uint_as_float(e.pos); raw.w = __uint_as_float(e.neg);
-    *reinterpret_cast<float4*>(tstate + slot) = raw;
+    *reinterpret_cast<float4*>(&tab[slot].st) = raw;
   }
   dn1 = warp_sum(dn1);
   dn2 = warp_sum(dn2);
@@ -330,9 +403,11 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
   const int lane = threadIdx.x & 31;
   const int world = P.seps.world;
 
-  phase_grad(M, L, gtid >> 5, gsz >> 5, lane);
+  __shared__ HotCache hot;
+  __shared__ uint32_t s_cnt[PSB_MAX_RANKS], s_base[PSB_MAX_RANKS];
+  phase_grad(M, L, gtid >> 5, gsz >> 5, lane, &hot);
   grid.sync();
-  phase_route_send(P, L, gtid >> 5, gsz >> 5, lane);
+  phase_route_send(P, L, s_cnt, s_base);
   grid.sync();
   // publish this sender's record count to every owner, then wait for all senders
   if (blockIdx.x == 0 && threadIdx.x < world) {
@@ -352,7 +427,7 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
   for (int s = 0; s < world; ++s) {
     const uint32_t n = __ldcg(L.recv_cnt + s);
     const size_t off = (size_t)s * P.in_cap;
-    phase_apply(P.tab_keys[P.rank], P.tab_state[P.rank], P.tab_mask, P.max_probe,
+    phase_apply(P.tab[P.rank], P.tab_mask, P.max_probe,
                 P.in_keys[P.rank] + off, P.in_g[P.rank] + off, P.in_cnt[P.rank] + off, n, H, L.stats,
                 L.status, gtid, gsz);
     grid.sync();
@@ -374,7 +449,8 @@ __global__ void k_spmv_loss(Minibatch M, LocalScratch L) {
 }
 __global__ void k_grad(Minibatch M, LocalScratch L) {
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  phase_grad(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31);
+  __shared__ HotCache hot;
+  phase_grad(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31, &hot);
 }
 // count unique keys per owner (pass 1 of packing for all_to_all_v)
 __global__ void k_count_owner(KeySeps seps, LocalScratch L, uint32_t* counts) {
@@ -401,17 +477,23 @@ __global__ void k_pack_keys(KeySeps seps, LocalScratch L, uint32_t* cursors, uin
   for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += gsz) {
     const uint64_t key = L.lt_keys[s];
     if (key != kEmptyKey) {
-      const uint32_t at = atomicAdd(cursors + route_owner(seps, key), 1u);
+      const int o = route_owner(seps, key);
+      const unsigned m = __match_any_sync(__activemask(), o);
+      const int leader = __ffs(m) - 1, lane = threadIdx.x & 31;
+      uint32_t base = 0;
+      if (lane == leader) base = atomicAdd(cursors + o, (uint32_t)__popc(m));
+      base = __shfl_sync(m, base, leader);
+      const uint32_t at = base + __popc(m & ((1u << lane) - 1u));
       out_keys[at] = key;
       out_slot[at] = (uint32_t)s;
     }
   }
 }
 // owner side of an unfused pull: w for each requested key (0 when absent)
-__global__ void k_lookup(const uint64_t* tkeys, const ShardState* tstate, uint64_t mask, int max_probe,
+__global__ void k_lookup(const ShardSlot* tab, uint64_t mask, int max_probe,
                          const uint64_t* keys, uint32_t n, float* out_w) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    out_w[i] = probe_weight(tkeys, tstate, mask, keys[i], max_probe);
+    out_w[i] = probe_weight(tab, mask, keys[i], max_probe);
 }
 __global__ void k_scatter_w(const uint32_t* slots, const float* w, uint32_t n, LocalScratch L) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -419,7 +501,8 @@ __global__ void k_scatter_w(const uint32_t* slots, const float* w, uint32_t n, L
     LocalSlot v;
     v.w = w[i];
     v.g = 0.f;
-    v.cnt = 0ull;
+    v.pos = 0.f;
+    v.neg = 0.f;
     L.lt_val[s] = v;
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) L.stats[5] += (double)n;
@@ -428,14 +511,14 @@ __global__ void k_pack_push(const uint32_t* slots, uint32_t n, LocalScratch L, f
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const uint32_t s = slots[i];
     out_g[i] = L.lt_val[s].g;
-    out_cnt[i] = L.lt_val[s].cnt;
+    out_cnt[i] = ((uint64_t)(uint32_t)L.lt_val[s].pos << 32) | (uint64_t)(uint32_t)L.lt_val[s].neg;
     L.lt_keys[s] = kEmptyKey;
   }
 }
-__global__ void k_apply(uint64_t* tkeys, ShardState* tstate, uint64_t mask, int max_probe, const uint64_t* rk,
+__global__ void k_apply(ShardSlot* tab, uint64_t mask, int max_probe, const uint64_t* rk,
                         const float* rg, const uint64_t* rc, uint32_t n, FtrlHyper h, double* stats,
                         uint32_t* status) {
-  phase_apply(tkeys, tstate, mask, max_probe, rk, rg, rc, n, h, stats, status,
+  phase_apply(tab, mask, max_probe, rk, rg, rc, n, h, stats, status,
               (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
 }
 __global__ void k_clear_local(LocalScratch L) {
@@ -443,14 +526,14 @@ __global__ void k_clear_local(LocalScratch L) {
     L.lt_keys[s] = kEmptyKey;
 }
 // dump the non-zero weights of a shard: out_keys/out_w sized by capacity, *count receives the number
-__global__ void k_dump_nonzero(const uint64_t* tkeys, const ShardState* tstate, uint64_t mask, uint64_t* out_keys,
+__global__ void k_dump_nonzero(const ShardSlot* tab, uint64_t mask, uint64_t* out_keys,
                                float* out_w, unsigned long long* count) {
   for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= mask; s += (size_t)gridDim.x * blockDim.x) {
-    const uint64_t k = tkeys[s];
-    if (k != kEmptyKey && tstate[s].w != 0.f) {
+    const uint64_t k = tab[s].key;
+    if (k != kEmptyKey && tab[s].st.w != 0.f) {
       const unsigned long long at = atomicAdd(count, 1ull);
       out_keys[at] = k;
-      out_w[at] = tstate[s].w;
+      out_w[at] = tab[s].st.w;
     }
   }
 }
@@ -472,7 +555,7 @@ int coop_grid(K kernel, int* cache) {
     int per_sm = 0, sms = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (per_sm > 4) per_sm = 4;
+    if (per_sm > 8) per_sm = 8;
     cache[dev] = per_sm * sms;
   }
   return cache[dev];
@@ -526,9 +609,9 @@ int psb_ftrl_pack_keys(const KeySeps* seps, const LocalScratch* L, uint32_t* cur
   k_pack_keys<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*seps, *L, cursors, out_keys, out_slot);
   return (int)cudaGetLastError();
 }
-int psb_ftrl_lookup(const uint64_t* tkeys, const void* tstate, uint64_t mask, int max_probe, const uint64_t* keys,
+int psb_ftrl_lookup(const void* tab, uint64_t mask, int max_probe, const uint64_t* keys,
                     uint32_t n, float* out_w, cudaStream_t s) {
-  k_lookup<<<flat_grid(n), 256, 0, s>>>(tkeys, (const ShardState*)tstate, mask, max_probe, keys, n, out_w);
+  k_lookup<<<flat_grid(n), 256, 0, s>>>((const ShardSlot*)tab, mask, max_probe, keys, n, out_w);
   return (int)cudaGetLastError();
 }
 int psb_ftrl_scatter_w(const uint32_t* slots, const float* w, uint32_t n, const LocalScratch* L, cudaStream_t s) {
@@ -540,19 +623,19 @@ int psb_ftrl_pack_push(const uint32_t* slots, uint32_t n, const LocalScratch* L,
   k_pack_push<<<flat_grid(n), 256, 0, s>>>(slots, n, *L, out_g, out_cnt);
   return (int)cudaGetLastError();
 }
-int psb_ftrl_apply(uint64_t* tkeys, void* tstate, uint64_t mask, int max_probe, const uint64_t* rk, const float* rg,
+int psb_ftrl_apply(void* tab, uint64_t mask, int max_probe, const uint64_t* rk, const float* rg,
                    const uint64_t* rc, uint32_t n, const FtrlHyper* h, double* stats, uint32_t* status,
                    cudaStream_t s) {
-  k_apply<<<flat_grid(n), 256, 0, s>>>(tkeys, (ShardState*)tstate, mask, max_probe, rk, rg, rc, n, *h, stats, status);
+  k_apply<<<flat_grid(n), 256, 0, s>>>((ShardSlot*)tab, mask, max_probe, rk, rg, rc, n, *h, stats, status);
   return (int)cudaGetLastError();
 }
 int psb_ftrl_clear_local(const LocalScratch* L, cudaStream_t s) {
   k_clear_local<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*L);
   return (int)cudaGetLastError();
 }
-int psb_ftrl_dump_nonzero(const uint64_t* tkeys, const void* tstate, uint64_t mask, uint64_t* out_keys, float* out_w,
+int psb_ftrl_dump_nonzero(const void* tab, uint64_t mask, uint64_t* out_keys, float* out_w,
                           unsigned long long* count, cudaStream_t s) {
-  k_dump_nonzero<<<flat_grid(mask + 1), 256, 0, s>>>(tkeys, (const ShardState*)tstate, mask, out_keys, out_w, count);
+  k_dump_nonzero<<<flat_grid(mask + 1), 256, 0, s>>>((const ShardSlot*)tab, mask, out_keys, out_w, count);
   return (int)cudaGetLastError();
 }
 

@@ -89,8 +89,9 @@ class FTRLEngine:
         i64, f32 = torch.int64, torch.float32
 
         # --- server side: shard table + inbox + flags (peer-addressable)
-        self.tab_keys = group.alloc((self.cap,), i64, fill=-1)
-        self.tab_state = group.alloc((self.cap, 4), f32, fill=0)
+        # one 32-byte slot per key: [(w,z), (pos,neg), key, reserved] viewed as 4 x int64
+        self.tab = group.alloc((self.cap, 4), i64, fill=0)
+        self.tab.local[:, 2] = -1
         self.in_keys = group.alloc((W * self.in_cap,), i64, fill=-1)
         self.in_g = group.alloc((W * self.in_cap,), f32)
         self.in_cnt = group.alloc((W * self.in_cap,), i64)
@@ -120,8 +121,7 @@ class FTRLEngine:
         P.seps = self._seps
         P.rank, P.max_probe, P.tab_mask = group.rank, max_probe, self.cap - 1
         for r in range(W):
-            P.tab_keys[r] = self.tab_keys.ptrs[r]
-            P.tab_state[r] = self.tab_state.ptrs[r]
+            P.tab[r] = self.tab.ptrs[r]
             P.in_keys[r] = self.in_keys.ptrs[r]
             P.in_g[r] = self.in_g.ptrs[r]
             P.in_cnt[r] = self.in_cnt.ptrs[r]
@@ -229,7 +229,7 @@ class FTRLEngine:
         nr = rkeys.numel()
         rw = torch.empty((nr,), dtype=torch.float32, device=self.dev)
         if nr:
-            N.check(lib.psb_ftrl_lookup(N.ptr(self.tab_keys.local), N.ptr(self.tab_state.local), C.c_uint64(self.cap - 1),
+            N.check(lib.psb_ftrl_lookup(N.ptr(self.tab.local), C.c_uint64(self.cap - 1),
                                         self._P.max_probe, N.ptr(rkeys), C.c_uint32(nr), N.ptr(rw), s), "lookup")
             self.kernel_launches += 1
         if W > 1:
@@ -266,7 +266,7 @@ class FTRLEngine:
         off = 0
         for n in in_counts:
             if n:
-                N.check(lib.psb_ftrl_apply(N.ptr(self.tab_keys.local), N.ptr(self.tab_state.local),
+                N.check(lib.psb_ftrl_apply(N.ptr(self.tab.local),
                                            C.c_uint64(self.cap - 1), self._P.max_probe, N.ptr(rkeys[off:off + n]),
                                            N.ptr(rg[off:off + n]), N.ptr(rc[off:off + n]), C.c_uint32(n),
                                            C.byref(self._H), N.ptr(self.stats), N.ptr(self.status), s), "apply")
@@ -293,7 +293,7 @@ class FTRLEngine:
         out_k = torch.empty((self.cap,), dtype=torch.int64, device=self.dev)
         out_w = torch.empty((self.cap,), dtype=torch.float32, device=self.dev)
         cnt = torch.zeros((1,), dtype=torch.int64, device=self.dev)
-        N.check(self._lib.psb_ftrl_dump_nonzero(N.ptr(self.tab_keys.local), N.ptr(self.tab_state.local),
+        N.check(self._lib.psb_ftrl_dump_nonzero(N.ptr(self.tab.local),
                                                 C.c_uint64(self.cap - 1), N.ptr(out_k), N.ptr(out_w), N.ptr(cnt),
                                                 N.stream_ptr()), "dump_nonzero")
         n = int(cnt.item())

@@ -42,7 +42,7 @@ _P8 = C.c_void_p * MAX_RANKS
 
 class FtrlPeers(C.Structure):
     _fields_ = [("seps", KeySeps), ("rank", C.c_int), ("max_probe", C.c_int), ("tab_mask", C.c_uint64),
-                ("tab_keys", _P8), ("tab_state", _P8), ("in_keys", _P8), ("in_g", _P8), ("in_cnt", _P8),
+                ("tab", _P8), ("in_keys", _P8), ("in_g", _P8), ("in_cnt", _P8),
                 ("in_flag", _P8), ("applied", _P8), ("timeout_ns", C.c_uint64), ("in_cap", C.c_uint32),
                 ("pad", C.c_uint32)]
 
