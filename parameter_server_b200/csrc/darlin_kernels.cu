@@ -1,0 +1,429 @@
+// DARLIN: delayed block proximal-Newton coordinate descent for L1 logistic regression,
+// as one persistent cooperative kernel per pass over the feature blocks.
+//
+// One rank = worker r (rows shard in CSC over its local unique keys) + server r (the
+// weights of its key range).  For every feature block, in schedule order:
+//
+//   A  worker  G_j = −Σ y_i τ_i x_ij ,  U_j = Σ min(τ_i(1−τ_i)·e^{|x_ij|δ_j}, ¼)·x_ij²   (τ_i = 1/(1+e^{m_i}))
+//              computed nnz-parallel with warp-segmented sums and pushed straight into the
+//              owner shard's (G,U) accumulators with red.add.v2.f32 over NVLink
+//      ── every CTA adds 1 to each owner's arrival counter (release, system scope) ──
+//   B  server  on arrival of all workers' CTAs: KKT filter, proximal-Newton step inside the
+//              trust region δ, δ update, accumulators cleared
+//      ── every CTA adds 1 to each worker's "updated" counter ──
+//   C  worker  pull: one peer load of w_new per local column of the block, Δw, δ, active
+//              set; then m_i += y_i·x_ij·Δw_j over the block's non-zeros
+//
+// Arithmetic follows Darling::computeGradients / updateWeight / updateDual
+// (src/linear_method/darling.cc:306-356, 437-477, 358-435).  Instead of
+// dual_i = exp(y_i·Xw_i) the worker keeps the margin m_i = y_i·Xw_i (dual = e^m), so the
+// multiplicative dual update becomes an additive, atomics-friendly one and fp32 does not
+// drift.  Inactive (KKT-filtered) keys are NaN in the server's weight array, exactly the
+// reference's sentinel convention.
+//
+// All waits (cross-GPU counters and the in-GPU barrier) are bounded; on expiry the kernel
+// records the place in the status word, raises the abort flag and every CTA leaves the
+// block loop.
+#include "psb_common.cuh"
+
+namespace psb {
+
+struct DarlinWorker {
+  const int64_t* col_ptr;   // cols+1 offsets into row_idx/vals (CSC over local columns)
+  const uint32_t* row_idx;  // nnz
+  const float* vals;        // nnz, or nullptr for binary features
+  const float* y;           // rows, ±1
+  float* margin;            // rows: y_i·(Xw)_i
+  float* w;                 // cols: worker's copy of the weights
+  float* delta;             // cols: trust region
+  uint8_t* active;          // cols: 1 = in the active set
+  const uint32_t* gslot;    // cols: slot in the owner's shard
+  const uint8_t* gowner;    // cols: owner rank
+  float* dw;                // cols: scratch Δw of the current block
+  int64_t cols;
+  int rows;
+  int pad;
+};
+
+struct DarlinPeers {
+  float* w[PSB_MAX_RANKS];        // owner shard weights (NaN = filtered)
+  float2* gu[PSB_MAX_RANKS];      // owner shard (G,U) accumulators
+  uint64_t* arrive[PSB_MAX_RANKS];   // on owner o: #CTAs (all workers) that finished phase A
+  uint64_t* updated[PSB_MAX_RANKS];  // on worker r: #CTAs (all owners) that finished phase B
+  int rank, world;
+  uint64_t timeout_ns;
+};
+
+struct DarlinServer {     // local arrays of this rank's shard
+  float* delta;           // slots
+  uint8_t* active;        // slots
+  uint32_t* violation;    // float bits of max violation (non-negative)
+  int64_t slots;
+};
+
+struct DarlinSched {
+  const int32_t* order;     // nblk block ids in pass order
+  const int64_t* blk_lc;    // [nblocks_total][2] local column range of each block
+  const int64_t* blk_sl;    // [nblocks_total][2] slot range of each block on this owner
+  int nblk;
+  int pad;
+  uint64_t seq0;            // blocks processed before this launch (same on all ranks)
+  uint64_t* local_bar;      // in-GPU barrier counter (monotone)
+  uint64_t bar0;            // barrier rounds completed before this launch
+  uint32_t* abort_flag;
+  uint32_t* status;
+};
+
+struct DarlinHyper {
+  float lambda, eta, delta_max, kkt_threshold;
+};
+
+__device__ __forceinline__ uint64_t ld_acquire_gpu_u64(const uint64_t* p) {
+  uint64_t v; asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u64(uint64_t* p, uint64_t v) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_v2_f32(float2* p, float a, float b) {
+  asm volatile("red.relaxed.sys.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+}
+
+// thread 0 of the CTA waits until *ctr >= target (bounded); result broadcast to the CTA
+__device__ __forceinline__ bool cta_wait_counter(const uint64_t* ctr, uint64_t target, uint64_t timeout_ns,
+                                                 bool sys_scope, bool* s_ok) {
+  if (threadIdx.x == 0) {
+    const uint64_t t0 = globaltimer_ns();
+    const uint64_t max_iters = timeout_ns / 32 + 1024;
+    bool ok = false;
+    for (uint64_t it = 0; it < max_iters; ++it) {
+      const uint64_t v = sys_scope ? ld_acquire_sys_u64(ctr) : ld_acquire_gpu_u64(ctr);
+      if (v >= target) { ok = true; break; }
+      if ((it & 63) == 63 && globaltimer_ns() - t0 > timeout_ns) break;
+      __nanosleep(20);
+    }
+    *s_ok = ok;
+  }
+  __syncthreads();
+  return *s_ok;
+}
+
+__device__ __forceinline__ int64_t find_col(const int64_t* col_ptr, int64_t lo, int64_t hi, int64_t e) {
+  // largest j in [lo, hi) with col_ptr[j] <= e
+  while (hi - lo > 1) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (col_ptr[mid] <= e) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// ---- phase A: block gradient (G,U) pushed into the owners' accumulators
+__device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
+                                                 int64_t lc1, size_t gwarp, size_t nwarps, int lane) {
+  const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
+  const bool binary = Wk.vals == nullptr;
+  for (int64_t base = p0 + (int64_t)gwarp * 32; base < p1; base += (int64_t)nwarps * 32) {
+    const int64_t e = base + lane;
+    const bool valid = e < p1;
+    int64_t j = -1;
+    float g = 0.f, u = 0.f;
+    if (valid) {
+      j = find_col(Wk.col_ptr, lc0, lc1, e);
+      if (Wk.active[j]) {
+        const uint32_t i = Wk.row_idx[e];
+        const float yi = Wk.y[i];
+        const float tau = 1.f / (1.f + __expf(Wk.margin[i]));
+        const float t2 = tau * (1.f - tau);
+        const float dj = Wk.delta[j];
+        if (binary) {
+          g = -yi * tau;
+          u = fminf(t2 * __expf(dj), 0.25f);
+        } else {
+          const float v = Wk.vals[e];
+          g = -yi * tau * v;
+          u = fminf(t2 * __expf(fabsf(v) * dj), 0.25f) * v * v;
+        }
+      } else {
+        j = -2 - j;  // inactive: keeps the segment boundary, contributes nothing
+      }
+    }
+    // segmented sum over runs of equal j (non-zeros of a column are contiguous)
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int64_t oj = __shfl_down_sync(0xffffffffu, j, off);
+      const float og = __shfl_down_sync(0xffffffffu, g, off);
+      const float ou = __shfl_down_sync(0xffffffffu, u, off);
+      if (lane + off < 32 && oj == j) { g += og; u += ou; }
+    }
+    const int64_t pj = __shfl_up_sync(0xffffffffu, j, 1);
+    const bool head = valid && j >= 0 && (lane == 0 || pj != j);
+    if (head) red_add_v2_f32(P.gu[Wk.gowner[j]] + Wk.gslot[j], g, u);
+  }
+}
+
+// ---- phase B: server-side proximal-Newton update of the block's slots
+__device__ __forceinline__ void darlin_update_weight(const DarlinPeers& P, const DarlinServer& S,
+                                                     const DarlinHyper& H, int64_t s0, int64_t s1, size_t gtid,
+                                                     size_t gsz) {
+  float* w = P.w[P.rank];
+  float2* gu = P.gu[P.rank];
+  float vmax = 0.f;
+  for (int64_t k = s0 + (int64_t)gtid; k < s1; k += (int64_t)gsz) {
+    const float2 a = __ldcg(gu + k);
+    gu[k] = make_float2(0.f, 0.f);
+    if (!S.active[k]) continue;
+    const float g = a.x, u = a.y / H.eta + 1e-10f;
+    const float gp = g + H.lambda, gn = g - H.lambda;
+    float wk = w[k];
+    float d = -wk, vio = 0.f;
+    if (wk == 0.f) {
+      if (gp < 0.f) vio = -gp;
+      else if (gn > 0.f) vio = gn;
+      else if (gp > H.kkt_threshold && gn < -H.kkt_threshold) {
+        S.active[k] = 0;
+        w[k] = __int_as_float(0x7fffffff);  // NaN sentinel: key filtered
+        continue;
+      }
+    }
+    vmax = fmaxf(vmax, vio);
+    if (gp <= u * wk) d = -gp / u;
+    else if (gn >= u * wk) d = -gn / u;
+    const float dl = S.delta[k];
+    d = fminf(dl, fmaxf(-dl, d));
+    S.delta[k] = fminf(H.delta_max, 2.f * fabsf(d) + 0.1f);
+    w[k] = wk + d;
+  }
+  vmax = warp_max(vmax);
+  if ((threadIdx.x & 31) == 0 && vmax > 0.f) atomicMax(S.violation, __float_as_uint(vmax));
+}
+
+// ---- phase C1: pull w_new for the block's local columns, Δw, δ, active set
+__device__ __forceinline__ void darlin_pull(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H,
+                                            int64_t lc0, int64_t lc1, size_t gtid, size_t gsz) {
+  for (int64_t j = lc0 + (int64_t)gtid; j < lc1; j += (int64_t)gsz) {
+    float d = 0.f;
+    if (Wk.active[j]) {
+      const float wn = ld_relaxed_sys_f32(P.w[Wk.gowner[j]] + Wk.gslot[j]);
+      if (wn != wn) {
+        Wk.active[j] = 0;
+        Wk.w[j] = 0.f;
+      } else {
+        d = wn - Wk.w[j];
+        Wk.delta[j] = fminf(H.delta_max, 2.f * fabsf(d) + 0.1f);
+        Wk.w[j] = wn;
+      }
+    }
+    Wk.dw[j] = d;
+  }
+}
+
+// ---- phase C2: m_i += y_i x_ij Δw_j over the block's non-zeros
+__device__ __forceinline__ void darlin_update_margin(const DarlinWorker& Wk, int64_t lc0, int64_t lc1, size_t gtid,
+                                                     size_t gsz) {
+  const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
+  for (int64_t e = p0 + (int64_t)gtid; e < p1; e += (int64_t)gsz) {
+    const int64_t j = find_col(Wk.col_ptr, lc0, lc1, e);
+    const float d = __ldcg(Wk.dw + j);
+    if (d != 0.f) {
+      const uint32_t i = Wk.row_idx[e];
+      const float v = Wk.vals ? Wk.vals[e] : 1.f;
+      atomicAdd(Wk.margin + i, Wk.y[i] * v * d);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512)
+darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q, DarlinHyper H) {
+  __shared__ bool s_ok;
+  __shared__ uint32_t s_abort;
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t gsz = (size_t)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const uint64_t G = gridDim.x;
+  uint64_t bar = Q.bar0;
+
+  for (int b = 0; b < Q.nblk; ++b) {
+    if (threadIdx.x == 0) s_abort = *(volatile uint32_t*)Q.abort_flag;
+    __syncthreads();
+    if (s_abort) break;  // uniform over the CTA
+    const int blk = Q.order[b];
+    const uint64_t seq = Q.seq0 + (uint64_t)b + 1;
+    const int64_t lc0 = Q.blk_lc[2 * blk], lc1 = Q.blk_lc[2 * blk + 1];
+    const int64_t s0 = Q.blk_sl[2 * blk], s1 = Q.blk_sl[2 * blk + 1];
+
+    // A: gradient + push, then announce arrival at every owner
+    darlin_grad_push(Wk, P, lc0, lc1, gtid >> 5, gsz >> 5, lane);
+    __syncthreads();
+    if (threadIdx.x < P.world) {
+      __threadfence_system();
+      red_release_sys_add_u64(P.arrive[threadIdx.x], 1ull);
+    }
+    // B: wait for all workers' CTAs, update this shard's slots of the block
+    if (!cta_wait_counter(P.arrive[P.rank], seq * G * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)blk, 11); *Q.abort_flag = 1u; }
+      break;
+    }
+    darlin_update_weight(P, S, H, s0, s1, gtid, gsz);
+    __syncthreads();
+    if (threadIdx.x < P.world) {
+      __threadfence_system();
+      red_release_sys_add_u64(P.updated[threadIdx.x], 1ull);
+    }
+    // C: wait for all owners' CTAs, pull and apply
+    if (!cta_wait_counter(P.updated[P.rank], seq * G * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)blk, 12); *Q.abort_flag = 1u; }
+      break;
+    }
+    darlin_pull(Wk, P, H, lc0, lc1, gtid, gsz);
+    __syncthreads();
+    if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
+    if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)blk, 13); *Q.abort_flag = 1u; }
+      break;
+    }
+    darlin_update_margin(Wk, lc0, lc1, gtid, gsz);
+    __syncthreads();
+    if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
+    if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)blk, 14); *Q.abort_flag = 1u; }
+      break;
+    }
+  }
+}
+
+// ---- stand-alone phase kernels (unfused NCCL baseline; gradients go to local buffers)
+__global__ void k_darlin_grad_local(DarlinWorker Wk, int64_t lc0, int64_t lc1, float2* gu_local) {
+  // same reduction as phase A, accumulated into a local per-column buffer (index j − lc0)
+  DarlinPeers P{};
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t gwarp = gtid >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
+  const bool binary = Wk.vals == nullptr;
+  (void)P;
+  for (int64_t base = p0 + (int64_t)gwarp * 32; base < p1; base += (int64_t)nwarps * 32) {
+    const int64_t e = base + lane;
+    const bool valid = e < p1;
+    int64_t j = -1;
+    float g = 0.f, u = 0.f;
+    if (valid) {
+      j = find_col(Wk.col_ptr, lc0, lc1, e);
+      if (Wk.active[j]) {
+        const uint32_t i = Wk.row_idx[e];
+        const float yi = Wk.y[i];
+        const float tau = 1.f / (1.f + __expf(Wk.margin[i]));
+        const float t2 = tau * (1.f - tau);
+        const float dj = Wk.delta[j];
+        if (binary) { g = -yi * tau; u = fminf(t2 * __expf(dj), 0.25f); }
+        else { const float v = Wk.vals[e]; g = -yi * tau * v; u = fminf(t2 * __expf(fabsf(v) * dj), 0.25f) * v * v; }
+      } else {
+        j = -2 - j;
+      }
+    }
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int64_t oj = __shfl_down_sync(0xffffffffu, j, off);
+      const float og = __shfl_down_sync(0xffffffffu, g, off);
+      const float ou = __shfl_down_sync(0xffffffffu, u, off);
+      if (lane + off < 32 && oj == j) { g += og; u += ou; }
+    }
+    const int64_t pj = __shfl_up_sync(0xffffffffu, j, 1);
+    if (valid && j >= 0 && (lane == 0 || pj != j)) {
+      atomicAdd(&gu_local[j - lc0].x, g);
+      atomicAdd(&gu_local[j - lc0].y, u);
+    }
+  }
+}
+__global__ void k_darlin_update_weight(DarlinPeers P, DarlinServer S, DarlinHyper H, int64_t s0, int64_t s1) {
+  darlin_update_weight(P, S, H, s0, s1, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+}
+// Δw etc. from an explicit array of new weights (w_new[j − lc0]) instead of peer loads
+__global__ void k_darlin_apply_pull(DarlinWorker Wk, DarlinHyper H, int64_t lc0, int64_t lc1, const float* w_new) {
+  for (int64_t j = lc0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < lc1; j += (int64_t)gridDim.x * blockDim.x) {
+    float d = 0.f;
+    if (Wk.active[j]) {
+      const float wn = w_new[j - lc0];
+      if (wn != wn) { Wk.active[j] = 0; Wk.w[j] = 0.f; }
+      else { d = wn - Wk.w[j]; Wk.delta[j] = fminf(H.delta_max, 2.f * fabsf(d) + 0.1f); Wk.w[j] = wn; }
+    }
+    Wk.dw[j] = d;
+  }
+}
+__global__ void k_darlin_update_margin(DarlinWorker Wk, int64_t lc0, int64_t lc1) {
+  darlin_update_margin(Wk, lc0, lc1, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+}
+// margin_i = y_i · Σ_j x_ij w_j from scratch (initialisation with non-zero weights, drift checks)
+__global__ void k_darlin_margin_init(DarlinWorker Wk) {
+  const int64_t p1 = Wk.col_ptr[Wk.cols];
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < p1; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t j = find_col(Wk.col_ptr, 0, Wk.cols, e);
+    const float wj = Wk.w[j];
+    if (wj != 0.f && wj == wj) {
+      const uint32_t i = Wk.row_idx[e];
+      atomicAdd(Wk.margin + i, Wk.y[i] * (Wk.vals ? Wk.vals[e] : 1.f) * wj);
+    }
+  }
+}
+
+}  // namespace psb
+
+using namespace psb;
+
+namespace {
+int g_darlin_grid[16] = {0};
+}
+
+extern "C" {
+
+// Number of CTAs of the pass kernel on the current device (every rank must use the same value).
+int psb_darlin_grid() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) dev = 0;
+  if (g_darlin_grid[dev] == 0) {
+    int per_sm = 0, sms = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, darlin_pass_kernel, 512, 0);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    g_darlin_grid[dev] = sms * (per_sm > 2 ? 2 : per_sm);  // upper bound; callers may launch fewer
+  }
+  return g_darlin_grid[dev];
+}
+
+int psb_darlin_pass(const DarlinWorker* Wk, const DarlinPeers* P, const DarlinServer* S, const DarlinSched* Q,
+                    const DarlinHyper* H, int grid, cudaStream_t stream) {
+  if (grid <= 0 || grid > psb_darlin_grid()) return (int)cudaErrorInvalidValue;
+  DarlinWorker w = *Wk; DarlinPeers p = *P; DarlinServer s = *S; DarlinSched q = *Q; DarlinHyper h = *H;
+  void* args[] = {&w, &p, &s, &q, &h};
+  return (int)cudaLaunchCooperativeKernel((void*)darlin_pass_kernel, dim3(grid), dim3(512), args, 0, stream);
+}
+
+static inline int dgrid(int64_t n) {
+  int64_t b = (n + 255) / 256;
+  if (b < 1) b = 1;
+  if (b > 148 * 8) b = 148 * 8;
+  return (int)b;
+}
+int psb_darlin_grad_local(const DarlinWorker* Wk, int64_t lc0, int64_t lc1, void* gu_local, int64_t nnz_hint,
+                          cudaStream_t s) {
+  k_darlin_grad_local<<<dgrid(nnz_hint), 256, 0, s>>>(*Wk, lc0, lc1, (float2*)gu_local);
+  return (int)cudaGetLastError();
+}
+int psb_darlin_update_weight(const DarlinPeers* P, const DarlinServer* S, const DarlinHyper* H, int64_t s0, int64_t s1,
+                             cudaStream_t s) {
+  k_darlin_update_weight<<<dgrid(s1 - s0), 256, 0, s>>>(*P, *S, *H, s0, s1);
+  return (int)cudaGetLastError();
+}
+int psb_darlin_apply_pull(const DarlinWorker* Wk, const DarlinHyper* H, int64_t lc0, int64_t lc1, const float* w_new,
+                          cudaStream_t s) {
+  k_darlin_apply_pull<<<dgrid(lc1 - lc0), 256, 0, s>>>(*Wk, *H, lc0, lc1, w_new);
+  return (int)cudaGetLastError();
+}
+int psb_darlin_update_margin(const DarlinWorker* Wk, int64_t lc0, int64_t lc1, int64_t nnz_hint, cudaStream_t s) {
+  k_darlin_update_margin<<<dgrid(nnz_hint), 256, 0, s>>>(*Wk, lc0, lc1);
+  return (int)cudaGetLastError();
+}
+int psb_darlin_margin_init(const DarlinWorker* Wk, int64_t nnz, cudaStream_t s) {
+  k_darlin_margin_init<<<dgrid(nnz), 256, 0, s>>>(*Wk);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

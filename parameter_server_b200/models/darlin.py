@@ -1,0 +1,390 @@
+"""DARLIN — block-coordinate L1 logistic regression on key-range sharded GPUs.
+
+Roles (reference → here): ``BatchSolver::run`` / ``Darling::runIteration`` scheduler loop
+(src/linear_method/batch_solver.cc:23-127, src/linear_method/darling.cc:18-104) →
+:meth:`DarlinSolver.run`; ``BatchSolver::preprocessData`` (unique keys, localisation, column-major
+storage, key exchange with the servers; src/linear_method/batch_solver.cc:227-384) →
+:meth:`DarlinSolver.preprocess`; the per-block worker/server step ``Darling::updateModel``
+(src/linear_method/darling.cc:155-273) → the persistent pass kernel in ``csrc/darlin_kernels.cu``.
+
+Every rank is worker r and server r.  After preprocessing the key set is fixed, so each local
+column carries its resolved ``(owner, slot)`` and pushes/pulls move values only — the steady state
+of the reference's sender/receiver key cache (src/system/remote_node.cc:96-184).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import sys
+import time
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..ops import _native as N
+from ..ops.reduce import reduce_sum
+from ..parallel.peer import PeerGroup
+from ..utils.range import Range
+
+_SIGN = -(1 << 63)
+
+
+def _ukey(t: torch.Tensor) -> torch.Tensor:
+    """Map uint64 bit patterns (int64) to int64 values whose signed order is the unsigned order."""
+    return t ^ _SIGN
+
+
+@dataclass
+class DarlinConfig:
+    lambda1: float = 1.0
+    eta: float = 1.0
+    delta_init: float = 1.0
+    delta_max: float = 5.0
+    kkt_ratio: float = 10.0
+    max_pass: int = 20
+    epsilon: float = 1e-4
+    feature_block_ratio: float = 4.0
+    random_block_order: bool = True
+    max_block_delay: int = 0          # accepted; blocks run in order (delay 0 is within any bound)
+    seed: int = 0
+    reset_nan_on_kkt_reset: bool = True
+    shard_by_data_range: bool = True  # servers split [min_key, max_key] instead of the whole uint64 space
+
+
+@dataclass
+class Progress:
+    objv: float
+    relative_objv: float
+    nnz_w: int
+    violation: float
+    nnz_active: int
+    kkt_threshold: float
+    seconds: float = 0.0
+
+
+def block_order(nblk: int, n_pass: int, random_order: bool, seed: int) -> List[np.ndarray]:
+    rng = np.random.RandomState(seed)
+    out = []
+    for _ in range(n_pass):
+        o = np.arange(nblk, dtype=np.int32)
+        if random_order:
+            rng.shuffle(o)
+        out.append(o)
+    return out
+
+
+class DarlinSolver:
+    """Worker + server of one rank; ``preprocess`` once, then ``run`` (or ``run_pass`` repeatedly)."""
+
+    def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused"):
+        self.group, self.cfg, self.impl = group, cfg, impl
+        self.dev = group.device
+        self.timeout_s = timeout_s
+        self._lib = N.lib()
+        self.progress: List[Progress] = []
+        self.kkt_threshold = 1e20
+        self.seq = 0
+        self.bar = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ preprocessing
+    def preprocess(self, offsets: torch.Tensor, keys: torch.Tensor, vals: Optional[torch.Tensor], y: torch.Tensor):
+        """Localise this rank's CSR rows shard, exchange key sets with the servers, build the CSC blocks.
+
+        ``keys`` are uint64 bit patterns in int64.  Collective over the group.
+        """
+        import torch.distributed as dist
+
+        g, dev, W = self.group, self.dev, self.group.world
+        rows, nnz = y.numel(), keys.numel()
+        # unique local keys in unsigned order + column id of every non-zero  (Localizer::countUniqIndex/remapIndex)
+        uk, inv = torch.unique(_ukey(keys), return_inverse=True)
+        lkeys = _ukey(uk)
+        P = lkeys.numel()
+        row_of = torch.repeat_interleave(torch.arange(rows, device=dev, dtype=torch.int32), offsets[1:] - offsets[:-1])
+        order = torch.sort(inv, stable=True).indices               # CSR → CSC (SparseMatrix::alterStorage)
+        row_idx = row_of[order].contiguous()
+        cvals = None if vals is None else vals[order].contiguous()
+        col_ptr = torch.zeros(P + 1, dtype=torch.int64, device=dev)
+        col_ptr[1:] = torch.bincount(inv, minlength=P).cumsum(0)
+        # global statistics (ExampleInfo merge): rows, nnz, key range
+        stats = g.all_reduce_sum([rows, nnz])
+        self.total_rows, self.total_nnz = int(stats[0]), int(stats[1])
+        kmin = int(uk.min().item()) if P else (1 << 62)
+        kmax = int(uk.max().item()) if P else -(1 << 62)
+        if W > 1:
+            t = torch.tensor([-kmin, kmax], dtype=torch.int64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=g.group)
+            kmin, kmax = -int(t[0].item()), int(t[1].item())
+        self.key_min, self.key_max = kmin - _SIGN, kmax - _SIGN + 1   # unsigned [min, max+1)
+        # server key ranges
+        rng = Range(self.key_min, self.key_max) if self.cfg.shard_by_data_range else Range.all()
+        self.seps = rng.separators(W)
+        # servers take the union of the workers' keys in their range (KVVector::setValue key-only push)
+        if W > 1:
+            sizes = [None] * W
+            dist.all_gather_object(sizes, P, group=g.group)
+            mx = max(sizes)
+            pad = torch.full((mx,), (1 << 63) - 1, dtype=torch.int64, device=dev)
+            pad[:P] = uk
+            allk = [torch.empty_like(pad) for _ in range(W)]
+            dist.all_gather(allk, pad, group=g.group)
+            gk = torch.unique(torch.cat([a[:n] for a, n in zip(allk, sizes)]))
+        else:
+            gk = uk
+        self.gkeys_sorted = gk                                     # ordered (sign-flipped) global keys
+        sep_s = torch.tensor([min(s, (1 << 64) - 1) + _SIGN for s in self.seps[:-1]], dtype=torch.int64, device=dev)
+        shard_begin = torch.searchsorted(gk, sep_s)                # first global index of every owner
+        shard_begin = torch.cat([shard_begin, torch.tensor([gk.numel()], device=dev)])
+        self.shard_begin = shard_begin.tolist()
+        r = g.rank
+        self.slots = self.shard_begin[r + 1] - self.shard_begin[r]
+        max_slots = max(self.shard_begin[i + 1] - self.shard_begin[i] for i in range(W))
+        self.skeys = _ukey(gk[self.shard_begin[r]: self.shard_begin[r + 1]])   # this shard's keys (bit patterns)
+        # resolve (owner, slot) of each local column
+        gidx = torch.searchsorted(gk, uk)
+        owner = (torch.searchsorted(shard_begin, gidx, right=True) - 1).clamp_(0, W - 1)
+        gslot = gidx - shard_begin[owner]
+        # feature blocks: even key sub-ranges of [min_key, max_key)  (batch_solver.cc:55-65)
+        nnz_per_row = self.total_nnz / max(self.total_rows, 1)
+        nblk = max(int(math.ceil(nnz_per_row * self.cfg.feature_block_ratio)), 1) if nnz_per_row > 1 + 1e-6 else 1
+        span = self.key_max - self.key_min
+        bounds = [self.key_min + span * i // nblk for i in range(nblk)] + [self.key_max]
+        self.block_keys = [(bounds[i], bounds[i + 1]) for i in range(nblk)]
+        b_s = torch.tensor([min(b, (1 << 64) - 1) + _SIGN for b in bounds],
+                           dtype=torch.int64, device=dev)
+        lc = torch.searchsorted(uk, b_s)
+        gc = torch.searchsorted(gk, b_s)
+        lc[-1] = P
+        gc[-1] = gk.numel()
+        sl = (gc - self.shard_begin[r]).clamp_(0, self.slots)
+        self.blk_lc = torch.stack([lc[:-1], lc[1:]], 1).contiguous()
+        self.blk_sl = torch.stack([sl[:-1], sl[1:]], 1).contiguous()
+        self.nblk = nblk
+        # ---- worker state
+        f32 = torch.float32
+        self.rows, self.cols, self.nnz = rows, P, nnz
+        self.lkeys = lkeys
+        self.col_ptr, self.row_idx, self.vals, self.y = col_ptr, row_idx, cvals, y.contiguous()
+        self.margin = torch.zeros(rows, dtype=f32, device=dev)
+        self.w = torch.zeros(P, dtype=f32, device=dev)
+        self.delta = torch.full((P,), self.cfg.delta_init, dtype=f32, device=dev)
+        self.active = torch.ones(P, dtype=torch.uint8, device=dev)
+        self.gslot = gslot.to(torch.int32).contiguous()
+        self.gowner = owner.to(torch.uint8).contiguous()
+        self.dw = torch.zeros(P, dtype=f32, device=dev)
+        # ---- server state (peer-addressable weights and accumulators)
+        cap = max(max_slots, 1)
+        self.srv_w = g.alloc((cap,), f32)
+        self.srv_gu = g.alloc((cap, 2), f32)
+        self.arrive = g.alloc((1,), torch.int64)
+        self.updated = g.alloc((1,), torch.int64)
+        self.srv_delta = torch.full((cap,), self.cfg.delta_init, dtype=f32, device=dev)
+        self.srv_active = torch.ones(cap, dtype=torch.uint8, device=dev)
+        self.violation = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.local_bar = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.abort = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(8, dtype=torch.int32, device=dev)
+        self._build_structs()
+        g.barrier()
+
+    def _build_structs(self):
+        Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),
+                            0 if self.vals is None else self.vals.data_ptr(), self.y.data_ptr(),
+                            self.margin.data_ptr(), self.w.data_ptr(), self.delta.data_ptr(), self.active.data_ptr(),
+                            self.gslot.data_ptr(), self.gowner.data_ptr(), self.dw.data_ptr(), self.cols, self.rows, 0)
+        P = N.DarlinPeers()
+        for r in range(self.group.world):
+            P.w[r], P.gu[r] = self.srv_w.ptrs[r], self.srv_gu.ptrs[r]
+            P.arrive[r], P.updated[r] = self.arrive.ptrs[r], self.updated.ptrs[r]
+        P.rank, P.world, P.timeout_ns = self.group.rank, self.group.world, int(self.timeout_s * 1e9)
+        S = N.DarlinServer(self.srv_delta.data_ptr(), self.srv_active.data_ptr(), self.violation.data_ptr(), self.slots)
+        self._Wk, self._P, self._S = Wk, P, S
+        self._lib.psb_darlin_grid.restype = C.c_int
+        grid = self._lib.psb_darlin_grid()
+        if self.group.world > 1:
+            import torch.distributed as dist
+
+            t = torch.tensor([grid], dtype=torch.int64, device=self.dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group.group)
+            grid = int(t.item())
+        self.grid = grid
+
+    def _hyper(self) -> N.DarlinHyper:
+        return N.DarlinHyper(self.cfg.lambda1, self.cfg.eta, self.cfg.delta_max, min(self.kkt_threshold, 1e30))
+
+    # ------------------------------------------------------------------ passes
+    def reset_active_sets(self) -> None:
+        """KKT filter reset (src/linear_method/darling.cc:167-169): every key re-enters the active set."""
+        self.active.fill_(1)
+        self.srv_active.fill_(1)
+        if self.cfg.reset_nan_on_kkt_reset:
+            torch.nan_to_num_(self.srv_w.local, nan=0.0)
+
+    def launch_pass(self, order: np.ndarray) -> None:
+        """Enqueue one pass over the blocks in ``order`` on the current stream."""
+        order_t = torch.as_tensor(order, dtype=torch.int32).to(self.dev, non_blocking=False)
+        self._order_keepalive = order_t
+        self.violation.zero_()
+        if self.impl == "nccl":
+            return self._pass_unfused(order)
+        Q = N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), len(order), 0, self.seq,
+                          self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr())
+        H = self._hyper()
+        N.check(self._lib.psb_darlin_pass(C.byref(self._Wk), C.byref(self._P), C.byref(self._S), C.byref(Q),
+                                          C.byref(H), self.grid, N.stream_ptr()), "darlin_pass")
+        self.seq += len(order)
+        self.bar += 2 * len(order)
+        self.kernel_launches += 1
+
+    def _pass_unfused(self, order: np.ndarray) -> None:
+        """Baseline: per block, stand-alone kernels + all_reduce of (G,U) + broadcast-free local update."""
+        import torch.distributed as dist
+
+        lib, s, H, W = self._lib, N.stream_ptr(), self._hyper(), self.group.world
+        blk_lc, blk_sl = self.blk_lc.tolist(), self.blk_sl.tolist()
+        gk_begin = self.shard_begin
+        nglobal = self.gkeys_sorted.numel()
+        # global column index of each local column, for dense exchange buffers
+        if not hasattr(self, "_gcol"):
+            self._gcol = (self.gslot.long() + torch.tensor(gk_begin, device=self.dev)[self.gowner.long()])
+            self._gu_glob = torch.zeros((nglobal, 2), dtype=torch.float32, device=self.dev)
+            self._w_glob = torch.zeros((nglobal,), dtype=torch.float32, device=self.dev)
+            gb = torch.searchsorted(self.gkeys_sorted, torch.tensor(
+                [min(b, (1 << 64) - 1) + _SIGN for b, _ in self.block_keys],
+                dtype=torch.int64, device=self.dev)).tolist() + [nglobal]
+            self._blk_g = gb
+        r = self.group.rank
+        for b in order.tolist():
+            lc0, lc1 = blk_lc[b]
+            g0, g1 = self._blk_g[b], self._blk_g[b + 1]
+            if g1 <= g0:
+                continue
+            gu_loc = torch.zeros((max(lc1 - lc0, 1), 2), dtype=torch.float32, device=self.dev)
+            nnz_b = int((self.col_ptr[lc1] - self.col_ptr[lc0]).item()) if lc1 > lc0 else 0
+            if nnz_b:
+                N.check(lib.psb_darlin_grad_local(C.byref(self._Wk), lc0, lc1, N.ptr(gu_loc), nnz_b, s), "grad_local")
+                self.kernel_launches += 1
+            gu = self._gu_glob[g0:g1]
+            gu.zero_()
+            if lc1 > lc0:
+                gu.index_add_(0, self._gcol[lc0:lc1] - g0, gu_loc[: lc1 - lc0])
+            if W > 1:
+                dist.all_reduce(gu, group=self.group.group)          # push + server-side sum
+            s0, s1 = blk_sl[b]
+            if s1 > s0:
+                self.srv_gu.local[s0:s1].copy_(gu[gk_begin[r] + s0 - g0: gk_begin[r] + s1 - g0])
+                N.check(lib.psb_darlin_update_weight(C.byref(self._P), C.byref(self._S), C.byref(H), s0, s1, s), "update_weight")
+                self.kernel_launches += 1
+            wb = self._w_glob[g0:g1]
+            wb.zero_()
+            if s1 > s0:
+                wb[gk_begin[r] + s0 - g0: gk_begin[r] + s1 - g0] = self.srv_w.local[s0:s1]
+            if W > 1:
+                wnan = torch.isnan(wb)
+                wz = torch.nan_to_num(wb, nan=0.0)
+                nanf = wnan.to(torch.float32)
+                dist.all_reduce(wz, group=self.group.group)          # pull (all-gather of disjoint shards)
+                dist.all_reduce(nanf, group=self.group.group)
+                wb = torch.where(nanf > 0, torch.full_like(wz, float("nan")), wz)
+            if lc1 > lc0:
+                wn = wb[self._gcol[lc0:lc1] - g0].contiguous()
+                N.check(lib.psb_darlin_apply_pull(C.byref(self._Wk), C.byref(H), lc0, lc1, N.ptr(wn), s), "apply_pull")
+                if nnz_b:
+                    N.check(lib.psb_darlin_update_margin(C.byref(self._Wk), lc0, lc1, nnz_b, s), "update_margin")
+                self.kernel_launches += 2
+
+    def evaluate(self) -> tuple:
+        """(objective, nnz_w, nnz_active, violation) summed/maxed over ranks (Darling::evaluateProgress)."""
+        loss = reduce_sum(self.margin, "sum_logistic")
+        srv = self.srv_w.local[: max(self.slots, 0)]
+        if self.slots > 0:
+            pen = reduce_sum(srv, "sum_abs").clone()
+            nz = reduce_sum(srv, "count_nonzero").clone()
+            nact = self.srv_active[: self.slots].sum(dtype=torch.float64)
+        else:
+            pen = nz = nact = torch.zeros(1, dtype=torch.float64, device=self.dev)
+        vals = torch.stack([loss.reshape(()), pen.reshape(()), nz.reshape(()), nact.reshape(())])
+        vio = self.violation.view(torch.float32).to(torch.float64)
+        if self.group.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(vals, group=self.group.group)
+            dist.all_reduce(vio, op=dist.ReduceOp.MAX, group=self.group.group)
+        v = vals.tolist()
+        return v[0] + self.cfg.lambda1 * v[1], int(v[2]), int(v[3]), float(vio.item())
+
+    def check_status(self) -> None:
+        st = self.status.tolist()
+        if st[0] != 0:
+            raise RuntimeError(f"rank {self.group.rank}: {N.STATUS_NAMES.get(st[0], st[0])} (block={st[1]}, phase={st[2]})")
+
+    def run_pass(self, order: np.ndarray, reset: bool = False) -> Progress:
+        t0 = time.time()
+        if reset:
+            self.reset_active_sets()
+        self.launch_pass(order)
+        objv, nnz_w, nnz_as, vio = self.evaluate()
+        self.check_status()
+        rel = 1.0 if not self.progress else self.progress[-1].objv / objv - 1.0
+        p = Progress(objv, rel, nnz_w, vio, nnz_as, self.kkt_threshold, time.time() - t0)
+        self.progress.append(p)
+        self.kkt_threshold = vio / max(self.total_rows, 1) * self.cfg.kkt_ratio
+        return p
+
+    def run(self, verbose: bool = False) -> List[Progress]:
+        """All passes with the reference's stopping rule (src/linear_method/darling.cc:83-99)."""
+        cfg = self.cfg
+        orders = block_order(self.nblk, cfg.max_pass, cfg.random_block_order, cfg.seed)
+        reset = False
+        for it in range(cfg.max_pass):
+            p = self.run_pass(orders[it], reset)
+            if verbose and self.group.rank == 0:
+                print_progress(it, p, file=sys.stderr)
+            if 0 < p.relative_objv <= cfg.epsilon:
+                if reset:
+                    break
+                reset = True
+            else:
+                reset = False
+        return self.progress
+
+    # ------------------------------------------------------------------ model
+    def model(self):
+        """(keys uint64, w float32) of this shard's non-zero weights, ascending keys."""
+        w = torch.nan_to_num(self.srv_w.local[: self.slots], nan=0.0)
+        nz = w != 0
+        return self.skeys[nz].cpu().numpy().view(np.uint64), w[nz].cpu().numpy()
+
+    def save_model(self, file_prefix: str) -> str:
+        """``<file>_S<rank>``: ``key<TAB>weight`` per non-zero weight (batch_solver.cc:403-426)."""
+        from ..utils.modelio import write_model_text
+
+        k, w = self.model()
+        path = f"{file_prefix}_S{self.group.rank}"
+        write_model_text(path, k, w)
+        return path
+
+
+def print_progress(it: int, p: Progress, file=sys.stderr) -> None:
+    """Progress table in the reference's layout (linear_method.cc:181-231, darling.cc:480-501)."""
+    if it == 0:
+        print("  iter |  objective    relative     |w|_0 |      KKT filter      |  time", file=file)
+        print("       |                                  | threshold  #active   |  (sec)", file=file)
+        print(" ------+----------------------------------+----------------------+-------", file=file)
+    print(f" {it:5d} | {p.objv:.5e}  {p.relative_objv:.3e} {p.nnz_w:8d} | {p.kkt_threshold:.1e} {p.nnz_active:11d} | {p.seconds:6.2f}",
+          file=file)
+
+
+def smoke(dev) -> None:
+    """Tiny end-to-end run used by the build driver's smoke test."""
+    from ..data.synthetic import zipf_sparse_matrix
+
+    off, idx, vals, y, _ = zipf_sparse_matrix(2000, 4096, 24, seed=0, device=dev)
+    sol = DarlinSolver(PeerGroup.single(dev), DarlinConfig(lambda1=0.5, max_pass=4))
+    sol.preprocess(off, idx, vals, y)
+    prog = sol.run()
+    assert prog[-1].objv < prog[0].objv * 1.0001 and prog[-1].objv == prog[-1].objv
+    print(f"smoke ok: DARLIN {len(prog)} passes, objective {prog[0].objv:.2f} -> {prog[-1].objv:.2f}, |w|_0 {prog[-1].nnz_w}")

@@ -85,3 +85,30 @@ def stream_ptr() -> C.c_void_p:
 
 def ptr(t) -> C.c_void_p:
     return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+# ------------------------------------------------------------------ DARLIN structs
+class DarlinWorker(C.Structure):
+    _fields_ = [("col_ptr", C.c_void_p), ("row_idx", C.c_void_p), ("vals", C.c_void_p), ("y", C.c_void_p),
+                ("margin", C.c_void_p), ("w", C.c_void_p), ("delta", C.c_void_p), ("active", C.c_void_p),
+                ("gslot", C.c_void_p), ("gowner", C.c_void_p), ("dw", C.c_void_p), ("cols", C.c_int64),
+                ("rows", C.c_int), ("pad", C.c_int)]
+
+
+class DarlinPeers(C.Structure):
+    _fields_ = [("w", _P8), ("gu", _P8), ("arrive", _P8), ("updated", _P8), ("rank", C.c_int), ("world", C.c_int),
+                ("timeout_ns", C.c_uint64)]
+
+
+class DarlinServer(C.Structure):
+    _fields_ = [("delta", C.c_void_p), ("active", C.c_void_p), ("violation", C.c_void_p), ("slots", C.c_int64)]
+
+
+class DarlinSched(C.Structure):
+    _fields_ = [("order", C.c_void_p), ("blk_lc", C.c_void_p), ("blk_sl", C.c_void_p), ("nblk", C.c_int),
+                ("pad", C.c_int), ("seq0", C.c_uint64), ("local_bar", C.c_void_p), ("bar0", C.c_uint64),
+                ("abort_flag", C.c_void_p), ("status", C.c_void_p)]
+
+
+class DarlinHyper(C.Structure):
+    _fields_ = [("lam", C.c_float), ("eta", C.c_float), ("delta_max", C.c_float), ("kkt_threshold", C.c_float)]

@@ -1,0 +1,66 @@
+"""DARLIN pass kernel on one GPU against the fp64 CPU restatement of the reference."""
+import numpy as np
+import pytest
+import torch
+
+from baseline.cpu_ref.darlin_ref import DarlinConfig as RefConfig
+from baseline.cpu_ref.darlin_ref import DarlinRef
+from parameter_server_b200.data.synthetic import zipf_sparse_matrix
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(binary, rows=1500, cols=2048, nnz=16, seed=1):
+    off, idx, vals, y, _ = zipf_sparse_matrix(rows, cols, nnz, seed=seed, device="cuda", binary=binary, zipf_s=0.8)
+    # spread ids over a larger uint64 key space, keep order
+    keys = idx * 7919 + 3
+    return off, keys, vals, y
+
+
+@pytest.mark.parametrize("binary", [False, True])
+@pytest.mark.parametrize("impl", ["fused", "nccl"])
+def test_darlin_matches_oracle(binary, impl):
+    from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver
+    from parameter_server_b200.parallel.peer import PeerGroup
+
+    off, keys, vals, y = _problem(binary)
+    kw = dict(lambda1=0.3, max_pass=6, feature_block_ratio=1.0, kkt_ratio=10.0, seed=3)
+    sol = DarlinSolver(PeerGroup.single(torch.device("cuda", 0)), DarlinConfig(**kw), impl=impl)
+    sol.preprocess(off, keys, vals, y)
+    prog = sol.run()
+    ref = DarlinRef([(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64),
+                      None if vals is None else vals.cpu().numpy(), y.cpu().numpy())], None, RefConfig(**kw))
+    rprog = ref.run()
+    assert sol.nblk == len(ref.blocks) and sol.nblk > 4
+    assert len(prog) == len(rprog)
+    for p, r in zip(prog, rprog):
+        assert p.objv == pytest.approx(r.objv, rel=2e-3)
+        assert abs(p.nnz_w - r.nnz_w) <= max(3, 0.03 * r.nnz_w)
+        assert p.violation == pytest.approx(r.violation, rel=2e-2, abs=1e-3)
+    objs = [p.objv for p in prog]
+    assert all(b <= a * (1 + 1e-4) for a, b in zip(objs, objs[1:])), objs
+    k, w = sol.model()
+    rk, rw = ref.model()
+    common = np.intersect1d(k, rk)
+    assert len(common) >= 0.95 * max(len(k), len(rk))
+    wd = dict(zip(k.tolist(), w.tolist()))
+    rd = dict(zip(rk.tolist(), rw.tolist()))
+    err = np.array([wd[c] - rd[c] for c in common.tolist()])
+    assert np.abs(err).max() < 5e-2
+    sol.check_status()
+
+
+def test_darlin_model_dump(tmp_path):
+    from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver
+    from parameter_server_b200.parallel.peer import PeerGroup
+    from parameter_server_b200.utils.modelio import read_model_text
+
+    off, keys, vals, y = _problem(False, rows=600, cols=512)
+    sol = DarlinSolver(PeerGroup.single(torch.device("cuda", 0)), DarlinConfig(lambda1=0.2, max_pass=3))
+    sol.preprocess(off, keys, vals, y)
+    sol.run()
+    path = sol.save_model(str(tmp_path / "m"))
+    m = read_model_text(path)
+    k, w = sol.model()
+    assert len(m) == len(k) > 0
+    assert list(m.keys()) == sorted(m.keys())
