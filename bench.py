@@ -134,6 +134,7 @@ def run_ftrl(args) -> dict:
     ms = group.all_reduce_max(e0.elapsed_time(e1))
     group.barrier()
     launches = eng.kernel_launches - launches0
+    phases = eng.phase_times_us() if args.impl != "nccl" else None
     st = eng.read_stats()
     eng.check_status()
     # ---------------------------------------------------------------- end to end (public API)
@@ -173,7 +174,8 @@ def run_ftrl(args) -> dict:
                    "l2_policy": f"inputs larger than L2: ring of {ring} distinct minibatches "
                                 f"({batches[0].nbytes() >> 20} MiB each) plus {max_nnz * 4 >> 20} MiB slot map per step",
                    "mean_logloss_last": st["loss_sum"] / max(st["rows"], 1), "nnz_w": st["nnz_w"],
-                   "unique_keys_per_step": st["unique_keys"] / max(args.steps, 1)},
+                   "unique_keys_per_step": st["unique_keys"] / max(args.steps, 1),
+                   "phase_us_last_step_rank0": phases},
         "e2e": e2e,
         "gpu_launches": launches,
         "clocks": clocks,

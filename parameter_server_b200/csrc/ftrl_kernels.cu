@@ -30,21 +30,25 @@
 
 namespace psb {
 
-struct ShardState {  // 16 B of per-key state
+struct ShardState {  // per-key state as the update rule sees it
   float w;
   float z;
   uint32_t pos;  // rule 0: #positive rows seen; rule 1: bit pattern of Σg² (float)
   uint32_t neg;
 };
 
-// One slot of an owner's table: key and state share one 32-byte sector, so a pull probe
-// is one sector read and an update is one read-modify-write of the same sector.
+// One slot of an owner's table: 32 bytes = one DRAM/NVLink sector.  Key and weight sit in
+// the same 16 bytes, so a pull probe is ONE 16-byte peer load; an update is a
+// read-modify-write of the same sector.
 struct __align__(32) ShardSlot {
-  ShardState st;     // offset 0: accessed as one 16-byte vector
-  uint64_t key;      // offset 16: kEmptyKey when free
-  uint64_t reserved;
+  uint64_t key;      // offset 0: kEmptyKey when free
+  float w;           // offset 8
+  float z;           // offset 12
+  uint32_t pos;      // offset 16
+  uint32_t neg;      // offset 20
+  uint64_t reserved; // offset 24
 };
-static_assert(sizeof(ShardSlot) == 32 && offsetof(ShardSlot, key) == 16, "ShardSlot layout");
+static_assert(sizeof(ShardSlot) == 32 && offsetof(ShardSlot, w) == 8 && offsetof(ShardSlot, pos) == 16, "ShardSlot layout");
 
 struct FtrlHyper {
   float alpha, beta, l1, l2;
@@ -65,7 +69,7 @@ struct FtrlPeers {
   uint64_t* applied[PSB_MAX_RANKS];        // rank r: [owner] = epoch<<32
   uint64_t timeout_ns;
   uint32_t in_cap;
-  uint32_t pad;
+  uint32_t tab_shift;                      // 64 − log2(table capacity): slot = mix64(key) >> tab_shift
 };
 
 struct Minibatch {
@@ -94,6 +98,7 @@ struct LocalScratch {
   uint64_t* lt_keys;   // per-minibatch dedup table (all kEmptyKey between steps)
   LocalSlot* lt_val;   // payload per slot (one 16-byte sector: w, g, counts)
   uint64_t lt_mask;
+  uint64_t lt_shift;   // 64 − log2(local capacity): slot = mix64(key) >> lt_shift
   uint32_t* slot_of;   // nnz: local slot of each non-zero
   float* coef;         // rows: −y/(1+e^{y·Xw})
   float* xw;           // rows: X·w (predictions)
@@ -101,32 +106,70 @@ struct LocalScratch {
   uint32_t* recv_cnt;  // [PSB_MAX_RANKS]
   double* stats;       // [0] Σloss [1] rows [2] ‖w‖₁ [3] ‖w‖₂² [4] nnz(w) [5] unique keys [6] table entries
   uint32_t* status;    // StatusCode etc.
+  uint64_t* trace;     // optional [16]: globaltimer at phase boundaries of the last step (see kTrace*)
 };
+
+// trace slots: pull kernel 0 start, 1 localized, 2 gathered, 3 block-0 end;
+//              push kernel 4 start, 5 gradients done, 6 records sent, 7 all senders arrived, 8 applied
+#define PSB_TRACE(L, gtid, i) do { if ((L).trace != nullptr && (gtid) == 0) (L).trace[i] = globaltimer_ns(); } while (0)
 
 constexpr uint32_t kBadSlot = 0xFFFFFFFFu;
 
-__device__ __forceinline__ uint64_t shard_hash(uint64_t key) { return mix64(key) >> 20; }
+// Both tables index with the TOP bits of the same 64-bit hash.  A scan of the local table in
+// slot order therefore visits keys in (nearly) increasing shard-slot order, so the gather and
+// the owner-side update walk the big shard table monotonically instead of at random.
+__device__ __forceinline__ uint64_t shard_hash(uint64_t key, uint32_t shift) { return mix64(key) >> shift; }
 
 // ------------------------------------------------------------------ phases
 __device__ __forceinline__ void phase_localize(const Minibatch& M, const LocalScratch& L, int max_probe,
                                                size_t gtid, size_t gsz) {
-  for (int64_t e = (int64_t)gtid; e < M.nnz; e += (int64_t)gsz) {
-    const uint64_t key = M.keys[e];
-    uint64_t slot = table_find_or_insert(L.lt_keys, L.lt_mask, mix64(key), key, max_probe);
-    if (slot == ~0ull) {
-      set_status(L.status, kLocalTableFull, 0, 0);
-      slot = kBadSlot;
+  // four independent probes in flight per thread: the first table read of each key is issued
+  // before any of them is resolved
+#ifndef PSB_LOCALIZE_UNROLL
+#define PSB_LOCALIZE_UNROLL 1
+#endif
+  constexpr int U = PSB_LOCALIZE_UNROLL;
+  for (int64_t e = (int64_t)gtid; e < M.nnz; e += (int64_t)gsz * U) {
+    uint64_t key[U], h[U], cur[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int64_t i = e + (int64_t)k * (int64_t)gsz;
+      key[k] = i < M.nnz ? M.keys[i] : kEmptyKey;
     }
-    L.slot_of[e] = (uint32_t)slot;
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+#ifdef PSB_LOCAL_HASH_LOW
+      h[k] = mix64(key[k]) & L.lt_mask;
+#else
+      h[k] = (mix64(key[k]) >> L.lt_shift) & L.lt_mask;
+#endif
+      cur[k] = key[k] != kEmptyKey ? L.lt_keys[h[k]] : 0ull;
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int64_t i = e + (int64_t)k * (int64_t)gsz;
+      if (i >= M.nnz) continue;
+      uint64_t slot = h[k];
+      if (cur[k] != key[k]) {
+        slot = table_find_or_insert(L.lt_keys, L.lt_mask, h[k], key[k], max_probe);
+        if (slot == ~0ull) {
+          set_status(L.status, kLocalTableFull, 0, 0);
+          slot = kBadSlot;
+        }
+      }
+      L.slot_of[i] = (uint32_t)slot;
+    }
   }
 }
 
-// weight of `key` in owner's table (peer memory), 0 when absent
-__device__ __forceinline__ float probe_weight(const ShardSlot* tab, uint64_t mask, uint64_t key, int max_probe) {
-  uint64_t slot = shard_hash(key) & mask;
+// weight of `key` in owner's table (peer memory), 0 when absent; one 16-byte load per probe
+__device__ __forceinline__ float probe_weight(const ShardSlot* tab, uint64_t mask, uint32_t shift, uint64_t key,
+                                              int max_probe) {
+  uint64_t slot = shard_hash(key, shift) & mask;
   for (int i = 0; i < max_probe; ++i) {
-    const uint64_t k = ld_relaxed_sys_u64(&tab[slot].key);
-    if (k == key) return ld_relaxed_sys_f32(&tab[slot].st.w);
+    uint64_t k, wz;
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(k), "=l"(wz) : "l"(tab + slot) : "memory");
+    if (k == key) return __uint_as_float((uint32_t)wz);
     if (k == kEmptyKey) return 0.f;
     slot = (slot + 1) & mask;
   }
@@ -141,7 +184,7 @@ __device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScra
     if (key != kEmptyKey) {
       const int o = route_owner(P.seps, key);
       LocalSlot v;
-      v.w = probe_weight(P.tab[o], P.tab_mask, key, P.max_probe);
+      v.w = probe_weight(P.tab[o], P.tab_mask, P.tab_shift, key, P.max_probe);
       v.g = 0.f;
       v.pos = 0.f;
       v.neg = 0.f;
@@ -326,7 +369,7 @@ __device__ __forceinline__ void ftrl_update(ShardState& e, float g, uint32_t dpo
   dnnz += (w != 0.f && w_old == 0.f) - (w == 0.f && w_old != 0.f);
 }
 
-__device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, int max_probe,
+__device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
                                             const uint64_t* rk, const float* rg, const uint64_t* rc,
                                             uint32_t n, const FtrlHyper& h, double* stats, uint32_t* status,
                                             size_t gtid, size_t gsz) {
@@ -337,7 +380,7 @@ __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, int m
     if (key == kEmptyKey) continue;
     const float g = __ldcg(rg + i);
     const uint64_t c = __ldcg(rc + i);
-    uint64_t slot = shard_hash(key) & mask;
+    uint64_t slot = shard_hash(key, shift) & mask;
     bool found = false;
     for (int p = 0; p < max_probe; ++p) {
       const uint64_t cur = tab[slot].key;
@@ -354,12 +397,13 @@ __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, int m
       set_status(status, kShardTableFull, 0, 0);
       continue;
     }
-    float4 raw = *reinterpret_cast<float4*>(&tab[slot].st);
+    const float2 wz = *reinterpret_cast<const float2*>(&tab[slot].w);
+    const uint2 pn = *reinterpret_cast<const uint2*>(&tab[slot].pos);
     ShardState e;
-    e.w = raw.x; e.z = raw.y; e.pos = __float_as_uint(raw.z); e.neg = __float_as_uint(raw.w);
+    e.w = wz.x; e.z = wz.y; e.pos = pn.x; e.neg = pn.y;
     ftrl_update(e, g, (uint32_t)(c >> 32), (uint32_t)c, h, dn1, dn2, dnnz);
-    raw.x = e.w; raw.y = e.z; raw.z = __uint_as_float(e.pos); raw.w = __uint_as_float(e.neg);
-    *reinterpret_cast<float4*>(&tab[slot].st) = raw;
+    *reinterpret_cast<float2*>(&tab[slot].w) = make_float2(e.w, e.z);
+    *reinterpret_cast<uint2*>(&tab[slot].pos) = make_uint2(e.pos, e.neg);
   }
   dn1 = warp_sum(dn1);
   dn2 = warp_sum(dn2);
@@ -388,11 +432,15 @@ ftrl_pull_spmv_kernel(FtrlPeers P, Minibatch M, LocalScratch L, uint32_t epoch) 
     if (!ok) set_status(L.status, kWaitTimeout, threadIdx.x, 1);
   }
   if (gtid == 0) L.stats[1] += (double)M.rows;
+  PSB_TRACE(L, gtid, 0);
   phase_localize(M, L, P.max_probe, gtid, gsz);
   grid.sync();
+  PSB_TRACE(L, gtid, 1);
   phase_gather(P, L, gtid, gsz);
   grid.sync();
+  PSB_TRACE(L, gtid, 2);
   phase_spmv_loss(M, L, gtid >> 5, gsz >> 5, lane);
+  PSB_TRACE(L, gtid, 3);
 }
 
 __global__ void __launch_bounds__(256)
@@ -405,10 +453,13 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
 
   __shared__ HotCache hot;
   __shared__ uint32_t s_cnt[PSB_MAX_RANKS], s_base[PSB_MAX_RANKS];
+  PSB_TRACE(L, gtid, 4);
   phase_grad(M, L, gtid >> 5, gsz >> 5, lane, &hot);
   grid.sync();
+  PSB_TRACE(L, gtid, 5);
   phase_route_send(P, L, s_cnt, s_base);
   grid.sync();
+  PSB_TRACE(L, gtid, 6);
   // publish this sender's record count to every owner, then wait for all senders
   if (blockIdx.x == 0 && threadIdx.x < world) {
     const int t = threadIdx.x;
@@ -423,15 +474,17 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
     if (!ok) set_status(L.status, kWaitTimeout, t, 2);
   }
   grid.sync();
+  PSB_TRACE(L, gtid, 7);
   // apply sender by sender (the reference applies each worker's push separately)
   for (int s = 0; s < world; ++s) {
     const uint32_t n = __ldcg(L.recv_cnt + s);
     const size_t off = (size_t)s * P.in_cap;
-    phase_apply(P.tab[P.rank], P.tab_mask, P.max_probe,
+    phase_apply(P.tab[P.rank], P.tab_mask, P.tab_shift, P.max_probe,
                 P.in_keys[P.rank] + off, P.in_g[P.rank] + off, P.in_cnt[P.rank] + off, n, H, L.stats,
                 L.status, gtid, gsz);
     grid.sync();
   }
+  PSB_TRACE(L, gtid, 8);
   if (blockIdx.x == 0 && threadIdx.x < world) {
     __threadfence_system();
     st_release_sys_u64(P.applied[threadIdx.x] + P.rank, (uint64_t)epoch << 32);
@@ -490,10 +543,10 @@ __global__ void k_pack_keys(KeySeps seps, LocalScratch L, uint32_t* cursors, uin
   }
 }
 // owner side of an unfused pull: w for each requested key (0 when absent)
-__global__ void k_lookup(const ShardSlot* tab, uint64_t mask, int max_probe,
+__global__ void k_lookup(const ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
                          const uint64_t* keys, uint32_t n, float* out_w) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    out_w[i] = probe_weight(tab, mask, keys[i], max_probe);
+    out_w[i] = probe_weight(tab, mask, shift, keys[i], max_probe);
 }
 __global__ void k_scatter_w(const uint32_t* slots, const float* w, uint32_t n, LocalScratch L) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -515,10 +568,10 @@ __global__ void k_pack_push(const uint32_t* slots, uint32_t n, LocalScratch L, f
     L.lt_keys[s] = kEmptyKey;
   }
 }
-__global__ void k_apply(ShardSlot* tab, uint64_t mask, int max_probe, const uint64_t* rk,
+__global__ void k_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe, const uint64_t* rk,
                         const float* rg, const uint64_t* rc, uint32_t n, FtrlHyper h, double* stats,
                         uint32_t* status) {
-  phase_apply(tab, mask, max_probe, rk, rg, rc, n, h, stats, status,
+  phase_apply(tab, mask, shift, max_probe, rk, rg, rc, n, h, stats, status,
               (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
 }
 __global__ void k_clear_local(LocalScratch L) {
@@ -530,10 +583,10 @@ __global__ void k_dump_nonzero(const ShardSlot* tab, uint64_t mask, uint64_t* ou
                                float* out_w, unsigned long long* count) {
   for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= mask; s += (size_t)gridDim.x * blockDim.x) {
     const uint64_t k = tab[s].key;
-    if (k != kEmptyKey && tab[s].st.w != 0.f) {
+    if (k != kEmptyKey && tab[s].w != 0.f) {
       const unsigned long long at = atomicAdd(count, 1ull);
       out_keys[at] = k;
-      out_w[at] = tab[s].st.w;
+      out_w[at] = tab[s].w;
     }
   }
 }
@@ -609,9 +662,9 @@ int psb_ftrl_pack_keys(const KeySeps* seps, const LocalScratch* L, uint32_t* cur
   k_pack_keys<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*seps, *L, cursors, out_keys, out_slot);
   return (int)cudaGetLastError();
 }
-int psb_ftrl_lookup(const void* tab, uint64_t mask, int max_probe, const uint64_t* keys,
+int psb_ftrl_lookup(const void* tab, uint64_t mask, uint32_t shift, int max_probe, const uint64_t* keys,
                     uint32_t n, float* out_w, cudaStream_t s) {
-  k_lookup<<<flat_grid(n), 256, 0, s>>>((const ShardSlot*)tab, mask, max_probe, keys, n, out_w);
+  k_lookup<<<flat_grid(n), 256, 0, s>>>((const ShardSlot*)tab, mask, shift, max_probe, keys, n, out_w);
   return (int)cudaGetLastError();
 }
 int psb_ftrl_scatter_w(const uint32_t* slots, const float* w, uint32_t n, const LocalScratch* L, cudaStream_t s) {
@@ -623,10 +676,10 @@ int psb_ftrl_pack_push(const uint32_t* slots, uint32_t n, const LocalScratch* L,
   k_pack_push<<<flat_grid(n), 256, 0, s>>>(slots, n, *L, out_g, out_cnt);
   return (int)cudaGetLastError();
 }
-int psb_ftrl_apply(void* tab, uint64_t mask, int max_probe, const uint64_t* rk, const float* rg,
+int psb_ftrl_apply(void* tab, uint64_t mask, uint32_t shift, int max_probe, const uint64_t* rk, const float* rg,
                    const uint64_t* rc, uint32_t n, const FtrlHyper* h, double* stats, uint32_t* status,
                    cudaStream_t s) {
-  k_apply<<<flat_grid(n), 256, 0, s>>>((ShardSlot*)tab, mask, max_probe, rk, rg, rc, n, *h, stats, status);
+  k_apply<<<flat_grid(n), 256, 0, s>>>((ShardSlot*)tab, mask, shift, max_probe, rk, rg, rc, n, *h, stats, status);
   return (int)cudaGetLastError();
 }
 int psb_ftrl_clear_local(const LocalScratch* L, cudaStream_t s) {

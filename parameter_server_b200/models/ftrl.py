@@ -89,9 +89,9 @@ class FTRLEngine:
         i64, f32 = torch.int64, torch.float32
 
         # --- server side: shard table + inbox + flags (peer-addressable)
-        # one 32-byte slot per key: [(w,z), (pos,neg), key, reserved] viewed as 4 x int64
+        # one 32-byte slot per key: [key, (w,z), (pos,neg), reserved] viewed as 4 x int64
         self.tab = group.alloc((self.cap, 4), i64, fill=0)
-        self.tab.local[:, 2] = -1
+        self.tab.local[:, 0] = -1
         self.in_keys = group.alloc((W * self.in_cap,), i64, fill=-1)
         self.in_g = group.alloc((W * self.in_cap,), f32)
         self.in_cnt = group.alloc((W * self.in_cap,), i64)
@@ -129,12 +129,16 @@ class FTRLEngine:
             P.applied[r] = self.applied.ptrs[r]
         P.timeout_ns = int(timeout_s * 1e9)
         P.in_cap = self.in_cap
+        P.tab_shift = 64 - (self.cap.bit_length() - 1)
         self._P = P
         L = N.LocalScratch()
         L.lt_keys, L.lt_val, L.lt_mask = self.lt_keys.data_ptr(), self.lt_val.data_ptr(), self.lcap - 1
+        L.lt_shift = 64 - (self.lcap.bit_length() - 1)
         L.slot_of, L.coef, L.xw = self.slot_of.data_ptr(), self.coef.data_ptr(), self.xw.data_ptr()
         L.send_cnt, L.recv_cnt = self.send_cnt.data_ptr(), self.recv_cnt.data_ptr()
         L.stats, L.status = self.stats.data_ptr(), self.status.data_ptr()
+        self.trace = torch.zeros((16,), dtype=torch.int64, device=d)
+        L.trace = self.trace.data_ptr()
         self._L = L
         self._H = hyper.native()
         self._lib = N.lib()
@@ -230,7 +234,7 @@ class FTRLEngine:
         rw = torch.empty((nr,), dtype=torch.float32, device=self.dev)
         if nr:
             N.check(lib.psb_ftrl_lookup(N.ptr(self.tab.local), C.c_uint64(self.cap - 1),
-                                        self._P.max_probe, N.ptr(rkeys), C.c_uint32(nr), N.ptr(rw), s), "lookup")
+                                        C.c_uint32(self._P.tab_shift), self._P.max_probe, N.ptr(rkeys), C.c_uint32(nr), N.ptr(rw), s), "lookup")
             self.kernel_launches += 1
         if W > 1:
             uw = torch.empty((total,), dtype=torch.float32, device=self.dev)
@@ -267,7 +271,8 @@ class FTRLEngine:
         for n in in_counts:
             if n:
                 N.check(lib.psb_ftrl_apply(N.ptr(self.tab.local),
-                                           C.c_uint64(self.cap - 1), self._P.max_probe, N.ptr(rkeys[off:off + n]),
+                                           C.c_uint64(self.cap - 1), C.c_uint32(self._P.tab_shift), self._P.max_probe,
+                                           N.ptr(rkeys[off:off + n]),
                                            N.ptr(rg[off:off + n]), N.ptr(rc[off:off + n]), C.c_uint32(n),
                                            C.byref(self._H), N.ptr(self.stats), N.ptr(self.status), s), "apply")
                 self.kernel_launches += 1
@@ -282,6 +287,13 @@ class FTRLEngine:
             self.stats[5].zero_()
         return {"loss_sum": v[0], "rows": v[1], "norm1": v[2], "norm2_sq": v[3], "nnz_w": v[4],
                 "unique_keys": v[5], "table_entries": v[6]}
+
+    def phase_times_us(self) -> dict:
+        """Durations (µs) of the phases of the last fused step, from in-kernel globaltimer marks."""
+        t = self.trace.tolist()
+        d = lambda a, b: (t[b] - t[a]) / 1e3
+        return {"localize": d(0, 1), "gather": d(1, 2), "spmv_loss": d(2, 3), "kernel_gap": d(3, 4), "grad": d(4, 5),
+                "route_send": d(5, 6), "wait_senders": d(6, 7), "apply": d(7, 8), "step": d(0, 8)}
 
     def penalty(self, st: dict) -> float:
         """λ₁‖w‖₁ + ½λ₂·sqrt(‖w‖₂²) exactly as FTRLModel::objv (src/linear_method/ftrl_model.h:31)."""

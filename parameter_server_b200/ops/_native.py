@@ -44,7 +44,7 @@ class FtrlPeers(C.Structure):
     _fields_ = [("seps", KeySeps), ("rank", C.c_int), ("max_probe", C.c_int), ("tab_mask", C.c_uint64),
                 ("tab", _P8), ("in_keys", _P8), ("in_g", _P8), ("in_cnt", _P8),
                 ("in_flag", _P8), ("applied", _P8), ("timeout_ns", C.c_uint64), ("in_cap", C.c_uint32),
-                ("pad", C.c_uint32)]
+                ("tab_shift", C.c_uint32)]
 
 
 class Minibatch(C.Structure):
@@ -54,9 +54,9 @@ class Minibatch(C.Structure):
 
 class LocalScratch(C.Structure):
     _fields_ = [("lt_keys", C.c_void_p), ("lt_val", C.c_void_p),
-                ("lt_mask", C.c_uint64), ("slot_of", C.c_void_p), ("coef", C.c_void_p), ("xw", C.c_void_p),
+                ("lt_mask", C.c_uint64), ("lt_shift", C.c_uint64), ("slot_of", C.c_void_p), ("coef", C.c_void_p), ("xw", C.c_void_p),
                 ("send_cnt", C.c_void_p), ("recv_cnt", C.c_void_p), ("stats", C.c_void_p),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("trace", C.c_void_p)]
 
 
 def lib() -> C.CDLL:

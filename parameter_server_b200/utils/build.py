@@ -88,7 +88,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     for src in sources:
         obj = OBJ / (src.stem + ".o")
         if force or _newer([src] + headers, obj):
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC)]
+            cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("PSB_NVCC_EXTRA", "").split(), "-I", str(CSRC)]
             cmd += ["-c", str(src), "-o", str(obj)]
             jobs.append((cmd, OBJ / (src.stem + ".log")))
     if jobs:

@@ -1,0 +1,70 @@
+"""Child process of the multi-GPU DARLIN test: every rank owns a rows shard and a key range;
+rank 0 replays the run on the fp64 oracle with the same shards and compares per-pass progress
+and the merged model.  Exit code 0 = match."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from baseline.cpu_ref.darlin_ref import DarlinConfig as RefConfig  # noqa: E402
+from baseline.cpu_ref.darlin_ref import DarlinRef  # noqa: E402
+from parameter_server_b200.data.synthetic import zipf_sparse_matrix  # noqa: E402
+from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver  # noqa: E402
+from parameter_server_b200.parallel.peer import PeerGroup  # noqa: E402
+
+
+def shard(off, keys, vals, y, r, W):
+    n = y.numel()
+    r0, r1 = n * r // W, n * (r + 1) // W
+    p0, p1 = int(off[r0].item()), int(off[r1].item())
+    return (off[r0:r1 + 1] - p0).contiguous(), keys[p0:p1].contiguous(), None if vals is None else vals[p0:p1].contiguous(), y[r0:r1].contiguous()
+
+
+def main():
+    impl = sys.argv[1] if len(sys.argv) > 1 else "fused"
+    group = PeerGroup.from_env()
+    rank, W, dev = group.rank, group.world, group.device
+    off, idx, vals, y, _ = zipf_sparse_matrix(2400, 3000, 14, seed=5, device=dev, zipf_s=0.8)
+    keys = idx * 104729 + 11
+    kw = dict(lambda1=0.3, max_pass=5, feature_block_ratio=1.0, seed=2)
+    sol = DarlinSolver(group, DarlinConfig(**kw), impl=impl)
+    sol.preprocess(*shard(off, keys, vals, y, rank, W))
+    prog = sol.run()
+    sol.check_status()
+    k, w = sol.model()
+    gathered = [None] * W
+    dist.all_gather_object(gathered, (k, w), group=group.group)
+    ok = True
+    if rank == 0:
+        shards = []
+        for r in range(W):
+            o, kk, vv, yy = shard(off, keys, vals, y, r, W)
+            shards.append((o.cpu().numpy(), kk.cpu().numpy().view(np.uint64), vv.cpu().numpy(), yy.cpu().numpy()))
+        ref = DarlinRef(shards, None, RefConfig(**kw))
+        rprog = ref.run()
+        ok &= len(prog) == len(rprog)
+        for p, q in zip(prog, rprog):
+            ok &= abs(p.objv / q.objv - 1) < 2e-3 and abs(p.nnz_w - q.nnz_w) <= max(3, 0.03 * q.nnz_w)
+        allk = np.concatenate([g[0] for g in gathered])
+        allw = np.concatenate([g[1] for g in gathered])
+        ok &= bool(np.all(np.diff(allk.astype(np.float64)) > 0))      # shards are disjoint ascending key ranges
+        rk, rw = ref.model()
+        common = np.intersect1d(allk, rk)
+        ok &= len(common) >= 0.95 * max(len(allk), len(rk))
+        wd, rd = dict(zip(allk.tolist(), allw.tolist())), dict(zip(rk.tolist(), rw.tolist()))
+        ok &= max(abs(wd[c] - rd[c]) for c in common.tolist()) < 5e-2
+        print(f"impl={impl} world={W} passes={len(prog)} objv={prog[-1].objv:.4f} ref={rprog[-1].objv:.4f} "
+              f"shard_sizes={[len(g[0]) for g in gathered]} match={bool(ok)}", flush=True)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.broadcast(flag, 0, group=group.group)
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

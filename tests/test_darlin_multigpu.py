@@ -1,0 +1,33 @@
+"""DARLIN over peer memory on 2+ GPUs == unfused NCCL baseline == fp64 oracle."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(nproc, impl, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_darlin_worker.py"), impl]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+
+
+@pytest.mark.parametrize("impl", ["fused", "nccl"])
+def test_two_gpus_match_oracle(impl):
+    r = _launch(2, impl, 29551 if impl == "fused" else 29552)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "match=True" in r.stdout
+
+
+def test_all_gpus_match_oracle():
+    import torch
+
+    n = torch.cuda.device_count()
+    if n < 4:
+        pytest.skip("needs >= 4 GPUs")
+    r = _launch(n, "fused", 29553)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "match=True" in r.stdout
