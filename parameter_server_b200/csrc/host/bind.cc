@@ -1,0 +1,371 @@
+// pybind11 surface of the host runtime (module `_psb_host`).  Python sees nodes, vans, the post
+// office, customers and messages (control plane), the data-ingest classes and the host numeric
+// containers.  Blocking calls release the GIL; callbacks from executor threads take it.
+#include <pybind11/functional.h>
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "data.h"
+#include "kv.h"
+#include "runtime.h"
+
+namespace py = pybind11;
+using namespace psb;
+
+namespace {
+
+template <typename T>
+py::array_t<T> to_array(const std::vector<T>& v) {
+  py::array_t<T> a((py::ssize_t)v.size());
+  if (!v.empty()) std::memcpy(a.mutable_data(), v.data(), v.size() * sizeof(T));
+  return a;
+}
+template <typename T>
+using carray = py::array_t<T, py::array::c_style | py::array::forcecast>;
+
+py::dict slot_info_dict(const SlotInfo& s) {
+  py::dict d;
+  d["id"] = s.id;
+  d["format"] = s.format == SlotFormat::DENSE ? "DENSE" : s.format == SlotFormat::SPARSE ? "SPARSE" : "SPARSE_BINARY";
+  d["min_key"] = s.min_key; d["max_key"] = s.max_key; d["nnz_ele"] = s.nnz_ele; d["nnz_ex"] = s.nnz_ex;
+  return d;
+}
+py::dict example_info_dict(const ExampleInfo& e) {
+  py::dict d, slots;
+  for (auto& kv : e.slot) slots[py::int_(kv.first)] = slot_info_dict(kv.second);
+  d["num_ex"] = e.num_ex;
+  d["slot"] = slots;
+  d["text"] = e.to_text();
+  return d;
+}
+py::dict slots_to_dict(const std::map<int, SlotData>& slots, uint64_t num_ex) {
+  py::dict out;
+  for (auto& kv : slots) {
+    py::dict s;
+    const SlotData& sd = kv.second;
+    if (kv.first == 0) {
+      s["value"] = to_array(sd.val);
+    } else {
+      std::vector<uint64_t> off(num_ex + 1, 0);
+      for (size_t i = 0; i < sd.row_siz.size() && i < num_ex; ++i) off[i + 1] = off[i] + sd.row_siz[i];
+      for (size_t i = sd.row_siz.size(); i < num_ex; ++i) off[i + 1] = off[i];
+      s["offset"] = to_array(off);
+      s["index"] = to_array(sd.col_idx);
+      s["value"] = to_array(sd.val);
+    }
+    out[py::int_(kv.first)] = s;
+  }
+  return out;
+}
+
+// A Python callable that may be copied and destroyed on threads that do not hold the GIL.
+inline std::shared_ptr<py::object> hold(py::object o) {
+  return std::shared_ptr<py::object>(new py::object(std::move(o)), [](py::object* p) { py::gil_scoped_acquire g; delete p; });
+}
+
+struct PyCustomer : public Customer {
+  using Customer::Customer;
+};
+
+MessagePtr make_message(const std::string& recver, int type, int cmd, const std::string& payload, py::object key,
+                        const std::vector<py::bytes>& values, int time, int wait_time, int channel, py::object key_range,
+                        uint32_t flags, int aux, bool erase_key_cache) {
+  auto m = std::make_shared<Message>();
+  m->recver = recver;
+  m->task.type = type;
+  m->task.cmd = cmd;
+  m->task.msg = payload;
+  m->task.time = time;
+  m->task.wait_time = wait_time;
+  m->task.key_channel = channel;
+  m->task.flags = flags;
+  m->task.aux = aux;
+  m->task.erase_key_cache = erase_key_cache;
+  if (!key.is_none()) {
+    m->key = key.cast<std::string>();
+    m->task.has_key = true;
+  }
+  if (!key_range.is_none()) {
+    auto r = key_range.cast<std::pair<uint64_t, uint64_t>>();
+    m->task.key_range = Range(r.first, r.second);
+    m->task.has_key_range = true;
+  }
+  for (auto& v : values) m->value.push_back(v);
+  return m;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_psb_host, m) {
+  m.doc() = "host runtime of parameter_server_b200 (control plane, data ingest, host containers)";
+
+  // ---------------------------------------------------------------- hashing / util
+  m.def("crc32c", [](py::bytes b) { std::string s = b; return crc32c_value(s.data(), s.size()); });
+  m.def("crc32c_extend", [](uint32_t c, py::bytes b) { std::string s = b; return crc32c_extend(c, s.data(), s.size()); });
+  m.def("crc32c_mask", &crc32c_mask);
+  m.def("crc32c_unmask", &crc32c_unmask);
+  m.def("murmur3_x64_128", [](py::bytes b, uint32_t seed) { std::string s = b; uint64_t o[2]; murmur3_x64_128(s.data(), (int)s.size(), seed, o); return std::make_pair(o[0], o[1]); });
+  m.def("shuffle_feature_id", &shuffle_feature_id);
+  m.def("djb_hash32", &djb_hash32);
+  m.def("key_signature", [](py::bytes b) { return key_signature(b); });
+  m.def("resource_usage", [] {
+    double rss, virt; uint64_t pj, hj, in, out;
+    ResUsage::memory_mb(&rss, &virt); ResUsage::cpu_jiffies(&pj, &hj); ResUsage::net_bytes(&in, &out);
+    py::dict d; d["rss_mb"] = rss; d["virt_mb"] = virt; d["proc_jiffies"] = pj; d["host_jiffies"] = hj; d["net_in"] = in; d["net_out"] = out;
+    return d;
+  });
+  m.def("parallel_sort_u64", [](carray<uint64_t> a, int threads) {
+    std::vector<uint64_t> v(a.data(), a.data() + a.size());
+    { py::gil_scoped_release r; parallel_sort(v.begin(), v.end(), threads, std::less<uint64_t>()); }
+    return to_array(v);
+  });
+  m.def("kv_partition", [](carray<uint64_t> keys, carray<double> vals, std::vector<uint64_t> pivots) {
+    std::vector<uint64_t> k(keys.data(), keys.data() + keys.size());
+    std::vector<double> v(vals.data(), vals.data() + vals.size());
+    auto off = kv_partition(k.data(), v.empty() ? (double*)nullptr : v.data(), k.size(), pivots);
+    return py::make_tuple(to_array(k), to_array(v), off);
+  });
+  m.def("zlib_roundtrip", [](py::bytes b) { std::string s = b; std::string z = zlib_compress(s.data(), s.size()); std::string o(s.size(), '\0'); bool ok = zlib_uncompress(z.data(), z.size(), &o[0], o.size()); return py::make_tuple(ok, z.size(), py::bytes(o)); });
+  m.def("record_write", [](const std::string& path, const std::vector<py::bytes>& recs) {
+    auto f = File::open(path, "w"); if (!f) return false; RecordWriter w(f.get());
+    for (auto& r : recs) if (!w.write(r)) return false;
+    return true;
+  });
+  m.def("record_read", [](const std::string& path) {
+    std::vector<py::bytes> out; auto f = File::open(path, "r"); if (!f) return out; RecordReader r(f.get()); std::string s;
+    while (r.read(&s)) out.emplace_back(s);
+    return out;
+  });
+
+  // ---------------------------------------------------------------- sorted-key algorithms
+  m.def("set_union", [](carray<uint64_t> a, carray<uint64_t> b) { return to_array(set_union(a.data(), a.size(), b.data(), b.size())); });
+  m.def("set_intersection", [](carray<uint64_t> a, carray<uint64_t> b) { return to_array(set_intersection(a.data(), a.size(), b.data(), b.size())); });
+  m.def("find_range", [](carray<uint64_t> a, uint64_t lo, uint64_t hi) { return find_range(a.data(), a.size(), Range(lo, hi)); });
+  m.def("match", [](carray<uint64_t> dst_key, py::array_t<double> dst_val, carray<uint64_t> src_key, carray<double> src_val, int k, bool add, int threads) {
+    return parallel_match_sorted(dst_key.data(), dst_key.size(), dst_val.mutable_data(), src_key.data(), src_key.size(), src_val.data(), (size_t)k,
+                                 add ? MatchOp::ADD : MatchOp::ASSIGN, threads);
+  }, py::arg("dst_key"), py::arg("dst_val"), py::arg("src_key"), py::arg("src_val"), py::arg("k") = 1, py::arg("add") = false, py::arg("threads") = 1);
+  m.def("even_divide", [](uint64_t b, uint64_t e, size_t n, size_t i) { Range r = Range(b, e).even_divide(n, i); return std::make_pair(r.begin, r.end); });
+  m.def("soft_thresholding", &soft_thresholding);
+  m.def("exact_auc", [](carray<float> label, carray<float> pred) { return exact_auc(label.data(), pred.data(), label.size()); });
+
+  py::class_<CountMin>(m, "CountMin")
+      .def(py::init<>())
+      .def("resize", &CountMin::resize, py::arg("n"), py::arg("k"), py::arg("saturate") = false)
+      .def("insert", [](CountMin& c, carray<uint64_t> k, carray<uint32_t> cnt) { for (py::ssize_t i = 0; i < k.size(); ++i) c.insert(k.data()[i], cnt.data()[i]); })
+      .def("query", [](const CountMin& c, carray<uint64_t> k) { std::vector<uint32_t> o(k.size()); for (py::ssize_t i = 0; i < k.size(); ++i) o[i] = c.query(k.data()[i]); return to_array(o); })
+      .def_static("hash", &CountMin::hash)
+      .def("size", &CountMin::size);
+  py::class_<FrequencyFilter>(m, "FrequencyFilter")
+      .def(py::init<>())
+      .def("resize", &FrequencyFilter::resize)
+      .def("empty", &FrequencyFilter::empty)
+      .def("clear", &FrequencyFilter::clear)
+      .def("insert_keys", [](FrequencyFilter& f, carray<uint64_t> k, carray<uint32_t> c) { f.insert_keys(k.data(), c.data(), k.size()); })
+      .def("query_keys", [](const FrequencyFilter& f, carray<uint64_t> k, uint32_t freq) { return to_array(f.query_keys(k.data(), k.size(), freq)); });
+  py::class_<Bitmap>(m, "Bitmap")
+      .def(py::init<size_t, bool>(), py::arg("n") = 0, py::arg("value") = false)
+      .def("resize", &Bitmap::resize, py::arg("n"), py::arg("value") = false)
+      .def("set", &Bitmap::set).def("clear", &Bitmap::clear).def("test", &Bitmap::test).def("fill", &Bitmap::fill)
+      .def("nnz", &Bitmap::nnz).def("size", &Bitmap::size);
+  py::class_<AUC>(m, "AUC")
+      .def(py::init<>())
+      .def("set_goodness", &AUC::set_goodness)
+      .def("add", [](AUC& a, carray<float> label, carray<float> pred) { a.add(label.data(), pred.data(), label.size()); })
+      .def("merge", [](AUC& a, const AUC& o) { a.merge(o); })
+      .def("merge_data", [](AUC& a, std::vector<int64_t> tk, std::vector<uint64_t> tc, std::vector<int64_t> fk, std::vector<uint64_t> fc) { a.merge(tk, tc, fk, fc); })
+      .def("data", [](const AUC& a) {
+        std::vector<int64_t> tk, fk; std::vector<uint64_t> tc, fc;
+        for (auto& kv : a.tp()) { tk.push_back(kv.first); tc.push_back(kv.second); }
+        for (auto& kv : a.fp()) { fk.push_back(kv.first); fc.push_back(kv.second); }
+        return py::make_tuple(tk, tc, fk, fc);
+      })
+      .def("clear", &AUC::clear).def("evaluate", &AUC::evaluate).def("accuracy", &AUC::accuracy, py::arg("threshold") = 0.0);
+  py::class_<KVVector>(m, "KVVector")
+      .def(py::init<int>(), py::arg("k") = 1)
+      .def("k", &KVVector::k)
+      .def("keys", [](KVVector& v, int ch) { return to_array(v.key(ch)); })
+      .def("values", [](KVVector& v, int ch) { return to_array(v.value(ch)); })
+      .def("set_keys", [](KVVector& v, int ch, carray<uint64_t> k) { v.key(ch).assign(k.data(), k.data() + k.size()); })
+      .def("set_values", [](KVVector& v, int ch, carray<double> a) { v.value(ch).assign(a.data(), a.data() + a.size()); })
+      .def("set_values_range", [](KVVector& v, int ch, size_t lo, carray<double> a) { std::copy(a.data(), a.data() + a.size(), v.value(ch).begin() + lo * v.k()); })
+      .def("merge_keys", [](KVVector& v, int ch, carray<uint64_t> k) { v.merge_keys(ch, k.data(), k.size()); })
+      .def("init_values", &KVVector::init_values, py::arg("ch"), py::arg("init") = 0.0)
+      .def("aggregate", [](KVVector& v, int ch, int t, uint64_t lo, uint64_t hi, carray<uint64_t> k, carray<double> a, int nval, int threads) {
+        return v.aggregate(ch, t, Range(lo, hi), k.data(), k.size(), a.data(), nval, threads);
+      })
+      .def("received", [](KVVector& v, int t) { auto r = v.received(t); return py::make_tuple(r.lo, r.hi, r.nval, to_array(r.vals)); })
+      .def("lookup", [](KVVector& v, int ch, carray<uint64_t> k) { return to_array(v.lookup(ch, k.data(), k.size())); })
+      .def("find", [](KVVector& v, int ch, uint64_t lo, uint64_t hi) { return v.find(ch, Range(lo, hi)); })
+      .def("clear", &KVVector::clear);
+
+  // ---------------------------------------------------------------- data ingest
+  py::enum_<TextFormat>(m, "TextFormat")
+      .value("PS_DENSE", TextFormat::PS_DENSE).value("PS_SPARSE", TextFormat::PS_SPARSE).value("PS_SPARSE_BINARY", TextFormat::PS_SPARSE_BINARY)
+      .value("ADFEA", TextFormat::ADFEA).value("LIBSVM", TextFormat::LIBSVM).value("TERAFEA", TextFormat::TERAFEA);
+  m.def("search_files", &search_files);
+  m.def("divide_files", &divide_files, py::arg("files"), py::arg("num_workers"), py::arg("load_limit") = 0);
+  m.def("parse_text", [](const std::string& text, TextFormat fmt, bool ignore_grp, bool shuffle, bool beta) {
+    ExampleParser p; p.init(fmt, ignore_grp, shuffle, beta);
+    std::map<int, SlotData> slots; ExampleInfo info; size_t bad = 0;
+    std::istringstream is(text); std::string line;
+    while (std::getline(is, line)) { if (line.empty()) continue; std::vector<char> buf(line.begin(), line.end()); buf.push_back(0); if (!p.parse_line(buf.data(), &slots, &info)) ++bad; }
+    ExampleParser::finish(&slots, info.num_ex);
+    return py::make_tuple(slots_to_dict(slots, info.num_ex), example_info_dict(info), bad);
+  }, py::arg("text"), py::arg("format"), py::arg("ignore_feature_group") = false, py::arg("shuffle_fea_id") = false, py::arg("add_beta_feature") = false);
+  py::class_<SlotReader>(m, "SlotReader")
+      .def(py::init<>())
+      .def("init", &SlotReader::init, py::arg("files"), py::arg("format"), py::arg("cache_dir"), py::arg("ignore_feature_group") = false,
+           py::arg("shuffle_fea_id") = false, py::arg("add_beta_feature") = false, py::arg("line_limit") = 0, py::arg("max_mb_per_thread") = 2048)
+      .def("read", [](SlotReader& r, int threads) { ExampleInfo info; int hits; { py::gil_scoped_release rel; hits = r.read(threads, &info); } return py::make_tuple(example_info_dict(info), hits); })
+      .def("index", [](SlotReader& r, int slot) { return to_array(r.index(slot)); })
+      .def("offset", [](SlotReader& r, int slot) { return to_array(r.offset(slot)); })
+      .def("value", [](SlotReader& r, int slot) { return to_array(r.value(slot)); })
+      .def("cache_name", &SlotReader::cache_name);
+  py::class_<StreamReader>(m, "StreamReader")
+      .def(py::init<>())
+      .def("init", &StreamReader::init, py::arg("files"), py::arg("format"), py::arg("ignore_feature_group") = false, py::arg("shuffle_fea_id") = false)
+      .def("read", [](StreamReader& r, size_t n) -> py::object {
+        std::map<int, SlotData> slots; ExampleInfo info; bool ok;
+        { py::gil_scoped_release rel; ok = r.read(n, &slots, &info); }
+        if (!ok) return py::none();
+        return py::make_tuple(slots_to_dict(slots, info.num_ex), example_info_dict(info));
+      });
+  m.def("write_bin_matrix", [](const std::string& name, bool row_major, uint64_t rows, uint64_t cols, carray<uint64_t> offset, carray<uint64_t> index, py::object value, int sizeof_index) {
+    BinMatrix b; b.row_major = row_major; b.rows = rows; b.cols = cols; b.sizeof_index = sizeof_index;
+    b.offset.assign(offset.data(), offset.data() + offset.size()); b.index.assign(index.data(), index.data() + index.size());
+    b.nnz = b.index.size(); b.binary = value.is_none();
+    if (!b.binary) { auto v = value.cast<carray<float>>(); b.value.assign(v.data(), v.data() + v.size()); }
+    return write_bin_matrix(name, b);
+  }, py::arg("name"), py::arg("row_major"), py::arg("rows"), py::arg("cols"), py::arg("offset"), py::arg("index"), py::arg("value") = py::none(), py::arg("sizeof_index") = 8);
+  m.def("read_bin_matrix", [](const std::string& name, uint64_t row_begin, uint64_t row_end) -> py::object {
+    BinMatrix b;
+    if (!read_bin_matrix(name, &b, row_begin, row_end)) return py::none();
+    py::dict d; d["row_major"] = b.row_major; d["rows"] = b.rows; d["cols"] = b.cols; d["nnz"] = b.nnz; d["binary"] = b.binary; d["sparse"] = b.sparse;
+    d["offset"] = to_array(b.offset); d["index"] = to_array(b.index); d["value"] = to_array(b.value);
+    return d;
+  }, py::arg("name"), py::arg("row_begin") = 0, py::arg("row_end") = ~0ull);
+
+  // ---------------------------------------------------------------- control plane
+  py::class_<Node>(m, "Node")
+      .def(py::init([](int role, std::string id, std::string host, int port) { Node n; n.role = role; n.id = id; n.hostname = host; n.port = port; n.key = Range::all(); return n; }),
+           py::arg("role"), py::arg("id"), py::arg("hostname") = "127.0.0.1", py::arg("port") = 0)
+      .def_readwrite("role", &Node::role).def_readwrite("id", &Node::id).def_readwrite("hostname", &Node::hostname).def_readwrite("port", &Node::port)
+      .def_property("key", [](const Node& n) { return std::make_pair(n.key.begin, n.key.end); }, [](Node& n, std::pair<uint64_t, uint64_t> r) { n.key = Range(r.first, r.second); })
+      .def("__repr__", [](const Node& n) { return "<Node " + n.id + " role=" + std::to_string(n.role) + " " + n.hostname + ":" + std::to_string(n.port) + " " + n.key.str() + ">"; });
+  m.attr("SERVER") = (int)Node::SERVER; m.attr("WORKER") = (int)Node::WORKER; m.attr("SCHEDULER") = (int)Node::SCHEDULER; m.attr("UNUSED") = (int)Node::UNUSED;
+  m.attr("kServerGroup") = kServerGroup; m.attr("kWorkerGroup") = kWorkerGroup; m.attr("kActiveGroup") = kActiveGroup;
+  m.attr("kReplicaGroup") = kReplicaGroup; m.attr("kOwnerGroup") = kOwnerGroup; m.attr("kLiveGroup") = kLiveGroup;
+  m.attr("TERMINATE") = (int)Task::TERMINATE; m.attr("REPLY") = (int)Task::REPLY; m.attr("MANAGE") = (int)Task::MANAGE;
+  m.attr("CALL_CUSTOMER") = (int)Task::CALL_CUSTOMER; m.attr("HEARTBEATING") = (int)Task::HEARTBEATING;
+
+  py::class_<InprocHub, std::shared_ptr<InprocHub>>(m, "InprocHub").def(py::init<>());
+  py::class_<Van, std::shared_ptr<Van>>(m, "Van")
+      .def("set_compress", &Van::set_compress)
+      .def("set_log", &Van::set_log)
+      .def("set_filter", [](Van& v, py::object f) {
+        if (f.is_none()) { v.set_filter(nullptr); return; }
+        v.set_filter([h = hold(f)](const Message& msg) { py::gil_scoped_acquire g; return (*h)(msg.sender, msg.recver, msg.task.type, msg.task.request, msg.task.time, msg.task.customer).cast<int>(); });
+      })
+      .def("sent_bytes", &Van::sent_bytes).def("recv_bytes", &Van::recv_bytes).def("dropped", &Van::dropped)
+      .def_property_readonly("my_node", [](Van& v) { return v.my_node; })
+      .def("close", &Van::close, py::call_guard<py::gil_scoped_release>());
+  py::class_<InprocVan, Van, std::shared_ptr<InprocVan>>(m, "InprocVan").def(py::init<std::shared_ptr<InprocHub>, const Node&>());
+  py::class_<TcpVan, Van, std::shared_ptr<TcpVan>>(m, "TcpVan")
+      .def(py::init<const Node&>())
+      .def("bind", [](TcpVan& v) { Status s = v.bind(); if (!s.ok()) throw std::runtime_error(s.ToString()); return v.my_node.port; })
+      .def("set_retries", &TcpVan::set_retries);
+
+  py::class_<Message, MessagePtr>(m, "Message")
+      .def_readonly("sender", &Message::sender).def_readonly("recver", &Message::recver)
+      .def_property_readonly("request", [](const Message& x) { return x.task.request; })
+      .def_property_readonly("type", [](const Message& x) { return x.task.type; })
+      .def_property_readonly("cmd", [](const Message& x) { return x.task.cmd; })
+      .def_property_readonly("time", [](const Message& x) { return x.task.time; })
+      .def_property_readonly("wait_time", [](const Message& x) { return x.task.wait_time; })
+      .def_property_readonly("payload", [](const Message& x) { return py::bytes(x.task.msg); })
+      .def_property_readonly("channel", [](const Message& x) { return x.task.key_channel; })
+      .def_property_readonly("flags", [](const Message& x) { return x.task.flags; })
+      .def_property_readonly("aux", [](const Message& x) { return x.task.aux; })
+      .def_property_readonly("has_key", [](const Message& x) { return x.task.has_key; })
+      .def_property_readonly("key_signature", [](const Message& x) { return x.task.key_signature; })
+      .def_property_readonly("key_range", [](const Message& x) -> py::object { if (!x.task.has_key_range) return py::none(); return py::cast(std::make_pair(x.task.key_range.begin, x.task.key_range.end)); })
+      .def_property_readonly("key", [](const Message& x) { return py::bytes(x.key); })
+      .def_property_readonly("values", [](const Message& x) { std::vector<py::bytes> v; for (auto& s : x.value) v.emplace_back(s); return v; })
+      .def_property_readonly("valid", [](const Message& x) { return x.valid; })
+      .def("defer", [](Message& x) { x.finished = false; }, "do not mark the task finished / ack it when process() returns")
+      .def("__repr__", [](const Message& x) { return "<Message " + x.short_debug() + ">"; });
+  m.def("slice_key_ordered", [](py::bytes key, std::vector<py::bytes> values, std::vector<uint64_t> sep, py::object key_range) {
+    auto msg = std::make_shared<Message>();
+    msg->key = key; msg->task.has_key = true;
+    for (auto& v : values) msg->value.push_back(v);
+    if (!key_range.is_none()) { auto r = key_range.cast<std::pair<uint64_t, uint64_t>>(); msg->task.key_range = Range(r.first, r.second); msg->task.has_key_range = true; }
+    return slice_key_ordered(msg, sep);
+  }, py::arg("key"), py::arg("values"), py::arg("separators"), py::arg("key_range") = py::none());
+  m.def("encode_decode", [](MessagePtr msg, bool compress) { std::string f = encode_message(*msg, compress); return py::make_tuple(f.size(), decode_message(f.data(), f.size())); });
+
+  py::class_<Postoffice>(m, "Postoffice")
+      .def(py::init<std::shared_ptr<Van>, int, int, int>(), py::arg("van"), py::arg("num_workers"), py::arg("num_servers"), py::arg("num_replicas") = 0)
+      .def_property_readonly("my_node", [](Postoffice& p) { return p.my_node(); })
+      .def("set_scheduler", &Postoffice::set_scheduler)
+      .def("start", &Postoffice::start)
+      .def("stop", &Postoffice::stop, py::call_guard<py::gil_scoped_release>())
+      .def("register_with_scheduler", &Postoffice::register_with_scheduler)
+      .def("wait_nodes_and_init", &Postoffice::wait_nodes_and_init, py::call_guard<py::gil_scoped_release>())
+      .def("wait_nodes_ready", &Postoffice::wait_nodes_ready, py::call_guard<py::gil_scoped_release>())
+      .def("set_nodes", &Postoffice::set_nodes)
+      .def("nodes", &Postoffice::nodes)
+      .def("stop_all", &Postoffice::stop_all, py::call_guard<py::gil_scoped_release>())
+      .def("wait_terminate", &Postoffice::wait_terminate, py::call_guard<py::gil_scoped_release>())
+      .def("set_key_cache", &Postoffice::set_key_cache)
+      .def("on_manage_app", [](Postoffice& p, py::function f) { p.on_manage_app([h = hold(f)](const std::string& s) { py::gil_scoped_acquire g; (*h)(py::bytes(s)); }); })
+      .def("start_heartbeat", [](Postoffice& p, double interval, py::object f) {
+        if (f.is_none()) { p.start_heartbeat(interval, nullptr); return; }
+        p.start_heartbeat(interval, [h = hold(f)]() { py::gil_scoped_acquire g; return (*h)().cast<std::string>(); });
+      })
+      .def("heartbeats", [](Postoffice& p) { py::dict d; const double now = now_seconds(); for (auto& kv : p.heartbeats()) d[py::str(kv.first)] = py::make_tuple(now - kv.second.when, py::bytes(kv.second.report)); return d; })
+      .def("dead_nodes", &Postoffice::dead_nodes)
+      .def("last_task_of", &Postoffice::last_task_of)
+      .def("sent_bytes", [](Postoffice& p) { return p.van()->sent_bytes(); })
+      .def("recv_bytes", [](Postoffice& p) { return p.van()->recv_bytes(); });
+
+  py::class_<PyCustomer>(m, "Customer")
+      .def(py::init([](Postoffice* po, std::string name, py::object process, bool key_ordered_slice) {
+        auto c = new PyCustomer(po, name);
+        c->key_ordered_slice = key_ordered_slice;
+        if (!process.is_none()) c->process = [h = hold(process)](const MessagePtr& msg) {
+          py::gil_scoped_acquire g;
+          try { (*h)(msg); } catch (py::error_already_set& e) { std::fprintf(stderr, "exception in process(): %s\n", e.what()); }
+        };
+        return c;
+      }), py::arg("postoffice"), py::arg("name"), py::arg("process") = py::none(), py::arg("key_ordered_slice") = true, py::keep_alive<1, 2>())
+      .def_property_readonly("name", &PyCustomer::name)
+      .def("submit", [](PyCustomer& c, const std::string& recver, int cmd, py::bytes payload, py::object key, std::vector<py::bytes> values, int time, int wait_time,
+                        int channel, py::object key_range, uint32_t flags, int aux, bool erase_key_cache, bool wait, py::object on_finish, int type) {
+        auto msg = make_message(recver, type, cmd, payload, key, values, time, wait_time, channel, key_range, flags, aux, erase_key_cache);
+        msg->wait = wait;
+        if (!on_finish.is_none()) msg->fin_handle = [h = hold(on_finish)]() {
+          py::gil_scoped_acquire g;
+          try { (*h)(); } catch (py::error_already_set& e) { std::fprintf(stderr, "exception in finish callback: %s\n", e.what()); }
+        };
+        py::gil_scoped_release rel;
+        return c.submit(msg);
+      }, py::arg("recver"), py::arg("cmd") = 0, py::arg("payload") = py::bytes(), py::arg("key") = py::none(), py::arg("values") = std::vector<py::bytes>(),
+         py::arg("time") = -1, py::arg("wait_time") = -1, py::arg("channel") = 0, py::arg("key_range") = py::none(), py::arg("flags") = 0, py::arg("aux") = 0,
+         py::arg("erase_key_cache") = false, py::arg("wait") = false, py::arg("on_finish") = py::none(), py::arg("type") = (int)Task::CALL_CUSTOMER)
+      .def("wait_out", &PyCustomer::wait_out, py::arg("node"), py::arg("time"), py::arg("timeout_s") = 1e9, py::call_guard<py::gil_scoped_release>())
+      .def("wait_in", &PyCustomer::wait_in, py::arg("node"), py::arg("time"), py::arg("timeout_s") = 1e9, py::call_guard<py::gil_scoped_release>())
+      .def("try_wait_out", &PyCustomer::try_wait_out)
+      .def("finish_in", &PyCustomer::finish_in)
+      .def("finish_out", &PyCustomer::finish_out)
+      .def("reply", [](PyCustomer& c, MessagePtr req, py::object key, std::vector<py::bytes> values, py::bytes payload) {
+        std::vector<std::string> v; for (auto& b : values) v.push_back(b);
+        c.reply(req, key.is_none() ? std::string() : key.cast<std::string>(), std::move(v), payload);
+      }, py::arg("request"), py::arg("key") = py::none(), py::arg("values") = std::vector<py::bytes>(), py::arg("payload") = py::bytes())
+      .def("take_replies", [](PyCustomer& c, int t) { py::dict d; for (auto& kv : c.exec()->take_replies(t)) d[py::str(kv.first)] = py::bytes(kv.second); return d; })
+      .def("group", [](PyCustomer& c, const std::string& id) { std::vector<std::string> ids; for (auto& r : c.exec()->group(id)) ids.push_back(r->node.id); return ids; })
+      .def("partition", [](PyCustomer& c, const std::string& id) { return c.exec()->partition(id); })
+      .def("processed", [](PyCustomer& c) { return (uint64_t)c.exec()->processed; })
+      .def("stop", [](PyCustomer& c) { c.exec()->stop(); }, py::call_guard<py::gil_scoped_release>());
+}

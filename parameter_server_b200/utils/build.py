@@ -119,14 +119,14 @@ def build_host(force: bool = False) -> Path | None:
     for src in sources:
         obj = OBJ / ("host_" + src.stem + ".o")
         if force or _newer([src] + headers, obj):
-            jobs.append(([os.environ.get("CXX", "g++"), *CXX_FLAGS, *inc, "-c", str(src), "-o", str(obj)], None))
+            jobs.append(([os.environ.get("PSB_CXX", "g++"), *CXX_FLAGS, *inc, "-c", str(src), "-o", str(obj)], None))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda j: _run(*j), jobs))
     objs = [OBJ / ("host_" + s.stem + ".o") for s in sources]
     out = host_lib_path()
     if force or jobs or _newer(objs, out):
-        _run([os.environ.get("CXX", "g++"), "-shared", "-o", str(out), *map(str, objs), "-pthread", "-lz"])
+        _run([os.environ.get("PSB_CXX", "g++"), "-shared", "-Wl,-Bsymbolic", "-o", str(out), *map(str, objs), "-pthread", "-lz"])
     return out
 
 

@@ -1,0 +1,166 @@
+"""Host utilities and containers (C++ via pybind11) against plain Python/NumPy restatements."""
+import numpy as np
+import pytest
+from hypothesis import given, settings
+from hypothesis import strategies as st
+
+from parameter_server_b200.runtime import host
+
+H = host()
+
+
+def test_crc32c_rfc3720_vectors():
+    assert H.crc32c(bytes(32)) == 0x8A9136AA
+    assert H.crc32c(bytes([0xFF] * 32)) == 0x62A8AB43
+    assert H.crc32c(bytes(range(32))) == 0x46DD794E
+    assert H.crc32c(bytes(range(31, -1, -1))) == 0x113FDB5C
+    assert H.crc32c(b"123456789") == 0xE3069283
+    assert H.crc32c_extend(H.crc32c(b"hello "), b"world") == H.crc32c(b"hello world")
+    c = H.crc32c(b"foo")
+    assert H.crc32c_unmask(H.crc32c_mask(c)) == c and H.crc32c_mask(c) != c
+
+
+def test_murmur_and_djb():
+    a = H.murmur3_x64_128(b"The quick brown fox jumps over the lazy dog", 0)
+    assert a == (0xE34BBC7BBC071B6C, 0x7A433CA9C49A9347)       # published reference digest, seed 0
+    assert H.murmur3_x64_128(b"", 0) == (0, 0)
+    ids = [H.shuffle_feature_id(i) for i in range(1000)]
+    assert len(set(ids)) == 1000
+    h = 5381
+    for ch in b"abc":
+        h = (h * 33 + ch) & 0xFFFFFFFF
+    assert H.djb_hash32("abc") == h
+
+
+@settings(max_examples=30, deadline=None)
+@given(st.lists(st.tuples(st.integers(0, 2**64 - 2), st.integers(1, 5)), min_size=1, max_size=200))
+def test_countmin_never_underestimates(pairs):
+    cm = H.CountMin()
+    cm.resize(4096, 2, True)
+    truth = {}
+    for k, c in pairs:
+        truth[k] = truth.get(k, 0) + c
+    keys = np.array([k for k, _ in pairs], dtype=np.uint64)
+    cnts = np.array([c for _, c in pairs], dtype=np.uint32)
+    cm.insert(keys, cnts)
+    uk = np.array(list(truth), dtype=np.uint64)
+    est = cm.query(uk)
+    for k, e in zip(uk.tolist(), est.tolist()):
+        assert e >= min(truth[k], 255)
+
+
+def test_frequency_filter_and_wrap():
+    f = H.FrequencyFilter()
+    f.resize(1 << 16, 2)
+    keys = np.arange(1000, dtype=np.uint64) * 7919
+    counts = np.where(np.arange(1000) % 10 == 0, 9, 1).astype(np.uint32)
+    f.insert_keys(keys, counts)
+    kept = f.query_keys(keys, 4)
+    assert set(keys[::10].tolist()) <= set(kept.tolist()) and len(kept) < 150
+    cm = H.CountMin()
+    cm.resize(64, 1, False)                      # uint8 counters wrap like the reference's
+    cm.insert(np.array([5], dtype=np.uint64), np.array([300], dtype=np.uint32))
+    assert cm.query(np.array([5], dtype=np.uint64))[0] == 300 % 256
+
+
+def test_bitmap():
+    b = H.Bitmap(130, False)
+    for i in (0, 63, 64, 129):
+        b.set(i)
+    assert b.nnz() == 4 and b.test(64) and not b.test(65)
+    b.clear(64)
+    assert b.nnz() == 3
+    b.fill(True)
+    assert b.nnz() == 130
+
+
+def test_auc_histogram_matches_exact():
+    rng = np.random.RandomState(0)
+    y = np.where(rng.rand(5000) < 0.3, 1, -1).astype(np.float32)
+    p = (rng.randn(5000) + 0.8 * (y > 0)).astype(np.float32)
+    exact = H.exact_auc(y, p)
+    pos, neg = p[y > 0], p[y <= 0]
+    brute = (pos[:, None] > neg[None, :]).mean() + 0.5 * (pos[:, None] == neg[None, :]).mean()
+    assert exact == pytest.approx(brute, abs=1e-9)
+    a, b = H.AUC(), H.AUC()
+    a.add(y[:2500], p[:2500])
+    b.add(y[2500:], p[2500:])
+    a.merge(b)
+    assert a.evaluate() == pytest.approx(exact, abs=2e-4)
+    c = H.AUC()
+    c.merge_data(*a.data())
+    assert c.evaluate() == a.evaluate()
+    assert 0.5 < a.accuracy(0.0) < 1.0
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.lists(st.integers(0, 500), max_size=80), st.lists(st.integers(0, 500), max_size=80))
+def test_set_ops_and_match(a, b):
+    a = np.array(sorted(set(a)), dtype=np.uint64)
+    b = np.array(sorted(set(b)), dtype=np.uint64)
+    assert H.set_union(a, b).tolist() == sorted(set(a.tolist()) | set(b.tolist()))
+    assert H.set_intersection(a, b).tolist() == sorted(set(a.tolist()) & set(b.tolist()))
+    lo, hi = H.find_range(a, 100, 300)
+    assert a[lo:hi].tolist() == [x for x in a.tolist() if 100 <= x < 300]
+    dst = np.zeros(len(a) * 2)
+    src = np.arange(len(b) * 2, dtype=np.float64) + 1
+    n = H.match(a, dst, b, src, 2, True, 3)
+    assert n == len(set(a.tolist()) & set(b.tolist()))
+    for j, k in enumerate(a.tolist()):
+        if k in b.tolist():
+            i = b.tolist().index(k)
+            assert dst[2 * j:2 * j + 2].tolist() == src[2 * i:2 * i + 2].tolist()
+        else:
+            assert dst[2 * j:2 * j + 2].tolist() == [0, 0]
+
+
+def test_kv_partition_and_sort():
+    rng = np.random.RandomState(1)
+    k = rng.randint(0, 1000, 500).astype(np.uint64)
+    v = k.astype(np.float64) * 2
+    pk, pv, off = H.kv_partition(k, v, [250, 500, 750])
+    assert off[0] == 0 and off[-1] == 500 and np.all(pv == pk * 2)
+    for p, (lo, hi) in enumerate([(0, 250), (250, 500), (500, 750), (750, 1001)]):
+        seg = pk[off[p]:off[p + 1]]
+        assert np.all((seg >= lo) & (seg < hi))
+    big = rng.randint(0, 2**62, 100000).astype(np.uint64)
+    assert np.array_equal(H.parallel_sort_u64(big, 4), np.sort(big))
+
+
+def test_slice_key_ordered():
+    keys = np.array([1, 5, 9, 10, 20, 31], dtype=np.uint64)
+    vals = np.arange(12, dtype=np.float64)       # 2 per key
+    parts = H.slice_key_ordered(keys.tobytes(), [vals.tobytes()], [0, 10, 20, 40], (0, 25))
+    got = [np.frombuffer(p.key, dtype=np.uint64).tolist() for p in parts]
+    assert got == [[1, 5, 9], [10], [20, 31]]
+    assert np.frombuffer(parts[1].values[0], dtype=np.float64).tolist() == [6.0, 7.0]
+    assert [p.key_range for p in parts] == [(0, 10), (10, 20), (20, 25)] and all(p.valid for p in parts)
+    parts = H.slice_key_ordered(keys.tobytes(), [], [0, 10, 20, 40], (0, 10))
+    assert [p.valid for p in parts] == [True, False, False]
+
+
+def test_even_divide_soft_threshold_recordio_zlib(tmp_path):
+    assert H.even_divide(0, 2**64 - 1, 2, 0) == (0, (2**64 - 1) // 2)
+    assert H.even_divide(0, 2**64 - 1, 2, 1)[1] == 2**64 - 1
+    assert H.soft_thresholding(3.0, 1.0, 2.0) == -1.0 and H.soft_thresholding(-3.0, 1.0, 2.0) == 1.0
+    assert H.soft_thresholding(0.5, 1.0, 2.0) == 0.0
+    recs = [b"", b"abc", bytes(range(256)) * 10]
+    path = str(tmp_path / "r.rec")
+    assert H.record_write(path, recs) and H.record_read(path) == recs
+    nan_like = (b"\xff" * 8) * 5000           # the inactive-weight sentinel compresses well
+    ok, zsize, back = H.zlib_roundtrip(nan_like)
+    assert ok and back == nan_like and zsize < len(nan_like) // 50
+
+
+def test_kvvector_aggregate_and_lookup():
+    kv = H.KVVector(1)
+    kv.merge_keys(0, np.array([2, 4, 6], dtype=np.uint64))
+    kv.merge_keys(0, np.array([4, 8, 10], dtype=np.uint64))
+    assert kv.keys(0).tolist() == [2, 4, 6, 8, 10]
+    kv.init_values(0, 0.0)
+    kv.aggregate(0, 7, 0, 9, np.array([2, 6], dtype=np.uint64), np.array([1, 10, 2, 20], dtype=np.float64), 2, 1)
+    kv.aggregate(0, 7, 0, 9, np.array([4, 6], dtype=np.uint64), np.array([5, 50, 3, 30], dtype=np.float64), 2, 1)
+    lo, hi, nval, vals = kv.received(7)
+    assert (lo, hi, nval) == (0, 4, 2) and vals.tolist() == [1, 10, 5, 50, 5, 50, 0, 0]
+    kv.set_values(0, np.array([.2, .4, .6, .8, 1.0]))
+    assert kv.lookup(0, np.array([1, 4, 10], dtype=np.uint64)).tolist() == [0.0, 0.4, 1.0]
