@@ -92,10 +92,10 @@ class DarlinRef:
             rows += n
         self.rows = rows
         self.w = np.zeros(P)
-        self.delta = np.full(P, cfg.delta_init)
+        self.delta = np.full(P, float(cfg.delta_init))
         self.active = np.ones(P, dtype=bool)
         self.wk_w = [np.zeros(P) for _ in shards]
-        self.wk_delta = [np.full(P, cfg.delta_init) for _ in shards]
+        self.wk_delta = [np.full(P, float(cfg.delta_init)) for _ in shards]
         self.wk_active = [np.ones(P, dtype=bool) for _ in shards]
         self.violation = 0.0
         self.kkt_threshold = 1e20

@@ -1,0 +1,434 @@
+"""The linear-method application on CPU nodes, driven through the control-plane runtime.
+
+This is the multi-process form of the job: a scheduler, S servers and W workers that talk only
+through messages (push / pull on a shared parameter, task calls with logical timestamps), the way
+the reference runs it.  It is used for CPU-only deployments, for the plumbing configuration
+(1 scheduler + 2 servers + 2 workers on localhost) and as the protocol-level test bed; the GPU
+engines in ``models/`` implement the same solvers on peer memory.
+
+Reference roles: LinearMethod::process / startSystem / mergeProgress
+(src/linear_method/linear_method.cc:62-179), BatchSolver::run / loadData / preprocessData /
+saveModel (src/linear_method/batch_solver.cc:23-127, 202-426), Darling::updateModel
+(src/linear_method/darling.cc:155-273), SharedParameter::process
+(src/parameter/shared_parameter.h:90-149), KVVector (src/parameter/kv_vector.h).
+"""
+from __future__ import annotations
+
+import math
+import sys
+import threading
+import time
+from typing import Dict, List, Optional
+
+import numpy as np
+import scipy.sparse as sp
+
+from .. import config as cfg
+from ..runtime import host
+from ..runtime.node import NodeContext
+from ..utils.modelio import write_model_text
+from ..utils.pbtext import dumps, parse
+
+PUSH, PULL = 1, 2
+F_INSERT_KEY_FREQ, F_INSERT_KEY = 1, 2
+K_PACE = 10                       # parameter timestamps per scheduler task (batch_solver.h:15)
+U64 = np.uint64
+NAN_SENTINEL = np.float64(np.nan)
+
+
+def _call(cmd: str, **kw) -> bytes:
+    m = cfg.LMCall(cmd=cmd)
+    for k, v in kw.items():
+        if k == "key":
+            m.key = cfg.PbRange(begin=v[0], end=v[1])
+        else:
+            m.set(k, v)
+    return dumps(m, oneline=True).encode()
+
+
+class SharedParam:
+    """The shared parameter ``w``: a customer that serves push / pull on a KVVector."""
+
+    def __init__(self, ctx: NodeContext, name: str, solver):
+        H = host()
+        self.H, self.ctx, self.solver = H, ctx, solver
+        self.kv = H.KVVector(1)
+        self.filter = H.FrequencyFilter()
+        self.pulled: Dict[int, Dict[str, tuple]] = {}
+        self.lock = threading.Lock()
+        self.cust = H.Customer(ctx.po, name, self.process, True)
+
+    # executor thread of this customer
+    def process(self, msg) -> None:
+        keys = np.frombuffer(msg.key, dtype=U64)
+        if msg.request and msg.cmd == PUSH:
+            if msg.flags & F_INSERT_KEY_FREQ:
+                if self.filter.empty():
+                    s = self.solver.conf.solver
+                    n = max(int(self.ctx.num_workers * len(keys) * s.countmin_n_ratio / math.log(self.ctx.num_workers + 1)), 64)
+                    self.filter.resize(n, s.countmin_k)
+                self.filter.insert_keys(keys, np.frombuffer(msg.values[0], dtype=np.uint32))
+            elif not msg.values:
+                self.kv.merge_keys(msg.channel, keys)
+            else:
+                vals = np.frombuffer(msg.values[0], dtype=np.float64)
+                nval = len(vals) // max(len(keys), 1) if len(keys) else 2
+                lo, hi = msg.key_range
+                self.kv.aggregate(msg.channel, msg.time, lo, hi, keys, vals, nval, 1)
+        elif msg.request and msg.cmd == PULL:
+            if msg.aux > 0:       # query_key_freq: reply the keys seen more than aux times
+                kept = self.filter.query_keys(keys, msg.aux)
+                self.cust.reply(msg, key=kept.tobytes(), values=[b""])
+            else:
+                vals = self.kv.lookup(msg.channel, keys)
+                self.cust.reply(msg, values=[vals.tobytes()])
+        elif not msg.request and msg.cmd == PULL:
+            with self.lock:
+                vals = np.frombuffer(msg.values[0], dtype=np.float64) if msg.values else np.zeros(0)
+                self.pulled.setdefault(msg.time, {})[msg.sender] = (keys, vals)
+
+    def take_pulled(self, t: int):
+        """Concatenate the replies of pull ``t`` in server (= key) order."""
+        with self.lock:
+            parts = self.pulled.pop(t, {})
+        order = self.cust.group(self.H.kServerGroup)
+        ks = [parts[s][0] for s in order if s in parts]
+        vs = [parts[s][1] for s in order if s in parts]
+        return (np.concatenate(ks) if ks else np.zeros(0, U64)), (np.concatenate(vs) if vs else np.zeros(0))
+
+
+class LinearMethodNode:
+    """Worker or server side of the batch DARLIN solver (one instance per non-scheduler node)."""
+
+    def __init__(self, ctx: NodeContext, app_conf, flags: cfg.Flags):
+        H = host()
+        self.H, self.ctx, self.flags = H, ctx, flags
+        self.app_conf = app_conf
+        self.conf = app_conf.linear_method
+        self.param = SharedParam(ctx, app_conf.parameter_name[0], self)
+        self.cust = H.Customer(ctx.po, app_conf.app_name, self.process, False)
+        self.kkt_threshold = 1e20
+        self.violation = 0.0
+        self.busy = 0.0
+        self.ch = 1               # single feature group channel (all slots merged), like LIBSVM data
+
+    # ------------------------------------------------------------------ dispatch
+    def process(self, msg) -> None:
+        if not msg.request:
+            return
+        call = parse(msg.payload.decode(), cfg.LMCall)
+        t0 = time.time()
+        reply = b""
+        if call.cmd == "LOAD_DATA":
+            reply = self.load_data()
+        elif call.cmd == "PREPROCESS_DATA":
+            self.preprocess(msg.time)
+        elif call.cmd == "UPDATE_MODEL":
+            self.update_model(msg, call)
+            self.busy += time.time() - t0
+            return
+        elif call.cmd == "EVALUATE_PROGRESS":
+            reply = self.evaluate()
+        elif call.cmd == "SAVE_MODEL":
+            self.save_model()
+        self.busy += time.time() - t0
+        self.cust.reply(msg, payload=reply)
+
+    # ------------------------------------------------------------------ LOAD_DATA
+    def load_data(self) -> bytes:
+        if not self.ctx.is_worker:
+            return b""
+        td = self.conf.training_data
+        fmt = getattr(self.H.TextFormat, td.text if td.has("text") else "LIBSVM")
+        cache = self.conf.local_cache.file[0] if self.conf.local_cache.file else "/tmp/psb200_cache/"
+        r = self.H.SlotReader()
+        r.init(list(td.file), fmt, cache + f"{self.ctx.node_id}/", True, bool(self.flags.shuffle_fea_id),
+               bool(self.flags.add_beta_feature), int(self.flags.line_limit), int(self.flags.load_data_max_mb_per_thread))
+        info, hits = r.read(max(int(self.flags.num_threads), 1))
+        self.y = r.value(0).astype(np.float64)
+        self.off, self.idx = r.offset(1).astype(np.int64), r.index(1)
+        v = r.value(1)
+        self.binary = len(v) == 0
+        self.val = np.ones(len(self.idx)) if self.binary else v.astype(np.float64)
+        return info["text"].encode()
+
+    # ------------------------------------------------------------------ PREPROCESS_DATA
+    def preprocess(self, T: int) -> None:
+        H, P, t = self.H, self.param, T * K_PACE
+        solver = self.conf.solver
+        allr = (0, 2**64 - 1)
+        freq = solver.tail_feature_freq
+        if self.ctx.is_worker:
+            ukeys, inv, cnt = np.unique(self.idx, return_inverse=True, return_counts=True)
+            if freq > 0:      # tail-feature filter through the servers' count-min sketch
+                P.cust.submit(H.kServerGroup, cmd=PUSH, key=ukeys.tobytes(), values=[cnt.astype(np.uint32).tobytes()],
+                              time=t, key_range=allr, channel=self.ch, flags=F_INSERT_KEY_FREQ, wait=True)
+                P.cust.submit(H.kServerGroup, cmd=PULL, key=ukeys.tobytes(), time=t + 2, wait_time=t + 1, key_range=allr,
+                              channel=self.ch, aux=freq, erase_key_cache=True, wait=True)
+                kept, _ = P.take_pulled(t + 2)
+                keep_col = np.isin(ukeys, kept)
+                sel = keep_col[inv]
+                rows = np.repeat(np.arange(len(self.y)), np.diff(self.off))[sel]
+                self.idx, self.val = self.idx[sel], self.val[sel]
+                self.off = np.concatenate([[0], np.cumsum(np.bincount(rows, minlength=len(self.y)))]).astype(np.int64)
+                ukeys, inv = np.unique(self.idx, return_inverse=True)
+            self.keys = ukeys
+            rows = np.repeat(np.arange(len(self.y)), np.diff(self.off))
+            self.X = sp.csc_matrix((self.val, (rows, inv)), shape=(len(self.y), len(ukeys)))
+            t2 = t + 4
+            P.cust.submit(H.kServerGroup, cmd=PUSH, key=ukeys.tobytes(), time=t2, key_range=allr, channel=self.ch,
+                          flags=F_INSERT_KEY, erase_key_cache=True, wait=True)
+            P.cust.submit(H.kServerGroup, cmd=PULL, key=ukeys.tobytes(), time=t2 + 2, wait_time=t2 + 1, key_range=allr,
+                          channel=self.ch, erase_key_cache=True, wait=True)
+            _, w0 = P.take_pulled(t2 + 2)
+            n = len(ukeys)
+            self.w = w0.copy() if len(w0) == n else np.zeros(n)
+            self.dual = np.exp(self.y * (self.X @ self.w))
+            self.delta = np.full(n, self.conf.darling.delta_init_value)
+            self.active = np.ones(n, dtype=bool)
+        else:
+            if freq > 0:
+                P.cust.wait_in(H.kWorkerGroup, t)
+                P.cust.finish_in(H.kWorkerGroup, t + 1)
+            t2 = t + 4
+            P.cust.wait_in(H.kWorkerGroup, t2)
+            P.filter.clear()
+            init = self.conf.init_w
+            P.kv.init_values(self.ch, init.constant if init.type == "CONSTANT" else 0.0)
+            n = len(P.kv.keys(self.ch))
+            self.delta = np.full(n, self.conf.darling.delta_init_value)
+            self.active = np.ones(n, dtype=bool)
+            P.cust.finish_in(H.kWorkerGroup, t2 + 1)
+
+    # ------------------------------------------------------------------ UPDATE_MODEL
+    def update_model(self, msg, call) -> None:
+        H, P = self.H, self.param
+        t = msg.time * K_PACE
+        if call.has("kkt_filter_threshold"):
+            self.kkt_threshold = call.kkt_filter_threshold
+            self.violation = 0.0
+        if call.has("kkt_filter_reset") and call.kkt_filter_reset:
+            self.active[:] = True
+            if self.ctx.is_server:
+                w = P.kv.values(self.ch)
+                P.kv.set_values(self.ch, np.nan_to_num(w, nan=0.0))
+        rng = (call.key.begin, call.key.end)
+        if self.ctx.is_worker:
+            c0, c1 = np.searchsorted(self.keys, [U64(rng[0]), U64(rng[1])])
+            G, Uu = self._gradients(c0, c1)
+            gu = np.stack([G, Uu], 1).ravel()
+            P.cust.submit(H.kServerGroup, cmd=PUSH, key=self.keys[c0:c1].tobytes(), values=[gu.tobytes()], time=t,
+                          key_range=rng, channel=self.ch)
+            msg.defer()
+            sender, T = msg.sender, msg.time
+
+            def on_pull():
+                _, wn = P.take_pulled(t + 2)
+                self._update_dual(c0, c1, wn)
+                self.cust.finish_in(sender, T)
+                self.cust.reply(msg)
+
+            P.cust.submit(H.kServerGroup, cmd=PULL, key=self.keys[c0:c1].tobytes(), time=t + 2, wait_time=t + 1,
+                          key_range=rng, channel=self.ch, on_finish=on_pull)
+        else:
+            lo, hi = self.ctx.po.my_node.key
+            if max(lo, rng[0]) < min(hi, rng[1]):
+                P.cust.wait_in(H.kWorkerGroup, t)
+                s0, s1, nval, vals = P.kv.received(t)
+                if nval and s1 > s0:
+                    self._update_weight(s0, s1, vals.reshape(-1, nval))
+                P.cust.finish_in(H.kWorkerGroup, t + 1)
+            self.cust.reply(msg)
+
+    def _gradients(self, c0: int, c1: int):
+        X, y = self.X, self.y
+        tau = 1.0 / (1.0 + self.dual)
+        t2 = tau * (1 - tau)
+        G, U = np.zeros(c1 - c0), np.zeros(c1 - c0)
+        for jj, j in enumerate(range(c0, c1)):
+            if not self.active[j]:
+                G[jj] = U[jj] = NAN_SENTINEL
+                continue
+            s, e = X.indptr[j], X.indptr[j + 1]
+            r, v = X.indices[s:e], X.data[s:e]
+            d = self.delta[j]
+            G[jj] = -np.sum(y[r] * tau[r] * v)
+            if self.binary:
+                U[jj] = np.sum(np.minimum(t2[r] * math.exp(d), 0.25))
+            else:
+                U[jj] = np.sum(np.minimum(t2[r] * np.exp(np.abs(v) * d), 0.25) * v * v)
+        return G, U
+
+    def _update_weight(self, s0: int, s1: int, GU: np.ndarray) -> None:
+        P, d = self.param, self.conf.darling
+        eta = self.conf.learning_rate.eta
+        lam = self.conf.penalty.get("lambda")[0]
+        w = P.kv.values(self.ch)
+        seg = w[s0:s1].copy()
+        for i in range(s1 - s0):
+            k = s0 + i
+            if not self.active[k]:
+                continue
+            g, u = GU[i, 0], GU[i, 1] / eta + 1e-10
+            if g != g:                       # every worker sent the inactive sentinel
+                continue
+            gp, gn = g + lam, g - lam
+            wk = seg[i]
+            dd, vio = -wk, 0.0
+            if wk == 0:
+                if gp < 0:
+                    vio = -gp
+                elif gn > 0:
+                    vio = gn
+                elif gp > self.kkt_threshold and gn < -self.kkt_threshold:
+                    self.active[k] = False
+                    seg[i] = np.nan
+                    continue
+            self.violation = max(self.violation, vio)
+            if gp <= u * wk:
+                dd = -gp / u
+            elif gn >= u * wk:
+                dd = -gn / u
+            dd = min(self.delta[k], max(-self.delta[k], dd))
+            self.delta[k] = min(d.delta_max_value, 2 * abs(dd) + 0.1)
+            seg[i] = wk + dd
+        P.kv.set_values_range(self.ch, s0, seg)
+
+    def _update_dual(self, c0: int, c1: int, w_new: np.ndarray) -> None:
+        X, y = self.X, self.y
+        dmax = self.conf.darling.delta_max_value
+        for jj, j in enumerate(range(c0, c1)):
+            if not self.active[j]:
+                continue
+            wn = w_new[jj]
+            if wn != wn:
+                self.active[j] = False
+                self.w[j] = 0.0
+                continue
+            dw = wn - self.w[j]
+            self.delta[j] = min(dmax, 2 * abs(dw) + 0.1)
+            self.w[j] = wn
+            if dw != 0:
+                s, e = X.indptr[j], X.indptr[j + 1]
+                r, v = X.indices[s:e], X.data[s:e]
+                self.dual[r] *= np.exp(y[r] * v * dw)
+
+    # ------------------------------------------------------------------ EVALUATE_PROGRESS / SAVE_MODEL
+    def evaluate(self) -> bytes:
+        p = cfg.Progress()
+        if self.ctx.is_worker:
+            p.objv = float(np.sum(np.log1p(1.0 / self.dual)))
+            p.busy_time = [self.busy]
+            self.busy = 0.0
+        else:
+            w = np.nan_to_num(self.param.kv.values(self.ch), nan=0.0)
+            p.objv = float(np.abs(w).sum() * self.conf.penalty.get("lambda")[0])
+            p.nnz_w = int((w != 0).sum())
+            p.violation = float(self.violation)
+            p.nnz_active_set = int(self.active.sum())
+        return dumps(p, oneline=True).encode()
+
+    def save_model(self) -> None:
+        if not self.ctx.is_server or not self.conf.model_output.file:
+            return
+        keys = self.param.kv.keys(self.ch)
+        w = self.param.kv.values(self.ch)
+        write_model_text(f"{self.conf.model_output.file[0]}_{self.ctx.node_id}", keys, w)
+
+    def stop(self) -> None:
+        self.cust.stop()
+        self.param.cust.stop()
+
+
+class BatchScheduler:
+    """Scheduler side: ``BatchSolver::run`` + ``Darling::runIteration``."""
+
+    def __init__(self, ctx: NodeContext, app_conf, flags: cfg.Flags):
+        H = host()
+        self.H, self.ctx, self.flags, self.app_conf = H, ctx, flags, app_conf
+        self.conf = app_conf.linear_method
+        self.param = H.Customer(ctx.po, app_conf.parameter_name[0], None, True)
+        self.cust = H.Customer(ctx.po, app_conf.app_name, None, False)
+        self.progress: List[dict] = []
+
+    def _submit(self, payload: bytes, wait: bool = True, wait_time: int = -1) -> int:
+        t = self.cust.submit(self.H.kActiveGroup, payload=payload, wait_time=wait_time)
+        if wait:
+            self.cust.wait_out(self.H.kActiveGroup, t)
+        return t
+
+    def run(self, verbose: bool = True) -> List[dict]:
+        from ..models.darlin import Progress, block_order, print_progress
+
+        H, conf, sol = self.H, self.conf, self.conf.solver
+        # LOAD_DATA, merge ExampleInfo
+        t = self._submit(_call("LOAD_DATA"))
+        num_ex = nnz = 0
+        kmin, kmax = 2**64 - 1, 0
+        for text in self.cust.take_replies(t).values():
+            info = parse(text.decode(), cfg.ExampleInfo)
+            num_ex += info.num_ex
+            for s in info.slot:
+                if s.id == 0:
+                    continue
+                nnz += s.nnz_ele
+                kmin, kmax = min(kmin, s.min_key), max(kmax, s.max_key)
+        self.num_ex = num_ex
+        # feature blocks (batch_solver.cc:48-66)
+        per_row = nnz / max(num_ex, 1)
+        nblk = max(int(math.ceil(per_row * sol.feature_block_ratio)), 1) if per_row > 1 + 1e-6 and sol.feature_block_ratio > 0 else 1
+        span = kmax - kmin
+        bounds = [kmin + span * i // nblk for i in range(nblk)] + [kmax]
+        self.blocks = [(bounds[i], bounds[i + 1]) for i in range(nblk)]
+        self._submit(_call("PREPROCESS_DATA"))
+        # iterations
+        tau = sol.max_block_delay
+        orders = block_order(nblk, sol.max_pass_of_data, sol.random_feature_block_order, int(self.flags.seed))
+        kkt, reset = 1e20, False
+        first_task = None
+        tm = None
+        t_start = time.time()
+        for it in range(sol.max_pass_of_data):
+            t_it = time.time()
+            for i, b in enumerate(orders[it].tolist()):
+                kw = dict(key=self.blocks[b], fea_grp=[1])
+                if i == 0:
+                    kw["kkt_filter_threshold"] = kkt
+                    if reset:
+                        kw["kkt_filter_reset"] = True
+                wait_time = -1
+                if tm is not None and first_task is not None and (tm + 1) - tau > first_task:
+                    wait_time = tm - tau
+                tm = self._submit(_call("UPDATE_MODEL", **kw), wait=False, wait_time=wait_time)
+                if first_task is None:
+                    first_task = tm
+            wt = tm - tau if tm - tau >= first_task else first_task
+            te = self._submit(_call("EVALUATE_PROGRESS"), wait=True, wait_time=wt)
+            tm = te
+            objv, nnz_w, nnz_as, vio, busy = 0.0, 0, 0, 0.0, []
+            for text in self.cust.take_replies(te).values():
+                p = parse(text.decode(), cfg.Progress)
+                objv += p.objv
+                nnz_w += p.nnz_w
+                nnz_as += p.nnz_active_set
+                vio = max(vio, p.violation)
+                busy += list(p.busy_time)
+            rel = 1.0 if not self.progress else self.progress[-1]["objv"] / objv - 1.0
+            rec = dict(objv=objv, relative_objv=rel, nnz_w=nnz_w, violation=vio, nnz_active_set=nnz_as,
+                       kkt_threshold=kkt, total_time=time.time() - t_start, busy_time=busy)
+            self.progress.append(rec)
+            if verbose:
+                print_progress(it, Progress(objv, rel, nnz_w, vio, nnz_as, kkt, time.time() - t_it), file=sys.stderr)
+            kkt = vio / max(num_ex, 1) * conf.darling.kkt_filter_threshold_ratio
+            if 0 < rel <= sol.epsilon:
+                if reset:
+                    break
+                reset = True
+            else:
+                reset = False
+        self._submit(_call("SAVE_MODEL"))
+        return self.progress
+
+    def stop(self) -> None:
+        self.cust.stop()
+        self.param.stop()

@@ -118,3 +118,28 @@ def zipf_sparse_matrix(rows: int, cols: int, nnz_per_row: int, *, seed: int, dev
         y = torch.sign(xw + noise * torch.randn(rows, generator=gen, device=device))
         y = torch.where(y == 0, torch.ones_like(y), y)
     return offsets, idx, vals, y.to(torch.float32), wstar.to(torch.float32)
+
+
+def write_libsvm_parts(directory: str, offsets, idx, vals, y, num_files: int, one_based: bool = False) -> list:
+    """Write a CSR matrix as ``num_files`` LIBSVM text parts (``part-000`` ...); returns the paths."""
+    import os
+
+    import numpy as np
+
+    os.makedirs(directory, exist_ok=True)
+    off = offsets.cpu().numpy()
+    ix = idx.cpu().numpy().astype(np.uint64) + (1 if one_based else 0)
+    v = None if vals is None else vals.cpu().numpy()
+    yy = y.cpu().numpy()
+    rows = len(yy)
+    paths = []
+    for f in range(num_files):
+        r0, r1 = rows * f // num_files, rows * (f + 1) // num_files
+        path = os.path.join(directory, f"part-{f:03d}")
+        with open(path, "w") as out:
+            for r in range(r0, r1):
+                a, b = off[r], off[r + 1]
+                feats = " ".join(f"{int(k)}:{(1 if v is None else float(v[i])):g}" for k, i in zip(ix[a:b], range(a, b)))
+                out.write(f"{int(yy[r]):+d} {feats}\n")
+        paths.append(path)
+    return paths

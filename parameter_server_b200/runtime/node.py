@@ -1,0 +1,132 @@
+"""Process bootstrap of one node of a job: identity from the rank, van, post office, membership.
+
+Identity rules of the reference (src/system/van.cc:243-281): rank 0 is the scheduler ``H``; ranks
+1..W are workers ``W0..``; ranks W+1..W+S are servers ``S0..``; anything above is an unused
+stand-by ``U*``.  The scheduler's address comes from ``-scheduler`` (a text-format ``Node``).
+"""
+from __future__ import annotations
+
+import json
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+from . import host
+from .. import config as cfg
+
+
+def role_of_rank(rank: int, num_workers: int, num_servers: int):
+    H = host()
+    if rank == 0:
+        return H.SCHEDULER, "H"
+    if rank <= num_workers:
+        return H.WORKER, f"W{rank - 1}"
+    if rank <= num_workers + num_servers:
+        return H.SERVER, f"S{rank - num_workers - 1}"
+    return H.UNUSED, f"U{rank - num_workers - num_servers - 1}"
+
+
+def heartbeat_report(node_id: str, state: dict) -> str:
+    """Text-format ``HeartbeatReport`` of this process (src/system/heartbeat_info.cc:37-155)."""
+    H = host()
+    u = H.resource_usage()
+    now = time.time()
+    dt = max(now - state.get("t", now - 1.0), 1e-3)
+    d_proc = u["proc_jiffies"] - state.get("proc", u["proc_jiffies"])
+    d_host = max(u["host_jiffies"] - state.get("host", u["host_jiffies"]), 1)
+    r = cfg.HeartbeatReport(
+        hostname=node_id, seconds_since_epoch=int(now), total_time_milli=int(dt * 1000),
+        busy_time_milli=int(state.get("busy_ms", 0)), net_in_mb=int(u["net_in"] >> 20), net_out_mb=int(u["net_out"] >> 20),
+        process_cpu_usage=int(100 * d_proc / d_host * (state.get("ncpu", 1))), host_cpu_usage=0,
+        process_rss_mb=int(u["rss_mb"]), process_virt_mb=int(u["virt_mb"]),
+        host_net_in_bw=int((u["net_in"] - state.get("in", u["net_in"])) / dt / 1e6),
+        host_net_out_bw=int((u["net_out"] - state.get("out", u["net_out"])) / dt / 1e6))
+    state.update(t=now, proc=u["proc_jiffies"], host=u["host_jiffies"], **{"in": u["net_in"], "out": u["net_out"]})
+    state["busy_ms"] = 0
+    from ..utils.pbtext import dumps
+
+    return dumps(r, oneline=True)
+
+
+@dataclass
+class NodeContext:
+    po: object
+    van: object
+    node_id: str
+    role: int
+    num_workers: int
+    num_servers: int
+
+    @property
+    def is_scheduler(self) -> bool:
+        return self.role == host().SCHEDULER
+
+    @property
+    def is_worker(self) -> bool:
+        return self.role == host().WORKER
+
+    @property
+    def is_server(self) -> bool:
+        return self.role == host().SERVER
+
+    def stop(self) -> None:
+        self.po.stop()
+
+
+def start_node(rank: int, flags: cfg.Flags, hub=None, timeout_s: float = 60.0) -> NodeContext:
+    """Create the van + post office of rank ``rank`` and join the job (blocks until the node table is known).
+
+    ``hub`` selects the in-process van (all nodes are threads of this process); otherwise TCP.
+    """
+    H = host()
+    W, S = flags.num_workers, flags.num_servers
+    role, nid = role_of_rank(rank, W, S)
+    sched = cfg.parse_node(flags.scheduler)
+    sched_node = H.Node(H.SCHEDULER, sched.id or "H", sched.hostname or "127.0.0.1", sched.port)
+    me = H.Node(role, nid, "127.0.0.1", sched.port if role == H.SCHEDULER else 0)
+    if hub is not None:
+        van = H.InprocVan(hub, me)
+    else:
+        van = H.TcpVan(me)
+        van.set_retries(max(flags.num_retries, 40))
+        van.bind()
+    van.set_compress(bool(flags.compress_message) and hub is None)
+    if flags.print_van:
+        van.set_log(f"van_{nid}")
+    po = H.Postoffice(van, W, S, flags.num_replicas)
+    po.set_key_cache(bool(flags.key_cache))
+    po.set_scheduler(sched_node if role != H.SCHEDULER else van.my_node)
+    po.start()
+    ctx = NodeContext(po, van, nid, role, W, S)
+    if role == H.SCHEDULER:
+        if not po.wait_nodes_and_init(timeout_s):
+            raise TimeoutError("scheduler: not every worker/server registered in time")
+    else:
+        po.register_with_scheduler()
+        if not po.wait_nodes_ready(timeout_s):
+            raise TimeoutError(f"{nid}: no node table from the scheduler")
+        if flags.report_interval > 0:
+            st: dict = {}
+            po.start_heartbeat(float(flags.report_interval), lambda: heartbeat_report(nid, st))
+    return ctx
+
+
+def dashboard(po) -> str:
+    """The scheduler's heartbeat table (src/system/postoffice.cc:292-374)."""
+    from ..utils.pbtext import parse
+
+    rows = ["Node  Task  MyCPU%  MyRSS  MyVir  Busy(ms)  InMB  OutMB  age(s)"]
+
+    def order(k):
+        return (k[0], int(k[1:]) if k[1:].isdigit() else 0)
+
+    hb = po.heartbeats()
+    for nid in sorted(hb, key=order):
+        age, text = hb[nid]
+        try:
+            r = parse(text.decode(), cfg.HeartbeatReport)
+            rows.append(f"{nid:<5} {po.last_task_of('default'):>4}  {r.process_cpu_usage:>6}  {r.process_rss_mb:>5}  "
+                        f"{r.process_virt_mb:>5}  {r.busy_time_milli:>8}  {r.net_in_mb:>4}  {r.net_out_mb:>5}  {age:6.2f}")
+        except Exception:
+            rows.append(f"{nid:<5} (no report yet)  {age:6.2f}")
+    return "\n".join(rows)

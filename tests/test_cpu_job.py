@@ -1,0 +1,98 @@
+"""The plumbing configuration: 1 scheduler + 2 servers + 2 workers as CPU nodes running DARLIN through
+the message protocol (LOAD -> PREPROCESS -> UPDATE per block -> EVALUATE -> SAVE); objective per pass and
+the per-server model dumps must equal the single-process fp64 oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from baseline.cpu_ref.darlin_ref import DarlinConfig as RefConfig
+from baseline.cpu_ref.darlin_ref import DarlinRef
+from parameter_server_b200 import config as cfg
+from parameter_server_b200.apps.job import run_local_threads
+from parameter_server_b200.data.synthetic import write_libsvm_parts
+from parameter_server_b200.utils.modelio import read_model_text
+
+CONF = '''
+app_name: "plumb"
+parameter_name: "plumb_w"
+linear_method {{
+  training_data {{ format: TEXT text: LIBSVM file: "{train}/part-.*" }}
+  local_cache {{ format: BIN file: "{cache}/" }}
+  model_output {{ format: TEXT file: "{out}/model" }}
+  loss {{ type: LOGIT }}
+  penalty {{ type: L1 lambda: {lam} }}
+  learning_rate {{ type: CONSTANT eta: 1 }}
+  solver {{ feature_block_ratio: {ratio} max_pass_of_data: {passes} max_block_delay: 0 epsilon: 1e-6
+           tail_feature_freq: {tail} random_feature_block_order: true }}
+  darling {{ delta_init_value: 1 delta_max_value: 5 kkt_filter_threshold_ratio: 10 }}
+}}
+'''
+
+
+def planted(rows, cols, nnz, seed, spread):
+    g = torch.Generator().manual_seed(seed)
+    keys = torch.randint(0, cols, (rows, nnz), generator=g).sort(1).values
+    keep = torch.ones_like(keys, dtype=torch.bool)
+    keep[:, 1:] = keys[:, 1:] != keys[:, :-1]
+    counts = keep.sum(1)
+    off = torch.zeros(rows + 1, dtype=torch.int64)
+    off[1:] = counts.cumsum(0)
+    idx = keys[keep]
+    w = torch.randn(cols, generator=g) * (torch.rand(cols, generator=g) < 0.05)
+    row_of = torch.repeat_interleave(torch.arange(rows), counts)
+    xw = torch.zeros(rows).index_add_(0, row_of, w[idx])
+    y = torch.sign(xw + 0.1 * torch.randn(rows, generator=g))
+    y[y == 0] = 1
+    if spread:                                   # keys over the whole uint64 space: both servers own some
+        idx = idx * ((1 << 63) // cols * 2 - 12345)
+    return off, idx, torch.ones(idx.numel()), y
+
+
+@pytest.mark.parametrize("spread", [False, True])
+def test_darlin_over_the_protocol_matches_oracle(tmp_path, spread):
+    rows, cols, nnz, passes, lam, ratio = 1200, 2048, 12, 4, 0.5, 0.5
+    off, idx, vals, y = planted(rows, cols, nnz, 0, spread)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    text = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=lam, ratio=ratio,
+                       passes=passes, tail=0)
+    flags = cfg.Flags(num_workers=2, num_servers=2, seed=0)
+    prog = run_local_threads(flags, text)
+    k = idx.numpy().view(np.uint64) if spread else idx.numpy().astype(np.uint64)
+    o = off.numpy()
+    h = rows // 2
+    shards = [(o[:h + 1], k[:o[h]], vals.numpy()[:o[h]], y.numpy()[:h]),
+              (o[h:] - o[h], k[o[h]:], vals.numpy()[o[h]:], y.numpy()[h:])]
+    ref = DarlinRef(shards, None, RefConfig(lambda1=lam, max_pass=passes, feature_block_ratio=ratio, epsilon=1e-6,
+                                            delta_init=1, delta_max=5, kkt_ratio=10, seed=0))
+    rprog = ref.run()
+    assert len(prog) == len(rprog) == passes
+    for p, r in zip(prog, rprog):
+        assert p["objv"] == pytest.approx(r.objv, rel=1e-9)
+        assert p["nnz_w"] == r.nnz_w and p["nnz_active_set"] == r.nnz_active
+        assert p["violation"] == pytest.approx(r.violation, rel=1e-9)
+    m0, m1 = (read_model_text(str(tmp_path / f"model_S{i}")) if os.path.exists(tmp_path / f"model_S{i}") else {} for i in (0, 1))
+    rk, rw = ref.model()
+    merged = {**m0, **m1}
+    assert sorted(merged) == rk.tolist()
+    for kk, ww in zip(rk.tolist(), rw.tolist()):
+        assert merged[kk] == pytest.approx(ww, rel=1e-5)
+    if spread:
+        assert len(m0) > 0 and len(m1) > 0 and max(m0) < min(m1)      # key-range sharded dumps
+    else:
+        assert len(m1) == 0                                            # small ids all fall into S0's range
+
+
+def test_tail_feature_filter_drops_rare_keys(tmp_path):
+    off, idx, vals, y = planted(600, 4096, 10, 3, False)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    text = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.2, ratio=0.5, passes=2, tail=2)
+    prog = run_local_threads(cfg.Flags(num_workers=2, num_servers=2), text)
+    cnt = np.bincount(idx.numpy(), minlength=4096)
+    model = read_model_text(str(tmp_path / "model_S0"))
+    rare_total = int(((cnt > 0) & (cnt <= 2)).sum())
+    rare_kept = sum(1 for k in model if cnt[k] <= 2)
+    # the sketch never drops a frequent key and lets only a few rare ones through (hash collisions)
+    assert len(model) > 0 and rare_total > 100 and rare_kept < 0.2 * rare_total
+    assert prog[-1]["objv"] < prog[0]["objv"] * 1.001
