@@ -28,12 +28,19 @@ def check_status(dev) -> None:
         raise RuntimeError(f"GEMM kernel gave up waiting (code {st[0]}, tile {st[1]},{st[2] - 100})")
 
 
-def gemm_tn(a: torch.Tensor, b: torch.Tensor, act: str = "IDENTITY", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, act: str = "IDENTITY", out: Optional[torch.Tensor] = None,
+            pad_k: bool = False) -> torch.Tensor:
     """``act(a @ b.T)`` for row-major fp32 ``a`` [M,K] and ``b`` [N,K] on the tcgen05 tensor cores (TF32)."""
     assert a.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32 and a.shape[1] == b.shape[1]
     assert a.stride(1) == 1 and b.stride(1) == 1
     M, K = a.shape
     Nn = b.shape[0]
+    if pad_k and K % 4:
+        # TMA needs row strides that are multiples of 16 bytes: zero-pad the contraction dimension
+        kp = (K + 3) // 4 * 4
+        a = torch.nn.functional.pad(a, (0, kp - K))
+        b = torch.nn.functional.pad(b, (0, kp - K))
+        K = kp
     if out is None:
         out = torch.empty((M, Nn), dtype=torch.float32, device=a.device)
     rc = N.lib().psb_gemm_tn_tf32(N.ptr(a), N.ptr(b), N.ptr(out), M, Nn, K, a.stride(0), b.stride(0), out.stride(0), ACT[act],
