@@ -100,15 +100,13 @@ class DarlinSolver:
         g, dev, W = self.group, self.dev, self.group.world
         rows, nnz = y.numel(), keys.numel()
         # unique local keys in unsigned order + column id of every non-zero  (Localizer::countUniqIndex/remapIndex)
-        uk, inv = torch.unique(_ukey(keys), return_inverse=True)
-        lkeys = _ukey(uk)
+        from ..ops import sparse
+
+        lkeys, _ = sparse.count_unique(keys.contiguous())          # radix sort + run-length unique (unsigned order)
+        uk = _ukey(lkeys)                                          # same keys as int64 values in that order
         P = lkeys.numel()
-        row_of = torch.repeat_interleave(torch.arange(rows, device=dev, dtype=torch.int32), offsets[1:] - offsets[:-1])
-        order = torch.sort(inv, stable=True).indices               # CSR → CSC (SparseMatrix::alterStorage)
-        row_idx = row_of[order].contiguous()
-        cvals = None if vals is None else vals[order].contiguous()
-        col_ptr = torch.zeros(P + 1, dtype=torch.int64, device=dev)
-        col_ptr[1:] = torch.bincount(inv, minlength=P).cumsum(0)
+        inv = sparse.remap(keys.contiguous(), lkeys)               # local column id of every non-zero
+        col_ptr, row_idx, cvals = sparse.csr_to_csc(offsets, inv, vals, P)   # CSR → CSC (SparseMatrix::alterStorage)
         # global statistics (ExampleInfo merge): rows, nnz, key range
         stats = g.all_reduce_sum([rows, nnz])
         self.total_rows, self.total_nnz = int(stats[0]), int(stats[1])
