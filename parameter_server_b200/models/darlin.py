@@ -78,8 +78,15 @@ def block_order(nblk: int, n_pass: int, random_order: bool, seed: int) -> List[n
 class DarlinSolver:
     """Worker + server of one rank; ``preprocess`` once, then ``run`` (or ``run_pass`` repeatedly)."""
 
-    def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused"):
+    def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused",
+                 out_of_core: bool = False, prefetch_depth: int = 3):
+        """``out_of_core``: keep the column blocks (row ids, values) in pinned host memory and stream each
+        block to the GPU on a side stream ahead of its turn in the block order — the role of the
+        reference's ``FeatureStation`` in ``-mmap_training_data`` mode with its task-id keyed look-ahead
+        prefetch (src/linear_method/feature_station.cc:212-279, src/linear_method/darling.cc:175-201)."""
         self.group, self.cfg, self.impl = group, cfg, impl
+        self.out_of_core, self.prefetch_depth = out_of_core, max(int(prefetch_depth), 2)
+        self.h2d_bytes = 0
         self.dev = group.device
         self.timeout_s = timeout_s
         self._lib = N.lib()
@@ -185,8 +192,67 @@ class DarlinSolver:
         self.local_bar = torch.zeros(1, dtype=torch.int64, device=dev)
         self.abort = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = torch.zeros(8, dtype=torch.int32, device=dev)
+        if self.out_of_core:
+            self._to_host_blocks()
         self._build_structs()
         g.barrier()
+
+    def _to_host_blocks(self) -> None:
+        """Move the CSC payload to pinned host memory; only a small ring of block buffers stays on the device."""
+        self.h_row = self.row_idx.cpu().pin_memory()
+        self.h_val = None if self.vals is None else self.vals.cpu().pin_memory()
+        cp = self.col_ptr[self.blk_lc.reshape(-1)].reshape(-1, 2)
+        self.blk_nnz = cp.cpu().tolist()                      # [p0, p1) of every block in the CSC arrays
+        cap = max(max(p1 - p0 for p0, p1 in self.blk_nnz), 1)
+        d = self.prefetch_depth
+        self.stage_row = [torch.empty(cap, dtype=torch.int32, device=self.dev) for _ in range(d)]
+        self.stage_val = [None if self.vals is None else torch.empty(cap, dtype=torch.float32, device=self.dev) for _ in range(d)]
+        self.stage_ready = [torch.cuda.Event() for _ in range(d)]
+        self.stage_free = [torch.cuda.Event() for _ in range(d)]
+        self.copy_stream = torch.cuda.Stream(device=self.dev)
+        self.row_idx = self.stage_row[0]                      # placeholders for the struct; replaced per block
+        self.vals = self.stage_val[0]
+
+    def _pass_streamed(self, order: np.ndarray, order_t: torch.Tensor) -> None:
+        """One pass with every block's rows/values copied host→device just ahead of its kernel."""
+        compute = torch.cuda.current_stream(self.dev)
+        d, n = self.prefetch_depth, len(order)
+        H = self._hyper()
+        blocks = order.tolist()
+
+        def issue(i: int) -> None:
+            p0, p1 = self.blk_nnz[blocks[i]]
+            s = i % d
+            with torch.cuda.stream(self.copy_stream):
+                self.copy_stream.wait_event(self.stage_free[s])
+                if p1 > p0:
+                    self.stage_row[s][: p1 - p0].copy_(self.h_row[p0:p1], non_blocking=True)
+                    self.h2d_bytes += (p1 - p0) * 4
+                    if self.h_val is not None:
+                        self.stage_val[s][: p1 - p0].copy_(self.h_val[p0:p1], non_blocking=True)
+                        self.h2d_bytes += (p1 - p0) * 4
+                self.stage_ready[s].record(self.copy_stream)
+
+        for i in range(min(d - 1, n)):
+            issue(i)
+        for i in range(n):
+            if i + d - 1 < n:
+                issue(i + d - 1)
+            s = i % d
+            p0, _ = self.blk_nnz[blocks[i]]
+            compute.wait_event(self.stage_ready[s])
+            Wk = N.DarlinWorker.from_buffer_copy(self._Wk)
+            # the kernel indexes row_idx/vals with absolute CSC positions: bias the staging pointers by p0
+            Wk.row_idx = self.stage_row[s].data_ptr() - 4 * p0
+            Wk.vals = 0 if self.h_val is None else self.stage_val[s].data_ptr() - 4 * p0
+            Q = N.DarlinSched(order_t.data_ptr() + 4 * i, self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), 1, 0, self.seq + i,
+                              self.local_bar.data_ptr(), self.bar + 2 * i, self.abort.data_ptr(), self.status.data_ptr())
+            N.check(self._lib.psb_darlin_pass(C.byref(Wk), C.byref(self._P), C.byref(self._S), C.byref(Q), C.byref(H), self.grid,
+                                              N.stream_ptr()), "darlin_pass")
+            self.stage_free[s].record(compute)
+            self.kernel_launches += 1
+        self.seq += n
+        self.bar += 2 * n
 
     def _build_structs(self):
         Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),
@@ -228,6 +294,8 @@ class DarlinSolver:
         self.violation.zero_()
         if self.impl == "nccl":
             return self._pass_unfused(order)
+        if self.out_of_core:
+            return self._pass_streamed(np.asarray(order), order_t)
         Q = N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), len(order), 0, self.seq,
                           self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr())
         H = self._hyper()
