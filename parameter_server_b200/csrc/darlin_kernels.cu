@@ -24,6 +24,8 @@
 // All waits (cross-GPU counters and the in-GPU barrier) are bounded; on expiry the kernel
 // records the place in the status word, raises the abort flag and every CTA leaves the
 // block loop.
+#include <cstdlib>
+
 #include "psb_common.cuh"
 
 namespace psb {
@@ -383,7 +385,9 @@ int psb_darlin_grid() {
     int per_sm = 0, sms = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, darlin_pass_kernel, 512, 0);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    g_darlin_grid[dev] = sms * (per_sm > 2 ? 2 : per_sm);  // upper bound; callers may launch fewer
+    int want = 2;  // CTAs per SM: more CTAs hide gather latency, fewer make the per-block barriers cheaper
+    if (const char* e = getenv("PSB_DARLIN_CTAS_PER_SM")) want = atoi(e) > 0 ? atoi(e) : want;
+    g_darlin_grid[dev] = sms * (per_sm > want ? want : per_sm);  // upper bound; callers may launch fewer
   }
   return g_darlin_grid[dev];
 }

@@ -79,7 +79,7 @@ def ctr_minibatch(rows: int, *, seed: int, device, key_space_log2: int = 30, zip
 
 def zipf_sparse_matrix(rows: int, cols: int, nnz_per_row: int, *, seed: int, device, zipf_s: float = 1.0,
                        binary: bool = False, wstar_frac: float = 0.02, noise: float = 0.3,
-                       uniform_keys: bool = False, logistic_labels: bool = False):
+                       uniform_keys: bool = False, logistic_labels: bool = False, wstar_seed: Optional[int] = None):
     """CSR (offsets, col ids int64, vals float32|None, y ±1 float32, w* float32[cols]) for batch L1-LR.
 
     Column ids are distinct within a row.  Values (unless ``binary``) are lognormal(0,1) with each
@@ -109,8 +109,12 @@ def zipf_sparse_matrix(rows: int, cols: int, nnz_per_row: int, *, seed: int, dev
         nrm = torch.zeros(rows, device=device).index_add_(0, row_of, v * v).sqrt_().clamp_min_(1e-12)
         v = (v / nrm[row_of]).to(torch.float32)
         vals = v
-    wstar = torch.randn(cols, generator=gen, device=device)
-    wstar = torch.where(torch.rand(cols, generator=gen, device=device) < wstar_frac, wstar, torch.zeros_like(wstar))
+    wgen = gen
+    if wstar_seed is not None:            # the same planted model on every rank, whatever the data seed
+        wgen = torch.Generator(device=device)
+        wgen.manual_seed(wstar_seed)
+    wstar = torch.randn(cols, generator=wgen, device=device)
+    wstar = torch.where(torch.rand(cols, generator=wgen, device=device) < wstar_frac, wstar, torch.zeros_like(wstar))
     xw = torch.zeros(rows, device=device).index_add_(0, row_of, v * wstar[idx])
     if logistic_labels:
         y = torch.where(torch.rand(rows, generator=gen, device=device) < torch.sigmoid(xw), 1.0, -1.0)

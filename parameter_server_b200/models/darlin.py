@@ -120,9 +120,11 @@ class DarlinSolver:
         kmin = int(uk.min().item()) if P else (1 << 62)
         kmax = int(uk.max().item()) if P else -(1 << 62)
         if W > 1:
-            t = torch.tensor([-kmin, kmax], dtype=torch.int64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=g.group)
-            kmin, kmax = -int(t[0].item()), int(t[1].item())
+            tmin = torch.tensor([kmin], dtype=torch.int64, device=dev)
+            tmax = torch.tensor([kmax], dtype=torch.int64, device=dev)
+            dist.all_reduce(tmin, op=dist.ReduceOp.MIN, group=g.group)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX, group=g.group)
+            kmin, kmax = int(tmin.item()), int(tmax.item())
         self.key_min, self.key_max = kmin - _SIGN, kmax - _SIGN + 1   # unsigned [min, max+1)
         # server key ranges
         rng = Range(self.key_min, self.key_max) if self.cfg.shard_by_data_range else Range.all()
@@ -286,6 +288,22 @@ class DarlinSolver:
         self.srv_active.fill_(1)
         if self.cfg.reset_nan_on_kkt_reset:
             torch.nan_to_num_(self.srv_w.local, nan=0.0)
+
+    def reset_state(self) -> None:
+        """Back to the state right after ``preprocess``: zero weights and margins, initial trust regions,
+        every key active, empty progress (the data and the key resolution are kept)."""
+        self.margin.zero_()
+        self.w.zero_()
+        self.dw.zero_()
+        self.delta.fill_(self.cfg.delta_init)
+        self.active.fill_(1)
+        self.srv_w.local.zero_()
+        self.srv_gu.local.zero_()
+        self.srv_delta.fill_(self.cfg.delta_init)
+        self.srv_active.fill_(1)
+        self.progress = []
+        self.kkt_threshold = 1e20
+        self.group.barrier()
 
     def launch_pass(self, order: np.ndarray) -> None:
         """Enqueue one pass over the blocks in ``order`` on the current stream."""
