@@ -385,7 +385,7 @@ int psb_darlin_grid() {
     int per_sm = 0, sms = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, darlin_pass_kernel, 512, 0);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int want = 2;  // CTAs per SM: more CTAs hide gather latency, fewer make the per-block barriers cheaper
+    int want = 1;  // CTAs per SM: more CTAs hide gather latency, fewer make the per-block barriers cheaper
     if (const char* e = getenv("PSB_DARLIN_CTAS_PER_SM")) want = atoi(e) > 0 ? atoi(e) : want;
     g_darlin_grid[dev] = sms * (per_sm > want ? want : per_sm);  // upper bound; callers may launch fewer
   }
