@@ -216,6 +216,168 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
 }
 
+// ------------------------------------------------------------------ persistent variant for large problems
+// One CTA per SM walks a list of 128x256 output tiles.  Six warps: warp 0 (one lane) TMA producer,
+// warp 1 (one lane) MMA issuer, warps 2-5 epilogue (warp w reads TMEM lanes 32·(w mod 4) ...).  The
+// accumulator is double-buffered in TMEM (2 x 256 columns): while the epilogue warps drain tile i, the
+// tensor core already works on tile i+1.  The shared-memory ring runs across tile boundaries.
+constexpr int kPBN = 256;
+constexpr int kPStages = 4;
+constexpr uint32_t kPStageBytesB = kPBN * kBK * 4;
+constexpr int kPThreads = 192;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+struct __align__(1024) GemmSmemP {
+  float a[kPStages][kBM * kBK];
+  float b[kPStages][kPBN * kBK];
+  uint64_t full[kPStages], empty[kPStages], tfull[2], tempty[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+__global__ void __launch_bounds__(kPThreads, 1)
+gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            float* __restrict__ out, int M, int N, int K, int ldo, int act, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  GemmSmemP& s = *reinterpret_cast<GemmSmemP*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nbm = (M + kBM - 1) / kBM, nbn = (N + kPBN - 1) / kPBN;
+  const int ntiles = nbm * nbn;
+  const int nkb = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kPStages; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s.tfull[i], 1); mbar_init(&s.tempty[i], 4); }
+    s.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = s.tmem_base;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer: tiles are walked m-fastest so that concurrent CTAs share a B panel
+    uint32_t g = 0;
+    for (int t = blockIdx.x; t < ntiles && !s.abort_flag; t += gridDim.x) {
+      const int m0 = (t % nbm) * kBM, n0 = (t / nbm) * kPBN;
+      for (int kb = 0; kb < nkb; ++kb, ++g) {
+        const int st = g % kPStages;
+        if (g >= (uint32_t)kPStages && !mbar_wait(&s.empty[st], ((g / kPStages) - 1) & 1)) { s.abort_flag = 1; break; }
+        if (s.abort_flag) break;
+        mbar_expect_tx(&s.full[st], kStageBytesA + kPStageBytesB);
+        tma_load_2d(s.a[st], &map_a, &s.full[st], kb * kBK, m0);
+        tma_load_2d(s.b[st], &map_b, &s.full[st], kb * kBK, n0);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    constexpr uint32_t idesc = make_idesc(kBM, kPBN);
+    uint32_t g = 0, it = 0;
+    for (int t = blockIdx.x; t < ntiles && !s.abort_flag; t += gridDim.x, ++it) {
+      const uint32_t acc = it & 1u;
+      if (it >= 2 && !mbar_wait(&s.tempty[acc], ((it >> 1) - 1) & 1)) { s.abort_flag = 1; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t d_tmem = tmem + acc * (uint32_t)kPBN;
+      for (int kb = 0; kb < nkb; ++kb, ++g) {
+        const int st = g % kPStages;
+        if (!mbar_wait(&s.full[st], (g / kPStages) & 1)) { s.abort_flag = 1; break; }
+        if (s.abort_flag) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t da = make_smem_desc(smem_u32(s.a[st]));
+        const uint64_t db = make_smem_desc(smem_u32(s.b[st]));
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+          const uint64_t adv = (uint64_t)((k * kUmmaK * 4) >> 4);
+          asm volatile(
+              "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+              ::"r"(d_tmem), "l"(da + adv), "l"(db + adv), "r"(idesc), "r"(accumulate) : "memory");
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&s.empty[st])) : "memory");
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&s.tfull[acc])) : "memory");
+    }
+  } else if (warp >= 2) {
+    // ---------------- epilogue warps
+    const int q = warp & 3;
+    uint32_t it = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+      const uint32_t acc = it & 1u;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(&s.tfull[acc], (it >> 1) & 1) ? 1 : 0;
+        if (!ok) s.abort_flag = 1;
+        if (s.abort_flag) ok = 0;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m0 = (t % nbm) * kBM, n0 = (t / nbm) * kPBN;
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kPBN; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)kPBN + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 >= kPBN) {
+          // last chunk is in registers: hand the accumulator back to the MMA warp before the stores
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.tempty[acc]);
+        }
+        if (row < M && n0 + c0 < N) {
+          float* dst = out + (size_t)row * ldo + n0 + c0;
+          const int ncol = N - (n0 + c0);
+          if (ncol >= 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v;
+              v.x = apply_act(__uint_as_float(r[j]), act);
+              v.y = apply_act(__uint_as_float(r[j + 1]), act);
+              v.z = apply_act(__uint_as_float(r[j + 2]), act);
+              v.w = apply_act(__uint_as_float(r[j + 3]), act);
+              *reinterpret_cast<float4*>(dst + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncol) dst[j] = apply_act(__uint_as_float(r[j]), act);
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (s.abort_flag) {
+    if (threadIdx.x == 0) set_status(status, kWaitTimeout, blockIdx.x, 200);
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ elementwise / layout kernels of the NN app
 // tiled transpose out[c][r] = in[r][c]   (src/base/dense_matrix.h:87-104)
 __global__ void k_transpose(const float* __restrict__ in, float* __restrict__ out, int rows, int cols) {
@@ -306,12 +468,12 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 // 2-D map over a row-major [rows, k] fp32 matrix with row stride ld (floats), box = 128 rows x 32 floats, 128B swizzle
-int make_map(CUtensorMap* map, const float* base, int rows, int k, int ld) {
+int make_map(CUtensorMap* map, const float* base, int rows, int k, int ld, int box_rows = kBM) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return -1;
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -334,6 +496,24 @@ int psb_gemm_tn_tf32(const float* a, const float* b, float* out, int M, int N, i
   CUtensorMap ma, mb;
   int r = make_map(&ma, a, M, K, lda);
   if (r) return r;
+  // large problems: persistent kernel with 128x256 tiles and a double-buffered accumulator
+  static int sms = 0;
+  if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  const long tiles_p = (long)((M + kBM - 1) / kBM) * ((N + kPBN - 1) / kPBN);
+  if (tiles_p >= sms && getenv("PSB_GEMM_SIMPLE") == nullptr) {
+    r = make_map(&mb, b, N, K, ldb, kPBN);
+    if (r) return r;
+    const size_t smem_p = sizeof(GemmSmemP) + 1024;
+    static bool attr_p = false;
+    if (!attr_p) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tf32_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
+      if (e != cudaSuccess) return (int)e;
+      attr_p = true;
+    }
+    const int grid = (int)(tiles_p < sms ? tiles_p : sms);
+    gemm_tf32_persistent_kernel<<<grid, kPThreads, smem_p, stream>>>(ma, mb, out, M, N, K, ldo, act, status);
+    return (int)cudaGetLastError();
+  }
   r = make_map(&mb, b, N, K, ldb);
   if (r) return r;
   const size_t smem = sizeof(GemmSmem) + 1024;

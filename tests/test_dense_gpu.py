@@ -15,7 +15,9 @@ def _ref_act(x, act):
     return x
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (128, 128, 256), (256, 384, 96), (200, 130, 72), (1000, 520, 1024), (64, 8, 4)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (128, 128, 256), (256, 384, 96), (200, 130, 72), (1000, 520, 1024), (64, 8, 4),
+                                   # >= 148 tiles of 128x256: the persistent kernel (several tiles per CTA, ragged edges, short K)
+                                   (2048, 4096, 512), (1925, 2563, 260), (4096, 4224, 36), (9000, 2100, 64)])
 @pytest.mark.parametrize("act", ["IDENTITY", "RELU", "SCALED_TANH"])
 def test_gemm_tn_matches_fp32(M, N, K, act):
     from parameter_server_b200.ops import dense
