@@ -130,6 +130,12 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
                           seed=int(flags.seed))
         if lm.has("darling"):
             sol = DarlinSolver(group, dc, timeout_s=float(flags.timeout_s), impl=flags.impl if flags.impl in ("fused", "nccl") else "fused")
+            from ..utils.trace import ChromeTrace, MetricsLog
+
+            if flags.trace_file:
+                sol.trace = ChromeTrace(f"{flags.trace_file}.rank{group.rank}.json", pid=group.rank)
+            if flags.metrics_file:
+                sol.metrics = MetricsLog(flags.metrics_file)
             sol.preprocess(off, keys, vals, y)
             t0 = time.time()
             if flags.checkpoint_dir:
@@ -148,6 +154,8 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
             prog = sol.run(verbose=True)
         out["seconds"] = time.time() - t0
         out["progress"] = [p.__dict__ for p in prog]
+        if getattr(sol, "trace", None) is not None:
+            out["trace"] = sol.trace.save()
         if lm.model_output.file:
             out["model"] = sol.save_model(lm.model_output.file[0])
         if lm.has("validation_data"):

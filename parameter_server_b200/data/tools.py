@@ -1,0 +1,106 @@
+"""Data tools: convert text data to the binary matrix format and inspect data sets.
+
+Counterparts of the reference's ``text2proto`` / ``proto2bin`` / ``showins`` programs
+(src/data/text2proto.cc, proto2bin.cc, showins.cc) and of its MATLAB converters
+(src/data/matlab/*.m: bin↔mat, ``saveas_pserver``).  Binary matrices are
+``name.info`` + ``.offset`` + ``.index`` + ``.value`` (+ ``name.label`` for the labels).
+
+  python -m parameter_server_b200.data.tools text2bin LIBSVM 'data/train/part-.*' out/train
+  python -m parameter_server_b200.data.tools show out/train
+  python -m parameter_server_b200.data.tools info ADFEA 'data/ctr/part-.*'
+  python -m parameter_server_b200.data.tools bin2text out/train out/train.libsvm
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+from ..runtime import host
+
+
+def text2bin(fmt: str, pattern: str, out: str, cache: str = "/tmp/psb200_cache/tools/") -> dict:
+    H = host()
+    files = H.search_files([pattern])
+    if not files:
+        raise FileNotFoundError(pattern)
+    r = H.SlotReader()
+    r.init(files, getattr(H.TextFormat, fmt), cache, True)
+    info, _ = r.read(4)
+    off, idx, val = r.offset(1), r.index(1), r.value(1)
+    cols = int(idx.max()) + 1 if len(idx) else 0
+    H.write_bin_matrix(out, True, info["num_ex"], cols, off, idx, val if len(val) else None, 8)
+    r.value(0).astype(np.float32).tofile(out + ".label")
+    return {"rows": info["num_ex"], "cols": cols, "nnz": int(len(idx)), "files": len(files)}
+
+
+def show(name: str, rows: int = 5) -> dict:
+    H = host()
+    m = H.read_bin_matrix(name)
+    if m is None:
+        raise FileNotFoundError(name + ".info")
+    out = {k: m[k] for k in ("rows", "cols", "nnz", "row_major", "binary", "sparse")}
+    for r in range(min(rows, m["rows"])):
+        a, b = int(m["offset"][r]), int(m["offset"][r + 1])
+        feats = " ".join(f"{int(i)}" + ("" if m["binary"] else f":{float(v):g}") for i, v in
+                         zip(m["index"][a:b], m["value"][a:b] if not m["binary"] else [0] * (b - a)))
+        print(f"row {r}: {feats}")
+    return out
+
+
+def info(fmt: str, pattern: str) -> str:
+    H = host()
+    files = H.search_files([pattern])
+    r = H.StreamReader()
+    r.init(files, getattr(H.TextFormat, fmt))
+    total = None
+    while True:
+        out = r.read(100000)
+        if out is None:
+            break
+        _, i = out
+        if total is None:
+            total = {"num_ex": 0, "slots": {}}
+        total["num_ex"] += i["num_ex"]
+        for sid, s in i["slot"].items():
+            t = total["slots"].setdefault(sid, {"nnz_ele": 0, "nnz_ex": 0, "min_key": 2**64 - 1, "max_key": 0})
+            t["nnz_ele"] += s["nnz_ele"]
+            t["nnz_ex"] += s["nnz_ex"]
+            t["min_key"], t["max_key"] = min(t["min_key"], s["min_key"]), max(t["max_key"], s["max_key"])
+    return str(total)
+
+
+def bin2text(name: str, out_path: str) -> int:
+    """Binary matrix (+ ``.label``) back to LIBSVM text (the MATLAB ``saveas_pserver`` direction)."""
+    H = host()
+    m = H.read_bin_matrix(name)
+    y = np.fromfile(name + ".label", dtype=np.float32)
+    with open(out_path, "w") as f:
+        for r in range(m["rows"]):
+            a, b = int(m["offset"][r]), int(m["offset"][r + 1])
+            vals = np.ones(b - a) if m["binary"] else m["value"][a:b]
+            f.write(f"{int(y[r]):+d} " + " ".join(f"{int(i)}:{float(v):g}" for i, v in zip(m["index"][a:b], vals)) + "\n")
+    return m["rows"]
+
+
+def main(argv=None) -> int:
+    a = list(sys.argv[1:] if argv is None else argv)
+    if not a:
+        print(__doc__)
+        return 2
+    if a[0] == "text2bin":
+        print(text2bin(a[1], a[2], a[3]))
+    elif a[0] == "show":
+        print(show(a[1]))
+    elif a[0] == "info":
+        print(info(a[1], a[2]))
+    elif a[0] == "bin2text":
+        print(bin2text(a[1], a[2]))
+    else:
+        print(__doc__)
+        return 2
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

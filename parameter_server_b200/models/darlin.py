@@ -406,12 +406,25 @@ class DarlinSolver:
             raise RuntimeError(f"rank {self.group.rank}: {N.STATUS_NAMES.get(st[0], st[0])} (block={st[1]}, phase={st[2]})")
 
     def run_pass(self, order: np.ndarray, reset: bool = False) -> Progress:
+        from ..utils.trace import nvtx_range
+
         t0 = time.time()
+        trace, metrics = getattr(self, "trace", None), getattr(self, "metrics", None)
         if reset:
             self.reset_active_sets()
-        self.launch_pass(order)
-        objv, nnz_w, nnz_as, vio = self.evaluate()
+        with nvtx_range("darlin_pass"):
+            if trace is not None:
+                with trace.span("darlin_pass", cat="solver", device_timed=True, blocks=len(order), it=len(self.progress)):
+                    self.launch_pass(order)
+            else:
+                self.launch_pass(order)
+        with nvtx_range("evaluate_progress"):
+            objv, nnz_w, nnz_as, vio = self.evaluate()
         self.check_status()
+        if metrics is not None and self.group.rank == 0:
+            metrics.log(event="pass", it=len(self.progress), objective=objv, nnz_w=nnz_w, active=nnz_as, violation=vio,
+                        seconds=time.time() - t0, examples_per_s=self.total_rows / max(time.time() - t0, 1e-9),
+                        h2d_bytes=self.h2d_bytes)
         rel = 1.0 if not self.progress else self.progress[-1].objv / objv - 1.0
         p = Progress(objv, rel, nnz_w, vio, nnz_as, self.kkt_threshold, time.time() - t0)
         self.progress.append(p)
