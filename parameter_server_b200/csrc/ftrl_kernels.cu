@@ -274,19 +274,30 @@ __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratc
   }
 }
 
-// Scan the local table, append every unique key's record to its owner's inbox
-// (segment of this sender) and empty the table for the next minibatch.  A block
-// handles chunks of kSendChunk slots: positions inside the chunk come from
-// shared-memory counters, so there is one global cursor update per owner and chunk.
+// Scan the local table, append every unique key's record to its owner's inbox (segment of this
+// sender) and empty the table for the next minibatch.  A block handles chunks of kSendChunk slots.
+// The records of a chunk are first grouped by owner in shared memory, then written out so that
+// consecutive threads write consecutive inbox entries of one owner: the stores that cross NVLink
+// are full, coalesced lines instead of scattered 8-byte pieces.  One global cursor update per
+// owner and chunk.
 constexpr int kSendItems = 4;
-__device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const LocalScratch& L, uint32_t* s_cnt,
-                                                 uint32_t* s_base) {
+constexpr int kSendChunk = 256 * kSendItems;
+struct SendStage {
+  uint64_t key[kSendChunk];
+  uint64_t cnt[kSendChunk];
+  float g[kSendChunk];
+  uint32_t count[PSB_MAX_RANKS];      // records per owner in this chunk
+  uint32_t off[PSB_MAX_RANKS + 1];    // start of every owner's run in the staging arrays
+  uint32_t base[PSB_MAX_RANKS];       // first inbox index granted to this chunk, per owner
+};
+
+__device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const LocalScratch& L, SendStage* st) {
   const uint64_t n = L.lt_mask + 1;
   const uint64_t chunk = (uint64_t)blockDim.x * kSendItems;
   const int lane = threadIdx.x & 31;
   const int world = P.seps.world;
   for (uint64_t c0 = (uint64_t)blockIdx.x * chunk; c0 < n; c0 += (uint64_t)gridDim.x * chunk) {
-    if (threadIdx.x < PSB_MAX_RANKS) s_cnt[threadIdx.x] = 0;
+    if (threadIdx.x < PSB_MAX_RANKS) st->count[threadIdx.x] = 0;
     __syncthreads();
     uint64_t key[kSendItems];
     uint32_t pos[kSendItems];
@@ -305,13 +316,18 @@ __device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const Local
         if (m == 0u) continue;
         const int leader = __ffs(m) - 1;
         uint32_t base = 0;
-        if (lane == leader) base = atomicAdd(&s_cnt[t], (uint32_t)__popc(m));
+        if (lane == leader) base = atomicAdd(&st->count[t], (uint32_t)__popc(m));
         base = __shfl_sync(0xffffffffu, base, leader);
         if (own[k] == t) pos[k] = base + __popc(m & ((1u << lane) - 1u));
       }
     }
     __syncthreads();
-    if (threadIdx.x < world) s_base[threadIdx.x] = s_cnt[threadIdx.x] ? atomicAdd(L.send_cnt + threadIdx.x, s_cnt[threadIdx.x]) : 0u;
+    if (threadIdx.x == 0) {
+      uint32_t run = 0;
+      for (int t = 0; t < world; ++t) { st->off[t] = run; run += st->count[t]; }
+      st->off[world] = run;
+    }
+    if (threadIdx.x < world) st->base[threadIdx.x] = st->count[threadIdx.x] ? atomicAdd(L.send_cnt + threadIdx.x, st->count[threadIdx.x]) : 0u;
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < kSendItems; ++k) {
@@ -319,13 +335,22 @@ __device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const Local
       const uint64_t s = c0 + (uint64_t)k * blockDim.x + threadIdx.x;
       const float4 v = __ldcg(reinterpret_cast<const float4*>(L.lt_val + s));
       L.lt_keys[s] = kEmptyKey;
-      const int t = own[k];
-      const uint32_t idx = s_base[t] + pos[k];
+      const uint32_t at = st->off[own[k]] + pos[k];
+      st->key[at] = key[k];
+      st->g[at] = v.y;
+      st->cnt[at] = ((uint64_t)(uint32_t)v.z << 32) | (uint64_t)(uint32_t)v.w;
+    }
+    __syncthreads();
+    const uint32_t total = st->off[world];
+    for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+      int t = 0;
+      while (t + 1 < world && i >= st->off[t + 1]) ++t;
+      const uint32_t idx = st->base[t] + (i - st->off[t]);
       if (idx < P.in_cap) {
         const size_t at = (size_t)P.rank * P.in_cap + idx;
-        P.in_keys[t][at] = key[k];
-        P.in_g[t][at] = v.y;
-        P.in_cnt[t][at] = ((uint64_t)(uint32_t)v.z << 32) | (uint64_t)(uint32_t)v.w;
+        P.in_keys[t][at] = st->key[i];
+        P.in_g[t][at] = st->g[i];
+        P.in_cnt[t][at] = st->cnt[i];
       } else {
         set_status(L.status, kInboxOverflow, (uint32_t)t, idx);
       }
@@ -451,13 +476,13 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
   const int lane = threadIdx.x & 31;
   const int world = P.seps.world;
 
-  __shared__ HotCache hot;
-  __shared__ uint32_t s_cnt[PSB_MAX_RANKS], s_base[PSB_MAX_RANKS];
+  // the hot-slot cache (gradient phase) and the send staging area (routing phase) are never live together
+  __shared__ union PushSmem { HotCache hot; SendStage stage; } sm;
   PSB_TRACE(L, gtid, 4);
-  phase_grad(M, L, gtid >> 5, gsz >> 5, lane, &hot);
+  phase_grad(M, L, gtid >> 5, gsz >> 5, lane, &sm.hot);
   grid.sync();
   PSB_TRACE(L, gtid, 5);
-  phase_route_send(P, L, s_cnt, s_base);
+  phase_route_send(P, L, &sm.stage);
   grid.sync();
   PSB_TRACE(L, gtid, 6);
   // publish this sender's record count to every owner, then wait for all senders
