@@ -29,6 +29,7 @@ class DarlinConfig:
     feature_block_ratio: float = 4.0
     random_block_order: bool = True
     seed: int = 0
+    max_block_delay: int = 0              # tau: groups of tau+1 blocks compute all gradients before any update
     reset_nan_on_kkt_reset: bool = True   # reference leaves filtered weights NaN forever (quirk)
 
 
@@ -183,6 +184,28 @@ class DarlinRef:
         for k in range(len(self.X)):
             self._update_dual(k, c0, c1)
 
+    def run_group(self, blocks) -> None:
+        """Bounded delay: gradients of every block of the group first, then the updates, then the duals."""
+        if len(blocks) == 1:
+            return self.run_block(blocks[0])
+        grads = []
+        for b in blocks:
+            c0, c1 = self.blocks[b]
+            G, U = np.zeros(max(c1 - c0, 0)), np.zeros(max(c1 - c0, 0))
+            if c1 > c0:
+                for k in range(len(self.X)):
+                    g, u = self._gradients(k, c0, c1)
+                    G += g
+                    U += u
+            grads.append((c0, c1, G, U))
+        for c0, c1, G, U in grads:
+            if c1 > c0:
+                self._update_weight(c0, c1, G, U)
+        for c0, c1, _, _ in grads:
+            for k in range(len(self.X)):
+                if c1 > c0:
+                    self._update_dual(k, c0, c1)
+
     # ------------------------------------------------------------------ passes
     def evaluate(self) -> Tuple[float, int, int]:
         loss = sum(float(np.sum(np.log1p(1.0 / d))) for d in self.dual)
@@ -197,8 +220,10 @@ class DarlinRef:
                 a[:] = True
             if self.cfg.reset_nan_on_kkt_reset:
                 self.w[np.isnan(self.w)] = 0.0
-        for b in order:
-            self.run_block(int(b))
+        g = max(int(self.cfg.max_block_delay), 0) + 1
+        order = [int(b) for b in order]
+        for i in range(0, len(order), g):
+            self.run_group(order[i:i + g])
         objv, nnz_w, nnz_as = self.evaluate()
         rel = 1.0 if not self.progress else self.progress[-1].objv / objv - 1.0
         p = Progress(objv, rel, nnz_w, self.violation, nnz_as, self.kkt_threshold)

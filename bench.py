@@ -206,7 +206,8 @@ def run_darlin(args):
     off, idx, vals, y, _ = zipf_sparse_matrix(r1 - r0, cols, 90, seed=17 + rank, device=dev, zipf_s=1.0, wstar_frac=0.02, noise=0.3,
                                              wstar_seed=4242)
     cfg = DarlinConfig(lambda1=1.0, eta=1.0, delta_init=5.0, delta_max=10.0, kkt_ratio=100.0, max_pass=args.steps,
-                       epsilon=0.0, feature_block_ratio=4.0, random_block_order=True, seed=0)
+                       epsilon=0.0, feature_block_ratio=4.0, random_block_order=True, seed=0,
+                       max_block_delay=args.block_delay)
     impl = "nccl" if args.impl == "nccl" else "fused"
 
     def timed(sol, with_eval):
@@ -258,6 +259,7 @@ def run_darlin(args):
         "impl": "nccl-baseline" if impl == "nccl" else "fused",
         "config": {"model": "L1 logistic regression, DARLIN, lambda1=1, feature_block_ratio=4, delta 5/10, KKT ratio 100",
                    "global_batch": rows_total, "seq_len": None, "rows": rows_total, "features": cols,
+                   "max_block_delay": args.block_delay,
                    "nnz_per_row": nnz_total / rows_total, "feature_blocks": nblk,
                    "parallelism": f"dp{world} rows x key-range shards {world} (worker+server per GPU)",
                    "l2_policy": f"inputs larger than L2: {nnz_total * 8 >> 20} MiB of CSC row ids and values read per pass",
@@ -271,6 +273,8 @@ def main() -> None:
     ap.add_argument("--config", default="ftrl", choices=["ftrl", "darlin"],
                     help="ftrl: CTR-scale online FTRL (headline); darlin: batch L1-LR by block coordinate descent")
     ap.add_argument("--darlin-rows", type=int, default=677399)
+    ap.add_argument("--block-delay", type=int, default=0,
+                    help="DARLIN bounded delay tau (max_block_delay): tau+1 blocks share their synchronisation points")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)

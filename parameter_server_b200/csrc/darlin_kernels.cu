@@ -34,8 +34,8 @@ struct DarlinWorker {
   const int64_t* col_ptr;   // cols+1 offsets into row_idx/vals (CSC over local columns)
   const uint32_t* row_idx;  // nnz
   const float* vals;        // nnz, or nullptr for binary features
-  const float* y;           // rows, ±1
-  float* margin;            // rows: y_i·(Xw)_i
+  float2* ym;               // rows: {y_i (±1), margin m_i = y_i·(Xw)_i} — one 8-byte gather per non-zero
+  const uint32_t* col_of;   // nnz: local column of every non-zero, or nullptr (then found by binary search)
   float* w;                 // cols: worker's copy of the weights
   float* delta;             // cols: trust region
   uint8_t* active;          // cols: 1 = in the active set
@@ -68,8 +68,8 @@ struct DarlinSched {
   const int64_t* blk_lc;    // [nblocks_total][2] local column range of each block
   const int64_t* blk_sl;    // [nblocks_total][2] slot range of each block on this owner
   int nblk;
-  int pad;
-  uint64_t seq0;            // blocks processed before this launch (same on all ranks)
+  int group;                // blocks per synchronisation group (max_block_delay + 1)
+  uint64_t seq0;            // groups processed before this launch (same on all ranks)
   uint64_t* local_bar;      // in-GPU barrier counter (monotone)
   uint64_t bar0;            // barrier rounds completed before this launch
   uint32_t* abort_flag;
@@ -129,11 +129,11 @@ __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const D
     int64_t j = -1;
     float g = 0.f, u = 0.f;
     if (valid) {
-      j = find_col(Wk.col_ptr, lc0, lc1, e);
+      j = Wk.col_of ? (int64_t)Wk.col_of[e] : find_col(Wk.col_ptr, lc0, lc1, e);
       if (Wk.active[j]) {
-        const uint32_t i = Wk.row_idx[e];
-        const float yi = Wk.y[i];
-        const float tau = 1.f / (1.f + __expf(Wk.margin[i]));
+        const float2 ym = Wk.ym[Wk.row_idx[e]];
+        const float yi = ym.x;
+        const float tau = 1.f / (1.f + __expf(ym.y));
         const float t2 = tau * (1.f - tau);
         const float dj = Wk.delta[j];
         if (binary) {
@@ -223,12 +223,12 @@ __device__ __forceinline__ void darlin_update_margin(const DarlinWorker& Wk, int
                                                      size_t gsz) {
   const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
   for (int64_t e = p0 + (int64_t)gtid; e < p1; e += (int64_t)gsz) {
-    const int64_t j = find_col(Wk.col_ptr, lc0, lc1, e);
+    const int64_t j = Wk.col_of ? (int64_t)Wk.col_of[e] : find_col(Wk.col_ptr, lc0, lc1, e);
     const float d = __ldcg(Wk.dw + j);
     if (d != 0.f) {
       const uint32_t i = Wk.row_idx[e];
       const float v = Wk.vals ? Wk.vals[e] : 1.f;
-      atomicAdd(Wk.margin + i, Wk.y[i] * v * d);
+      atomicAdd(&Wk.ym[i].y, Wk.ym[i].x * v * d);
     }
   }
 }
@@ -243,28 +243,38 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
   const uint64_t G = gridDim.x;
   uint64_t bar = Q.bar0;
 
-  for (int b = 0; b < Q.nblk; ++b) {
+  // Blocks are processed in groups of Q.group consecutive entries of the order (group = max_block_delay + 1):
+  // the gradients of all blocks of a group are computed before any of them is updated, i.e. a block may see
+  // weights that are up to `group - 1` block updates old — the bounded-delay schedule of the reference
+  // (wait_time = time - tau, src/linear_method/darling.cc:45-69) with one set of synchronisation points per group.
+  const int group = Q.group > 0 ? Q.group : 1;
+  uint64_t seq = Q.seq0;
+  for (int b = 0; b < Q.nblk; b += group) {
     if (threadIdx.x == 0) s_abort = *(volatile uint32_t*)Q.abort_flag;
     __syncthreads();
     if (s_abort) break;  // uniform over the CTA
-    const int blk = Q.order[b];
-    const uint64_t seq = Q.seq0 + (uint64_t)b + 1;
-    const int64_t lc0 = Q.blk_lc[2 * blk], lc1 = Q.blk_lc[2 * blk + 1];
-    const int64_t s0 = Q.blk_sl[2 * blk], s1 = Q.blk_sl[2 * blk + 1];
+    const int ge = min(b + group, Q.nblk);
+    ++seq;
 
     // A: gradient + push, then announce arrival at every owner
-    darlin_grad_push(Wk, P, lc0, lc1, gtid >> 5, gsz >> 5, lane);
+    for (int q = b; q < ge; ++q) {
+      const int blk = Q.order[q];
+      darlin_grad_push(Wk, P, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid >> 5, gsz >> 5, lane);
+    }
     __syncthreads();
     if (threadIdx.x < P.world) {
       __threadfence_system();
       red_release_sys_add_u64(P.arrive[threadIdx.x], 1ull);
     }
-    // B: wait for all workers' CTAs, update this shard's slots of the block
+    // B: wait for all workers' CTAs, update this shard's slots of the blocks
     if (!cta_wait_counter(P.arrive[P.rank], seq * G * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
-      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)blk, 11); *Q.abort_flag = 1u; }
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 11); *Q.abort_flag = 1u; }
       break;
     }
-    darlin_update_weight(P, S, H, s0, s1, gtid, gsz);
+    for (int q = b; q < ge; ++q) {
+      const int blk = Q.order[q];
+      darlin_update_weight(P, S, H, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], gtid, gsz);
+    }
     __syncthreads();
     if (threadIdx.x < P.world) {
       __threadfence_system();
@@ -272,21 +282,27 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
     }
     // C: wait for all owners' CTAs, pull and apply
     if (!cta_wait_counter(P.updated[P.rank], seq * G * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
-      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)blk, 12); *Q.abort_flag = 1u; }
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 12); *Q.abort_flag = 1u; }
       break;
     }
-    darlin_pull(Wk, P, H, lc0, lc1, gtid, gsz);
+    for (int q = b; q < ge; ++q) {
+      const int blk = Q.order[q];
+      darlin_pull(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
+    }
     __syncthreads();
     if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
     if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
-      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)blk, 13); *Q.abort_flag = 1u; }
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 13); *Q.abort_flag = 1u; }
       break;
     }
-    darlin_update_margin(Wk, lc0, lc1, gtid, gsz);
+    for (int q = b; q < ge; ++q) {
+      const int blk = Q.order[q];
+      darlin_update_margin(Wk, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
+    }
     __syncthreads();
     if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
     if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
-      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)blk, 14); *Q.abort_flag = 1u; }
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 14); *Q.abort_flag = 1u; }
       break;
     }
   }
@@ -308,11 +324,11 @@ __global__ void k_darlin_grad_local(DarlinWorker Wk, int64_t lc0, int64_t lc1, f
     int64_t j = -1;
     float g = 0.f, u = 0.f;
     if (valid) {
-      j = find_col(Wk.col_ptr, lc0, lc1, e);
+      j = Wk.col_of ? (int64_t)Wk.col_of[e] : find_col(Wk.col_ptr, lc0, lc1, e);
       if (Wk.active[j]) {
-        const uint32_t i = Wk.row_idx[e];
-        const float yi = Wk.y[i];
-        const float tau = 1.f / (1.f + __expf(Wk.margin[i]));
+        const float2 ym = Wk.ym[Wk.row_idx[e]];
+        const float yi = ym.x;
+        const float tau = 1.f / (1.f + __expf(ym.y));
         const float t2 = tau * (1.f - tau);
         const float dj = Wk.delta[j];
         if (binary) { g = -yi * tau; u = fminf(t2 * __expf(dj), 0.25f); }
@@ -357,11 +373,11 @@ __global__ void k_darlin_update_margin(DarlinWorker Wk, int64_t lc0, int64_t lc1
 __global__ void k_darlin_margin_init(DarlinWorker Wk) {
   const int64_t p1 = Wk.col_ptr[Wk.cols];
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < p1; e += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t j = find_col(Wk.col_ptr, 0, Wk.cols, e);
+    const int64_t j = Wk.col_of ? (int64_t)Wk.col_of[e] : find_col(Wk.col_ptr, 0, Wk.cols, e);
     const float wj = Wk.w[j];
     if (wj != 0.f && wj == wj) {
       const uint32_t i = Wk.row_idx[e];
-      atomicAdd(Wk.margin + i, Wk.y[i] * (Wk.vals ? Wk.vals[e] : 1.f) * wj);
+      atomicAdd(&Wk.ym[i].y, Wk.ym[i].x * (Wk.vals ? Wk.vals[e] : 1.f) * wj);
     }
   }
 }
@@ -385,7 +401,7 @@ int psb_darlin_grid() {
     int per_sm = 0, sms = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, darlin_pass_kernel, 512, 0);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int want = 1;  // CTAs per SM: more CTAs hide gather latency, fewer make the per-block barriers cheaper
+    int want = 2;  // CTAs per SM (upper bound of the grid; the solver launches 1 per SM when every block synchronises): more CTAs hide gather latency, fewer make the per-block barriers cheaper
     if (const char* e = getenv("PSB_DARLIN_CTAS_PER_SM")) want = atoi(e) > 0 ? atoi(e) : want;
     g_darlin_grid[dev] = sms * (per_sm > want ? want : per_sm);  // upper bound; callers may launch fewer
   }

@@ -47,7 +47,7 @@ class DarlinConfig:
     epsilon: float = 1e-4
     feature_block_ratio: float = 4.0
     random_block_order: bool = True
-    max_block_delay: int = 0          # accepted; blocks run in order (delay 0 is within any bound)
+    max_block_delay: int = 0          # tau: tau+1 consecutive blocks form a group whose gradients precede its updates
     seed: int = 0
     reset_nan_on_kkt_reset: bool = True
     shard_by_data_range: bool = True  # servers split [min_key, max_key] instead of the whole uint64 space
@@ -175,7 +175,13 @@ class DarlinSolver:
         self.rows, self.cols, self.nnz = rows, P, nnz
         self.lkeys = lkeys
         self.col_ptr, self.row_idx, self.vals, self.y = col_ptr, row_idx, cvals, y.contiguous()
-        self.margin = torch.zeros(rows, dtype=f32, device=dev)
+        # label and margin of a row share 8 bytes: every non-zero gathers them with one access
+        self.ym = torch.stack([y.to(f32), torch.zeros(rows, dtype=f32, device=dev)], 1).contiguous()
+        self.margin = self.ym[:, 1]
+        # column id of every non-zero (saves a binary search per non-zero and phase); not kept in out-of-core
+        # mode, where it would add 50 % to the bytes streamed from the host
+        self.col_of = None if self.out_of_core else torch.repeat_interleave(
+            torch.arange(P, dtype=torch.int32, device=dev), col_ptr[1:] - col_ptr[:-1]).contiguous()
         self.w = torch.zeros(P, dtype=f32, device=dev)
         self.delta = torch.full((P,), self.cfg.delta_init, dtype=f32, device=dev)
         self.active = torch.ones(P, dtype=torch.uint8, device=dev)
@@ -247,7 +253,7 @@ class DarlinSolver:
             # the kernel indexes row_idx/vals with absolute CSC positions: bias the staging pointers by p0
             Wk.row_idx = self.stage_row[s].data_ptr() - 4 * p0
             Wk.vals = 0 if self.h_val is None else self.stage_val[s].data_ptr() - 4 * p0
-            Q = N.DarlinSched(order_t.data_ptr() + 4 * i, self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), 1, 0, self.seq + i,
+            Q = N.DarlinSched(order_t.data_ptr() + 4 * i, self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), 1, 1, self.seq + i,
                               self.local_bar.data_ptr(), self.bar + 2 * i, self.abort.data_ptr(), self.status.data_ptr())
             N.check(self._lib.psb_darlin_pass(C.byref(Wk), C.byref(self._P), C.byref(self._S), C.byref(Q), C.byref(H), self.grid,
                                               N.stream_ptr()), "darlin_pass")
@@ -258,8 +264,9 @@ class DarlinSolver:
 
     def _build_structs(self):
         Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),
-                            0 if self.vals is None else self.vals.data_ptr(), self.y.data_ptr(),
-                            self.margin.data_ptr(), self.w.data_ptr(), self.delta.data_ptr(), self.active.data_ptr(),
+                            0 if self.vals is None else self.vals.data_ptr(), self.ym.data_ptr(),
+                            0 if self.col_of is None else self.col_of.data_ptr(), self.w.data_ptr(), self.delta.data_ptr(),
+                            self.active.data_ptr(),
                             self.gslot.data_ptr(), self.gowner.data_ptr(), self.dw.data_ptr(), self.cols, self.rows, 0)
         P = N.DarlinPeers()
         for r in range(self.group.world):
@@ -270,6 +277,10 @@ class DarlinSolver:
         self._Wk, self._P, self._S = Wk, P, S
         self._lib.psb_darlin_grid.restype = C.c_int
         grid = self._lib.psb_darlin_grid()
+        # one CTA per SM keeps the per-block barriers cheap; with bounded delay the barriers are amortised over
+        # tau+1 blocks and a second CTA per SM hides more gather latency
+        sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
+        grid = min(grid, sms * (1 if self.cfg.max_block_delay <= 0 else 2))
         if self.group.world > 1:
             import torch.distributed as dist
 
@@ -314,13 +325,15 @@ class DarlinSolver:
             return self._pass_unfused(order)
         if self.out_of_core:
             return self._pass_streamed(np.asarray(order), order_t)
-        Q = N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), len(order), 0, self.seq,
+        group = max(int(self.cfg.max_block_delay), 0) + 1        # bounded delay: tau+1 blocks share their sync points
+        Q = N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), len(order), group, self.seq,
                           self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr())
         H = self._hyper()
         N.check(self._lib.psb_darlin_pass(C.byref(self._Wk), C.byref(self._P), C.byref(self._S), C.byref(Q),
                                           C.byref(H), self.grid, N.stream_ptr()), "darlin_pass")
-        self.seq += len(order)
-        self.bar += 2 * len(order)
+        ngroups = (len(order) + group - 1) // group
+        self.seq += ngroups
+        self.bar += 2 * ngroups
         self.kernel_launches += 1
 
     def _pass_unfused(self, order: np.ndarray) -> None:
@@ -382,7 +395,7 @@ class DarlinSolver:
 
     def evaluate(self) -> tuple:
         """(objective, nnz_w, nnz_active, violation) summed/maxed over ranks (Darling::evaluateProgress)."""
-        loss = reduce_sum(self.margin, "sum_logistic")
+        loss = reduce_sum(self.margin.contiguous(), "sum_logistic")
         srv = self.srv_w.local[: max(self.slots, 0)]
         if self.slots > 0:
             pen = reduce_sum(srv, "sum_abs").clone()

@@ -89,8 +89,8 @@ def ptr(t) -> C.c_void_p:
 
 # ------------------------------------------------------------------ DARLIN structs
 class DarlinWorker(C.Structure):
-    _fields_ = [("col_ptr", C.c_void_p), ("row_idx", C.c_void_p), ("vals", C.c_void_p), ("y", C.c_void_p),
-                ("margin", C.c_void_p), ("w", C.c_void_p), ("delta", C.c_void_p), ("active", C.c_void_p),
+    _fields_ = [("col_ptr", C.c_void_p), ("row_idx", C.c_void_p), ("vals", C.c_void_p), ("ym", C.c_void_p),
+                ("col_of", C.c_void_p), ("w", C.c_void_p), ("delta", C.c_void_p), ("active", C.c_void_p),
                 ("gslot", C.c_void_p), ("gowner", C.c_void_p), ("dw", C.c_void_p), ("cols", C.c_int64),
                 ("rows", C.c_int), ("pad", C.c_int)]
 
@@ -106,7 +106,7 @@ class DarlinServer(C.Structure):
 
 class DarlinSched(C.Structure):
     _fields_ = [("order", C.c_void_p), ("blk_lc", C.c_void_p), ("blk_sl", C.c_void_p), ("nblk", C.c_int),
-                ("pad", C.c_int), ("seq0", C.c_uint64), ("local_bar", C.c_void_p), ("bar0", C.c_uint64),
+                ("group", C.c_int), ("seq0", C.c_uint64), ("local_bar", C.c_void_p), ("bar0", C.c_uint64),
                 ("abort_flag", C.c_void_p), ("status", C.c_void_p)]
 
 

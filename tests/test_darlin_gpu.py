@@ -50,6 +50,25 @@ def test_darlin_matches_oracle(binary, impl):
     sol.check_status()
 
 
+@pytest.mark.parametrize("tau", [1, 3])
+def test_bounded_delay_groups_match_oracle(tau):
+    """max_block_delay = tau: tau+1 blocks share their synchronisation points (all gradients before any update)."""
+    from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver
+    from parameter_server_b200.parallel.peer import PeerGroup
+
+    off, keys, vals, y = _problem(False)
+    kw = dict(lambda1=0.3, max_pass=4, feature_block_ratio=1.0, seed=3, max_block_delay=tau)
+    sol = DarlinSolver(PeerGroup.single(torch.device("cuda", 0)), DarlinConfig(**kw))
+    sol.preprocess(off, keys, vals, y)
+    prog = sol.run()
+    ref = DarlinRef([(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64), vals.cpu().numpy(), y.cpu().numpy())], None,
+                    RefConfig(**kw))
+    rprog = ref.run()
+    for p, r in zip(prog, rprog):
+        assert p.objv == pytest.approx(r.objv, rel=2e-3)
+    sol.check_status()
+
+
 def test_darlin_model_dump(tmp_path):
     from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver
     from parameter_server_b200.parallel.peer import PeerGroup
