@@ -326,7 +326,6 @@ class SlotReader {
     }
     auto f = File::open(file, "r");
     if (!f) throw std::runtime_error("cannot open");
-    for (int s : {0}) (void)s;
     ExampleParser parser;
     parser.init(fmt_, ignore_grp_, shuffle_, beta_);
     std::map<int, SlotData> slots;

@@ -135,22 +135,9 @@ inline double exact_auc(const float* label, const float* pred, size_t n) {
   std::vector<size_t> idx(n);
   for (size_t i = 0; i < n; ++i) idx[i] = i;
   std::sort(idx.begin(), idx.end(), [&](size_t a, size_t b) { return pred[a] < pred[b]; });
-  double area = 0, cum_tp = 0, npos = 0;
+  // Mann-Whitney U statistic with average ranks for ties
+  double npos = 0, rank = 1, sum_pos_rank = 0;
   size_t i = 0;
-  while (i < n) {     // ties share the rank
-    size_t j = i;
-    double tp = 0, fp = 0;
-    while (j < n && pred[idx[j]] == pred[idx[i]]) { if (label[idx[j]] > 0) ++tp; else ++fp; ++j; }
-    area += fp * 0 + 0;  // placeholder to keep the structure obvious
-    (void)cum_tp;
-    i = j;
-    (void)tp;
-  }
-  // Mann-Whitney U with average ranks
-  area = 0;
-  double rank = 1;
-  i = 0;
-  double sum_pos_rank = 0;
   while (i < n) {
     size_t j = i;
     while (j < n && pred[idx[j]] == pred[idx[i]]) ++j;

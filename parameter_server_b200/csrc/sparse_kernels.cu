@@ -60,24 +60,9 @@ k_radix_count(const uint64_t* __restrict__ keys, size_t n, int pass, uint32_t* _
     block_hist[(size_t)d * gridDim.x + blockIdx.x] = s;
   }
 }
-// exclusive scan of block_hist in (digit-major, block-minor) order, in place; one thread per digit
-__global__ void k_radix_scan(uint32_t* __restrict__ block_hist, int nblocks, unsigned long long* __restrict__ digit_base /*[256]*/) {
-  __shared__ unsigned long long tot[kRadix];
-  const int d = threadIdx.x;
-  unsigned long long s = 0;
-  for (int b = 0; b < nblocks; ++b) s += block_hist[(size_t)d * nblocks + b];
-  tot[d] = s;
-  __syncthreads();
-  if (d == 0) {
-    unsigned long long run = 0;
-    for (int i = 0; i < kRadix; ++i) { const unsigned long long t = tot[i]; tot[i] = run; run += t; }
-  }
-  __syncthreads();
-  digit_base[d] = tot[d];
-}
 __global__ void __launch_bounds__(kSortThreads)
 k_radix_scatter(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ vals, size_t n, int pass,
-                const uint32_t* __restrict__ block_hist, const unsigned long long* __restrict__ digit_base,
+                const unsigned long long* __restrict__ block_off /*[256][nblocks]: first output position of (digit, block)*/,
                 uint64_t* __restrict__ out_keys, uint32_t* __restrict__ out_vals) {
   __shared__ unsigned long long woff[kSortThreads / 32][kRadix];
   __shared__ uint32_t wcnt[kSortThreads / 32][kRadix];
@@ -99,8 +84,7 @@ k_radix_scatter(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ 
   __syncthreads();
   // start of every (warp, digit) run: digit base + keys of this digit in earlier blocks + in earlier warps
   for (int d = threadIdx.x; d < kRadix; d += blockDim.x) {
-    // block_hist holds, after k_radix_prefix, the number of keys with digit d in earlier blocks
-    unsigned long long run = digit_base[d] + block_hist[(size_t)d * gridDim.x + blockIdx.x];
+    unsigned long long run = block_off[(size_t)d * gridDim.x + blockIdx.x];
 #pragma unroll
     for (int w = 0; w < kSortThreads / 32; ++w) { woff[w][d] = run; run += wcnt[w][d]; }
   }
@@ -121,13 +105,6 @@ k_radix_scatter(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ 
     __syncwarp();
   }
 }
-// turn per-block counts into exclusive prefixes over the blocks of each digit (row-wise), one thread per digit
-__global__ void k_radix_prefix(uint32_t* __restrict__ block_hist, int nblocks) {
-  const int d = threadIdx.x;
-  uint32_t run = 0;
-  for (int b = 0; b < nblocks; ++b) { const uint32_t t = block_hist[(size_t)d * nblocks + b]; block_hist[(size_t)d * nblocks + b] = run; run += t; }
-}
-
 // ---------------------------------------------------------------- scan (uint64 in, exclusive) in three kernels
 constexpr int kScanThreads = 256, kScanItems = 4, kScanTile = kScanThreads * kScanItems;
 __global__ void __launch_bounds__(kScanThreads)
@@ -150,12 +127,25 @@ k_scan_tiles(const uint32_t* __restrict__ in, unsigned long long* __restrict__ o
   for (int j = 0; j < kScanItems; ++j) { if (base + j < n) out[base + j] = run; run += v[j]; }
   if (threadIdx.x == kScanThreads - 1) tile_sum[blockIdx.x] = sh[threadIdx.x];
 }
-__global__ void k_scan_sums(unsigned long long* __restrict__ tile_sum, int ntiles, unsigned long long* __restrict__ total) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    unsigned long long run = 0;
-    for (int i = 0; i < ntiles; ++i) { const unsigned long long t = tile_sum[i]; tile_sum[i] = run; run += t; }
-    *total = run;
+// exclusive scan of the tile sums by one block of 1024 threads: every thread owns a contiguous run of tiles
+__global__ void __launch_bounds__(1024)
+k_scan_sums(unsigned long long* __restrict__ tile_sum, int ntiles, unsigned long long* __restrict__ total) {
+  __shared__ unsigned long long sh[1024];
+  const int per = (ntiles + 1023) / 1024;
+  const int b = threadIdx.x * per, e = min(b + per, ntiles);
+  unsigned long long s = 0;
+  for (int i = b; i < e; ++i) s += tile_sum[i];
+  sh[threadIdx.x] = s;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const unsigned long long t = threadIdx.x >= off ? sh[threadIdx.x - off] : 0;
+    __syncthreads();
+    sh[threadIdx.x] += t;
+    __syncthreads();
   }
+  unsigned long long run = sh[threadIdx.x] - s;
+  for (int i = b; i < e; ++i) { const unsigned long long t = tile_sum[i]; tile_sum[i] = run; run += t; }
+  if (threadIdx.x == 1023) *total = sh[1023];
 }
 __global__ void k_scan_add(unsigned long long* __restrict__ out, size_t n, const unsigned long long* __restrict__ tile_sum) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -297,16 +287,21 @@ int psb_digit_histograms(const uint64_t* keys, size_t n, unsigned long long* his
   k_digit_histograms<<<g1(n, 148 * 4), 256, 0, s>>>(keys, n, hist);
   return (int)cudaGetLastError();
 }
-// one stable radix pass on byte `pass`.  block_hist: 256 * nblocks uint32 (nblocks = ceil(n / psb_sort_tile())),
-// digit_base: 256 uint64.  vals / out_vals may be null.
-int psb_radix_pass(const uint64_t* keys, const uint32_t* vals, size_t n, int pass, uint32_t* block_hist, unsigned long long* digit_base,
-                   uint64_t* out_keys, uint32_t* out_vals, cudaStream_t s) {
+// one stable radix pass on byte `pass`.  Scratch: block_hist 256*nblocks uint32, block_off 256*nblocks uint64,
+// tile_sum ceil(256*nblocks / psb_scan_tile()) uint64, total 1 uint64 (nblocks = ceil(n / psb_sort_tile())).
+// vals / out_vals may be null.
+int psb_radix_pass(const uint64_t* keys, const uint32_t* vals, size_t n, int pass, uint32_t* block_hist, unsigned long long* block_off,
+                   unsigned long long* tile_sum, unsigned long long* total, uint64_t* out_keys, uint32_t* out_vals, cudaStream_t s) {
   if (n == 0) return 0;
   const int nblocks = (int)((n + kSortTile - 1) / kSortTile);
   k_radix_count<<<nblocks, kSortThreads, 0, s>>>(keys, n, pass, block_hist);
-  k_radix_scan<<<1, kRadix, 0, s>>>(block_hist, nblocks, digit_base);
-  k_radix_prefix<<<1, kRadix, 0, s>>>(block_hist, nblocks);
-  k_radix_scatter<<<nblocks, kSortThreads, 0, s>>>(keys, vals, n, pass, block_hist, digit_base, out_keys, out_vals);
+  // flattened digit-major exclusive scan: position of the first key of every (digit, block)
+  const size_t m = (size_t)kRadix * nblocks;
+  const int ntiles = (int)((m + kScanTile - 1) / kScanTile);
+  k_scan_tiles<<<ntiles, kScanThreads, 0, s>>>(block_hist, block_off, m, tile_sum);
+  k_scan_sums<<<1, 1024, 0, s>>>(tile_sum, ntiles, total);
+  k_scan_add<<<(unsigned)((m + 255) / 256), 256, 0, s>>>(block_off, m, tile_sum);
+  k_radix_scatter<<<nblocks, kSortThreads, 0, s>>>(keys, vals, n, pass, block_off, out_keys, out_vals);
   return (int)cudaGetLastError();
 }
 size_t psb_scan_tile() { return kScanTile; }
@@ -316,7 +311,7 @@ int psb_exclusive_scan_u32(const uint32_t* in, unsigned long long* out, size_t n
   const int ntiles = (int)((n + kScanTile - 1) / kScanTile);
   if (n == 0) { cudaMemsetAsync(total, 0, 8, s); return 0; }
   k_scan_tiles<<<ntiles, kScanThreads, 0, s>>>(in, out, n, tile_sum);
-  k_scan_sums<<<1, 32, 0, s>>>(tile_sum, ntiles, total);
+  k_scan_sums<<<1, 1024, 0, s>>>(tile_sum, ntiles, total);
   k_scan_add<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(out, n, tile_sum);
   return (int)cudaGetLastError();
 }

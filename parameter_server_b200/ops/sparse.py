@@ -54,7 +54,9 @@ def sort_pairs(keys: torch.Tensor, vals: Optional[torch.Tensor] = None) -> Tuple
     need = ((hist.view(8, 256) > 0).sum(1) > 1).tolist()
     nblocks = (n + lib.psb_sort_tile() - 1) // lib.psb_sort_tile()
     block_hist = torch.empty(256 * nblocks, dtype=torch.int32, device=dev)
-    digit_base = torch.empty(256, dtype=torch.int64, device=dev)
+    block_off = torch.empty(256 * nblocks, dtype=torch.int64, device=dev)
+    tile_sum = torch.empty((256 * nblocks + lib.psb_scan_tile() - 1) // lib.psb_scan_tile(), dtype=torch.int64, device=dev)
+    total = torch.empty(1, dtype=torch.int64, device=dev)
     # ping-pong between two scratch buffers; the caller's tensors are only ever read
     kbuf = [torch.empty_like(keys), None]
     vbuf = [None if vals is None else torch.empty_like(vals), None]
@@ -66,8 +68,8 @@ def sort_pairs(keys: torch.Tensor, vals: Optional[torch.Tensor] = None) -> Tuple
             kbuf[turn] = torch.empty_like(keys)
             vbuf[turn] = None if vals is None else torch.empty_like(vals)
         dst_k, dst_v = kbuf[turn], vbuf[turn]
-        N.check(lib.psb_radix_pass(N.ptr(src_k), N.ptr(src_v), _sz(n), p, N.ptr(block_hist), N.ptr(digit_base), N.ptr(dst_k),
-                                   N.ptr(dst_v), N.stream_ptr()), "radix_pass")
+        N.check(lib.psb_radix_pass(N.ptr(src_k), N.ptr(src_v), _sz(n), p, N.ptr(block_hist), N.ptr(block_off), N.ptr(tile_sum),
+                                   N.ptr(total), N.ptr(dst_k), N.ptr(dst_v), N.stream_ptr()), "radix_pass")
         src_k, src_v, turn = dst_k, dst_v, 1 - turn
     if src_k is keys:
         return keys.clone(), None if vals is None else vals.clone()
