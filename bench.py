@@ -248,7 +248,9 @@ def run_darlin(args):
         ooc.preprocess(off, idx, vals, y)
         ms2, _, h2d, objs = timed(ooc, True)
         e2e = {"value": rows_total * args.steps / (ms2 / 1e3), "unit": "examples/s", "ms_per_step": ms2 / args.steps,
-               "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": 40, "objective_last": objs[-1] if objs else None}
+               "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": 40, "objective_last": objs[-1] if objs else None,
+               # time to objective: objective after every pass; pass i completes at (i+1) * ms_per_step
+               "objective_trace": [round(o, 2) for o in objs]}
     clocks = sampler.stop()
     group.barrier()
     return {

@@ -20,7 +20,16 @@ def main(argv=None) -> int:
     if flags.gpus > 0 or "LOCAL_RANK" in os.environ:
         from .apps.gpu_job import run_gpu_job
 
-        run_gpu_job(flags)
+        try:
+            run_gpu_job(flags)
+        finally:
+            try:
+                import torch.distributed as dist
+
+                if dist.is_initialized():
+                    dist.destroy_process_group()
+            except Exception:
+                pass
         return 0
     if flags.my_rank < 0:
         print("-my_rank is required", file=sys.stderr)
