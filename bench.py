@@ -115,7 +115,8 @@ def run_ftrl(args) -> dict:
     eng = FTRLEngine(group, FTRLHyper(alpha=0.1, beta=1.0, lambda1=1.0, lambda2=0.1, rule=args.rule),
                      table_capacity=1 << args.table_log2, max_rows=rows, max_nnz=max_nnz,
                      local_capacity=1 << args.local_log2, timeout_s=args.timeout_s,
-                     impl="nccl" if args.impl == "nccl" else "fused")
+                     impl="nccl" if args.impl == "nccl" else "fused",
+                     track_counts=True if args.track_counts else None)
     # ---------------------------------------------------------------- device-resident timing
     for i in range(args.warmup):
         eng.step(batches[i % ring])
@@ -288,6 +289,8 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host-streaming) measurement")
     ap.add_argument("--rule", default="sumsq", choices=["count", "sumsq"],
                     help="per-key learning-rate statistic: reference count-based estimate or sum of g^2")
+    ap.add_argument("--track-counts", action="store_true",
+                    help="keep per-key pos/neg row counts although the sum-of-squares rule does not need them")
     ap.add_argument("--timeout-s", type=float, default=5.0, help="limit of in-kernel cross-GPU waits")
     args = ap.parse_args()
     if args.impl == "reference":

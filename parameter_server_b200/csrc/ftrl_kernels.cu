@@ -25,6 +25,7 @@
 // The schedule is bulk-synchronous (one legal serialisation of the reference's
 // eventual-consistency execution): pull(e) sees every update of step e-1.
 #include <cstddef>
+#include <cstdlib>
 
 #include "psb_common.cuh"
 
@@ -107,7 +108,34 @@ struct LocalScratch {
   double* stats;       // [0] Σloss [1] rows [2] ‖w‖₁ [3] ‖w‖₂² [4] nnz(w) [5] unique keys [6] table entries
   uint32_t* status;    // StatusCode etc.
   uint64_t* trace;     // optional [16]: globaltimer at phase boundaries of the last step (see kTrace*)
+  // Split layout for update rules that need no pos/neg counts (soa != 0): the pulled weight and
+  // the gradient accumulator live in two 4-byte arrays, a quarter of the footprint of lt_val, so
+  // the random accesses of the SpMV and of the gradient scatter stay inside L2.  The gather
+  // phase writes lt_w and resets lt_g for every key of the minibatch.
+  float* lt_w;
+  float* lt_g;
+  uint32_t soa;
+  uint32_t pad;
 };
+
+// Streams (keys, slot map, inbox records) are read or written once per phase; with
+// PSB_L2_HINTS they carry an evict-first L2 policy so that the hash tables stay resident.
+#ifndef PSB_L2_HINTS
+#define PSB_L2_HINTS 1
+#endif
+#if PSB_L2_HINTS
+#define PSB_STREAM_POLICY(pol) const uint64_t pol = l2_evict_first_policy()
+#define PSB_LD_U64(p, pol) ld_stream_u64((p), (pol))
+#define PSB_LD_U32(p, pol) ld_stream_u32((p), (pol))
+#define PSB_LD_F32(p, pol) ld_stream_f32((p), (pol))
+#define PSB_ST_U32(p, v, pol) st_stream_u32((p), (v), (pol))
+#else
+#define PSB_STREAM_POLICY(pol) const uint64_t pol = 0; (void)pol
+#define PSB_LD_U64(p, pol) (*(p))
+#define PSB_LD_U32(p, pol) (*(p))
+#define PSB_LD_F32(p, pol) (*(p))
+#define PSB_ST_U32(p, v, pol) (*(p) = (v))
+#endif
 
 // trace slots: pull kernel 0 start, 1 localized, 2 gathered, 3 block-0 end;
 //              push kernel 4 start, 5 gradients done, 6 records sent, 7 all senders arrived, 8 applied
@@ -121,44 +149,45 @@ constexpr uint32_t kBadSlot = 0xFFFFFFFFu;
 __device__ __forceinline__ uint64_t shard_hash(uint64_t key, uint32_t shift) { return mix64(key) >> shift; }
 
 // ------------------------------------------------------------------ phases
+// De-duplication of the minibatch's keys is bound by memory latency, not by bandwidth: every key
+// costs a streamed load of the key and then a dependent random read of the table.  The loop is
+// therefore software-pipelined: while key i is resolved, the table read of the thread's next key
+// and the load of the key after that are already in flight (the asm loads are issued in program
+// order, their results are used one and two iterations later).  A table read that is stale by the
+// time it is used only sends the key through the compare-and-swap path, which re-reads.
+__device__ __forceinline__ uint64_t ld_table_u64(const uint64_t* p) {
+  uint64_t v; asm volatile("ld.global.u64 %0, [%1];" : "=l"(v) : "l"(p)); return v;
+}
+
 __device__ __forceinline__ void phase_localize(const Minibatch& M, const LocalScratch& L, int max_probe,
                                                size_t gtid, size_t gsz) {
-  // four independent probes in flight per thread: the first table read of each key is issued
-  // before any of them is resolved
-#ifndef PSB_LOCALIZE_UNROLL
-#define PSB_LOCALIZE_UNROLL 1
-#endif
-  constexpr int U = PSB_LOCALIZE_UNROLL;
-  for (int64_t e = (int64_t)gtid; e < M.nnz; e += (int64_t)gsz * U) {
-    uint64_t key[U], h[U], cur[U];
-#pragma unroll
-    for (int k = 0; k < U; ++k) {
-      const int64_t i = e + (int64_t)k * (int64_t)gsz;
-      key[k] = i < M.nnz ? M.keys[i] : kEmptyKey;
+  PSB_STREAM_POLICY(pol);
+  const int64_t step = (int64_t)gsz;
+  int64_t i = (int64_t)gtid;
+  if (i >= M.nnz) return;
+  uint64_t key0 = PSB_LD_U64(M.keys + i, pol);
+  uint64_t key1 = i + step < M.nnz ? PSB_LD_U64(M.keys + i + step, pol) : kEmptyKey;
+  uint64_t h0 = (mix64(key0) >> L.lt_shift) & L.lt_mask;
+  uint64_t cur0 = ld_table_u64(L.lt_keys + h0);
+  for (; i < M.nnz; i += step) {
+    uint64_t key2 = kEmptyKey, h1 = 0, cur1 = 0;
+    if (i + 2 * step < M.nnz) key2 = PSB_LD_U64(M.keys + i + 2 * step, pol);
+    if (i + step < M.nnz) {
+      h1 = (mix64(key1) >> L.lt_shift) & L.lt_mask;
+      cur1 = ld_table_u64(L.lt_keys + h1);
     }
-#pragma unroll
-    for (int k = 0; k < U; ++k) {
-#ifdef PSB_LOCAL_HASH_LOW
-      h[k] = mix64(key[k]) & L.lt_mask;
-#else
-      h[k] = (mix64(key[k]) >> L.lt_shift) & L.lt_mask;
-#endif
-      cur[k] = key[k] != kEmptyKey ? L.lt_keys[h[k]] : 0ull;
-    }
-#pragma unroll
-    for (int k = 0; k < U; ++k) {
-      const int64_t i = e + (int64_t)k * (int64_t)gsz;
-      if (i >= M.nnz) continue;
-      uint64_t slot = h[k];
-      if (cur[k] != key[k]) {
-        slot = table_find_or_insert(L.lt_keys, L.lt_mask, h[k], key[k], max_probe);
-        if (slot == ~0ull) {
-          set_status(L.status, kLocalTableFull, 0, 0);
-          slot = kBadSlot;
-        }
+    uint32_t slot = (uint32_t)h0;
+    if (cur0 != key0) {
+      const uint64_t s = table_find_or_insert(L.lt_keys, L.lt_mask, h0, key0, max_probe);
+      if (s == ~0ull) {
+        set_status(L.status, kLocalTableFull, 0, 0);
+        slot = kBadSlot;
+      } else {
+        slot = (uint32_t)s;
       }
-      L.slot_of[i] = (uint32_t)slot;
     }
+    PSB_ST_U32(L.slot_of + i, slot, pol);
+    key0 = key1; h0 = h1; cur0 = cur1; key1 = key2;
   }
 }
 
@@ -176,6 +205,7 @@ __device__ __forceinline__ float probe_weight(const ShardSlot* tab, uint64_t mas
   return 0.f;
 }
 
+template <bool kCounts>
 __device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScratch& L, size_t gtid,
                                              size_t gsz) {
   uint32_t uniq = 0;
@@ -183,12 +213,18 @@ __device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScra
     const uint64_t key = __ldcg(L.lt_keys + s);
     if (key != kEmptyKey) {
       const int o = route_owner(P.seps, key);
-      LocalSlot v;
-      v.w = probe_weight(P.tab[o], P.tab_mask, P.tab_shift, key, P.max_probe);
-      v.g = 0.f;
-      v.pos = 0.f;
-      v.neg = 0.f;
-      *reinterpret_cast<float4*>(L.lt_val + s) = *reinterpret_cast<float4*>(&v);
+      const float w = probe_weight(P.tab[o], P.tab_mask, P.tab_shift, key, P.max_probe);
+      if (kCounts) {
+        LocalSlot v;
+        v.w = w;
+        v.g = 0.f;
+        v.pos = 0.f;
+        v.neg = 0.f;
+        *reinterpret_cast<float4*>(L.lt_val + s) = *reinterpret_cast<float4*>(&v);
+      } else {
+        L.lt_w[s] = w;
+        L.lt_g[s] = 0.f;  // here, not after the read in the routing phase: a store there costs 70 us
+      }
       ++uniq;
     }
   }
@@ -196,17 +232,33 @@ __device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScra
   if ((threadIdx.x & 31) == 0 && uniq) atomicAdd(&L.stats[5], (double)uniq);
 }
 
+// Rows are walked a warp at a time; a lane first issues the loads of up to kRowBatch of its
+// non-zeros, then consumes them, so that several slot-map loads are in flight per lane.
+#ifndef PSB_ROW_BATCH
+#define PSB_ROW_BATCH 4
+#endif
+constexpr int kRowBatch = PSB_ROW_BATCH;
+
+template <bool kCounts>
 __device__ __forceinline__ void phase_spmv_loss(const Minibatch& M, const LocalScratch& L, size_t gwarp,
                                                 size_t nwarps, int lane) {
   double loss = 0.0;
+  PSB_STREAM_POLICY(pol);
   for (int64_t row = (int64_t)gwarp; row < M.rows; row += (int64_t)nwarps) {
     const int64_t b = M.offsets[row], e = M.offsets[row + 1];
     float s = 0.f;
-    for (int64_t i = b + lane; i < e; i += 32) {
-      const uint32_t sl = L.slot_of[i];
-      if (sl != kBadSlot) {
-        const float w = L.lt_val[sl].w;
-        s += M.vals ? w * M.vals[i] : w;
+    for (int64_t i0 = b + lane; i0 < e; i0 += 32 * kRowBatch) {
+      uint32_t sl[kRowBatch];
+      float x[kRowBatch];
+#pragma unroll
+      for (int k = 0; k < kRowBatch; ++k) {
+        const int64_t i = i0 + 32 * k;
+        sl[k] = i < e ? PSB_LD_U32(L.slot_of + i, pol) : kBadSlot;
+        x[k] = (M.vals != nullptr && i < e) ? PSB_LD_F32(M.vals + i, pol) : 1.f;
+      }
+#pragma unroll
+      for (int k = 0; k < kRowBatch; ++k) {
+        if (sl[k] != kBadSlot) s += x[k] * (kCounts ? L.lt_val[sl[k]].w : L.lt_w[sl[k]]);
       }
     }
     s = warp_sum(s);
@@ -226,41 +278,59 @@ __device__ __forceinline__ void phase_spmv_loss(const Minibatch& M, const LocalS
 // shared memory and flushing once per block removes the same-address serialisation of
 // global atomics.  Entries are claimed first come, first served; a slot that finds its
 // cache line taken by another slot falls back to the global atomic.
-constexpr int kHotEntries = 1024;
+#ifndef PSB_HOT_LOG2
+#define PSB_HOT_LOG2 10
+#endif
+constexpr int kHotEntries = 1 << PSB_HOT_LOG2;
 struct HotCache {
   uint32_t slot[kHotEntries];
   float g[kHotEntries];
   unsigned long long cnt[kHotEntries];
 };
 
+template <bool kCounts>
 __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratch& L, size_t gwarp,
                                            size_t nwarps, int lane, HotCache* hc) {
   for (int i = threadIdx.x; i < kHotEntries; i += blockDim.x) {
     hc->slot[i] = kBadSlot;
     hc->g[i] = 0.f;
-    hc->cnt[i] = 0ull;
+    if (kCounts) hc->cnt[i] = 0ull;
   }
   __syncthreads();
+  PSB_STREAM_POLICY(pol);
   for (int64_t row = (int64_t)gwarp; row < M.rows; row += (int64_t)nwarps) {
     const int64_t b = M.offsets[row], e = M.offsets[row + 1];
     const float c = L.coef[row];
     const bool is_pos = M.y[row] > 0.f;
     const unsigned long long inc = is_pos ? (1ull << 32) : 1ull;
-    for (int64_t i = b + lane; i < e; i += 32) {
-      const uint32_t sl = L.slot_of[i];
-      if (sl == kBadSlot) continue;
-      const float gv = M.vals ? c * M.vals[i] : c;
-      const int h = (int)((sl * 2654435761u) >> 22);  // top 10 bits
-      uint32_t cur = hc->slot[h];
-      if (cur == kBadSlot) {
-        const uint32_t prev = atomicCAS(&hc->slot[h], kBadSlot, sl);
-        cur = prev == kBadSlot ? sl : prev;
+    for (int64_t i0 = b + lane; i0 < e; i0 += 32 * kRowBatch) {
+      uint32_t sls[kRowBatch];
+      float x[kRowBatch];
+#pragma unroll
+      for (int k = 0; k < kRowBatch; ++k) {
+        const int64_t i = i0 + 32 * k;
+        sls[k] = i < e ? PSB_LD_U32(L.slot_of + i, pol) : kBadSlot;
+        x[k] = (M.vals != nullptr && i < e) ? PSB_LD_F32(M.vals + i, pol) : 1.f;
       }
-      if (cur == sl) {
-        atomicAdd(&hc->g[h], gv);
-        atomicAdd(&hc->cnt[h], inc);
-      } else {
-        red_add_slot(L.lt_val + sl, gv, is_pos ? 1.f : 0.f, is_pos ? 0.f : 1.f);
+#pragma unroll
+      for (int k = 0; k < kRowBatch; ++k) {
+        const uint32_t sl = sls[k];
+        if (sl == kBadSlot) continue;
+        const float gv = c * x[k];
+        const int h = (int)((sl * 2654435761u) >> (32 - PSB_HOT_LOG2));  // top bits
+        uint32_t cur = hc->slot[h];
+        if (cur == kBadSlot) {
+          const uint32_t prev = atomicCAS(&hc->slot[h], kBadSlot, sl);
+          cur = prev == kBadSlot ? sl : prev;
+        }
+        if (cur == sl) {
+          atomicAdd(&hc->g[h], gv);
+          if (kCounts) atomicAdd(&hc->cnt[h], inc);
+        } else if (kCounts) {
+          red_add_slot(L.lt_val + sl, gv, is_pos ? 1.f : 0.f, is_pos ? 0.f : 1.f);
+        } else {
+          atomicAdd(L.lt_g + sl, gv);
+        }
       }
     }
   }
@@ -268,8 +338,12 @@ __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratc
   for (int i = threadIdx.x; i < kHotEntries; i += blockDim.x) {
     const uint32_t sl = hc->slot[i];
     if (sl != kBadSlot) {
-      const unsigned long long c = hc->cnt[i];
-      red_add_slot(L.lt_val + sl, hc->g[i], (float)(uint32_t)(c >> 32), (float)(uint32_t)c);
+      if (kCounts) {
+        const unsigned long long c = hc->cnt[i];
+        red_add_slot(L.lt_val + sl, hc->g[i], (float)(uint32_t)(c >> 32), (float)(uint32_t)c);
+      } else {
+        atomicAdd(L.lt_g + sl, hc->g[i]);
+      }
     }
   }
 }
@@ -291,6 +365,7 @@ struct SendStage {
   uint32_t base[PSB_MAX_RANKS];       // first inbox index granted to this chunk, per owner
 };
 
+template <bool kCounts>
 __device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const LocalScratch& L, SendStage* st) {
   const uint64_t n = L.lt_mask + 1;
   const uint64_t chunk = (uint64_t)blockDim.x * kSendItems;
@@ -333,12 +408,16 @@ __device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const Local
     for (int k = 0; k < kSendItems; ++k) {
       if (own[k] < 0) continue;
       const uint64_t s = c0 + (uint64_t)k * blockDim.x + threadIdx.x;
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(L.lt_val + s));
-      L.lt_keys[s] = kEmptyKey;
       const uint32_t at = st->off[own[k]] + pos[k];
       st->key[at] = key[k];
-      st->g[at] = v.y;
-      st->cnt[at] = ((uint64_t)(uint32_t)v.z << 32) | (uint64_t)(uint32_t)v.w;
+      L.lt_keys[s] = kEmptyKey;
+      if (kCounts) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(L.lt_val + s));
+        st->g[at] = v.y;
+        st->cnt[at] = ((uint64_t)(uint32_t)v.z << 32) | (uint64_t)(uint32_t)v.w;
+      } else {
+        st->g[at] = __ldcg(L.lt_g + s);
+      }
     }
     __syncthreads();
     const uint32_t total = st->off[world];
@@ -350,7 +429,7 @@ __device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const Local
         const size_t at = (size_t)P.rank * P.in_cap + idx;
         P.in_keys[t][at] = st->key[i];
         P.in_g[t][at] = st->g[i];
-        P.in_cnt[t][at] = st->cnt[i];
+        if (kCounts) P.in_cnt[t][at] = st->cnt[i];
       } else {
         set_status(L.status, kInboxOverflow, (uint32_t)t, idx);
       }
@@ -394,6 +473,7 @@ __device__ __forceinline__ void ftrl_update(ShardState& e, float g, uint32_t dpo
   dnnz += (w != 0.f && w_old == 0.f) - (w == 0.f && w_old != 0.f);
 }
 
+template <bool kCounts>
 __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
                                             const uint64_t* rk, const float* rg, const uint64_t* rc,
                                             uint32_t n, const FtrlHyper& h, double* stats, uint32_t* status,
@@ -404,7 +484,7 @@ __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint3
     const uint64_t key = __ldcg(rk + i);
     if (key == kEmptyKey) continue;
     const float g = __ldcg(rg + i);
-    const uint64_t c = __ldcg(rc + i);
+    const uint64_t c = kCounts ? __ldcg(rc + i) : 0ull;
     uint64_t slot = shard_hash(key, shift) & mask;
     bool found = false;
     for (int p = 0; p < max_probe; ++p) {
@@ -443,7 +523,13 @@ __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint3
 }
 
 // ------------------------------------------------------------ fused kernels
-__global__ void __launch_bounds__(256)
+// 8 blocks of 256 threads per SM (32 registers per thread): the phases of this kernel are bound by
+// memory latency and speed up with every resident warp.
+#ifndef PSB_PULL_MIN_BLOCKS
+#define PSB_PULL_MIN_BLOCKS 8
+#endif
+template <bool kCounts>
+__global__ void __launch_bounds__(256, PSB_PULL_MIN_BLOCKS)
 ftrl_pull_spmv_kernel(FtrlPeers P, Minibatch M, LocalScratch L, uint32_t epoch) {
   cg::grid_group grid = cg::this_grid();
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -461,13 +547,14 @@ ftrl_pull_spmv_kernel(FtrlPeers P, Minibatch M, LocalScratch L, uint32_t epoch) 
   phase_localize(M, L, P.max_probe, gtid, gsz);
   grid.sync();
   PSB_TRACE(L, gtid, 1);
-  phase_gather(P, L, gtid, gsz);
+  phase_gather<kCounts>(P, L, gtid, gsz);
   grid.sync();
   PSB_TRACE(L, gtid, 2);
-  phase_spmv_loss(M, L, gtid >> 5, gsz >> 5, lane);
+  phase_spmv_loss<kCounts>(M, L, gtid >> 5, gsz >> 5, lane);
   PSB_TRACE(L, gtid, 3);
 }
 
+template <bool kCounts>
 __global__ void __launch_bounds__(256)
 ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, uint32_t epoch) {
   cg::grid_group grid = cg::this_grid();
@@ -479,10 +566,10 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
   // the hot-slot cache (gradient phase) and the send staging area (routing phase) are never live together
   __shared__ union PushSmem { HotCache hot; SendStage stage; } sm;
   PSB_TRACE(L, gtid, 4);
-  phase_grad(M, L, gtid >> 5, gsz >> 5, lane, &sm.hot);
+  phase_grad<kCounts>(M, L, gtid >> 5, gsz >> 5, lane, &sm.hot);
   grid.sync();
   PSB_TRACE(L, gtid, 5);
-  phase_route_send(P, L, &sm.stage);
+  phase_route_send<kCounts>(P, L, &sm.stage);
   grid.sync();
   PSB_TRACE(L, gtid, 6);
   // publish this sender's record count to every owner, then wait for all senders
@@ -504,9 +591,9 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
   for (int s = 0; s < world; ++s) {
     const uint32_t n = __ldcg(L.recv_cnt + s);
     const size_t off = (size_t)s * P.in_cap;
-    phase_apply(P.tab[P.rank], P.tab_mask, P.tab_shift, P.max_probe,
-                P.in_keys[P.rank] + off, P.in_g[P.rank] + off, P.in_cnt[P.rank] + off, n, H, L.stats,
-                L.status, gtid, gsz);
+    phase_apply<kCounts>(P.tab[P.rank], P.tab_mask, P.tab_shift, P.max_probe,
+                         P.in_keys[P.rank] + off, P.in_g[P.rank] + off, P.in_cnt[P.rank] + off, n, H, L.stats,
+                         L.status, gtid, gsz);
     grid.sync();
   }
   PSB_TRACE(L, gtid, 8);
@@ -523,12 +610,12 @@ __global__ void k_localize(Minibatch M, LocalScratch L, int max_probe) {
 __global__ void k_spmv_loss(Minibatch M, LocalScratch L) {
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gtid == 0) L.stats[1] += (double)M.rows;
-  phase_spmv_loss(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31);
+  phase_spmv_loss<true>(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31);
 }
 __global__ void k_grad(Minibatch M, LocalScratch L) {
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   __shared__ HotCache hot;
-  phase_grad(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31, &hot);
+  phase_grad<true>(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31, &hot);
 }
 // count unique keys per owner (pass 1 of packing for all_to_all_v)
 __global__ void k_count_owner(KeySeps seps, LocalScratch L, uint32_t* counts) {
@@ -596,8 +683,8 @@ __global__ void k_pack_push(const uint32_t* slots, uint32_t n, LocalScratch L, f
 __global__ void k_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe, const uint64_t* rk,
                         const float* rg, const uint64_t* rc, uint32_t n, FtrlHyper h, double* stats,
                         uint32_t* status) {
-  phase_apply(tab, mask, shift, max_probe, rk, rg, rc, n, h, stats, status,
-              (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+  phase_apply<true>(tab, mask, shift, max_probe, rk, rg, rc, n, h, stats, status,
+                    (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
 }
 __global__ void k_clear_local(LocalScratch L) {
   for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += (size_t)gridDim.x * blockDim.x)
@@ -622,7 +709,7 @@ __global__ void k_dump_nonzero(const ShardSlot* tab, uint64_t mask, uint64_t* ou
 using namespace psb;
 
 namespace {
-int g_coop_blocks_pull[16] = {0}, g_coop_blocks_push[16] = {0};
+int g_coop_blocks_pull[2][16] = {{0}}, g_coop_blocks_push[2][16] = {{0}};
 
 template <typename K>
 int coop_grid(K kernel, int* cache) {
@@ -633,7 +720,9 @@ int coop_grid(K kernel, int* cache) {
     int per_sm = 0, sms = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (per_sm > 8) per_sm = 8;
+    int cap = 8;
+    if (const char* e = getenv("PSB_FTRL_CTAS_PER_SM")) cap = atoi(e) > 0 ? atoi(e) : cap;
+    if (per_sm > cap) per_sm = cap;
     cache[dev] = per_sm * sms;
   }
   return cache[dev];
@@ -650,20 +739,29 @@ extern "C" {
 
 int psb_ftrl_pull_spmv(const FtrlPeers* P, const Minibatch* M, const LocalScratch* L, uint32_t epoch,
                        cudaStream_t stream) {
-  const int grid = coop_grid(ftrl_pull_spmv_kernel, g_coop_blocks_pull);
+  const bool soa = L->soa != 0;
+  if (soa && (L->lt_w == nullptr || L->lt_g == nullptr)) return (int)cudaErrorInvalidValue;
+  void* kernel = soa ? (void*)ftrl_pull_spmv_kernel<false> : (void*)ftrl_pull_spmv_kernel<true>;
+  const int grid = soa ? coop_grid(ftrl_pull_spmv_kernel<false>, g_coop_blocks_pull[0])
+                       : coop_grid(ftrl_pull_spmv_kernel<true>, g_coop_blocks_pull[1]);
   if (grid <= 0) return (int)cudaErrorLaunchFailure;
   FtrlPeers p = *P; Minibatch m = *M; LocalScratch l = *L;
   void* args[] = {&p, &m, &l, &epoch};
-  return (int)cudaLaunchCooperativeKernel((void*)ftrl_pull_spmv_kernel, dim3(grid), dim3(256), args, 0, stream);
+  return (int)cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(256), args, 0, stream);
 }
 
 int psb_ftrl_push_update(const FtrlPeers* P, const Minibatch* M, const LocalScratch* L, const FtrlHyper* H,
                          uint32_t epoch, cudaStream_t stream) {
-  const int grid = coop_grid(ftrl_push_update_kernel, g_coop_blocks_push);
+  const bool soa = L->soa != 0;
+  // the count-based rule needs the pos/neg counts that the split layout does not carry
+  if (soa && (H->rule == 0 || L->lt_w == nullptr || L->lt_g == nullptr)) return (int)cudaErrorInvalidValue;
+  void* kernel = soa ? (void*)ftrl_push_update_kernel<false> : (void*)ftrl_push_update_kernel<true>;
+  const int grid = soa ? coop_grid(ftrl_push_update_kernel<false>, g_coop_blocks_push[0])
+                       : coop_grid(ftrl_push_update_kernel<true>, g_coop_blocks_push[1]);
   if (grid <= 0) return (int)cudaErrorLaunchFailure;
   FtrlPeers p = *P; Minibatch m = *M; LocalScratch l = *L; FtrlHyper h = *H;
   void* args[] = {&p, &m, &l, &h, &epoch};
-  return (int)cudaLaunchCooperativeKernel((void*)ftrl_push_update_kernel, dim3(grid), dim3(256), args, 0, stream);
+  return (int)cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(256), args, 0, stream);
 }
 
 int psb_ftrl_localize(const Minibatch* M, const LocalScratch* L, int max_probe, cudaStream_t s) {

@@ -76,6 +76,29 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
 }
 
+// ---- L2 residency hints ----
+// A minibatch step streams large arrays once (keys, slot maps, inbox records) next to hash
+// tables that are probed at random many times.  Streams carry an evict-first policy so that
+// they do not push the tables out of the 126 MB L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t p; asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p)); return p;
+}
+__device__ __forceinline__ uint64_t l2_evict_last_policy() {
+  uint64_t p; asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p)); return p;
+}
+__device__ __forceinline__ uint64_t ld_stream_u64(const uint64_t* p, uint64_t pol) {
+  uint64_t v; asm volatile("ld.global.L2::cache_hint.u64 %0, [%1], %2;" : "=l"(v) : "l"(p), "l"(pol)); return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_u32(const uint32_t* p, uint64_t pol) {
+  uint32_t v; asm volatile("ld.global.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol)); return v;
+}
+__device__ __forceinline__ float ld_stream_f32(const float* p, uint64_t pol) {
+  float v; asm volatile("ld.global.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol)); return v;
+}
+__device__ __forceinline__ void st_stream_u32(uint32_t* p, uint32_t v, uint64_t pol) {
+  asm volatile("st.global.L2::cache_hint.u32 [%0], %1, %2;" :: "l"(p), "r"(v), "l"(pol) : "memory");
+}
+
 // Wait until (*flag >> 32) >= want_epoch, at most timeout_ns. Returns the flag
 // value on success; on timeout sets *ok=false and returns the last value seen.
 __device__ __forceinline__ uint64_t wait_epoch_ge(const uint64_t* flag, uint32_t want_epoch,

@@ -71,9 +71,18 @@ class FTRLEngine:
 
     def __init__(self, group: PeerGroup, hyper: FTRLHyper, *, table_capacity: int, max_rows: int, max_nnz: int,
                  local_capacity: Optional[int] = None, timeout_s: float = 2.0, max_probe: int = 512,
-                 key_range: Optional[Range] = None, impl: str = "fused"):
+                 key_range: Optional[Range] = None, impl: str = "fused", track_counts: Optional[bool] = None):
+        """``track_counts``: keep the per-key pos/neg row counts of FTRL::countKeys
+        (src/linear_method/ftrl.cc:154-174).  The count rule needs them; the Σg² rule does not, and
+        without them the fused kernels use a 4-byte-per-value split layout of the minibatch table and
+        12-byte push records.  Default: on for ``rule="count"``, off for ``rule="sumsq"``."""
         if group.world > N.MAX_RANKS:
             raise ValueError(f"at most {N.MAX_RANKS} ranks per box")
+        if track_counts is None:
+            track_counts = hyper.rule == "count" or impl != "fused"
+        if hyper.rule == "count" and not track_counts:
+            raise ValueError('rule="count" needs track_counts')
+        self.track_counts = bool(track_counts) or impl != "fused"
         self.group, self.hyper, self.impl = group, hyper, impl
         self.dev = group.device
         self.cap = _pow2_at_least(table_capacity)
@@ -139,6 +148,10 @@ class FTRLEngine:
         L.stats, L.status = self.stats.data_ptr(), self.status.data_ptr()
         self.trace = torch.zeros((16,), dtype=torch.int64, device=d)
         L.trace = self.trace.data_ptr()
+        if not self.track_counts:
+            self.lt_w = torch.zeros((self.lcap,), dtype=f32, device=d)
+            self.lt_g = torch.zeros((self.lcap,), dtype=f32, device=d)
+            L.lt_w, L.lt_g, L.soa = self.lt_w.data_ptr(), self.lt_g.data_ptr(), 1
         self._L = L
         self._H = hyper.native()
         self._lib = N.lib()

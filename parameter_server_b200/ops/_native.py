@@ -8,6 +8,7 @@ an error, never a silent fallback.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 
 from ..utils import build as _build
@@ -56,19 +57,25 @@ class LocalScratch(C.Structure):
     _fields_ = [("lt_keys", C.c_void_p), ("lt_val", C.c_void_p),
                 ("lt_mask", C.c_uint64), ("lt_shift", C.c_uint64), ("slot_of", C.c_void_p), ("coef", C.c_void_p), ("xw", C.c_void_p),
                 ("send_cnt", C.c_void_p), ("recv_cnt", C.c_void_p), ("stats", C.c_void_p),
-                ("status", C.c_void_p), ("trace", C.c_void_p)]
+                ("status", C.c_void_p), ("trace", C.c_void_p),
+                ("lt_w", C.c_void_p), ("lt_g", C.c_void_p), ("soa", C.c_uint32), ("pad", C.c_uint32)]
 
 
 def lib() -> C.CDLL:
-    """Load (building first if needed) the kernel library."""
+    """Load (building first if needed) the kernel library.  ``PSB_KERNELS_LIB`` names an alternative
+    build of the same sources (for instance one compiled with other ``-D`` switches)."""
     global _lib
     if _lib is None:
         with _lock:
             if _lib is None:
-                path = _build.kernels_lib_path()
-                if not path.exists():
-                    _build.build_kernels()
-                _lib = C.CDLL(str(path))
+                override = os.environ.get("PSB_KERNELS_LIB")
+                if override:
+                    _lib = C.CDLL(override)
+                else:
+                    path = _build.kernels_lib_path()
+                    if not path.exists():
+                        _build.build_kernels()
+                    _lib = C.CDLL(str(path))
     return _lib
 
 

@@ -24,11 +24,13 @@ def _batches(n, rows=700, log2=13):
                           wstar_std=1.0) for i in range(n)]
 
 
-@pytest.mark.parametrize("impl,rule", [("fused", "count"), ("fused", "sumsq"), ("nccl", "count")])
-def test_ftrl_matches_oracle(impl, rule):
+@pytest.mark.parametrize("impl,rule,counts", [("fused", "count", None), ("fused", "sumsq", None),
+                                              ("fused", "sumsq", True), ("nccl", "count", None)])
+def test_ftrl_matches_oracle(impl, rule, counts):
     from parameter_server_b200.models.ftrl import DeviceMinibatch
 
-    eng, hy = _engine(impl, rule)
+    eng, hy = _engine(impl, rule, track_counts=counts)
+    assert eng.track_counts == (rule == "count" or bool(counts))
     ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2, rule)
     for off, keys, y in _batches(6):
         eng.step(DeviceMinibatch(off, keys, y))
@@ -49,11 +51,12 @@ def test_ftrl_matches_oracle(impl, rule):
     assert eng.penalty(st) == pytest.approx(ref.objv(), rel=1e-3)
 
 
-def test_ftrl_valued_features_and_predict():
+@pytest.mark.parametrize("rule", ["count", "sumsq"])
+def test_ftrl_valued_features_and_predict(rule):
     from parameter_server_b200.models.ftrl import DeviceMinibatch
 
-    eng, hy = _engine()
-    ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2)
+    eng, hy = _engine(rule=rule)
+    ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2, rule)
     g = torch.Generator(device="cuda").manual_seed(3)
     for off, keys, y in _batches(4, rows=300, log2=10):
         vals = torch.rand(keys.numel(), generator=g, device="cuda") + 0.5
