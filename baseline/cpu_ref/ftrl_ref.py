@@ -26,6 +26,45 @@ class Entry:
     z: float = 0.0
 
 
+class CountMinRef:
+    """Count-min sketch with the reference's probe sequence (src/base/countmin.h:33-67): 32-bit
+    hash h of the 64-bit key, probes (h + j·rotr17(h)) mod n, insert adds, query takes the minimum.
+    Counters are uint32 (the reference's uint8 counters wrap at 256)."""
+
+    def __init__(self, n: int, k: int):
+        self.n, self.k = max(int(n), 64), max(int(k), 1)
+        self.table = np.zeros(self.n, dtype=np.uint64)
+
+    @staticmethod
+    def _hash(keys: np.ndarray) -> np.ndarray:
+        m, mask = np.uint64(0xc6a4a793), np.uint64(0xFFFFFFFF)
+        keys = keys.astype(np.uint64)
+        h = np.full(keys.shape, (0xbc9f1d34 ^ ((8 * 0xc6a4a793) & 0xFFFFFFFF)), dtype=np.uint64)
+        for part in (keys & mask, keys >> np.uint64(32)):
+            h = (h + part) & mask
+            h = (h * m) & mask
+            h ^= h >> np.uint64(16)
+        return h
+
+    def _probes(self, keys: np.ndarray):
+        h = self._hash(keys)
+        mask = np.uint64(0xFFFFFFFF)
+        d = ((h >> np.uint64(17)) | (h << np.uint64(15))) & mask
+        for _ in range(self.k):
+            yield (h % np.uint64(self.n)).astype(np.int64)
+            h = (h + d) & mask
+
+    def insert(self, keys: np.ndarray, counts: np.ndarray) -> None:
+        for idx in self._probes(keys):
+            np.add.at(self.table, idx, counts.astype(np.uint64))
+
+    def query(self, keys: np.ndarray) -> np.ndarray:
+        out = np.full(len(keys), np.iinfo(np.uint64).max, dtype=np.uint64)
+        for idx in self._probes(keys):
+            out = np.minimum(out, self.table[idx])
+        return out
+
+
 @dataclass
 class FTRLRef:
     alpha: float = 0.1
@@ -37,6 +76,33 @@ class FTRLRef:
     norm1: float = 0.0
     norm2: float = 0.0
     nnz: int = 0
+    # tail-feature filter: every server s owns keys in [seps[s], seps[s+1]) and a sketch of width
+    # countmin_n / num_servers; a pushed key is applied only once its estimate exceeds tail_freq
+    tail_freq: int = 0
+    countmin_n: int = 1 << 20
+    countmin_k: int = 2
+    seps: Optional[Sequence[int]] = None
+    _sketch: Optional[list] = None
+
+    def _admitted(self, keys: np.ndarray, pos: np.ndarray, neg: np.ndarray) -> np.ndarray:
+        """Insert one worker's row counts server by server, then query: mask of keys that pass the filter."""
+        if self.tail_freq <= 0:
+            return np.ones(len(keys), dtype=bool)
+        seps = list(self.seps) if self.seps is not None else [0, 1 << 64]
+        S = len(seps) - 1
+        if self._sketch is None:
+            self._sketch = [CountMinRef(int(self.countmin_n) // S, self.countmin_k) for _ in range(S)]
+        keys = np.asarray(keys, dtype=np.uint64)
+        ok = np.zeros(len(keys), dtype=bool)
+        for s in range(S):
+            hi = seps[s + 1]
+            sel = (keys >= np.uint64(seps[s])) & ((keys < np.uint64(hi)) if hi < (1 << 64) else np.ones(len(keys), bool))
+            if not sel.any():
+                continue
+            cnt = (pos[sel] + neg[sel]).astype(np.uint64)
+            self._sketch[s].insert(keys[sel], cnt)
+            ok[sel] = self._sketch[s].query(keys[sel]) > np.uint64(self.tail_freq)
+        return ok
 
     @staticmethod
     def _sqrt_n(pos: float, neg: float) -> float:
@@ -101,7 +167,8 @@ class FTRLRef:
             pushes.append((uk, pos, neg, g))
             loss += l
         for uk, pos, neg, g in pushes:
-            self.set_value(uk, pos, neg, g)
+            ok = self._admitted(uk, pos, neg)
+            self.set_value(uk[ok], pos[ok], neg[ok], g[ok])
         return loss
 
     def nonzero(self):

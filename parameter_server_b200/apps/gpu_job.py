@@ -127,7 +127,8 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
                           delta_max=d.delta_max_value, kkt_ratio=d.kkt_filter_threshold_ratio, max_pass=s.max_pass_of_data,
                           epsilon=s.epsilon, feature_block_ratio=s.feature_block_ratio,
                           random_block_order=s.random_feature_block_order, max_block_delay=s.max_block_delay,
-                          seed=int(flags.seed))
+                          seed=int(flags.seed), tail_feature_freq=int(s.tail_feature_freq),
+                          countmin_k=int(s.countmin_k), countmin_n_ratio=float(s.countmin_n_ratio))
         if lm.has("darling"):
             sol = DarlinSolver(group, dc, timeout_s=float(flags.timeout_s), impl=flags.impl if flags.impl in ("fused", "nccl") else "fused")
             from ..utils.trace import ChromeTrace, MetricsLog
@@ -177,7 +178,9 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
     H = host()
     s = lm.solver
     lam = list(lm.penalty.get("lambda")) + [0.0, 0.0]
-    hyper = FTRLHyper(alpha=lm.learning_rate.alpha, beta=lm.learning_rate.beta, lambda1=lam[0], lambda2=lam[1])
+    hyper = FTRLHyper(alpha=lm.learning_rate.alpha, beta=lm.learning_rate.beta, lambda1=lam[0], lambda2=lam[1],
+                      tail_feature_freq=int(s.tail_feature_freq), countmin_n=int(s.countmin_n),
+                      countmin_k=int(s.countmin_k))
     files = _my_files(lm.training_data.file, group, int(flags.load_limit))
     fmt = getattr(H.TextFormat, lm.training_data.text if lm.training_data.has("text") else "LIBSVM")
     reader = H.StreamReader()

@@ -55,6 +55,17 @@ struct FtrlHyper {
   float alpha, beta, l1, l2;
   int rule;  // 0 = count-based ‖g‖ estimate (reference), 1 = Σ g² (McMahan et al.)
   int pad;
+  // Tail-feature filter (src/linear_method/ftrl.cc:99-106, src/parameter/frequency_filter.h:28-43):
+  // the owner adds every pushed key's row count to its count-min sketch and updates (and creates)
+  // a key only once the estimate exceeds tail_freq, so rare keys never enter the model.  The
+  // reference filters on the pull path; here the counts travel with the push anyway, the sketch
+  // is local to the owner, and a key without a table entry pulls as 0 — the same model, no extra
+  // message.  Off when tail_freq == 0 or cm == nullptr.
+  uint32_t* cm;
+  uint32_t cm_width;
+  int cm_k;
+  uint32_t tail_freq;
+  uint32_t pad2;
 };
 
 struct FtrlPeers {
@@ -473,6 +484,19 @@ __device__ __forceinline__ void ftrl_update(ShardState& e, float g, uint32_t dpo
   dnnz += (w != 0.f && w_old == 0.f) - (w == 0.f && w_old != 0.f);
 }
 
+__device__ __forceinline__ bool tail_filter_on(const FtrlHyper& h) { return h.tail_freq != 0u && h.cm != nullptr; }
+
+// first half of the tail-feature filter: add one sender's row counts to the owner's sketch
+__device__ __forceinline__ void phase_sketch_insert(const uint64_t* rk, const uint64_t* rc, uint32_t n,
+                                                    const FtrlHyper& h, size_t gtid, size_t gsz) {
+  for (size_t i = gtid; i < n; i += gsz) {
+    const uint64_t key = __ldcg(rk + i);
+    if (key == kEmptyKey) continue;
+    const uint64_t c = __ldcg(rc + i);
+    cm_insert(h.cm, h.cm_width, h.cm_k, key, (uint32_t)(c >> 32) + (uint32_t)c);
+  }
+}
+
 template <bool kCounts>
 __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
                                             const uint64_t* rk, const float* rg, const uint64_t* rc,
@@ -480,9 +504,11 @@ __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint3
                                             size_t gtid, size_t gsz) {
   float dn1 = 0.f, dn2 = 0.f;
   int dnnz = 0, dins = 0;
+  const bool filter = kCounts && tail_filter_on(h);
   for (size_t i = gtid; i < n; i += gsz) {
     const uint64_t key = __ldcg(rk + i);
     if (key == kEmptyKey) continue;
+    if (filter && cm_query(h.cm, h.cm_width, h.cm_k, key, 0xFFFFFFFFu) <= h.tail_freq) continue;
     const float g = __ldcg(rg + i);
     const uint64_t c = kCounts ? __ldcg(rc + i) : 0ull;
     uint64_t slot = shard_hash(key, shift) & mask;
@@ -591,6 +617,10 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
   for (int s = 0; s < world; ++s) {
     const uint32_t n = __ldcg(L.recv_cnt + s);
     const size_t off = (size_t)s * P.in_cap;
+    if (kCounts && tail_filter_on(H)) {
+      phase_sketch_insert(P.in_keys[P.rank] + off, P.in_cnt[P.rank] + off, n, H, gtid, gsz);
+      grid.sync();
+    }
     phase_apply<kCounts>(P.tab[P.rank], P.tab_mask, P.tab_shift, P.max_probe,
                          P.in_keys[P.rank] + off, P.in_g[P.rank] + off, P.in_cnt[P.rank] + off, n, H, L.stats,
                          L.status, gtid, gsz);
@@ -686,6 +716,9 @@ __global__ void k_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_p
   phase_apply<true>(tab, mask, shift, max_probe, rk, rg, rc, n, h, stats, status,
                     (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
 }
+__global__ void k_sketch_insert(const uint64_t* rk, const uint64_t* rc, uint32_t n, FtrlHyper h) {
+  phase_sketch_insert(rk, rc, n, h, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+}
 __global__ void k_clear_local(LocalScratch L) {
   for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += (size_t)gridDim.x * blockDim.x)
     L.lt_keys[s] = kEmptyKey;
@@ -754,7 +787,8 @@ int psb_ftrl_push_update(const FtrlPeers* P, const Minibatch* M, const LocalScra
                          uint32_t epoch, cudaStream_t stream) {
   const bool soa = L->soa != 0;
   // the count-based rule needs the pos/neg counts that the split layout does not carry
-  if (soa && (H->rule == 0 || L->lt_w == nullptr || L->lt_g == nullptr)) return (int)cudaErrorInvalidValue;
+  if (soa && (H->rule == 0 || (H->tail_freq != 0u && H->cm != nullptr) || L->lt_w == nullptr || L->lt_g == nullptr))
+    return (int)cudaErrorInvalidValue;
   void* kernel = soa ? (void*)ftrl_push_update_kernel<false> : (void*)ftrl_push_update_kernel<true>;
   const int grid = soa ? coop_grid(ftrl_push_update_kernel<false>, g_coop_blocks_push[0])
                        : coop_grid(ftrl_push_update_kernel<true>, g_coop_blocks_push[1]);
@@ -802,6 +836,7 @@ int psb_ftrl_pack_push(const uint32_t* slots, uint32_t n, const LocalScratch* L,
 int psb_ftrl_apply(void* tab, uint64_t mask, uint32_t shift, int max_probe, const uint64_t* rk, const float* rg,
                    const uint64_t* rc, uint32_t n, const FtrlHyper* h, double* stats, uint32_t* status,
                    cudaStream_t s) {
+  if (h->tail_freq != 0u && h->cm != nullptr) k_sketch_insert<<<flat_grid(n), 256, 0, s>>>(rk, rc, n, *h);
   k_apply<<<flat_grid(n), 256, 0, s>>>((ShardSlot*)tab, mask, shift, max_probe, rk, rg, rc, n, *h, stats, status);
   return (int)cudaGetLastError();
 }

@@ -164,6 +164,27 @@ __device__ __forceinline__ uint64_t table_find_or_insert(uint64_t* keys, uint64_
   return ~0ull;
 }
 
+// ---- count-min sketch probes (src/base/countmin.h:33-67) ----
+// 32-bit hash of a 64-bit key; probe j of k looks at (h + j·rotr17(h)) mod width.
+__device__ __forceinline__ uint32_t cm_hash(uint64_t key) {
+  const uint32_t seed = 0xbc9f1d34u, m = 0xc6a4a793u;
+  uint32_t h = seed ^ (8u * m);
+  h += (uint32_t)key; h *= m; h ^= (h >> 16);
+  h += (uint32_t)(key >> 32); h *= m; h ^= (h >> 16);
+  return h;
+}
+__device__ __forceinline__ void cm_insert(uint32_t* table, uint32_t width, int k, uint64_t key, uint32_t c) {
+  uint32_t h = cm_hash(key);
+  const uint32_t d = (h >> 17) | (h << 15);
+  for (int j = 0; j < k; ++j) { atomicAdd(&table[h % width], c); h += d; }
+}
+__device__ __forceinline__ uint32_t cm_query(const uint32_t* table, uint32_t width, int k, uint64_t key, uint32_t wrap_mask) {
+  uint32_t h = cm_hash(key), r = 0xFFFFFFFFu;
+  const uint32_t d = (h >> 17) | (h << 15);
+  for (int j = 0; j < k; ++j) { r = min(r, __ldcg(table + h % width) & wrap_mask); h += d; }
+  return r;
+}
+
 // numerically safe log(1+exp(x))
 __device__ __forceinline__ float log1pexp(float x) {
   return x > 0.f ? x + log1pf(__expf(-x)) : log1pf(__expf(x));

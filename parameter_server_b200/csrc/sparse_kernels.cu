@@ -198,30 +198,15 @@ __global__ void k_owner_of_keys(const uint64_t* __restrict__ keys, size_t n, Key
 }
 
 // ---------------------------------------------------------------- count-min sketch (uint32 saturating or uint8-wrapping counters)
-__device__ __forceinline__ uint32_t cm_hash(uint64_t key) {
-  const uint32_t seed = 0xbc9f1d34u, m = 0xc6a4a793u;
-  uint32_t h = seed ^ (8u * m);
-  h += (uint32_t)key; h *= m; h ^= (h >> 16);
-  h += (uint32_t)(key >> 32); h *= m; h ^= (h >> 16);
-  return h;
-}
 __global__ void k_countmin_insert(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ counts, size_t n, uint32_t* __restrict__ table,
                                   uint32_t width, int k) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    uint32_t h = cm_hash(keys[i]);
-    const uint32_t d = (h >> 17) | (h << 15);
-    const uint32_t c = counts ? counts[i] : 1u;
-    for (int j = 0; j < k; ++j) { atomicAdd(&table[h % width], c); h += d; }
-  }
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    cm_insert(table, width, k, keys[i], counts ? counts[i] : 1u);
 }
 __global__ void k_countmin_query(const uint64_t* __restrict__ keys, size_t n, const uint32_t* __restrict__ table, uint32_t width, int k,
                                  uint32_t wrap_mask, uint32_t* __restrict__ out) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    uint32_t h = cm_hash(keys[i]), r = 0xFFFFFFFFu;
-    const uint32_t d = (h >> 17) | (h << 15);
-    for (int j = 0; j < k; ++j) { r = min(r, table[h % width] & wrap_mask); h += d; }
-    out[i] = r;
-  }
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = cm_query(table, width, k, keys[i], wrap_mask);
 }
 
 // ---------------------------------------------------------------- generic CSR products and init

@@ -51,6 +51,11 @@ class DarlinConfig:
     seed: int = 0
     reset_nan_on_kkt_reset: bool = True
     shard_by_data_range: bool = True  # servers split [min_key, max_key] instead of the whole uint64 space
+    # tail-feature filter of BatchSolver::preprocessData (src/linear_method/batch_solver.cc:227-290): features
+    # whose count-min estimate of occurrences is <= tail_feature_freq are dropped before training; 0 = off
+    tail_feature_freq: int = 0
+    countmin_k: int = 2
+    countmin_n_ratio: float = 2.0
 
 
 @dataclass
@@ -97,6 +102,63 @@ class DarlinSolver:
         self.kernel_launches = 0
 
     # ------------------------------------------------------------------ preprocessing
+    def _drop_tail_features(self, offsets: torch.Tensor, keys: torch.Tensor, vals: Optional[torch.Tensor]):
+        """Tail-feature filter (src/linear_method/batch_solver.cc:250-290, src/parameter/shared_parameter.h:114-133).
+
+        Every worker sends its unique keys with their occurrence counts to the servers (the whole key space
+        split evenly); a server adds them to its count-min sketch worker by worker in rank order, then answers
+        which keys have an estimate above ``tail_feature_freq``; the worker drops all other columns.  The
+        sketch of a server is ``max(W · n · countmin_n_ratio / log(W+1), 64)`` wide, n = keys in the first
+        non-empty message it got.  Returns the filtered CSR (offsets, keys, vals).  Collective.
+        """
+        import torch.distributed as dist
+
+        from ..ops import sparse
+
+        g, dev, W, cfg = self.group, self.dev, self.group.world, self.cfg
+        keys = keys.contiguous()
+        lkeys, cnt = sparse.count_unique(keys)
+        P = lkeys.numel()
+        i64 = torch.int64
+        if W > 1:
+            seps = Range.all().separators(W)
+            sep_s = torch.tensor([s + _SIGN for s in seps[1:-1]], dtype=i64, device=dev)
+            bounds = [0] + torch.searchsorted(_ukey(lkeys), sep_s).tolist() + [P]
+            send = [bounds[i + 1] - bounds[i] for i in range(W)]
+            recv_t = torch.empty(W, dtype=i64, device=dev)
+            dist.all_to_all_single(recv_t, torch.tensor(send, dtype=i64, device=dev), group=g.group)
+            recv = recv_t.tolist()
+            rk = torch.empty(sum(recv), dtype=i64, device=dev)
+            rc = torch.empty(sum(recv), dtype=torch.int32, device=dev)
+            dist.all_to_all_single(rk, lkeys, recv, send, group=g.group)
+            dist.all_to_all_single(rc, cnt, recv, send, group=g.group)
+        else:
+            send = recv = [P]
+            rk, rc = lkeys, cnt
+        n_first = next((n for n in recv if n > 0), 0)
+        width = max(int(W * n_first * cfg.countmin_n_ratio / math.log(W + 1)), 64)
+        sketch = sparse.CountMinDevice(width, cfg.countmin_k, dev)
+        at = 0
+        for n in recv:
+            if n:
+                sketch.insert(rk[at:at + n], rc[at:at + n])
+            at += n
+        est = sketch.query(rk) if rk.numel() else torch.zeros(0, dtype=torch.int32, device=dev)
+        passed = (est > cfg.tail_feature_freq).to(torch.uint8)
+        if W > 1:
+            keep = torch.empty(P, dtype=torch.uint8, device=dev)
+            dist.all_to_all_single(keep, passed, send, recv, group=g.group)
+        else:
+            keep = passed
+        inv = sparse.remap(keys, lkeys)
+        sel = keep[inv.long()].bool()
+        rows = offsets.numel() - 1
+        row_of = torch.repeat_interleave(torch.arange(rows, device=dev), offsets[1:] - offsets[:-1])
+        new_off = torch.zeros(rows + 1, dtype=i64, device=dev)
+        new_off[1:] = torch.cumsum(torch.bincount(row_of[sel], minlength=rows), 0)
+        self.tail_filter_stats = {"features": P, "dropped": P - int(keep.sum().item()), "sketch_width": width}
+        return new_off, keys[sel].contiguous(), None if vals is None else vals[sel].contiguous()
+
     def preprocess(self, offsets: torch.Tensor, keys: torch.Tensor, vals: Optional[torch.Tensor], y: torch.Tensor):
         """Localise this rank's CSR rows shard, exchange key sets with the servers, build the CSC blocks.
 
@@ -105,10 +167,12 @@ class DarlinSolver:
         import torch.distributed as dist
 
         g, dev, W = self.group, self.dev, self.group.world
-        rows, nnz = y.numel(), keys.numel()
-        # unique local keys in unsigned order + column id of every non-zero  (Localizer::countUniqIndex/remapIndex)
         from ..ops import sparse
 
+        if self.cfg.tail_feature_freq > 0:
+            offsets, keys, vals = self._drop_tail_features(offsets, keys, vals)
+        rows, nnz = y.numel(), keys.numel()
+        # unique local keys in unsigned order + column id of every non-zero  (Localizer::countUniqIndex/remapIndex)
         lkeys, _ = sparse.count_unique(keys.contiguous())          # radix sort + run-length unique (unsigned order)
         uk = _ukey(lkeys)                                          # same keys as int64 values in that order
         P = lkeys.numel()

@@ -33,9 +33,15 @@ class FTRLHyper:
     lambda1: float = 1.0
     lambda2: float = 0.1
     rule: str = "count"  # "count": reference's sqrt(pos*neg/(pos+neg)); "sumsq": Σg²
+    # tail-feature filter (LearnerConfig tail_feature_freq, countmin_n, countmin_k): a key is updated only
+    # once its count-min estimate of rows seen exceeds tail_feature_freq; 0 = off
+    tail_feature_freq: int = 0
+    countmin_n: int = 1 << 20   # sketch width summed over all servers (src/linear_method/ftrl.cc:14-16)
+    countmin_k: int = 2
 
     def native(self) -> N.FtrlHyper:
-        return N.FtrlHyper(self.alpha, self.beta, self.lambda1, self.lambda2, 0 if self.rule == "count" else 1, 0)
+        return N.FtrlHyper(self.alpha, self.beta, self.lambda1, self.lambda2, 0 if self.rule == "count" else 1, 0,
+                           None, 0, 0, 0, 0)
 
 
 @dataclass
@@ -78,10 +84,11 @@ class FTRLEngine:
         12-byte push records.  Default: on for ``rule="count"``, off for ``rule="sumsq"``."""
         if group.world > N.MAX_RANKS:
             raise ValueError(f"at most {N.MAX_RANKS} ranks per box")
+        needs_counts = hyper.rule == "count" or hyper.tail_feature_freq > 0
         if track_counts is None:
-            track_counts = hyper.rule == "count" or impl != "fused"
-        if hyper.rule == "count" and not track_counts:
-            raise ValueError('rule="count" needs track_counts')
+            track_counts = needs_counts or impl != "fused"
+        if needs_counts and not track_counts:
+            raise ValueError('rule="count" and the tail-feature filter need track_counts')
         self.track_counts = bool(track_counts) or impl != "fused"
         self.group, self.hyper, self.impl = group, hyper, impl
         self.dev = group.device
@@ -154,6 +161,12 @@ class FTRLEngine:
             L.lt_w, L.lt_g, L.soa = self.lt_w.data_ptr(), self.lt_g.data_ptr(), 1
         self._L = L
         self._H = hyper.native()
+        if hyper.tail_feature_freq > 0:
+            # this server's share of the sketch (FTRL::init sizes it countmin_n / num_servers)
+            self.cm_width = max(int(hyper.countmin_n) // W, 64)
+            self.cm = torch.zeros((self.cm_width,), dtype=torch.int32, device=d)
+            self._H.cm, self._H.cm_width = self.cm.data_ptr(), self.cm_width
+            self._H.cm_k, self._H.tail_freq = max(int(hyper.countmin_k), 1), int(hyper.tail_feature_freq)
         self._lib = N.lib()
         self.kernel_launches = 0
         if impl == "nccl":

@@ -35,7 +35,9 @@ class KeySeps(C.Structure):
 
 class FtrlHyper(C.Structure):
     _fields_ = [("alpha", C.c_float), ("beta", C.c_float), ("l1", C.c_float), ("l2", C.c_float),
-                ("rule", C.c_int), ("pad", C.c_int)]
+                ("rule", C.c_int), ("pad", C.c_int),
+                ("cm", C.c_void_p), ("cm_width", C.c_uint32), ("cm_k", C.c_int), ("tail_freq", C.c_uint32),
+                ("pad2", C.c_uint32)]
 
 
 _P8 = C.c_void_p * MAX_RANKS

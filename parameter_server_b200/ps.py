@@ -3,7 +3,8 @@
   python -m parameter_server_b200.ps -num_servers 2 -num_workers 2 -my_rank 0 \
       -scheduler "role:SCHEDULER,hostname:'127.0.0.1',port:2060,id:'H'" -app config/rcv1_l1lr.conf
 
-CPU nodes talk over TCP (src/ps.cc:5-16, src/system/postoffice.cc:34-84).  With ``-gpus N`` (or under
+CPU nodes talk over TCP (src/ps.cc:5-16, src/system/postoffice.cc:34-84); under ``mpirun -np 1+S+W`` the rank
+is taken from the launcher's environment like the reference's MPI scripts do.  With ``-gpus N`` (or under
 ``torch.distributed.run``) the job runs on the GPU engines instead: every rank is worker + server on
 one B200 and the same ``.conf`` selects DARLIN or FTRL.
 """
@@ -32,7 +33,13 @@ def main(argv=None) -> int:
                 pass
         return 0
     if flags.my_rank < 0:
-        print("-my_rank is required", file=sys.stderr)
+        # under mpirun / srun the rank comes from the launcher's environment (script/mpi_node.sh:8-17)
+        for var in ("PMI_RANK", "OMPI_COMM_WORLD_RANK", "SLURM_PROCID"):
+            if os.environ.get(var, "").isdigit():
+                flags.my_rank = int(os.environ[var])
+                break
+    if flags.my_rank < 0:
+        print("-my_rank is required (or PMI_RANK / OMPI_COMM_WORLD_RANK / SLURM_PROCID in the environment)", file=sys.stderr)
         return 2
     from .apps.job import run_node
 

@@ -118,8 +118,9 @@ def save_ftrl(eng, directory: str, step: int) -> str:
     os.makedirs(directory, exist_ok=True)
     path = _path(directory, "ftrl", eng.group.rank, step)
     tmp = path + ".tmp"
+    sketch = eng.cm.cpu() if getattr(eng, "cm", None) is not None else None
     torch.save({"step": step, "cap": eng.cap, "seps": eng.seps, "hyper": eng.hyper.__dict__, "table": eng.tab.local.cpu(),
-                "stats": eng.stats.cpu()}, tmp)
+                "stats": eng.stats.cpu(), "sketch": sketch}, tmp)
     os.replace(tmp, path)
     return path
 
@@ -135,5 +136,9 @@ def load_ftrl(eng, directory: str, step: int = -1) -> int:
         raise RuntimeError("checkpoint was written with a different table capacity or key-range partition")
     eng.tab.local.copy_(st["table"].to(eng.dev))
     eng.stats.copy_(st["stats"].to(eng.dev))
+    if st.get("sketch") is not None and getattr(eng, "cm", None) is not None:
+        if st["sketch"].numel() != eng.cm.numel():
+            raise RuntimeError("checkpoint was written with a different count-min width")
+        eng.cm.copy_(st["sketch"].to(eng.dev))
     eng.group.barrier()
     return st["step"]

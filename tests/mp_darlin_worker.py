@@ -25,14 +25,46 @@ def shard(off, keys, vals, y, r, W):
     return (off[r0:r1 + 1] - p0).contiguous(), keys[p0:p1].contiguous(), None if vals is None else vals[p0:p1].contiguous(), y[r0:r1].contiguous()
 
 
+def filter_tail(shards, W, freq, k=2, ratio=2.0):
+    """NumPy restatement of the tail-feature filter: W servers split the key space evenly; each adds the
+    workers' (key, count) lists to its count-min sketch in rank order, then keys with estimate <= freq go."""
+    import math
+
+    from baseline.cpu_ref.ftrl_ref import CountMinRef
+    from parameter_server_b200.utils.range import Range
+
+    seps = Range.all().separators(W)
+    uniq = [np.unique(sh[1], return_inverse=True, return_counts=True) for sh in shards]
+    keep = [np.zeros(len(u[0]), dtype=bool) for u in uniq]
+    for s in range(W):
+        lo, hi = np.uint64(seps[s]), np.uint64(min(seps[s + 1], (1 << 64) - 1))
+        parts = [(u[0] >= lo) & (u[0] < hi) for u in uniq]
+        n_first = next((int(m.sum()) for m in parts if m.any()), 0)
+        cm = CountMinRef(max(int(W * n_first * ratio / math.log(W + 1)), 64), k)
+        for u, m in zip(uniq, parts):
+            if m.any():
+                cm.insert(u[0][m], u[2][m])
+        for u, m, kp in zip(uniq, parts, keep):
+            if m.any():
+                kp[m] = cm.query(u[0][m]) > freq
+    out = []
+    for (o, kk, vv, yy), u, kp in zip(shards, uniq, keep):
+        sel = kp[u[1]]
+        row_of = np.repeat(np.arange(len(yy)), np.diff(o))
+        no = np.concatenate([[0], np.cumsum(np.bincount(row_of[sel], minlength=len(yy)))]).astype(np.int64)
+        out.append((no, kk[sel], vv[sel], yy))
+    return out, sum(int((~kp).sum()) for kp in keep)
+
+
 def main():
     impl = sys.argv[1] if len(sys.argv) > 1 else "fused"
+    tail = int(sys.argv[2]) if len(sys.argv) > 2 else 0
     group = PeerGroup.from_env()
     rank, W, dev = group.rank, group.world, group.device
     off, idx, vals, y, _ = zipf_sparse_matrix(2400, 3000, 14, seed=5, device=dev, zipf_s=0.8)
     keys = idx * 104729 + 11
     kw = dict(lambda1=0.3, max_pass=5, feature_block_ratio=1.0, seed=2)
-    sol = DarlinSolver(group, DarlinConfig(**kw), impl=impl)
+    sol = DarlinSolver(group, DarlinConfig(tail_feature_freq=tail, **kw), impl=impl)
     sol.preprocess(*shard(off, keys, vals, y, rank, W))
     prog = sol.run()
     sol.check_status()
@@ -45,6 +77,10 @@ def main():
         for r in range(W):
             o, kk, vv, yy = shard(off, keys, vals, y, r, W)
             shards.append((o.cpu().numpy(), kk.cpu().numpy().view(np.uint64), vv.cpu().numpy(), yy.cpu().numpy()))
+        dropped = 0
+        if tail > 0:
+            shards, dropped = filter_tail(shards, W, tail)
+            ok &= dropped > 0
         ref = DarlinRef(shards, None, RefConfig(**kw))
         rprog = ref.run()
         ok &= len(prog) == len(rprog)
@@ -58,7 +94,7 @@ def main():
         ok &= len(common) >= 0.95 * max(len(allk), len(rk))
         wd, rd = dict(zip(allk.tolist(), allw.tolist())), dict(zip(rk.tolist(), rw.tolist()))
         ok &= max(abs(wd[c] - rd[c]) for c in common.tolist()) < 5e-2
-        print(f"impl={impl} world={W} passes={len(prog)} objv={prog[-1].objv:.4f} ref={rprog[-1].objv:.4f} "
+        print(f"impl={impl} tail={tail} dropped={dropped} world={W} passes={len(prog)} objv={prog[-1].objv:.4f} ref={rprog[-1].objv:.4f} "
               f"shard_sizes={[len(g[0]) for g in gathered]} match={bool(ok)}", flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, 0, group=group.group)

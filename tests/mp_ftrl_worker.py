@@ -22,10 +22,13 @@ from parameter_server_b200.parallel.peer import PeerGroup  # noqa: E402
 
 def main():
     impl = sys.argv[1] if len(sys.argv) > 1 else "fused"
+    rule = sys.argv[2] if len(sys.argv) > 2 else "count"
+    tail = int(sys.argv[3]) if len(sys.argv) > 3 else 0
     steps = 5
     group = PeerGroup.from_env()
     rank, world, dev = group.rank, group.world, group.device
-    hy = FTRLHyper(alpha=0.02, beta=1.0, lambda1=0.05, lambda2=0.1)
+    hy = FTRLHyper(alpha=0.02, beta=1.0, lambda1=0.05, lambda2=0.1, rule=rule, tail_feature_freq=tail,
+                   countmin_n=1 << 14, countmin_k=2)
     eng = FTRLEngine(group, hy, table_capacity=1 << 16, max_rows=2048, max_nnz=1 << 18, local_capacity=1 << 16,
                      timeout_s=2.0, impl=impl)
 
@@ -51,7 +54,8 @@ def main():
     dist.all_gather_object(gathered, (k, w, losses), group=group.group)
     ok = True
     if rank == 0:
-        ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2)
+        ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2, rule, tail_freq=tail, countmin_n=hy.countmin_n,
+                      countmin_k=hy.countmin_k, seps=eng.seps)
         ref_losses = []
         for i in range(steps):
             mbs = []
@@ -73,7 +77,8 @@ def main():
                                                  y.cpu().numpy().astype(np.float64))
         ok &= np.allclose(xw, rxw, rtol=3e-3, atol=3e-4)
         sizes = [len(g[0]) for g in gathered]
-        print(f"impl={impl} world={world} shards={sizes} model_nnz={len(rk)} match={ok}", flush=True)
+        print(f"impl={impl} rule={rule} tail={tail} world={world} shards={sizes} model_nnz={len(rk)} "
+              f"entries={len(ref.model)} match={ok}", flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, 0, group=group.group)
     dist.destroy_process_group()

@@ -69,6 +69,37 @@ def test_bounded_delay_groups_match_oracle(tau):
     sol.check_status()
 
 
+def test_tail_feature_filter_drops_rare_columns():
+    """Columns whose count-min estimate is <= tail_feature_freq are removed before training; the rest of the
+    run equals the oracle on the data filtered by a NumPy restatement of the same sketch."""
+    import math
+
+    from baseline.cpu_ref.ftrl_ref import CountMinRef
+    from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver
+    from parameter_server_b200.parallel.peer import PeerGroup
+
+    off, keys, vals, y = _problem(False, rows=1200, cols=4096, nnz=12)
+    freq = 2
+    kw = dict(lambda1=0.3, max_pass=3, feature_block_ratio=1.0, seed=3)
+    sol = DarlinSolver(PeerGroup.single(torch.device("cuda", 0)), DarlinConfig(tail_feature_freq=freq, **kw))
+    sol.preprocess(off, keys, vals, y)
+    hk = keys.cpu().numpy().view(np.uint64)
+    uk, inv, cnt = np.unique(hk, return_inverse=True, return_counts=True)
+    cm = CountMinRef(max(int(len(uk) * 2.0 / math.log(2)), 64), 2)
+    cm.insert(uk, cnt)
+    keep = cm.query(uk) > freq
+    assert sol.tail_filter_stats["dropped"] == int((~keep).sum()) and 0 < int((~keep).sum()) < len(uk)
+    assert np.array_equal(sol.lkeys.cpu().numpy().view(np.uint64), uk[keep])
+    sel = keep[inv]
+    ho = off.cpu().numpy()
+    row_of = np.repeat(np.arange(len(ho) - 1), np.diff(ho))
+    foff = np.concatenate([[0], np.cumsum(np.bincount(row_of[sel], minlength=len(ho) - 1))]).astype(np.int64)
+    ref = DarlinRef([(foff, hk[sel], vals.cpu().numpy()[sel], y.cpu().numpy())], None, RefConfig(**kw))
+    for p, r in zip(sol.run(), ref.run()):
+        assert p.objv == pytest.approx(r.objv, rel=2e-3)
+    sol.check_status()
+
+
 def test_darlin_model_dump(tmp_path):
     from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver
     from parameter_server_b200.parallel.peer import PeerGroup

@@ -9,15 +9,22 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _launch(nproc, impl, port):
+def _launch(nproc, impl, port, tail=0):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_darlin_worker.py"), impl]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_darlin_worker.py"), impl,
+           str(tail)]
     return subprocess.run(cmd, capture_output=True, text=True, timeout=300)
 
 
 @pytest.mark.parametrize("impl", ["fused", "nccl"])
 def test_two_gpus_match_oracle(impl):
     r = _launch(2, impl, 29551 if impl == "fused" else 29552)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "match=True" in r.stdout
+
+
+def test_two_gpus_tail_filter_matches_oracle():
+    r = _launch(2, "fused", 29554, tail=2)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "match=True" in r.stdout
 

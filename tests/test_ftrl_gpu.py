@@ -78,6 +78,32 @@ def test_ftrl_valued_features_and_predict(rule):
     eng.check_status()
 
 
+@pytest.mark.parametrize("impl", ["fused", "nccl"])
+def test_tail_feature_filter_matches_oracle(impl):
+    """Keys enter the model only once their count-min estimate exceeds tail_feature_freq."""
+    from parameter_server_b200.models.ftrl import DeviceMinibatch, FTRLEngine, FTRLHyper
+    from parameter_server_b200.parallel.peer import PeerGroup
+
+    hy = FTRLHyper(alpha=0.02, beta=1.0, lambda1=0.05, lambda2=0.1, tail_feature_freq=3, countmin_n=1 << 15, countmin_k=2)
+    eng = FTRLEngine(PeerGroup.single(torch.device("cuda", 0)), hy, impl=impl, table_capacity=1 << 16, max_rows=4096,
+                     max_nnz=1 << 19, local_capacity=1 << 16)
+    ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2, tail_freq=3, countmin_n=hy.countmin_n, countmin_k=2)
+    seen = set()
+    for off, keys, y in _batches(4, rows=300, log2=14):
+        eng.step(DeviceMinibatch(off, keys, y))
+        eng.check_status()
+        hk = keys.cpu().numpy().view(np.uint64)
+        seen.update(hk.tolist())
+        ref.step([(off.cpu().numpy(), hk, y.cpu().numpy().astype(np.float64))])
+    st = eng.read_stats(reset=False)
+    assert st["table_entries"] == len(ref.model)
+    assert 50 < len(ref.model) < 0.8 * len(seen)      # the filter kept a real share of the keys out
+    k, w = eng.dump_model()
+    rk, rw = ref.nonzero()
+    assert np.array_equal(k, rk)
+    np.testing.assert_allclose(w, rw, rtol=2e-3, atol=2e-5)
+
+
 def test_ftrl_reports_local_table_overflow():
     from parameter_server_b200.models.ftrl import DeviceMinibatch
 
