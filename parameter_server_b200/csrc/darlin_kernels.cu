@@ -11,8 +11,11 @@
 //   B  server  on arrival of all workers' CTAs: KKT filter, proximal-Newton step inside the
 //              trust region δ, δ update, accumulators cleared
 //      ── every CTA adds 1 to each worker's "updated" counter ──
-//   C  worker  pull: one peer load of w_new per local column of the block, Δw, δ, active
-//              set; then m_i += y_i·x_ij·Δw_j over the block's non-zeros
+//   C  worker  m_i += y_i·x_ij·(w_new_j − w_j) over the block's non-zeros, w_new_j loaded from the
+//              owner (peer load); one in-GPU barrier; the worker's own copy of w, δ and the
+//              active set of these columns is brought up to date one phase later, next to the
+//              gradients of the following block (other columns), so a block costs three
+//              synchronisation points, not four
 //
 // Arithmetic follows Darling::computeGradients / updateWeight / updateDual
 // (src/linear_method/darling.cc:306-356, 437-477, 358-435).  Instead of
@@ -233,6 +236,26 @@ __device__ __forceinline__ void darlin_update_margin(const DarlinWorker& Wk, int
   }
 }
 
+// ---- fused phase C of the persistent kernel: every non-zero fetches its column's new weight from the
+// owner and the column's old weight from the worker and updates the margin with the difference.  The
+// worker-side column state (w, δ, active) is NOT written here — other CTAs are still reading it — but
+// one phase later by darlin_pull_commit, which saves the barrier between "pull" and "margin update".
+__device__ __forceinline__ void darlin_pull_margin(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
+                                                   int64_t lc1, size_t gtid, size_t gsz) {
+  const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
+  for (int64_t e = p0 + (int64_t)gtid; e < p1; e += (int64_t)gsz) {
+    const int64_t j = Wk.col_of ? (int64_t)Wk.col_of[e] : find_col(Wk.col_ptr, lc0, lc1, e);
+    if (!Wk.active[j]) continue;
+    const float wn = ld_relaxed_sys_f32(P.w[Wk.gowner[j]] + Wk.gslot[j]);
+    const float d = wn - Wk.w[j];
+    if (wn == wn && d != 0.f) {
+      const uint32_t i = Wk.row_idx[e];
+      const float v = Wk.vals ? Wk.vals[e] : 1.f;
+      atomicAdd(&Wk.ym[i].y, Wk.ym[i].x * v * d);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(512)
 darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q, DarlinHyper H) {
   __shared__ bool s_ok;
@@ -256,7 +279,12 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
     const int ge = min(b + group, Q.nblk);
     ++seq;
 
-    // A: gradient + push, then announce arrival at every owner
+    // A: gradient + push, then announce arrival at every owner.  In the same phase: commit the pulled
+    // weights of the previous group's columns (a different set of columns; all CTAs are past its phase C).
+    for (int q = max(b - group, 0); q < b; ++q) {
+      const int blk = Q.order[q];
+      darlin_pull(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
+    }
     for (int q = b; q < ge; ++q) {
       const int blk = Q.order[q];
       darlin_grad_push(Wk, P, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid >> 5, gsz >> 5, lane);
@@ -287,23 +315,19 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
     }
     for (int q = b; q < ge; ++q) {
       const int blk = Q.order[q];
-      darlin_pull(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
-    if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
-      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 13); *Q.abort_flag = 1u; }
-      break;
-    }
-    for (int q = b; q < ge; ++q) {
-      const int blk = Q.order[q];
-      darlin_update_margin(Wk, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
+      darlin_pull_margin(Wk, P, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
     }
     __syncthreads();
     if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
     if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
       if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 14); *Q.abort_flag = 1u; }
       break;
+    }
+    if (ge == Q.nblk) {  // last group of the launch: commit its pulled weights now
+      for (int q = b; q < ge; ++q) {
+        const int blk = Q.order[q];
+        darlin_pull(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
+      }
     }
   }
 }

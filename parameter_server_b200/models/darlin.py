@@ -318,13 +318,13 @@ class DarlinSolver:
             Wk.row_idx = self.stage_row[s].data_ptr() - 4 * p0
             Wk.vals = 0 if self.h_val is None else self.stage_val[s].data_ptr() - 4 * p0
             Q = N.DarlinSched(order_t.data_ptr() + 4 * i, self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), 1, 1, self.seq + i,
-                              self.local_bar.data_ptr(), self.bar + 2 * i, self.abort.data_ptr(), self.status.data_ptr())
+                              self.local_bar.data_ptr(), self.bar + i, self.abort.data_ptr(), self.status.data_ptr())
             N.check(self._lib.psb_darlin_pass(C.byref(Wk), C.byref(self._P), C.byref(self._S), C.byref(Q), C.byref(H), self.grid,
                                               N.stream_ptr()), "darlin_pass")
             self.stage_free[s].record(compute)
             self.kernel_launches += 1
         self.seq += n
-        self.bar += 2 * n
+        self.bar += n
 
     def _build_structs(self):
         Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),
@@ -397,7 +397,7 @@ class DarlinSolver:
                                           C.byref(H), self.grid, N.stream_ptr()), "darlin_pass")
         ngroups = (len(order) + group - 1) // group
         self.seq += ngroups
-        self.bar += 2 * ngroups
+        self.bar += ngroups
         self.kernel_launches += 1
 
     def _pass_unfused(self, order: np.ndarray) -> None:
