@@ -156,7 +156,9 @@ def run_ftrl(args) -> dict:
         e2e = {"value": ex_per_step * args.steps / (e2e_ms / 1e3), "unit": "examples/s",
                "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": trainer.h2d_bytes // args.steps,
                "d2h_bytes_per_step": trainer.d2h_bytes // args.steps,
-               "mean_logloss_last": losses[-1] if losses else None}
+               "mean_logloss_last": losses[-1] if losses else None,
+               "h2d_gbs_per_gpu": trainer.h2d_bytes / args.steps / (e2e_ms / args.steps) / 1e6,
+               "numa": getattr(group, "numa", None)}
     clocks = sampler.stop()
     group.barrier()
     return {

@@ -7,10 +7,10 @@
 //   A  worker  G_j = −Σ y_i τ_i x_ij ,  U_j = Σ min(τ_i(1−τ_i)·e^{|x_ij|δ_j}, ¼)·x_ij²   (τ_i = 1/(1+e^{m_i}))
 //              computed nnz-parallel with warp-segmented sums and pushed straight into the
 //              owner shard's (G,U) accumulators with red.add.v2.f32 over NVLink
-//      ── every CTA adds 1 to each owner's arrival counter (release, system scope) ──
+//      ── the rank's last CTA to finish adds 1 to each owner's arrival counter (release, system scope) ──
 //   B  server  on arrival of all workers' CTAs: KKT filter, proximal-Newton step inside the
 //              trust region δ, δ update, accumulators cleared
-//      ── every CTA adds 1 to each worker's "updated" counter ──
+//      ── the rank's last CTA to finish adds 1 to each worker's "updated" counter ──
 //   C  worker  m_i += y_i·x_ij·(w_new_j − w_j) over the block's non-zeros, w_new_j loaded from the
 //              owner (peer load); one in-GPU barrier; the worker's own copy of w, δ and the
 //              active set of these columns is brought up to date one phase later, next to the
@@ -53,8 +53,8 @@ struct DarlinWorker {
 struct DarlinPeers {
   float* w[PSB_MAX_RANKS];        // owner shard weights (NaN = filtered)
   float2* gu[PSB_MAX_RANKS];      // owner shard (G,U) accumulators
-  uint64_t* arrive[PSB_MAX_RANKS];   // on owner o: #CTAs (all workers) that finished phase A
-  uint64_t* updated[PSB_MAX_RANKS];  // on worker r: #CTAs (all owners) that finished phase B
+  uint64_t* arrive[PSB_MAX_RANKS];   // on owner o: +1 per worker whose CTAs all finished phase A of a group
+  uint64_t* updated[PSB_MAX_RANKS];  // on worker r: +1 per owner whose CTAs all finished phase B of a group
   int rank, world;
   uint64_t timeout_ns;
 };
@@ -91,6 +91,25 @@ __device__ __forceinline__ void red_release_sys_add_u64(uint64_t* p, uint64_t v)
 }
 __device__ __forceinline__ void red_add_v2_f32(float2* p, float a, float b) {
   asm volatile("red.relaxed.sys.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+}
+
+// Cross-GPU arrival, two levels.  Every CTA first counts itself on a counter of its own GPU; the
+// CTA that completes the count (G·seq) notifies every rank's counter once.  A rank's counter thus
+// receives `world` remote increments per synchronisation point instead of world × G increments
+// on one address, which the owner's L2 would serialise (G = 148 CTAs: > 1000 remote atomics).
+// Ordering: the CTA's pushes → __syncthreads → fence.sys → acq_rel add (gpu scope) by thread 0;
+// the last adder therefore observes all CTAs' pushes before its release.sys notifications.
+template <bool kUpdated>
+__device__ __forceinline__ void cta_arrive_all(const DarlinPeers& P, uint64_t* local_ctr, uint64_t local_target) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    unsigned long long prev;
+    asm volatile("atom.acq_rel.gpu.global.add.u64 %0, [%1], %2;" : "=l"(prev) : "l"(local_ctr), "l"(1ull) : "memory");
+    if (prev + 1ull == local_target) {
+      for (int t = 0; t < P.world; ++t) red_release_sys_add_u64(kUpdated ? P.updated[t] : P.arrive[t], 1ull);
+    }
+  }
 }
 
 // thread 0 of the CTA waits until *ctr >= target (bounded); result broadcast to the CTA
@@ -289,13 +308,9 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       const int blk = Q.order[q];
       darlin_grad_push(Wk, P, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid >> 5, gsz >> 5, lane);
     }
-    __syncthreads();
-    if (threadIdx.x < P.world) {
-      __threadfence_system();
-      red_release_sys_add_u64(P.arrive[threadIdx.x], 1ull);
-    }
-    // B: wait for all workers' CTAs, update this shard's slots of the blocks
-    if (!cta_wait_counter(P.arrive[P.rank], seq * G * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
+    cta_arrive_all<false>(P, Q.local_bar + 1, seq * G);
+    // B: wait for all workers, update this shard's slots of the blocks
+    if (!cta_wait_counter(P.arrive[P.rank], seq * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
       if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 11); *Q.abort_flag = 1u; }
       break;
     }
@@ -303,13 +318,9 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       const int blk = Q.order[q];
       darlin_update_weight(P, S, H, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], gtid, gsz);
     }
-    __syncthreads();
-    if (threadIdx.x < P.world) {
-      __threadfence_system();
-      red_release_sys_add_u64(P.updated[threadIdx.x], 1ull);
-    }
-    // C: wait for all owners' CTAs, pull and apply
-    if (!cta_wait_counter(P.updated[P.rank], seq * G * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
+    cta_arrive_all<true>(P, Q.local_bar + 2, seq * G);
+    // C: wait for all owners, pull and apply
+    if (!cta_wait_counter(P.updated[P.rank], seq * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
       if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 12); *Q.abort_flag = 1u; }
       break;
     }

@@ -82,7 +82,20 @@ struct FtrlPeers {
   uint64_t timeout_ns;
   uint32_t in_cap;
   uint32_t tab_shift;                      // 64 − log2(table capacity): slot = mix64(key) >> tab_shift
+  uint32_t* in_chunk[PSB_MAX_RANKS];       // owner o: [sender][nchunks] records in every chunk segment of the inbox
+  uint32_t nchunks;                        // chunks of kChunkSlots slots in a per-minibatch table (same on all ranks)
+  uint32_t pad;
 };
+
+// The per-minibatch table is cut into aligned chunks of kChunkSlots slots; probing never leaves a
+// chunk.  All ranks hash with the same function into tables of the same size, so chunk c holds the
+// same range of hash values on every rank, and hence of every owner's shard table.  The records
+// that sender s routes to owner o from its chunk c go to a FIXED segment of o's inbox:
+//   [s · in_cap + c · kChunkSlots, … + in_chunk[o][s · nchunks + c])
+// (in_cap = table capacity, so the segments tile the inbox exactly).  No cursor atomics on the
+// sending side, and on the owner one thread block can apply chunk c of sender 0, 1, … in order
+// with block-level barriers only: no other block ever touches the keys of that hash range.
+constexpr int kChunkSlots = 1024;
 
 struct Minibatch {
   const int64_t* offsets;  // rows+1
@@ -174,6 +187,7 @@ __device__ __forceinline__ void phase_localize(const Minibatch& M, const LocalSc
                                                size_t gtid, size_t gsz) {
   PSB_STREAM_POLICY(pol);
   const int64_t step = (int64_t)gsz;
+  const uint64_t cmask = L.lt_mask < (uint64_t)(kChunkSlots - 1) ? L.lt_mask : (uint64_t)(kChunkSlots - 1);
   int64_t i = (int64_t)gtid;
   if (i >= M.nnz) return;
   uint64_t key0 = PSB_LD_U64(M.keys + i, pol);
@@ -189,7 +203,7 @@ __device__ __forceinline__ void phase_localize(const Minibatch& M, const LocalSc
     }
     uint32_t slot = (uint32_t)h0;
     if (cur0 != key0) {
-      const uint64_t s = table_find_or_insert(L.lt_keys, L.lt_mask, h0, key0, max_probe);
+      const uint64_t s = table_find_or_insert(L.lt_keys, L.lt_mask, cmask, h0, key0, max_probe);
       if (s == ~0ull) {
         set_status(L.status, kLocalTableFull, 0, 0);
         slot = kBadSlot;
@@ -359,14 +373,15 @@ __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratc
   }
 }
 
-// Scan the local table, append every unique key's record to its owner's inbox (segment of this
-// sender) and empty the table for the next minibatch.  A block handles chunks of kSendChunk slots.
+// Scan the local table, write every unique key's record into its owner's inbox and empty the
+// table for the next minibatch.  A block handles one chunk of kSendChunk slots per iteration.
 // The records of a chunk are first grouped by owner in shared memory, then written out so that
 // consecutive threads write consecutive inbox entries of one owner: the stores that cross NVLink
-// are full, coalesced lines instead of scattered 8-byte pieces.  One global cursor update per
-// owner and chunk.
+// are full, coalesced lines instead of scattered 8-byte pieces.  Chunk c always writes to the
+// c-th segment of the sender's part of the inbox and leaves the number of records beside it.
 constexpr int kSendItems = 4;
 constexpr int kSendChunk = 256 * kSendItems;
+static_assert(kSendChunk == kChunkSlots, "a block of 256 threads routes exactly one chunk per iteration");
 struct SendStage {
   uint64_t key[kSendChunk];
   uint64_t cnt[kSendChunk];
@@ -413,7 +428,11 @@ __device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const Local
       for (int t = 0; t < world; ++t) { st->off[t] = run; run += st->count[t]; }
       st->off[world] = run;
     }
-    if (threadIdx.x < world) st->base[threadIdx.x] = st->count[threadIdx.x] ? atomicAdd(L.send_cnt + threadIdx.x, st->count[threadIdx.x]) : 0u;
+    // fixed segment of this chunk in every owner's inbox; its fill level goes next to it
+    if (threadIdx.x < world) {
+      st->base[threadIdx.x] = (uint32_t)c0;
+      P.in_chunk[threadIdx.x][(size_t)P.rank * P.nchunks + (size_t)(c0 / chunk)] = st->count[threadIdx.x];
+    }
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < kSendItems; ++k) {
@@ -497,11 +516,29 @@ __device__ __forceinline__ void phase_sketch_insert(const uint64_t* rk, const ui
   }
 }
 
+struct ApplyAcc {  // per-thread deltas of the model statistics, flushed once per kernel
+  float dn1 = 0.f, dn2 = 0.f;
+  int dnnz = 0, dins = 0;
+};
+
+__device__ __forceinline__ void apply_flush(ApplyAcc& a, double* stats) {
+  const float dn1 = warp_sum(a.dn1), dn2 = warp_sum(a.dn2);
+  const int dnnz = __reduce_add_sync(0xffffffffu, a.dnnz), dins = __reduce_add_sync(0xffffffffu, a.dins);
+  if ((threadIdx.x & 31) == 0) {
+    if (dn1 != 0.f) atomicAdd(stats + 2, (double)dn1);
+    if (dn2 != 0.f) atomicAdd(stats + 3, (double)dn2);
+    if (dnnz != 0) atomicAdd(stats + 4, (double)dnnz);
+    if (dins != 0) atomicAdd(stats + 6, (double)dins);
+  }
+  a = ApplyAcc();
+}
+
+// apply records [0, n) of one sender; thread `tid` of `nthr` takes records tid, tid + nthr, …
 template <bool kCounts>
-__device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
-                                            const uint64_t* rk, const float* rg, const uint64_t* rc,
-                                            uint32_t n, const FtrlHyper& h, double* stats, uint32_t* status,
-                                            size_t gtid, size_t gsz) {
+__device__ __forceinline__ void apply_records(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
+                                              const uint64_t* rk, const float* rg, const uint64_t* rc,
+                                              uint32_t n, const FtrlHyper& h, ApplyAcc& acc, uint32_t* status,
+                                              size_t gtid, size_t gsz) {
   float dn1 = 0.f, dn2 = 0.f;
   int dnnz = 0, dins = 0;
   const bool filter = kCounts && tail_filter_on(h);
@@ -536,16 +573,18 @@ __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint3
     *reinterpret_cast<float2*>(&tab[slot].w) = make_float2(e.w, e.z);
     *reinterpret_cast<uint2*>(&tab[slot].pos) = make_uint2(e.pos, e.neg);
   }
-  dn1 = warp_sum(dn1);
-  dn2 = warp_sum(dn2);
-  dnnz = __reduce_add_sync(0xffffffffu, dnnz);
-  dins = __reduce_add_sync(0xffffffffu, dins);
-  if ((threadIdx.x & 31) == 0) {
-    if (dn1 != 0.f) atomicAdd(stats + 2, (double)dn1);
-    if (dn2 != 0.f) atomicAdd(stats + 3, (double)dn2);
-    if (dnnz != 0) atomicAdd(stats + 4, (double)dnnz);
-    if (dins != 0) atomicAdd(stats + 6, (double)dins);
-  }
+  acc.dn1 += dn1; acc.dn2 += dn2; acc.dnnz += dnnz; acc.dins += dins;
+}
+
+// stand-alone form: one flat record list (unfused baseline)
+template <bool kCounts>
+__device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
+                                            const uint64_t* rk, const float* rg, const uint64_t* rc,
+                                            uint32_t n, const FtrlHyper& h, double* stats, uint32_t* status,
+                                            size_t gtid, size_t gsz) {
+  ApplyAcc acc;
+  apply_records<kCounts>(tab, mask, shift, max_probe, rk, rg, rc, n, h, acc, status, gtid, gsz);
+  apply_flush(acc, stats);
 }
 
 // ------------------------------------------------------------ fused kernels
@@ -598,34 +637,62 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
   phase_route_send<kCounts>(P, L, &sm.stage);
   grid.sync();
   PSB_TRACE(L, gtid, 6);
-  // publish this sender's record count to every owner, then wait for all senders
+  // tell every owner that this sender's records and fill levels are in place, then wait for all senders
   if (blockIdx.x == 0 && threadIdx.x < world) {
     const int t = threadIdx.x;
-    uint32_t cnt = L.send_cnt[t];
-    if (cnt > P.in_cap) cnt = P.in_cap;
-    L.send_cnt[t] = 0;
     __threadfence_system();
-    st_release_sys_u64(P.in_flag[t] + P.rank, ((uint64_t)epoch << 32) | cnt);
+    st_release_sys_u64(P.in_flag[t] + P.rank, (uint64_t)epoch << 32);
     bool ok;
-    const uint64_t v = wait_epoch_ge(P.in_flag[P.rank] + t, epoch, P.timeout_ns, &ok);
-    L.recv_cnt[t] = ok ? (uint32_t)v : 0u;
+    wait_epoch_ge(P.in_flag[P.rank] + t, epoch, P.timeout_ns, &ok);
+    L.recv_cnt[t] = ok ? 1u : 0u;  // a sender that never arrived is skipped
     if (!ok) set_status(L.status, kWaitTimeout, t, 2);
   }
   grid.sync();
   PSB_TRACE(L, gtid, 7);
-  // apply sender by sender (the reference applies each worker's push separately)
-  for (int s = 0; s < world; ++s) {
-    const uint32_t n = __ldcg(L.recv_cnt + s);
-    const size_t off = (size_t)s * P.in_cap;
-    if (kCounts && tail_filter_on(H)) {
-      phase_sketch_insert(P.in_keys[P.rank] + off, P.in_cnt[P.rank] + off, n, H, gtid, gsz);
-      grid.sync();
+  // Apply sender by sender (the reference applies each worker's push separately).  The order only
+  // matters per key, and a key lives in one chunk: a block takes chunk c and walks the senders'
+  // segments of that chunk in rank order with block-level barriers.  With the tail filter on, a
+  // sender's counts must all be in the sketch before any of its keys is queried, so that case keeps
+  // grid-wide barriers around every sender.
+  {
+    ApplyAcc acc;
+    ShardSlot* tab = P.tab[P.rank];
+    const uint64_t* rk = P.in_keys[P.rank];
+    const float* rg = P.in_g[P.rank];
+    const uint64_t* rc = P.in_cnt[P.rank];
+    const uint32_t* fill = P.in_chunk[P.rank];
+    if (!(kCounts && tail_filter_on(H))) {
+      for (uint32_t c = blockIdx.x; c < P.nchunks; c += gridDim.x) {
+        for (int s = 0; s < world; ++s) {
+          if (__ldcg(L.recv_cnt + s) == 0u) continue;
+          const uint32_t n = min(__ldcg(fill + (size_t)s * P.nchunks + c), (uint32_t)kChunkSlots);
+          const size_t off = (size_t)s * P.in_cap + (size_t)c * kChunkSlots;
+          apply_records<kCounts>(tab, P.tab_mask, P.tab_shift, P.max_probe, rk + off, rg + off, rc + off, n, H, acc,
+                                 L.status, threadIdx.x, blockDim.x);
+          __syncthreads();
+        }
+      }
+    } else {
+      for (int s = 0; s < world; ++s) {
+        const bool have = __ldcg(L.recv_cnt + s) != 0u;
+        for (uint32_t c = blockIdx.x; have && c < P.nchunks; c += gridDim.x) {
+          const uint32_t n = min(__ldcg(fill + (size_t)s * P.nchunks + c), (uint32_t)kChunkSlots);
+          const size_t off = (size_t)s * P.in_cap + (size_t)c * kChunkSlots;
+          phase_sketch_insert(rk + off, rc + off, n, H, threadIdx.x, blockDim.x);
+        }
+        grid.sync();
+        for (uint32_t c = blockIdx.x; have && c < P.nchunks; c += gridDim.x) {
+          const uint32_t n = min(__ldcg(fill + (size_t)s * P.nchunks + c), (uint32_t)kChunkSlots);
+          const size_t off = (size_t)s * P.in_cap + (size_t)c * kChunkSlots;
+          apply_records<kCounts>(tab, P.tab_mask, P.tab_shift, P.max_probe, rk + off, rg + off, rc + off, n, H, acc,
+                                 L.status, threadIdx.x, blockDim.x);
+        }
+        grid.sync();
+      }
     }
-    phase_apply<kCounts>(P.tab[P.rank], P.tab_mask, P.tab_shift, P.max_probe,
-                         P.in_keys[P.rank] + off, P.in_g[P.rank] + off, P.in_cnt[P.rank] + off, n, H, L.stats,
-                         L.status, gtid, gsz);
-    grid.sync();
+    apply_flush(acc, L.stats);
   }
+  grid.sync();
   PSB_TRACE(L, gtid, 8);
   if (blockIdx.x == 0 && threadIdx.x < world) {
     __threadfence_system();

@@ -147,10 +147,12 @@ __device__ __forceinline__ float warp_max(float v) {
 
 // ---- open-addressing u64 set/map probes ----
 // insert-or-find in a local (same GPU) table; returns slot or ~0ull when the
-// probe limit is hit.
-__device__ __forceinline__ uint64_t table_find_or_insert(uint64_t* keys, uint64_t mask, uint64_t h,
-                                                        uint64_t key, int max_probe) {
+// probe limit is hit.  Probing wraps inside the aligned chunk of (chunk_mask + 1) slots that
+// holds the home slot h, so a key never leaves its home chunk (chunk_mask = mask: whole table).
+__device__ __forceinline__ uint64_t table_find_or_insert(uint64_t* keys, uint64_t mask, uint64_t chunk_mask,
+                                                        uint64_t h, uint64_t key, int max_probe) {
   uint64_t slot = h & mask;
+  const uint64_t base = slot & ~chunk_mask;
   for (int i = 0; i < max_probe; ++i) {
     uint64_t cur = keys[slot];
     if (cur == key) return slot;
@@ -159,7 +161,7 @@ __device__ __forceinline__ uint64_t table_find_or_insert(uint64_t* keys, uint64_
                                           (unsigned long long)kEmptyKey, (unsigned long long)key);
       if (prev == kEmptyKey || prev == key) return slot;
     }
-    slot = (slot + 1) & mask;
+    slot = base | ((slot + 1) & chunk_mask);
   }
   return ~0ull;
 }

@@ -261,7 +261,9 @@ class DarlinSolver:
         self.srv_delta = torch.full((cap,), self.cfg.delta_init, dtype=f32, device=dev)
         self.srv_active = torch.ones(cap, dtype=torch.uint8, device=dev)
         self.violation = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.local_bar = torch.zeros(1, dtype=torch.int64, device=dev)
+        # monotone in-GPU counters: [0] barrier after the margin update, [1]/[2] this GPU's CTAs that finished
+        # the gradient / update phase (the CTA completing a count notifies the other ranks)
+        self.local_bar = torch.zeros(4, dtype=torch.int64, device=dev)
         self.abort = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = torch.zeros(8, dtype=torch.int32, device=dev)
         if self.out_of_core:

@@ -111,6 +111,10 @@ class FTRLEngine:
         self.in_keys = group.alloc((W * self.in_cap,), i64, fill=-1)
         self.in_g = group.alloc((W * self.in_cap,), f32)
         self.in_cnt = group.alloc((W * self.in_cap,), i64)
+        # the per-minibatch table is cut into chunks of 1024 slots; chunk c of sender s owns the fixed inbox
+        # segment [s * in_cap + c * 1024, ...) and reports its fill level in in_chunk[s * nchunks + c]
+        self.nchunks = (self.lcap + 1023) // 1024
+        self.in_chunk = group.alloc((W * self.nchunks,), torch.int32)
         self.in_flag = group.alloc((N.MAX_RANKS,), i64)
         self.applied = group.alloc((N.MAX_RANKS,), i64)
 
@@ -142,9 +146,11 @@ class FTRLEngine:
             P.in_g[r] = self.in_g.ptrs[r]
             P.in_cnt[r] = self.in_cnt.ptrs[r]
             P.in_flag[r] = self.in_flag.ptrs[r]
+            P.in_chunk[r] = self.in_chunk.ptrs[r]
             P.applied[r] = self.applied.ptrs[r]
         P.timeout_ns = int(timeout_s * 1e9)
         P.in_cap = self.in_cap
+        P.nchunks = self.nchunks
         P.tab_shift = 64 - (self.cap.bit_length() - 1)
         self._P = P
         L = N.LocalScratch()

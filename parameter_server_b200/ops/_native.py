@@ -47,7 +47,7 @@ class FtrlPeers(C.Structure):
     _fields_ = [("seps", KeySeps), ("rank", C.c_int), ("max_probe", C.c_int), ("tab_mask", C.c_uint64),
                 ("tab", _P8), ("in_keys", _P8), ("in_g", _P8), ("in_cnt", _P8),
                 ("in_flag", _P8), ("applied", _P8), ("timeout_ns", C.c_uint64), ("in_cap", C.c_uint32),
-                ("tab_shift", C.c_uint32)]
+                ("tab_shift", C.c_uint32), ("in_chunk", _P8), ("nchunks", C.c_uint32), ("pad", C.c_uint32)]
 
 
 class Minibatch(C.Structure):

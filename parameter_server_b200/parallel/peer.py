@@ -32,6 +32,7 @@ class PeerGroup:
     device: torch.device = field(default_factory=lambda: torch.device("cuda", 0))
     group: object = None
     _buffers: list = field(default_factory=list)
+    numa: dict = field(default_factory=dict)   # what bind_to_gpu_node found / did for this rank
 
     @staticmethod
     def single(device: Optional[torch.device] = None) -> "PeerGroup":
@@ -42,18 +43,25 @@ class PeerGroup:
         """Join the process group described by RANK/LOCAL_RANK/WORLD_SIZE/MASTER_* (torchrun)."""
         import torch.distributed as dist
 
+        from ..utils.numa import bind_to_gpu_node
+
         world = int(os.environ.get("WORLD_SIZE", "1"))
         if world == 1:
             dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
             torch.cuda.set_device(dev)
-            return PeerGroup(0, 1, dev)
+            g = PeerGroup(0, 1, dev)
+            g.numa = bind_to_gpu_node(dev.index)
+            return g
         rank = int(os.environ["RANK"])
         local = int(os.environ.get("LOCAL_RANK", rank))
         dev = torch.device("cuda", local)
         torch.cuda.set_device(dev)
+        numa = bind_to_gpu_node(local)      # before any pinned buffer is allocated (PSB_NUMA_BIND=1)
         if not dist.is_initialized():
             dist.init_process_group(backend=backend, rank=rank, world_size=world, device_id=dev)
-        return PeerGroup(rank, world, dev, dist.group.WORLD)
+        g = PeerGroup(rank, world, dev, dist.group.WORLD)
+        g.numa = numa
+        return g
 
     # ------------------------------------------------------------------ memory
     def alloc(self, shape, dtype, fill=0) -> SymmetricBuffer:
