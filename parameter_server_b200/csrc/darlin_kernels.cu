@@ -99,16 +99,32 @@ __device__ __forceinline__ void red_add_v2_f32(float2* p, float a, float b) {
 // on one address, which the owner's L2 would serialise (G = 148 CTAs: > 1000 remote atomics).
 // Ordering: the CTA's pushes → __syncthreads → fence.sys → acq_rel add (gpu scope) by thread 0;
 // the last adder therefore observes all CTAs' pushes before its release.sys notifications.
+// The notifications go out from `world` threads at once: a release at system scope waits for the
+// thread's earlier remote writes, so one thread sending them one after the other would pay a
+// round trip per rank.
 template <bool kUpdated>
-__device__ __forceinline__ void cta_arrive_all(const DarlinPeers& P, uint64_t* local_ctr, uint64_t local_target) {
+__device__ __forceinline__ void cta_arrive_all(const DarlinPeers& P, uint64_t* local_ctr, uint64_t local_target,
+                                               bool* s_last) {
+#ifdef PSB_DARLIN_FLAT_ARRIVE
+  // one level: every CTA notifies every rank (compile-time alternative, kept for comparisons)
+  __syncthreads();
+  if (threadIdx.x < P.world) {
+    __threadfence_system();
+    red_release_sys_add_u64(kUpdated ? P.updated[threadIdx.x] : P.arrive[threadIdx.x], 1ull);
+  }
+  return;
+#endif
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
     unsigned long long prev;
     asm volatile("atom.acq_rel.gpu.global.add.u64 %0, [%1], %2;" : "=l"(prev) : "l"(local_ctr), "l"(1ull) : "memory");
-    if (prev + 1ull == local_target) {
-      for (int t = 0; t < P.world; ++t) red_release_sys_add_u64(kUpdated ? P.updated[t] : P.arrive[t], 1ull);
-    }
+    *s_last = prev + 1ull == local_target;
+  }
+  __syncthreads();
+  if (*s_last && threadIdx.x < P.world) {
+    __threadfence_system();
+    red_release_sys_add_u64(kUpdated ? P.updated[threadIdx.x] : P.arrive[threadIdx.x], 1ull);
   }
 }
 
@@ -277,12 +293,17 @@ __device__ __forceinline__ void darlin_pull_margin(const DarlinWorker& Wk, const
 
 __global__ void __launch_bounds__(512)
 darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q, DarlinHyper H) {
-  __shared__ bool s_ok;
+  __shared__ bool s_ok, s_last;
   __shared__ uint32_t s_abort;
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t gsz = (size_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
   const uint64_t G = gridDim.x;
+#ifdef PSB_DARLIN_FLAT_ARRIVE
+  const uint64_t fan = G;    // increments a rank contributes to a cross-GPU counter per synchronisation point
+#else
+  const uint64_t fan = 1;
+#endif
   uint64_t bar = Q.bar0;
 
   // Blocks are processed in groups of Q.group consecutive entries of the order (group = max_block_delay + 1):
@@ -308,9 +329,9 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       const int blk = Q.order[q];
       darlin_grad_push(Wk, P, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid >> 5, gsz >> 5, lane);
     }
-    cta_arrive_all<false>(P, Q.local_bar + 1, seq * G);
+    cta_arrive_all<false>(P, Q.local_bar + 1, seq * G, &s_last);
     // B: wait for all workers, update this shard's slots of the blocks
-    if (!cta_wait_counter(P.arrive[P.rank], seq * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
+    if (!cta_wait_counter(P.arrive[P.rank], seq * (uint64_t)P.world * fan, P.timeout_ns, true, &s_ok)) {
       if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 11); *Q.abort_flag = 1u; }
       break;
     }
@@ -318,9 +339,9 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       const int blk = Q.order[q];
       darlin_update_weight(P, S, H, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], gtid, gsz);
     }
-    cta_arrive_all<true>(P, Q.local_bar + 2, seq * G);
+    cta_arrive_all<true>(P, Q.local_bar + 2, seq * G, &s_last);
     // C: wait for all owners, pull and apply
-    if (!cta_wait_counter(P.updated[P.rank], seq * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
+    if (!cta_wait_counter(P.updated[P.rank], seq * (uint64_t)P.world * fan, P.timeout_ns, true, &s_ok)) {
       if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 12); *Q.abort_flag = 1u; }
       break;
     }
