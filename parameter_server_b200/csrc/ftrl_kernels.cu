@@ -619,8 +619,13 @@ ftrl_pull_spmv_kernel(FtrlPeers P, Minibatch M, LocalScratch L, uint32_t epoch) 
   PSB_TRACE(L, gtid, 3);
 }
 
+// 6 blocks per SM (42 registers): measured best; 3 blocks (69 registers, no cap) and 8 blocks
+// (32 registers, spills) are both about 4 % slower per step.
+#ifndef PSB_PUSH_MIN_BLOCKS
+#define PSB_PUSH_MIN_BLOCKS 6
+#endif
 template <bool kCounts>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, PSB_PUSH_MIN_BLOCKS)
 ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, uint32_t epoch) {
   cg::grid_group grid = cg::this_grid();
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
