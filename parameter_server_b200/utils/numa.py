@@ -66,18 +66,65 @@ def node_cpus(node: int, sysfs: str = "/sys") -> Set[int]:
     return parse_cpulist(text) if text else set()
 
 
+def parse_topo_cpu_affinity(text: str) -> Dict[int, Set[int]]:
+    """CPU affinity per GPU from the matrix that ``nvidia-smi topo -m`` prints (tab-separated cells, one
+    header line that names a ``CPU Affinity`` column, one row per ``GPU<i>``)."""
+    import re
+
+    out: Dict[int, Set[int]] = {}
+    col = None
+    for line in re.sub(r"\x1b\[[0-9;]*m", "", text).splitlines():
+        cells = [c.strip() for c in line.split("\t")]
+        if col is None:
+            if "CPU Affinity" in cells:
+                col = cells.index("CPU Affinity")
+            continue
+        name = cells[0] if cells else ""
+        if name.startswith("GPU") and name[3:].isdigit() and col < len(cells):
+            try:
+                out[int(name[3:])] = parse_cpulist(cells[col])
+            except ValueError:
+                pass
+    return out
+
+
+def gpu_cpus_from_driver(device_index: int) -> Set[int]:
+    """Fallback when sysfs hides the NUMA node (containers): ask the driver's topology report (read only)."""
+    import subprocess
+
+    try:
+        r = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20)
+    except (OSError, subprocess.SubprocessError):
+        return set()
+    if r.returncode != 0:
+        return set()
+    # torch's device order follows CUDA_VISIBLE_DEVICES; the report lists physical indices
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    phys = device_index
+    ids = [v.strip() for v in vis.split(",") if v.strip()]
+    if ids and device_index < len(ids) and ids[device_index].isdigit():
+        phys = int(ids[device_index])
+    return parse_topo_cpu_affinity(r.stdout).get(phys, set())
+
+
 def bind_to_gpu_node(device_index: int, sysfs: str = "/sys") -> Dict[str, object]:
-    """Restrict this process to the CPUs of the GPU's NUMA node.  Returns what was found and done."""
-    info: Dict[str, object] = {"node": -1, "bound": False, "cpus": 0}
+    """Restrict this process to the CPUs next to the GPU.  Returns what was found and done."""
+    info: Dict[str, object] = {"node": -1, "bound": False, "cpus": 0, "source": None}
     if os.environ.get("PSB_NUMA_BIND", "0") != "1" or not hasattr(os, "sched_setaffinity"):
         return info
     node = gpu_numa_node(device_index, sysfs)
     info["node"] = node
-    if node < 0:
+    cpus: Set[int] = set()
+    if node >= 0:
+        cpus, info["source"] = node_cpus(node, sysfs), "sysfs"
+    if not cpus:
+        cpus = gpu_cpus_from_driver(device_index)
+        info["source"] = "driver" if cpus else None
+    if not cpus:
         return info
     try:
         allowed = os.sched_getaffinity(0)
-        want = node_cpus(node, sysfs) & allowed
+        want = cpus & allowed
         if want and want != allowed:
             os.sched_setaffinity(0, want)
             info["bound"] = True
