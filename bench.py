@@ -247,7 +247,8 @@ def run_darlin(args):
     if not args.no_e2e and impl == "fused":
         del sol
         torch.cuda.empty_cache()
-        ooc = DarlinSolver(group, cfg, timeout_s=args.timeout_s, impl="fused", out_of_core=True)
+        ooc = DarlinSolver(group, cfg, timeout_s=args.timeout_s, impl="fused", out_of_core=True,
+                           prefetch_depth=args.prefetch_depth)
         ooc.preprocess(off, idx, vals, y)
         ms2, _, h2d, objs = timed(ooc, True)
         e2e = {"value": rows_total * args.steps / (ms2 / 1e3), "unit": "examples/s", "ms_per_step": ms2 / args.steps,
@@ -291,6 +292,8 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host-streaming) measurement")
     ap.add_argument("--rule", default="sumsq", choices=["count", "sumsq"],
                     help="per-key learning-rate statistic: reference count-based estimate or sum of g^2")
+    ap.add_argument("--prefetch-depth", type=int, default=4,
+                    help="DARLIN end-to-end run: column blocks in flight between pinned host memory and the GPU")
     ap.add_argument("--track-counts", action="store_true",
                     help="keep per-key pos/neg row counts although the sum-of-squares rule does not need them")
     ap.add_argument("--timeout-s", type=float, default=5.0, help="limit of in-kernel cross-GPU waits")

@@ -217,12 +217,16 @@ __device__ __forceinline__ void phase_localize(const Minibatch& M, const LocalSc
 }
 
 // weight of `key` in owner's table (peer memory), 0 when absent; one 16-byte load per probe
+// (`peer` = the table is another GPU's: system scope; this GPU's own shard is read at GPU scope)
 __device__ __forceinline__ float probe_weight(const ShardSlot* tab, uint64_t mask, uint32_t shift, uint64_t key,
-                                              int max_probe) {
+                                              int max_probe, bool peer = true) {
   uint64_t slot = shard_hash(key, shift) & mask;
   for (int i = 0; i < max_probe; ++i) {
     uint64_t k, wz;
-    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(k), "=l"(wz) : "l"(tab + slot) : "memory");
+    if (peer)
+      asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(k), "=l"(wz) : "l"(tab + slot) : "memory");
+    else
+      asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(k), "=l"(wz) : "l"(tab + slot) : "memory");
     if (k == key) return __uint_as_float((uint32_t)wz);
     if (k == kEmptyKey) return 0.f;
     slot = (slot + 1) & mask;
@@ -238,7 +242,7 @@ __device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScra
     const uint64_t key = __ldcg(L.lt_keys + s);
     if (key != kEmptyKey) {
       const int o = route_owner(P.seps, key);
-      const float w = probe_weight(P.tab[o], P.tab_mask, P.tab_shift, key, P.max_probe);
+      const float w = probe_weight(P.tab[o], P.tab_mask, P.tab_shift, key, P.max_probe, o != P.rank);
       if (kCounts) {
         LocalSlot v;
         v.w = w;
@@ -466,7 +470,8 @@ __device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const Local
     }
     __syncthreads();
   }
-  __threadfence_system();
+  // the records must be visible to their owners before the flag is: system scope only when other GPUs exist
+  if (world > 1) __threadfence_system(); else __threadfence();
 }
 
 __device__ __forceinline__ float ftrl_sqrt_n(float pos, float neg) {
@@ -760,7 +765,7 @@ __global__ void k_pack_keys(KeySeps seps, LocalScratch L, uint32_t* cursors, uin
 __global__ void k_lookup(const ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
                          const uint64_t* keys, uint32_t n, float* out_w) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    out_w[i] = probe_weight(tab, mask, shift, keys[i], max_probe);
+    out_w[i] = probe_weight(tab, mask, shift, keys[i], max_probe, false);
 }
 __global__ void k_scatter_w(const uint32_t* slots, const float* w, uint32_t n, LocalScratch L) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {

@@ -84,13 +84,17 @@ class DarlinSolver:
     """Worker + server of one rank; ``preprocess`` once, then ``run`` (or ``run_pass`` repeatedly)."""
 
     def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused",
-                 out_of_core: bool = False, prefetch_depth: int = 3):
+                 out_of_core: bool = False, prefetch_depth: int = 3, blocks_per_launch: int = 16):
         """``out_of_core``: keep the column blocks (row ids, values) in pinned host memory and stream each
         block to the GPU on a side stream ahead of its turn in the block order — the role of the
         reference's ``FeatureStation`` in ``-mmap_training_data`` mode with its task-id keyed look-ahead
         prefetch (src/linear_method/feature_station.cc:212-279, src/linear_method/darling.cc:175-201)."""
         self.group, self.cfg, self.impl = group, cfg, impl
         self.out_of_core, self.prefetch_depth = out_of_core, max(int(prefetch_depth), 2)
+        # out-of-core mode: blocks per kernel launch (a launch costs about as much as a block); rounded up to a
+        # multiple of max_block_delay + 1
+        grp = max(int(cfg.max_block_delay), 0) + 1
+        self.blocks_per_launch = (max(int(blocks_per_launch), 1) + grp - 1) // grp * grp
         self.h2d_bytes = 0
         self.dev = group.device
         self.timeout_s = timeout_s
@@ -273,60 +277,65 @@ class DarlinSolver:
 
     def _to_host_blocks(self) -> None:
         """Move the CSC payload to pinned host memory; only a small ring of block buffers stays on the device."""
-        self.h_row = self.row_idx.cpu().pin_memory()
-        self.h_val = None if self.vals is None else self.vals.cpu().pin_memory()
-        cp = self.col_ptr[self.blk_lc.reshape(-1)].reshape(-1, 2)
-        self.blk_nnz = cp.cpu().tolist()                      # [p0, p1) of every block in the CSC arrays
-        cap = max(max(p1 - p0 for p0, p1 in self.blk_nnz), 1)
-        d = self.prefetch_depth
-        self.stage_row = [torch.empty(cap, dtype=torch.int32, device=self.dev) for _ in range(d)]
-        self.stage_val = [None if self.vals is None else torch.empty(cap, dtype=torch.float32, device=self.dev) for _ in range(d)]
-        self.stage_ready = [torch.cuda.Event() for _ in range(d)]
-        self.stage_free = [torch.cuda.Event() for _ in range(d)]
-        self.copy_stream = torch.cuda.Stream(device=self.dev)
-        self.row_idx = self.stage_row[0]                      # placeholders for the struct; replaced per block
-        self.vals = self.stage_val[0]
+        has_vals = self.vals is not None
+        words = 2 if has_vals else 1
+        cp = self.col_ptr[self.blk_lc.reshape(-1)].reshape(-1, 2).cpu()
+        self.blk_nnz = np.ascontiguousarray(cp.numpy().astype(np.int64))   # [p0, p1) of every block in the CSC arrays
+        # pinned host copy, packed per block as [row ids | values]: one copy per block brings both
+        rows_h = self.row_idx.cpu()
+        vals_h = self.vals.cpu().view(torch.int32) if has_vals else None
+        self.h_pack = torch.empty(max(rows_h.numel() * words, 1), dtype=torch.int32).pin_memory()
+        for p0, p1 in self.blk_nnz.tolist():
+            n = p1 - p0
+            self.h_pack[words * p0: words * p0 + n] = rows_h[p0:p1]
+            if has_vals:
+                self.h_pack[words * p0 + n: words * p1] = vals_h[p0:p1]
+        cap = max(int((self.blk_nnz[:, 1] - self.blk_nnz[:, 0]).max()) if len(self.blk_nnz) else 1, 1)
+        d = min(self.prefetch_depth, 16)
+        # a ring slot holds one launch's worth of blocks; stage_base gets every block's address for the kernel
+        self.stage = [torch.empty(cap * words * self.blocks_per_launch, dtype=torch.int32, device=self.dev)
+                      for _ in range(d)]
+        self.stage_base = torch.zeros(max(len(self.blk_nnz), 1), dtype=torch.int64, device=self.dev)
+        self._stage_ptrs = (C.c_void_p * d)(*[t.data_ptr() for t in self.stage])
+        lib = self._lib
+        lib.psb_darlin_streamer_create.restype = C.c_void_p
+        self._streamer = C.c_void_p(lib.psb_darlin_streamer_create(d))
+        if not self._streamer:
+            raise RuntimeError("could not create the block streamer (copy stream / events)")
+        self.row_idx = self.stage[0]                          # placeholders for the struct; replaced per block
+        self.vals = self.stage[0].view(torch.float32) if has_vals else None
+
+    def __del__(self):
+        st = getattr(self, "_streamer", None)
+        if st:
+            try:
+                self._lib.psb_darlin_streamer_destroy(st)
+            except Exception:
+                pass
+            self._streamer = None
 
     def _pass_streamed(self, order: np.ndarray, order_t: torch.Tensor) -> None:
-        """One pass with every block's rows/values copied host→device just ahead of its kernel."""
-        compute = torch.cuda.current_stream(self.dev)
-        d, n = self.prefetch_depth, len(order)
+        """One pass with every block's rows/values copied host→device just ahead of its kernel: one native
+        call issues the copies, events and launches of all blocks (``psb_darlin_pass_streamed``)."""
+        n = len(order)
         H = self._hyper()
-        blocks = order.tolist()
-
-        def issue(i: int) -> None:
-            p0, p1 = self.blk_nnz[blocks[i]]
-            s = i % d
-            with torch.cuda.stream(self.copy_stream):
-                self.copy_stream.wait_event(self.stage_free[s])
-                if p1 > p0:
-                    self.stage_row[s][: p1 - p0].copy_(self.h_row[p0:p1], non_blocking=True)
-                    self.h2d_bytes += (p1 - p0) * 4
-                    if self.h_val is not None:
-                        self.stage_val[s][: p1 - p0].copy_(self.h_val[p0:p1], non_blocking=True)
-                        self.h2d_bytes += (p1 - p0) * 4
-                self.stage_ready[s].record(self.copy_stream)
-
-        for i in range(min(d - 1, n)):
-            issue(i)
-        for i in range(n):
-            if i + d - 1 < n:
-                issue(i + d - 1)
-            s = i % d
-            p0, _ = self.blk_nnz[blocks[i]]
-            compute.wait_event(self.stage_ready[s])
-            Wk = N.DarlinWorker.from_buffer_copy(self._Wk)
-            # the kernel indexes row_idx/vals with absolute CSC positions: bias the staging pointers by p0
-            Wk.row_idx = self.stage_row[s].data_ptr() - 4 * p0
-            Wk.vals = 0 if self.h_val is None else self.stage_val[s].data_ptr() - 4 * p0
-            Q = N.DarlinSched(order_t.data_ptr() + 4 * i, self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), 1, 1, self.seq + i,
-                              self.local_bar.data_ptr(), self.bar + i, self.abort.data_ptr(), self.status.data_ptr())
-            N.check(self._lib.psb_darlin_pass(C.byref(Wk), C.byref(self._P), C.byref(self._S), C.byref(Q), C.byref(H), self.grid,
-                                              N.stream_ptr()), "darlin_pass")
-            self.stage_free[s].record(compute)
-            self.kernel_launches += 1
-        self.seq += n
-        self.bar += n
+        order_h = np.ascontiguousarray(order, dtype=np.int32)
+        group = max(int(self.cfg.max_block_delay), 0) + 1
+        Q = N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), n, group, self.seq,
+                          self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr())
+        moved, launches = C.c_ulonglong(0), C.c_int(0)
+        N.check(self._lib.psb_darlin_pass_streamed(
+            self._streamer, C.byref(self._Wk), C.byref(self._P), C.byref(self._S), C.byref(Q), C.byref(H), self.grid,
+            order_h.ctypes.data_as(C.c_void_p), n, self.blk_nnz.ctypes.data_as(C.c_void_p),
+            C.c_void_p(self.h_pack.data_ptr()), 1 if self.vals is not None else 0, self._stage_ptrs,
+            C.c_void_p(self.stage_base.data_ptr()), self.blocks_per_launch, N.stream_ptr(), C.byref(moved),
+            C.byref(launches)), "darlin_pass_streamed")
+        self.h2d_bytes += moved.value
+        self.kernel_launches += launches.value
+        # a launch of `blocks_per_launch` blocks (a multiple of the group size) runs ceil(blocks / group) groups
+        ngroups = sum((min(self.blocks_per_launch, n - f) + group - 1) // group for f in range(0, n, self.blocks_per_launch))
+        self.seq += ngroups
+        self.bar += ngroups
 
     def _build_structs(self):
         Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),

@@ -116,7 +116,7 @@ class DarlinServer(C.Structure):
 class DarlinSched(C.Structure):
     _fields_ = [("order", C.c_void_p), ("blk_lc", C.c_void_p), ("blk_sl", C.c_void_p), ("nblk", C.c_int),
                 ("group", C.c_int), ("seq0", C.c_uint64), ("local_bar", C.c_void_p), ("bar0", C.c_uint64),
-                ("abort_flag", C.c_void_p), ("status", C.c_void_p)]
+                ("abort_flag", C.c_void_p), ("status", C.c_void_p), ("stage_base", C.c_void_p)]
 
 
 class DarlinHyper(C.Structure):
