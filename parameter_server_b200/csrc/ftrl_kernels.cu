@@ -470,7 +470,8 @@ __device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const Local
     }
     __syncthreads();
   }
-  // the records must be visible to their owners before the flag is: system scope only when other GPUs exist
+  // the records must be visible to their owners before the flag is: system scope only when other GPUs
+  // exist (a fence by one thread per block after the barrier measured the same: 48.4 vs 49.2 us at N=2)
   if (world > 1) __threadfence_system(); else __threadfence();
 }
 
