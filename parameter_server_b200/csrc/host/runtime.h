@@ -41,8 +41,10 @@ class RNode {
   RNode(const Node& n, Executor* e) : node(n), exec_(e) {}
   Node node;
   TaskTracker incoming, outgoing;
-  int time = 0;                         // newest timestamp used with this node
+  int time = 0;                         // newest timestamp used with this node (guarded by Executor::clock_mu)
   std::mutex mu;
+  std::mutex send_mu;                   // orders key-cache decisions with the send queue
+  std::atomic<uint64_t> key_cache_misses{0};   // requests that named a key list this node no longer caches
   std::map<int, MessagePtr> pending;    // sent, not yet acknowledged
   std::map<int, std::function<void()>> recv_handles, fin_handles;
   // key caches: (channel, range) -> (signature, keys)
@@ -87,6 +89,9 @@ inline void RNode::cache_key_recver(const MessagePtr& m, bool enabled) {
     if (it != key_cache.end() && it->second.first == m->task.key_signature) {
       m->key = it->second.second;
       m->task.has_key = true;
+    } else if (key_cache_misses++ == 0) {
+      std::fprintf(stderr, "key cache miss: %s sent signature %u on channel %d that is not cached here\n",
+                   m->sender.c_str(), m->task.key_signature, m->task.key_channel);
     }
   }
 }
@@ -159,6 +164,7 @@ class Executor {
   int last_task() const { return last_task_; }
   bool key_cache_enabled = true;
   std::atomic<uint64_t> processed{0};
+  std::mutex clock_mu;   // guards RNode::time of every node and group of this executor
   // payloads (task.msg) of the replies to outgoing task t, by replying node
   std::map<std::string, std::string> take_replies(int t) {
     std::lock_guard<std::mutex> l(mu_);
@@ -634,14 +640,20 @@ inline int Customer::submit(const MessagePtr& msg) {
   msg->original_recver = msg->recver;
   auto members = exec_->group(msg->recver);
   {
-    std::lock_guard<std::mutex> l(dst->mu);
+    // the logical clocks of all remote nodes of this customer advance under one lock: a group's clock
+    // reads its members' clocks, and several application threads may submit at the same time
+    std::lock_guard<std::mutex> lc(exec_->clock_mu);
     if (task.time > kInvalidTime) {
       dst->time = std::max(task.time, dst->time);
     } else {
       for (auto& w : members) dst->time = std::max(dst->time, w->time);
       task.time = ++dst->time;
     }
-    if (msg->fin_handle) dst->fin_handles[task.time] = msg->fin_handle;
+    for (auto& w : members) w->time = std::max(task.time, w->time);
+  }
+  if (msg->fin_handle) {
+    std::lock_guard<std::mutex> l(dst->mu);
+    dst->fin_handles[task.time] = msg->fin_handle;
   }
   const int t = task.time;
   for (auto& w : members) w->outgoing.start(t);
@@ -654,12 +666,18 @@ inline int Customer::submit(const MessagePtr& msg) {
     pieces[i]->original_recver = msg->recver;
     {
       std::lock_guard<std::mutex> l(w->mu);
-      w->time = std::max(t, w->time);
       w->pending[t] = pieces[i];
       if (msg->recv_handle) w->recv_handles[t] = msg->recv_handle;
     }
-    if (pieces[i]->valid) w->cache_key_sender(pieces[i], exec_->key_cache_enabled);
-    po_->queue(pieces[i]);
+    if (pieces[i]->valid) {
+      // the key-cache decision and the place in the send queue are taken together: the receiver
+      // replays the same sequence of cache updates, so two threads must not interleave here
+      std::lock_guard<std::mutex> ls(w->send_mu);
+      w->cache_key_sender(pieces[i], exec_->key_cache_enabled);
+      po_->queue(pieces[i]);
+    } else {
+      po_->queue(pieces[i]);
+    }
   }
   if (members.empty() && msg->fin_handle) msg->fin_handle();
   if (msg->wait) wait_out(msg->recver, t);

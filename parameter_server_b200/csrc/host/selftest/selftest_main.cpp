@@ -1,0 +1,198 @@
+// Native self-test of the host runtime, meant to be built with -fsanitize=thread or
+// -fsanitize=address,undefined and run on a machine without a GPU.
+//
+// The reference has no sanitizer builds and a few documented hazards ("Van::send is not thread
+// safe", src/system/van.cc:106-108; key/value maps shared between the app thread and the executor
+// thread, guarded only by protocol order).  This program drives the same code paths from several
+// threads at once so that a sanitizer can see them: 1 scheduler + 2 servers + 2 workers over the
+// in-process van, membership, concurrent pushes from two threads per worker, pulls with a
+// wait_time dependency on the push, heartbeats and the deadline-based failure detector, shutdown
+// while traffic is still queued.  Exit code 0 = every check passed (the sanitizer adds its own
+// non-zero exit code when it finds something).
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../kv.h"
+#include "../runtime.h"
+
+using namespace psb;
+
+namespace {
+
+int g_failed = 0;
+#define CHECK_TRUE(cond)                                                          \
+  do {                                                                            \
+    if (!(cond)) {                                                                \
+      std::fprintf(stderr, "selftest: %s failed (line %d)\n", #cond, __LINE__);   \
+      ++g_failed;                                                                 \
+    }                                                                             \
+  } while (0)
+
+std::string bytes_of(const std::vector<uint64_t>& v) {
+  return std::string(reinterpret_cast<const char*>(v.data()), v.size() * sizeof(uint64_t));
+}
+std::string bytes_of(const std::vector<double>& v) {
+  return std::string(reinterpret_cast<const char*>(v.data()), v.size() * sizeof(double));
+}
+
+struct NodeRt {  // one node of the in-process cluster
+  std::shared_ptr<Van> van;
+  std::unique_ptr<Postoffice> po;
+  std::unique_ptr<Customer> cust;
+  std::mutex mu;
+  std::map<uint64_t, double> store;   // server: key -> summed value
+  std::atomic<int> pushes{0};
+};
+
+}  // namespace
+
+int main() {
+  const int W = 2, S = 2, kRounds = 40, kThreadsPerWorker = 2;
+  auto hub = std::make_shared<InprocHub>();
+  std::vector<std::pair<std::string, int>> ids = {{"H", Node::SCHEDULER}, {"W0", Node::WORKER}, {"W1", Node::WORKER},
+                                                   {"S0", Node::SERVER}, {"S1", Node::SERVER}};
+  std::map<std::string, std::unique_ptr<NodeRt>> rt;
+  Node sched;
+  for (auto& id : ids) {
+    Node n;
+    n.role = id.second;
+    n.id = id.first;
+    n.hostname = "127.0.0.1";
+    auto r = std::make_unique<NodeRt>();
+    r->van = std::make_shared<InprocVan>(hub, n);
+    r->po = std::make_unique<Postoffice>(r->van, W, S);
+    if (id.first == "H") sched = r->van->my_node;
+    r->po->set_scheduler(sched);
+    r->po->start();
+    rt[id.first] = std::move(r);
+  }
+  for (auto& id : ids)
+    if (id.first != "H") rt[id.first]->po->register_with_scheduler();
+  CHECK_TRUE(rt["H"]->po->wait_nodes_and_init(10.0));
+  for (auto& id : ids)
+    if (id.first != "H") CHECK_TRUE(rt[id.first]->po->wait_nodes_ready(10.0));
+
+  // customers: servers sum pushed values per key and answer pulls with the current sums
+  std::atomic<int> pulled_ok{0};
+  for (auto& id : ids) {
+    NodeRt* r = rt[id.first].get();
+    r->cust = std::make_unique<Customer>(r->po.get(), "w");
+    if (id.second == Node::SERVER) {
+      r->cust->process = [r](const MessagePtr& m) {
+        if (!m->task.request) return;
+        const size_t n = m->key.size() / sizeof(uint64_t);
+        const uint64_t* k = reinterpret_cast<const uint64_t*>(m->key.data());
+        if (m->task.cmd == 1) {
+          const double* v = reinterpret_cast<const double*>(m->value.at(0).data());
+          std::lock_guard<std::mutex> l(r->mu);
+          for (size_t i = 0; i < n; ++i) r->store[k[i]] += v[i];
+          ++r->pushes;
+        } else if (m->task.cmd == 2) {
+          std::vector<double> out(n);
+          {
+            std::lock_guard<std::mutex> l(r->mu);
+            for (size_t i = 0; i < n; ++i) out[i] = r->store[k[i]];
+          }
+          r->cust->reply(m, m->key, {bytes_of(out)});
+        }
+      };
+    } else if (id.second == Node::WORKER) {
+      r->cust->process = [&pulled_ok](const MessagePtr& m) {
+        if (!m->task.request && m->task.cmd == 2 && !m->value.empty()) ++pulled_ok;
+      };
+    }
+  }
+
+  // heartbeats from every non-scheduler node
+  for (auto& id : ids)
+    if (id.first != "H") {
+      std::string who = id.first;
+      rt[id.first]->po->start_heartbeat(0.02, [who] { return "alive " + who; });
+    }
+
+  // concurrent pushes (two threads per worker), each followed by a pull that waits for it
+  const uint64_t half = (~0ull - 1) / 2;
+  std::vector<std::thread> threads;
+  for (int w = 0; w < W; ++w)
+    for (int t = 0; t < kThreadsPerWorker; ++t)
+      threads.emplace_back([&, w, t] {
+        Customer* c = rt["W" + std::to_string(w)]->cust.get();
+        for (int r = 0; r < kRounds; ++r) {
+          std::vector<uint64_t> keys = {3, 7 + (uint64_t)t, half + 5, half + 9 + (uint64_t)r % 3};
+          std::vector<double> vals = {1.0, 2.0, 3.0, 4.0};
+          auto push = std::make_shared<Message>();
+          push->recver = kServerGroup;
+          push->task.cmd = 1;
+          push->task.has_key = true;
+          push->key = bytes_of(keys);
+          push->value.push_back(bytes_of(vals));
+          push->task.has_key_range = true;
+          push->task.key_range = Range::all();
+          const int tp = c->submit(push);
+          auto pull = std::make_shared<Message>();
+          pull->recver = kServerGroup;
+          pull->task.cmd = 2;
+          pull->task.has_key = true;
+          pull->key = bytes_of(keys);
+          pull->task.has_key_range = true;
+          pull->task.key_range = Range::all();
+          pull->task.wait_time = tp;
+          const int tl = c->submit(pull);
+          if (!c->wait_out(kServerGroup, tl, 20.0)) ++g_failed;
+        }
+      });
+  for (auto& th : threads) th.join();
+
+  // every push arrived exactly once at both servers; sums are what the workers sent
+  const int total_pushes = W * kThreadsPerWorker * kRounds;
+  CHECK_TRUE(rt["S0"]->pushes == total_pushes && rt["S1"]->pushes == total_pushes);
+  {
+    std::lock_guard<std::mutex> l(rt["S0"]->mu);
+    CHECK_TRUE(rt["S0"]->store[3] == 1.0 * total_pushes);
+  }
+  {
+    std::lock_guard<std::mutex> l(rt["S1"]->mu);
+    CHECK_TRUE(rt["S1"]->store[half + 5] == 3.0 * total_pushes);
+  }
+  CHECK_TRUE(pulled_ok == 2 * total_pushes);   // one data reply per server and pull
+
+  // failure detector: everybody reported recently; after S1 stops, it shows up as dead
+  std::this_thread::sleep_for(std::chrono::milliseconds(100));
+  CHECK_TRUE(rt["H"]->po->dead_nodes(5.0).empty());
+  rt["S1"]->cust->exec()->stop();
+  rt["S1"]->po->stop();
+  std::this_thread::sleep_for(std::chrono::milliseconds(300));
+  auto dead = rt["H"]->po->dead_nodes(0.2);
+  CHECK_TRUE(dead.size() == 1 && dead[0] == "S1");
+
+  // host containers touched from several threads
+  {
+    ThreadsafeQueue<int> q;
+    std::atomic<long> sum{0};
+    std::vector<std::thread> ts;
+    for (int p = 0; p < 3; ++p) ts.emplace_back([&q] { for (int i = 1; i <= 1000; ++i) q.push(i); });
+    for (int cns = 0; cns < 3; ++cns) ts.emplace_back([&q, &sum] { int v; for (int i = 0; i < 1000; ++i) { q.wait_and_pop(v); sum += v; } });
+    for (auto& t : ts) t.join();
+    CHECK_TRUE(sum == 3L * 500500);
+    ThreadPool pool(4);
+    std::atomic<int> done{0};
+    for (int i = 0; i < 64; ++i) pool.add([&done] { ++done; });
+    pool.join();
+    CHECK_TRUE(done == 64);
+  }
+
+  // shutdown with traffic possibly still queued
+  for (auto& id : ids) {
+    rt[id.first]->cust->exec()->stop();
+    rt[id.first]->po->stop();
+  }
+  for (auto& id : ids) rt[id.first]->cust.reset();
+  std::printf("selftest: %s\n", g_failed == 0 ? "ok" : "FAILED");
+  return g_failed == 0 ? 0 : 1;
+}

@@ -130,6 +130,25 @@ def build_host(force: bool = False) -> Path | None:
     return out
 
 
+def build_host_selftest(sanitizer: str = "thread") -> Path | None:
+    """Compile the native self-test of the host runtime (``csrc/host/selftest``) with a sanitizer
+    (``thread`` or ``address,undefined``).  Returns the executable, or None when the compiler or its
+    sanitizer runtime is missing."""
+    src = HOST / "selftest" / "selftest_main.cpp"
+    LIB.mkdir(exist_ok=True)
+    out = LIB / ("host_selftest_" + sanitizer.split(",")[0])
+    headers = list(HOST.glob("*.h"))
+    if not _newer([src] + headers, out):
+        return out
+    cmd = [os.environ.get("PSB_CXX", "g++"), "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={sanitizer}",
+           "-pthread", str(src), "-o", str(out), "-lz"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stderr[-2000:])
+        return None
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False):
     k = build_kernels(force=force, verbose=verbose)
     h = build_host(force=force)
