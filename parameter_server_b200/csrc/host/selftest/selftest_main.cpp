@@ -18,6 +18,7 @@
 #include <thread>
 #include <vector>
 
+#include "../data.h"
 #include "../kv.h"
 #include "../runtime.h"
 
@@ -52,7 +53,8 @@ struct NodeRt {  // one node of the in-process cluster
 
 }  // namespace
 
-int main() {
+int main(int argc, char** argv) {
+  const bool tcp = argc > 1 && std::strcmp(argv[1], "tcp") == 0;   // loopback TCP van instead of the in-process hub
   const int W = 2, S = 2, kRounds = 40, kThreadsPerWorker = 2;
   auto hub = std::make_shared<InprocHub>();
   std::vector<std::pair<std::string, int>> ids = {{"H", Node::SCHEDULER}, {"W0", Node::WORKER}, {"W1", Node::WORKER},
@@ -65,7 +67,14 @@ int main() {
     n.id = id.first;
     n.hostname = "127.0.0.1";
     auto r = std::make_unique<NodeRt>();
-    r->van = std::make_shared<InprocVan>(hub, n);
+    if (tcp) {
+      auto tv = std::make_shared<TcpVan>(n);
+      CHECK_TRUE(tv->bind().ok());
+      tv->set_compress(true);
+      r->van = tv;
+    } else {
+      r->van = std::make_shared<InprocVan>(hub, n);
+    }
     r->po = std::make_unique<Postoffice>(r->van, W, S);
     if (id.first == "H") sched = r->van->my_node;
     r->po->set_scheduler(sched);
@@ -187,12 +196,37 @@ int main() {
     CHECK_TRUE(done == 64);
   }
 
+  // data ingest: four LIBSVM files parsed by four threads into the slot cache, then served from it
+  if (argc > 2) {
+    const std::string dir = argv[2];
+    std::vector<std::string> files;
+    size_t nnz = 0;
+    for (int f = 0; f < 4; ++f) {
+      files.push_back(dir + "/part-" + std::to_string(f));
+      std::ofstream out(files.back());
+      for (int i = 0; i < 500; ++i) {
+        out << (i % 3 ? "+1" : "-1");
+        for (int k = 0; k < 1 + (i + f) % 7; ++k) { out << " " << (10 * k + f + 1) << ":" << (0.5 + k); ++nnz; }
+        out << "\n";
+      }
+    }
+    for (int round = 0; round < 2; ++round) {
+      SlotReader rd;
+      rd.init(files, TextFormat::LIBSVM, dir + "/cache", true);
+      ExampleInfo info;
+      const int hits = rd.read(4, &info);
+      CHECK_TRUE(hits == (round == 0 ? 0 : 4));
+      CHECK_TRUE(info.num_ex == 2000);
+      CHECK_TRUE(rd.index(1).size() == nnz && rd.value(1).size() == nnz && rd.offset(1).back() == nnz);
+    }
+  }
+
   // shutdown with traffic possibly still queued
   for (auto& id : ids) {
     rt[id.first]->cust->exec()->stop();
     rt[id.first]->po->stop();
   }
   for (auto& id : ids) rt[id.first]->cust.reset();
-  std::printf("selftest: %s\n", g_failed == 0 ? "ok" : "FAILED");
+  std::printf("selftest (%s van): %s\n", tcp ? "tcp" : "in-process", g_failed == 0 ? "ok" : "FAILED");
   return g_failed == 0 ? 0 : 1;
 }

@@ -12,15 +12,16 @@ import pytest
 from parameter_server_b200.utils import build
 
 
+@pytest.mark.parametrize("van", ["inproc", "tcp"])
 @pytest.mark.parametrize("sanitizer", ["thread", "address,undefined"])
-def test_host_runtime_under_sanitizer(sanitizer):
+def test_host_runtime_under_sanitizer(sanitizer, van, tmp_path):
     exe = build.build_host_selftest(sanitizer)
     if exe is None:
         pytest.skip(f"compiler has no -fsanitize={sanitizer}")
     env = dict(os.environ, TSAN_OPTIONS="halt_on_error=0 exitcode=66", ASAN_OPTIONS="detect_leaks=1 exitcode=67",
                UBSAN_OPTIONS="halt_on_error=1 exitcode=68")
-    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
+    r = subprocess.run([str(exe)] + ["tcp" if van == "tcp" else "inproc", str(tmp_path)], capture_output=True, text=True, timeout=300, env=env)
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-4000:]
-    assert "selftest: ok" in out
+    assert "): ok" in out
     assert "ThreadSanitizer" not in out and "AddressSanitizer" not in out and "runtime error" not in out, out[-4000:]
