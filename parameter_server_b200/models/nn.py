@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import math
 import sys
+import zlib
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -128,7 +129,7 @@ class FullyConnectedLayer(Layer):
                 self.model = shared                      # CLONE: the test net shares the training net's model
                 return
             w = init_tensor((self.out_dim, in_dim), self.conf.init if self.conf.has("init") else None, self.net.device,
-                            seed=hash(self.name) % (1 << 30))
+                            seed=zlib.crc32(self.name.encode()) % (1 << 30))   # same weights in every process
             self.model = Parameter(self.name, w, torch.zeros_like(w), None)
             self.net.shared_models[self.name] = self.model
 
