@@ -32,7 +32,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 REFERENCE_UNAVAILABLE = ("reference is a CPU-only C++/ZeroMQ program with a make build and no Python package: "
-                         "pip install of /root/reference fails (no setup.py/pyproject.toml) and its build needs "
+                         "pip install of the reference tree fails (no setup.py/pyproject.toml) and its build needs "
                          "zeromq, gflags, glog, protobuf+protoc, snappy, eigen3, tcmalloc, none present offline")
 
 CLOCK_QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"

@@ -26,7 +26,11 @@ def test_parse_shipped_configs():
     assert d.solver.prior_fea_group == [127, 120] and d.solver.max_block_delay == 8
 
 
-@pytest.mark.parametrize("path", sorted(glob.glob("/root/reference/config/*.conf")))
+# the reference checkout, when present, sits beside this repository (or where PSB_REFERENCE_DIR points)
+REFERENCE = os.environ.get("PSB_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference"))
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(REFERENCE, "config", "*.conf"))))
 def test_reference_job_files_parse_unchanged(path):
     if path.endswith("mpi.conf"):
         pytest.skip("sourced bash file, not an AppConfig")
