@@ -164,3 +164,28 @@ def test_kvvector_aggregate_and_lookup():
     assert (lo, hi, nval) == (0, 4, 2) and vals.tolist() == [1, 10, 5, 50, 5, 50, 0, 0]
     kv.set_values(0, np.array([.2, .4, .6, .8, 1.0]))
     assert kv.lookup(0, np.array([1, 4, 10], dtype=np.uint64)).tolist() == [0.0, 0.4, 1.0]
+
+
+def test_numpy_countmin_restatement_matches_host():
+    """The oracle's NumPy count-min (used by the FTRL / DARLIN tail-filter tests) equals the C++ one."""
+    from baseline.cpu_ref.ftrl_ref import CountMinRef, FTRLRef
+
+    rng = np.random.RandomState(0)
+    keys = rng.randint(0, 2**63, size=2000, dtype=np.int64).astype(np.uint64) * np.uint64(2) + np.uint64(1)
+    cnt = rng.randint(1, 6, size=2000).astype(np.uint32)
+    assert np.array_equal(CountMinRef._hash(keys), np.array([H.CountMin.hash(int(k)) for k in keys], dtype=np.uint64))
+    cm = H.CountMin()
+    cm.resize(4096, 2, True)
+    cm.insert(keys, cnt)
+    ref = CountMinRef(4096, 2)
+    ref.insert(keys, cnt)
+    assert np.array_equal(np.asarray(cm.query(keys)).astype(np.uint64), ref.query(keys))
+    assert np.all(ref.query(keys) >= cnt)                       # one-sided error
+    # the filter keeps a key out of the oracle's model until its estimate passes the threshold
+    f = FTRLRef(0.1, 1.0, 0.0, 0.0, tail_freq=3, countmin_n=1 << 12, countmin_k=2)
+    off = np.array([0, 2, 4], dtype=np.int64)
+    mb = (off, np.array([5, 9, 5, 11], dtype=np.uint64), np.array([1.0, -1.0]))
+    f.step([mb])
+    assert len(f.model) == 0                                    # counts 2, 1, 1: nobody above 3 yet
+    f.step([mb])
+    assert set(f.model) == {5}                                  # key 5 reached 4 > 3
