@@ -1,0 +1,274 @@
+"""Online FTRL on CPU nodes, driven through the control-plane runtime (scheduler, servers, workers).
+
+The multi-process form of the reference's online solver for deployments without GPUs and as the
+protocol-level twin of the GPU engine (``models/ftrl.py``).  Reference roles: ``FTRL::run`` (scheduler
+starts the system, sends UPDATE_MODEL to everybody, saves the model; src/linear_method/ftrl.cc:38-59),
+``FTRL::updateModel`` (worker loop: read a minibatch, count keys, tail filter through the servers'
+count-min sketch, pull the working set, loss + gradient + pos/neg counts, push;
+src/linear_method/ftrl.cc:61-152), ``FTRLModel::setValue / getValue`` (per-key server update with the
+count-based learning rate; src/linear_method/ftrl_model.h:60-112).
+
+Consistency: like the reference, pushes are not waited for (eventual consistency); a worker's pull
+of minibatch t only waits for its own filter round trip.  With one worker the run is deterministic
+and equals the fp64 oracle step by step.
+"""
+from __future__ import annotations
+
+import math
+import sys
+import threading
+import time
+from typing import Dict, List
+
+import numpy as np
+
+from .. import config as cfg
+from ..runtime import host
+from ..runtime.node import NodeContext
+from ..utils.modelio import write_model_text
+from ..utils.pbtext import dumps, parse
+from .linear_cpu import F_INSERT_KEY_FREQ, PULL, PUSH, U64, _call
+
+ALL_KEYS = (0, 2**64 - 1)
+
+
+class FTRLStore:
+    """Server-side state {key -> pos, neg, w, z} in growable arrays (``FTRLModel``'s unordered_map)."""
+
+    def __init__(self, alpha: float, beta: float, lambda1: float, lambda2: float):
+        self.alpha, self.beta, self.l1, self.l2 = alpha, beta, lambda1, lambda2
+        self.index: Dict[int, int] = {}
+        self.n = 0
+        self.pos = np.zeros(1024)
+        self.neg = np.zeros(1024)
+        self.w = np.zeros(1024)
+        self.z = np.zeros(1024)
+        self.keys = np.zeros(1024, dtype=U64)
+
+    def _rows(self, keys: np.ndarray, create: bool) -> np.ndarray:
+        out = np.empty(len(keys), dtype=np.int64)
+        for i, k in enumerate(keys.tolist()):
+            j = self.index.get(k, -1)
+            if j < 0 and create:
+                j = self.n
+                self.index[k] = j
+                self.n += 1
+                if self.n > len(self.w):
+                    grow = len(self.w)
+                    for name in ("pos", "neg", "w", "z"):
+                        setattr(self, name, np.concatenate([getattr(self, name), np.zeros(grow)]))
+                    self.keys = np.concatenate([self.keys, np.zeros(grow, dtype=U64)])
+                self.keys[j] = k
+            out[i] = j
+        return out
+
+    def get(self, keys: np.ndarray) -> np.ndarray:
+        r = self._rows(keys, create=False)
+        return np.where(r >= 0, self.w[np.maximum(r, 0)], 0.0)
+
+    def update(self, keys: np.ndarray, grad: np.ndarray, pos: np.ndarray, neg: np.ndarray) -> None:
+        """FTRLModel::setValue: count-based ‖g‖ estimate sqrt(pos·neg/(pos+neg)), proximal step."""
+        if len(keys) == 0:
+            return
+        r = self._rows(keys, create=True)
+
+        def sqrt_n(p, n):
+            a = p + n
+            return np.where(a > 0, np.sqrt(p * n / np.maximum(a, 1e-300)), 0.0)
+
+        sq = sqrt_n(self.pos[r], self.neg[r])
+        self.pos[r] += pos
+        self.neg[r] += neg
+        sq_new = sqrt_n(self.pos[r], self.neg[r])
+        sigma = (sq_new - sq) / self.alpha
+        self.z[r] += grad - sigma * self.w[r]
+        l2 = self.l2 + (self.beta + sq_new) / self.alpha
+        az = np.abs(self.z[r]) - self.l1
+        self.w[r] = np.where(az > 0, -np.sign(self.z[r]) * az / l2, 0.0)
+
+    def stats(self):
+        w = self.w[: self.n]
+        return float(np.abs(w).sum()), float((w * w).sum()), int(np.count_nonzero(w))
+
+    def nonzero(self):
+        w = self.w[: self.n]
+        nz = w != 0
+        k, v = self.keys[: self.n][nz], w[nz]
+        o = np.argsort(k, kind="stable")
+        return k[o], v[o]
+
+
+class FTRLNode:
+    """Worker or server side of the online solver (one instance per non-scheduler node)."""
+
+    def __init__(self, ctx: NodeContext, app_conf, flags: cfg.Flags):
+        H = host()
+        self.H, self.ctx, self.flags, self.app_conf = H, ctx, flags, app_conf
+        self.conf = app_conf.linear_method
+        lam = list(self.conf.penalty.get("lambda")) + [0.0, 0.0]
+        lr = self.conf.learning_rate
+        self.store = FTRLStore(lr.alpha, lr.beta, lam[0], lam[1])
+        self.filter = H.FrequencyFilter()
+        self.pulled: Dict[int, Dict[str, tuple]] = {}
+        self.lock = threading.Lock()
+        self.param = H.Customer(ctx.po, app_conf.parameter_name[0], self.process_param, True)
+        self.cust = H.Customer(ctx.po, app_conf.app_name, self.process, False)
+        self.examples, self.loss_sum, self.steps = 0, 0.0, 0
+
+    # ---- shared parameter (executor thread of `param`)
+    def process_param(self, msg) -> None:
+        keys = np.frombuffer(msg.key, dtype=U64)
+        if msg.request and msg.cmd == PUSH:
+            if msg.flags & F_INSERT_KEY_FREQ:
+                if self.filter.empty():
+                    s = self.conf.solver
+                    self.filter.resize(max(int(s.countmin_n) // max(self.ctx.num_servers, 1), 64), int(s.countmin_k))
+                self.filter.insert_keys(keys, np.frombuffer(msg.values[0], dtype=np.uint32))
+            else:
+                g, pos, neg = (np.frombuffer(v, dtype=np.float64) for v in msg.values[:3])
+                self.store.update(keys, g, pos, neg)
+        elif msg.request and msg.cmd == PULL:
+            if msg.aux > 0:       # query_key_freq: reply the keys seen more than aux times
+                self.param.reply(msg, key=self.filter.query_keys(keys, msg.aux).tobytes(), values=[b""])
+            else:
+                self.param.reply(msg, values=[self.store.get(keys).tobytes()])
+        elif not msg.request and msg.cmd == PULL:
+            with self.lock:
+                vals = np.frombuffer(msg.values[0], dtype=np.float64) if msg.values else np.zeros(0)
+                self.pulled.setdefault(msg.time, {})[msg.sender] = (keys, vals)
+
+    def _take(self, t: int):
+        with self.lock:
+            parts = self.pulled.pop(t, {})
+        order = self.param.group(self.H.kServerGroup)
+        ks = [parts[s][0] for s in order if s in parts]
+        vs = [parts[s][1] for s in order if s in parts]
+        return (np.concatenate(ks) if ks else np.zeros(0, U64)), (np.concatenate(vs) if vs else np.zeros(0))
+
+    # ---- application calls from the scheduler
+    def process(self, msg) -> None:
+        if not msg.request:
+            return
+        call = parse(msg.payload.decode(), cfg.LMCall)
+        reply = b""
+        if call.cmd == "UPDATE_MODEL":
+            if self.ctx.is_worker:
+                self.update_model()
+        elif call.cmd == "EVALUATE_PROGRESS":
+            reply = self.progress()
+        elif call.cmd == "SAVE_MODEL":
+            self.save_model()
+        self.cust.reply(msg, payload=reply)
+
+    def update_model(self) -> None:
+        """FTRL::updateModel: one pass over this worker's files in minibatches."""
+        H, P, s = self.H, self.param, self.conf.solver
+        td = self.conf.training_data
+        files = H.search_files(list(td.file))
+        if not files:
+            return
+        reader = H.StreamReader()
+        reader.init(files, getattr(H.TextFormat, td.text if td.has("text") else "LIBSVM"), True, bool(self.flags.shuffle_fea_id))
+        mb, freq = int(s.minibatch_size), int(s.tail_feature_freq)
+        ch = 0
+        last_push = None
+        while True:
+            out = reader.read(mb)
+            if out is None:
+                break
+            slots, info = out
+            rows = info["num_ex"]
+            y = np.where(slots[0]["value"] > 0, 1.0, -1.0)
+            sl = slots.get(1)
+            if sl is None or len(sl["index"]) == 0:
+                continue
+            off = sl["offset"].astype(np.int64)
+            idx = sl["index"]
+            val = sl["value"].astype(np.float64) if len(sl["value"]) else np.ones(len(idx))
+            ukeys, inv, cnt = np.unique(idx, return_inverse=True, return_counts=True)
+            ch += 1
+            if freq > 0:      # tail filter: insert this minibatch's key counts, keep the keys above the threshold
+                P.submit(H.kServerGroup, cmd=PUSH, key=ukeys.tobytes(), values=[cnt.astype(np.uint32).tobytes()],
+                         key_range=ALL_KEYS, channel=ch, flags=F_INSERT_KEY_FREQ, wait=True)
+                t = P.submit(H.kServerGroup, cmd=PULL, key=ukeys.tobytes(), key_range=ALL_KEYS, channel=ch, aux=freq,
+                             erase_key_cache=True, wait=True)
+                kept, _ = self._take(t)
+            else:
+                kept = ukeys
+            t = P.submit(H.kServerGroup, cmd=PULL, key=kept.tobytes(), key_range=ALL_KEYS, channel=ch, wait=True)
+            _, wk = self._take(t)
+            if len(wk) != len(kept):
+                wk = np.zeros(len(kept))
+            pos_k = np.searchsorted(kept, ukeys)
+            in_set = (pos_k < len(kept)) & (kept[np.minimum(pos_k, max(len(kept) - 1, 0))] == ukeys) if len(kept) else np.zeros(len(ukeys), bool)
+            w_u = np.where(in_set, wk[np.minimum(pos_k, max(len(kept) - 1, 0))] if len(kept) else 0.0, 0.0)
+            row_of = np.repeat(np.arange(rows), np.diff(off))
+            xw = np.bincount(row_of, weights=w_u[inv] * val, minlength=rows)
+            m = y * xw
+            self.loss_sum += float(np.sum(np.logaddexp(0.0, -m)))
+            self.examples += rows
+            self.steps += 1
+            coef = -y / (1.0 + np.exp(m))
+            g = np.bincount(inv, weights=coef[row_of] * val, minlength=len(ukeys))
+            pos = np.bincount(inv, weights=(y[row_of] > 0).astype(np.float64), minlength=len(ukeys))
+            neg = np.bincount(inv, weights=(y[row_of] <= 0).astype(np.float64), minlength=len(ukeys))
+            last_push = P.submit(H.kServerGroup, cmd=PUSH, key=ukeys[in_set].tobytes(),
+                                 values=[g[in_set].tobytes(), pos[in_set].tobytes(), neg[in_set].tobytes()],
+                                 key_range=ALL_KEYS, channel=ch, erase_key_cache=True)
+        # pushes are not waited for while training; before reporting back, the last one must have been applied
+        # (a server handles one sender's messages in order, so that covers the earlier ones too)
+        if last_push is not None:
+            P.wait_out(H.kServerGroup, last_push)
+
+    def progress(self) -> bytes:
+        n1, n2, nnz = self.store.stats() if self.ctx.is_server else (0.0, 0.0, 0)
+        lam = list(self.conf.penalty.get("lambda")) + [0.0, 0.0]
+        p = cfg.Progress(objv=self.loss_sum + lam[0] * n1 + 0.5 * lam[1] * math.sqrt(max(n2, 0.0)), nnz_w=nnz,
+                         num_ex_trained=self.examples)
+        return dumps(p, oneline=True).encode()
+
+    def save_model(self) -> None:
+        mo = self.conf.model_output
+        if self.ctx.is_server and mo.file:
+            k, v = self.store.nonzero()
+            write_model_text(f"{mo.file[0]}_{self.ctx.node_id}", k, v)
+
+    def stop(self) -> None:
+        self.cust.stop()
+        self.param.stop()
+
+
+class FTRLScheduler:
+    """Scheduler side: ``FTRL::run``."""
+
+    def __init__(self, ctx: NodeContext, app_conf, flags: cfg.Flags):
+        H = host()
+        self.H, self.ctx, self.flags, self.app_conf = H, ctx, flags, app_conf
+        self.param = H.Customer(ctx.po, app_conf.parameter_name[0], None, True)
+        self.cust = H.Customer(ctx.po, app_conf.app_name, None, False)
+        self.progress: List[dict] = []
+
+    def run(self, verbose: bool = True) -> List[dict]:
+        H = self.H
+        t0 = time.time()
+        t = self.cust.submit(H.kWorkerGroup, payload=_call("UPDATE_MODEL"))
+        self.cust.wait_out(H.kWorkerGroup, t)            # workers return when their data is exhausted and applied
+        t = self.cust.submit(H.kActiveGroup, payload=_call("EVALUATE_PROGRESS"))
+        self.cust.wait_out(H.kActiveGroup, t)
+        objv, nnz_w, examples = 0.0, 0, 0
+        for text in self.cust.take_replies(t).values():
+            p = parse(text.decode(), cfg.Progress)
+            objv += p.objv
+            nnz_w += p.nnz_w
+            examples += p.num_ex_trained
+        rec = dict(objv=objv, nnz_w=nnz_w, examples=examples, seconds=time.time() - t0)
+        self.progress.append(rec)
+        if verbose:
+            print("%10d examples, objective %.5e, |w|_0 %8d, %.2f s" % (examples, objv, nnz_w, rec["seconds"]), file=sys.stderr)
+        t = self.cust.submit(H.kActiveGroup, payload=_call("SAVE_MODEL"))
+        self.cust.wait_out(H.kActiveGroup, t)
+        return self.progress
+
+    def stop(self) -> None:
+        self.cust.stop()
+        self.param.stop()

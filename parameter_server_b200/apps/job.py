@@ -27,7 +27,11 @@ def make_app(ctx: NodeContext, app_conf, flags: cfg.Flags):
         from .linear_cpu import BatchScheduler, LinearMethodNode
 
         return BatchScheduler(ctx, app_conf, flags) if ctx.is_scheduler else LinearMethodNode(ctx, app_conf, flags)
-    raise ValueError("online solvers run on the GPU engine (models.ftrl)")
+    if not lm.has("ftrl"):
+        raise ValueError("online solver requested (solver.minibatch_size > 0) but no ftrl{} section")
+    from .ftrl_cpu import FTRLNode, FTRLScheduler
+
+    return FTRLScheduler(ctx, app_conf, flags) if ctx.is_scheduler else FTRLNode(ctx, app_conf, flags)
 
 
 def run_node(rank: int, flags: cfg.Flags, hub=None, app_text: Optional[str] = None, verbose: bool = True):
