@@ -217,11 +217,27 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
     losses = []
     seen = 0
     last = time.time()
+    # checkpoint / resume: the shard tables are saved every checkpoint_interval minibatches; a restarted job
+    # reloads the newest step all ranks have and skips the minibatches that were applied before it
+    ckdir, ckint = flags.checkpoint_dir, int(flags.checkpoint_interval)
+    start_step, step = 0, 0
+    if ckdir:
+        from ..utils.checkpoint import load_ftrl, save_ftrl
+
+        start_step = max(load_ftrl(eng, ckdir), 0)
+        if start_step and group.rank == 0:
+            print(f"resuming after minibatch {start_step} from {ckdir}", file=sys.stderr)
     for hb in batches():
+        step += 1
+        if step <= start_step:
+            seen += hb.y.numel()
+            continue
         if hb.vals is None:
             hb.vals = torch.ones(hb.keys.numel()).pin_memory() if hb.keys.numel() else torch.zeros(0)
         losses += trainer_with_vals.train([hb])
         seen += hb.y.numel()
+        if ckdir and ckint > 0 and step % ckint == 0:
+            save_ftrl(eng, ckdir, step)
         if group.rank == 0 and time.time() - last >= s.eval_interval:
             st = eng.read_stats(reset=False)
             print("%10d examples, loss %.5e, penalty %.5e, |w|_0 %8d" % (seen * group.world, losses[-1], eng.penalty(st), int(st["nnz_w"])))

@@ -96,3 +96,34 @@ def test_ftrl_job_from_adfea_text(tmp_path):
     assert out["examples"] == 6000 and out["mean_logloss_last"] < 0.69 and out["nnz_w"] > 50
     model = read_model_text(out["model"])
     assert len(model) == out["nnz_w"] and all((k - 11) % 7919 == 0 for k in model)
+
+
+def test_ftrl_job_checkpoint_resume(tmp_path):
+    """A restarted online job reloads the newest checkpoint, skips the minibatches applied before it and
+    ends in the model of the uninterrupted run."""
+    rng = np.random.RandomState(1)
+    w = {k: rng.randn() for k in range(200)}
+    (tmp_path / "ctr").mkdir()
+    lines = []
+    for i in range(4000):
+        ks = rng.choice(200, size=6, replace=False)
+        p = 1 / (1 + np.exp(-(sum(w[k] for k in ks) * 0.8)))
+        lines.append(f"{i} 1 {int(rng.rand() < p)} " + " ".join(f"{k * 7919 + 11}:1" for k in ks))
+    (tmp_path / "ctr" / "part-0").write_text("\n".join(lines) + "\n")
+    text = f'''app_name: "ctr" parameter_name: "ctr_w"
+      linear_method {{ training_data {{ format: TEXT text: ADFEA file: "{tmp_path}/ctr/part-.*" ignore_feature_group: true }}
+        model_output {{ format: TEXT file: "{tmp_path}/ftrl" }} loss {{ type: LOGIT }}
+        penalty {{ type: L1 lambda: 0.01 lambda: 0.01 }} learning_rate {{ type: CONSTANT alpha: 0.1 beta: 1 }}
+        solver {{ minibatch_size: 500 countmin_n: 100000 tail_feature_freq: 2 eval_interval: 1000 }} ftrl {{ }} }}'''
+    ck = tmp_path / "ck"
+    full = _run(tmp_path, text, checkpoint_dir=str(ck), checkpoint_interval=3)
+    model_full = read_model_text(full["model"])
+    steps = sorted(int(n.split("step")[1][:-3]) for n in os.listdir(ck))
+    assert steps == [3, 6]                                   # 8 minibatches, a checkpoint every 3
+    os.remove(ck / "ftrl_rank0_step6.pt")                    # "crash" after minibatch 3..5: resume from step 3
+    again = _run(tmp_path, text, checkpoint_dir=str(ck), checkpoint_interval=3)
+    model_again = read_model_text(again["model"])
+    common = set(model_again) & set(model_full)                # float atomics: a weight at the L1 threshold may flip to 0
+    assert again["examples"] == 4000 and len(model_full) > 20 and len(common) >= 0.97 * max(len(model_full), len(model_again))
+    for k in common:
+        assert model_again[k] == pytest.approx(model_full[k], rel=2e-3, abs=1e-5)
