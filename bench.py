@@ -203,14 +203,30 @@ def run_darlin(args):
     dev, rank, world = group.device, group.rank, group.world
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    rows_total, cols = args.darlin_rows, 47236
-    r0, r1 = rows_total * rank // world, rows_total * (rank + 1) // world
-    # every rank generates the same matrix chunk-wise and keeps its rows (no file system, no network)
-    off, idx, vals, y, _ = zipf_sparse_matrix(r1 - r0, cols, 90, seed=17 + rank, device=dev, zipf_s=1.0, wstar_frac=0.02, noise=0.3,
-                                             wstar_seed=4242)
-    cfg = DarlinConfig(lambda1=1.0, eta=1.0, delta_init=5.0, delta_max=10.0, kkt_ratio=100.0, max_pass=args.steps,
-                       epsilon=0.0, feature_block_ratio=4.0, random_block_order=True, seed=0,
-                       max_block_delay=args.block_delay)
+    ooc_shape = args.config == "ooc"
+    if ooc_shape:
+        # the out-of-core configuration, scaled to --ooc-rows rows per GPU (weak scaling): ~120 binary features per
+        # row, hashed uint64 keys over a 2^32 key space drawn Zipf(1.05), labels Bernoulli(sigmoid(X.w*)) from a
+        # planted 0.5 % w*, lambda1 = 4, 64 feature blocks, KKT filter ratio 10
+        from parameter_server_b200.data.synthetic import ctr_minibatch
+
+        rows_total, cols = args.ooc_rows * world, 1 << 32
+        off, idx, y = ctr_minibatch(args.ooc_rows, seed=31 + rank, device=dev, key_space_log2=32, zipf_s=1.05, groups=12,
+                                    feats_lo=8, feats_hi=12, bias=0.0, wstar_frac=0.005, wstar_std=1.0)
+        vals = None
+        per_row = idx.numel() / max(args.ooc_rows, 1)
+        cfg = DarlinConfig(lambda1=4.0, eta=1.0, delta_init=1.0, delta_max=5.0, kkt_ratio=10.0, max_pass=args.steps,
+                           epsilon=0.0, feature_block_ratio=63.5 / per_row, random_block_order=True, seed=0,
+                           max_block_delay=args.block_delay)
+    else:
+        rows_total, cols = args.darlin_rows, 47236
+        r0, r1 = rows_total * rank // world, rows_total * (rank + 1) // world
+        # every rank generates the same matrix chunk-wise and keeps its rows (no file system, no network)
+        off, idx, vals, y, _ = zipf_sparse_matrix(r1 - r0, cols, 90, seed=17 + rank, device=dev, zipf_s=1.0, wstar_frac=0.02,
+                                                 noise=0.3, wstar_seed=4242)
+        cfg = DarlinConfig(lambda1=1.0, eta=1.0, delta_init=5.0, delta_max=10.0, kkt_ratio=100.0, max_pass=args.steps,
+                           epsilon=0.0, feature_block_ratio=4.0, random_block_order=True, seed=0,
+                           max_block_delay=args.block_delay)
     impl = "nccl" if args.impl == "nccl" else "fused"
 
     def timed(sol, with_eval):
@@ -261,14 +277,19 @@ def run_darlin(args):
         "metric": "examples/sec (L1-LR, DARLIN block coordinate descent, one pass = one step)",
         "value": rows_total * args.steps / (ms / 1e3), "unit": "examples/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak" if ooc_shape else "strong", "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic",
         "impl": "nccl-baseline" if impl == "nccl" else "fused",
-        "config": {"model": "L1 logistic regression, DARLIN, lambda1=1, feature_block_ratio=4, delta 5/10, KKT ratio 100",
+        "config": {"model": ("out-of-core L1 logistic regression, DARLIN over 64 feature blocks, lambda1=4, KKT ratio 10, binary "
+                             "features, uint64 keys over 2^32 Zipf(1.05); e2e streams every block from pinned host memory")
+                            if ooc_shape else
+                            "L1 logistic regression, DARLIN, lambda1=1, feature_block_ratio=4, delta 5/10, KKT ratio 100",
                    "global_batch": rows_total, "seq_len": None, "rows": rows_total, "features": cols,
                    "max_block_delay": args.block_delay,
                    "nnz_per_row": nnz_total / rows_total, "feature_blocks": nblk,
                    "parallelism": f"dp{world} rows x key-range shards {world} (worker+server per GPU)",
-                   "l2_policy": f"inputs larger than L2: {nnz_total * 8 >> 20} MiB of CSC row ids and values read per pass",
+                   "l2_policy": f"inputs larger than L2: {nnz_total * (4 if vals is None else 8) >> 20} MiB of CSC row ids"
+                                f"{'' if vals is None else ' and values'} read per pass",
                    "objective_after_timed_passes": objv, "nnz_w": nnz_w, "active_keys": nnz_as},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
     }, rank
@@ -276,9 +297,11 @@ def run_darlin(args):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="ftrl", choices=["ftrl", "darlin"],
-                    help="ftrl: CTR-scale online FTRL (headline); darlin: batch L1-LR by block coordinate descent")
+    ap.add_argument("--config", default="ftrl", choices=["ftrl", "darlin", "ooc"],
+                    help="ftrl: CTR-scale online FTRL (headline); darlin: batch L1-LR by block coordinate descent; "
+                         "ooc: the out-of-core batch configuration (64 blocks, binary hashed features), scaled by --ooc-rows")
     ap.add_argument("--darlin-rows", type=int, default=677399)
+    ap.add_argument("--ooc-rows", type=int, default=1000000, help="rows per GPU of the out-of-core configuration")
     ap.add_argument("--block-delay", type=int, default=0,
                     help="DARLIN bounded delay tau (max_block_delay): tau+1 blocks share their synchronisation points")
     ap.add_argument("--gpus", type=int, default=1)
@@ -303,7 +326,7 @@ def main() -> None:
         return
     if args.warmup < 3:
         args.warmup = 3
-    result, rank = run_darlin(args) if args.config == "darlin" else run_ftrl(args)
+    result, rank = run_darlin(args) if args.config in ("darlin", "ooc") else run_ftrl(args)
     if rank == 0:
         print(json.dumps(result))
     try:
