@@ -176,6 +176,23 @@ __device__ __forceinline__ int64_t find_col(const int64_t* col_ptr, int64_t lo, 
   return lo;
 }
 
+// Column of CSC position e when the lanes of a warp hold consecutive positions (e = base + lane) and no
+// per-nnz column array is kept (out-of-core mode): one binary search per warp (lane 0, always valid), then
+// every lane walks forward over the few column boundaries inside the warp's 32 positions.  A binary search
+// per non-zero costs ~log2(columns of the block) dependent loads; with 485 k columns per block it made the
+// streamed pass twice as slow as the resident one.  Must be called by all 32 lanes.
+__device__ __forceinline__ int64_t find_col_warp(const int64_t* col_ptr, int64_t lo, int64_t hi, int64_t e, bool valid) {
+  const int64_t e0 = __shfl_sync(0xffffffffu, e, 0);
+  int64_t j = (threadIdx.x & 31) == 0 ? find_col(col_ptr, lo, hi, e0) : 0;
+  j = __shfl_sync(0xffffffffu, j, 0);
+  if (valid) {
+    for (int steps = 0; j + 1 < hi && col_ptr[j + 1] <= e; ++j) {
+      if (++steps > 48) { j = find_col(col_ptr, j, hi, e); break; }   // many empty columns: finish by bisection
+    }
+  }
+  return j;
+}
+
 // ---- phase A: block gradient (G,U) pushed into the owners' accumulators
 __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
                                                  int64_t lc1, size_t gwarp, size_t nwarps, int lane) {
@@ -184,10 +201,12 @@ __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const D
   for (int64_t base = p0 + (int64_t)gwarp * 32; base < p1; base += (int64_t)nwarps * 32) {
     const int64_t e = base + lane;
     const bool valid = e < p1;
+    // the warp-level search is collective: every lane takes part, valid or not
+    const int64_t jc = Wk.col_of ? (valid ? (int64_t)Wk.col_of[e] : -1) : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
     int64_t j = -1;
     float g = 0.f, u = 0.f;
     if (valid) {
-      j = Wk.col_of ? (int64_t)Wk.col_of[e] : find_col(Wk.col_ptr, lc0, lc1, e);
+      j = jc;
       if (Wk.active[j]) {
         const float2 ym = Wk.ym[Wk.row_idx[e]];
         const float yi = ym.x;
@@ -302,11 +321,15 @@ __device__ __forceinline__ void darlin_update_margin(const DarlinWorker& Wk, int
 __device__ __forceinline__ void darlin_pull_margin(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
                                                    int64_t lc1, size_t gtid, size_t gsz) {
   const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
-  for (int64_t e = p0 + (int64_t)gtid; e < p1; e += (int64_t)gsz) {
-    const int64_t j = Wk.col_of ? (int64_t)Wk.col_of[e] : find_col(Wk.col_ptr, lc0, lc1, e);
-    if (!Wk.active[j]) continue;
+  const int lane = threadIdx.x & 31;
+  // warp-uniform trip count (gsz is a multiple of 32): the column search without col_of is a warp collective
+  for (int64_t base = p0 + (int64_t)gtid - lane; base < p1; base += (int64_t)gsz) {
+    const int64_t e = base + lane;
+    const bool valid = e < p1;
+    const int64_t j = Wk.col_of ? (valid ? (int64_t)Wk.col_of[e] : -1) : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
+    if (!valid || !Wk.active[j]) continue;
     const float* wsrc = P.w[Wk.gowner[j]] + Wk.gslot[j];
-      const float wn = P.world > 1 ? ld_relaxed_sys_f32(wsrc) : ld_relaxed_gpu_f32(wsrc);
+    const float wn = P.world > 1 ? ld_relaxed_sys_f32(wsrc) : ld_relaxed_gpu_f32(wsrc);
     const float d = wn - Wk.w[j];
     if (wn == wn && d != 0.f) {
       const uint32_t i = Wk.row_idx[e];

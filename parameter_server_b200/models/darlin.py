@@ -84,17 +84,19 @@ class DarlinSolver:
     """Worker + server of one rank; ``preprocess`` once, then ``run`` (or ``run_pass`` repeatedly)."""
 
     def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused",
-                 out_of_core: bool = False, prefetch_depth: int = 3, blocks_per_launch: int = 16):
+                 out_of_core: bool = False, prefetch_depth: int = 3, blocks_per_launch: Optional[int] = None):
         """``out_of_core``: keep the column blocks (row ids, values) in pinned host memory and stream each
         block to the GPU on a side stream ahead of its turn in the block order — the role of the
         reference's ``FeatureStation`` in ``-mmap_training_data`` mode with its task-id keyed look-ahead
         prefetch (src/linear_method/feature_station.cc:212-279, src/linear_method/darling.cc:175-201)."""
         self.group, self.cfg, self.impl = group, cfg, impl
         self.out_of_core, self.prefetch_depth = out_of_core, max(int(prefetch_depth), 2)
-        # out-of-core mode: blocks per kernel launch (a launch costs about as much as a block); rounded up to a
-        # multiple of max_block_delay + 1
-        grp = max(int(cfg.max_block_delay), 0) + 1
-        self.blocks_per_launch = (max(int(blocks_per_launch), 1) + grp - 1) // grp * grp
+        # out-of-core mode: blocks per kernel launch, rounded up to a multiple of max_block_delay + 1.  A launch
+        # costs about 28 us, so small blocks are batched (up to 16); a batch is also the unit that must be on the
+        # device before its kernel starts, so it is kept near 24 MB (chosen in _to_host_blocks when not given)
+        self._launch_group = max(int(cfg.max_block_delay), 0) + 1
+        self._blocks_per_launch_arg = blocks_per_launch
+        self.blocks_per_launch = self._round_launch(16 if blocks_per_launch is None else blocks_per_launch)
         self.h2d_bytes = 0
         self.dev = group.device
         self.timeout_s = timeout_s
@@ -291,6 +293,9 @@ class DarlinSolver:
             if has_vals:
                 self.h_pack[words * p0 + n: words * p1] = vals_h[p0:p1]
         cap = max(int((self.blk_nnz[:, 1] - self.blk_nnz[:, 0]).max()) if len(self.blk_nnz) else 1, 1)
+        if self._blocks_per_launch_arg is None and len(self.blk_nnz):
+            avg_bytes = max(float((self.blk_nnz[:, 1] - self.blk_nnz[:, 0]).mean()) * 4 * words, 1.0)
+            self.blocks_per_launch = self._round_launch(min(16, max(1, int(24e6 // avg_bytes))))
         d = min(self.prefetch_depth, 16)
         # a ring slot holds one launch's worth of blocks; stage_base gets every block's address for the kernel
         self.stage = [torch.empty(cap * words * self.blocks_per_launch, dtype=torch.int32, device=self.dev)
@@ -304,6 +309,10 @@ class DarlinSolver:
             raise RuntimeError("could not create the block streamer (copy stream / events)")
         self.row_idx = self.stage[0]                          # placeholders for the struct; replaced per block
         self.vals = self.stage[0].view(torch.float32) if has_vals else None
+
+    def _round_launch(self, n: int) -> int:
+        g = self._launch_group
+        return (max(int(n), 1) + g - 1) // g * g
 
     def __del__(self):
         st = getattr(self, "_streamer", None)
