@@ -250,7 +250,10 @@ class DarlinSolver:
         self.margin = self.ym[:, 1]
         # column id of every non-zero (saves a binary search per non-zero and phase); not kept in out-of-core
         # mode, where it would add 50 % to the bytes streamed from the host
-        self.col_of = None if self.out_of_core else torch.repeat_interleave(
+        # (PSB_DARLIN_NO_COL_OF=1 drops it for resident data too: isolates the cost of the in-kernel column search)
+        import os
+
+        self.col_of = None if self.out_of_core or os.environ.get("PSB_DARLIN_NO_COL_OF") == "1" else torch.repeat_interleave(
             torch.arange(P, dtype=torch.int32, device=dev), col_ptr[1:] - col_ptr[:-1]).contiguous()
         self.w = torch.zeros(P, dtype=f32, device=dev)
         self.delta = torch.full((P,), self.cfg.delta_init, dtype=f32, device=dev)
