@@ -172,6 +172,7 @@ class FTRLNode:
         mb, freq = int(s.minibatch_size), int(s.tail_feature_freq)
         ch = 0
         last_push = None
+        last_report, reported = time.time(), [0.0, 0]
         while True:
             out = reader.read(mb)
             if out is None:
@@ -215,6 +216,12 @@ class FTRLNode:
             last_push = P.submit(H.kServerGroup, cmd=PUSH, key=ukeys[in_set].tobytes(),
                                  values=[g[in_set].tobytes(), pos[in_set].tobytes(), neg[in_set].tobytes()],
                                  key_range=ALL_KEYS, channel=ch, erase_key_cache=True)
+            # periodic progress report to the scheduler (FTRL::evalProgress / showProgress, ftrl.cc:184-219)
+            if time.time() - last_report >= float(s.eval_interval):
+                last_report = time.time()
+                rep = cfg.Progress(objv=self.loss_sum - reported[0], num_ex_trained=self.examples - reported[1])
+                reported = [self.loss_sum, self.examples]
+                self.cust.submit("H", payload=_call("REPORT_PROGRESS", progress=rep))   # "H" = the scheduler's node id
         # pushes are not waited for while training; before reporting back, the last one must have been applied
         # (a server handles one sender's messages in order, so that covers the earlier ones too)
         if last_push is not None:
@@ -245,11 +252,30 @@ class FTRLScheduler:
         H = host()
         self.H, self.ctx, self.flags, self.app_conf = H, ctx, flags, app_conf
         self.param = H.Customer(ctx.po, app_conf.parameter_name[0], None, True)
-        self.cust = H.Customer(ctx.po, app_conf.app_name, None, False)
+        self.verbose = True
+        self.reports: List[dict] = []          # periodic worker reports, in arrival order
+        self._seen, self._loss = 0, 0.0
+        self.cust = H.Customer(ctx.po, app_conf.app_name, self.process, False)
         self.progress: List[dict] = []
+
+    def process(self, msg) -> None:
+        """Workers' REPORT_PROGRESS calls: running totals and the mean loss since the previous report."""
+        if not msg.request or not msg.payload:
+            return
+        call = parse(msg.payload.decode(), cfg.LMCall)
+        if call.cmd != "REPORT_PROGRESS":
+            return
+        p = call.progress
+        self._seen += p.num_ex_trained
+        self._loss += p.objv
+        rec = dict(worker=msg.sender, examples=self._seen, mean_loss=p.objv / max(p.num_ex_trained, 1))
+        self.reports.append(rec)
+        if self.verbose:
+            print("%10d examples, loss %.5e (%s)" % (rec["examples"], rec["mean_loss"], rec["worker"]), file=sys.stderr)
 
     def run(self, verbose: bool = True) -> List[dict]:
         H = self.H
+        self.verbose = verbose
         t0 = time.time()
         t = self.cust.submit(H.kWorkerGroup, payload=_call("UPDATE_MODEL"))
         self.cust.wait_out(H.kWorkerGroup, t)            # workers return when their data is exhausted and applied
@@ -261,7 +287,7 @@ class FTRLScheduler:
             objv += p.objv
             nnz_w += p.nnz_w
             examples += p.num_ex_trained
-        rec = dict(objv=objv, nnz_w=nnz_w, examples=examples, seconds=time.time() - t0)
+        rec = dict(objv=objv, nnz_w=nnz_w, examples=examples, seconds=time.time() - t0, reports=list(self.reports))
         self.progress.append(rec)
         if verbose:
             print("%10d examples, objective %.5e, |w|_0 %8d, %.2f s" % (examples, objv, nnz_w, rec["seconds"]), file=sys.stderr)

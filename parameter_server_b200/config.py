@@ -88,7 +88,8 @@ Progress = Schema("LM.Progress", F("objv", "double"), F("relative_objv", "double
 LMCommand = Enum("LM.Call.Command", LOAD_DATA=1, PREPROCESS_DATA=2, UPDATE_MODEL=3, EVALUATE_PROGRESS=4, SAVE_MODEL=5,
                  RECOVER=6, COMPUTE_VALIDATION_AUC=7, REPORT_PROGRESS=8)
 LMCall = Schema("LM.Call", F("cmd", LMCommand, "required"), F("key", PbRange), F("kkt_filter_threshold", "double"),
-                F("kkt_filter_reset", "bool"), F("fea_grp", "int32", "repeated"), F("hit_cache", "bool"))
+                F("kkt_filter_reset", "bool"), F("fea_grp", "int32", "repeated"), F("hit_cache", "bool"),
+                F("progress", Progress))   # REPORT_PROGRESS carries the worker's increment
 
 # ---------------------------------------------------------------- neural_network.proto
 LayerType = Enum("LayerConfig.Type", NONE=0, FULLY_CONNECTED=1, DATA=2, LOGISTIC_LOSS=3, AUC=4)

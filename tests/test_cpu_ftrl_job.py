@@ -23,7 +23,7 @@ linear_method {{
   loss {{ type: LOGIT }}
   penalty {{ type: L1 lambda: 0.05 lambda: 0.1 }}
   learning_rate {{ type: CONSTANT alpha: 0.05 beta: 1 }}
-  solver {{ minibatch_size: {mb} tail_feature_freq: {tail} countmin_n: 8192 countmin_k: 2 }}
+  solver {{ minibatch_size: {mb} tail_feature_freq: {tail} countmin_n: 8192 countmin_k: 2 eval_interval: 0 }}
   ftrl {{ }}
 }}
 '''
@@ -71,6 +71,9 @@ def test_two_workers_learn(tmp_path):
     flags = cfg.Flags(num_workers=2, num_servers=2, seed=0)
     prog = run_local_threads(flags, CONF.format(train=tmp_path / "train", out=tmp_path, mb=100, tail=0))
     assert prog[0]["examples"] == rows and prog[0]["nnz_w"] > 10
+    # eval_interval 0: every minibatch is reported to the scheduler (2 workers x 10 minibatches of 100 rows)
+    reps = prog[0]["reports"]
+    assert len(reps) == 20 and {r["worker"] for r in reps} == {"W0", "W1"} and reps[-1]["examples"] == rows
     # mean logistic loss over the stream must beat the constant predictor (log 2)
     model = {}
     for s in ("S0", "S1"):
