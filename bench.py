@@ -322,7 +322,8 @@ def main() -> None:
     ap.add_argument("--timeout-s", type=float, default=5.0, help="limit of in-kernel cross-GPU waits")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        if int(os.environ.get("RANK", "0")) == 0:       # one line per job, also under torch.distributed.run
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return
     if args.warmup < 3:
         args.warmup = 3
