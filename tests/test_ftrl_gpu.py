@@ -129,3 +129,4 @@ def test_model_text_dump(tmp_path):
     assert len(m) == len(k)
     for kk, ww in zip(k[:50], w[:50]):
         assert m[int(kk)] == pytest.approx(float(ww), rel=1e-5)
+
