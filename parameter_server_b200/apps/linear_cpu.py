@@ -18,7 +18,7 @@ import math
 import sys
 import threading
 import time
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import numpy as np
 import scipy.sparse as sp

@@ -15,7 +15,7 @@ from __future__ import annotations
 import math
 import sys
 import time
-from typing import List, Optional
+from typing import List
 
 import numpy as np
 import torch

@@ -20,13 +20,12 @@ from __future__ import annotations
 import math
 import sys
 import zlib
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 import numpy as np
 import torch
 
-from .. import config as cfg
 from ..ops import dense
 from ..parallel.peer import PeerGroup
 from ..runtime import host

@@ -10,7 +10,7 @@ same rows with ``all_to_all_single`` and is the comparison baseline.
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Optional, Tuple
+from typing import Optional, Tuple
 
 import torch
 

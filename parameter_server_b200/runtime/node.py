@@ -6,10 +6,8 @@ stand-by ``U*``.  The scheduler's address comes from ``-scheduler`` (a text-form
 """
 from __future__ import annotations
 
-import json
 import time
 from dataclasses import dataclass
-from typing import Optional
 
 from . import host
 from .. import config as cfg

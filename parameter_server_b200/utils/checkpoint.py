@@ -10,7 +10,6 @@ order of every pass is a function of (seed, pass), so it needs no saving.
 """
 from __future__ import annotations
 
-import json
 import os
 import sys
 from typing import List
