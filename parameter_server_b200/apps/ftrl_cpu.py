@@ -32,72 +32,6 @@ from .linear_cpu import F_INSERT_KEY_FREQ, PULL, PUSH, U64, _call
 ALL_KEYS = (0, 2**64 - 1)
 
 
-class FTRLStore:
-    """Server-side state {key -> pos, neg, w, z} in growable arrays (``FTRLModel``'s unordered_map)."""
-
-    def __init__(self, alpha: float, beta: float, lambda1: float, lambda2: float):
-        self.alpha, self.beta, self.l1, self.l2 = alpha, beta, lambda1, lambda2
-        self.index: Dict[int, int] = {}
-        self.n = 0
-        self.pos = np.zeros(1024)
-        self.neg = np.zeros(1024)
-        self.w = np.zeros(1024)
-        self.z = np.zeros(1024)
-        self.keys = np.zeros(1024, dtype=U64)
-
-    def _rows(self, keys: np.ndarray, create: bool) -> np.ndarray:
-        out = np.empty(len(keys), dtype=np.int64)
-        for i, k in enumerate(keys.tolist()):
-            j = self.index.get(k, -1)
-            if j < 0 and create:
-                j = self.n
-                self.index[k] = j
-                self.n += 1
-                if self.n > len(self.w):
-                    grow = len(self.w)
-                    for name in ("pos", "neg", "w", "z"):
-                        setattr(self, name, np.concatenate([getattr(self, name), np.zeros(grow)]))
-                    self.keys = np.concatenate([self.keys, np.zeros(grow, dtype=U64)])
-                self.keys[j] = k
-            out[i] = j
-        return out
-
-    def get(self, keys: np.ndarray) -> np.ndarray:
-        r = self._rows(keys, create=False)
-        return np.where(r >= 0, self.w[np.maximum(r, 0)], 0.0)
-
-    def update(self, keys: np.ndarray, grad: np.ndarray, pos: np.ndarray, neg: np.ndarray) -> None:
-        """FTRLModel::setValue: count-based ‖g‖ estimate sqrt(pos·neg/(pos+neg)), proximal step."""
-        if len(keys) == 0:
-            return
-        r = self._rows(keys, create=True)
-
-        def sqrt_n(p, n):
-            a = p + n
-            return np.where(a > 0, np.sqrt(p * n / np.maximum(a, 1e-300)), 0.0)
-
-        sq = sqrt_n(self.pos[r], self.neg[r])
-        self.pos[r] += pos
-        self.neg[r] += neg
-        sq_new = sqrt_n(self.pos[r], self.neg[r])
-        sigma = (sq_new - sq) / self.alpha
-        self.z[r] += grad - sigma * self.w[r]
-        l2 = self.l2 + (self.beta + sq_new) / self.alpha
-        az = np.abs(self.z[r]) - self.l1
-        self.w[r] = np.where(az > 0, -np.sign(self.z[r]) * az / l2, 0.0)
-
-    def stats(self):
-        w = self.w[: self.n]
-        return float(np.abs(w).sum()), float((w * w).sum()), int(np.count_nonzero(w))
-
-    def nonzero(self):
-        w = self.w[: self.n]
-        nz = w != 0
-        k, v = self.keys[: self.n][nz], w[nz]
-        o = np.argsort(k, kind="stable")
-        return k[o], v[o]
-
-
 class FTRLNode:
     """Worker or server side of the online solver (one instance per non-scheduler node)."""
 
@@ -107,7 +41,7 @@ class FTRLNode:
         self.conf = app_conf.linear_method
         lam = list(self.conf.penalty.get("lambda")) + [0.0, 0.0]
         lr = self.conf.learning_rate
-        self.store = FTRLStore(lr.alpha, lr.beta, lam[0], lam[1])
+        self.store = H.FTRLModel(lr.alpha, lr.beta, lam[0], lam[1])   # native key -> {pos, neg, w, z} map (csrc/host/kv.h)
         self.filter = H.FrequencyFilter()
         self.pulled: Dict[int, Dict[str, tuple]] = {}
         self.lock = threading.Lock()

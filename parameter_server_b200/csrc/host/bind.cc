@@ -182,6 +182,20 @@ PYBIND11_MODULE(_psb_host, m) {
         return py::make_tuple(tk, tc, fk, fc);
       })
       .def("clear", &AUC::clear).def("evaluate", &AUC::evaluate).def("accuracy", &AUC::accuracy, py::arg("threshold") = 0.0);
+  py::class_<FTRLModel>(m, "FTRLModel")
+      .def(py::init<double, double, double, double>(), py::arg("alpha"), py::arg("beta"), py::arg("lambda1"), py::arg("lambda2"))
+      .def("update", [](FTRLModel& f, carray<uint64_t> k, carray<double> g, carray<double> pos, carray<double> neg) {
+        if (g.size() != k.size() || pos.size() != k.size() || neg.size() != k.size()) throw std::invalid_argument("FTRLModel.update: array sizes differ");
+        f.update(k.data(), (size_t)k.size(), g.data(), pos.data(), neg.data());
+      })
+      .def("get", [](const FTRLModel& f, carray<uint64_t> k) { return to_array(f.get(k.data(), (size_t)k.size())); })
+      .def("stats", [](const FTRLModel& f) { return py::make_tuple(f.norm1(), f.norm2(), f.nnz()); })
+      .def("size", &FTRLModel::size)
+      .def("nonzero", [](const FTRLModel& f) {
+        std::vector<Key> k; std::vector<double> w;
+        f.nonzero(&k, &w);
+        return py::make_tuple(to_array(k), to_array(w));
+      });
   py::class_<KVVector>(m, "KVVector")
       .def(py::init<int>(), py::arg("k") = 1)
       .def("k", &KVVector::k)

@@ -5,6 +5,7 @@
 // src/base/bitmap.h, src/base/auc.h, src/base/evaluation.h, src/base/shared_array_inl.h:146-171
 // (setUnion/setIntersection/findRange), src/parameter/kv_vector.h.
 #pragma once
+#include <unordered_map>
 #include <cmath>
 
 #include "message.h"
@@ -216,6 +217,62 @@ class KVVector {
   std::map<int, std::vector<Key>> key_;
   std::map<int, std::vector<double>> val_;
   std::map<int, Received> recved_;
+};
+
+// Server-side state of the online solver on CPU nodes: key -> {pos, neg, w, z} with the per-key
+// FTRL-proximal update and the count-based estimate of the gradient norm, plus running |w|_1, |w|_2^2
+// and nnz(w) (FTRLModel::setValue / getValue / objv, src/linear_method/ftrl_model.h:60-127).
+class FTRLModel {
+ public:
+  struct Entry { double pos = 0, neg = 0, w = 0, z = 0; };
+  FTRLModel(double alpha, double beta, double lambda1, double lambda2) : alpha_(alpha), beta_(beta), l1_(lambda1), l2_(lambda2) {}
+  static double sqrt_n(double pos, double neg) {
+    const double all = pos + neg;
+    return all == 0 ? 0 : std::sqrt(pos * neg / all);
+  }
+  void update(const Key* keys, size_t n, const double* grad, const double* pos, const double* neg) {
+    for (size_t i = 0; i < n; ++i) {
+      Entry& e = model_[keys[i]];
+      const double sq = sqrt_n(e.pos, e.neg);
+      e.pos += pos[i];
+      e.neg += neg[i];
+      const double sq_new = sqrt_n(e.pos, e.neg);
+      const double sigma = (sq_new - sq) / alpha_;
+      e.z += grad[i] - sigma * e.w;
+      const double l2 = l2_ + (beta_ + sq_new) / alpha_;
+      const double w_old = e.w, az = std::fabs(e.z) - l1_;
+      e.w = az > 0 ? -std::copysign(az, e.z) / l2 : 0.0;
+      norm1_ += std::fabs(e.w) - std::fabs(w_old);
+      norm2_ += e.w * e.w - w_old * w_old;
+      nnz_ += (e.w != 0 && w_old == 0) - (e.w == 0 && w_old != 0);
+    }
+  }
+  std::vector<double> get(const Key* keys, size_t n) const {
+    std::vector<double> out(n, 0.0);
+    for (size_t i = 0; i < n; ++i) {
+      auto it = model_.find(keys[i]);
+      if (it != model_.end()) out[i] = it->second.w;
+    }
+    return out;
+  }
+  double norm1() const { return norm1_; }
+  double norm2() const { return norm2_; }
+  long long nnz() const { return nnz_; }
+  size_t size() const { return model_.size(); }
+  // non-zero weights in ascending key order
+  void nonzero(std::vector<Key>* keys, std::vector<double>* w) const {
+    std::vector<std::pair<Key, double>> v;
+    for (auto& kv : model_) if (kv.second.w != 0) v.emplace_back(kv.first, kv.second.w);
+    std::sort(v.begin(), v.end());
+    keys->clear(); w->clear();
+    for (auto& p : v) { keys->push_back(p.first); w->push_back(p.second); }
+  }
+
+ private:
+  double alpha_, beta_, l1_, l2_;
+  double norm1_ = 0, norm2_ = 0;
+  long long nnz_ = 0;
+  std::unordered_map<Key, Entry> model_;
 };
 
 inline double soft_thresholding(double x, double l1, double l2) {

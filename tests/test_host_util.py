@@ -189,3 +189,26 @@ def test_numpy_countmin_restatement_matches_host():
     assert len(f.model) == 0                                    # counts 2, 1, 1: nobody above 3 yet
     f.step([mb])
     assert set(f.model) == {5}                                  # key 5 reached 4 > 3
+
+
+def test_native_ftrl_model_matches_oracle():
+    """FTRLModel (server-side store of the CPU online job): per-key update, pulls, running norms."""
+    from baseline.cpu_ref.ftrl_ref import FTRLRef
+
+    m = H.FTRLModel(0.05, 1.0, 0.05, 0.1)
+    ref = FTRLRef(0.05, 1.0, 0.05, 0.1, "count")
+    rng = np.random.RandomState(0)
+    for _ in range(30):
+        k = np.unique(rng.randint(0, 80, size=25)).astype(np.uint64) * np.uint64(2**57 + 3)
+        g, pos, neg = rng.randn(len(k)), rng.randint(0, 5, len(k)).astype(float), rng.randint(0, 5, len(k)).astype(float)
+        m.update(k, g, pos, neg)
+        ref.set_value(k, pos, neg, g)
+    k, w = m.nonzero()
+    rk, rw = ref.nonzero()
+    assert np.array_equal(k, rk) and np.allclose(w, rw, rtol=1e-12)
+    n1, n2, nnz = m.stats()
+    assert n1 == pytest.approx(ref.norm1) and n2 == pytest.approx(ref.norm2) and nnz == ref.nnz and m.size() == len(ref.model)
+    probe = np.array([int(rk[0]), 12345], dtype=np.uint64)
+    assert m.get(probe).tolist() == [pytest.approx(rw[0]), 0.0]
+    with pytest.raises(ValueError):
+        m.update(k, w[:-1], w, w)
