@@ -82,3 +82,25 @@ def test_two_workers_learn(tmp_path):
     row_of = np.repeat(np.arange(rows), np.diff(oo))
     xw = np.bincount(row_of, weights=np.array([model.get(int(k), 0.0) for k in keys]), minlength=rows)
     assert np.mean(np.logaddexp(0.0, -yy * xw)) < 0.66      # log 2 = 0.693 for the constant predictor
+
+
+def test_processes_over_tcp(tmp_path):
+    """The same job as five real processes (1 + 2 + 2) over the TCP van, started by the launcher."""
+    import os
+    import subprocess
+    import sys
+
+    rows, cols = 1200, 256
+    off, idx, vals, y = planted(rows, cols, 10, 4, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    conf = tmp_path / "job.conf"
+    conf.write_text(CONF.format(train=tmp_path / "train", out=tmp_path, mb=150, tail=2))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "parameter_server_b200.launch", "-num_servers", "2", "-num_workers", "2",
+                        "-app", str(conf)], cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert f"{rows} examples" in r.stderr + r.stdout
+    model = {}
+    for s_ in ("S0", "S1"):
+        model.update(read_model_text(str(tmp_path / f"model_{s_}")))
+    assert len(model) > 20
