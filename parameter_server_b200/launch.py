@@ -36,9 +36,22 @@ def main(argv=None) -> int:
     for r in range(n):
         cmd = [sys.executable, "-m", "parameter_server_b200.ps", *args, "-my_rank", str(r), "-scheduler", sched]
         procs.append(subprocess.Popen(cmd))
+    # wait for all of them; when one fails the job cannot finish, so the others (exactly these children) are stopped
+    import time
+
     rc = 0
-    for p in procs:
-        rc = p.wait() or rc
+    alive = list(procs)
+    while alive:
+        for p in list(alive):
+            code = p.poll()
+            if code is None:
+                continue
+            alive.remove(p)
+            if code != 0 and rc == 0:
+                rc = code
+                for q in alive:
+                    q.terminate()
+        time.sleep(0.05)
     return rc
 
 

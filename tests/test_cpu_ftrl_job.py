@@ -104,3 +104,17 @@ def test_processes_over_tcp(tmp_path):
     for s_ in ("S0", "S1"):
         model.update(read_model_text(str(tmp_path / f"model_{s_}")))
     assert len(model) > 20
+
+
+def test_launcher_stops_the_job_when_a_node_fails(tmp_path):
+    """A scheduler that cannot read its job file exits; the launcher ends the other nodes instead of waiting forever."""
+    import os
+    import subprocess
+    import sys
+    import time
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    t0 = time.time()
+    r = subprocess.run([sys.executable, "-m", "parameter_server_b200.launch", "-num_servers", "1", "-num_workers", "1",
+                        "-app", str(tmp_path / "missing.conf")], cwd=root, capture_output=True, text=True, timeout=120)
+    assert r.returncode != 0 and time.time() - t0 < 60
