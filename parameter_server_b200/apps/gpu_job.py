@@ -137,6 +137,10 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
                 sol.trace = ChromeTrace(f"{flags.trace_file}.rank{group.rank}.json", pid=group.rank)
             if flags.metrics_file:
                 sol.metrics = MetricsLog(flags.metrics_file)
+            if group.world > 1 and float(flags.report_interval) > 0:
+                from ..parallel.monitor import RankMonitor
+
+                sol.monitor = RankMonitor(group.rank, group.world, deadline_s=max(10.0, 5.0 * float(flags.report_interval)))
             sol.preprocess(off, keys, vals, y)
             t0 = time.time()
             if flags.checkpoint_dir:
@@ -227,8 +231,17 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
         start_step = max(load_ftrl(eng, ckdir), 0)
         if start_step and group.rank == 0:
             print(f"resuming after minibatch {start_step} from {ckdir}", file=sys.stderr)
+    # -report_interval > 0 (the reference's heartbeat switch): every rank heartbeats into the job's store and
+    # looks at the others before launching; a rank that left or went silent stops the job with RankLost
+    mon = None
+    if group.world > 1 and float(flags.report_interval) > 0:
+        from ..parallel.monitor import RankMonitor
+
+        mon = RankMonitor(group.rank, group.world, deadline_s=max(10.0, 5.0 * float(flags.report_interval)))
     for hb in batches():
         step += 1
+        if mon is not None:
+            mon.tick(step, float(flags.report_interval))
         if step <= start_step:
             seen += hb.y.numel()
             continue

@@ -510,6 +510,9 @@ class DarlinSolver:
 
         t0 = time.time()
         trace, metrics = getattr(self, "trace", None), getattr(self, "metrics", None)
+        monitor = getattr(self, "monitor", None)     # parallel.monitor.RankMonitor: look at the other ranks before launching
+        if monitor is not None:
+            monitor.tick(len(self.progress))
         if reset:
             self.reset_active_sets()
         with nvtx_range("darlin_pass"):
