@@ -127,8 +127,8 @@ struct LocalScratch {
   uint32_t* slot_of;   // nnz: local slot of each non-zero
   float* coef;         // rows: −y/(1+e^{y·Xw})
   float* xw;           // rows: X·w (predictions)
-  uint32_t* send_cnt;  // [PSB_MAX_RANKS] cursors, zero between steps
-  uint32_t* recv_cnt;  // [PSB_MAX_RANKS]
+  uint32_t* send_cnt;  // [PSB_MAX_RANKS] scratch of the unfused baseline (the fused push uses fixed chunk segments)
+  uint32_t* recv_cnt;  // [PSB_MAX_RANKS] 1 = sender s's records of this step arrived, 0 = its flag wait ran out
   double* stats;       // [0] Σloss [1] rows [2] ‖w‖₁ [3] ‖w‖₂² [4] nnz(w) [5] unique keys [6] table entries
   uint32_t* status;    // StatusCode etc.
   uint64_t* trace;     // optional [16]: globaltimer at phase boundaries of the last step (see kTrace*)
