@@ -175,6 +175,7 @@ class LinearMethodNode:
             self.keys = ukeys
             rows = np.repeat(np.arange(len(self.y)), np.diff(self.off))
             self.X = sp.csc_matrix((self.val, (rows, inv)), shape=(len(self.y), len(ukeys)))
+            self._csc_cache = None
             t2 = t + 4
             P.cust.submit(H.kServerGroup, cmd=PUSH, key=ukeys.tobytes(), time=t2, key_range=allr, channel=self.ch,
                           flags=F_INSERT_KEY, erase_key_cache=True, wait=True)
@@ -185,7 +186,7 @@ class LinearMethodNode:
             self.w = w0.copy() if len(w0) == n else np.zeros(n)
             self.dual = np.exp(self.y * (self.X @ self.w))
             self.delta = np.full(n, self.conf.darling.delta_init_value)
-            self.active = np.ones(n, dtype=bool)
+            self.active = np.ones(n, dtype=np.uint8)
         else:
             if freq > 0:
                 P.cust.wait_in(H.kWorkerGroup, t)
@@ -197,7 +198,7 @@ class LinearMethodNode:
             P.kv.init_values(self.ch, init.constant if init.type == "CONSTANT" else 0.0)
             n = len(P.kv.keys(self.ch))
             self.delta = np.full(n, self.conf.darling.delta_init_value)
-            self.active = np.ones(n, dtype=bool)
+            self.active = np.ones(n, dtype=np.uint8)
             P.cust.finish_in(H.kWorkerGroup, t2 + 1)
 
     # ------------------------------------------------------------------ UPDATE_MODEL
@@ -208,7 +209,7 @@ class LinearMethodNode:
             self.kkt_threshold = call.kkt_filter_threshold
             self.violation = 0.0
         if call.has("kkt_filter_reset") and call.kkt_filter_reset:
-            self.active[:] = True
+            self.active[:] = 1
             if self.ctx.is_server:
                 w = P.kv.values(self.ch)
                 P.kv.set_values(self.ch, np.nan_to_num(w, nan=0.0))
@@ -240,78 +241,39 @@ class LinearMethodNode:
                 P.cust.finish_in(H.kWorkerGroup, t + 1)
             self.cust.reply(msg)
 
+    # The three block steps run in the native runtime (csrc/host/darlin_cpu.h): threaded column gradients, the
+    # server's proximal-Newton update, the worker's dual update.
+    def _csc(self):
+        if getattr(self, "_csc_cache", None) is None:
+            X = self.X
+            self._csc_cache = (np.ascontiguousarray(X.indptr, dtype=np.int64), np.ascontiguousarray(X.indices, dtype=np.int32),
+                               None if self.binary else np.ascontiguousarray(X.data, dtype=np.float64),
+                               np.ascontiguousarray(self.y, dtype=np.float64))
+        return self._csc_cache
+
     def _gradients(self, c0: int, c1: int):
-        X, y = self.X, self.y
-        tau = 1.0 / (1.0 + self.dual)
-        t2 = tau * (1 - tau)
-        G, U = np.zeros(c1 - c0), np.zeros(c1 - c0)
-        for jj, j in enumerate(range(c0, c1)):
-            if not self.active[j]:
-                G[jj] = U[jj] = NAN_SENTINEL
-                continue
-            s, e = X.indptr[j], X.indptr[j + 1]
-            r, v = X.indices[s:e], X.data[s:e]
-            d = self.delta[j]
-            G[jj] = -np.sum(y[r] * tau[r] * v)
-            if self.binary:
-                U[jj] = np.sum(np.minimum(t2[r] * math.exp(d), 0.25))
-            else:
-                U[jj] = np.sum(np.minimum(t2[r] * np.exp(np.abs(v) * d), 0.25) * v * v)
-        return G, U
+        indptr, indices, data, y = self._csc()
+        return self.H.darlin_block_gradient(indptr, indices, data, y, self.dual, self.delta, self.active, c0, c1,
+                                            max(int(self.flags.num_threads), 1))
 
     def _update_weight(self, s0: int, s1: int, GU: np.ndarray) -> None:
         P, d = self.param, self.conf.darling
-        eta = self.conf.learning_rate.eta
-        lam = self.conf.penalty.get("lambda")[0]
         w = P.kv.values(self.ch)
-        seg = w[s0:s1].copy()
-        for i in range(s1 - s0):
-            k = s0 + i
-            if not self.active[k]:
-                continue
-            g, u = GU[i, 0], GU[i, 1] / eta + 1e-10
-            if g != g:                       # every worker sent the inactive sentinel
-                continue
-            gp, gn = g + lam, g - lam
-            wk = seg[i]
-            dd, vio = -wk, 0.0
-            if wk == 0:
-                if gp < 0:
-                    vio = -gp
-                elif gn > 0:
-                    vio = gn
-                elif gp > self.kkt_threshold and gn < -self.kkt_threshold:
-                    self.active[k] = False
-                    seg[i] = np.nan
-                    continue
-            self.violation = max(self.violation, vio)
-            if gp <= u * wk:
-                dd = -gp / u
-            elif gn >= u * wk:
-                dd = -gn / u
-            dd = min(self.delta[k], max(-self.delta[k], dd))
-            self.delta[k] = min(d.delta_max_value, 2 * abs(dd) + 0.1)
-            seg[i] = wk + dd
+        seg = np.ascontiguousarray(w[s0:s1], dtype=np.float64).copy()
+        dl = np.ascontiguousarray(self.delta[s0:s1]).copy()
+        ac = np.ascontiguousarray(self.active[s0:s1]).copy()
+        vio = self.H.darlin_update_weight(seg, dl, ac, np.ascontiguousarray(GU[:, 0]), np.ascontiguousarray(GU[:, 1]),
+                                          float(self.conf.penalty.get("lambda")[0]), float(self.conf.learning_rate.eta),
+                                          float(self.kkt_threshold), float(d.delta_max_value))
+        self.delta[s0:s1] = dl
+        self.active[s0:s1] = ac
+        self.violation = max(self.violation, vio)
         P.kv.set_values_range(self.ch, s0, seg)
 
     def _update_dual(self, c0: int, c1: int, w_new: np.ndarray) -> None:
-        X, y = self.X, self.y
-        dmax = self.conf.darling.delta_max_value
-        for jj, j in enumerate(range(c0, c1)):
-            if not self.active[j]:
-                continue
-            wn = w_new[jj]
-            if wn != wn:
-                self.active[j] = False
-                self.w[j] = 0.0
-                continue
-            dw = wn - self.w[j]
-            self.delta[j] = min(dmax, 2 * abs(dw) + 0.1)
-            self.w[j] = wn
-            if dw != 0:
-                s, e = X.indptr[j], X.indptr[j + 1]
-                r, v = X.indices[s:e], X.data[s:e]
-                self.dual[r] *= np.exp(y[r] * v * dw)
+        indptr, indices, data, y = self._csc()
+        self.H.darlin_update_dual(indptr, indices, data, y, self.dual, self.w, self.delta, self.active,
+                                  np.ascontiguousarray(w_new, dtype=np.float64), c0, c1, float(self.conf.darling.delta_max_value))
 
     # ------------------------------------------------------------------ EVALUATE_PROGRESS / SAVE_MODEL
     def evaluate(self) -> bytes:

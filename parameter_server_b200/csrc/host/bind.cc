@@ -6,6 +6,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "darlin_cpu.h"
 #include "data.h"
 #include "kv.h"
 #include "runtime.h"
@@ -182,6 +183,48 @@ PYBIND11_MODULE(_psb_host, m) {
         return py::make_tuple(tk, tc, fk, fc);
       })
       .def("clear", &AUC::clear).def("evaluate", &AUC::evaluate).def("accuracy", &AUC::accuracy, py::arg("threshold") = 0.0);
+  // ---- DARLIN block steps on CPU nodes (in-place arrays must be C-contiguous, writeable and of the exact dtype)
+  using marray_d = py::array_t<double, py::array::c_style>;
+  using marray_b = py::array_t<uint8_t, py::array::c_style>;
+  auto need_rw = [](const py::array& a, const char* what) {
+    if (!a.writeable()) throw std::invalid_argument(std::string(what) + " must be writeable");
+  };
+  m.def("darlin_block_gradient", [](carray<int64_t> indptr, carray<int32_t> indices, py::object data, carray<double> y,
+                                    carray<double> dual, carray<double> delta, carray<uint8_t> active, int64_t c0, int64_t c1,
+                                    int threads) {
+    carray<double> dv;
+    const double* dp = nullptr;
+    if (!data.is_none()) { dv = data.cast<carray<double>>(); dp = dv.data(); }
+    if (c0 < 0 || c1 < c0 || c1 + 1 > indptr.size() || c1 > delta.size() || c1 > active.size()) throw std::invalid_argument("bad column range");
+    py::array_t<double> G(c1 - c0), U(c1 - c0);
+    CscBlock B{indptr.data(), indices.data(), dp, c0, c1};
+    {
+      py::gil_scoped_release rel;
+      darlin_block_gradient(B, y.data(), dual.data(), delta.data(), active.data(), G.mutable_data(), U.mutable_data(), threads);
+    }
+    return py::make_tuple(G, U);
+  }, py::arg("indptr"), py::arg("indices"), py::arg("data"), py::arg("y"), py::arg("dual"), py::arg("delta"), py::arg("active"),
+     py::arg("c0"), py::arg("c1"), py::arg("threads") = 1);
+  m.def("darlin_update_weight", [need_rw](marray_d w, marray_d delta, marray_b active, carray<double> G, carray<double> U,
+                                          double lambda, double eta, double kkt_threshold, double delta_max) {
+    need_rw(w, "w"); need_rw(delta, "delta"); need_rw(active, "active");
+    const py::ssize_t n = w.size();
+    if (delta.size() != n || active.size() != n || G.size() != n || U.size() != n) throw std::invalid_argument("segment sizes differ");
+    return darlin_update_weight(w.mutable_data(), delta.mutable_data(), active.mutable_data(), G.data(), U.data(), n, lambda, eta,
+                                kkt_threshold, delta_max);
+  });
+  m.def("darlin_update_dual", [need_rw](carray<int64_t> indptr, carray<int32_t> indices, py::object data, carray<double> y,
+                                        marray_d dual, marray_d w, marray_d delta, marray_b active, carray<double> w_new,
+                                        int64_t c0, int64_t c1, double delta_max) {
+    need_rw(dual, "dual"); need_rw(w, "w"); need_rw(delta, "delta"); need_rw(active, "active");
+    carray<double> dv;
+    const double* dp = nullptr;
+    if (!data.is_none()) { dv = data.cast<carray<double>>(); dp = dv.data(); }
+    if (c0 < 0 || c1 < c0 || c1 + 1 > indptr.size() || c1 > w.size() || w_new.size() != c1 - c0) throw std::invalid_argument("bad column range");
+    CscBlock B{indptr.data(), indices.data(), dp, c0, c1};
+    darlin_update_dual(B, y.data(), dual.mutable_data(), w.mutable_data(), delta.mutable_data(), active.mutable_data(), w_new.data(),
+                       delta_max);
+  });
   py::class_<FTRLModel>(m, "FTRLModel")
       .def(py::init<double, double, double, double>(), py::arg("alpha"), py::arg("beta"), py::arg("lambda1"), py::arg("lambda2"))
       .def("update", [](FTRLModel& f, carray<uint64_t> k, carray<double> g, carray<double> pos, carray<double> neg) {

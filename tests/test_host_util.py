@@ -212,3 +212,61 @@ def test_native_ftrl_model_matches_oracle():
     assert m.get(probe).tolist() == [pytest.approx(rw[0]), 0.0]
     with pytest.raises(ValueError):
         m.update(k, w[:-1], w, w)
+
+
+@pytest.mark.parametrize("binary", [False, True])
+def test_native_darlin_block_steps(binary):
+    """Block gradient (threaded), server update and dual update of the CPU nodes against a NumPy restatement."""
+    import scipy.sparse as sp
+
+    rng = np.random.RandomState(1)
+    rows, cols = 300, 200
+    X = sp.random(rows, cols, density=0.05, random_state=rng, format="csc")
+    if binary:
+        X.data[:] = 1.0
+    indptr, indices = X.indptr.astype(np.int64), X.indices.astype(np.int32)
+    data = None if binary else X.data.astype(np.float64)
+    y = np.where(rng.rand(rows) < 0.5, 1.0, -1.0)
+    dual = np.exp(rng.randn(rows) * 0.3)
+    delta = rng.rand(cols) + 0.5
+    active = (rng.rand(cols) < 0.9).astype(np.uint8)
+    c0, c1 = 20, 180
+    G, U = H.darlin_block_gradient(indptr, indices, data, y, dual, delta, active, c0, c1, 4)
+    tau = 1 / (1 + dual)
+    t2 = tau * (1 - tau)
+    for j in range(c0, c1):
+        s, e = indptr[j], indptr[j + 1]
+        r, v = indices[s:e], X.data[s:e]
+        if not active[j]:
+            assert np.isnan(G[j - c0]) and np.isnan(U[j - c0])
+            continue
+        assert G[j - c0] == pytest.approx(-np.sum(y[r] * tau[r] * v), rel=1e-12, abs=1e-15)
+        assert U[j - c0] == pytest.approx(np.sum(np.minimum(t2[r] * np.exp(np.abs(v) * delta[j]), 0.25) * v * v), rel=1e-12, abs=1e-15)
+    # server update: zero weights with a small gradient are filtered (NaN), the others move inside the trust region
+    n = c1 - c0
+    w = np.where(rng.rand(n) < 0.5, 0.0, rng.randn(n) * 0.1)
+    dl, ac = np.ones(n), np.ones(n, dtype=np.uint8)
+    g = np.nan_to_num(G, nan=0.0)
+    u = np.nan_to_num(U, nan=1.0)
+    w2, dl2, ac2 = w.copy(), dl.copy(), ac.copy()
+    vio = H.darlin_update_weight(w2, dl2, ac2, g, u, 0.05, 1.0, 0.02, 5.0)
+    filtered = (w == 0) & (g + 0.05 > 0.02) & (g - 0.05 < -0.02) & ~((g + 0.05 < 0) | (g - 0.05 > 0))
+    assert np.array_equal(np.isnan(w2), filtered) and np.array_equal(ac2 == 0, filtered)
+    assert vio == pytest.approx(max(0.0, np.max(np.where(w == 0, np.maximum(-(g + 0.05), g - 0.05), 0.0))))
+    moved = ~filtered
+    assert np.all(np.abs(w2[moved] - w[moved]) <= dl[moved] + 1e-15)
+    # dual update: dual_i *= exp(y_i x_ij dw_j); NaN in w_new deactivates the column
+    wn = rng.randn(n) * 0.1
+    wn[3] = np.nan
+    wloc, dloc, aloc, dual2 = np.zeros(cols), np.ones(cols), np.ones(cols, dtype=np.uint8), dual.copy()
+    H.darlin_update_dual(indptr, indices, data, y, dual2, wloc, dloc, aloc, wn, c0, c1, 5.0)
+    expect = dual.copy()
+    for j in range(c0, c1):
+        if np.isnan(wn[j - c0]):
+            continue
+        s, e = indptr[j], indptr[j + 1]
+        expect[indices[s:e]] *= np.exp(y[indices[s:e]] * X.data[s:e] * wn[j - c0])
+    np.testing.assert_allclose(dual2, expect, rtol=1e-12)
+    assert aloc[c0 + 3] == 0 and wloc[c0 + 3] == 0 and np.allclose(np.delete(wloc[c0:c1], 3), np.delete(wn, 3))
+    with pytest.raises(ValueError):
+        H.darlin_block_gradient(indptr, indices, data, y, dual, delta, active, 0, cols + 5, 1)
