@@ -130,7 +130,15 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
                           seed=int(flags.seed), tail_feature_freq=int(s.tail_feature_freq),
                           countmin_k=int(s.countmin_k), countmin_n_ratio=float(s.countmin_n_ratio))
         if lm.has("darling"):
-            sol = DarlinSolver(group, dc, timeout_s=float(flags.timeout_s), impl=flags.impl if flags.impl in ("fused", "nccl") else "fused")
+            impl = flags.impl if flags.impl in ("fused", "nccl") else "fused"
+            # -mmap_training_data: the column blocks stay in pinned host memory and are streamed per pass
+            # (FeatureStation's out-of-core mode, src/linear_method/feature_station.cc:70-109); one GPU per job so far
+            ooc = bool(flags.mmap_training_data) and impl == "fused"
+            if ooc and group.world > 1:
+                if group.rank == 0:
+                    print("-mmap_training_data: streaming from host memory runs on one GPU; this job keeps its data resident")
+                ooc = False
+            sol = DarlinSolver(group, dc, timeout_s=float(flags.timeout_s), impl=impl, out_of_core=ooc)
             from ..utils.trace import ChromeTrace, MetricsLog
 
             if flags.trace_file:

@@ -15,6 +15,8 @@ saveModel (src/linear_method/batch_solver.cc:23-127, 202-426), Darling::updateMo
 from __future__ import annotations
 
 import math
+import os
+import shutil
 import sys
 import threading
 import time
@@ -111,6 +113,7 @@ class LinearMethodNode:
         self.violation = 0.0
         self.busy = 0.0
         self.ch = 1               # single feature group channel (all slots merged), like LIBSVM data
+        self.station = None       # feature store on disk (-mmap_training_data)
 
     # ------------------------------------------------------------------ dispatch
     def process(self, msg) -> None:
@@ -187,6 +190,8 @@ class LinearMethodNode:
             self.dual = np.exp(self.y * (self.X @ self.w))
             self.delta = np.full(n, self.conf.darling.delta_init_value)
             self.active = np.ones(n, dtype=np.uint8)
+            if bool(self.flags.mmap_training_data):
+                self._to_station()
         else:
             if freq > 0:
                 P.cust.wait_in(H.kWorkerGroup, t)
@@ -216,7 +221,9 @@ class LinearMethodNode:
         rng = (call.key.begin, call.key.end)
         if self.ctx.is_worker:
             c0, c1 = np.searchsorted(self.keys, [U64(rng[0]), U64(rng[1])])
-            G, Uu = self._gradients(c0, c1)
+            if self.station is not None:
+                self._prefetch_ahead(msg.time)
+            G, Uu = self._gradients(c0, c1, msg.time)
             gu = np.stack([G, Uu], 1).ravel()
             P.cust.submit(H.kServerGroup, cmd=PUSH, key=self.keys[c0:c1].tobytes(), values=[gu.tobytes()], time=t,
                           key_range=rng, channel=self.ch)
@@ -225,7 +232,9 @@ class LinearMethodNode:
 
             def on_pull():
                 _, wn = P.take_pulled(t + 2)
-                self._update_dual(c0, c1, wn)
+                self._update_dual(c0, c1, wn, T)
+                if self.station is not None:
+                    self.station.drop(T)
                 self.cust.finish_in(sender, T)
                 self.cust.reply(msg)
 
@@ -251,7 +260,44 @@ class LinearMethodNode:
                                np.ascontiguousarray(self.y, dtype=np.float64))
         return self._csc_cache
 
-    def _gradients(self, c0: int, c1: int):
+    def _to_station(self) -> None:
+        """-mmap_training_data: the column-major features go to the local cache directory and leave memory;
+        column ranges come back through the station's prefetch threads (csrc/host/feature_station.h)."""
+        indptr, indices, data, y = self._csc()
+        base = self.conf.local_cache.file[0] if self.conf.local_cache.file else "/tmp/psb200_cache/"
+        self._station_dir = f"{base}{self.ctx.node_id}_features_{os.getpid()}"
+        self.station = self.H.FeatureStation(self._station_dir, self.ctx.node_id,
+                                             int(self.flags.prefetch_mem_limit_kb), max(int(self.flags.num_threads), 1),
+                                             int(self.flags.prefetch_job_limit), bool(self.flags.prefetch_detail))
+        self.station.add_group(self.ch, len(y), indptr, indices, data)
+        self._y = y
+        self.X = None
+        self._csc_cache = None
+        self.idx = self.val = self.off = None
+
+    def _prefetch_ahead(self, now: int) -> None:
+        """Queue reads for the UPDATE_MODEL tasks that have arrived but not started, up to 4 (τ + 1) tasks ahead of
+        the newest one seen (the reference's window: src/linear_method/darling.cc:175-200)."""
+        st, tau = self.station, int(self.conf.solver.max_block_delay)
+        if st.pending() >= tau + 8:
+            return
+        horizon = max(st.max_task(), now) + 4 * max(tau, 1)
+        for m in self.cust.pending_requests():
+            if m.time > horizon or st.task_used(m.time):
+                continue
+            try:
+                call = parse(m.payload.decode(), cfg.LMCall)
+            except Exception:
+                continue
+            if call.cmd != "UPDATE_MODEL":
+                continue
+            c0, c1 = np.searchsorted(self.keys, [U64(call.key.begin), U64(call.key.end)])
+            st.prefetch(m.time, self.ch, int(c0), int(c1))
+
+    def _gradients(self, c0: int, c1: int, task: int = 0):
+        if self.station is not None:
+            return self.station.block_gradient(task, self.ch, int(c0), int(c1), self._y, self.dual, self.delta, self.active,
+                                               max(int(self.flags.num_threads), 1))
         indptr, indices, data, y = self._csc()
         return self.H.darlin_block_gradient(indptr, indices, data, y, self.dual, self.delta, self.active, c0, c1,
                                             max(int(self.flags.num_threads), 1))
@@ -270,7 +316,11 @@ class LinearMethodNode:
         self.violation = max(self.violation, vio)
         P.kv.set_values_range(self.ch, s0, seg)
 
-    def _update_dual(self, c0: int, c1: int, w_new: np.ndarray) -> None:
+    def _update_dual(self, c0: int, c1: int, w_new: np.ndarray, task: int = 0) -> None:
+        if self.station is not None:
+            self.station.block_update_dual(task, self.ch, int(c0), int(c1), self._y, self.dual, self.w, self.delta, self.active,
+                                           np.ascontiguousarray(w_new, dtype=np.float64), float(self.conf.darling.delta_max_value))
+            return
         indptr, indices, data, y = self._csc()
         self.H.darlin_update_dual(indptr, indices, data, y, self.dual, self.w, self.delta, self.active,
                                   np.ascontiguousarray(w_new, dtype=np.float64), c0, c1, float(self.conf.darling.delta_max_value))
@@ -300,6 +350,11 @@ class LinearMethodNode:
     def stop(self) -> None:
         self.cust.stop()
         self.param.cust.stop()
+        if self.station is not None:
+            if bool(self.flags.verbose):
+                print(f"[{self.ctx.node_id}] feature station: {self.station.stats()}", flush=True)
+            self.station = None               # joins the prefetch threads, closes the files
+            shutil.rmtree(self._station_dir, ignore_errors=True)
 
 
 class BatchScheduler:

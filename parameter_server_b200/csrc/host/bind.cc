@@ -8,6 +8,7 @@
 
 #include "darlin_cpu.h"
 #include "data.h"
+#include "feature_station.h"
 #include "kv.h"
 #include "runtime.h"
 
@@ -225,6 +226,70 @@ PYBIND11_MODULE(_psb_host, m) {
     darlin_update_dual(B, y.data(), dual.mutable_data(), w.mutable_data(), delta.mutable_data(), active.mutable_data(), w_new.data(),
                        delta_max);
   });
+  // ---- worker-side feature store (memory or disk with prefetch) and the block steps on its ranges
+  py::class_<FeatureStation>(m, "FeatureStation")
+      .def(py::init<std::string, std::string, size_t, int, size_t, bool>(), py::arg("dir"), py::arg("name"), py::arg("mem_limit_kb") = 1048576,
+           py::arg("threads") = 2, py::arg("job_limit") = 64, py::arg("detail") = false)
+      .def_property_readonly("disk", &FeatureStation::disk)
+      .def("add_group", [](FeatureStation& f, int grp, uint64_t rows, carray<int64_t> indptr, carray<int32_t> indices, py::object data) {
+        carray<double> dv;
+        const double* dp = nullptr;
+        if (!data.is_none()) { dv = data.cast<carray<double>>(); dp = dv.data(); }
+        if (indptr.size() < 1 || indptr.data()[indptr.size() - 1] != indices.size() || (dp && dv.size() != indices.size()))
+          throw std::invalid_argument("offsets, row ids and values do not fit together");
+        py::gil_scoped_release rel;
+        f.add_group(grp, rows, indptr.data(), indptr.size() - 1, indices.data(), dp);
+      }, py::arg("grp"), py::arg("rows"), py::arg("indptr"), py::arg("indices"), py::arg("data"))
+      .def("mem_size", &FeatureStation::mem_size)
+      .def("cols", &FeatureStation::cols)
+      .def("file_base", &FeatureStation::file_base)
+      .def("range_bytes", &FeatureStation::range_bytes)
+      .def("prefetch", &FeatureStation::prefetch)
+      .def("pending", &FeatureStation::pending)
+      .def("task_used", &FeatureStation::task_used)
+      .def("max_task", &FeatureStation::max_task)
+      .def("resident_bytes", &FeatureStation::resident_bytes)
+      .def("drop", &FeatureStation::drop)
+      .def("get", [](FeatureStation& f, int task, int grp, int64_t c0, int64_t c1) {
+        FeatureBlockPtr b;
+        { py::gil_scoped_release rel; b = f.get(task, grp, c0, c1); }
+        const int64_t p0 = b->indptr[0], n = b->indptr[c1 - c0] - p0;
+        py::array_t<int64_t> ip(c1 - c0 + 1);
+        for (int64_t j = 0; j <= c1 - c0; ++j) ip.mutable_data()[j] = b->indptr[j] - p0;
+        py::array_t<int32_t> idx(n);
+        if (n) std::memcpy(idx.mutable_data(), b->indices + (p0 - b->pos0), (size_t)n * 4);
+        py::object val = py::none();
+        if (b->values) { py::array_t<double> v(n); if (n) std::memcpy(v.mutable_data(), b->values + (p0 - b->pos0), (size_t)n * 8); val = v; }
+        return py::make_tuple(ip, idx, val);
+      }, "copies of columns [c0, c1): (offsets from 0, row ids, values or None)")
+      .def("block_gradient", [](FeatureStation& f, int task, int grp, int64_t c0, int64_t c1, carray<double> y, carray<double> dual,
+                                carray<double> delta, carray<uint8_t> active, int threads) {
+        if (c1 > delta.size() || c1 > active.size()) throw std::invalid_argument("bad column range");
+        py::array_t<double> G(c1 - c0), U(c1 - c0);
+        {
+          py::gil_scoped_release rel;
+          FeatureBlockPtr b = f.get(task, grp, c0, c1);
+          CscBlock B{b->indptr, b->indices, b->values, c0, c1, c0, b->pos0};
+          darlin_block_gradient(B, y.data(), dual.data(), delta.data(), active.data(), G.mutable_data(), U.mutable_data(), threads);
+        }
+        return py::make_tuple(G, U);
+      })
+      .def("block_update_dual", [need_rw](FeatureStation& f, int task, int grp, int64_t c0, int64_t c1, carray<double> y, marray_d dual, marray_d w,
+                                          marray_d delta, marray_b active, carray<double> w_new, double delta_max) {
+        need_rw(dual, "dual"); need_rw(w, "w"); need_rw(delta, "delta"); need_rw(active, "active");
+        if (c1 > w.size() || w_new.size() != c1 - c0) throw std::invalid_argument("bad column range");
+        py::gil_scoped_release rel;
+        FeatureBlockPtr b = f.get(task, grp, c0, c1);
+        CscBlock B{b->indptr, b->indices, b->values, c0, c1, c0, b->pos0};
+        darlin_update_dual(B, y.data(), dual.mutable_data(), w.mutable_data(), delta.mutable_data(), active.mutable_data(), w_new.data(), delta_max);
+      })
+      .def("stats", [](FeatureStation& f) {
+        auto s = f.stats();
+        py::dict d;
+        d["bytes_written"] = s.bytes_written; d["bytes_read"] = s.bytes_read; d["prefetched"] = s.prefetched; d["hits"] = s.hits;
+        d["misses"] = s.misses; d["peak_resident"] = s.peak_resident; d["budget_waits"] = s.budget_waits;
+        return d;
+      });
   py::class_<FTRLModel>(m, "FTRLModel")
       .def(py::init<double, double, double, double>(), py::arg("alpha"), py::arg("beta"), py::arg("lambda1"), py::arg("lambda2"))
       .def("update", [](FTRLModel& f, carray<uint64_t> k, carray<double> g, carray<double> pos, carray<double> neg) {
@@ -424,5 +489,6 @@ PYBIND11_MODULE(_psb_host, m) {
       .def("group", [](PyCustomer& c, const std::string& id) { std::vector<std::string> ids; for (auto& r : c.exec()->group(id)) ids.push_back(r->node.id); return ids; })
       .def("partition", [](PyCustomer& c, const std::string& id) { return c.exec()->partition(id); })
       .def("processed", [](PyCustomer& c) { return (uint64_t)c.exec()->processed; })
+      .def("pending_requests", [](PyCustomer& c) { return c.exec()->pending_requests(); })
       .def("stop", [](PyCustomer& c) { c.exec()->stop(); }, py::call_guard<py::gil_scoped_release>());
 }

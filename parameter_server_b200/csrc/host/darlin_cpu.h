@@ -16,10 +16,11 @@
 namespace psb {
 
 struct CscBlock {            // columns [c0, c1) of a CSC matrix with 64-bit offsets and 32-bit row ids
-  const int64_t* indptr;
-  const int32_t* indices;
+  const int64_t* indptr;     // offset of column j at indptr[j - col_base]
+  const int32_t* indices;    // row id / value of position p at [p - pos_base]
   const double* data;        // nullptr: all values are 1 (binary features)
   int64_t c0, c1;
+  int64_t col_base = 0, pos_base = 0;   // non-zero when the arrays hold a column range loaded on its own
 };
 
 // G_j = -sum_i y_i tau_i x_ij,  U_j = sum_i min(tau_i (1 - tau_i) e^{|x_ij| delta_j}, 1/4) x_ij^2,
@@ -33,7 +34,8 @@ inline void darlin_block_gradient(const CscBlock& B, const double* y, const doub
       if (!active[j]) { G[jj] = U[jj] = nan; continue; }
       double g = 0, u = 0;
       const double d = delta[j], ed = std::exp(d);
-      for (int64_t p = B.indptr[j]; p < B.indptr[j + 1]; ++p) {
+      const int64_t* ip = B.indptr + (j - B.col_base);
+      for (int64_t p = ip[0] - B.pos_base; p < ip[1] - B.pos_base; ++p) {
         const int32_t r = B.indices[p];
         const double tau = 1.0 / (1.0 + dual[r]), t2 = tau * (1.0 - tau);
         if (B.data == nullptr) {
@@ -98,7 +100,8 @@ inline void darlin_update_dual(const CscBlock& B, const double* y, double* dual,
     delta[j] = std::min(delta_max, 2 * std::fabs(dw) + 0.1);
     w[j] = wn;
     if (dw == 0) continue;
-    for (int64_t p = B.indptr[j]; p < B.indptr[j + 1]; ++p) {
+    const int64_t* ip = B.indptr + (j - B.col_base);
+    for (int64_t p = ip[0] - B.pos_base; p < ip[1] - B.pos_base; ++p) {
       const int32_t r = B.indices[p];
       dual[r] *= std::exp(y[r] * (B.data ? B.data[p] : 1.0) * dw);
     }

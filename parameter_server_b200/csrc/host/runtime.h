@@ -162,6 +162,15 @@ class Executor {
   }
   bool initialized() const { return inited_; }
   int last_task() const { return last_task_; }
+  // Requests that have arrived but not started yet, in arrival order (a worker looks ahead in them to
+  // prefetch the data of coming tasks; the reference walks its queue with Executor::forEach,
+  // src/system/executor.cc:262-272).
+  std::vector<MessagePtr> pending_requests() {
+    std::lock_guard<std::mutex> l(mu_);
+    std::vector<MessagePtr> out;
+    for (auto& m : recved_) if (m->task.request) out.push_back(m);
+    return out;
+  }
   bool key_cache_enabled = true;
   std::atomic<uint64_t> processed{0};
   std::mutex clock_mu;   // guards RNode::time of every node and group of this executor

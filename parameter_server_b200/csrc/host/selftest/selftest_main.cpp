@@ -7,7 +7,8 @@
 // threads at once so that a sanitizer can see them: 1 scheduler + 2 servers + 2 workers over the
 // in-process van, membership, concurrent pushes from two threads per worker, pulls with a
 // wait_time dependency on the push, heartbeats and the deadline-based failure detector, shutdown
-// while traffic is still queued.  Exit code 0 = every check passed (the sanitizer adds its own
+// while traffic is still queued; then the thread pool, the slot reader's parser threads and the feature
+// store's prefetch threads against two solver threads.  Exit code 0 = every check passed (the sanitizer adds its own
 // non-zero exit code when it finds something).
 #include <atomic>
 #include <cstdio>
@@ -18,6 +19,8 @@
 #include <thread>
 #include <vector>
 
+#include "../darlin_cpu.h"
+#include "../feature_station.h"
 #include "../data.h"
 #include "../kv.h"
 #include "../runtime.h"
@@ -219,6 +222,57 @@ int main(int argc, char** argv) {
       CHECK_TRUE(info.num_ex == 2000);
       CHECK_TRUE(rd.index(1).size() == nnz && rd.value(1).size() == nnz && rd.offset(1).back() == nnz);
     }
+  }
+
+  // feature store on disk: one thread queues read-ahead, two solver threads take, use and release ranges under a
+  // budget that holds about two of them; then the block gradient on a loaded range against the resident arrays
+  if (argc > 2) {
+    const std::string dir = argv[2];
+    const int64_t cols = 240, rows = 300;
+    std::vector<int64_t> indptr(1, 0);
+    std::vector<int32_t> indices;
+    std::vector<double> values;
+    for (int64_t j = 0; j < cols; ++j) {
+      for (int64_t r = j % 5; r < rows; r += 3 + j % 11) { indices.push_back((int32_t)r); values.push_back(0.25 + (r + j) % 7); }
+      indptr.push_back((int64_t)indices.size());
+    }
+    FeatureStation st(dir + "/features", "T0", 12, 3, 64, false);
+    st.add_group(1, rows, indptr.data(), cols, indices.data(), values.data());
+    CHECK_TRUE(st.mem_size() == indices.size() * 12 + (cols + 1) * 8);
+    const int tasks = 24;
+    std::thread ahead([&] { for (int t = 0; t < tasks; t += 2) st.prefetch(t, 1, t * 10, t * 10 + 10); });   // even tasks only
+    std::atomic<int> bad{0};
+    auto solver = [&](int first) {
+      for (int t = first; t < tasks; t += 2) {
+        auto b = st.get(t, 1, t * 10, t * 10 + 10);
+        for (int64_t j = 0; j < 10; ++j) {
+          const int64_t c = t * 10 + j;
+          if (b->indptr[j + 1] - b->indptr[j] != indptr[c + 1] - indptr[c]) ++bad;
+          for (int64_t p = b->indptr[j]; p < b->indptr[j + 1]; ++p)
+            if (b->indices[p - b->pos0] != indices[p] || b->values[p - b->pos0] != values[p]) ++bad;
+        }
+        st.drop(t);
+      }
+    };
+    std::thread s0(solver, 0), s1(solver, 1);
+    ahead.join(); s0.join(); s1.join();
+    CHECK_TRUE(bad == 0);
+    CHECK_TRUE(st.resident_bytes() == 0 && st.pending() == 0);
+    auto stats = st.stats();
+    CHECK_TRUE(stats.hits + stats.misses == (uint64_t)tasks && stats.misses >= (uint64_t)tasks / 2);
+
+    std::vector<double> y(rows), dual(rows), delta(cols, 1.0), G0(40), U0(40), G1(40), U1(40);
+    std::vector<uint8_t> active(cols, 1);
+    for (int64_t r = 0; r < rows; ++r) { y[r] = r % 2 ? 1 : -1; dual[r] = 0.5 + (r % 9) * 0.2; }
+    active[105] = 0;
+    CscBlock whole{indptr.data(), indices.data(), values.data(), 100, 140};
+    darlin_block_gradient(whole, y.data(), dual.data(), delta.data(), active.data(), G0.data(), U0.data(), 1);
+    auto b = st.get(1000, 1, 100, 140);
+    CscBlock part{b->indptr, b->indices, b->values, 100, 140, 100, b->pos0};
+    darlin_block_gradient(part, y.data(), dual.data(), delta.data(), active.data(), G1.data(), U1.data(), 2);
+    for (int i = 0; i < 40; ++i)
+      CHECK_TRUE((G0[i] == G1[i] && U0[i] == U1[i]) || (i == 5 && G0[i] != G0[i] && G1[i] != G1[i]));
+    st.drop(1000);
   }
 
   // shutdown with traffic possibly still queued

@@ -96,3 +96,30 @@ def test_tail_feature_filter_drops_rare_keys(tmp_path):
     # the sketch never drops a frequent key and lets only a few rare ones through (hash collisions)
     assert len(model) > 0 and rare_total > 100 and rare_kept < 0.2 * rare_total
     assert prog[-1]["objv"] < prog[0]["objv"] * 1.001
+
+
+def test_features_on_disk_give_the_same_job(tmp_path, capfd):
+    """-mmap_training_data: workers keep their column blocks in files of the local cache directory and read them
+    back through prefetch threads under a small budget; nothing about the result may change."""
+    rows, cols, nnz, passes, lam, ratio = 1200, 2048, 12, 3, 0.5, 2.0
+    off, idx, vals, y = planted(rows, cols, nnz, 5, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    progs, models = [], []
+    for mode, tau in (("mem", 0), ("disk", 0), ("disk", 2)):
+        out = tmp_path / f"{mode}{tau}"
+        out.mkdir()
+        text = CONF.format(train=tmp_path / "train", cache=tmp_path / f"cache_{mode}{tau}", out=out, lam=lam, ratio=ratio,
+                           passes=passes, tail=0).replace("max_block_delay: 0", f"max_block_delay: {tau}")
+        flags = cfg.Flags(num_workers=2, num_servers=2, seed=0, mmap_training_data=(mode == "disk"), prefetch_mem_limit_kb=16,
+                          num_threads=2, verbose=(mode == "disk"))
+        progs.append(run_local_threads(flags, text))
+        models.append({**{k: v for i in (0, 1) if os.path.exists(out / f"model_S{i}") for k, v in read_model_text(str(out / f"model_S{i}")).items()}})
+        if mode == "disk":
+            left = [p for p in os.listdir(tmp_path / f"cache_{mode}{tau}") if "_features_" in p]
+            assert left == [], left                                    # the workers removed their feature files
+    text = capfd.readouterr().out
+    assert "feature station" in text and "'prefetched': 0" not in text     # read-ahead happened on every worker
+    for p, q in zip(progs[0], progs[1]):                                # same schedule, same arithmetic
+        assert p["objv"] == q["objv"] and p["nnz_w"] == q["nnz_w"]
+    assert models[0] == models[1] and len(models[0]) > 0
+    assert progs[2][-1]["objv"] < progs[2][0]["objv"]                    # bounded delay: runs and converges
