@@ -98,7 +98,7 @@ class FTRLNode:
         """FTRL::updateModel: one pass over this worker's files in minibatches."""
         H, P, s = self.H, self.param, self.conf.solver
         td = self.conf.training_data
-        files = H.search_files(list(td.file))
+        files = H.search_files(cfg.data_files(td, H))
         if not files:
             return
         reader = H.StreamReader()

@@ -22,9 +22,10 @@ from ..parallel.peer import PeerGroup
 from ..runtime import host
 
 
-def _my_files(patterns: List[str], group: PeerGroup, load_limit: int) -> List[str]:
+def _my_files(data_conf, group: PeerGroup, load_limit: int) -> List[str]:
     H = host()
-    files = H.search_files(list(patterns))
+    patterns = cfg.data_files(data_conf, H)
+    files = H.search_files(patterns)
     if patterns and not files:
         raise FileNotFoundError(f"no file matches {list(patterns)}")
     return H.divide_files(files, group.world, load_limit)[group.rank]
@@ -83,7 +84,7 @@ def predict_csr(off, keys, vals, mk: np.ndarray, mw: np.ndarray) -> torch.Tensor
 def validation_auc(group: PeerGroup, conf_data, flags, cache: str, mk, mw, goodness: int) -> Optional[float]:
     """AUC over the validation files, histograms merged across ranks (src/base/auc.h, batch_solver.cc:114-123)."""
     H = host()
-    files = _my_files(conf_data.file, group, 0)
+    files = _my_files(conf_data, group, 0)
     auc = H.AUC()
     auc.set_goodness(int(goodness))
     if files:
@@ -119,7 +120,7 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
     if lm.solver.minibatch_size <= 0:
         from ..models.darlin import DarlinConfig, DarlinSolver
 
-        files = _my_files(lm.training_data.file, group, int(flags.load_limit))
+        files = _my_files(lm.training_data, group, int(flags.load_limit))
         off, keys, vals, y, info = load_csr(lm.training_data, files, flags, cache, group.device)
         d, s = lm.darling, lm.solver
         lam = lm.penalty.get("lambda")
@@ -193,7 +194,7 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
     hyper = FTRLHyper(alpha=lm.learning_rate.alpha, beta=lm.learning_rate.beta, lambda1=lam[0], lambda2=lam[1],
                       tail_feature_freq=int(s.tail_feature_freq), countmin_n=int(s.countmin_n),
                       countmin_k=int(s.countmin_k))
-    files = _my_files(lm.training_data.file, group, int(flags.load_limit))
+    files = _my_files(lm.training_data, group, int(flags.load_limit))
     fmt = getattr(H.TextFormat, lm.training_data.text if lm.training_data.has("text") else "LIBSVM")
     reader = H.StreamReader()
     reader.init(files, fmt, True, bool(flags.shuffle_fea_id))

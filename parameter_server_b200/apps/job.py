@@ -44,7 +44,7 @@ def run_node(rank: int, flags: cfg.Flags, hub=None, app_text: Optional[str] = No
             text = app_text if app_text is not None else open(flags.app).read()
             conf = parse(text, cfg.AppConfig)
             lm = conf.linear_method
-            files = H.search_files(list(lm.training_data.file))
+            files = H.search_files(cfg.data_files(lm.training_data, H))
             if lm.training_data.file and not files:
                 raise FileNotFoundError(f"no training file matches {list(lm.training_data.file)}")
             parts = H.divide_files(files, max(flags.num_workers, 1), int(flags.load_limit))

@@ -145,7 +145,7 @@ class LinearMethodNode:
         fmt = getattr(self.H.TextFormat, td.text if td.has("text") else "LIBSVM")
         cache = self.conf.local_cache.file[0] if self.conf.local_cache.file else "/tmp/psb200_cache/"
         r = self.H.SlotReader()
-        r.init(list(td.file), fmt, cache + f"{self.ctx.node_id}/", True, bool(self.flags.shuffle_fea_id),
+        r.init(cfg.data_files(td, self.H), fmt, cache + f"{self.ctx.node_id}/", True, bool(self.flags.shuffle_fea_id),
                bool(self.flags.add_beta_feature), int(self.flags.line_limit), int(self.flags.load_data_max_mb_per_thread))
         info, hits = r.read(max(int(self.flags.num_threads), 1))
         self.y = r.value(0).astype(np.float64)

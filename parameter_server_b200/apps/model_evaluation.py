@@ -11,6 +11,7 @@ import sys
 
 import numpy as np
 
+from .. import config as cfg
 from ..runtime import host
 from ..utils.modelio import model_arrays, read_model_text
 
@@ -19,10 +20,10 @@ def evaluate_model(lm, flags, group) -> dict:
     from .gpu_job import _my_files, load_csr, predict_csr
 
     H = host()
-    files = H.search_files(list(lm.model_input.file)) or list(lm.model_input.file)
+    files = H.search_files(cfg.data_files(lm.model_input, H)) or cfg.data_files(lm.model_input, H)
     mk, mw = model_arrays(read_model_text(*files))
     cache = (lm.local_cache.file[0] if lm.local_cache.file else "/tmp/psb200_cache/") + f"eval{group.rank}/"
-    vfiles = _my_files(lm.validation_data.file, group, 0)
+    vfiles = _my_files(lm.validation_data, group, 0)
     auc = H.AUC()
     y_all, p_all = np.zeros(0, np.float32), np.zeros(0, np.float32)
     if vfiles:

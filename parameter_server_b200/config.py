@@ -146,6 +146,30 @@ def parse_app_config(text: str) -> Message:
     return parse(text, AppConfig)
 
 
+def data_files(dc, H) -> list:
+    """File patterns of a DataConfig as the host runtime reads them.  With an ``hdfs { home ugi namenode }`` block
+    every pattern becomes ``hdfs:<pattern>`` (listed with ``hadoop fs -ls``, read through ``hadoop fs -cat``;
+    src/util/file.cc:50-66, 250-300) and this process's hadoop command is set from the block: ``<home>/bin/hadoop``
+    (``$HADOOP_HOME`` or the PATH when home is empty), the user of ``ugi`` as ``HADOOP_USER_NAME``, the name node as
+    ``-D fs.defaultFS``."""
+    import os
+    import shlex
+
+    files = list(dc.file)
+    if not dc.has("hdfs"):
+        return files
+    h = dc.hdfs
+    home = h.home if h.has("home") and h.home else os.environ.get("HADOOP_HOME", "")
+    cmd = shlex.quote(os.path.join(home, "bin", "hadoop")) if home else "hadoop"
+    cmd += " fs"
+    if h.has("namenode") and h.namenode:
+        cmd += " -D " + shlex.quote("fs.defaultFS=" + h.namenode)
+    if h.has("ugi") and h.ugi:
+        cmd = "HADOOP_USER_NAME=" + shlex.quote(h.ugi.split(",")[0]) + " " + cmd
+    H.set_hadoop_fs(cmd)
+    return [f if f.startswith("hdfs:") else "hdfs:" + f for f in files]
+
+
 def parse_node(text: str) -> Message:
     """``role:SCHEDULER,hostname:'127.0.0.1',port:8000,id:'H'`` → Node (src/system/van.h:32-36)."""
     return parse(text, Node)

@@ -326,6 +326,8 @@ PYBIND11_MODULE(_psb_host, m) {
   py::enum_<TextFormat>(m, "TextFormat")
       .value("PS_DENSE", TextFormat::PS_DENSE).value("PS_SPARSE", TextFormat::PS_SPARSE).value("PS_SPARSE_BINARY", TextFormat::PS_SPARSE_BINARY)
       .value("ADFEA", TextFormat::ADFEA).value("LIBSVM", TextFormat::LIBSVM).value("TERAFEA", TextFormat::TERAFEA);
+  m.def("set_hadoop_fs", [](const std::string& cmd) { hadoop_fs_command() = cmd; }, "command that stands for `hadoop fs` when \"hdfs:\" paths are read");
+  m.def("hadoop_fs", [] { return hadoop_fs_command(); });
   m.def("search_files", &search_files);
   m.def("divide_files", &divide_files, py::arg("files"), py::arg("num_workers"), py::arg("load_limit") = 0);
   m.def("parse_text", [](const std::string& text, TextFormat fmt, bool ignore_grp, bool shuffle, bool beta) {

@@ -13,6 +13,7 @@
 #include <sys/stat.h>
 
 #include <regex>
+#include <sstream>
 
 #include "message.h"
 
@@ -82,7 +83,11 @@ struct SlotData {
 };
 
 // ------------------------------------------------------------------ files
-inline bool file_exists(const std::string& p) { struct stat st; return ::stat(p.c_str(), &st) == 0; }
+inline bool file_exists(const std::string& p) {
+  if (is_hdfs_path(p)) return std::system((hadoop_fs_command() + " -test -e " + shell_quote(p.substr(5)) + " >/dev/null 2>&1").c_str()) == 0;
+  struct stat st;
+  return ::stat(p.c_str(), &st) == 0;
+}
 inline std::string path_dir(const std::string& p) { auto s = p.find_last_of('/'); return s == std::string::npos ? "." : (s == 0 ? "/" : p.substr(0, s)); }
 inline std::string path_name(const std::string& p) { auto s = p.find_last_of('/'); return s == std::string::npos ? p : p.substr(s + 1); }
 inline bool make_dirs(const std::string& dir) {
@@ -93,7 +98,26 @@ inline bool make_dirs(const std::string& dir) {
   }
   return file_exists(dir);
 }
+// Names of the files in a directory "hdfs:<dir>": the last of the eight columns of `hadoop fs -ls`, directories left out.
+inline std::vector<std::string> list_hdfs_dir(const std::string& dir) {
+  std::vector<std::string> out;
+  FILE* p = ::popen((hadoop_fs_command() + " -ls " + shell_quote(dir.substr(5)) + " 2>/dev/null").c_str(), "r");
+  if (!p) return out;
+  char line[10000];
+  while (std::fgets(line, sizeof(line), p)) {
+    std::vector<std::string> col;
+    std::istringstream in(line);
+    for (std::string t; in >> t;) col.push_back(t);
+    if (col.size() != 8 || col[0][0] == 'd') continue;
+    auto s = col.back().find_last_of('/');
+    out.push_back(s == std::string::npos ? col.back() : col.back().substr(s + 1));
+  }
+  ::pclose(p);
+  std::sort(out.begin(), out.end());
+  return out;
+}
 inline std::vector<std::string> list_dir(const std::string& dir) {
+  if (is_hdfs_path(dir)) return list_hdfs_dir(dir);
   std::vector<std::string> out;
   DIR* d = ::opendir(dir.c_str());
   if (!d) return out;

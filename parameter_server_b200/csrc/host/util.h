@@ -374,15 +374,41 @@ std::vector<size_t> kv_partition(K* keys, V* vals, size_t n, const std::vector<K
 
 // ------------------------------------------------------------------ files
 // Sequential reader over plain or gzip files (zlib's gz layer reads both transparently).
+// Files on HDFS.  A path "hdfs:<path>" is read through a pipe from `<hadoop fs command> -cat <path>` and a
+// directory "hdfs:<dir>" is listed with `-ls`, like the reference (src/util/file.cc:50-66, 270-300; its
+// hadoopFS() hard-codes a user name, here the command is set from the job's HDFSConfig).  Read-only.
+inline std::string& hadoop_fs_command() { static std::string c = "hadoop fs"; return c; }
+inline bool is_hdfs_path(const std::string& p) { return p.compare(0, 5, "hdfs:") == 0; }
+inline std::string shell_quote(const std::string& s) {
+  std::string q = "'";
+  for (char c : s) { if (c == '\'') q += "'\\''"; else q += c; }
+  return q + "'";
+}
+
 class File {
  public:
+  // Plain and gzip files alike (zlib reads both); "hdfs:" paths through a pipe, gzip or not.
   static std::unique_ptr<File> open(const std::string& path, const char* mode) {
+    if (is_hdfs_path(path)) {
+      if (mode[0] != 'r') return nullptr;
+      FILE* p = ::popen((hadoop_fs_command() + " -cat " + shell_quote(path.substr(5))).c_str(), "r");
+      if (!p) return nullptr;
+      gzFile f = gzdopen(::dup(fileno(p)), "r");
+      if (!f) { ::pclose(p); return nullptr; }
+      gzbuffer(f, 1 << 20);
+      auto out = std::unique_ptr<File>(new File(f));
+      out->pipe_ = p;
+      return out;
+    }
     gzFile f = gzopen(path.c_str(), mode);
     if (!f) return nullptr;
     gzbuffer(f, 1 << 20);
     return std::unique_ptr<File>(new File(f));
   }
-  ~File() { if (f_) gzclose(f_); }
+  ~File() {
+    if (f_) gzclose(f_);
+    if (pipe_) ::pclose(pipe_);
+  }
   int read(void* buf, size_t n) { return gzread(f_, buf, (unsigned)n); }
   bool write(const void* buf, size_t n) { return gzwrite(f_, buf, (unsigned)n) == (int)n; }
   char* read_line(char* buf, int n) { return gzgets(f_, buf, n); }
@@ -392,6 +418,7 @@ class File {
  private:
   explicit File(gzFile f) : f_(f) {}
   gzFile f_;
+  FILE* pipe_ = nullptr;
 };
 
 // Record stream: [magic u32 = 0x3ed7230a][size u32][payload]

@@ -28,6 +28,7 @@ import torch
 
 from ..ops import dense
 from ..parallel.peer import PeerGroup
+from ..config import data_files
 from ..runtime import host
 
 
@@ -77,7 +78,7 @@ class DataLayer(Layer):
     def load_files(self) -> None:
         H = host()
         dc = self.conf.data
-        files = H.divide_files(H.search_files(list(dc.file)), self.net.group.world, 0)[self.net.group.rank]
+        files = H.divide_files(H.search_files(data_files(dc, H)), self.net.group.world, 0)[self.net.group.rank]
         r = H.SlotReader()
         r.init(files, getattr(H.TextFormat, dc.text if dc.has("text") else "LIBSVM"), f"/tmp/psb200_cache/nn{self.net.group.rank}/", True)
         info, _ = r.read(2)
