@@ -134,7 +134,7 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
             impl = flags.impl if flags.impl in ("fused", "nccl") else "fused"
             # -mmap_training_data: the column blocks stay in pinned host memory and are streamed per pass
             # (FeatureStation's out-of-core mode, src/linear_method/feature_station.cc:70-109); one GPU per job so far
-            ooc = bool(flags.mmap_training_data) and impl == "fused"
+            ooc = bool(flags.mmap_training_data) and impl == "fused" and lm.init_w.type != "FILE"
             if ooc and group.world > 1:
                 if group.rank == 0:
                     print("-mmap_training_data: streaming from host memory runs on one GPU; this job keeps its data resident")
@@ -151,6 +151,13 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
 
                 sol.monitor = RankMonitor(group.rank, group.world, deadline_s=max(10.0, 5.0 * float(flags.report_interval)))
             sol.preprocess(off, keys, vals, y)
+            if lm.init_w.type == "FILE":      # warm start from a model dump (one file, or the parts <name>_S<i>)
+                from ..utils.modelio import model_arrays, model_files, read_model_text
+
+                paths = model_files(lm.init_w.file_name)
+                if not paths:
+                    raise FileNotFoundError(f"init_w: no model file at {lm.init_w.file_name}")
+                sol.warm_start(*model_arrays(read_model_text(*paths)))
             t0 = time.time()
             if flags.checkpoint_dir:
                 from ..utils.checkpoint import run_with_checkpoints

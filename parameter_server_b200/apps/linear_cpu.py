@@ -20,6 +20,7 @@ import shutil
 import sys
 import threading
 import time
+import zlib
 from typing import Dict, List
 
 import numpy as np
@@ -201,10 +202,29 @@ class LinearMethodNode:
             P.filter.clear()
             init = self.conf.init_w
             P.kv.init_values(self.ch, init.constant if init.type == "CONSTANT" else 0.0)
+            if init.type == "GAUSSIAN":
+                rng = np.random.default_rng(int(self.flags.seed) + zlib.crc32(self.ctx.node_id.encode()))
+                P.kv.set_values(self.ch, rng.normal(init.mean, init.std, len(P.kv.keys(self.ch))))
+            elif init.type == "FILE":
+                self._init_from_model(init.file_name)
             n = len(P.kv.keys(self.ch))
             self.delta = np.full(n, self.conf.darling.delta_init_value)
             self.active = np.ones(n, dtype=np.uint8)
             P.cust.finish_in(H.kWorkerGroup, t2 + 1)
+
+    def _init_from_model(self, name: str) -> None:
+        """``init_w { type: FILE file_name: ... }``: start from a model dump (``key<TAB>value`` lines).  ``name`` is one
+        file, or the ``model_output`` prefix of an earlier job, whose per-server parts ``<name>_S<i>`` are all read: the
+        key ranges of the two jobs need not agree.  Keys of the dump that this job's data lacks are ignored.  (The
+        reference declares the FILE type and aborts on it: src/base/shared_array_inl.h:115-123.)"""
+        from ..utils.modelio import lookup_model, model_arrays, model_files, read_model_text
+
+        paths = model_files(name)
+        if not paths:
+            raise FileNotFoundError(f"init_w: no model file at {name} or {name}_*")
+        mk, mv = model_arrays(read_model_text(*paths))
+        w = lookup_model(mk, mv, self.param.kv.keys(self.ch))
+        self.param.kv.set_values(self.ch, w)
 
     # ------------------------------------------------------------------ UPDATE_MODEL
     def update_model(self, msg, call) -> None:

@@ -80,6 +80,18 @@ def block_order(nblk: int, n_pass: int, random_order: bool, seed: int) -> List[n
     return out
 
 
+def margins_from_weights(col_ptr: torch.Tensor, row_idx: torch.Tensor, vals: Optional[torch.Tensor], y: torch.Tensor,
+                         w: torch.Tensor) -> torch.Tensor:
+    """``y * (X w)`` for a column-major matrix (``col_ptr`` offsets, ``row_idx`` per non-zero, ``vals`` or None = binary)."""
+    P = col_ptr.numel() - 1
+    cols = torch.repeat_interleave(torch.arange(P, device=col_ptr.device), (col_ptr[1:] - col_ptr[:-1]).long())
+    contrib = w.to(torch.float32)[cols]
+    if vals is not None:
+        contrib = contrib * vals.to(torch.float32)
+    xw = torch.zeros(y.numel(), dtype=torch.float32, device=y.device).index_add_(0, row_idx.long(), contrib)
+    return y.to(torch.float32) * xw
+
+
 class DarlinSolver:
     """Worker + server of one rank; ``preprocess`` once, then ``run`` (or ``run_pass`` repeatedly)."""
 
@@ -380,6 +392,24 @@ class DarlinSolver:
         return N.DarlinHyper(self.cfg.lambda1, self.cfg.eta, self.cfg.delta_max, min(self.kkt_threshold, 1e30))
 
     # ------------------------------------------------------------------ passes
+    def warm_start(self, mkeys: np.ndarray, mvals: np.ndarray) -> None:
+        """Start from a model (ascending uint64 ``mkeys`` with weights ``mvals``, e.g. an earlier job's dump) instead of
+        zero: owners take the weights of their keys, workers those of their columns, and the margins become ``y * Xw``.
+        Keys that the data lacks are ignored.  Call it right after ``preprocess`` on every rank with the same model."""
+        if self.out_of_core:
+            raise NotImplementedError("warm start needs the column blocks on the device")
+        from ..utils.modelio import lookup_model
+
+        def look(keys_t: torch.Tensor) -> torch.Tensor:
+            w = lookup_model(mkeys, mvals, keys_t.cpu().numpy().view(np.uint64))
+            return torch.from_numpy(w.astype(np.float32)).to(self.dev)
+
+        self.srv_w.local.zero_()
+        self.srv_w.local[: self.slots].copy_(look(self.skeys)[: self.slots])
+        self.w.copy_(look(self.lkeys))
+        self.margin.copy_(margins_from_weights(self.col_ptr, self.row_idx, self.vals, self.y, self.w))
+        self.group.barrier()
+
     def reset_active_sets(self) -> None:
         """KKT filter reset (src/linear_method/darling.cc:167-169): every key re-enters the active set."""
         self.active.fill_(1)

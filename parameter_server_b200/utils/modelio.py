@@ -9,7 +9,7 @@ ModelEvaluation does (src/linear_method/model_evaluation.h:20-27).
 from __future__ import annotations
 
 import math
-from typing import Dict, Iterable, Tuple
+from typing import Dict, Iterable, List, Tuple
 
 import numpy as np
 
@@ -40,3 +40,24 @@ def model_arrays(model: Dict[int, float]) -> Tuple[np.ndarray, np.ndarray]:
     vals = np.fromiter(model.values(), dtype=np.float64, count=len(model))
     order = np.argsort(keys, kind="stable")
     return keys[order], vals[order]
+
+
+def model_files(name: str) -> List[str]:
+    """The files of a model given as one file or as the ``model_output`` prefix of an earlier job (``<name>_S0`` ...)."""
+    import glob
+    import os
+
+    if os.path.isfile(name):
+        return [name]
+    return sorted(glob.glob(glob.escape(name) + "_*"))
+
+
+def lookup_model(mkeys: np.ndarray, mvals: np.ndarray, keys: np.ndarray) -> np.ndarray:
+    """Weights of ``keys`` (uint64) in a model given as ascending ``mkeys`` (uint64) and ``mvals``; 0 where absent."""
+    keys = np.asarray(keys, dtype=np.uint64)
+    out = np.zeros(len(keys), dtype=np.float64)
+    if len(mkeys) and len(keys):
+        pos = np.clip(np.searchsorted(mkeys, keys), 0, len(mkeys) - 1)
+        hit = mkeys[pos] == keys
+        out[hit] = mvals[pos[hit]]
+    return out

@@ -123,3 +123,21 @@ def test_features_on_disk_give_the_same_job(tmp_path, capfd):
         assert p["objv"] == q["objv"] and p["nnz_w"] == q["nnz_w"]
     assert models[0] == models[1] and len(models[0]) > 0
     assert progs[2][-1]["objv"] < progs[2][0]["objv"]                    # bounded delay: runs and converges
+
+
+def test_warm_start_from_a_model_dump(tmp_path):
+    """init_w { type: FILE }: a second job starts from the dump of the first and carries on from its objective."""
+    off, idx, vals, y = planted(1200, 2048, 12, 7, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    first = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path / "a", lam=0.5, ratio=0.5, passes=4, tail=0)
+    p1 = run_local_threads(cfg.Flags(num_workers=2, num_servers=2, seed=0), first)
+    second = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path / "b", lam=0.5, ratio=0.5, passes=1, tail=0)
+    second = second.replace("loss {", 'init_w { type: FILE file_name: "%s/model" }\n  loss {' % (tmp_path / "a"))
+    # other key ranges than the first job: three servers read the two parts
+    p2 = run_local_threads(cfg.Flags(num_workers=2, num_servers=3, seed=1), second)
+    assert p2[0]["objv"] < p1[-1]["objv"] * (1 + 1e-4)           # the dump keeps six digits
+    assert p2[0]["objv"] < p1[1]["objv"]                          # far below where a cold start is after two passes
+    cold = run_local_threads(cfg.Flags(num_workers=2, num_servers=3, seed=1), second.replace("type: FILE", "type: ZERO"))
+    assert cold[0]["objv"] > p2[0]["objv"] * 1.01

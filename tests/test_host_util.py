@@ -270,3 +270,33 @@ def test_native_darlin_block_steps(binary):
     assert aloc[c0 + 3] == 0 and wloc[c0 + 3] == 0 and np.allclose(np.delete(wloc[c0:c1], 3), np.delete(wn, 3))
     with pytest.raises(ValueError):
         H.darlin_block_gradient(indptr, indices, data, y, dual, delta, active, 0, cols + 5, 1)
+
+
+def test_model_lookup_and_margins_for_a_warm_start(tmp_path):
+    """The pieces a warm start is made of: weights of a key list from a model dump, and y * Xw from column-major data."""
+    import scipy.sparse as sp
+    import torch
+
+    from parameter_server_b200.models.darlin import margins_from_weights
+    from parameter_server_b200.utils.modelio import lookup_model, model_arrays, model_files, read_model_text, write_model_text
+
+    write_model_text(str(tmp_path / "m_S0"), [3, 9, 2**63 + 5], [0.5, -1.25, 2.0])
+    write_model_text(str(tmp_path / "m_S1"), [2**64 - 2], [4.0])
+    paths = model_files(str(tmp_path / "m"))
+    assert [p.rsplit("_", 1)[1] for p in paths] == ["S0", "S1"] and model_files(paths[0]) == [paths[0]]
+    mk, mv = model_arrays(read_model_text(*paths))
+    keys = np.array([1, 3, 4, 9, 2**63 + 5, 2**64 - 2, 2**64 - 1], dtype=np.uint64)
+    np.testing.assert_array_equal(lookup_model(mk, mv, keys), [0, 0.5, 0, -1.25, 2.0, 4.0, 0])
+    assert lookup_model(mk[:0], mv[:0], keys).sum() == 0 and len(lookup_model(mk, mv, keys[:0])) == 0
+
+    rng = np.random.default_rng(0)
+    for binary in (False, True):
+        X = sp.random(50, 30, density=0.2, format="csc", random_state=1, dtype=np.float64)
+        if binary:
+            X.data[:] = 1
+        y = np.where(rng.random(50) < 0.5, -1.0, 1.0)
+        w = rng.normal(size=30)
+        m = margins_from_weights(torch.from_numpy(X.indptr.astype(np.int64)), torch.from_numpy(X.indices.astype(np.int32)),
+                                 None if binary else torch.from_numpy(X.data.astype(np.float32)), torch.from_numpy(y.astype(np.float32)),
+                                 torch.from_numpy(w.astype(np.float32)))
+        np.testing.assert_allclose(m.numpy(), y * (X @ w), rtol=1e-4, atol=1e-5)
