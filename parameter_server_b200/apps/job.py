@@ -48,11 +48,17 @@ def run_node(rank: int, flags: cfg.Flags, hub=None, app_text: Optional[str] = No
             if lm.training_data.file and not files:
                 raise FileNotFoundError(f"no training file matches {list(lm.training_data.file)}")
             parts = H.divide_files(files, max(flags.num_workers, 1), int(flags.load_limit))
+            vparts = None
+            if lm.has("validation_data") and lm.validation_data.file:       # linear_method.cc:154-172
+                vfiles = H.search_files(cfg.data_files(lm.validation_data, H))
+                vparts = H.divide_files(vfiles, max(flags.num_workers, 1), int(flags.load_limit))
             workers = boot.group(H.kWorkerGroup)
             for nid in boot.group(H.kActiveGroup):
                 c = conf.copy()
                 if nid in workers:
                     c.linear_method.mutable("training_data").file = list(parts[workers.index(nid)])
+                    if vparts is not None:
+                        c.linear_method.mutable("validation_data").file = list(vparts[workers.index(nid)])
                 t = boot.submit(nid, payload=dumps(c).encode())
                 boot.wait_out(nid, t)
             app = make_app(ctx, conf, flags)

@@ -135,6 +135,10 @@ class LinearMethodNode:
             reply = self.evaluate()
         elif call.cmd == "SAVE_MODEL":
             self.save_model()
+        elif call.cmd == "COMPUTE_VALIDATION_AUC":
+            reply = self.validation_auc(msg.time)
+        elif call.cmd == "RECOVER":
+            pass                      # "FIXME" in the reference (linear_method.cc:90-93); recovery here = restart from a dump
         self.busy += time.time() - t0
         self.cust.reply(msg, payload=reply)
 
@@ -360,6 +364,37 @@ class LinearMethodNode:
             p.nnz_active_set = int(self.active.sum())
         return dumps(p, oneline=True).encode()
 
+    def validation_auc(self, T: int) -> bytes:
+        """COMPUTE_VALIDATION_AUC on a worker: read its validation files, pull the weights of their keys from the
+        servers, predict, and reply the histogram form of the AUC that the scheduler merges.  (The reference dispatches
+        the command and merges the replies, batch_solver.cc:114-123; its worker side is a commented-out sketch,
+        batch_solver.cc:437-480.)"""
+        data = cfg.AUCData()
+        vd = self.conf.validation_data
+        if not self.ctx.is_worker or not vd.file:
+            return dumps(data, oneline=True).encode()
+        H, P = self.H, self.param
+        fmt = getattr(H.TextFormat, vd.text if vd.has("text") else "LIBSVM")
+        cache = self.conf.local_cache.file[0] if self.conf.local_cache.file else "/tmp/psb200_cache/"
+        r = H.SlotReader()
+        r.init(cfg.data_files(vd, H), fmt, cache + f"{self.ctx.node_id}_valid/", True, bool(self.flags.shuffle_fea_id),
+               bool(self.flags.add_beta_feature), int(self.flags.line_limit), int(self.flags.load_data_max_mb_per_thread))
+        r.read(max(int(self.flags.num_threads), 1))
+        y = r.value(0).astype(np.float32)
+        off, idx, v = r.offset(1).astype(np.int64), r.index(1), r.value(1)
+        ukeys, inv = np.unique(idx, return_inverse=True)
+        t = T * K_PACE
+        P.cust.submit(H.kServerGroup, cmd=PULL, key=ukeys.tobytes(), time=t, key_range=(0, 2**64 - 1), channel=self.ch,
+                      erase_key_cache=True, wait=True)
+        _, w = P.take_pulled(t)
+        w = np.nan_to_num(w, nan=0.0) if len(w) == len(ukeys) else np.zeros(len(ukeys))
+        X = sp.csr_matrix((np.ones(len(idx)) if len(v) == 0 else v.astype(np.float64), inv, off), shape=(len(y), len(ukeys)))
+        auc = H.AUC()
+        auc.set_goodness(int(self.conf.solver.auc_goodness))
+        auc.add(y, (X @ w).astype(np.float32))
+        data.tp_key, data.tp_count, data.fp_key, data.fp_count = (list(a) for a in auc.data())
+        return dumps(data, oneline=True).encode()
+
     def save_model(self) -> None:
         if not self.ctx.is_server or not self.conf.model_output.file:
             return
@@ -463,6 +498,19 @@ class BatchScheduler:
                 reset = True
             else:
                 reset = False
+        if conf.has("validation_data") and conf.validation_data.file:
+            tv = self._submit(_call("COMPUTE_VALIDATION_AUC"))
+            auc = self.H.AUC()
+            auc.set_goodness(int(sol.auc_goodness))
+            for text in self.cust.take_replies(tv).values():
+                d = parse(text.decode(), cfg.AUCData)
+                auc.merge_data(list(d.tp_key), list(d.tp_count), list(d.fp_key), list(d.fp_count))
+            self.validation = dict(auc=auc.evaluate(), accuracy=auc.accuracy(0.0))
+            if self.progress:
+                self.progress[-1]["validation_auc"] = self.validation["auc"]
+                self.progress[-1]["validation_accuracy"] = self.validation["accuracy"]
+            if verbose:
+                print(f"\tEvaluation accuracy: {self.validation['accuracy']:.6g}, auc: {self.validation['auc']:.6g}", file=sys.stderr)
         self._submit(_call("SAVE_MODEL"))
         return self.progress
 

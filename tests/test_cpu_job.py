@@ -141,3 +141,35 @@ def test_warm_start_from_a_model_dump(tmp_path):
     assert p2[0]["objv"] < p1[1]["objv"]                          # far below where a cold start is after two passes
     cold = run_local_threads(cfg.Flags(num_workers=2, num_servers=3, seed=1), second.replace("type: FILE", "type: ZERO"))
     assert cold[0]["objv"] > p2[0]["objv"] * 1.01
+
+
+def test_validation_auc_after_training(tmp_path):
+    """validation_data in the job file: after the last pass the workers score their validation files with the servers'
+    weights and the scheduler merges the AUC histograms."""
+    from parameter_server_b200.runtime import host
+
+    off, idx, vals, y = planted(1600, 1024, 12, 11, False)
+    h = 1200
+    o = off.numpy()
+    write_libsvm_parts(str(tmp_path / "train"), off[:h + 1], idx[:o[h]], vals[:o[h]], y[:h], 2)
+    write_libsvm_parts(str(tmp_path / "valid"), off[h:] - off[h], idx[o[h]:], vals[o[h]:], y[h:], 2)
+    text = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.2, ratio=0.5, passes=4, tail=0)
+    text = text.replace("local_cache {", 'validation_data { format: TEXT text: LIBSVM file: "%s/part-.*" }\n  local_cache {' % (tmp_path / "valid"))
+    prog = run_local_threads(cfg.Flags(num_workers=2, num_servers=2, seed=0), text)
+    last = prog[-1]
+    assert 0.6 < last["validation_auc"] <= 1.0 and 0.55 < last["validation_accuracy"] <= 1.0
+    # the same numbers from the dumped model, computed exactly
+    model = {}
+    for i in (0, 1):
+        p = tmp_path / f"model_S{i}"
+        if p.exists():
+            model.update(read_model_text(str(p)))
+    w = np.zeros(1024)
+    for k, v in model.items():
+        w[k] = v
+    rows = np.repeat(np.arange(1600 - h), np.diff(o[h:]))
+    xw = np.bincount(rows, weights=w[idx.numpy()[o[h]:]], minlength=1600 - h)
+    yv = y.numpy()[h:]
+    exact = host().exact_auc(yv.astype(np.float32), xw.astype(np.float32))
+    assert last["validation_auc"] == pytest.approx(exact, abs=2e-3)          # histogram bins and the dump's six digits
+    assert last["validation_accuracy"] == pytest.approx(float(np.mean((xw >= 0) == (yv > 0))), abs=5e-3)
