@@ -59,6 +59,10 @@ class SharedParam:
         self.filter = H.FrequencyFilter()
         self.pulled: Dict[int, Dict[str, tuple]] = {}
         self.lock = threading.Lock()
+        # -parallel_match: the server's merge-join of a push into its key list runs on -num_threads threads
+        # (src/parameter/kv_vector.h:77-137)
+        fl = getattr(solver, "flags", None)
+        self.match_threads = max(int(fl.num_threads), 1) if fl is not None and bool(fl.parallel_match) else 1
         self.cust = H.Customer(ctx.po, name, self.process, True)
 
     # executor thread of this customer
@@ -77,7 +81,7 @@ class SharedParam:
                 vals = np.frombuffer(msg.values[0], dtype=np.float64)
                 nval = len(vals) // max(len(keys), 1) if len(keys) else 2
                 lo, hi = msg.key_range
-                self.kv.aggregate(msg.channel, msg.time, lo, hi, keys, vals, nval, 1)
+                self.kv.aggregate(msg.channel, msg.time, lo, hi, keys, vals, nval, self.match_threads)
         elif msg.request and msg.cmd == PULL:
             if msg.aux > 0:       # query_key_freq: reply the keys seen more than aux times
                 kept = self.filter.query_keys(keys, msg.aux)

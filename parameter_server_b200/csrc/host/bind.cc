@@ -111,6 +111,8 @@ PYBIND11_MODULE(_psb_host, m) {
   m.def("shuffle_feature_id", &shuffle_feature_id);
   m.def("djb_hash32", &djb_hash32);
   m.def("key_signature", [](py::bytes b) { return key_signature(b); });
+  m.def("interfaces", &LocalMachine::interfaces, "(name, IPv4 address) of every interface that is up, loopback last");
+  m.def("local_ip", &LocalMachine::ip, py::arg("interface") = std::string());
   m.def("resource_usage", [] {
     double rss, virt; uint64_t pj, hj, in, out;
     ResUsage::memory_mb(&rss, &virt); ResUsage::cpu_jiffies(&pj, &hj); ResUsage::net_bytes(&in, &out);

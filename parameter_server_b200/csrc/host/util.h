@@ -7,6 +7,10 @@
 // threadsafe_limited_set.h, threadsafe_map.h, parallel_sort.h, kv_partition.h, recordio.h,
 // file.{h,cc}, filelinereader.{h,cc}, status.h.
 #pragma once
+#include <arpa/inet.h>
+#include <ifaddrs.h>
+#include <net/if.h>
+#include <netinet/in.h>
 #include <zlib.h>
 
 #include <algorithm>
@@ -374,6 +378,32 @@ std::vector<size_t> kv_partition(K* keys, V* vals, size_t n, const std::vector<K
 
 // ------------------------------------------------------------------ files
 // Sequential reader over plain or gzip files (zlib's gz layer reads both transparently).
+// Network interfaces of this machine (src/util/local_machine.h: IP(interface), pickupAvailableInterfaceAndIP).
+// A node of a job that spans machines advertises the address of -interface, or of the first interface that
+// is up and not the loopback.
+struct LocalMachine {
+  // (name, IPv4 address) of every interface that is up, loopback last
+  static std::vector<std::pair<std::string, std::string>> interfaces() {
+    std::vector<std::pair<std::string, std::string>> out, lo;
+    ifaddrs* list = nullptr;
+    if (getifaddrs(&list) != 0) return out;
+    for (ifaddrs* a = list; a; a = a->ifa_next) {
+      if (!a->ifa_addr || a->ifa_addr->sa_family != AF_INET || !(a->ifa_flags & IFF_UP)) continue;
+      char buf[INET_ADDRSTRLEN] = {0};
+      inet_ntop(AF_INET, &reinterpret_cast<sockaddr_in*>(a->ifa_addr)->sin_addr, buf, sizeof(buf));
+      ((a->ifa_flags & IFF_LOOPBACK) ? lo : out).emplace_back(a->ifa_name, buf);
+    }
+    freeifaddrs(list);
+    out.insert(out.end(), lo.begin(), lo.end());
+    return out;
+  }
+  // address of `interface`; empty name: the first interface that is not the loopback, else the loopback; "" if none
+  static std::string ip(const std::string& interface = std::string()) {
+    for (auto& kv : interfaces()) if (interface.empty() || kv.first == interface) return kv.second;
+    return std::string();
+  }
+};
+
 // Files on HDFS.  A path "hdfs:<path>" is read through a pipe from `<hadoop fs command> -cat <path>` and a
 // directory "hdfs:<dir>" is listed with `-ls`, like the reference (src/util/file.cc:50-66, 270-300; its
 // hadoopFS() hard-codes a user name, here the command is set from the job's HDFSConfig).  Read-only.

@@ -71,6 +71,21 @@ class NodeContext:
         self.po.stop()
 
 
+def advertised_address(scheduler_host: str, interface: str = "") -> str:
+    """The address other nodes use to reach this one.  A job whose scheduler is on the loopback runs on one machine
+    and stays there; otherwise the address of ``-interface``, or of the first interface that is up and not the
+    loopback (src/system/van.cc:262-275)."""
+    H = host()
+    if interface:
+        ip = H.local_ip(interface)
+        if not ip:
+            raise ValueError(f"-interface {interface}: no such interface with an IPv4 address ({H.interfaces()})")
+        return ip
+    if scheduler_host in ("127.0.0.1", "localhost", ""):
+        return "127.0.0.1"
+    return H.local_ip("") or "127.0.0.1"
+
+
 def start_node(rank: int, flags: cfg.Flags, hub=None, timeout_s: float = 60.0) -> NodeContext:
     """Create the van + post office of rank ``rank`` and join the job (blocks until the node table is known).
 
@@ -81,7 +96,7 @@ def start_node(rank: int, flags: cfg.Flags, hub=None, timeout_s: float = 60.0) -
     role, nid = role_of_rank(rank, W, S)
     sched = cfg.parse_node(flags.scheduler)
     sched_node = H.Node(H.SCHEDULER, sched.id or "H", sched.hostname or "127.0.0.1", sched.port)
-    me = H.Node(role, nid, "127.0.0.1", sched.port if role == H.SCHEDULER else 0)
+    me = H.Node(role, nid, advertised_address(sched.hostname or "127.0.0.1", flags.interface), sched.port if role == H.SCHEDULER else 0)
     if hub is not None:
         van = H.InprocVan(hub, me)
     else:

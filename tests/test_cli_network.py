@@ -1,0 +1,94 @@
+"""Addresses of CPU nodes: a job whose scheduler is not on the loopback makes every node advertise the address of a
+real interface (-interface, or the first one that is up), so that nodes on other machines can reach it."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from parameter_server_b200.data.synthetic import write_libsvm_parts
+from parameter_server_b200.runtime import host
+from parameter_server_b200.runtime.node import advertised_address
+from parameter_server_b200.utils.modelio import read_model_text
+from test_cpu_job import CONF, planted
+from test_rank_monitor import _free_port
+
+
+def test_interface_table():
+    H = host()
+    table = H.interfaces()
+    assert table and table[-1][1].startswith("127.")                  # loopback last
+    assert H.local_ip(table[0][0]) == table[0][1] and H.local_ip("no_such_if0") == ""
+    assert advertised_address("127.0.0.1") == "127.0.0.1"             # single-machine job stays on the loopback
+    assert advertised_address("10.1.2.3") == H.local_ip("")
+    assert advertised_address("127.0.0.1", table[0][0]) == table[0][1]
+    with pytest.raises(ValueError):
+        advertised_address("10.1.2.3", "no_such_if0")
+
+
+def test_job_over_a_real_interface(tmp_path):
+    ip = host().local_ip("")
+    if not ip or ip.startswith("127."):
+        pytest.skip("no interface besides the loopback")
+    off, idx, vals, y = planted(600, 512, 8, 2, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    conf = tmp_path / "job.conf"
+    conf.write_text(CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.5, ratio=0.5, passes=2, tail=0))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sched = f"role:SCHEDULER,hostname:'{ip}',port:{_free_port()},id:'H'"
+    r = subprocess.run([sys.executable, "-m", "parameter_server_b200.launch", "-num_servers", "2", "-num_workers", "2",
+                        "-app", str(conf), "-scheduler", sched, "-print_van", "-parallel_match", "-num_threads", "3"],
+                       cwd=tmp_path, env=dict(os.environ, PYTHONPATH=root), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    model = {}
+    for s_ in ("S0", "S1"):
+        model.update(read_model_text(str(tmp_path / f"model_{s_}")))
+    assert len(model) > 10
+    log = open(tmp_path / "van_W0").read()                              # -print_van: the worker's message log
+    assert "S0" in log and "S1" in log
+
+
+FAKE_MPIRUN = r'''#!/bin/sh
+# stand-in for mpirun: -np N --hostfile F cmd... -> N local processes with PMI_RANK set
+[ "$1" = "-np" ] || exit 2
+n=$2; shift 2
+[ "$1" = "--hostfile" ] || exit 2
+echo "$2" > "$FAKE_MPI_LOG"; shift 2
+echo "$@" >> "$FAKE_MPI_LOG"
+pids=""
+i=0
+while [ $i -lt $n ]; do
+  PMI_RANK=$i "$@" &
+  pids="$pids $!"
+  i=$((i+1))
+done
+rc=0
+for p in $pids; do wait $p || rc=1; done
+exit $rc
+'''
+
+
+def test_mpirun_launch(tmp_path):
+    """-mpi_hostfile: one mpirun line starts all ranks; every rank reads its rank from the MPI environment and the
+    scheduler's address is this machine's."""
+    ip = host().local_ip("")
+    bindir = tmp_path / "bin"
+    bindir.mkdir()
+    exe = bindir / "mpirun"
+    exe.write_text(FAKE_MPIRUN)
+    exe.chmod(0o755)
+    (tmp_path / "hosts").write_text("localhost slots=8\n")
+    off, idx, vals, y = planted(600, 512, 8, 2, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    conf = tmp_path / "job.conf"
+    conf.write_text(CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.5, ratio=0.5, passes=2, tail=0))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root, PATH=str(bindir) + os.pathsep + os.environ["PATH"], FAKE_MPI_LOG=str(tmp_path / "mpi.log"))
+    r = subprocess.run([sys.executable, "-m", "parameter_server_b200.launch", "-mpi_hostfile", str(tmp_path / "hosts"),
+                        "-num_servers", "1", "-num_workers", "2", "-app", str(conf)],
+                       cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    hostfile, line = open(tmp_path / "mpi.log").read().splitlines()[:2]
+    assert hostfile == str(tmp_path / "hosts")
+    assert "parameter_server_b200.ps" in line and "-my_rank" not in line and f"hostname:'{ip}'" in line and "mpi_hostfile" not in line
+    assert len(read_model_text(str(tmp_path / "model_S0"))) > 10
