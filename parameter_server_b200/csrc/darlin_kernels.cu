@@ -193,16 +193,64 @@ __device__ __forceinline__ int64_t find_col_warp(const int64_t* col_ptr, int64_t
   return j;
 }
 
+// Build option PSB_DARLIN_RANGE_WALK (off by default): without the per-non-zero column array a warp takes one
+// contiguous share of the block's positions instead of every nwarps-th group of 32, so that only its first
+// group needs a bisection; every later group starts its walk at the column where the previous one ended.
+#ifdef PSB_DARLIN_RANGE_WALK
+constexpr bool kRangeWalk = true;
+#else
+constexpr bool kRangeWalk = false;
+#endif
+
+// Share of warp `gwarp` of the positions [p0, p1): a multiple of 32 long, so only the last share is ragged.
+__device__ __forceinline__ void warp_share(int64_t p0, int64_t p1, size_t gwarp, size_t nwarps, int64_t* b, int64_t* e) {
+  const int64_t per = (((p1 - p0) + (int64_t)nwarps - 1) / (int64_t)nwarps + 31) & ~(int64_t)31;
+  const int64_t lo = p0 + (int64_t)gwarp * per;
+  *b = lo < p1 ? lo : p1;
+  *e = *b + per < p1 ? *b + per : p1;
+}
+
+// find_col_warp with a starting point: `hint` is the column found for this warp's previous 32 positions
+// (-1: none yet, bisect).  Must be called by all 32 lanes.
+__device__ __forceinline__ int64_t find_col_from(const int64_t* col_ptr, int64_t lo, int64_t hi, int64_t hint, int64_t e,
+                                                 bool valid) {
+  const int64_t e0 = __shfl_sync(0xffffffffu, e, 0);
+  int64_t j = 0;
+  if ((threadIdx.x & 31) == 0) {
+    if (hint < 0) {
+      j = find_col(col_ptr, lo, hi, e0);
+    } else {
+      j = hint;
+      for (int steps = 0; j + 1 < hi && col_ptr[j + 1] <= e0; ++j) {
+        if (++steps > 48) { j = find_col(col_ptr, j, hi, e0); break; }
+      }
+    }
+  }
+  j = __shfl_sync(0xffffffffu, j, 0);
+  if (valid) {
+    for (int steps = 0; j + 1 < hi && col_ptr[j + 1] <= e; ++j) {
+      if (++steps > 48) { j = find_col(col_ptr, j, hi, e); break; }
+    }
+  }
+  return j;
+}
+
 // ---- phase A: block gradient (G,U) pushed into the owners' accumulators
 __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
                                                  int64_t lc1, size_t gwarp, size_t nwarps, int lane) {
   const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
   const bool binary = Wk.vals == nullptr;
-  for (int64_t base = p0 + (int64_t)gwarp * 32; base < p1; base += (int64_t)nwarps * 32) {
+  const bool shares = kRangeWalk && Wk.col_of == nullptr;
+  int64_t base = p0 + (int64_t)gwarp * 32, end = p1, step = (int64_t)nwarps * 32, hint = -1;
+  if (shares) { warp_share(p0, p1, gwarp, nwarps, &base, &end); step = 32; }
+  for (; base < end; base += step) {
     const int64_t e = base + lane;
-    const bool valid = e < p1;
+    const bool valid = e < end;
     // the warp-level search is collective: every lane takes part, valid or not
-    const int64_t jc = Wk.col_of ? (valid ? (int64_t)Wk.col_of[e] : -1) : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
+    const int64_t jc = Wk.col_of ? (valid ? (int64_t)Wk.col_of[e] : -1)
+                       : shares  ? find_col_from(Wk.col_ptr, lc0, lc1, hint, e, valid)
+                                 : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
+    if (shares) hint = __shfl_sync(0xffffffffu, jc, 31);
     int64_t j = -1;
     float g = 0.f, u = 0.f;
     if (valid) {
@@ -323,10 +371,16 @@ __device__ __forceinline__ void darlin_pull_margin(const DarlinWorker& Wk, const
   const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
   const int lane = threadIdx.x & 31;
   // warp-uniform trip count (gsz is a multiple of 32): the column search without col_of is a warp collective
-  for (int64_t base = p0 + (int64_t)gtid - lane; base < p1; base += (int64_t)gsz) {
+  const bool shares = kRangeWalk && Wk.col_of == nullptr;
+  int64_t base = p0 + (int64_t)gtid - lane, end = p1, step = (int64_t)gsz, hint = -1;
+  if (shares) { warp_share(p0, p1, gtid >> 5, gsz >> 5, &base, &end); step = 32; }
+  for (; base < end; base += step) {
     const int64_t e = base + lane;
-    const bool valid = e < p1;
-    const int64_t j = Wk.col_of ? (valid ? (int64_t)Wk.col_of[e] : -1) : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
+    const bool valid = e < end;
+    const int64_t j = Wk.col_of ? (valid ? (int64_t)Wk.col_of[e] : -1)
+                      : shares  ? find_col_from(Wk.col_ptr, lc0, lc1, hint, e, valid)
+                                : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
+    if (shares) hint = __shfl_sync(0xffffffffu, j, 31);
     if (!valid || !Wk.active[j]) continue;
     const float* wsrc = P.w[Wk.gowner[j]] + Wk.gslot[j];
     const float wn = P.world > 1 ? ld_relaxed_sys_f32(wsrc) : ld_relaxed_gpu_f32(wsrc);
