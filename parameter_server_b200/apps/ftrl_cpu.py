@@ -107,8 +107,27 @@ class FTRLNode:
         ch = 0
         last_push = None
         last_report, reported = time.time(), [0.0, 0]
+        # a reader thread parses ahead of the solver into a bounded buffer (FTRL::run's reader thread and
+        # threadsafeLimitedQueue, src/linear_method/ftrl.cc:38-59); parsing runs without the interpreter lock
+        import queue
+
+        ahead: "queue.Queue" = queue.Queue(maxsize=max(int(self.flags.num_threads), 2))
+
+        def read_ahead():
+            try:
+                while True:
+                    out = reader.read(mb)
+                    ahead.put(out)
+                    if out is None:
+                        return
+            except BaseException as e:          # hand the error to the solver thread instead of dying silently
+                ahead.put(e)
+
+        threading.Thread(target=read_ahead, name=f"{self.ctx.node_id}-reader", daemon=True).start()
         while True:
-            out = reader.read(mb)
+            out = ahead.get()
+            if isinstance(out, BaseException):
+                raise out
             if out is None:
                 break
             slots, info = out
