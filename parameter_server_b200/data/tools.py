@@ -9,6 +9,7 @@ Counterparts of the reference's ``text2proto`` / ``proto2bin`` / ``showins`` pro
   python -m parameter_server_b200.data.tools show out/train
   python -m parameter_server_b200.data.tools info ADFEA 'data/ctr/part-.*'
   python -m parameter_server_b200.data.tools bin2text out/train out/train.libsvm
+  python -m parameter_server_b200.data.tools split rcv1_train.binary rcv1 1000 13   # train/part-000.. + test/part-013..
 """
 from __future__ import annotations
 
@@ -83,6 +84,39 @@ def bin2text(name: str, out_path: str) -> int:
     return m["rows"]
 
 
+def split_parts(path: str, out_dir: str, lines_per_part: int = 1000, train_parts: int = 13) -> dict:
+    """Cut a text data set (plain, gzip or bzip2) into ``part-NNN`` files of ``lines_per_part`` lines: the first
+    ``train_parts`` go to ``<out_dir>/train``, the rest to ``<out_dir>/test`` — the layout the reference's dataset
+    script produces for rcv1 (data/rcv1_binary.sh:11-36; its download step needs a network and is left to the user)."""
+    import bz2
+    import gzip
+    import os
+
+    opener = bz2.open if path.endswith(".bz2") else gzip.open if path.endswith(".gz") else open
+    train, test = os.path.join(out_dir, "train"), os.path.join(out_dir, "test")
+    for d in (train, test):
+        os.makedirs(d, exist_ok=True)
+        for old in os.listdir(d):
+            if old.startswith("part-"):
+                os.remove(os.path.join(d, old))
+    counts = {"train": 0, "test": 0, "lines": 0}
+    out, part = None, -1
+    with opener(path, "rt") as f:
+        for n, line in enumerate(f):
+            if n % lines_per_part == 0:
+                if out:
+                    out.close()
+                part += 1
+                which = "train" if part < train_parts else "test"
+                counts[which] += 1
+                out = open(os.path.join(train if which == "train" else test, f"part-{part:03d}"), "w")
+            out.write(line)
+            counts["lines"] += 1
+    if out:
+        out.close()
+    return counts
+
+
 def main(argv=None) -> int:
     a = list(sys.argv[1:] if argv is None else argv)
     if not a:
@@ -96,6 +130,8 @@ def main(argv=None) -> int:
         print(info(a[1], a[2]))
     elif a[0] == "bin2text":
         print(bin2text(a[1], a[2]))
+    elif a[0] == "split":
+        print(split_parts(a[1], a[2], int(a[3]) if len(a) > 3 else 1000, int(a[4]) if len(a) > 4 else 13))
     else:
         print(__doc__)
         return 2

@@ -30,3 +30,24 @@ def test_chrome_trace_and_metrics(tmp_path):
     ml.log(examples_per_s=1.5e8, step=3)
     rec = json.loads(open(tmp_path / "m.jsonl").read().strip())
     assert rec["step"] == 3 and "time" in rec
+
+
+def test_split_into_train_and_test_parts(tmp_path):
+    """The dataset script's layout: 1000-line parts, the first 13 for training, the rest for testing (here: 10 / 3)."""
+    import bz2
+
+    from parameter_server_b200.data import tools
+
+    lines = [f"{'+1' if i % 3 else '-1'} {i % 50 + 1}:1 {i % 7 + 60}:0.5\n" for i in range(47)]
+    src = tmp_path / "toy.binary.bz2"
+    with bz2.open(src, "wt") as f:
+        f.writelines(lines)
+    (tmp_path / "out" / "train").mkdir(parents=True)
+    (tmp_path / "out" / "train" / "part-999").write_text("stale\n")          # an earlier split is cleared, like rm -f
+    assert tools.main(["split", str(src), str(tmp_path / "out"), "10", "3"]) == 0
+    tr = sorted(p.name for p in (tmp_path / "out" / "train").iterdir())
+    te = sorted(p.name for p in (tmp_path / "out" / "test").iterdir())
+    assert tr == ["part-000", "part-001", "part-002"] and te == ["part-003", "part-004"]
+    back = "".join((tmp_path / "out" / d / n).read_text() for d, names in (("train", tr), ("test", te)) for n in names)
+    assert back == "".join(lines)
+    assert len((tmp_path / "out" / "test" / "part-004").read_text().splitlines()) == 7
