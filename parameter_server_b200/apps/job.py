@@ -62,9 +62,22 @@ def run_node(rank: int, flags: cfg.Flags, hub=None, app_text: Optional[str] = No
                 t = boot.submit(nid, payload=dumps(c).encode())
                 boot.wait_out(nid, t)
             app = make_app(ctx, conf, flags)
+            stop_monitor = threading.Event()
+            if float(flags.report_interval) > 0:
+                # the scheduler's monitor thread: the heartbeat table every report interval (postoffice.cc:271-290)
+                import sys
+
+                from ..runtime.node import dashboard
+
+                def monitor():
+                    while not stop_monitor.wait(float(flags.report_interval)):
+                        print(dashboard(ctx.po), file=sys.stderr, flush=True)
+
+                threading.Thread(target=monitor, name="H-monitor", daemon=True).start()
             try:
                 return app.run(verbose=verbose)
             finally:
+                stop_monitor.set()
                 ctx.po.stop_all()
                 app.stop()
                 boot.stop()

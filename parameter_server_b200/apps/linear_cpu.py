@@ -126,6 +126,8 @@ class LinearMethodNode:
             return
         call = parse(msg.payload.decode(), cfg.LMCall)
         t0 = time.time()
+        if self.ctx.hb_state is not None:
+            self.ctx.hb_state["task"] = msg.time          # the task this node is at, for the scheduler's table
         reply = b""
         if call.cmd == "LOAD_DATA":
             reply = self.load_data()
@@ -134,6 +136,7 @@ class LinearMethodNode:
         elif call.cmd == "UPDATE_MODEL":
             self.update_model(msg, call)
             self.busy += time.time() - t0
+            self.ctx.add_busy(time.time() - t0)
             return
         elif call.cmd == "EVALUATE_PROGRESS":
             reply = self.evaluate()
@@ -144,6 +147,7 @@ class LinearMethodNode:
         elif call.cmd == "RECOVER":
             pass                      # "FIXME" in the reference (linear_method.cc:90-93); recovery here = restart from a dump
         self.busy += time.time() - t0
+        self.ctx.add_busy(time.time() - t0)
         self.cust.reply(msg, payload=reply)
 
     # ------------------------------------------------------------------ LOAD_DATA

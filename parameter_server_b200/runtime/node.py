@@ -24,22 +24,52 @@ def role_of_rank(rank: int, num_workers: int, num_servers: int):
     return H.UNUSED, f"U{rank - num_workers - num_servers - 1}"
 
 
+def _host_stats() -> dict:
+    """Busy / total jiffies of the machine and its memory in use, from /proc (zeros where /proc is absent)."""
+    out = dict(busy=0, total=0, used_gb=0, used_pct=0)
+    try:
+        with open("/proc/stat") as f:
+            v = [int(x) for x in f.readline().split()[1:]]
+        out["total"] = sum(v)
+        out["busy"] = sum(v) - v[3] - (v[4] if len(v) > 4 else 0)          # all but idle and iowait
+        mem = {}
+        with open("/proc/meminfo") as f:
+            for line in f:
+                k, _, rest = line.partition(":")
+                mem[k] = int(rest.split()[0])
+        used = mem.get("MemTotal", 0) - mem.get("MemAvailable", mem.get("MemFree", 0))
+        out["used_gb"] = used >> 20
+        out["used_pct"] = int(100 * used / max(mem.get("MemTotal", 1), 1))
+    except (OSError, ValueError, IndexError):
+        pass
+    return out
+
+
 def heartbeat_report(node_id: str, state: dict) -> str:
-    """Text-format ``HeartbeatReport`` of this process (src/system/heartbeat_info.cc:37-155)."""
+    """Text-format ``HeartbeatReport`` of this process (src/system/heartbeat_info.cc:37-155): CPU share of the process
+    and of the machine since the previous report, memory of both, time spent in compute sections (``busy_ms``, added
+    by the application), network totals and rates."""
+    import socket
+
     H = host()
     u = H.resource_usage()
+    hs = _host_stats()
     now = time.time()
     dt = max(now - state.get("t", now - 1.0), 1e-3)
     d_proc = u["proc_jiffies"] - state.get("proc", u["proc_jiffies"])
     d_host = max(u["host_jiffies"] - state.get("host", u["host_jiffies"]), 1)
+    d_busy = hs["busy"] - state.get("hbusy", hs["busy"])
+    d_total = max(hs["total"] - state.get("htotal", hs["total"]), 1)
     r = cfg.HeartbeatReport(
-        hostname=node_id, seconds_since_epoch=int(now), total_time_milli=int(dt * 1000),
+        task_id=int(state.get("task", 0)), hostname=f"{node_id}@{socket.gethostname()}", seconds_since_epoch=int(now), total_time_milli=int(dt * 1000),
         busy_time_milli=int(state.get("busy_ms", 0)), net_in_mb=int(u["net_in"] >> 20), net_out_mb=int(u["net_out"] >> 20),
-        process_cpu_usage=int(100 * d_proc / d_host * (state.get("ncpu", 1))), host_cpu_usage=0,
+        process_cpu_usage=int(100 * d_proc / d_host * (state.get("ncpu", 1))), host_cpu_usage=int(100 * d_busy / d_total),
         process_rss_mb=int(u["rss_mb"]), process_virt_mb=int(u["virt_mb"]),
+        host_in_use_gb=int(hs["used_gb"]), host_in_use_percentage=int(hs["used_pct"]),
         host_net_in_bw=int((u["net_in"] - state.get("in", u["net_in"])) / dt / 1e6),
         host_net_out_bw=int((u["net_out"] - state.get("out", u["net_out"])) / dt / 1e6))
-    state.update(t=now, proc=u["proc_jiffies"], host=u["host_jiffies"], **{"in": u["net_in"], "out": u["net_out"]})
+    state.update(t=now, proc=u["proc_jiffies"], host=u["host_jiffies"], hbusy=hs["busy"], htotal=hs["total"],
+                 **{"in": u["net_in"], "out": u["net_out"]})
     state["busy_ms"] = 0
     from ..utils.pbtext import dumps
 
@@ -54,6 +84,11 @@ class NodeContext:
     role: int
     num_workers: int
     num_servers: int
+    hb_state: dict = None          # heartbeat bookkeeping; applications add their compute time to hb_state["busy_ms"]
+
+    def add_busy(self, seconds: float) -> None:
+        if self.hb_state is not None:
+            self.hb_state["busy_ms"] = self.hb_state.get("busy_ms", 0) + 1000.0 * seconds
 
     @property
     def is_scheduler(self) -> bool:
@@ -110,7 +145,7 @@ def start_node(rank: int, flags: cfg.Flags, hub=None, timeout_s: float = 60.0) -
     po.set_key_cache(bool(flags.key_cache))
     po.set_scheduler(sched_node if role != H.SCHEDULER else van.my_node)
     po.start()
-    ctx = NodeContext(po, van, nid, role, W, S)
+    ctx = NodeContext(po, van, nid, role, W, S, hb_state={})
     if role == H.SCHEDULER:
         if not po.wait_nodes_and_init(timeout_s):
             raise TimeoutError("scheduler: not every worker/server registered in time")
@@ -119,8 +154,7 @@ def start_node(rank: int, flags: cfg.Flags, hub=None, timeout_s: float = 60.0) -
         if not po.wait_nodes_ready(timeout_s):
             raise TimeoutError(f"{nid}: no node table from the scheduler")
         if flags.report_interval > 0:
-            st: dict = {}
-            po.start_heartbeat(float(flags.report_interval), lambda: heartbeat_report(nid, st))
+            po.start_heartbeat(float(flags.report_interval), lambda: heartbeat_report(nid, ctx.hb_state))
     return ctx
 
 
@@ -128,7 +162,7 @@ def dashboard(po) -> str:
     """The scheduler's heartbeat table (src/system/postoffice.cc:292-374)."""
     from ..utils.pbtext import parse
 
-    rows = ["Node  Task  MyCPU%  MyRSS  MyVir  Busy(ms)  InMB  OutMB  age(s)"]
+    rows = ["Node  Task  MyCPU%  MyRSS  MyVir  Busy(ms)  Busy%  InMB  OutMB  HostCPU%  HostUseGB(%)  HostInBW  HostOutBW  age(s)  HostName"]
 
     def order(k):
         return (k[0], int(k[1:]) if k[1:].isdigit() else 0)
@@ -138,8 +172,12 @@ def dashboard(po) -> str:
         age, text = hb[nid]
         try:
             r = parse(text.decode(), cfg.HeartbeatReport)
-            rows.append(f"{nid:<5} {po.last_task_of('default'):>4}  {r.process_cpu_usage:>6}  {r.process_rss_mb:>5}  "
-                        f"{r.process_virt_mb:>5}  {r.busy_time_milli:>8}  {r.net_in_mb:>4}  {r.net_out_mb:>5}  {age:6.2f}")
+            busy_pct = int(100 * r.busy_time_milli / max(r.total_time_milli, 1))
+            use = f"{r.host_in_use_gb}({r.host_in_use_percentage}%)"
+            rows.append(f"{nid:<5} {r.task_id:>4}  {r.process_cpu_usage:>6}  {r.process_rss_mb:>5}  "
+                        f"{r.process_virt_mb:>5}  {r.busy_time_milli:>8}  {busy_pct:>5}  {r.net_in_mb:>4}  {r.net_out_mb:>5}  "
+                        f"{r.host_cpu_usage:>8}  {use:>12}  "
+                        f"{r.host_net_in_bw:>8}  {r.host_net_out_bw:>9}  {age:6.2f}  {r.hostname}")
         except Exception:
             rows.append(f"{nid:<5} (no report yet)  {age:6.2f}")
     return "\n".join(rows)

@@ -173,3 +173,21 @@ def test_validation_auc_after_training(tmp_path):
     exact = host().exact_auc(yv.astype(np.float32), xw.astype(np.float32))
     assert last["validation_auc"] == pytest.approx(exact, abs=2e-3)          # histogram bins and the dump's six digits
     assert last["validation_accuracy"] == pytest.approx(float(np.mean((xw >= 0) == (yv > 0))), abs=5e-3)
+
+
+def test_heartbeats_and_dashboard(tmp_path, capfd):
+    """-report_interval: nodes report their resource use, the scheduler prints the table while the job runs."""
+    off, idx, vals, y = planted(2000, 2048, 12, 3, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    text = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.5, ratio=4.0, passes=6, tail=0)
+    run_local_threads(cfg.Flags(num_workers=2, num_servers=1, seed=0, report_interval=0.1), text)
+    err = capfd.readouterr().err
+    head = [l for l in err.splitlines() if l.startswith("Node  Task")]
+    assert head and "HostCPU%" in head[0] and "HostName" in head[0]
+    rows = [l for l in err.splitlines() if l.startswith(("W0 ", "W1 ", "S0 "))]
+    full = [l for l in rows if "no report yet" not in l]
+    assert full, err[-2000:]
+    cols = full[-1].split()
+    assert len(cols) == 15 and "@" in cols[-1]                      # every column filled, host name last
+    assert any(int(l.split()[5]) > 0 for l in full)                 # some compute time was reported as busy
+    assert max(int(l.split()[1]) for l in full) > 10                # and the task each node was at
