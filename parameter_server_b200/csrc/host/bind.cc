@@ -111,6 +111,7 @@ PYBIND11_MODULE(_psb_host, m) {
   m.def("shuffle_feature_id", &shuffle_feature_id);
   m.def("djb_hash32", &djb_hash32);
   m.def("key_signature", [](py::bytes b) { return key_signature(b); });
+  m.def("set_verbose", [](bool on) { verbose_flag() = on; }, "executors narrate the messages they process (-verbose)");
   m.def("interfaces", &LocalMachine::interfaces, "(name, IPv4 address) of every interface that is up, loopback last");
   m.def("local_ip", &LocalMachine::ip, py::arg("interface") = std::string());
   m.def("resource_usage", [] {

@@ -17,6 +17,10 @@
 
 namespace psb {
 
+// -verbose: every executor narrates the messages it picks and those it holds back for a dependency
+// (src/system/executor.cc:95-133).
+inline std::atomic<bool>& verbose_flag() { static std::atomic<bool> v{false}; return v; }
+
 class TaskTracker {
  public:
   void start(int t) { std::lock_guard<std::mutex> l(mu_); task_.emplace(t, false); }
@@ -556,6 +560,7 @@ inline void Executor::init(const std::vector<Node>& nodes, const Node& me, int n
 inline void Executor::run() {
   for (;;) {
     MessagePtr msg;
+    size_t queued = 0;
     {
       std::unique_lock<std::mutex> l(mu_);
       for (;;) {
@@ -573,6 +578,7 @@ inline void Executor::run() {
           if (!(*it)->task.request || w <= kInvalidTime || s->incoming.try_wait(w)) {
             msg = *it;
             recved_.erase(it);
+            queued = recved_.size();
             break;
           }
         }
@@ -583,6 +589,9 @@ inline void Executor::run() {
     const bool req = msg->task.request;
     const int t = msg->task.time;
     RNodePtr sender = rnode(msg->sender);
+    if (verbose_flag())
+      std::fprintf(stderr, "[%s@%s] %s t=%d wait=%d from %s (%zu queued)\n", obj_->name().c_str(), po_->my_node().id.c_str(),
+                   req ? "request" : "reply", t, msg->task.wait_time, msg->sender.c_str(), queued);
     if (req) { sender->incoming.start(t); last_task_ = t; }
     if (msg->task.type != Task::REPLY && obj_->process) obj_->process(msg);
     ++processed;

@@ -77,6 +77,10 @@ def main(argv=None) -> int:
 
     redirect_logs(node_name(flags.my_rank, int(flags.num_workers), int(flags.num_servers)), bool(flags.log_to_file),
                   bool(flags.log_instant))
+    if bool(flags.verbose):
+        from .runtime import host
+
+        host().set_verbose(True)          # executors narrate every message they process
     run_node(flags.my_rank, flags, verbose=True)
     return 0
 

@@ -21,7 +21,7 @@ def test_every_node_logs_to_its_own_file(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
     r = subprocess.run([sys.executable, "-m", "parameter_server_b200.launch", "-num_servers", "1", "-num_workers", "1",
-                        "-app", str(conf), "-log_to_file", "-log_instant"], cwd=tmp_path, env=env, capture_output=True, text=True,
+                        "-app", str(conf), "-log_to_file", "-log_instant", "-verbose"], cwd=tmp_path, env=env, capture_output=True, text=True,
                        timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     logs = {n: glob.glob(str(tmp_path / f"log_{n}_*")) for n in ("H", "W0", "S0")}
@@ -30,3 +30,5 @@ def test_every_node_logs_to_its_own_file(tmp_path):
     assert "objective" in table and "|w|_0" in table          # the scheduler's progress table went to its file
     assert "objective" not in r.stderr                          # and not to the terminal
     assert (tmp_path / "model_S0").exists()
+    narration = open(logs["W0"][0]).read()                     # -verbose: the worker's executors tell what they process
+    assert "[plumb@W0] request t=" in narration and "[plumb_w@W0] reply t=" in narration
