@@ -21,6 +21,10 @@ def make_app(ctx: NodeContext, app_conf, flags: cfg.Flags):
     lm = app_conf.linear_method
     if not app_conf.has("linear_method"):
         raise ValueError("only linear_method apps run on CPU nodes")
+    if not lm.has("solver") and lm.has("validation_data") and lm.has("model_input"):
+        from .model_evaluation import ModelEvaluationNode
+
+        return ModelEvaluationNode(ctx, app_conf, flags)
     if lm.solver.minibatch_size <= 0:
         if not lm.has("darling"):
             raise ValueError("batch solver without darling{} is not available on CPU nodes; use the GPU engine")

@@ -191,3 +191,32 @@ def test_heartbeats_and_dashboard(tmp_path, capfd):
     assert len(cols) == 15 and "@" in cols[-1]                      # every column filled, host name last
     assert any(int(l.split()[5]) > 0 for l in full)                 # some compute time was reported as busy
     assert max(int(l.split()[1]) for l in full) > 10                # and the task each node was at
+
+
+def test_model_evaluation_app_on_cpu_nodes(tmp_path):
+    """A job file with validation_data + model_input and no solver runs the evaluation app: the scheduler scores the
+    validation files with the dumped model; the result equals the validation step of the training job."""
+    off, idx, vals, y = planted(1600, 1024, 12, 11, False)
+    h = 1200
+    o = off.numpy()
+    write_libsvm_parts(str(tmp_path / "train"), off[:h + 1], idx[:o[h]], vals[:o[h]], y[:h], 2)
+    write_libsvm_parts(str(tmp_path / "valid"), off[h:] - off[h], idx[o[h]:], vals[o[h]:], y[h:], 2)
+    text = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.2, ratio=0.5, passes=4, tail=0)
+    text = text.replace("local_cache {", 'validation_data { format: TEXT text: LIBSVM file: "%s/part-.*" }\n  local_cache {' % (tmp_path / "valid"))
+    trained = run_local_threads(cfg.Flags(num_workers=2, num_servers=2, seed=0), text)[-1]
+    ev = '''
+app_name: "eval" parameter_name: "eval_w"
+linear_method {
+  validation_data { format: TEXT text: LIBSVM file: "%s/part-.*" }
+  model_input { format: TEXT file: "%s/model_S.*" }
+  model_output { format: TEXT file: "%s/scores" }
+}''' % (tmp_path / "valid", tmp_path, tmp_path)
+    res = run_local_threads(cfg.Flags(num_workers=1, num_servers=1), ev)[0]
+    assert res["examples"] == 400 and res["model_nnz"] > 10
+    assert res["auc"] == pytest.approx(trained["validation_auc"], abs=2e-3)         # the dump keeps six digits
+    assert res["accuracy"] == pytest.approx(trained["validation_accuracy"], abs=5e-3)
+    assert res["auc"] == pytest.approx(res["exact_auc"], abs=2e-3)
+    L = np.fromfile(tmp_path / "scores_L", dtype=np.float32)
+    P = np.fromfile(tmp_path / "scores_P", dtype=np.float32)
+    np.testing.assert_array_equal(L, y.numpy()[h:])
+    assert len(P) == 400 and float(np.mean((P >= 0) == (L > 0))) == pytest.approx(res["accuracy"], abs=1e-6)
