@@ -175,23 +175,21 @@ class LinearMethodNode:
         allr = (0, 2**64 - 1)
         freq = solver.tail_feature_freq
         if self.ctx.is_worker:
-            ukeys, inv, cnt = np.unique(self.idx, return_inverse=True, return_counts=True)
+            # localisation in the native runtime (csrc/host/localizer.h): unique keys with counts, local column ids,
+            # column-major storage
+            T_ = max(int(self.flags.num_threads), 1)
+            ukeys, cnt = H.count_unique(self.idx, T_)
             if freq > 0:      # tail-feature filter through the servers' count-min sketch
                 P.cust.submit(H.kServerGroup, cmd=PUSH, key=ukeys.tobytes(), values=[cnt.astype(np.uint32).tobytes()],
                               time=t, key_range=allr, channel=self.ch, flags=F_INSERT_KEY_FREQ, wait=True)
                 P.cust.submit(H.kServerGroup, cmd=PULL, key=ukeys.tobytes(), time=t + 2, wait_time=t + 1, key_range=allr,
                               channel=self.ch, aux=freq, erase_key_cache=True, wait=True)
-                kept, _ = P.take_pulled(t + 2)
-                keep_col = np.isin(ukeys, kept)
-                sel = keep_col[inv]
-                rows = np.repeat(np.arange(len(self.y)), np.diff(self.off))[sel]
-                self.idx, self.val = self.idx[sel], self.val[sel]
-                self.off = np.concatenate([[0], np.cumsum(np.bincount(rows, minlength=len(self.y)))]).astype(np.int64)
-                ukeys, inv = np.unique(self.idx, return_inverse=True)
+                ukeys, _ = P.take_pulled(t + 2)           # the surviving keys, ascending (servers answer in key order)
             self.keys = ukeys
-            rows = np.repeat(np.arange(len(self.y)), np.diff(self.off))
-            self.X = sp.csc_matrix((self.val, (rows, inv)), shape=(len(self.y), len(ukeys)))
-            self._csc_cache = None
+            loc = H.remap_keys(self.idx, ukeys, T_)       # -1: dropped by the filter
+            indptr, rix, cval = H.csr_to_csc(self.off, loc, None if self.binary else self.val, len(ukeys), T_)
+            self._csc_cache = (indptr, rix, cval, np.ascontiguousarray(self.y, dtype=np.float64))
+            self.idx = self.val = self.off = None
             t2 = t + 4
             P.cust.submit(H.kServerGroup, cmd=PUSH, key=ukeys.tobytes(), time=t2, key_range=allr, channel=self.ch,
                           flags=F_INSERT_KEY, erase_key_cache=True, wait=True)
@@ -200,7 +198,11 @@ class LinearMethodNode:
             _, w0 = P.take_pulled(t2 + 2)
             n = len(ukeys)
             self.w = w0.copy() if len(w0) == n else np.zeros(n)
-            self.dual = np.exp(self.y * (self.X @ self.w))
+            xw = np.zeros(len(self.y))
+            if np.any(self.w != 0):
+                wcol = np.repeat(self.w, np.diff(indptr))
+                xw = np.bincount(rix, weights=wcol if cval is None else wcol * cval, minlength=len(self.y))
+            self.dual = np.exp(self.y * xw)
             self.delta = np.full(n, self.conf.darling.delta_init_value)
             self.active = np.ones(n, dtype=np.uint8)
             if bool(self.flags.mmap_training_data):
@@ -285,12 +287,7 @@ class LinearMethodNode:
     # The three block steps run in the native runtime (csrc/host/darlin_cpu.h): threaded column gradients, the
     # server's proximal-Newton update, the worker's dual update.
     def _csc(self):
-        if getattr(self, "_csc_cache", None) is None:
-            X = self.X
-            self._csc_cache = (np.ascontiguousarray(X.indptr, dtype=np.int64), np.ascontiguousarray(X.indices, dtype=np.int32),
-                               None if self.binary else np.ascontiguousarray(X.data, dtype=np.float64),
-                               np.ascontiguousarray(self.y, dtype=np.float64))
-        return self._csc_cache
+        return self._csc_cache            # (offsets per column, row ids, values or None, labels), built in preprocess
 
     def _to_station(self) -> None:
         """-mmap_training_data: the column-major features go to the local cache directory and leave memory;
@@ -303,9 +300,7 @@ class LinearMethodNode:
                                              int(self.flags.prefetch_job_limit), bool(self.flags.prefetch_detail))
         self.station.add_group(self.ch, len(y), indptr, indices, data)
         self._y = y
-        self.X = None
         self._csc_cache = None
-        self.idx = self.val = self.off = None
 
     def _prefetch_ahead(self, now: int) -> None:
         """Queue reads for the UPDATE_MODEL tasks that have arrived but not started, up to 4 (τ + 1) tasks ahead of

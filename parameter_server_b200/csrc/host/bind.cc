@@ -10,6 +10,7 @@
 #include "data.h"
 #include "feature_station.h"
 #include "kv.h"
+#include "localizer.h"
 #include "runtime.h"
 
 namespace py = pybind11;
@@ -125,6 +126,29 @@ PYBIND11_MODULE(_psb_host, m) {
     { py::gil_scoped_release r; parallel_sort(v.begin(), v.end(), threads, std::less<uint64_t>()); }
     return to_array(v);
   });
+  // ---- localisation: unique keys with counts, global -> local ids, row-major -> column-major
+  m.def("count_unique", [](carray<uint64_t> keys, int threads) {
+    std::vector<uint64_t> u; std::vector<uint32_t> c;
+    { py::gil_scoped_release r; count_unique(keys.data(), (size_t)keys.size(), threads, &u, &c); }
+    return py::make_tuple(to_array(u), to_array(c));
+  }, py::arg("keys"), py::arg("threads") = 1, "(sorted unique keys, their counts)");
+  m.def("remap_keys", [](carray<uint64_t> keys, carray<uint64_t> dict, int threads) {
+    py::array_t<int32_t> out(keys.size());
+    { py::gil_scoped_release r; remap_keys(keys.data(), (size_t)keys.size(), dict.data(), (size_t)dict.size(), threads, out.mutable_data()); }
+    return out;
+  }, py::arg("keys"), py::arg("dict"), py::arg("threads") = 1, "position of every key in the sorted dictionary, -1 where absent");
+  m.def("csr_to_csc", [](carray<int64_t> offsets, carray<int32_t> col, py::object vals, size_t cols, int threads) {
+    carray<double> dv;
+    const double* dp = nullptr;
+    if (!vals.is_none()) { dv = vals.cast<carray<double>>(); dp = dv.data(); }
+    if (offsets.size() < 1 || offsets.data()[offsets.size() - 1] != col.size() || (dp && dv.size() != col.size()))
+      throw std::invalid_argument("offsets, column ids and values do not fit together");
+    for (py::ssize_t i = 0; i < col.size(); ++i) if (col.data()[i] >= (int64_t)cols) throw std::invalid_argument("column id out of range");
+    std::vector<int64_t> ip; std::vector<int32_t> rows; std::vector<double> ov;
+    { py::gil_scoped_release r; csr_to_csc(offsets.data(), (size_t)offsets.size() - 1, col.data(), dp, cols, threads, &ip, &rows, &ov); }
+    return py::make_tuple(to_array(ip), to_array(rows), dp ? py::object(to_array(ov)) : py::object(py::none()));
+  }, py::arg("offsets"), py::arg("col"), py::arg("vals"), py::arg("cols"), py::arg("threads") = 1,
+     "(indptr, row ids, values or None) of the column-major form; column id -1 drops a non-zero");
   m.def("kv_partition", [](carray<uint64_t> keys, carray<double> vals, std::vector<uint64_t> pivots) {
     std::vector<uint64_t> k(keys.data(), keys.data() + keys.size());
     std::vector<double> v(vals.data(), vals.data() + vals.size());

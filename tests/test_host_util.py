@@ -300,3 +300,41 @@ def test_model_lookup_and_margins_for_a_warm_start(tmp_path):
                                  None if binary else torch.from_numpy(X.data.astype(np.float32)), torch.from_numpy(y.astype(np.float32)),
                                  torch.from_numpy(w.astype(np.float32)))
         np.testing.assert_allclose(m.numpy(), y * (X @ w), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("threads", [1, 4])
+def test_native_localizer(threads):
+    """Unique keys with counts, global -> local ids and the change to column-major storage against NumPy / SciPy."""
+    import scipy.sparse as sp
+
+    rng = np.random.default_rng(threads)
+    rows, nnz_row = 5000, 9
+    keys = (rng.integers(0, 3000, rows * nnz_row).astype(np.uint64) * np.uint64(6148914691236517)) + np.uint64(2**63)
+    off = np.arange(0, rows * nnz_row + 1, nnz_row, dtype=np.int64)
+    vals = rng.normal(size=len(keys))
+    u, c = H.count_unique(keys, threads)
+    ru, rc = np.unique(keys, return_counts=True)
+    np.testing.assert_array_equal(u, ru)
+    np.testing.assert_array_equal(c, rc)
+    # a dictionary that lacks every third key: those non-zeros are dropped
+    d = ru[np.arange(len(ru)) % 3 != 0]
+    loc = H.remap_keys(keys, d, threads)
+    pos = np.searchsorted(d, keys)
+    hit = (pos < len(d)) & (d[np.minimum(pos, len(d) - 1)] == keys)
+    np.testing.assert_array_equal(loc, np.where(hit, pos, -1))
+    for v in (vals, None):
+        ip, ri, ov = H.csr_to_csc(off, loc, v, len(d), threads)
+        row_of = np.repeat(np.arange(rows), nnz_row)[hit]
+        ref = sp.csr_matrix((np.ones(hit.sum()) if v is None else v[hit], (row_of, loc[hit])), shape=(rows, len(d)))
+        # duplicates inside a row stay separate entries here, SciPy sums them: compare through dense products
+        assert ip[-1] == hit.sum() and len(ri) == hit.sum() and (ov is None) == (v is None)
+        assert np.all(np.diff(ip) >= 0)
+        for j in (0, 7, len(d) - 1):
+            seg = ri[ip[j]:ip[j + 1]]
+            assert np.all(np.diff(seg) >= 0)                                  # rows ascend inside a column
+        x = rng.normal(size=rows)
+        got = np.zeros(len(d))
+        np.add.at(got, np.repeat(np.arange(len(d)), np.diff(ip)), x[ri] * (1.0 if ov is None else ov))
+        np.testing.assert_allclose(got, ref.T @ x, rtol=1e-9, atol=1e-9)
+    with pytest.raises(ValueError):
+        H.csr_to_csc(off, loc, None, 5, 1)
