@@ -160,16 +160,11 @@ class FTRLNode:
             pos_k = np.searchsorted(kept, ukeys)
             in_set = (pos_k < len(kept)) & (kept[np.minimum(pos_k, max(len(kept) - 1, 0))] == ukeys) if len(kept) else np.zeros(len(ukeys), bool)
             w_u = np.where(in_set, wk[np.minimum(pos_k, max(len(kept) - 1, 0))] if len(kept) else 0.0, 0.0)
-            row_of = np.repeat(np.arange(rows), np.diff(off))
-            xw = np.bincount(row_of, weights=w_u[inv] * val, minlength=rows)
-            m = y * xw
-            self.loss_sum += float(np.sum(np.logaddexp(0.0, -m)))
+            # margins, loss, per-key gradient and label counts in the native runtime (csrc/host/ftrl_cpu.h)
+            loss, g, pos, neg = H.ftrl_minibatch(off, inv, val if len(sl["value"]) else None, y, w_u, T_)
+            self.loss_sum += float(loss)
             self.examples += rows
             self.steps += 1
-            coef = -y / (1.0 + np.exp(m))
-            g = np.bincount(inv, weights=coef[row_of] * val, minlength=len(ukeys))
-            pos = np.bincount(inv, weights=(y[row_of] > 0).astype(np.float64), minlength=len(ukeys))
-            neg = np.bincount(inv, weights=(y[row_of] <= 0).astype(np.float64), minlength=len(ukeys))
             last_push = P.submit(H.kServerGroup, cmd=PUSH, key=ukeys[in_set].tobytes(),
                                  values=[g[in_set].tobytes(), pos[in_set].tobytes(), neg[in_set].tobytes()],
                                  key_range=ALL_KEYS, channel=ch, erase_key_cache=True)

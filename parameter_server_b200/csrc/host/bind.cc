@@ -9,6 +9,7 @@
 #include "darlin_cpu.h"
 #include "data.h"
 #include "feature_station.h"
+#include "ftrl_cpu.h"
 #include "kv.h"
 #include "localizer.h"
 #include "runtime.h"
@@ -317,6 +318,19 @@ PYBIND11_MODULE(_psb_host, m) {
         d["misses"] = s.misses; d["peak_resident"] = s.peak_resident; d["budget_waits"] = s.budget_waits;
         return d;
       });
+  m.def("ftrl_minibatch", [](carray<int64_t> off, carray<int32_t> loc, py::object vals, carray<double> y, carray<double> w, int threads) {
+    carray<double> dv;
+    const double* dp = nullptr;
+    if (!vals.is_none()) { dv = vals.cast<carray<double>>(); dp = dv.data(); }
+    const py::ssize_t rows = off.size() - 1, nk = w.size();
+    if (rows < 0 || y.size() != rows || off.data()[rows] != loc.size() || (dp && dv.size() != loc.size())) throw std::invalid_argument("minibatch arrays do not fit together");
+    for (py::ssize_t i = 0; i < loc.size(); ++i) if (loc.data()[i] < 0 || loc.data()[i] >= nk) throw std::invalid_argument("local key id out of range");
+    py::array_t<double> g(nk), pos(nk), neg(nk);
+    double loss;
+    { py::gil_scoped_release r; loss = ftrl_minibatch(off.data(), (size_t)rows, loc.data(), dp, y.data(), w.data(), (size_t)nk, threads, g.mutable_data(), pos.mutable_data(), neg.mutable_data()); }
+    return py::make_tuple(loss, g, pos, neg);
+  }, py::arg("offsets"), py::arg("loc"), py::arg("vals"), py::arg("y"), py::arg("w"), py::arg("threads") = 1,
+     "(summed logistic loss, gradient, positive count, negative count per local key) of one minibatch");
   py::class_<FTRLModel>(m, "FTRLModel")
       .def(py::init<double, double, double, double>(), py::arg("alpha"), py::arg("beta"), py::arg("lambda1"), py::arg("lambda2"))
       .def("update", [](FTRLModel& f, carray<uint64_t> k, carray<double> g, carray<double> pos, carray<double> neg) {

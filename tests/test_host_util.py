@@ -338,3 +338,26 @@ def test_native_localizer(threads):
         np.testing.assert_allclose(got, ref.T @ x, rtol=1e-9, atol=1e-9)
     with pytest.raises(ValueError):
         H.csr_to_csc(off, loc, None, 5, 1)
+
+
+@pytest.mark.parametrize("binary,threads", [(False, 1), (True, 3)])
+def test_native_ftrl_minibatch(binary, threads):
+    rng = np.random.default_rng(5)
+    rows, nk = 1500, 400
+    per = rng.integers(0, 12, rows)
+    off = np.concatenate([[0], np.cumsum(per)]).astype(np.int64)
+    loc = rng.integers(0, nk, off[-1]).astype(np.int32)
+    val = None if binary else rng.normal(size=off[-1])
+    y = np.where(rng.random(rows) < 0.4, 1.0, -1.0)
+    w = rng.normal(size=nk) * 3                                        # large margins: the loss must not overflow
+    loss, g, pos, neg = H.ftrl_minibatch(off, loc, val, y, w, threads)
+    v = np.ones(off[-1]) if binary else val
+    row_of = np.repeat(np.arange(rows), per)
+    m = y * np.bincount(row_of, weights=w[loc] * v, minlength=rows)
+    assert loss == pytest.approx(np.sum(np.logaddexp(0.0, -m)), rel=1e-12)
+    coef = -y / (1.0 + np.exp(m))
+    np.testing.assert_allclose(g, np.bincount(loc, weights=coef[row_of] * v, minlength=nk), rtol=1e-12, atol=1e-12)
+    np.testing.assert_array_equal(pos, np.bincount(loc, weights=(y[row_of] > 0).astype(float), minlength=nk))
+    np.testing.assert_array_equal(neg, np.bincount(loc, weights=(y[row_of] <= 0).astype(float), minlength=nk))
+    with pytest.raises(ValueError):
+        H.ftrl_minibatch(off, loc + nk, val, y, w, 1)
