@@ -50,58 +50,31 @@ def _call(cmd: str, **kw) -> bytes:
 
 
 class SharedParam:
-    """The shared parameter ``w``: a customer that serves push / pull on a KVVector."""
+    """The shared parameter ``w``.  Push and pull are served by the native customer ``SharedParamCustomer``
+    (csrc/host/shared_param.h) on its executor thread; this class is the handle the solver code talks to."""
+
+    class _Filter:
+        def __init__(self, cust):
+            self._c = cust
+
+        def clear(self) -> None:
+            self._c.clear_filter()
 
     def __init__(self, ctx: NodeContext, name: str, solver):
         H = host()
         self.H, self.ctx, self.solver = H, ctx, solver
-        self.kv = H.KVVector(1)
-        self.filter = H.FrequencyFilter()
-        self.pulled: Dict[int, Dict[str, tuple]] = {}
-        self.lock = threading.Lock()
         # -parallel_match: the server's merge-join of a push into its key list runs on -num_threads threads
         # (src/parameter/kv_vector.h:77-137)
         fl = getattr(solver, "flags", None)
-        self.match_threads = max(int(fl.num_threads), 1) if fl is not None and bool(fl.parallel_match) else 1
-        self.cust = H.Customer(ctx.po, name, self.process, True)
-
-    # executor thread of this customer
-    def process(self, msg) -> None:
-        keys = np.frombuffer(msg.key, dtype=U64)
-        if msg.request and msg.cmd == PUSH:
-            if msg.flags & F_INSERT_KEY_FREQ:
-                if self.filter.empty():
-                    s = self.solver.conf.solver
-                    n = max(int(self.ctx.num_workers * len(keys) * s.countmin_n_ratio / math.log(self.ctx.num_workers + 1)), 64)
-                    self.filter.resize(n, s.countmin_k)
-                self.filter.insert_keys(keys, np.frombuffer(msg.values[0], dtype=np.uint32))
-            elif not msg.values:
-                self.kv.merge_keys(msg.channel, keys)
-            else:
-                vals = np.frombuffer(msg.values[0], dtype=np.float64)
-                nval = len(vals) // max(len(keys), 1) if len(keys) else 2
-                lo, hi = msg.key_range
-                self.kv.aggregate(msg.channel, msg.time, lo, hi, keys, vals, nval, self.match_threads)
-        elif msg.request and msg.cmd == PULL:
-            if msg.aux > 0:       # query_key_freq: reply the keys seen more than aux times
-                kept = self.filter.query_keys(keys, msg.aux)
-                self.cust.reply(msg, key=kept.tobytes(), values=[b""])
-            else:
-                vals = self.kv.lookup(msg.channel, keys)
-                self.cust.reply(msg, values=[vals.tobytes()])
-        elif not msg.request and msg.cmd == PULL:
-            with self.lock:
-                vals = np.frombuffer(msg.values[0], dtype=np.float64) if msg.values else np.zeros(0)
-                self.pulled.setdefault(msg.time, {})[msg.sender] = (keys, vals)
+        threads = max(int(fl.num_threads), 1) if fl is not None and bool(fl.parallel_match) else 1
+        s = solver.conf.solver
+        self.cust = H.SharedParamCustomer(ctx.po, name, threads, max(int(ctx.num_workers), 1), int(s.countmin_k), float(s.countmin_n_ratio))
+        self.kv = self.cust                      # keys / values / received / set_values... of the channel store, under its lock
+        self.filter = SharedParam._Filter(self.cust)
 
     def take_pulled(self, t: int):
-        """Concatenate the replies of pull ``t`` in server (= key) order."""
-        with self.lock:
-            parts = self.pulled.pop(t, {})
-        order = self.cust.group(self.H.kServerGroup)
-        ks = [parts[s][0] for s in order if s in parts]
-        vs = [parts[s][1] for s in order if s in parts]
-        return (np.concatenate(ks) if ks else np.zeros(0, U64)), (np.concatenate(vs) if vs else np.zeros(0))
+        """The replies of pull ``t`` concatenated in server (= key) order: (keys, values)."""
+        return self.cust.take_pulled(t, self.cust.group(self.H.kServerGroup))
 
 
 class LinearMethodNode:

@@ -13,6 +13,7 @@
 #include "kv.h"
 #include "localizer.h"
 #include "runtime.h"
+#include "shared_param.h"
 
 namespace py = pybind11;
 using namespace psb;
@@ -534,4 +535,27 @@ PYBIND11_MODULE(_psb_host, m) {
       .def("processed", [](PyCustomer& c) { return (uint64_t)c.exec()->processed; })
       .def("pending_requests", [](PyCustomer& c) { return c.exec()->pending_requests(); })
       .def("stop", [](PyCustomer& c) { c.exec()->stop(); }, py::call_guard<py::gil_scoped_release>());
+
+  // the shared parameter of the batch solvers: push / pull served natively on the executor thread
+  using PyShared = SharedParamCustomerT<PyCustomer>;
+  py::class_<PyShared, PyCustomer>(m, "SharedParamCustomer")
+      .def(py::init([](Postoffice* po, std::string name, int match_threads, int num_workers, int countmin_k, double countmin_n_ratio) {
+        return new PyShared(po, std::move(name), match_threads, num_workers, countmin_k, countmin_n_ratio);
+      }), py::arg("postoffice"), py::arg("name"), py::arg("match_threads") = 1, py::arg("num_workers") = 1, py::arg("countmin_k") = 2,
+          py::arg("countmin_n_ratio") = 2.0, py::keep_alive<1, 2>())
+      .def("keys", [](PyShared& c, int ch) { return to_array(c.keys(ch)); })
+      .def("values", [](PyShared& c, int ch) { return to_array(c.values(ch)); })
+      .def("set_values", [](PyShared& c, int ch, carray<double> a) { c.set_values(ch, a.data(), (size_t)a.size()); })
+      .def("set_values_range", [](PyShared& c, int ch, size_t lo, carray<double> a) { c.set_values_range(ch, lo, a.data(), (size_t)a.size()); })
+      .def("init_values", [](PyShared& c, int ch, double init) { c.init_values(ch, init); }, py::arg("ch"), py::arg("init") = 0.0)
+      .def("received", [](PyShared& c, int t) { auto r = c.received(t); return py::make_tuple(r.lo, r.hi, r.nval, to_array(r.vals)); })
+      .def("clear_filter", [](PyShared& c) { c.clear_filter(); })
+      .def("take_pulled", [](PyShared& c, int t, const std::vector<std::string>& servers) {
+        auto p = c.take_pulled(t, servers);
+        py::array_t<uint64_t> k((py::ssize_t)(p.first.size() / 8));
+        py::array_t<double> v((py::ssize_t)(p.second.size() / 8));
+        if (p.first.size()) std::memcpy(k.mutable_data(), p.first.data(), p.first.size() / 8 * 8);
+        if (p.second.size()) std::memcpy(v.mutable_data(), p.second.data(), p.second.size() / 8 * 8);
+        return py::make_tuple(k, v);
+      });
 }

@@ -24,6 +24,7 @@
 #include "../data.h"
 #include "../kv.h"
 #include "../runtime.h"
+#include "../shared_param.h"
 
 using namespace psb;
 
@@ -173,6 +174,77 @@ int main(int argc, char** argv) {
     CHECK_TRUE(rt["S1"]->store[half + 5] == 3.0 * total_pushes);
   }
   CHECK_TRUE(pulled_ok == 2 * total_pushes);   // one data reply per server and pull
+
+  // the native shared-parameter customer under the batch solvers' protocol: workers push keys, then per round
+  // values at time t; a solver thread on every server waits for both pushes, takes the aggregate, writes the new
+  // weights and releases t + 1; the workers' pulls (time t + 2, waiting for t + 1) must see exactly those weights.
+  // The servers' executor threads (push / pull handling) and solver threads (received / set_values_range) run
+  // at the same time, rounds overlap between the two workers.
+  {
+    std::map<std::string, std::unique_ptr<SharedParamCustomer>> sp;
+    for (auto& id : ids)
+      if (id.first != "H") sp[id.first] = std::make_unique<SharedParamCustomer>(rt[id.first]->po.get(), "p", 2, W, 2, 2.0);
+    const std::vector<uint64_t> wk[2] = {{2, 4, 6, half + 2, half + 4}, {4, 6, 8, half + 4, half + 8}};
+    const int kR = 20;
+    std::atomic<int> bad{0};
+    std::vector<std::thread> ts;
+    for (int w = 0; w < W; ++w)
+      ts.emplace_back([&, w] {
+        auto* c = sp["W" + std::to_string(w)].get();
+        auto mk = [&](int cmd, int time, int wait) {
+          auto m = std::make_shared<Message>();
+          m->recver = kServerGroup;
+          m->task.cmd = cmd;
+          m->task.time = time;
+          m->task.wait_time = wait;
+          m->task.has_key = true;
+          m->key = bytes_of(wk[w]);
+          m->task.has_key_range = true;
+          m->task.key_range = Range::all();
+          return m;
+        };
+        c->submit(mk(1, 10, -1));                                   // keys only
+        if (!c->wait_out(kServerGroup, 10, 20.0)) ++bad;
+        for (int r = 0; r < kR; ++r) {
+          const int t = 20 + 10 * r;
+          auto push = mk(1, t, -1);
+          std::vector<double> v(wk[w].size(), (double)(w + 1));     // every key of worker w carries w + 1
+          push->value.push_back(bytes_of(v));
+          c->submit(push);
+          c->submit(mk(2, t + 2, t + 1));
+          if (!c->wait_out(kServerGroup, t + 2, 20.0)) { ++bad; continue; }
+          auto got = c->take_pulled(t + 2, {"S0", "S1"});
+          const double* x = reinterpret_cast<const double*>(got.second.data());     // values only: a value reply carries no keys
+          if (got.second.size() != wk[w].size() * 8) { ++bad; continue; }
+          for (size_t i = 0; i < wk[w].size(); ++i) {
+            const uint64_t k = wk[w][i];
+            const bool both = k == 4 || k == 6 || k == half + 4;               // keys that the two workers share
+            if (x[i] != (r + 1) * (both ? 3.0 : (double)(w + 1))) ++bad;
+          }
+        }
+      });
+    for (int sv = 0; sv < S; ++sv)
+      ts.emplace_back([&, sv] {
+        auto* c = sp["S" + std::to_string(sv)].get();
+        if (!c->wait_in(kWorkerGroup, 10, 20.0)) ++bad;
+        c->init_values(0, 0.0);
+        c->finish_in(kWorkerGroup, 11);
+        for (int r = 0; r < kR; ++r) {
+          const int t = 20 + 10 * r;
+          if (!c->wait_in(kWorkerGroup, t, 20.0)) { ++bad; continue; }
+          auto agg = c->received(t);
+          auto w = c->values(0);
+          if (agg.nval != 1 || agg.hi - agg.lo != w.size()) { ++bad; continue; }
+          for (size_t i = 0; i < w.size(); ++i) w[i] += agg.vals[i];
+          c->set_values_range(0, agg.lo, w.data(), w.size());
+          c->finish_in(kWorkerGroup, t + 1);
+        }
+      });
+    for (auto& th : ts) th.join();
+    CHECK_TRUE(bad == 0);
+    CHECK_TRUE(sp["S0"]->keys(0) == (std::vector<uint64_t>{2, 4, 6, 8}));
+    for (auto& kv : sp) kv.second->exec()->stop();
+  }
 
   // failure detector: everybody reported recently; after S1 stops, it shows up as dead
   std::this_thread::sleep_for(std::chrono::milliseconds(100));
