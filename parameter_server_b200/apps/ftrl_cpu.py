@@ -41,43 +41,18 @@ class FTRLNode:
         self.conf = app_conf.linear_method
         lam = list(self.conf.penalty.get("lambda")) + [0.0, 0.0]
         lr = self.conf.learning_rate
-        self.store = H.FTRLModel(lr.alpha, lr.beta, lam[0], lam[1])   # native key -> {pos, neg, w, z} map (csrc/host/kv.h)
-        self.filter = H.FrequencyFilter()
-        self.pulled: Dict[int, Dict[str, tuple]] = {}
-        self.lock = threading.Lock()
-        self.param = H.Customer(ctx.po, app_conf.parameter_name[0], self.process_param, True)
+        # the shared parameter: a native customer that keeps this server's FTRL model (key -> {pos, neg, w, z}), applies
+        # pushes as they arrive and answers pulls on its executor thread (csrc/host/shared_param.h::FTRLParamCustomer)
+        s = self.conf.solver
+        self.param = H.FTRLParamCustomer(ctx.po, app_conf.parameter_name[0], lr.alpha, lr.beta, lam[0], lam[1],
+                                         max(int(s.countmin_n) // max(ctx.num_servers, 1), 64), int(s.countmin_k))
+        self.store = self.param
         self.cust = H.Customer(ctx.po, app_conf.app_name, self.process, False)
         self.examples, self.loss_sum, self.steps = 0, 0.0, 0
 
-    # ---- shared parameter (executor thread of `param`)
-    def process_param(self, msg) -> None:
-        keys = np.frombuffer(msg.key, dtype=U64)
-        if msg.request and msg.cmd == PUSH:
-            if msg.flags & F_INSERT_KEY_FREQ:
-                if self.filter.empty():
-                    s = self.conf.solver
-                    self.filter.resize(max(int(s.countmin_n) // max(self.ctx.num_servers, 1), 64), int(s.countmin_k))
-                self.filter.insert_keys(keys, np.frombuffer(msg.values[0], dtype=np.uint32))
-            else:
-                g, pos, neg = (np.frombuffer(v, dtype=np.float64) for v in msg.values[:3])
-                self.store.update(keys, g, pos, neg)
-        elif msg.request and msg.cmd == PULL:
-            if msg.aux > 0:       # query_key_freq: reply the keys seen more than aux times
-                self.param.reply(msg, key=self.filter.query_keys(keys, msg.aux).tobytes(), values=[b""])
-            else:
-                self.param.reply(msg, values=[self.store.get(keys).tobytes()])
-        elif not msg.request and msg.cmd == PULL:
-            with self.lock:
-                vals = np.frombuffer(msg.values[0], dtype=np.float64) if msg.values else np.zeros(0)
-                self.pulled.setdefault(msg.time, {})[msg.sender] = (keys, vals)
-
     def _take(self, t: int):
-        with self.lock:
-            parts = self.pulled.pop(t, {})
-        order = self.param.group(self.H.kServerGroup)
-        ks = [parts[s][0] for s in order if s in parts]
-        vs = [parts[s][1] for s in order if s in parts]
-        return (np.concatenate(ks) if ks else np.zeros(0, U64)), (np.concatenate(vs) if vs else np.zeros(0))
+        """The replies of pull ``t`` concatenated in server (= key) order: (keys, values)."""
+        return self.param.take_pulled(t, self.param.group(self.H.kServerGroup))
 
     # ---- application calls from the scheduler
     def process(self, msg) -> None:

@@ -73,6 +73,15 @@ struct PyCustomer : public Customer {
   using Customer::Customer;
 };
 
+// (keys, values) arrays of concatenated pull replies
+py::tuple pulled_arrays(const std::pair<std::string, std::string>& p) {
+  py::array_t<uint64_t> k((py::ssize_t)(p.first.size() / 8));
+  py::array_t<double> v((py::ssize_t)(p.second.size() / 8));
+  if (p.first.size() >= 8) std::memcpy(k.mutable_data(), p.first.data(), p.first.size() / 8 * 8);
+  if (p.second.size() >= 8) std::memcpy(v.mutable_data(), p.second.data(), p.second.size() / 8 * 8);
+  return py::make_tuple(k, v);
+}
+
 MessagePtr make_message(const std::string& recver, int type, int cmd, const std::string& payload, py::object key,
                         const std::vector<py::bytes>& values, int time, int wait_time, int channel, py::object key_range,
                         uint32_t flags, int aux, bool erase_key_cache) {
@@ -550,12 +559,17 @@ PYBIND11_MODULE(_psb_host, m) {
       .def("init_values", [](PyShared& c, int ch, double init) { c.init_values(ch, init); }, py::arg("ch"), py::arg("init") = 0.0)
       .def("received", [](PyShared& c, int t) { auto r = c.received(t); return py::make_tuple(r.lo, r.hi, r.nval, to_array(r.vals)); })
       .def("clear_filter", [](PyShared& c) { c.clear_filter(); })
-      .def("take_pulled", [](PyShared& c, int t, const std::vector<std::string>& servers) {
-        auto p = c.take_pulled(t, servers);
-        py::array_t<uint64_t> k((py::ssize_t)(p.first.size() / 8));
-        py::array_t<double> v((py::ssize_t)(p.second.size() / 8));
-        if (p.first.size()) std::memcpy(k.mutable_data(), p.first.data(), p.first.size() / 8 * 8);
-        if (p.second.size()) std::memcpy(v.mutable_data(), p.second.data(), p.second.size() / 8 * 8);
-        return py::make_tuple(k, v);
-      });
+      .def("take_pulled", [](PyShared& c, int t, const std::vector<std::string>& servers) { return pulled_arrays(c.take_pulled(t, servers)); });
+
+  // the shared parameter of the online solver: an FTRL model per server, updated as pushes arrive
+  using PyFtrlParam = FTRLParamCustomerT<PyCustomer>;
+  py::class_<PyFtrlParam, PyCustomer>(m, "FTRLParamCustomer")
+      .def(py::init([](Postoffice* po, std::string name, double alpha, double beta, double l1, double l2, size_t width, int k) {
+        return new PyFtrlParam(po, std::move(name), alpha, beta, l1, l2, width, k);
+      }), py::arg("postoffice"), py::arg("name"), py::arg("alpha"), py::arg("beta"), py::arg("lambda1"), py::arg("lambda2"),
+          py::arg("sketch_width") = 1 << 20, py::arg("countmin_k") = 2, py::keep_alive<1, 2>())
+      .def("stats", [](PyFtrlParam& c) { double a, b; size_t n; c.stats(&a, &b, &n); return py::make_tuple(a, b, n); })
+      .def("size", &PyFtrlParam::size)
+      .def("nonzero", [](PyFtrlParam& c) { std::vector<Key> k; std::vector<double> w; c.nonzero(&k, &w); return py::make_tuple(to_array(k), to_array(w)); })
+      .def("take_pulled", [](PyFtrlParam& c, int t, const std::vector<std::string>& servers) { return pulled_arrays(c.take_pulled(t, servers)); });
 }

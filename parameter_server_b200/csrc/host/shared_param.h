@@ -124,4 +124,90 @@ class SharedParamCustomerT : public Base {
 
 using SharedParamCustomer = SharedParamCustomerT<Customer>;
 
+// The shared parameter of the online solver: the server keeps an FTRLModel (key -> {pos, neg, w, z}), a push
+// carries (gradient, positive count, negative count) per key and is applied on arrival, a pull answers the
+// current weights; key counts go through the tail-feature sketch like above, whose width is countmin_n divided
+// over the servers.  Counterpart: FTRLModel as the store of SharedParameter (src/linear_method/ftrl_model.h
+// :72-112, src/parameter/shared_parameter.h:90-149).
+template <class Base = Customer>
+class FTRLParamCustomerT : public Base {
+ public:
+  using Base::key_ordered_slice;
+  using Base::process;
+  using Base::reply;
+  static constexpr int kPush = 1, kPull = 2;
+  static constexpr uint32_t kInsertKeyFreq = 1;
+
+  FTRLParamCustomerT(Postoffice* po, std::string name, double alpha, double beta, double lambda1, double lambda2, size_t sketch_width,
+                     int countmin_k)
+      : Base(po, std::move(name)), store_(alpha, beta, lambda1, lambda2), width_(std::max<size_t>(sketch_width, 64)), cm_k_(countmin_k) {
+    key_ordered_slice = true;
+    process = [this](const MessagePtr& m) { handle(m); };
+  }
+  // (|w|_1, |w|_2^2, non-zero weights) of this shard
+  void stats(double* n1, double* n2, size_t* nnz) { std::lock_guard<std::mutex> l(mu_); *n1 = store_.norm1(); *n2 = store_.norm2(); *nnz = store_.nnz(); }
+  void nonzero(std::vector<Key>* k, std::vector<double>* w) { std::lock_guard<std::mutex> l(mu_); store_.nonzero(k, w); }
+  size_t size() { std::lock_guard<std::mutex> l(mu_); return store_.size(); }
+  std::pair<std::string, std::string> take_pulled(int t, const std::vector<std::string>& servers) {
+    std::map<std::string, std::pair<std::string, std::string>> parts;
+    {
+      std::lock_guard<std::mutex> l(mu_);
+      auto it = pulled_.find(t);
+      if (it != pulled_.end()) { parts.swap(it->second); pulled_.erase(it); }
+    }
+    std::pair<std::string, std::string> out;
+    for (auto& s : servers) {
+      auto it = parts.find(s);
+      if (it == parts.end()) continue;
+      out.first += it->second.first;
+      out.second += it->second.second;
+    }
+    return out;
+  }
+
+ private:
+  void handle(const MessagePtr& msg) {
+    const Task& t = msg->task;
+    const Key* keys = reinterpret_cast<const Key*>(msg->key.data());
+    const size_t n = msg->key.size() / sizeof(Key);
+    if (t.request && t.cmd == kPush) {
+      std::lock_guard<std::mutex> l(mu_);
+      if (t.flags & kInsertKeyFreq) {
+        if (msg->value.empty() || msg->value[0].size() != n * sizeof(uint32_t)) return;
+        if (filter_.empty()) filter_.resize(width_, cm_k_);
+        filter_.insert_keys(keys, reinterpret_cast<const uint32_t*>(msg->value[0].data()), n);
+      } else {
+        if (msg->value.size() < 3) return;
+        for (int i = 0; i < 3; ++i) if (msg->value[i].size() != n * sizeof(double)) return;
+        store_.update(keys, n, reinterpret_cast<const double*>(msg->value[0].data()), reinterpret_cast<const double*>(msg->value[1].data()),
+                      reinterpret_cast<const double*>(msg->value[2].data()));
+      }
+    } else if (t.request && t.cmd == kPull) {
+      std::string rk, rv;
+      {
+        std::lock_guard<std::mutex> l(mu_);
+        if (t.aux > 0) {
+          auto kept = filter_.query_keys(keys, n, (uint32_t)t.aux);
+          rk.assign(reinterpret_cast<const char*>(kept.data()), kept.size() * sizeof(Key));
+        } else {
+          auto w = store_.get(keys, n);
+          rv.assign(reinterpret_cast<const char*>(w.data()), w.size() * sizeof(double));
+        }
+      }
+      reply(msg, std::move(rk), {std::move(rv)});
+    } else if (!t.request && t.cmd == kPull) {
+      std::lock_guard<std::mutex> l(mu_);
+      pulled_[t.time][msg->sender] = {msg->key, msg->value.empty() ? std::string() : msg->value[0]};
+    }
+  }
+
+  std::mutex mu_;
+  FTRLModel store_;
+  FrequencyFilter filter_;
+  std::map<int, std::map<std::string, std::pair<std::string, std::string>>> pulled_;
+  size_t width_;
+  int cm_k_;
+};
+using FTRLParamCustomer = FTRLParamCustomerT<Customer>;
+
 }  // namespace psb
