@@ -246,6 +246,55 @@ int main(int argc, char** argv) {
     for (auto& kv : sp) kv.second->exec()->stop();
   }
 
+  // the online solver's parameter customer: two workers push (gradient, positive, negative) per key without
+  // waiting and pull in between, the servers update their FTRL models on arrival; stats are read meanwhile
+  {
+    std::map<std::string, std::unique_ptr<FTRLParamCustomer>> fp;
+    for (auto& id : ids)
+      if (id.first != "H") fp[id.first] = std::make_unique<FTRLParamCustomer>(rt[id.first]->po.get(), "f", 0.1, 1.0, 0.01, 0.0, 4096, 2);
+    std::atomic<int> bad{0};
+    std::vector<std::thread> ts;
+    for (int w = 0; w < W; ++w)
+      ts.emplace_back([&, w] {
+        auto* c = fp["W" + std::to_string(w)].get();
+        int last = -1;
+        for (int r = 0; r < 30; ++r) {
+          std::vector<uint64_t> keys = {5, 9 + (uint64_t)w, half + 1, half + 7 + (uint64_t)(r % 2)};
+          std::vector<double> g = {0.5, -0.25, 1.0, -1.5}, pos = {1, 0, 1, 0}, neg = {0, 1, 0, 1};
+          auto push = std::make_shared<Message>();
+          push->recver = kServerGroup;
+          push->task.cmd = 1;
+          push->task.has_key = true;
+          push->key = bytes_of(keys);
+          push->value = {bytes_of(g), bytes_of(pos), bytes_of(neg)};
+          push->task.has_key_range = true;
+          push->task.key_range = Range::all();
+          last = c->submit(push);
+          auto pull = std::make_shared<Message>();
+          pull->recver = kServerGroup;
+          pull->task.cmd = 2;
+          pull->task.has_key = true;
+          pull->key = bytes_of(keys);
+          pull->task.has_key_range = true;
+          pull->task.key_range = Range::all();
+          const int tl = c->submit(pull);
+          if (!c->wait_out(kServerGroup, tl, 20.0)) { ++bad; continue; }
+          if (c->take_pulled(tl, {"S0", "S1"}).second.size() != keys.size() * 8) ++bad;
+        }
+        if (!c->wait_out(kServerGroup, last, 20.0)) ++bad;
+      });
+    ts.emplace_back([&] {
+      for (int i = 0; i < 200; ++i) { double a, b; size_t n; fp["S0"]->stats(&a, &b, &n); fp["S1"]->size(); }
+    });
+    for (auto& th : ts) th.join();
+    CHECK_TRUE(bad == 0);
+    CHECK_TRUE(fp["S0"]->size() == 3 && fp["S1"]->size() == 3);       // {5, 9, 10} and {half + 1, half + 7, half + 8}
+    std::vector<Key> k; std::vector<double> wv;
+    fp["S0"]->nonzero(&k, &wv);
+    CHECK_TRUE(!k.empty());
+    for (auto& kv : fp) kv.second->exec()->stop();
+  }
+
   // failure detector: everybody reported recently; after S1 stops, it shows up as dead
   std::this_thread::sleep_for(std::chrono::milliseconds(100));
   CHECK_TRUE(rt["H"]->po->dead_nodes(5.0).empty());
