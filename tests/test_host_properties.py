@@ -12,7 +12,7 @@ H = host()
 U64 = st.integers(min_value=0, max_value=2**64 - 2)
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(st.lists(U64, max_size=200, unique=True), st.lists(U64, min_size=1, max_size=6, unique=True), st.integers(1, 3))
 def test_slices_partition_a_message(keys, cuts, k):
     keys = np.array(sorted(keys), dtype=np.uint64)
@@ -29,7 +29,7 @@ def test_slices_partition_a_message(keys, cuts, k):
         assert all(lo <= int(x) < hi for x in kk)
 
 
-@settings(max_examples=25, deadline=None)
+@settings(max_examples=25, deadline=None, derandomize=True)
 @given(st.integers(0, 2**32), st.integers(1, 7), st.integers(1, 3))
 def test_threaded_aggregation_equals_serial(seed, threads, nval):
     rng = np.random.default_rng(seed)
@@ -49,7 +49,7 @@ def test_threaded_aggregation_equals_serial(seed, threads, nval):
     np.testing.assert_array_equal(out[0][3], out[1][3])
 
 
-@settings(max_examples=100, deadline=None)
+@settings(max_examples=100, deadline=None, derandomize=True)
 @given(U64, U64, st.integers(1, 64))
 def test_even_divide_covers_the_range(a, b, n):
     lo, hi = min(a, b), max(a, b)
@@ -61,7 +61,7 @@ def test_even_divide_covers_the_range(a, b, n):
     assert max(sizes) - min(sizes) <= 1 or hi - lo < n
 
 
-@settings(max_examples=30, deadline=None)
+@settings(max_examples=30, deadline=None, derandomize=True)
 @given(st.lists(U64, max_size=3000), st.integers(1, 8))
 def test_parallel_sort(keys, threads):
     a = np.array(keys, dtype=np.uint64)
@@ -71,7 +71,7 @@ def test_parallel_sort(keys, threads):
 names = st.text(alphabet="abcdefghijklmnopqrstuvwxyz_/.-0123456789", min_size=1, max_size=12)
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(st.lists(names, max_size=4), st.floats(min_value=1e-6, max_value=1e3, allow_nan=False), st.integers(0, 50),
        st.booleans(), st.integers(0, 2**63), st.integers(0, 2**63))
 def test_job_file_round_trip(files, lam, delay, rand, k0, k1):
