@@ -219,6 +219,59 @@ class KVVector {
   std::map<int, Received> recved_;
 };
 
+// Open-addressing hash map from 64-bit keys to small records (linear probing, power-of-two capacity, grows at
+// 60 % load; no erase).  The host form of the hash-map store that the reference only declares (KVMap,
+// src/parameter/kv_map.h); the online solver's model lives in it: one cache line per probe instead of the
+// node allocation and pointer chase of std::unordered_map.
+template <typename V>
+class KeyMap {
+ public:
+  explicit KeyMap(size_t capacity = 1024) { rehash(capacity); }
+  size_t size() const { return size_; }
+  V& operator[](Key k) {
+    if ((size_ + 1) * 5 > slots_.size() * 3) rehash(slots_.size() * 2);
+    size_t i = index(k);
+    while (used_[i] && slots_[i].first != k) i = (i + 1) & mask_;
+    if (!used_[i]) { used_[i] = 1; slots_[i].first = k; slots_[i].second = V(); ++size_; }
+    return slots_[i].second;
+  }
+  const V* find(Key k) const {
+    size_t i = index(k);
+    while (used_[i]) {
+      if (slots_[i].first == k) return &slots_[i].second;
+      i = (i + 1) & mask_;
+    }
+    return nullptr;
+  }
+  template <typename F> void for_each(F f) const {
+    for (size_t i = 0; i < slots_.size(); ++i) if (used_[i]) f(slots_[i].first, slots_[i].second);
+  }
+
+ private:
+  size_t index(Key k) const {                 // Fibonacci hashing: the top bits of k * 2^64 / phi
+    return (size_t)((k * 0x9E3779B97F4A7C15ull) >> shift_) & mask_;
+  }
+  void rehash(size_t want) {
+    size_t cap = 16;
+    int bits = 4;
+    while (cap < want) { cap <<= 1; ++bits; }
+    std::vector<std::pair<Key, V>> old_slots;
+    std::vector<uint8_t> old_used;
+    old_slots.swap(slots_);
+    old_used.swap(used_);
+    slots_.assign(cap, std::pair<Key, V>());
+    used_.assign(cap, 0);
+    mask_ = cap - 1;
+    shift_ = 64 - bits;
+    size_ = 0;
+    for (size_t i = 0; i < old_slots.size(); ++i) if (old_used[i]) (*this)[old_slots[i].first] = old_slots[i].second;
+  }
+  std::vector<std::pair<Key, V>> slots_;
+  std::vector<uint8_t> used_;
+  size_t mask_ = 0, size_ = 0;
+  int shift_ = 60;
+};
+
 // Server-side state of the online solver on CPU nodes: key -> {pos, neg, w, z} with the per-key
 // FTRL-proximal update and the count-based estimate of the gradient norm, plus running |w|_1, |w|_2^2
 // and nnz(w) (FTRLModel::setValue / getValue / objv, src/linear_method/ftrl_model.h:60-127).
@@ -250,8 +303,8 @@ class FTRLModel {
   std::vector<double> get(const Key* keys, size_t n) const {
     std::vector<double> out(n, 0.0);
     for (size_t i = 0; i < n; ++i) {
-      auto it = model_.find(keys[i]);
-      if (it != model_.end()) out[i] = it->second.w;
+      const Entry* e = model_.find(keys[i]);
+      if (e) out[i] = e->w;
     }
     return out;
   }
@@ -262,7 +315,7 @@ class FTRLModel {
   // non-zero weights in ascending key order
   void nonzero(std::vector<Key>* keys, std::vector<double>* w) const {
     std::vector<std::pair<Key, double>> v;
-    for (auto& kv : model_) if (kv.second.w != 0) v.emplace_back(kv.first, kv.second.w);
+    model_.for_each([&](Key k, const Entry& e) { if (e.w != 0) v.emplace_back(k, e.w); });
     std::sort(v.begin(), v.end());
     keys->clear(); w->clear();
     for (auto& p : v) { keys->push_back(p.first); w->push_back(p.second); }
@@ -272,7 +325,7 @@ class FTRLModel {
   double alpha_, beta_, l1_, l2_;
   double norm1_ = 0, norm2_ = 0;
   long long nnz_ = 0;
-  std::unordered_map<Key, Entry> model_;
+  KeyMap<Entry> model_;
 };
 
 inline double soft_thresholding(double x, double l1, double l2) {
