@@ -361,3 +361,30 @@ def test_native_ftrl_minibatch(binary, threads):
     np.testing.assert_array_equal(neg, np.bincount(loc, weights=(y[row_of] <= 0).astype(float), minlength=nk))
     with pytest.raises(ValueError):
         H.ftrl_minibatch(off, loc + nk, val, y, w, 1)
+
+
+def test_ftrl_model_store_grows_and_keeps_every_key():
+    """The model's hash map through several doublings: sizes, look-ups of present and absent keys, key 0 and the
+    largest key, and independence from how the updates were batched."""
+    rng = np.random.default_rng(9)
+    keys = np.unique(np.concatenate([rng.integers(0, 2**63, 60000).astype(np.uint64) * np.uint64(2),
+                                     np.array([0, 2**64 - 1, 2**64 - 2], dtype=np.uint64)]))
+    g = rng.normal(size=len(keys))
+    pos = rng.integers(0, 3, len(keys)).astype(np.float64)
+    neg = rng.integers(1, 3, len(keys)).astype(np.float64)
+    a, b = H.FTRLModel(0.1, 1.0, 0.01, 0.1), H.FTRLModel(0.1, 1.0, 0.01, 0.1)
+    a.update(keys, g, pos, neg)
+    perm = rng.permutation(len(keys))
+    for part in np.array_split(perm, 37):                      # same updates, other order and batching
+        b.update(keys[part], g[part], pos[part], neg[part])
+    assert a.size() == b.size() == len(keys)
+    wa, wb = a.get(keys), b.get(keys)
+    np.testing.assert_array_equal(wa, wb)
+    assert np.count_nonzero(wa) > len(keys) // 2
+    absent = keys[:1000] + np.uint64(1)                        # odd keys were never inserted (0 + 1 = 1 neither)
+    absent = absent[~np.isin(absent, keys)]
+    assert np.all(a.get(absent) == 0) and a.size() == len(keys)   # a look-up inserts nothing
+    ka, va = a.nonzero()
+    assert np.all(np.diff(ka.astype(np.float64)) >= 0) and len(ka) == np.count_nonzero(wa)
+    n1, n2, nnz = a.stats()
+    assert nnz == len(ka) and n1 == pytest.approx(np.abs(va).sum(), rel=1e-9) and n2 == pytest.approx((va ** 2).sum(), rel=1e-9)
