@@ -117,8 +117,7 @@ class FTRLNode:
             # the minibatch's keys: unique with counts (FTRL::countKeys, ftrl.cc:154-174) and the local id of every
             # non-zero, in the native runtime (csrc/host/localizer.h)
             T_ = max(int(self.flags.num_threads), 1)
-            ukeys, cnt = H.count_unique(idx, T_)
-            inv = H.remap_keys(idx, ukeys, T_)
+            ukeys, cnt, inv = H.localize(idx)
             ch += 1
             if freq > 0:      # tail filter: insert this minibatch's key counts, keep the keys above the threshold
                 P.submit(H.kServerGroup, cmd=PUSH, key=ukeys.tobytes(), values=[cnt.astype(np.uint32).tobytes()],

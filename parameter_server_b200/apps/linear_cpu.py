@@ -151,15 +151,15 @@ class LinearMethodNode:
             # localisation in the native runtime (csrc/host/localizer.h): unique keys with counts, local column ids,
             # column-major storage
             T_ = max(int(self.flags.num_threads), 1)
-            ukeys, cnt = H.count_unique(self.idx, T_)
+            ukeys, cnt, loc = H.localize(self.idx)
             if freq > 0:      # tail-feature filter through the servers' count-min sketch
                 P.cust.submit(H.kServerGroup, cmd=PUSH, key=ukeys.tobytes(), values=[cnt.astype(np.uint32).tobytes()],
                               time=t, key_range=allr, channel=self.ch, flags=F_INSERT_KEY_FREQ, wait=True)
                 P.cust.submit(H.kServerGroup, cmd=PULL, key=ukeys.tobytes(), time=t + 2, wait_time=t + 1, key_range=allr,
                               channel=self.ch, aux=freq, erase_key_cache=True, wait=True)
                 ukeys, _ = P.take_pulled(t + 2)           # the surviving keys, ascending (servers answer in key order)
+                loc = H.remap_keys(self.idx, ukeys, T_)   # ids among the survivors, -1: dropped by the filter
             self.keys = ukeys
-            loc = H.remap_keys(self.idx, ukeys, T_)       # -1: dropped by the filter
             indptr, rix, cval = H.csr_to_csc(self.off, loc, None if self.binary else self.val, len(ukeys), T_)
             self._csc_cache = (indptr, rix, cval, np.ascontiguousarray(self.y, dtype=np.float64))
             self.idx = self.val = self.off = None

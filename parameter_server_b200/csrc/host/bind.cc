@@ -143,6 +143,13 @@ PYBIND11_MODULE(_psb_host, m) {
     { py::gil_scoped_release r; count_unique(keys.data(), (size_t)keys.size(), threads, &u, &c); }
     return py::make_tuple(to_array(u), to_array(c));
   }, py::arg("keys"), py::arg("threads") = 1, "(sorted unique keys, their counts)");
+  m.def("localize", [](carray<uint64_t> keys) {
+    if (keys.size() >= (py::ssize_t)1 << 31) throw std::invalid_argument("localize: more than 2^31 positions");
+    std::vector<uint64_t> u; std::vector<uint32_t> c;
+    py::array_t<int32_t> local(keys.size());
+    { py::gil_scoped_release r; localize(keys.data(), (size_t)keys.size(), &u, &c, local.mutable_data()); }
+    return py::make_tuple(to_array(u), to_array(c), local);
+  }, "(sorted unique keys, their counts, local id of every position)");
   m.def("remap_keys", [](carray<uint64_t> keys, carray<uint64_t> dict, int threads) {
     py::array_t<int32_t> out(keys.size());
     { py::gil_scoped_release r; remap_keys(keys.data(), (size_t)keys.size(), dict.data(), (size_t)dict.size(), threads, out.mutable_data()); }
@@ -543,7 +550,12 @@ PYBIND11_MODULE(_psb_host, m) {
       .def("partition", [](PyCustomer& c, const std::string& id) { return c.exec()->partition(id); })
       .def("processed", [](PyCustomer& c) { return (uint64_t)c.exec()->processed; })
       .def("pending_requests", [](PyCustomer& c) { return c.exec()->pending_requests(); })
-      .def("stop", [](PyCustomer& c) { c.exec()->stop(); }, py::call_guard<py::gil_scoped_release>());
+      .def("stop", [](PyCustomer& c) {
+        c.exec()->stop();
+        // the callback usually is a bound method of the object that owns this customer: dropping it breaks that cycle,
+        // which the interpreter's collector cannot see through
+        if (!dynamic_cast<SharedParamCustomerT<PyCustomer>*>(&c) && !dynamic_cast<FTRLParamCustomerT<PyCustomer>*>(&c)) c.process = nullptr;
+      }, py::call_guard<py::gil_scoped_release>());
 
   // the shared parameter of the batch solvers: push / pull served natively on the executor thread
   using PyShared = SharedParamCustomerT<PyCustomer>;

@@ -34,6 +34,36 @@ inline void count_unique(const uint64_t* keys, size_t n, int threads, std::vecto
   }
 }
 
+// Unique keys, their counts and the local id of every input position in one go: an LSD radix sort of
+// (key, position) pairs, 16 bits per pass, passes whose digit is the same for every key skipped, then one
+// run-length pass that hands out the ids (the reference sorts the pairs by comparison, localizer.h:50-87).
+inline void localize(const uint64_t* keys, size_t n, std::vector<uint64_t>* uniq, std::vector<uint32_t>* count, int32_t* local) {
+  std::vector<std::pair<uint64_t, uint32_t>> a(n), b(n);
+  uint64_t all_or = 0, all_and = ~0ull;
+  for (size_t i = 0; i < n; ++i) { a[i] = {keys[i], (uint32_t)i}; all_or |= keys[i]; all_and &= keys[i]; }
+  std::vector<size_t> hist(1 << 16);
+  for (int pass = 0; pass < 4; ++pass) {
+    const int sh = 16 * pass;
+    if ((((all_or ^ all_and) >> sh) & 0xffff) == 0) continue;       // every key has the same digit here
+    std::fill(hist.begin(), hist.end(), 0);
+    for (size_t i = 0; i < n; ++i) ++hist[(a[i].first >> sh) & 0xffff];
+    size_t run = 0;
+    for (auto& h : hist) { const size_t c = h; h = run; run += c; }
+    for (size_t i = 0; i < n; ++i) b[hist[(a[i].first >> sh) & 0xffff]++] = a[i];
+    a.swap(b);
+  }
+  uniq->clear();
+  count->clear();
+  for (size_t i = 0; i < n;) {
+    size_t j = i;
+    const int32_t id = (int32_t)uniq->size();
+    while (j < n && a[j].first == a[i].first) { local[a[j].second] = id; ++j; }
+    uniq->push_back(a[i].first);
+    count->push_back((uint32_t)std::min<size_t>(j - i, 0xffffffffu));
+    i = j;
+  }
+}
+
 template <typename F>
 inline void parallel_ranges(size_t n, int threads, size_t min_per_thread, F f) {
   const int t = (int)std::max<size_t>(1, std::min<size_t>((size_t)std::max(threads, 1), n / std::max<size_t>(min_per_thread, 1)));

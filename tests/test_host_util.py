@@ -313,9 +313,16 @@ def test_native_localizer(threads):
     off = np.arange(0, rows * nnz_row + 1, nnz_row, dtype=np.int64)
     vals = rng.normal(size=len(keys))
     u, c = H.count_unique(keys, threads)
-    ru, rc = np.unique(keys, return_counts=True)
+    ru, rinv, rc = np.unique(keys, return_inverse=True, return_counts=True)
     np.testing.assert_array_equal(u, ru)
     np.testing.assert_array_equal(c, rc)
+    for kk in (keys, keys[:1], keys[:0], np.arange(70000, dtype=np.uint64)[::-1].copy() % np.uint64(1000),
+               np.array([0, 2**64 - 1, 0, 2**63, 2**64 - 1], dtype=np.uint64)):
+        lu, lc, linv = H.localize(kk)                               # radix sort of (key, position) pairs
+        eu, einv, ec = np.unique(kk, return_inverse=True, return_counts=True)
+        np.testing.assert_array_equal(lu, eu)
+        np.testing.assert_array_equal(lc, ec)
+        np.testing.assert_array_equal(linv, einv)
     # a dictionary that lacks every third key: those non-zeros are dropped
     d = ru[np.arange(len(ru)) % 3 != 0]
     loc = H.remap_keys(keys, d, threads)
