@@ -30,6 +30,13 @@ def test_parse_shipped_configs():
 REFERENCE = os.environ.get("PSB_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
+def test_evaluation_and_warm_start_job_files():
+    ev = cfg.load_app_config(os.path.join(ROOT, "config", "rcv1_eval.conf")).linear_method
+    assert not ev.has("solver") and ev.has("validation_data") and ev.has("model_input")        # selects the evaluation app
+    warm = cfg.load_app_config(os.path.join(ROOT, "config", "rcv1_l1lr_warm.conf")).linear_method
+    assert warm.init_w.type == "FILE" and warm.init_w.file_name == "output/rcv1" and warm.has("validation_data")
+
+
 @pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(REFERENCE, "config", "*.conf"))))
 def test_reference_job_files_parse_unchanged(path):
     if path.endswith("mpi.conf"):
