@@ -432,13 +432,27 @@ class BatchScheduler:
         # iterations
         tau = sol.max_block_delay
         orders = block_order(nblk, sol.max_pass_of_data, sol.random_feature_block_order, int(self.flags.seed))
+        # blocks of the important feature groups come first in the first pass, num_iter_for_prior_fea_group times
+        # each and with zero delay (batch_solver.cc:89-107, darling.cc:39-50).  A TERAFEA key carries its group in
+        # its top 10 bits, so a group's blocks are those whose key range meets the group's.
+        prior: List[int] = []
+        prng = np.random.RandomState(int(self.flags.seed) + 1)
+        for g in sol.prior_fea_group:
+            glo, ghi = int(g) << 54, (int(g) + 1) << 54
+            tmp = [k for k, (b0, b1) in enumerate(self.blocks) if max(b0, glo) < min(b1, ghi)]
+            for _ in range(int(sol.num_iter_for_prior_fea_group) if tmp else 0):
+                if sol.random_feature_block_order:
+                    prng.shuffle(tmp)
+                prior += list(tmp)
+        self.prior_blocks = prior
         kkt, reset = 1e20, False
         first_task = None
         tm = None
         t_start = time.time()
         for it in range(sol.max_pass_of_data):
             t_it = time.time()
-            for i, b in enumerate(orders[it].tolist()):
+            order = (prior if it == 0 else []) + orders[it].tolist()
+            for i, b in enumerate(order):
                 kw = dict(key=self.blocks[b], fea_grp=[1])
                 if i == 0:
                     kw["kkt_filter_threshold"] = kkt
@@ -446,7 +460,7 @@ class BatchScheduler:
                         kw["kkt_filter_reset"] = True
                 wait_time = -1
                 if tm is not None and first_task is not None and (tm + 1) - tau > first_task:
-                    wait_time = tm - tau
+                    wait_time = tm if (it == 0 and i < len(prior)) else tm - tau       # zero delay for the prior blocks
                 tm = self._submit(_call("UPDATE_MODEL", **kw), wait=False, wait_time=wait_time)
                 if first_task is None:
                     first_task = tm

@@ -220,3 +220,39 @@ linear_method {
     P = np.fromfile(tmp_path / "scores_P", dtype=np.float32)
     np.testing.assert_array_equal(L, y.numpy()[h:])
     assert len(P) == 400 and float(np.mean((P >= 0) == (L > 0))) == pytest.approx(res["accuracy"], abs=1e-6)
+
+
+def test_prior_feature_groups_go_first(tmp_path):
+    """solver { prior_fea_group: g num_iter_for_prior_fea_group: n }: the blocks that hold group g's keys (top 10 bits
+    of a key) are swept n extra times at the start of the first pass, before the regular order."""
+    from parameter_server_b200.apps import linear_cpu
+
+    rows, cols = 800, 600
+    off, idx, vals, y = planted(rows, cols, 10, 13, False)
+    grp = torch.where(idx % 3 == 0, 127, torch.where(idx % 3 == 1, 120, 5)).to(torch.int64)     # three feature groups
+    keys = (grp << 54) | idx
+    write_libsvm_parts(str(tmp_path / "train"), off, keys, vals, y, 2)
+    text = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.5, ratio=1.0, passes=2, tail=0)
+    text = text.replace("random_feature_block_order: true", "random_feature_block_order: true prior_fea_group: 127 num_iter_for_prior_fea_group: 3")
+    seen = []
+    orig = linear_cpu.BatchScheduler._submit
+
+    def spy(self, payload, wait=True, wait_time=-1):
+        call = linear_cpu.parse(payload.decode(), cfg.LMCall)
+        if call.cmd == "UPDATE_MODEL":
+            seen.append((call.key.begin, call.key.end))
+        return orig(self, payload, wait, wait_time)
+
+    linear_cpu.BatchScheduler._submit = spy
+    try:
+        prog = run_local_threads(cfg.Flags(num_workers=2, num_servers=2, seed=0), text)
+    finally:
+        linear_cpu.BatchScheduler._submit = orig
+    glo, ghi = 127 << 54, 128 << 54
+    nblk = len(set(seen))
+    in_group = [r for r in set(seen) if max(r[0], glo) < min(r[1], ghi)]
+    assert 0 < len(in_group) < nblk
+    head = seen[:3 * len(in_group)]
+    assert all(r in in_group for r in head) and len(seen) == 3 * len(in_group) + 2 * nblk
+    assert all(head.count(r) == 3 for r in in_group)
+    assert prog[-1]["objv"] < prog[0]["objv"]
