@@ -280,14 +280,25 @@ class Postoffice {
   bool wait_nodes_and_init(double timeout_s) {
     {
       std::unique_lock<std::mutex> l(mu_);
-      if (!nodes_cv_.wait_for(l, std::chrono::duration<double>(timeout_s), [&] { return (int)pending_nodes_.size() >= num_workers_ + num_servers_; }))
-        return false;
+      // every worker and every server must have registered; stand-by nodes (role UNUSED) join the table if they
+      // are there by then, they are not waited for
+      auto complete = [&] {
+        int w = 0, s = 0;
+        for (auto& n : pending_nodes_) { w += n.role == Node::WORKER; s += n.role == Node::SERVER; }
+        return w >= num_workers_ && s >= num_servers_;
+      };
+      if (!nodes_cv_.wait_for(l, std::chrono::duration<double>(timeout_s), complete)) return false;
     }
     std::vector<Node> nodes;
     {
       std::lock_guard<std::mutex> l(mu_);
       int si = 0;
-      std::sort(pending_nodes_.begin(), pending_nodes_.end(), [](const Node& a, const Node& b) { return a.id < b.id; });
+      // by role letter, then by number: S2 before S10, so that server i owns the i-th key range
+      auto num = [](const std::string& id) { return id.size() > 1 ? std::atoi(id.c_str() + 1) : 0; };
+      std::sort(pending_nodes_.begin(), pending_nodes_.end(), [&](const Node& a, const Node& b) {
+        if (a.id.empty() || b.id.empty() || a.id[0] != b.id[0]) return a.id < b.id;
+        return num(a.id) != num(b.id) ? num(a.id) < num(b.id) : a.id < b.id;
+      });
       for (auto n : pending_nodes_) {
         if (n.role == Node::SERVER) n.key = Range::all().even_divide(num_servers_, si++);
         else n.key = Range::all();

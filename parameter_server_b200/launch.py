@@ -30,7 +30,7 @@ def mpi_command(args, flags, hostfile: str) -> list:
     ``-scheduler`` unless the caller gave one."""
     from .runtime import host
 
-    n = 1 + flags.num_workers + flags.num_servers
+    n = 1 + flags.num_workers + flags.num_servers + max(int(flags.num_unused), 0)
     cmd = ["mpirun", "-np", str(n), "--hostfile", hostfile, sys.executable, "-m", "parameter_server_b200.ps", *args]
     if not any(a.lstrip("-").split("=")[0] == "scheduler" for a in args):
         ip = host().local_ip(flags.interface or "")
@@ -58,7 +58,7 @@ def main(argv=None) -> int:
     # the scheduler's address: the caller's -scheduler, else the loopback with a free port
     given = any(a.lstrip("-").split("=")[0] == "scheduler" for a in args)
     extra = [] if given else ["-scheduler", f"role:SCHEDULER,hostname:'127.0.0.1',port:{free_port()},id:'H'"]
-    n = 1 + flags.num_workers + flags.num_servers
+    n = 1 + flags.num_workers + flags.num_servers + max(int(flags.num_unused), 0)
     procs = []
     for r in range(n):
         cmd = [sys.executable, "-m", "parameter_server_b200.ps", *args, "-my_rank", str(r), *extra]

@@ -92,3 +92,19 @@ def test_mpirun_launch(tmp_path):
     assert hostfile == str(tmp_path / "hosts")
     assert "parameter_server_b200.ps" in line and "-my_rank" not in line and f"hostname:'{ip}'" in line and "mpi_hostfile" not in line
     assert len(read_model_text(str(tmp_path / "model_S0"))) > 10
+
+
+def test_stand_by_node_joins_and_leaves_with_the_job(tmp_path):
+    """-num_unused 1: a stand-by node U0 registers, idles through the job and ends with it."""
+    off, idx, vals, y = planted(400, 256, 8, 6, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 1)
+    conf = tmp_path / "job.conf"
+    conf.write_text(CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.5, ratio=0.5, passes=2, tail=0))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "parameter_server_b200.launch", "-num_servers", "1", "-num_workers", "1", "-num_unused", "1",
+                        "-app", str(conf), "-print_van"], cwd=tmp_path, env=dict(os.environ, PYTHONPATH=root), capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert (tmp_path / "model_S0").exists()
+    log = open(tmp_path / "van_U0").read()                    # it talked to the scheduler: registration, node table, termination
+    assert "U0=>H" in log and "H=>U0" in log

@@ -256,3 +256,25 @@ def test_prior_feature_groups_go_first(tmp_path):
     assert all(r in in_group for r in head) and len(seen) == 3 * len(in_group) + 2 * nblk
     assert all(head.count(r) == 3 for r in in_group)
     assert prog[-1]["objv"] < prog[0]["objv"]
+
+
+def test_many_servers_own_ranges_in_numeric_order(tmp_path):
+    """With more than ten servers S2 must come before S10: server i owns the i-th key range and its dump holds it."""
+    off, idx, vals, y = planted(600, 1024, 10, 4, True)           # keys spread over the whole uint64 space
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 1)
+    text = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.1, ratio=0.5, passes=2, tail=0)
+    run_local_threads(cfg.Flags(num_workers=1, num_servers=12, seed=0), text)
+    prev = -1
+    seen = 0
+    for i in range(12):
+        p = tmp_path / f"model_S{i}"
+        if not p.exists():
+            continue
+        m = read_model_text(str(p))
+        if not m:
+            continue
+        assert min(m) > prev, (i, min(m), prev)
+        assert (i * (2**64 - 1)) // 12 <= min(m) and max(m) < ((i + 1) * (2**64 - 1)) // 12 + 1
+        prev = max(m)
+        seen += 1
+    assert seen >= 10
