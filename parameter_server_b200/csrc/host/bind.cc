@@ -332,7 +332,7 @@ PYBIND11_MODULE(_psb_host, m) {
         auto s = f.stats();
         py::dict d;
         d["bytes_written"] = s.bytes_written; d["bytes_read"] = s.bytes_read; d["prefetched"] = s.prefetched; d["hits"] = s.hits;
-        d["misses"] = s.misses; d["peak_resident"] = s.peak_resident; d["budget_waits"] = s.budget_waits;
+        d["misses"] = s.misses; d["peak_resident"] = s.peak_resident; d["limit_waits"] = s.limit_waits;
         return d;
       });
   m.def("ftrl_minibatch", [](carray<int64_t> off, carray<int32_t> loc, py::object vals, carray<double> y, carray<double> w, int threads) {

@@ -3,7 +3,7 @@
 // Two modes.  In memory: a group's arrays stay resident and a column range is a view.  On disk
 // (-mmap_training_data): a group is written once to <dir>/<name>_grp<g>.{info,offset,index,value} in the binary
 // matrix layout and its index / value arrays leave memory; column ranges come back through a pool of prefetch
-// threads that read ahead of the solver, keyed by the task that will use the range, under a byte budget
+// threads that read ahead of the solver, keyed by the task that will use the range, under a memory limit
 // (-prefetch_mem_limit_kb) and a limit on queued jobs (-prefetch_job_limit); a range is released when its
 // task is done.  The column offsets (8 bytes per column) stay resident in both modes, so a range's size is
 // known without touching the disk.
@@ -13,7 +13,7 @@
 // the unused generic block store Ocean (src/system/ocean.{h,cc}).  Differences: ranges are read with
 // pread() into plain buffers instead of through SArray file reads, a task that was not prefetched is
 // loaded by the caller itself (counted as a miss) instead of waiting forever, and a range larger than the
-// whole budget is admitted when nothing else is resident so that it cannot block the queue.
+// whole limit is admitted when nothing else is resident so that it cannot block the queue.
 #pragma once
 #include <fcntl.h>
 #include <sys/stat.h>
@@ -57,10 +57,10 @@ using FeatureBlockPtr = std::shared_ptr<FeatureBlock>;
 class FeatureStation {
  public:
   struct Stats {
-    uint64_t bytes_written = 0, bytes_read = 0, prefetched = 0, hits = 0, misses = 0, peak_resident = 0, budget_waits = 0;
+    uint64_t bytes_written = 0, bytes_read = 0, prefetched = 0, hits = 0, misses = 0, peak_resident = 0, limit_waits = 0;
   };
 
-  // dir empty: in-memory mode.  threads: prefetch threads (disk mode).  mem_limit_kb: budget of resident ranges.
+  // dir empty: in-memory mode.  threads: prefetch threads (disk mode).  mem_limit_kb: bytes that resident ranges may take.
   FeatureStation(std::string dir, std::string name, size_t mem_limit_kb, int threads, size_t job_limit = 64, bool detail = false)
       : dir_(std::move(dir)), name_(std::move(name)), limit_(mem_limit_kb * 1024), job_limit_(job_limit), detail_(detail) {
     if (disk()) {
@@ -169,7 +169,7 @@ class FeatureStation {
     ++stats_.misses;
     const size_t cost = range_bytes_nolock(g, c0, c1);
     l.unlock();
-    FeatureBlockPtr b = load(g, grp, c0, c1);      // outside the budget's wait: the solver needs it now
+    FeatureBlockPtr b = load(g, grp, c0, c1);      // without waiting for room under the limit: the solver needs it now
     l.lock();
     resident_ += cost;
     stats_.peak_resident = std::max<uint64_t>(stats_.peak_resident, resident_);
@@ -270,9 +270,9 @@ class FeatureStation {
         j = jobs_.front();
         g = &groups_.at(j.grp);
         cost = range_bytes_nolock(*g, j.c0, j.c1);
-        // the budget: wait until the range fits, or nothing else is resident (an oversized range must not block)
+        // the memory limit: wait until the range fits, or nothing else is resident (an oversized range must not block)
         if (resident_ + reserved_ != 0 && resident_ + reserved_ + cost > limit_) {
-          ++stats_.budget_waits;
+          ++stats_.limit_waits;
           cv_.wait(l, [&] { return done_ || resident_ + reserved_ == 0 || resident_ + reserved_ + cost <= limit_; });
           if (done_) return;
           if (jobs_.empty() || jobs_.front().task != j.task) continue;   // another thread took it meanwhile

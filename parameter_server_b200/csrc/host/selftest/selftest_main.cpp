@@ -346,7 +346,7 @@ int main(int argc, char** argv) {
   }
 
   // feature store on disk: one thread queues read-ahead, two solver threads take, use and release ranges under a
-  // budget that holds about two of them; then the block gradient on a loaded range against the resident arrays
+  // memory limit that holds about two of them; then the block gradient on a loaded range against the resident arrays
   if (argc > 2) {
     const std::string dir = argv[2];
     const int64_t cols = 240, rows = 300;

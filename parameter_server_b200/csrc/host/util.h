@@ -295,7 +295,7 @@ class ThreadsafeLimitedQueue {
 };
 
 // Set bounded by total cost; insert blocks (up to a deadline) while full.  Used as the memory
-// budget of prefetch jobs.
+// allowance of prefetch jobs.
 template <typename T>
 class ThreadsafeLimitedSet {
  public:

@@ -100,7 +100,7 @@ def test_tail_feature_filter_drops_rare_keys(tmp_path):
 
 def test_features_on_disk_give_the_same_job(tmp_path, capfd):
     """-mmap_training_data: workers keep their column blocks in files of the local cache directory and read them
-    back through prefetch threads under a small budget; nothing about the result may change."""
+    back through prefetch threads under a small memory limit; nothing about the result may change."""
     rows, cols, nnz, passes, lam, ratio = 1200, 2048, 12, 3, 0.5, 2.0
     off, idx, vals, y = planted(rows, cols, nnz, 5, True)
     write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)

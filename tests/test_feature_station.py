@@ -1,5 +1,5 @@
 """Worker-side feature store: memory and disk mode give the same column ranges; prefetch threads read ahead
-under a byte budget; the native block steps run on a range that was loaded on its own."""
+under a memory limit; the native block steps run on a range that was loaded on its own."""
 import os
 import time
 
@@ -62,7 +62,7 @@ def test_disk_ranges_equal_memory_ranges(tmp_path, binary):
         disk.get(99, 1, 0, 301)
 
 
-def test_budget_bounds_what_is_resident(tmp_path):
+def test_memory_limit_bounds_what_is_resident(tmp_path):
     H = host()
     X, _ = _matrix(rows=2000, cols=400, density=0.05)
     st = H.FeatureStation(str(tmp_path), "W1", mem_limit_kb=40, threads=3)
@@ -76,7 +76,7 @@ def test_budget_bounds_what_is_resident(tmp_path):
     while st.stats()["prefetched"] < 1 and time.time() < deadline:
         time.sleep(0.01)
     time.sleep(0.1)
-    assert st.stats()["prefetched"] == 1                                # the second waits for the budget
+    assert st.stats()["prefetched"] == 1                                # the second waits for room under the limit
     assert st.resident_bytes() == sizes[0]
     for t, (c0, c1) in enumerate(blocks):                                # the solver: use, release, next
         ip, idx, val = st.get(t, 1, c0, c1)
@@ -85,7 +85,7 @@ def test_budget_bounds_what_is_resident(tmp_path):
     s = st.stats()
     assert s["prefetched"] == len(blocks) and s["misses"] == 0
     assert s["peak_resident"] <= 40 * 1024
-    assert s["budget_waits"] >= 1
+    assert s["limit_waits"] >= 1
     assert st.pending() == 0 and st.resident_bytes() == 0
 
 
@@ -100,7 +100,7 @@ def test_unprefetched_and_oversized_ranges(tmp_path):
     assert st.stats()["misses"] == 1 and st.task_used(7) and st.max_task() == 7
     st.drop(7)
     assert not st.task_used(7)
-    # larger than the whole budget: admitted once nothing else is resident
+    # larger than the whole limit: admitted once nothing else is resident
     assert st.prefetch(8, 1, 0, 100)
     ip, idx, val = st.get(8, 1, 0, 100)
     assert len(idx) == X.nnz
