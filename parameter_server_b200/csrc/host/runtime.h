@@ -307,9 +307,14 @@ class Postoffice {
       Node me = my_node();
       me.key = Range::all();
       nodes.push_back(me);
+      // table_sent_ flips under the same lock as the copy of the table that goes out and nodes_ is
+      // filled before the lock is dropped, so a registration is either in that copy or handled as
+      // a late one (never both, never neither)
+      nodes_ = nodes;
+      table_sent_ = true;
     }
-    set_nodes(nodes);
     std::string table = "INIT";
+    set_nodes(nodes);
     for (auto& n : nodes) table += " " + encode_node(n);
     for (auto& n : nodes) {
       if (n.id == my_node().id) continue;
@@ -473,10 +478,36 @@ class Postoffice {
       is >> cmd;
       if (cmd == "ADD") {
         is >> tok;
-        std::lock_guard<std::mutex> l(mu_);
-        pending_nodes_.push_back(decode_node(tok));
-        hb_[pending_nodes_.back().id].when = now_seconds();
-        nodes_cv_.notify_all();
+        MessagePtr late;
+        {
+          std::lock_guard<std::mutex> l(mu_);
+          Node n = decode_node(tok);
+          hb_[n.id].when = now_seconds();
+          if (!table_sent_) {
+            pending_nodes_.push_back(n);
+            nodes_cv_.notify_all();
+          } else {
+            // A node that registers after the table went out (a stand-by node started last, a slow
+            // machine): it joins the scheduler's table and receives the table itself, so that it is
+            // told when the job ends.  Workers and servers are never late: the broadcast waits for them.
+            bool known = false;
+            for (auto& o : nodes_) known |= o.id == n.id;
+            if (!known) {
+              n.key = Range::all();
+              nodes_.push_back(n);
+              van_->connect(n);
+            }
+            late = std::make_shared<Message>();
+            late->task.type = Task::MANAGE;
+            late->task.request = true;
+            late->task.customer = "default";
+            late->task.msg = "INIT";
+            for (auto& o : nodes_) late->task.msg += " " + encode_node(o);
+            late->sender = my_node().id;
+            late->recver = n.id;
+          }
+        }
+        if (late) queue(late);
       } else if (cmd == "INIT") {
         std::vector<Node> nodes;
         while (is >> tok) nodes.push_back(decode_node(tok));
@@ -512,7 +543,7 @@ class Postoffice {
   std::map<std::string, Customer*> customers_;
   std::map<std::string, std::vector<MessagePtr>> orphan_;
   std::vector<Node> nodes_, pending_nodes_;
-  bool nodes_ready_ = false, terminated_ = false, key_cache_ = true;
+  bool nodes_ready_ = false, table_sent_ = false, terminated_ = false, key_cache_ = true;
   std::map<std::string, HeartbeatRecord> hb_;
   std::function<void(const std::string&)> manage_app_;
   double start_time_ = now_seconds();

@@ -13,6 +13,7 @@
 // or duplicate outgoing messages.
 #pragma once
 #include <arpa/inet.h>
+#include <netdb.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <sys/socket.h>
@@ -149,7 +150,16 @@ class TcpVan : public Van {
     return Status::OK();
   }
   Status send_frame(const std::string& to, std::string frame) override {
-    std::lock_guard<std::mutex> l(send_mu_);
+    // one lock per peer: frames to one peer go out whole and in order, a peer that is slow to accept
+    // a connection holds up nobody else's traffic
+    std::mutex* peer_mu;
+    {
+      std::lock_guard<std::mutex> l2(mu_);
+      auto& slot = peer_mu_[to];
+      if (!slot) slot.reset(new std::mutex);
+      peer_mu = slot.get();
+    }
+    std::lock_guard<std::mutex> l(*peer_mu);
     int fd = -1;
     {
       std::lock_guard<std::mutex> l2(mu_);
@@ -164,29 +174,34 @@ class TcpVan : public Van {
         if (it == peers_.end()) return Status::NetError("unknown peer " + to);
         peer = it->second;
       }
+      // numeric address or host name (the reference's tcp://host:port accepts both)
+      const std::string host = peer.hostname.empty() ? "127.0.0.1" : peer.hostname;
+      addrinfo hints{}, *res = nullptr;
+      hints.ai_family = AF_INET;
+      hints.ai_socktype = SOCK_STREAM;
+      if (getaddrinfo(host.c_str(), std::to_string(peer.port).c_str(), &hints, &res) != 0 || res == nullptr)
+        return Status::NetError("cannot resolve " + host + " (node " + to + ")");
       for (int attempt = 0; attempt < retries_ && fd < 0; ++attempt) {
         fd = ::socket(AF_INET, SOCK_STREAM, 0);
-        sockaddr_in a{};
-        a.sin_family = AF_INET;
-        a.sin_port = htons((uint16_t)peer.port);
-        inet_pton(AF_INET, peer.hostname.empty() ? "127.0.0.1" : peer.hostname.c_str(), &a.sin_addr);
-        if (::connect(fd, reinterpret_cast<sockaddr*>(&a), sizeof(a)) != 0) {
-          ::close(fd);
+        if (fd < 0 || ::connect(fd, res->ai_addr, res->ai_addrlen) != 0) {
+          if (fd >= 0) ::close(fd);
           fd = -1;
           std::this_thread::sleep_for(std::chrono::milliseconds(50 * (attempt + 1)));
         }
       }
+      freeaddrinfo(res);
       if (fd < 0) return Status::NetError("cannot connect to " + to);
       int one = 1;
       setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
       std::lock_guard<std::mutex> l2(mu_);
+      if (closed_) { ::close(fd); return Status::NetError("van closed"); }
       out_fd_[to] = fd;
     }
     const uint64_t n = frame.size();
     if (!write_all(fd, &n, 8) || !write_all(fd, frame.data(), n)) {
       std::lock_guard<std::mutex> l2(mu_);
-      ::close(fd);
-      out_fd_.erase(to);
+      auto it = out_fd_.find(to);
+      if (it != out_fd_.end() && it->second == fd) { ::close(fd); out_fd_.erase(it); }
       return Status::NetError("send to " + to + " failed");
     }
     return Status::OK();
@@ -247,14 +262,19 @@ class TcpVan : public Van {
           if (n && !read_all(fd, &frame[0], n)) break;
           inbox_.push(std::move(frame));
         }
+        // forget the descriptor before closing it: its number may be handed to any other socket of
+        // the process right away, and close() must not shut that one down
+        std::lock_guard<std::mutex> l2(mu_);
+        in_fd_.erase(std::remove(in_fd_.begin(), in_fd_.end(), fd), in_fd_.end());
         ::close(fd);
       });
     }
   }
   int listen_fd_ = -1, retries_ = 3;
   std::atomic<bool> closed_{false};
-  std::mutex mu_, send_mu_;
+  std::mutex mu_;
   std::map<std::string, Node> peers_;
+  std::map<std::string, std::unique_ptr<std::mutex>> peer_mu_;
   std::map<std::string, int> out_fd_;
   std::vector<int> in_fd_;
   std::vector<std::thread> readers_;

@@ -1,7 +1,6 @@
 // psb_reduce_sum_static: the deterministic sum reduction with built-in scratch space,
 // for callers that cannot allocate device memory (see psb_noalloc.h).
 #include <cstdio>
-#include <mutex>
 
 #include "psb_noalloc.h"
 #include "reduce_kernels.cuh"
@@ -15,26 +14,10 @@ namespace {
 // address and must never be passed to a kernel.
 static __device__ __align__(256) unsigned char g_static_scratch[kReduceScratchBytes];
 
-constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {nullptr};
-std::mutex g_mu;
-
-// Device address of g_static_scratch on the current device (looked up once per device).
-cudaError_t scratch_address(void** addr) {
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-  std::lock_guard<std::mutex> lock(g_mu);
-  if (g_scratch_addr[dev] == nullptr) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_static_scratch);
-    if (e != cudaSuccess) return e;
-    g_scratch_addr[dev] = p;
-  }
-  *addr = g_scratch_addr[dev];
-  return cudaSuccess;
-}
+// Device address of g_static_scratch on the current device.  Asked for on every call: after
+// the first call on a device the runtime answers from its own tables (no device work), and
+// an address remembered here would go stale if the application reset the device.
+cudaError_t scratch_address(void** addr) { return cudaGetSymbolAddress(addr, g_static_scratch); }
 
 }  // namespace
 

@@ -34,10 +34,13 @@ extern "C" {
 // Returns 0 or a cudaError_t value.
 //
 // The function calls no cudaMalloc/cudaFree and no allocating library routine.
-// * The first call on each device looks up the device address of the built-in
-//   scratch array (cudaGetSymbolAddress, with that device current) and remembers
-//   it.  Make that first call during start-up, before any stream capture begins
-//   on that device.
+// * Every call asks the runtime for the device address of the built-in scratch
+//   array (cudaGetSymbolAddress, with the caller's device current).  The first
+//   such call on a device makes the runtime load the library's device image
+//   there: make it during start-up, before any stream capture begins on that
+//   device.  Later calls are answered from the runtime's tables.  Nothing is
+//   remembered inside this library, so a cudaDeviceReset between calls is safe
+//   (the array's contents are lost, which no call depends on).
 // * All calls on one device share the one scratch array.  The word that must be
 //   zero at launch is cleared on `stream` before every launch, but two calls
 //   whose kernels overlap on the GPU (different streams, no dependency) race on

@@ -74,10 +74,8 @@ def lib() -> C.CDLL:
                 if override:
                     _lib = C.CDLL(override)
                 else:
-                    path = _build.kernels_lib_path()
-                    if not path.exists():
-                        _build.build_kernels()
-                    _lib = C.CDLL(str(path))
+                    # returns at once when the library matches its sources (digest stamp beside it)
+                    _lib = C.CDLL(str(_build.build_kernels()))
     return _lib
 
 

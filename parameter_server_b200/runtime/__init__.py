@@ -13,9 +13,7 @@ def host():
     """The pybind11 module with the control plane, data ingest and host containers."""
     global _mod
     if _mod is None:
-        path = _build.host_lib_path()
-        if not path.exists():
-            _build.build_host()
+        path = _build.build_host()      # returns at once when the module matches its sources
         spec = importlib.util.spec_from_file_location("_psb_host", str(path))
         _mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(_mod)

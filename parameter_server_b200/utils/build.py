@@ -9,10 +9,18 @@ Two shared objects are produced next to the sources, under ``parameter_server_b2
 * ``_psb_host*.so`` — the host runtime (control-plane van, executor, parsers,
   slot reader, ...) as a pybind11 module compiled with g++.
 
-Objects are rebuilt only when a source or header is newer than the object.
+Objects are rebuilt only when a source or header is newer than the object.  Beside each library
+sits a ``.stamp`` file with a digest of the sources and flags it was built from; a loader that
+finds the digest unchanged uses the library as it is (no object files are needed for that, so
+a tree copied to another machine with its built libraries does not rebuild), any edit of a
+source or header triggers a rebuild on the next load.  Builds take a file lock, so several
+processes (one per GPU) starting at once build once.
 """
 from __future__ import annotations
 
+import contextlib
+import fcntl
+import hashlib
 import os
 import shutil
 import subprocess
@@ -67,22 +75,49 @@ def host_lib_path() -> Path:
     return LIB / ("_psb_host" + suffix)
 
 
-def extra_include_dirs() -> list[str]:
-    """CUTLASS/CuTe header trees vendored inside site-packages (used by the GEMM kernels)."""
-    out = []
-    for p in sys.path:
-        cand = Path(p) / "flashinfer" / "data" / "cutlass" / "include"
-        if cand.is_dir():
-            out.append(str(cand))
-            break
-    return out
+def _digest(paths, flags) -> str:
+    h = hashlib.sha256(" ".join(flags).encode())
+    for p in sorted(paths):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def _fresh(out: Path, digest: str) -> bool:
+    stamp = out.with_suffix(".stamp")
+    try:
+        return out.exists() and stamp.read_text().strip() == digest
+    except OSError:
+        return False
+
+
+@contextlib.contextmanager
+def _build_lock():
+    LIB.mkdir(exist_ok=True)
+    with open(LIB / ".build.lock", "w") as f:
+        fcntl.flock(f, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(f, fcntl.LOCK_UN)
 
 
 def build_kernels(force: bool = False, verbose: bool = False) -> Path:
-    LIB.mkdir(exist_ok=True)
-    OBJ.mkdir(exist_ok=True)
     headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
     sources = sorted(CSRC.glob("*.cu"))
+    extra = os.environ.get("PSB_NVCC_EXTRA", "").split()
+    digest = _digest(sources + headers, NVCC_FLAGS + extra)
+    out = kernels_lib_path()
+    if not force and _fresh(out, digest):
+        return out
+    with _build_lock():
+        if not force and _fresh(out, digest):      # another process built it while this one waited
+            return out
+        return _build_kernels_locked(sources, headers, digest, force, verbose)
+
+
+def _build_kernels_locked(sources, headers, digest, force, verbose) -> Path:
+    OBJ.mkdir(exist_ok=True)
     nvcc = _nvcc()
     jobs = []
     for src in sources:
@@ -98,8 +133,10 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
                     sys.stderr.write(r.stderr)
     objs = [OBJ / (s.stem + ".o") for s in sources]
     out = kernels_lib_path()
-    if force or jobs or _newer(objs, out):
-        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-lcudart", "-lcuda"])
+    tmp = out.with_suffix(".so.tmp")
+    _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart", "-lcuda"])
+    os.replace(tmp, out)
+    out.with_suffix(".stamp").write_text(digest)
     return out
 
 
@@ -109,11 +146,21 @@ def build_host(force: bool = False) -> Path | None:
     sources = sorted(HOST.glob("*.cc"))
     if not sources:
         return None
+    headers = list(HOST.glob("*.h"))
+    digest = _digest(sources + headers, CXX_FLAGS + [os.environ.get("PSB_CXX", "g++")])
+    out = host_lib_path()
+    if not force and _fresh(out, digest):
+        return out
+    with _build_lock():
+        if not force and _fresh(out, digest):
+            return out
+        return _build_host_locked(sources, headers, digest, force)
+
+
+def _build_host_locked(sources, headers, digest, force) -> Path:
     import pybind11
 
-    LIB.mkdir(exist_ok=True)
     OBJ.mkdir(exist_ok=True)
-    headers = list(HOST.glob("*.h"))
     inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(HOST)]
     jobs = []
     for src in sources:
@@ -125,8 +172,10 @@ def build_host(force: bool = False) -> Path | None:
             list(ex.map(lambda j: _run(*j), jobs))
     objs = [OBJ / ("host_" + s.stem + ".o") for s in sources]
     out = host_lib_path()
-    if force or jobs or _newer(objs, out):
-        _run([os.environ.get("PSB_CXX", "g++"), "-shared", "-Wl,-Bsymbolic", "-o", str(out), *map(str, objs), "-pthread", "-lz"])
+    tmp = out.with_suffix(".tmp")
+    _run([os.environ.get("PSB_CXX", "g++"), "-shared", "-Wl,-Bsymbolic", "-o", str(tmp), *map(str, objs), "-pthread", "-lz"])
+    os.replace(tmp, out)
+    out.with_suffix(".stamp").write_text(digest)
     return out
 
 

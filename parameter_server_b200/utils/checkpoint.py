@@ -118,8 +118,9 @@ def save_ftrl(eng, directory: str, step: int) -> str:
     path = _path(directory, "ftrl", eng.group.rank, step)
     tmp = path + ".tmp"
     sketch = eng.cm.cpu() if getattr(eng, "cm", None) is not None else None
-    torch.save({"step": step, "cap": eng.cap, "seps": eng.seps, "hyper": eng.hyper.__dict__, "table": eng.tab.local.cpu(),
-                "stats": eng.stats.cpu(), "sketch": sketch}, tmp)
+    # plain tensors, numbers and strings only, so that the file loads with weights_only=True
+    torch.save({"step": step, "cap": eng.cap, "seps": [int(x) for x in eng.seps], "hyper": dict(eng.hyper.__dict__),
+                "epoch": int(eng.epoch), "table": eng.tab.local.cpu(), "stats": eng.stats.cpu(), "sketch": sketch}, tmp)
     os.replace(tmp, path)
     return path
 
@@ -130,8 +131,8 @@ def load_ftrl(eng, directory: str, step: int = -1) -> int:
         step = _agree_on_step(eng.group, _latest(directory, "ftrl", eng.group.rank))
     if step < 0:
         return -1
-    st = torch.load(_path(directory, "ftrl", eng.group.rank, step), map_location="cpu", weights_only=False)
-    if st["cap"] != eng.cap or list(st["seps"]) != list(eng.seps):
+    st = torch.load(_path(directory, "ftrl", eng.group.rank, step), map_location="cpu", weights_only=True)
+    if st["cap"] != eng.cap or [int(x) for x in st["seps"]] != [int(x) for x in eng.seps]:
         raise RuntimeError("checkpoint was written with a different table capacity or key-range partition")
     eng.tab.local.copy_(st["table"].to(eng.dev))
     eng.stats.copy_(st["stats"].to(eng.dev))
@@ -139,5 +140,17 @@ def load_ftrl(eng, directory: str, step: int = -1) -> int:
         if st["sketch"].numel() != eng.cm.numel():
             raise RuntimeError("checkpoint was written with a different count-min width")
         eng.cm.copy_(st["sketch"].to(eng.dev))
+    # The step protocol of the fused kernels compares flag words with the engine's epoch: every rank
+    # continues from the stored epoch with its flags saying "everything up to here has arrived and is
+    # applied", whether the engine is fresh or has run steps before the load.
+    epoch = int(st.get("epoch", 0))
+    epochs = eng.group.all_reduce_max(float(epoch))
+    if int(epochs) != epoch:
+        raise RuntimeError(f"rank {eng.group.rank}: checkpoint epoch {epoch} differs from another rank's ({int(epochs)})")
+    eng.group.barrier()           # no kernel of an earlier step is still writing flags
+    eng.epoch = epoch
+    eng.in_flag.local.fill_(epoch << 32)
+    eng.applied.local.fill_(epoch << 32)
+    torch.cuda.synchronize(eng.dev) if eng.dev.type == "cuda" else None
     eng.group.barrier()
     return st["step"]

@@ -204,3 +204,29 @@ def test_wire_roundtrip_with_compression():
     n_plain, m1 = H.encode_decode(parts[0], False)
     n_zip, m2 = H.encode_decode(parts[0], True)
     assert m1.key == m2.key == parts[0].key and m1.values == m2.values and n_zip < n_plain
+
+
+@pytest.mark.parametrize("tcp", [False, True])
+def test_stand_by_node_that_registers_after_the_table_went_out(tcp):
+    """A stand-by node (role UNUSED) started late still gets the node table and the end of the job
+    (node roles of src/system/postoffice.cc:185-243; stand-by nodes are never waited for)."""
+    c = Cluster(W=1, S=1, tcp=tcp)
+    try:
+        node = H.Node(H.UNUSED, "U0", "127.0.0.1", 0)
+        if tcp:
+            van = H.TcpVan(node)
+            van.bind()
+        else:
+            van = H.InprocVan(c.hub, node)
+        po = H.Postoffice(van, 1, 1)
+        po.set_scheduler(c.vans["H"].my_node)
+        po.start()
+        c.po["U0"] = po
+        po.register_with_scheduler()                 # the scheduler broadcast its table long ago
+        assert po.wait_nodes_ready(10.0)
+        assert sorted(n.id for n in po.nodes()) == ["H", "S0", "U0", "W0"]
+        assert "U0" in [n.id for n in c.po["H"].nodes()]
+        c.po["H"].stop_all()
+        assert po.wait_terminate(10.0)
+    finally:
+        c.stop()

@@ -17,9 +17,9 @@ pytestmark = pytest.mark.gpu
 
 
 def _lib():
-    from parameter_server_b200.utils.build import kernels_lib_path
+    from parameter_server_b200.ops._native import lib as kernels_lib
 
-    lib = C.CDLL(str(kernels_lib_path()))
+    lib = kernels_lib()             # builds the library first when it is missing or out of date
     lib.psb_reduce_sum_static.restype = C.c_int
     lib.psb_reduce_sum_static.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p]
     return lib
