@@ -52,7 +52,7 @@ class ClockSampler:
             if not uuid.startswith("GPU-"):
                 uuid = "GPU-" + uuid
             self.cmd = ["nvidia-smi", "-i", uuid, f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits",
-                        "-lms", "100"]
+                        "-lms", "50"]
         except Exception:
             self.cmd = None
 
@@ -94,11 +94,41 @@ class ClockSampler:
         return out
 
 
+def _cpu_ftrl_arm(rows: int, steps: int) -> dict:
+    """The host runtime's own online step (what a CPU worker + CPU server do per minibatch: radix localizer,
+    model lookup, threaded margins / loss / gradient, per-key FTRL update; csrc/host) on a sub-sample of the
+    same stream, all cores of this machine, no network in between."""
+    import numpy as np
+
+    from parameter_server_b200.data.synthetic import ctr_minibatch
+    from parameter_server_b200.runtime import host
+
+    H = host()
+    threads = os.cpu_count() or 1
+    model = H.FTRLModel(0.1, 1.0, 1.0, 0.1)
+    data = []
+    for i in range(steps + 1):
+        off, keys, y = ctr_minibatch(rows, seed=900001 + i, device="cpu")
+        data.append((off.numpy(), keys.numpy().view(np.uint64), y.numpy().astype(np.float64)))
+    t0 = None
+    for i, (off, keys, y) in enumerate(data):
+        if i == 1:
+            t0 = time.perf_counter()        # the first minibatch warms the code up
+        ukeys, _, loc = H.localize(keys)
+        w = model.get(ukeys)
+        _, g, pos, neg = H.ftrl_minibatch(off, loc, None, y, w, threads)
+        model.update(ukeys, g, pos, neg)
+    dt = time.perf_counter() - t0
+    return {"value": rows * steps / dt, "unit": "examples/s", "rows_per_minibatch": rows, "minibatches": steps,
+            "threads": threads, "what": "native host runtime step (localize, lookup, minibatch gradient, FTRL update), "
+                                        "count rule, in-process, declared sub-sample of the same stream"}
+
+
 def run_ftrl(args) -> dict:
     import torch
 
     from parameter_server_b200.data.synthetic import ctr_minibatch
-    from parameter_server_b200.models.ftrl import DeviceMinibatch, FTRLEngine, FTRLHyper
+    from parameter_server_b200.models.ftrl import KEY_U32_HASHED, DeviceMinibatch, FTRLEngine, FTRLHyper
     from parameter_server_b200.models.ftrl_trainer import FTRLTrainer, HostMinibatch
     from parameter_server_b200.parallel.peer import PeerGroup
 
@@ -106,81 +136,145 @@ def run_ftrl(args) -> dict:
     dev, rank, world = group.device, group.rank, group.world
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    rows, ring = args.rows, args.ring
-    batches = []
+    rows = args.rows
+    # every step of warm-up and of the timed region gets a minibatch of its own, so that the timed steps
+    # meet keys that the model has not seen (entries are created inside the timed region)
+    # (at most 48 per GPU: beyond that the stream wraps around and `new_keys_per_step` says so)
+    ring = min(max(args.ring, args.warmup + args.steps), max(args.ring, 48))
+    if args.ring < 0:
+        ring = -args.ring        # replay exactly this many minibatches (after warm-up no step creates a key)
+    batches, ids = [], []
     for i in range(ring):
-        off, keys, y = ctr_minibatch(rows, seed=1000 * rank + i + 1, device=dev)
+        off, keys, y, fid = ctr_minibatch(rows, seed=1000 * rank + i + 1, device=dev, return_ids=True)
         batches.append(DeviceMinibatch(off, keys, y))
+        ids.append(fid)
     max_nnz = max(b.nnz for b in batches)
-    eng = FTRLEngine(group, FTRLHyper(alpha=0.1, beta=1.0, lambda1=1.0, lambda2=0.1, rule=args.rule),
-                     table_capacity=1 << args.table_log2, max_rows=rows, max_nnz=max_nnz,
-                     local_capacity=1 << args.local_log2, timeout_s=args.timeout_s,
-                     impl="nccl" if args.impl == "nccl" else "fused",
-                     track_counts=True if args.track_counts else None)
-    # ---------------------------------------------------------------- device-resident timing
-    for i in range(args.warmup):
-        eng.step(batches[i % ring])
-    eng.read_stats()
-    eng.check_status()
-    group.barrier()
-    sampler = ClockSampler(dev)
-    sampler.start()
-    launches0 = eng.kernel_launches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        eng.step(batches[(args.warmup + i) % ring])
-    e1.record()
-    torch.cuda.synchronize(dev)
-    ms = group.all_reduce_max(e0.elapsed_time(e1))
-    group.barrier()
-    launches = eng.kernel_launches - launches0
-    phases = eng.phase_times_us() if args.impl != "nccl" else None
-    st = eng.read_stats()
-    eng.check_status()
-    # ---------------------------------------------------------------- end to end (public API)
-    ex_per_step = rows * world
-    e2e = None
-    if not args.no_e2e:
-        host = [HostMinibatch(b.offsets.cpu(), b.keys.cpu(), b.y.cpu()).pin() for b in batches]
+    hyper = FTRLHyper(alpha=0.1, beta=1.0, lambda1=1.0, lambda2=0.1, rule=args.rule)
+
+    def engine(impl):
+        return FTRLEngine(group, hyper, table_capacity=1 << args.table_log2, max_rows=rows, max_nnz=max_nnz,
+                          local_capacity=1 << args.local_log2, timeout_s=args.timeout_s, impl=impl,
+                          track_counts=True if args.track_counts else None)
+
+    def device_arm(impl, sampler=None):
+        """W warm-up steps, then K timed steps on minibatches resident on the device; CUDA events, max over ranks."""
+        eng = engine(impl)
+        for i in range(args.warmup):
+            eng.step(batches[i % ring])
+        st0 = eng.read_stats()
+        eng.check_status()
+        group.barrier()
+        if sampler:
+            sampler.start()
+        launches0 = eng.kernel_launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            eng.step(batches[(args.warmup + i) % ring])
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = group.all_reduce_max(e0.elapsed_time(e1))
+        group.barrier()
+        out = {"ms": ms, "launches": eng.kernel_launches - launches0,
+               "phases": eng.phase_times_us() if impl == "fused" else None}
+        st = eng.read_stats()
+        eng.check_status()
+        out["stats"], out["entries_before"] = st, st0["table_entries"]
+        del eng
+        torch.cuda.empty_cache()
+        return out
+
+    def e2e_arm(impl, host, what):
+        """The public streaming API on a fresh model: every step copies its minibatch from pinned host memory and
+        reads its loss back; W warm-up steps, K timed steps."""
+        eng = engine(impl)
         trainer = FTRLTrainer(eng)
-        trainer.train(host[i % ring] for i in range(max(3, args.warmup)))
+        warm = trainer.train(host[i % ring] for i in range(args.warmup))
         group.barrier()
         trainer.h2d_bytes = trainer.d2h_bytes = 0
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
-        losses = trainer.train(host[i % ring] for i in range(args.steps))
+        losses = trainer.train(host[(args.warmup + i) % ring] for i in range(args.steps))
         t1.record()
         torch.cuda.synchronize(dev)
-        e2e_ms = group.all_reduce_max(t0.elapsed_time(t1))
-        e2e = {"value": ex_per_step * args.steps / (e2e_ms / 1e3), "unit": "examples/s",
-               "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": trainer.h2d_bytes // args.steps,
-               "d2h_bytes_per_step": trainer.d2h_bytes // args.steps,
-               "mean_logloss_last": losses[-1] if losses else None,
-               "h2d_gbs_per_gpu": trainer.h2d_bytes / args.steps / (e2e_ms / args.steps) / 1e6,
-               "numa": getattr(group, "numa", None)}
+        ms = group.all_reduce_max(t0.elapsed_time(t1))
+        group.barrier()
+        out = {"value": rows * world * args.steps / (ms / 1e3), "unit": "examples/s", "ms_per_step": ms / args.steps,
+               "h2d_bytes_per_step": trainer.h2d_bytes // args.steps, "d2h_bytes_per_step": trainer.d2h_bytes // args.steps,
+               "h2d_gbs_per_gpu": trainer.h2d_bytes / args.steps / (ms / args.steps) / 1e6, "input_encoding": what,
+               # progressive validation: every minibatch is scored with the model from before it was trained on
+               "logloss_per_step_rank0": [round(x, 4) for x in warm + losses], "table_grown": eng.grown}
+        del trainer, eng
+        torch.cuda.empty_cache()
+        return out
+
+    ex_per_step = rows * world
+    main_impl = "nccl" if args.impl == "nccl" else "fused"
+    sampler = ClockSampler(dev)      # samples from the first timed region to the last one
+    fused = device_arm(main_impl, sampler)
+    nccl = None if (args.no_baseline or main_impl == "nccl") else device_arm("nccl")
+    value = ex_per_step * args.steps / (fused["ms"] / 1e3)
+    vs = None
+    if nccl is not None:
+        nccl_value = ex_per_step * args.steps / (nccl["ms"] / 1e3)
+        vs = {"baseline": "NCCL-only path of the same algorithm (stand-alone kernels, all_to_all_single), same process "
+                          "group, same minibatches, same warm-up and steps",
+              "nccl_ms_per_step": nccl["ms"] / args.steps, "nccl_value": nccl_value, "ratio": value / nccl_value,
+              "nccl_gpu_launches": nccl["launches"]}
+    # ---------------------------------------------------------------- end to end (public API)
+    e2e = None
+    if not args.no_e2e:
+        host = [HostMinibatch(b.offsets.cpu(), b.keys.cpu(), b.y.cpu()).pin() for b in batches]
+        e2e = e2e_arm(main_impl, host, "uint64 keys, int64 row offsets")
+        if nccl is not None:
+            base = e2e_arm("nccl", host, "uint64 keys, int64 row offsets")
+            vs["nccl_e2e_value"], vs["e2e_ratio"] = base["value"], e2e["value"] / base["value"]
+            # time to a stated progressive logloss: both arms run the same arithmetic, so the step count is the same
+            target = args.logloss_target
+            trace = e2e["logloss_per_step_rank0"]
+            hit = next((i + 1 for i, x in enumerate(trace) if i > 0 and x <= target), None)
+            vs["time_to_logloss"] = {"target": target, "steps": hit,
+                                     "fused_ms": None if hit is None else hit * e2e["ms_per_step"],
+                                     "nccl_ms": None if hit is None else hit * base["ms_per_step"]}
+        del host
+        # the same stream in its compact form: 32-bit feature ids (hashed to the same uint64 keys on the device)
+        # and 32-bit row offsets
+        compact = [HostMinibatch(b.offsets.to(torch.int32).cpu(), f.cpu(), b.y.cpu(), None, KEY_U32_HASHED).pin()
+                   for b, f in zip(batches, ids)]
+        e2e["compact"] = e2e_arm(main_impl, compact, "uint32 feature ids hashed on the device, int32 row offsets")
     clocks = sampler.stop()
+    cpu = None
+    if rank == 0 and not args.no_cpu:
+        try:
+            cpu = _cpu_ftrl_arm(20000, 3)
+        except Exception as e:      # the CPU arm never fails the GPU benchmark
+            cpu = {"unavailable": repr(e)}
     group.barrier()
+    st = fused["stats"]
     return {
         "metric": "examples/sec (online FTRL-proximal L1-LR, CTR-scale stream)",
-        "value": ex_per_step * args.steps / (ms / 1e3),
+        "value": value,
         "unit": "examples/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": fused["ms"] / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": vs,
         "dtype": "fp32", "data": "synthetic",
-        "impl": "nccl-baseline" if args.impl == "nccl" else "fused",
+        "impl": "nccl-baseline" if main_impl == "nccl" else "fused",
         "config": {"model": "FTRL-proximal logistic regression, 2^30 hashed uint64 keys Zipf(1.1), ~96 nnz/row, "
                             "alpha=0.1 beta=1 lambda1=1 lambda2=0.1, per-key fp32 state, rule=" + args.rule,
                    "global_batch": ex_per_step, "seq_len": None, "nnz_per_row": max_nnz / rows,
                    "parallelism": f"dp{world} x key-range shards {world} (worker+server per GPU)",
-                   "l2_policy": f"inputs larger than L2: ring of {ring} distinct minibatches "
-                                f"({batches[0].nbytes() >> 20} MiB each) plus {max_nnz * 4 >> 20} MiB slot map per step",
+                   "l2_policy": f"inputs larger than L2: every step reads a minibatch of its own "
+                                f"({batches[0].nbytes() >> 20} MiB, {ring} distinct ones per GPU) and writes a "
+                                f"{max_nnz * 4 >> 20} MiB slot map",
                    "mean_logloss_last": st["loss_sum"] / max(st["rows"], 1), "nnz_w": st["nnz_w"],
                    "unique_keys_per_step": st["unique_keys"] / max(args.steps, 1),
-                   "phase_us_last_step_rank0": phases},
+                   "new_keys_per_step": (st["table_entries"] - fused["entries_before"]) / max(args.steps, 1),
+                   "table_entries": st["table_entries"],
+                   "phase_us_last_step_rank0": fused["phases"]},
         "e2e": e2e,
-        "gpu_launches": launches,
+        "cpu": cpu,
+        "gpu_launches": fused["launches"],
         "clocks": clocks,
     }, rank
 
@@ -309,7 +403,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "fused", "nccl", "reference"])
     ap.add_argument("--rows", type=int, default=100000, help="minibatch rows per GPU")
-    ap.add_argument("--ring", type=int, default=4, help="distinct minibatches per GPU")
+    ap.add_argument("--ring", type=int, default=0, help="distinct minibatches per GPU (at least warm-up + steps; negative: replay exactly that many)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL-only arm (vs_baseline stays null)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU arm")
+    ap.add_argument("--logloss-target", type=float, default=0.2,
+                    help="progressive mean logloss whose first crossing is reported as time to objective")
     ap.add_argument("--table-log2", type=int, default=26, help="log2 slots of each GPU's shard table")
     ap.add_argument("--local-log2", type=int, default=22, help="log2 slots of the per-minibatch dedup table")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host-streaming) measurement")

@@ -210,17 +210,20 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
     eng = FTRLEngine(group, hyper, table_capacity=max(int(s.countmin_n) // max(group.world, 1), 1 << 16), max_rows=mb,
                      max_nnz=max_nnz, local_capacity=min(max_nnz, 1 << 24), timeout_s=float(flags.timeout_s),
                      impl="nccl" if flags.impl == "nccl" else "fused")
-    trainer = FTRLTrainer(eng, with_vals=True)
+    trainer = FTRLTrainer(eng)
 
     def batches():
-        # every rank must run the same number of steps: ranks that run out of data feed empty minibatches
+        # every rank must run the same number of steps: ranks that run out of data feed empty minibatches.
+        # The ranks agree on "anybody still has data" over a host-side (gloo) group, so that the question never
+        # waits for, or holds up, the kernels of the step in flight.
         import torch.distributed as dist
 
+        ctl = dist.new_group(backend="gloo") if group.world > 1 else None
         while True:
             out = reader.read(mb)
-            have = torch.tensor([0 if out is None else 1], device=group.device)
-            if group.world > 1:
-                dist.all_reduce(have, group=group.group)
+            have = torch.tensor([0 if out is None else 1])
+            if ctl is not None:
+                dist.all_reduce(have, group=ctl)
             if have.item() == 0:
                 return
             if out is None:
@@ -233,8 +236,6 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
             yield HostMinibatch(torch.from_numpy(sl["offset"].astype(np.int64)), torch.from_numpy(sl["index"].view(np.int64)), y, v).pin()
 
     t0 = time.time()
-    trainer_with_vals = trainer
-    losses = []
     seen = 0
     last = time.time()
     # checkpoint / resume: the shard tables are saved every checkpoint_interval minibatches; a restarted job
@@ -254,23 +255,33 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
         from ..parallel.monitor import RankMonitor
 
         mon = RankMonitor(group.rank, group.world, deadline_s=max(10.0, 5.0 * float(flags.report_interval)))
-    for hb in batches():
-        step += 1
-        if mon is not None:
-            mon.tick(step, float(flags.report_interval))
-        if step <= start_step:
+
+    def stream():
+        # minibatches that a checkpoint already covers are read and skipped; the rest go to the trainer, which
+        # uploads minibatch i+1 while step i computes
+        nonlocal step, seen
+        for hb in batches():
+            step += 1
+            if mon is not None:
+                mon.tick(step, float(flags.report_interval))
             seen += hb.y.numel()
-            continue
-        if hb.vals is None:
-            hb.vals = torch.ones(hb.keys.numel()).pin_memory() if hb.keys.numel() else torch.zeros(0)
-        losses += trainer_with_vals.train([hb])
-        seen += hb.y.numel()
-        if ckdir and ckint > 0 and step % ckint == 0:
-            save_ftrl(eng, ckdir, step)
+            if step > start_step:
+                yield hb
+
+    def after_step(i):
+        at = start_step + i + 1
+        if ckdir and ckint > 0 and at % ckint == 0:
+            torch.cuda.synchronize(group.device)        # the model as of minibatch `at`
+            save_ftrl(eng, ckdir, at)
+
+    def on_loss(i, loss):
+        nonlocal last
         if group.rank == 0 and time.time() - last >= s.eval_interval:
             st = eng.read_stats(reset=False)
-            print("%10d examples, loss %.5e, penalty %.5e, |w|_0 %8d" % (seen * group.world, losses[-1], eng.penalty(st), int(st["nnz_w"])))
+            print("%10d examples, loss %.5e, penalty %.5e, |w|_0 %8d" % (seen * group.world, loss, eng.penalty(st), int(st["nnz_w"])))
             last = time.time()
+
+    losses = trainer.train(stream(), after_step=after_step, on_loss=on_loss)
     st = eng.read_stats(reset=False)
     out = {"seconds": time.time() - t0, "examples": seen, "mean_logloss_last": losses[-1] if losses else None,
            "nnz_w": st["nnz_w"], "penalty": eng.penalty(st)}

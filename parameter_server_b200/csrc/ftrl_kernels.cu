@@ -5,23 +5,32 @@
 // One rank = one GPU = worker r (streams minibatches) + server r (owns the keys
 // of [sep[r], sep[r+1]) in an open-addressing table {key -> w, z, pos, neg}).
 //
-//   ftrl_pull_spmv  : de-duplicate the minibatch's keys into an L2-resident local
-//                     table, gather each unique key's weight straight from the
-//                     owner shard's table with peer loads over NVLink, then run
-//                     the CSR SpMV X·w, the logistic loss and the per-row
-//                     coefficient −y/(1+e^{y·Xw}) — one cooperative kernel.
-//   ftrl_push_update: Xᵀ·coef and the pos/neg row counts per unique key, routed by
-//                     key range into the owner's per-sender inbox with peer
-//                     stores, a release flag per (sender, owner), and — on
-//                     arrival of all senders — the owner-side FTRL update applied
-//                     sender by sender, then an "applied" notification to every
-//                     peer — one cooperative kernel.
+//   ftrl_pull_spmv  : de-duplicate the minibatch's keys into a per-minibatch table
+//                     that is laid out by owner; every owner then reads "its" region
+//                     of every worker's table with coalesced peer loads over NVLink,
+//                     looks the keys up in its own shard (creating missing ones),
+//                     remembers the shard slot of every request and stores the
+//                     weights straight into the worker's weight array with coalesced
+//                     peer stores; the worker runs the CSR SpMV X·w, the logistic
+//                     loss and the per-row coefficient −y/(1+e^{y·Xw}) — one
+//                     cooperative kernel.
+//   ftrl_push_update: Xᵀ·coef and the pos/neg row counts per unique key into the
+//                     worker's accumulator array; every owner reads its region of
+//                     every worker's accumulators with coalesced peer loads and
+//                     applies the FTRL update to the slots it remembered, worker by
+//                     worker — one cooperative kernel.
+//
+// No key is hashed twice on the owner, no record is packed, routed or copied into an
+// inbox: the per-minibatch table IS the message, and what crosses NVLink are whole
+// 1024-slot chunks (8 bytes of key out, 4 bytes of weight back, 4 or 16 bytes of
+// gradient out per slot).
 //
 // The arithmetic is the reference's server rule FTRLModel::setValue
 // (src/linear_method/ftrl_model.h:81-112), the worker gradient of LogitLoss
 // (src/linear_method/loss.h:73-88) and FTRL::countKeys
 // (src/linear_method/ftrl.cc:154-174); the message flow replaces
-// SharedParameter::push/pull (src/parameter/shared_parameter.h:14-26,90-149).
+// SharedParameter::push/pull (src/parameter/shared_parameter.h:14-26,90-149) and
+// KVVector::getValue (src/parameter/kv_vector.h:215-227).
 // The schedule is bulk-synchronous (one legal serialisation of the reference's
 // eventual-consistency execution): pull(e) sees every update of step e-1.
 #include <cstddef>
@@ -38,8 +47,8 @@ struct ShardState {  // per-key state as the update rule sees it
   uint32_t neg;
 };
 
-// One slot of an owner's table: 32 bytes = one DRAM/NVLink sector.  Key and weight sit in
-// the same 16 bytes, so a pull probe is ONE 16-byte peer load; an update is a
+// One slot of an owner's table: 32 bytes = one DRAM sector.  Key and weight sit in
+// the same 16 bytes, so a lookup is ONE 16-byte load per probe; an update is a
 // read-modify-write of the same sector.
 struct __align__(32) ShardSlot {
   uint64_t key;      // offset 0: kEmptyKey when free
@@ -68,82 +77,87 @@ struct FtrlHyper {
   uint32_t pad2;
 };
 
+// The per-minibatch table of every rank is cut into one region of R = 2^region_log2 slots per
+// owner: a key of owner o lives in region o at the top region_log2 bits of its hash (linear
+// probing confined to an aligned chunk of kChunkSlots slots).  The shard tables index with the
+// top bits of the same hash, so chunk c of region o on EVERY worker covers the same contiguous
+// range of owner o's shard table: an owner block that takes chunk c walks all workers' requests
+// for one narrow range of its table, and the same key sent by two workers is always in the
+// same chunk (worker-by-worker order needs block-level barriers only).
+constexpr int kChunkSlots = 1024;
+constexpr uint32_t kBadSlot = 0xFFFFFFFFu;   // request slot is empty
+constexpr uint32_t kAbsent = 0xFFFFFFFEu;    // key has no entry in the shard (and none was made)
+
 struct FtrlPeers {
   KeySeps seps;
   int rank;
   int max_probe;
-  uint64_t tab_mask;                       // table capacity − 1 (same on all ranks)
-  ShardSlot* tab[PSB_MAX_RANKS];
-  uint64_t* in_keys[PSB_MAX_RANKS];        // owner o: [sender][in_cap]
-  float* in_g[PSB_MAX_RANKS];
-  uint64_t* in_cnt[PSB_MAX_RANKS];         // pos<<32 | neg
-  uint64_t* in_flag[PSB_MAX_RANKS];        // owner o: [sender] = epoch<<32 | count
-  uint64_t* applied[PSB_MAX_RANKS];        // rank r: [owner] = epoch<<32
+  uint64_t tab_mask;                       // shard capacity − 1
+  ShardSlot* tab;                          // this rank's shard (only its owner touches it)
+  uint64_t* lt_keys[PSB_MAX_RANKS];        // rank r: per-minibatch key table [world << region_log2]
+  float* lt_w[PSB_MAX_RANKS];              // rank r: pulled weight per slot (written by the owners)
+  void* lt_acc[PSB_MAX_RANKS];             // rank r: gradient accumulators, two buffers of float or float4 per slot
+  uint64_t* ready[PSB_MAX_RANKS];          // rank o: [sender] pull sequence whose table is complete
+  uint64_t* replied[PSB_MAX_RANKS];        // rank s: [owner]  pull sequence whose weights are written
+  uint64_t* grads[PSB_MAX_RANKS];          // rank o: [sender] push sequence whose accumulators are complete
+  uint32_t* in_slot;                       // owner: [sender << region_log2 | index] shard slot of the request
+  uint64_t* in_keys;                       // owner: copy of the requested keys (tail filter only, else nullptr)
   uint64_t timeout_ns;
-  uint32_t in_cap;
-  uint32_t tab_shift;                      // 64 − log2(table capacity): slot = mix64(key) >> tab_shift
-  uint32_t* in_chunk[PSB_MAX_RANKS];       // owner o: [sender][nchunks] records in every chunk segment of the inbox
-  uint32_t nchunks;                        // chunks of kChunkSlots slots in a per-minibatch table (same on all ranks)
-  uint32_t pad;
+  uint32_t tab_shift;                      // 64 − log2(shard capacity): slot = mix64(key) >> tab_shift
+  uint32_t region_log2;
 };
 
-// The per-minibatch table is cut into aligned chunks of kChunkSlots slots; probing never leaves a
-// chunk.  All ranks hash with the same function into tables of the same size, so chunk c holds the
-// same range of hash values on every rank, and hence of every owner's shard table.  The records
-// that sender s routes to owner o from its chunk c go to a FIXED segment of o's inbox:
-//   [s · in_cap + c · kChunkSlots, … + in_chunk[o][s · nchunks + c])
-// (in_cap = table capacity, so the segments tile the inbox exactly).  No cursor atomics on the
-// sending side, and on the owner one thread block can apply chunk c of sender 0, 1, … in order
-// with block-level barriers only: no other block ever touches the keys of that hash range.
-constexpr int kChunkSlots = 1024;
-
 struct Minibatch {
-  const int64_t* offsets;  // rows+1
-  const uint64_t* keys;    // nnz global keys
+  const void* offsets;     // rows+1, int64 (or int32 when off32)
+  const void* keys;        // nnz keys: uint64, or uint32 feature ids (key_mode 1, 2)
   const float* vals;       // nnz values or nullptr (binary features)
   const float* y;          // rows, ±1
   int64_t nnz;
   int rows;
-  int pad;
+  uint16_t off32;          // offsets are int32
+  uint16_t key_mode;       // 0: uint64 keys; 1: uint32 ids, key = id; 2: uint32 ids, key = mix64(id)
 };
 
-struct __align__(16) LocalSlot {  // 16 B payload of one local dedup-table slot
-  float w;    // pulled weight
-  float g;    // gradient accumulator
+__device__ __forceinline__ int64_t mb_offset(const Minibatch& M, int64_t r) {
+  return M.off32 ? (int64_t) reinterpret_cast<const int32_t*>(M.offsets)[r] : reinterpret_cast<const int64_t*>(M.offsets)[r];
+}
+
+struct __align__(16) AccSlot {  // accumulator of one per-minibatch slot when row counts are tracked
+  float g;    // gradient
   float pos;  // #positive rows containing the key (exact in fp32: a minibatch has < 2^24 rows)
   float neg;  // #negative rows containing the key
+  float pad;
 };
 
 // One 16-byte vector reduction per non-zero instead of separate atomics on g and counts.
-__device__ __forceinline__ void red_add_slot(LocalSlot* p, float g, float pos, float neg) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(0.f), "f"(g), "f"(pos), "f"(neg) : "memory");
+__device__ __forceinline__ void red_add_acc(AccSlot* p, float g, float pos, float neg) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(g), "f"(pos), "f"(neg), "f"(0.f) : "memory");
 }
 
 struct LocalScratch {
-  uint64_t* lt_keys;   // per-minibatch dedup table (all kEmptyKey between steps)
-  LocalSlot* lt_val;   // payload per slot (one 16-byte sector: w, g, counts)
-  uint64_t lt_mask;
-  uint64_t lt_shift;   // 64 − log2(local capacity): slot = mix64(key) >> lt_shift
+  uint64_t* lt_keys;   // this rank's per-minibatch table (all kEmptyKey between steps)
+  float* lt_w;         // pulled weight per slot
+  void* lt_acc;        // accumulators: [2][slots] float (soa) or AccSlot
+  uint64_t lt_slots;   // world << region_log2
   uint32_t* slot_of;   // nnz: local slot of each non-zero
   float* coef;         // rows: −y/(1+e^{y·Xw})
   float* xw;           // rows: X·w (predictions)
-  uint32_t* send_cnt;  // [PSB_MAX_RANKS] scratch of the unfused baseline (the fused push uses fixed chunk segments)
-  uint32_t* recv_cnt;  // [PSB_MAX_RANKS] 1 = sender s's records of this step arrived, 0 = its flag wait ran out
+  uint32_t* send_cnt;  // [PSB_MAX_RANKS] scratch of the unfused baseline
+  uint32_t* recv_cnt;  // [PSB_MAX_RANKS] scratch of the unfused baseline
   double* stats;       // [0] Σloss [1] rows [2] ‖w‖₁ [3] ‖w‖₂² [4] nnz(w) [5] unique keys [6] table entries
   uint32_t* status;    // StatusCode etc.
   uint64_t* trace;     // optional [16]: globaltimer at phase boundaries of the last step (see kTrace*)
-  // Split layout for update rules that need no pos/neg counts (soa != 0): the pulled weight and
-  // the gradient accumulator live in two 4-byte arrays, a quarter of the footprint of lt_val, so
-  // the random accesses of the SpMV and of the gradient scatter stay inside L2.  The gather
-  // phase writes lt_w and resets lt_g for every key of the minibatch.
-  float* lt_w;
-  float* lt_g;
+  // soa != 0: no pos/neg row counts are tracked, an accumulator is one float (the random
+  // accesses of the gradient scatter then stay inside L2: a quarter of the footprint).
   uint32_t soa;
-  uint32_t pad;
+  uint32_t parity;     // which of the two accumulator buffers this step uses
 };
 
-// Streams (keys, slot map, inbox records) are read or written once per phase; with
-// PSB_L2_HINTS they carry an evict-first L2 policy so that the hash tables stay resident.
+template <bool kCounts>
+__device__ __forceinline__ size_t acc_bytes() { return kCounts ? sizeof(AccSlot) : sizeof(float); }
+
+// Streams (keys, slot map) are read or written once per phase; with PSB_L2_HINTS they carry an
+// evict-first L2 policy so that the hash tables stay resident.
 #ifndef PSB_L2_HINTS
 #define PSB_L2_HINTS 1
 #endif
@@ -161,16 +175,25 @@ struct LocalScratch {
 #define PSB_ST_U32(p, v, pol) (*(p) = (v))
 #endif
 
-// trace slots: pull kernel 0 start, 1 localized, 2 gathered, 3 block-0 end;
-//              push kernel 4 start, 5 gradients done, 6 records sent, 7 all senders arrived, 8 applied
+// trace slots: pull kernel 0 start, 1 localized, 2 all owners replied, 3 block-0 end;
+//              push kernel 4 start, 5 gradients done, 6 flags sent and tables cleared, 8 applied
 #define PSB_TRACE(L, gtid, i) do { if ((L).trace != nullptr && (gtid) == 0) (L).trace[i] = globaltimer_ns(); } while (0)
 
-constexpr uint32_t kBadSlot = 0xFFFFFFFFu;
-
-// Both tables index with the TOP bits of the same 64-bit hash.  A scan of the local table in
-// slot order therefore visits keys in (nearly) increasing shard-slot order, so the gather and
-// the owner-side update walk the big shard table monotonically instead of at random.
+// Both tables index with the TOP bits of the same 64-bit hash (see FtrlPeers).
 __device__ __forceinline__ uint64_t shard_hash(uint64_t key, uint32_t shift) { return mix64(key) >> shift; }
+
+__device__ __forceinline__ uint64_t mb_key(const Minibatch& M, int64_t i, uint64_t pol) {
+  if (M.key_mode == 0) return PSB_LD_U64(reinterpret_cast<const uint64_t*>(M.keys) + i, pol);
+  const uint64_t id = PSB_LD_U32(reinterpret_cast<const uint32_t*>(M.keys) + i, pol);
+  return M.key_mode == 2 ? mix64(id) : id;
+}
+
+// slot of `key` in a per-minibatch table: region of its owner, top bits of its hash inside
+__device__ __forceinline__ uint64_t local_home(const FtrlPeers& P, uint64_t key) {
+  const uint64_t o = (uint64_t)route_owner(P.seps, key);
+  const uint64_t h = P.region_log2 ? (mix64(key) >> (64 - P.region_log2)) : 0ull;
+  return (o << P.region_log2) | h;
+}
 
 // ------------------------------------------------------------------ phases
 // De-duplication of the minibatch's keys is bound by memory latency, not by bandwidth: every key
@@ -183,82 +206,151 @@ __device__ __forceinline__ uint64_t ld_table_u64(const uint64_t* p) {
   uint64_t v; asm volatile("ld.global.u64 %0, [%1];" : "=l"(v) : "l"(p)); return v;
 }
 
-__device__ __forceinline__ void phase_localize(const Minibatch& M, const LocalScratch& L, int max_probe,
+__device__ __forceinline__ void phase_localize(const FtrlPeers& P, const Minibatch& M, const LocalScratch& L,
                                                size_t gtid, size_t gsz) {
   PSB_STREAM_POLICY(pol);
   const int64_t step = (int64_t)gsz;
-  const uint64_t cmask = L.lt_mask < (uint64_t)(kChunkSlots - 1) ? L.lt_mask : (uint64_t)(kChunkSlots - 1);
+  const uint64_t region = 1ull << P.region_log2;
+  const uint64_t cmask = (region < (uint64_t)kChunkSlots ? region : (uint64_t)kChunkSlots) - 1;
+  uint32_t fresh = 0;
   int64_t i = (int64_t)gtid;
-  if (i >= M.nnz) return;
-  uint64_t key0 = PSB_LD_U64(M.keys + i, pol);
-  uint64_t key1 = i + step < M.nnz ? PSB_LD_U64(M.keys + i + step, pol) : kEmptyKey;
-  uint64_t h0 = (mix64(key0) >> L.lt_shift) & L.lt_mask;
-  uint64_t cur0 = ld_table_u64(L.lt_keys + h0);
-  for (; i < M.nnz; i += step) {
-    uint64_t key2 = kEmptyKey, h1 = 0, cur1 = 0;
-    if (i + 2 * step < M.nnz) key2 = PSB_LD_U64(M.keys + i + 2 * step, pol);
-    if (i + step < M.nnz) {
-      h1 = (mix64(key1) >> L.lt_shift) & L.lt_mask;
-      cur1 = ld_table_u64(L.lt_keys + h1);
-    }
-    uint32_t slot = (uint32_t)h0;
-    if (cur0 != key0) {
-      const uint64_t s = table_find_or_insert(L.lt_keys, L.lt_mask, cmask, h0, key0, max_probe);
-      if (s == ~0ull) {
-        set_status(L.status, kLocalTableFull, 0, 0);
-        slot = kBadSlot;
-      } else {
-        slot = (uint32_t)s;
+  if (i < M.nnz) {
+    uint64_t key0 = mb_key(M, i, pol);
+    uint64_t key1 = i + step < M.nnz ? mb_key(M, i + step, pol) : kEmptyKey;
+    uint64_t h0 = local_home(P, key0);
+    uint64_t cur0 = ld_table_u64(L.lt_keys + h0);
+    for (; i < M.nnz; i += step) {
+      uint64_t key2 = kEmptyKey, h1 = 0, cur1 = 0;
+      if (i + 2 * step < M.nnz) key2 = mb_key(M, i + 2 * step, pol);
+      if (i + step < M.nnz) {
+        h1 = local_home(P, key1);
+        cur1 = ld_table_u64(L.lt_keys + h1);
       }
+      uint32_t slot = (uint32_t)h0;
+      if (cur0 != key0) {
+        bool inserted = false;
+        const uint64_t s = table_find_or_insert(L.lt_keys, ~0ull, cmask, h0, key0, P.max_probe, &inserted);
+        if (s == ~0ull) {
+          set_status(L.status, kLocalTableFull, 0, 0);
+          slot = kBadSlot;
+        } else {
+          slot = (uint32_t)s;
+          fresh += inserted ? 1u : 0u;
+        }
+      }
+      PSB_ST_U32(L.slot_of + i, slot, pol);
+      key0 = key1; h0 = h1; cur0 = cur1; key1 = key2;
     }
-    PSB_ST_U32(L.slot_of + i, slot, pol);
-    key0 = key1; h0 = h1; cur0 = cur1; key1 = key2;
   }
+  fresh = __reduce_add_sync(0xffffffffu, fresh);
+  if ((threadIdx.x & 31) == 0 && fresh) atomicAdd(&L.stats[5], (double)fresh);
 }
 
-// weight of `key` in owner's table (peer memory), 0 when absent; one 16-byte load per probe
-// (`peer` = the table is another GPU's: system scope; this GPU's own shard is read at GPU scope)
-__device__ __forceinline__ float probe_weight(const ShardSlot* tab, uint64_t mask, uint32_t shift, uint64_t key,
-                                              int max_probe, bool peer = true) {
+// ---- shard table probes (owner side, this GPU's own memory)
+// weight of `key` and its slot; kAbsent when the key has no entry
+__device__ __forceinline__ uint32_t shard_find(const ShardSlot* tab, uint64_t mask, uint32_t shift, uint64_t key,
+                                               int max_probe, float* w) {
   uint64_t slot = shard_hash(key, shift) & mask;
   for (int i = 0; i < max_probe; ++i) {
     uint64_t k, wz;
-    if (peer)
-      asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(k), "=l"(wz) : "l"(tab + slot) : "memory");
-    else
-      asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(k), "=l"(wz) : "l"(tab + slot) : "memory");
-    if (k == key) return __uint_as_float((uint32_t)wz);
-    if (k == kEmptyKey) return 0.f;
+    asm volatile("ld.global.v2.u64 {%0, %1}, [%2];" : "=l"(k), "=l"(wz) : "l"(tab + slot) : "memory");
+    if (k == key) { *w = __uint_as_float((uint32_t)wz); return (uint32_t)slot; }
+    if (k == kEmptyKey) break;
     slot = (slot + 1) & mask;
   }
-  return 0.f;
+  *w = 0.f;
+  return kAbsent;
 }
 
-template <bool kCounts>
-__device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScratch& L, size_t gtid,
-                                             size_t gsz) {
-  uint32_t uniq = 0;
-  for (uint64_t s = gtid; s <= L.lt_mask; s += gsz) {
-    const uint64_t key = __ldcg(L.lt_keys + s);
-    if (key != kEmptyKey) {
-      const int o = route_owner(P.seps, key);
-      const float w = probe_weight(P.tab[o], P.tab_mask, P.tab_shift, key, P.max_probe, o != P.rank);
-      if (kCounts) {
-        LocalSlot v;
-        v.w = w;
-        v.g = 0.f;
-        v.pos = 0.f;
-        v.neg = 0.f;
-        *reinterpret_cast<float4*>(L.lt_val + s) = *reinterpret_cast<float4*>(&v);
-      } else {
-        L.lt_w[s] = w;
-        L.lt_g[s] = 0.f;  // here, not after the read in the routing phase: a store there costs 70 us
+// slot of `key`, created when missing (w = z = n = 0: the same model as "absent"); kAbsent when the
+// probe limit is reached
+__device__ __forceinline__ uint32_t shard_find_or_insert(ShardSlot* tab, uint64_t mask, uint32_t shift, uint64_t key,
+                                                         int max_probe, float* w, int* inserted) {
+  uint64_t slot = shard_hash(key, shift) & mask;
+  for (int i = 0; i < max_probe; ++i) {
+    uint64_t k, wz;
+    asm volatile("ld.global.v2.u64 {%0, %1}, [%2];" : "=l"(k), "=l"(wz) : "l"(tab + slot) : "memory");
+    if (k == key) { *w = __uint_as_float((uint32_t)wz); return (uint32_t)slot; }
+    if (k == kEmptyKey) {
+      const unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long*>(&tab[slot].key),
+                                                (unsigned long long)kEmptyKey, (unsigned long long)key);
+      if (prev == kEmptyKey) { *w = 0.f; ++*inserted; return (uint32_t)slot; }
+      if (prev == key) { *w = tab[slot].w; return (uint32_t)slot; }
+    }
+    slot = (slot + 1) & mask;
+  }
+  *w = 0.f;
+  return kAbsent;
+}
+
+// One thread of a block waits (bounded) until flag's epoch reaches `want`; the block learns the outcome.
+__device__ __forceinline__ bool block_wait_flag(const uint64_t* flag, uint32_t want, uint64_t timeout_ns, int* sh_ok) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    bool ok;
+    wait_epoch_ge(flag, want, timeout_ns, &ok);
+    *sh_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  return *sh_ok != 0;
+}
+
+constexpr int kLookupItems = kChunkSlots / 256;   // slots per thread and chunk (blocks of 256 threads)
+
+// Owner side of the pull.  A task is (sender s, chunk c of this owner's region in s's table).
+// Tasks are numbered sender-major starting with this rank itself, so the blocks that serve
+// different senders wait for different flags and a slow sender holds up only its own blocks.
+// `insert`: create missing keys (training); off for predictions and under the tail filter.
+__device__ __forceinline__ void phase_lookup(const FtrlPeers& P, const LocalScratch& L, uint32_t seq, bool insert,
+                                             int* sh_ok) {
+  const int world = P.seps.world;
+  const uint64_t region = 1ull << P.region_log2;
+  const uint32_t chunk = region < (uint64_t)kChunkSlots ? (uint32_t)region : (uint32_t)kChunkSlots;
+  const uint32_t chunks = (uint32_t)(region / chunk);
+  const uint32_t tasks = chunks * (uint32_t)world;
+  int dins = 0;
+  int have = -1;   // sender whose flag this block has seen
+  bool have_ok = false;
+  for (uint32_t t = blockIdx.x; t < tasks; t += gridDim.x) {
+    const int s = (P.rank + (int)(t / chunks)) % world;
+    const uint32_t c = t % chunks;
+    if (s != have) {
+      have_ok = s == P.rank ? true : block_wait_flag(P.ready[P.rank] + s, seq, P.timeout_ns, sh_ok);
+      have = s;
+      if (!have_ok && threadIdx.x == 0) set_status(L.status, kWaitTimeout, (uint32_t)s, 1);
+    }
+    const size_t in0 = ((size_t)s << P.region_log2) + (size_t)c * chunk;          // owner-side index
+    const size_t lt0 = ((size_t)P.rank << P.region_log2) + (size_t)c * chunk;     // index in the sender's table
+    const bool peer = s != P.rank;
+    const uint64_t* rk = P.lt_keys[s] + lt0;
+    float* rw = P.lt_w[s] + lt0;
+    uint64_t key[kLookupItems];
+#pragma unroll
+    for (int k = 0; k < kLookupItems; ++k) {
+      const uint32_t i = (uint32_t)k * 256u + threadIdx.x;
+      key[k] = kEmptyKey;
+      if (i < chunk && have_ok) key[k] = peer ? ld_relaxed_sys_u64(rk + i) : __ldcg(rk + i);
+    }
+#pragma unroll
+    for (int k = 0; k < kLookupItems; ++k) {
+      const uint32_t i = (uint32_t)k * 256u + threadIdx.x;
+      if (i >= chunk) continue;
+      uint32_t slot = kBadSlot;
+      float w = 0.f;
+      if (key[k] != kEmptyKey) {
+        slot = insert ? shard_find_or_insert(P.tab, P.tab_mask, P.tab_shift, key[k], P.max_probe, &w, &dins)
+                      : shard_find(P.tab, P.tab_mask, P.tab_shift, key[k], P.max_probe, &w);
+        if (insert && slot == kAbsent) set_status(L.status, kShardTableFull, 0, 0);
       }
-      ++uniq;
+      P.in_slot[in0 + i] = slot;
+      if (P.in_keys != nullptr) P.in_keys[in0 + i] = key[k];
+      if (have_ok) {
+        if (peer) st_relaxed_sys_f32(rw + i, w); else rw[i] = w;
+      }
     }
   }
-  uniq = __reduce_add_sync(0xffffffffu, uniq);
-  if ((threadIdx.x & 31) == 0 && uniq) atomicAdd(&L.stats[5], (double)uniq);
+  dins = __reduce_add_sync(0xffffffffu, dins);
+  if ((threadIdx.x & 31) == 0 && dins) atomicAdd(&L.stats[6], (double)dins);
 }
 
 // Rows are walked a warp at a time; a lane first issues the loads of up to kRowBatch of its
@@ -268,13 +360,12 @@ __device__ __forceinline__ void phase_gather(const FtrlPeers& P, const LocalScra
 #endif
 constexpr int kRowBatch = PSB_ROW_BATCH;
 
-template <bool kCounts>
 __device__ __forceinline__ void phase_spmv_loss(const Minibatch& M, const LocalScratch& L, size_t gwarp,
                                                 size_t nwarps, int lane) {
   double loss = 0.0;
   PSB_STREAM_POLICY(pol);
   for (int64_t row = (int64_t)gwarp; row < M.rows; row += (int64_t)nwarps) {
-    const int64_t b = M.offsets[row], e = M.offsets[row + 1];
+    const int64_t b = mb_offset(M, row), e = mb_offset(M, row + 1);
     float s = 0.f;
     for (int64_t i0 = b + lane; i0 < e; i0 += 32 * kRowBatch) {
       uint32_t sl[kRowBatch];
@@ -287,7 +378,7 @@ __device__ __forceinline__ void phase_spmv_loss(const Minibatch& M, const LocalS
       }
 #pragma unroll
       for (int k = 0; k < kRowBatch; ++k) {
-        if (sl[k] != kBadSlot) s += x[k] * (kCounts ? L.lt_val[sl[k]].w : L.lt_w[sl[k]]);
+        if (sl[k] != kBadSlot) s += x[k] * __ldcg(L.lt_w + sl[k]);   // written by other GPUs: not through L1
       }
     }
     s = warp_sum(s);
@@ -320,6 +411,8 @@ struct HotCache {
 template <bool kCounts>
 __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratch& L, size_t gwarp,
                                            size_t nwarps, int lane, HotCache* hc) {
+  float* accf = reinterpret_cast<float*>(L.lt_acc) + (size_t)L.parity * L.lt_slots;
+  AccSlot* accv = reinterpret_cast<AccSlot*>(L.lt_acc) + (size_t)L.parity * L.lt_slots;
   for (int i = threadIdx.x; i < kHotEntries; i += blockDim.x) {
     hc->slot[i] = kBadSlot;
     hc->g[i] = 0.f;
@@ -328,7 +421,7 @@ __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratc
   __syncthreads();
   PSB_STREAM_POLICY(pol);
   for (int64_t row = (int64_t)gwarp; row < M.rows; row += (int64_t)nwarps) {
-    const int64_t b = M.offsets[row], e = M.offsets[row + 1];
+    const int64_t b = mb_offset(M, row), e = mb_offset(M, row + 1);
     const float c = L.coef[row];
     const bool is_pos = M.y[row] > 0.f;
     const unsigned long long inc = is_pos ? (1ull << 32) : 1ull;
@@ -356,9 +449,9 @@ __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratc
           atomicAdd(&hc->g[h], gv);
           if (kCounts) atomicAdd(&hc->cnt[h], inc);
         } else if (kCounts) {
-          red_add_slot(L.lt_val + sl, gv, is_pos ? 1.f : 0.f, is_pos ? 0.f : 1.f);
+          red_add_acc(accv + sl, gv, is_pos ? 1.f : 0.f, is_pos ? 0.f : 1.f);
         } else {
-          atomicAdd(L.lt_g + sl, gv);
+          atomicAdd(accf + sl, gv);
         }
       }
     }
@@ -369,110 +462,30 @@ __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratc
     if (sl != kBadSlot) {
       if (kCounts) {
         const unsigned long long c = hc->cnt[i];
-        red_add_slot(L.lt_val + sl, hc->g[i], (float)(uint32_t)(c >> 32), (float)(uint32_t)c);
+        red_add_acc(accv + sl, hc->g[i], (float)(uint32_t)(c >> 32), (float)(uint32_t)c);
       } else {
-        atomicAdd(L.lt_g + sl, hc->g[i]);
+        atomicAdd(accf + sl, hc->g[i]);
       }
     }
   }
 }
 
-// Scan the local table, write every unique key's record into its owner's inbox and empty the
-// table for the next minibatch.  A block handles one chunk of kSendChunk slots per iteration.
-// The records of a chunk are first grouped by owner in shared memory, then written out so that
-// consecutive threads write consecutive inbox entries of one owner: the stores that cross NVLink
-// are full, coalesced lines instead of scattered 8-byte pieces.  Chunk c always writes to the
-// c-th segment of the sender's part of the inbox and leaves the number of records beside it.
-constexpr int kSendItems = 4;
-constexpr int kSendChunk = 256 * kSendItems;
-static_assert(kSendChunk == kChunkSlots, "a block of 256 threads routes exactly one chunk per iteration");
-struct SendStage {
-  uint64_t key[kSendChunk];
-  uint64_t cnt[kSendChunk];
-  float g[kSendChunk];
-  uint32_t count[PSB_MAX_RANKS];      // records per owner in this chunk
-  uint32_t off[PSB_MAX_RANKS + 1];    // start of every owner's run in the staging arrays
-  uint32_t base[PSB_MAX_RANKS];       // first inbox index granted to this chunk, per owner
-};
-
+// Between the gradient phase and the owners' update a worker empties its key table for the next
+// minibatch (every owner has finished reading it: the worker saw all `replied` flags before its
+// SpMV) and zeroes the accumulator buffer of the NEXT step (the owners read that one during the
+// previous step's update, which they finished before they replied to this step's pull).
 template <bool kCounts>
-__device__ __forceinline__ void phase_route_send(const FtrlPeers& P, const LocalScratch& L, SendStage* st) {
-  const uint64_t n = L.lt_mask + 1;
-  const uint64_t chunk = (uint64_t)blockDim.x * kSendItems;
-  const int lane = threadIdx.x & 31;
-  const int world = P.seps.world;
-  for (uint64_t c0 = (uint64_t)blockIdx.x * chunk; c0 < n; c0 += (uint64_t)gridDim.x * chunk) {
-    if (threadIdx.x < PSB_MAX_RANKS) st->count[threadIdx.x] = 0;
-    __syncthreads();
-    uint64_t key[kSendItems];
-    uint32_t pos[kSendItems];
-    int own[kSendItems];
-#pragma unroll
-    for (int k = 0; k < kSendItems; ++k) {
-      const uint64_t s = c0 + (uint64_t)k * blockDim.x + threadIdx.x;
-      key[k] = s < n ? __ldcg(L.lt_keys + s) : kEmptyKey;
-      own[k] = key[k] != kEmptyKey ? route_owner(P.seps, key[k]) : -1;
-      pos[k] = 0;
-    }
-#pragma unroll
-    for (int k = 0; k < kSendItems; ++k) {
-      for (int t = 0; t < world; ++t) {
-        const unsigned m = __ballot_sync(0xffffffffu, own[k] == t);
-        if (m == 0u) continue;
-        const int leader = __ffs(m) - 1;
-        uint32_t base = 0;
-        if (lane == leader) base = atomicAdd(&st->count[t], (uint32_t)__popc(m));
-        base = __shfl_sync(0xffffffffu, base, leader);
-        if (own[k] == t) pos[k] = base + __popc(m & ((1u << lane) - 1u));
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      uint32_t run = 0;
-      for (int t = 0; t < world; ++t) { st->off[t] = run; run += st->count[t]; }
-      st->off[world] = run;
-    }
-    // fixed segment of this chunk in every owner's inbox; its fill level goes next to it
-    if (threadIdx.x < world) {
-      st->base[threadIdx.x] = (uint32_t)c0;
-      P.in_chunk[threadIdx.x][(size_t)P.rank * P.nchunks + (size_t)(c0 / chunk)] = st->count[threadIdx.x];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < kSendItems; ++k) {
-      if (own[k] < 0) continue;
-      const uint64_t s = c0 + (uint64_t)k * blockDim.x + threadIdx.x;
-      const uint32_t at = st->off[own[k]] + pos[k];
-      st->key[at] = key[k];
-      L.lt_keys[s] = kEmptyKey;
-      if (kCounts) {
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(L.lt_val + s));
-        st->g[at] = v.y;
-        st->cnt[at] = ((uint64_t)(uint32_t)v.z << 32) | (uint64_t)(uint32_t)v.w;
-      } else {
-        st->g[at] = __ldcg(L.lt_g + s);
-      }
-    }
-    __syncthreads();
-    const uint32_t total = st->off[world];
-    for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
-      int t = 0;
-      while (t + 1 < world && i >= st->off[t + 1]) ++t;
-      const uint32_t idx = st->base[t] + (i - st->off[t]);
-      if (idx < P.in_cap) {
-        const size_t at = (size_t)P.rank * P.in_cap + idx;
-        P.in_keys[t][at] = st->key[i];
-        P.in_g[t][at] = st->g[i];
-        if (kCounts) P.in_cnt[t][at] = st->cnt[i];
-      } else {
-        set_status(L.status, kInboxOverflow, (uint32_t)t, idx);
-      }
-    }
-    __syncthreads();
-  }
-  // the records must be visible to their owners before the flag is: system scope only when other GPUs
-  // exist (a fence by one thread per block after the barrier measured the same: 48.4 vs 49.2 us at N=2)
-  if (world > 1) __threadfence_system(); else __threadfence();
+__device__ __forceinline__ void phase_reset_tables(const LocalScratch& L, size_t gtid, size_t gsz) {
+  uint4* k = reinterpret_cast<uint4*>(L.lt_keys);
+  const uint4 empty = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+  for (size_t i = gtid; i < L.lt_slots / 2; i += gsz) k[i] = empty;
+  if (L.lt_slots & 1) { if (gtid == 0) L.lt_keys[L.lt_slots - 1] = kEmptyKey; }
+  const size_t bytes = L.lt_slots * acc_bytes<kCounts>();
+  char* next = reinterpret_cast<char*>(L.lt_acc) + (size_t)(L.parity ^ 1u) * bytes;
+  uint4* a = reinterpret_cast<uint4*>(next);
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  for (size_t i = gtid; i < bytes / 16; i += gsz) a[i] = zero;
+  for (size_t i = (bytes / 16) * 16 + gtid; i < bytes; i += gsz) next[i] = 0;
 }
 
 __device__ __forceinline__ float ftrl_sqrt_n(float pos, float neg) {
@@ -511,17 +524,6 @@ __device__ __forceinline__ void ftrl_update(ShardState& e, float g, uint32_t dpo
 
 __device__ __forceinline__ bool tail_filter_on(const FtrlHyper& h) { return h.tail_freq != 0u && h.cm != nullptr; }
 
-// first half of the tail-feature filter: add one sender's row counts to the owner's sketch
-__device__ __forceinline__ void phase_sketch_insert(const uint64_t* rk, const uint64_t* rc, uint32_t n,
-                                                    const FtrlHyper& h, size_t gtid, size_t gsz) {
-  for (size_t i = gtid; i < n; i += gsz) {
-    const uint64_t key = __ldcg(rk + i);
-    if (key == kEmptyKey) continue;
-    const uint64_t c = __ldcg(rc + i);
-    cm_insert(h.cm, h.cm_width, h.cm_k, key, (uint32_t)(c >> 32) + (uint32_t)c);
-  }
-}
-
 struct ApplyAcc {  // per-thread deltas of the model statistics, flushed once per kernel
   float dn1 = 0.f, dn2 = 0.f;
   int dnnz = 0, dins = 0;
@@ -539,58 +541,117 @@ __device__ __forceinline__ void apply_flush(ApplyAcc& a, double* stats) {
   a = ApplyAcc();
 }
 
-// apply records [0, n) of one sender; thread `tid` of `nthr` takes records tid, tid + nthr, …
-template <bool kCounts>
-__device__ __forceinline__ void apply_records(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
-                                              const uint64_t* rk, const float* rg, const uint64_t* rc,
-                                              uint32_t n, const FtrlHyper& h, ApplyAcc& acc, uint32_t* status,
-                                              size_t gtid, size_t gsz) {
-  float dn1 = 0.f, dn2 = 0.f;
-  int dnnz = 0, dins = 0;
-  const bool filter = kCounts && tail_filter_on(h);
-  for (size_t i = gtid; i < n; i += gsz) {
-    const uint64_t key = __ldcg(rk + i);
-    if (key == kEmptyKey) continue;
-    if (filter && cm_query(h.cm, h.cm_width, h.cm_k, key, 0xFFFFFFFFu) <= h.tail_freq) continue;
-    const float g = __ldcg(rg + i);
-    const uint64_t c = kCounts ? __ldcg(rc + i) : 0ull;
-    uint64_t slot = shard_hash(key, shift) & mask;
-    bool found = false;
-    for (int p = 0; p < max_probe; ++p) {
-      const uint64_t cur = tab[slot].key;
-      if (cur == key) { found = true; break; }
-      if (cur == kEmptyKey) {
-        const unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long*>(&tab[slot].key),
-                                                  (unsigned long long)kEmptyKey, (unsigned long long)key);
-        if (prev == kEmptyKey) { found = true; ++dins; break; }
-        if (prev == key) { found = true; break; }
-      }
-      slot = (slot + 1) & mask;
-    }
-    if (!found) {
-      set_status(status, kShardTableFull, 0, 0);
-      continue;
-    }
-    const float2 wz = *reinterpret_cast<const float2*>(&tab[slot].w);
-    const uint2 pn = *reinterpret_cast<const uint2*>(&tab[slot].pos);
-    ShardState e;
-    e.w = wz.x; e.z = wz.y; e.pos = pn.x; e.neg = pn.y;
-    ftrl_update(e, g, (uint32_t)(c >> 32), (uint32_t)c, h, dn1, dn2, dnnz);
-    *reinterpret_cast<float2*>(&tab[slot].w) = make_float2(e.w, e.z);
-    *reinterpret_cast<uint2*>(&tab[slot].pos) = make_uint2(e.pos, e.neg);
-  }
-  acc.dn1 += dn1; acc.dn2 += dn2; acc.dnnz += dnnz; acc.dins += dins;
+__device__ __forceinline__ void apply_slot(ShardSlot* tab, uint32_t slot, float g, uint32_t dpos, uint32_t dneg,
+                                           const FtrlHyper& h, ApplyAcc& acc) {
+  const float2 wz = *reinterpret_cast<const float2*>(&tab[slot].w);
+  const uint2 pn = *reinterpret_cast<const uint2*>(&tab[slot].pos);
+  ShardState e;
+  e.w = wz.x; e.z = wz.y; e.pos = pn.x; e.neg = pn.y;
+  ftrl_update(e, g, dpos, dneg, h, acc.dn1, acc.dn2, acc.dnnz);
+  *reinterpret_cast<float2*>(&tab[slot].w) = make_float2(e.w, e.z);
+  *reinterpret_cast<uint2*>(&tab[slot].pos) = make_uint2(e.pos, e.neg);
 }
 
-// stand-alone form: one flat record list (unfused baseline)
+// gradient (and row counts) of request `i` of a chunk, from the sender's accumulators
 template <bool kCounts>
-__device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
-                                            const uint64_t* rk, const float* rg, const uint64_t* rc,
-                                            uint32_t n, const FtrlHyper& h, double* stats, uint32_t* status,
-                                            size_t gtid, size_t gsz) {
-  ApplyAcc acc;
-  apply_records<kCounts>(tab, mask, shift, max_probe, rk, rg, rc, n, h, acc, status, gtid, gsz);
-  apply_flush(acc, stats);
+__device__ __forceinline__ void load_acc(const void* base, size_t i, bool peer, float* g, uint32_t* dpos, uint32_t* dneg) {
+  if (kCounts) {
+    const AccSlot* p = reinterpret_cast<const AccSlot*>(base) + i;
+    float4 v;
+    if (peer)
+      asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    else
+      v = __ldcg(reinterpret_cast<const float4*>(p));
+    *g = v.x; *dpos = (uint32_t)v.y; *dneg = (uint32_t)v.z;
+  } else {
+    const float* p = reinterpret_cast<const float*>(base) + i;
+    *g = peer ? ld_relaxed_sys_f32(p) : __ldcg(p);
+    *dpos = 0u; *dneg = 0u;
+  }
+}
+
+// Owner side of the push: chunk c of every sender, sender by sender in rank order (the reference
+// applies each worker's push separately; the order only matters per key, and a key is in the
+// same chunk on every sender).  The shard slots were resolved by the pull of the same step.
+template <bool kCounts>
+__device__ __forceinline__ void phase_apply_chunks(const FtrlPeers& P, const LocalScratch& L, const FtrlHyper& H,
+                                                   uint32_t seq, ApplyAcc& acc, int* sh_ok) {
+  const int world = P.seps.world;
+  const uint64_t region = 1ull << P.region_log2;
+  const uint32_t chunk = region < (uint64_t)kChunkSlots ? (uint32_t)region : (uint32_t)kChunkSlots;
+  const uint32_t chunks = (uint32_t)(region / chunk);
+  const size_t abytes = L.lt_slots * acc_bytes<kCounts>();
+  uint32_t arrived = 0, failed = 0;   // bit s: this block has seen sender s's flag / its wait ran out
+  for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+    for (int s = 0; s < world; ++s) {
+      if (!((arrived | failed) >> s & 1u)) {
+        const bool ok = s == P.rank ? true : block_wait_flag(P.grads[P.rank] + s, seq, P.timeout_ns, sh_ok);
+        if (ok) arrived |= 1u << s; else failed |= 1u << s;
+        if (!ok && threadIdx.x == 0) set_status(L.status, kWaitTimeout, (uint32_t)s, 2);
+      }
+      if (failed >> s & 1u) continue;   // a sender that never arrived is skipped
+      const size_t in0 = ((size_t)s << P.region_log2) + (size_t)c * chunk;
+      const size_t lt0 = ((size_t)P.rank << P.region_log2) + (size_t)c * chunk;
+      const bool peer = s != P.rank;
+      const char* abase = reinterpret_cast<const char*>(P.lt_acc[s]) + (size_t)L.parity * abytes;
+      uint32_t slot[kLookupItems];
+#pragma unroll
+      for (int k = 0; k < kLookupItems; ++k) {
+        const uint32_t i = (uint32_t)k * 256u + threadIdx.x;
+        slot[k] = i < chunk ? __ldcg(P.in_slot + in0 + i) : kBadSlot;
+      }
+#pragma unroll
+      for (int k = 0; k < kLookupItems; ++k) {
+        const uint32_t i = (uint32_t)k * 256u + threadIdx.x;
+        if (slot[k] >= kAbsent) continue;
+        float g; uint32_t dpos, dneg;
+        load_acc<kCounts>(abase, lt0 + i, peer, &g, &dpos, &dneg);
+        apply_slot(P.tab, slot[k], g, dpos, dneg, H, acc);
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// Tail-filter form of the owner's update: a sender's counts must all be in the sketch before any
+// of its keys is queried, so every sender is bracketed by grid-wide barriers; keys that pass the
+// filter and have no entry yet get one here (the pull did not create them).
+__device__ __forceinline__ void phase_apply_filtered(cg::grid_group& grid, const FtrlPeers& P, const LocalScratch& L,
+                                                     const FtrlHyper& H, uint32_t seq, ApplyAcc& acc, int* sh_ok) {
+  const int world = P.seps.world;
+  const uint64_t region = 1ull << P.region_log2;
+  const size_t abytes = L.lt_slots * sizeof(AccSlot);
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, gsz = (size_t)gridDim.x * blockDim.x;
+  for (int s = 0; s < world; ++s) {
+    const bool ok = s == P.rank ? true : block_wait_flag(P.grads[P.rank] + s, seq, P.timeout_ns, sh_ok);
+    if (!ok && threadIdx.x == 0) set_status(L.status, kWaitTimeout, (uint32_t)s, 2);
+    const size_t in0 = (size_t)s << P.region_log2, lt0 = (size_t)P.rank << P.region_log2;
+    const bool peer = s != P.rank;
+    const char* abase = reinterpret_cast<const char*>(P.lt_acc[s]) + (size_t)L.parity * abytes;
+    for (size_t i = gtid; ok && i < region; i += gsz) {
+      const uint64_t key = P.in_keys[in0 + i];
+      if (key == kEmptyKey) continue;
+      float g; uint32_t dpos, dneg;
+      load_acc<true>(abase, lt0 + i, peer, &g, &dpos, &dneg);
+      cm_insert(H.cm, H.cm_width, H.cm_k, key, dpos + dneg);
+    }
+    grid.sync();
+    for (size_t i = gtid; ok && i < region; i += gsz) {
+      const uint64_t key = P.in_keys[in0 + i];
+      if (key == kEmptyKey) continue;
+      if (cm_query(H.cm, H.cm_width, H.cm_k, key, 0xFFFFFFFFu) <= H.tail_freq) continue;
+      uint32_t slot = __ldcg(P.in_slot + in0 + i);
+      if (slot >= kAbsent) {
+        float w;
+        slot = shard_find_or_insert(P.tab, P.tab_mask, P.tab_shift, key, P.max_probe, &w, &acc.dins);
+        if (slot == kAbsent) { set_status(L.status, kShardTableFull, 0, 0); continue; }
+      }
+      float g; uint32_t dpos, dneg;
+      load_acc<true>(abase, lt0 + i, peer, &g, &dpos, &dneg);
+      apply_slot(P.tab, slot, g, dpos, dneg, H, acc);
+    }
+    grid.sync();
+  }
 }
 
 // ------------------------------------------------------------ fused kernels
@@ -599,29 +660,45 @@ __device__ __forceinline__ void phase_apply(ShardSlot* tab, uint64_t mask, uint3
 #ifndef PSB_PULL_MIN_BLOCKS
 #define PSB_PULL_MIN_BLOCKS 8
 #endif
-template <bool kCounts>
+constexpr uint32_t kPullInsert = 1u;   // flags: create missing keys in the shard
+
 __global__ void __launch_bounds__(256, PSB_PULL_MIN_BLOCKS)
-ftrl_pull_spmv_kernel(FtrlPeers P, Minibatch M, LocalScratch L, uint32_t epoch) {
+ftrl_pull_spmv_kernel(FtrlPeers P, Minibatch M, LocalScratch L, uint32_t seq, uint32_t flags) {
   cg::grid_group grid = cg::this_grid();
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t gsz = (size_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
+  const int world = P.seps.world;
+  __shared__ int sh_ok;
 
-  // every owner must have applied step epoch-1 before its table is read
-  if (blockIdx.x == 0 && threadIdx.x < P.seps.world) {
-    bool ok;
-    wait_epoch_ge(P.applied[P.rank] + threadIdx.x, epoch - 1, P.timeout_ns, &ok);
-    if (!ok) set_status(L.status, kWaitTimeout, threadIdx.x, 1);
-  }
   if (gtid == 0) L.stats[1] += (double)M.rows;
   PSB_TRACE(L, gtid, 0);
-  phase_localize(M, L, P.max_probe, gtid, gsz);
+  phase_localize(P, M, L, gtid, gsz);
+  if (world > 1) __threadfence_system();   // the table must be visible to its owners before the flag is
   grid.sync();
   PSB_TRACE(L, gtid, 1);
-  phase_gather<kCounts>(P, L, gtid, gsz);
+  // this worker's table is complete: tell every owner, then serve the other workers' tables
+  if (blockIdx.x == 0 && threadIdx.x < world && world > 1) {
+    __threadfence_system();
+    st_release_sys_u64(P.ready[threadIdx.x] + P.rank, (uint64_t)seq << 32);
+  }
+  phase_lookup(P, L, seq, (flags & kPullInsert) != 0u, &sh_ok);
+  if (world > 1) __threadfence_system();   // the weights must be visible to their workers before the flag is
   grid.sync();
+  if (blockIdx.x == 0 && threadIdx.x < world && world > 1)
+    st_release_sys_u64(P.replied[threadIdx.x] + P.rank, (uint64_t)seq << 32);
+  // every owner must have answered before the rows are multiplied
+  if (world > 1) {
+    __syncthreads();
+    if (threadIdx.x < world && threadIdx.x != P.rank) {
+      bool ok;
+      wait_epoch_ge(P.replied[P.rank] + threadIdx.x, seq, P.timeout_ns, &ok);
+      if (!ok) set_status(L.status, kWaitTimeout, threadIdx.x, 3);
+    }
+    __syncthreads();
+  }
   PSB_TRACE(L, gtid, 2);
-  phase_spmv_loss<kCounts>(M, L, gtid >> 5, gsz >> 5, lane);
+  phase_spmv_loss(M, L, gtid >> 5, gsz >> 5, lane);
   PSB_TRACE(L, gtid, 3);
 }
 
@@ -632,93 +709,45 @@ ftrl_pull_spmv_kernel(FtrlPeers P, Minibatch M, LocalScratch L, uint32_t epoch) 
 #endif
 template <bool kCounts>
 __global__ void __launch_bounds__(256, PSB_PUSH_MIN_BLOCKS)
-ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, uint32_t epoch) {
+ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, uint32_t seq) {
   cg::grid_group grid = cg::this_grid();
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t gsz = (size_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
   const int world = P.seps.world;
 
-  // the hot-slot cache (gradient phase) and the send staging area (routing phase) are never live together
-  __shared__ union PushSmem { HotCache hot; SendStage stage; } sm;
+  __shared__ HotCache hot;
+  __shared__ int sh_ok;
   PSB_TRACE(L, gtid, 4);
-  phase_grad<kCounts>(M, L, gtid >> 5, gsz >> 5, lane, &sm.hot);
+  phase_grad<kCounts>(M, L, gtid >> 5, gsz >> 5, lane, &hot);
+  if (world > 1) __threadfence_system();   // the accumulators must be visible to their owners before the flag is
   grid.sync();
   PSB_TRACE(L, gtid, 5);
-  phase_route_send<kCounts>(P, L, &sm.stage);
-  grid.sync();
+  if (blockIdx.x == 0 && threadIdx.x < world && world > 1)
+    st_release_sys_u64(P.grads[threadIdx.x] + P.rank, (uint64_t)seq << 32);
+  phase_reset_tables<kCounts>(L, gtid, gsz);
   PSB_TRACE(L, gtid, 6);
-  // tell every owner that this sender's records and fill levels are in place, then wait for all senders
-  if (blockIdx.x == 0 && threadIdx.x < world) {
-    const int t = threadIdx.x;
-    __threadfence_system();
-    st_release_sys_u64(P.in_flag[t] + P.rank, (uint64_t)epoch << 32);
-    bool ok;
-    wait_epoch_ge(P.in_flag[P.rank] + t, epoch, P.timeout_ns, &ok);
-    L.recv_cnt[t] = ok ? 1u : 0u;  // a sender that never arrived is skipped
-    if (!ok) set_status(L.status, kWaitTimeout, t, 2);
-  }
-  grid.sync();
-  PSB_TRACE(L, gtid, 7);
-  // Apply sender by sender (the reference applies each worker's push separately).  The order only
-  // matters per key, and a key lives in one chunk: a block takes chunk c and walks the senders'
-  // segments of that chunk in rank order with block-level barriers.  With the tail filter on, a
-  // sender's counts must all be in the sketch before any of its keys is queried, so that case keeps
-  // grid-wide barriers around every sender.
   {
     ApplyAcc acc;
-    ShardSlot* tab = P.tab[P.rank];
-    const uint64_t* rk = P.in_keys[P.rank];
-    const float* rg = P.in_g[P.rank];
-    const uint64_t* rc = P.in_cnt[P.rank];
-    const uint32_t* fill = P.in_chunk[P.rank];
-    if (!(kCounts && tail_filter_on(H))) {
-      for (uint32_t c = blockIdx.x; c < P.nchunks; c += gridDim.x) {
-        for (int s = 0; s < world; ++s) {
-          if (__ldcg(L.recv_cnt + s) == 0u) continue;
-          const uint32_t n = min(__ldcg(fill + (size_t)s * P.nchunks + c), (uint32_t)kChunkSlots);
-          const size_t off = (size_t)s * P.in_cap + (size_t)c * kChunkSlots;
-          apply_records<kCounts>(tab, P.tab_mask, P.tab_shift, P.max_probe, rk + off, rg + off, rc + off, n, H, acc,
-                                 L.status, threadIdx.x, blockDim.x);
-          __syncthreads();
-        }
-      }
+    if (kCounts && tail_filter_on(H)) {
+      phase_apply_filtered(grid, P, L, H, seq, acc, &sh_ok);
     } else {
-      for (int s = 0; s < world; ++s) {
-        const bool have = __ldcg(L.recv_cnt + s) != 0u;
-        for (uint32_t c = blockIdx.x; have && c < P.nchunks; c += gridDim.x) {
-          const uint32_t n = min(__ldcg(fill + (size_t)s * P.nchunks + c), (uint32_t)kChunkSlots);
-          const size_t off = (size_t)s * P.in_cap + (size_t)c * kChunkSlots;
-          phase_sketch_insert(rk + off, rc + off, n, H, threadIdx.x, blockDim.x);
-        }
-        grid.sync();
-        for (uint32_t c = blockIdx.x; have && c < P.nchunks; c += gridDim.x) {
-          const uint32_t n = min(__ldcg(fill + (size_t)s * P.nchunks + c), (uint32_t)kChunkSlots);
-          const size_t off = (size_t)s * P.in_cap + (size_t)c * kChunkSlots;
-          apply_records<kCounts>(tab, P.tab_mask, P.tab_shift, P.max_probe, rk + off, rg + off, rc + off, n, H, acc,
-                                 L.status, threadIdx.x, blockDim.x);
-        }
-        grid.sync();
-      }
+      phase_apply_chunks<kCounts>(P, L, H, seq, acc, &sh_ok);
     }
     apply_flush(acc, L.stats);
   }
-  grid.sync();
   PSB_TRACE(L, gtid, 8);
-  if (blockIdx.x == 0 && threadIdx.x < world) {
-    __threadfence_system();
-    st_release_sys_u64(P.applied[threadIdx.x] + P.rank, (uint64_t)epoch << 32);
-  }
 }
 
 // ------------------------------------------------- stand-alone phase kernels
-__global__ void k_localize(Minibatch M, LocalScratch L, int max_probe) {
-  phase_localize(M, L, max_probe, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+// (the unfused baseline: same arithmetic, records packed by owner and exchanged with all_to_all)
+__global__ void k_localize(FtrlPeers P, Minibatch M, LocalScratch L) {
+  phase_localize(P, M, L, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
 }
 __global__ void k_spmv_loss(Minibatch M, LocalScratch L) {
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gtid == 0) L.stats[1] += (double)M.rows;
-  phase_spmv_loss<true>(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31);
+  phase_spmv_loss(M, L, gtid >> 5, ((size_t)gridDim.x * blockDim.x) >> 5, threadIdx.x & 31);
 }
 __global__ void k_grad(Minibatch M, LocalScratch L) {
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -729,7 +758,7 @@ __global__ void k_grad(Minibatch M, LocalScratch L) {
 __global__ void k_count_owner(KeySeps seps, LocalScratch L, uint32_t* counts) {
   const size_t gsz = (size_t)gridDim.x * blockDim.x;
   uint32_t c[PSB_MAX_RANKS] = {0};
-  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += gsz) {
+  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s < L.lt_slots; s += gsz) {
     const uint64_t key = L.lt_keys[s];
     if (key != kEmptyKey) {
       const int o = route_owner(seps, key);
@@ -747,7 +776,7 @@ __global__ void k_count_owner(KeySeps seps, LocalScratch L, uint32_t* counts) {
 __global__ void k_pack_keys(KeySeps seps, LocalScratch L, uint32_t* cursors, uint64_t* out_keys,
                             uint32_t* out_slot) {
   const size_t gsz = (size_t)gridDim.x * blockDim.x;
-  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += gsz) {
+  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s < L.lt_slots; s += gsz) {
     const uint64_t key = L.lt_keys[s];
     if (key != kEmptyKey) {
       const int o = route_owner(seps, key);
@@ -765,40 +794,59 @@ __global__ void k_pack_keys(KeySeps seps, LocalScratch L, uint32_t* cursors, uin
 // owner side of an unfused pull: w for each requested key (0 when absent)
 __global__ void k_lookup(const ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe,
                          const uint64_t* keys, uint32_t n, float* out_w) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    out_w[i] = probe_weight(tab, mask, shift, keys[i], max_probe, false);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float w;
+    shard_find(tab, mask, shift, keys[i], max_probe, &w);
+    out_w[i] = w;
+  }
 }
 __global__ void k_scatter_w(const uint32_t* slots, const float* w, uint32_t n, LocalScratch L) {
+  AccSlot* acc = reinterpret_cast<AccSlot*>(L.lt_acc) + (size_t)L.parity * L.lt_slots;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const uint32_t s = slots[i];
-    LocalSlot v;
-    v.w = w[i];
-    v.g = 0.f;
-    v.pos = 0.f;
-    v.neg = 0.f;
-    L.lt_val[s] = v;
+    L.lt_w[s] = w[i];
+    AccSlot z;
+    z.g = 0.f; z.pos = 0.f; z.neg = 0.f; z.pad = 0.f;
+    acc[s] = z;
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0) L.stats[5] += (double)n;
 }
 __global__ void k_pack_push(const uint32_t* slots, uint32_t n, LocalScratch L, float* out_g, uint64_t* out_cnt) {
+  const AccSlot* acc = reinterpret_cast<const AccSlot*>(L.lt_acc) + (size_t)L.parity * L.lt_slots;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const uint32_t s = slots[i];
-    out_g[i] = L.lt_val[s].g;
-    out_cnt[i] = ((uint64_t)(uint32_t)L.lt_val[s].pos << 32) | (uint64_t)(uint32_t)L.lt_val[s].neg;
+    out_g[i] = acc[s].g;
+    out_cnt[i] = ((uint64_t)(uint32_t)acc[s].pos << 32) | (uint64_t)(uint32_t)acc[s].neg;
     L.lt_keys[s] = kEmptyKey;
   }
 }
+__global__ void k_sketch_insert(const uint64_t* rk, const uint64_t* rc, uint32_t n, FtrlHyper h) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint64_t key = __ldcg(rk + i);
+    if (key == kEmptyKey) continue;
+    const uint64_t c = __ldcg(rc + i);
+    cm_insert(h.cm, h.cm_width, h.cm_k, key, (uint32_t)(c >> 32) + (uint32_t)c);
+  }
+}
+// one flat record list of one sender: find or create every key, apply the update
 __global__ void k_apply(ShardSlot* tab, uint64_t mask, uint32_t shift, int max_probe, const uint64_t* rk,
                         const float* rg, const uint64_t* rc, uint32_t n, FtrlHyper h, double* stats,
                         uint32_t* status) {
-  phase_apply<true>(tab, mask, shift, max_probe, rk, rg, rc, n, h, stats, status,
-                    (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
-}
-__global__ void k_sketch_insert(const uint64_t* rk, const uint64_t* rc, uint32_t n, FtrlHyper h) {
-  phase_sketch_insert(rk, rc, n, h, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+  ApplyAcc acc;
+  const bool filter = tail_filter_on(h);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint64_t key = __ldcg(rk + i);
+    if (key == kEmptyKey) continue;
+    if (filter && cm_query(h.cm, h.cm_width, h.cm_k, key, 0xFFFFFFFFu) <= h.tail_freq) continue;
+    float w;
+    const uint32_t slot = shard_find_or_insert(tab, mask, shift, key, max_probe, &w, &acc.dins);
+    if (slot == kAbsent) { set_status(status, kShardTableFull, 0, 0); continue; }
+    const uint64_t c = __ldcg(rc + i);
+    apply_slot(tab, slot, __ldcg(rg + i), (uint32_t)(c >> 32), (uint32_t)c, h, acc);
+  }
+  apply_flush(acc, stats);
 }
 __global__ void k_clear_local(LocalScratch L) {
-  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= L.lt_mask; s += (size_t)gridDim.x * blockDim.x)
+  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s < L.lt_slots; s += (size_t)gridDim.x * blockDim.x)
     L.lt_keys[s] = kEmptyKey;
 }
 // dump the non-zero weights of a shard: out_keys/out_w sized by capacity, *count receives the number
@@ -813,6 +861,21 @@ __global__ void k_dump_nonzero(const ShardSlot* tab, uint64_t mask, uint64_t* ou
     }
   }
 }
+// Move every entry of a shard into a larger table (same hash, more top bits): the table grows
+// like the reference's unordered_map (src/linear_method/ftrl_model.h:57) instead of filling up.
+__global__ void k_rehash(const ShardSlot* from, uint64_t from_mask, ShardSlot* to, uint64_t to_mask, uint32_t to_shift,
+                         int max_probe, uint32_t* status) {
+  for (uint64_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x; s <= from_mask; s += (size_t)gridDim.x * blockDim.x) {
+    const ShardSlot e = from[s];
+    if (e.key == kEmptyKey) continue;
+    float w;
+    int ins = 0;
+    const uint32_t slot = shard_find_or_insert(to, to_mask, to_shift, e.key, max_probe, &w, &ins);
+    if (slot == kAbsent) { set_status(status, kShardTableFull, 0, 1); continue; }
+    *reinterpret_cast<float2*>(&to[slot].w) = make_float2(e.w, e.z);
+    *reinterpret_cast<uint2*>(&to[slot].pos) = make_uint2(e.pos, e.neg);
+  }
+}
 
 }  // namespace psb
 
@@ -820,7 +883,7 @@ __global__ void k_dump_nonzero(const ShardSlot* tab, uint64_t mask, uint64_t* ou
 using namespace psb;
 
 namespace {
-int g_coop_blocks_pull[2][16] = {{0}}, g_coop_blocks_push[2][16] = {{0}};
+int g_coop_blocks_pull[16] = {0}, g_coop_blocks_push[2][16] = {{0}};
 
 template <typename K>
 int coop_grid(K kernel, int* cache) {
@@ -831,9 +894,7 @@ int coop_grid(K kernel, int* cache) {
     int per_sm = 0, sms = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int cap = 8;
-    if (const char* e = getenv("PSB_FTRL_CTAS_PER_SM")) cap = atoi(e) > 0 ? atoi(e) : cap;
-    if (per_sm > cap) per_sm = cap;
+    if (per_sm > 8) per_sm = 8;
     cache[dev] = per_sm * sms;
   }
   return cache[dev];
@@ -848,36 +909,35 @@ inline int flat_grid(size_t n, int cap = 148 * 8) {
 
 extern "C" {
 
-int psb_ftrl_pull_spmv(const FtrlPeers* P, const Minibatch* M, const LocalScratch* L, uint32_t epoch,
+// flags bit 0: create missing keys in the shard (a training step; off for predictions)
+int psb_ftrl_pull_spmv(const FtrlPeers* P, const Minibatch* M, const LocalScratch* L, uint32_t seq, uint32_t flags,
                        cudaStream_t stream) {
-  const bool soa = L->soa != 0;
-  if (soa && (L->lt_w == nullptr || L->lt_g == nullptr)) return (int)cudaErrorInvalidValue;
-  void* kernel = soa ? (void*)ftrl_pull_spmv_kernel<false> : (void*)ftrl_pull_spmv_kernel<true>;
-  const int grid = soa ? coop_grid(ftrl_pull_spmv_kernel<false>, g_coop_blocks_pull[0])
-                       : coop_grid(ftrl_pull_spmv_kernel<true>, g_coop_blocks_pull[1]);
+  if (L->lt_w == nullptr || L->lt_acc == nullptr || P->in_slot == nullptr) return (int)cudaErrorInvalidValue;
+  const int grid = coop_grid(ftrl_pull_spmv_kernel, g_coop_blocks_pull);
   if (grid <= 0) return (int)cudaErrorLaunchFailure;
   FtrlPeers p = *P; Minibatch m = *M; LocalScratch l = *L;
-  void* args[] = {&p, &m, &l, &epoch};
-  return (int)cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(256), args, 0, stream);
+  void* args[] = {&p, &m, &l, &seq, &flags};
+  return (int)cudaLaunchCooperativeKernel((void*)ftrl_pull_spmv_kernel, dim3(grid), dim3(256), args, 0, stream);
 }
 
 int psb_ftrl_push_update(const FtrlPeers* P, const Minibatch* M, const LocalScratch* L, const FtrlHyper* H,
-                         uint32_t epoch, cudaStream_t stream) {
+                         uint32_t seq, cudaStream_t stream) {
   const bool soa = L->soa != 0;
-  // the count-based rule needs the pos/neg counts that the split layout does not carry
-  if (soa && (H->rule == 0 || (H->tail_freq != 0u && H->cm != nullptr) || L->lt_w == nullptr || L->lt_g == nullptr))
-    return (int)cudaErrorInvalidValue;
+  const bool filter = H->tail_freq != 0u && H->cm != nullptr;
+  // the count-based rule and the tail filter need the pos/neg counts that the one-float accumulators do not carry
+  if (soa && (H->rule == 0 || filter)) return (int)cudaErrorInvalidValue;
+  if (filter && P->in_keys == nullptr) return (int)cudaErrorInvalidValue;
   void* kernel = soa ? (void*)ftrl_push_update_kernel<false> : (void*)ftrl_push_update_kernel<true>;
   const int grid = soa ? coop_grid(ftrl_push_update_kernel<false>, g_coop_blocks_push[0])
                        : coop_grid(ftrl_push_update_kernel<true>, g_coop_blocks_push[1]);
   if (grid <= 0) return (int)cudaErrorLaunchFailure;
   FtrlPeers p = *P; Minibatch m = *M; LocalScratch l = *L; FtrlHyper h = *H;
-  void* args[] = {&p, &m, &l, &h, &epoch};
+  void* args[] = {&p, &m, &l, &h, &seq};
   return (int)cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(256), args, 0, stream);
 }
 
-int psb_ftrl_localize(const Minibatch* M, const LocalScratch* L, int max_probe, cudaStream_t s) {
-  k_localize<<<flat_grid(M->nnz), 256, 0, s>>>(*M, *L, max_probe);
+int psb_ftrl_localize(const FtrlPeers* P, const Minibatch* M, const LocalScratch* L, cudaStream_t s) {
+  k_localize<<<flat_grid(M->nnz), 256, 0, s>>>(*P, *M, *L);
   return (int)cudaGetLastError();
 }
 int psb_ftrl_spmv_loss(const Minibatch* M, const LocalScratch* L, cudaStream_t s) {
@@ -889,12 +949,12 @@ int psb_ftrl_grad(const Minibatch* M, const LocalScratch* L, cudaStream_t s) {
   return (int)cudaGetLastError();
 }
 int psb_ftrl_count_owner(const KeySeps* seps, const LocalScratch* L, uint32_t* counts, cudaStream_t s) {
-  k_count_owner<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*seps, *L, counts);
+  k_count_owner<<<flat_grid(L->lt_slots), 256, 0, s>>>(*seps, *L, counts);
   return (int)cudaGetLastError();
 }
 int psb_ftrl_pack_keys(const KeySeps* seps, const LocalScratch* L, uint32_t* cursors, uint64_t* out_keys,
                        uint32_t* out_slot, cudaStream_t s) {
-  k_pack_keys<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*seps, *L, cursors, out_keys, out_slot);
+  k_pack_keys<<<flat_grid(L->lt_slots), 256, 0, s>>>(*seps, *L, cursors, out_keys, out_slot);
   return (int)cudaGetLastError();
 }
 int psb_ftrl_lookup(const void* tab, uint64_t mask, uint32_t shift, int max_probe, const uint64_t* keys,
@@ -919,12 +979,18 @@ int psb_ftrl_apply(void* tab, uint64_t mask, uint32_t shift, int max_probe, cons
   return (int)cudaGetLastError();
 }
 int psb_ftrl_clear_local(const LocalScratch* L, cudaStream_t s) {
-  k_clear_local<<<flat_grid(L->lt_mask + 1), 256, 0, s>>>(*L);
+  k_clear_local<<<flat_grid(L->lt_slots), 256, 0, s>>>(*L);
   return (int)cudaGetLastError();
 }
 int psb_ftrl_dump_nonzero(const void* tab, uint64_t mask, uint64_t* out_keys, float* out_w,
                           unsigned long long* count, cudaStream_t s) {
   k_dump_nonzero<<<flat_grid(mask + 1), 256, 0, s>>>((const ShardSlot*)tab, mask, out_keys, out_w, count);
+  return (int)cudaGetLastError();
+}
+int psb_ftrl_rehash(const void* from, uint64_t from_mask, void* to, uint64_t to_mask, uint32_t to_shift, int max_probe,
+                    uint32_t* status, cudaStream_t s) {
+  k_rehash<<<flat_grid(from_mask + 1), 256, 0, s>>>((const ShardSlot*)from, from_mask, (ShardSlot*)to, to_mask, to_shift,
+                                                     max_probe, status);
   return (int)cudaGetLastError();
 }
 

@@ -55,8 +55,10 @@ def planted_weight(keys: torch.Tensor, frac: float, std: float, salt: int = 0x5E
 
 def ctr_minibatch(rows: int, *, seed: int, device, key_space_log2: int = 30, zipf_s: float = 1.1, groups: int = 12,
                   feats_lo: int = 6, feats_hi: int = 10, bias: float = -3.2, wstar_frac: float = 0.01,
-                  wstar_std: float = 0.5) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """One minibatch (offsets int64[rows+1], keys int64[nnz], y float32[rows] in ±1)."""
+                  wstar_std: float = 0.5, return_ids: bool = False) -> Tuple[torch.Tensor, ...]:
+    """One minibatch (offsets int64[rows+1], keys int64[nnz], y float32[rows] in ±1).  A key is the 64-bit mix
+    of a feature id below 2^key_space_log2; with ``return_ids`` the ids come back too (int32[nnz], for the
+    compact input encoding that hashes on the device)."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     per_group = torch.randint(feats_lo, feats_hi + 1, (rows, groups), generator=gen, device=device)
@@ -68,12 +70,14 @@ def ctr_minibatch(rows: int, *, seed: int, device, key_space_log2: int = 30, zip
     ranks = zipf_ranks(nnz, zipf_s, vocab, gen, device)
     # group of each non-zero: expand per-row group counts
     grp = torch.repeat_interleave(torch.arange(groups, device=device).repeat(rows), per_group.reshape(-1))
-    keys = mix64(ranks * groups + grp)
-    keys = torch.where(keys == -1, torch.zeros_like(keys), keys)  # 2^64-1 is reserved
+    fid = ranks * groups + grp
+    keys = mix64(fid)     # (a bijection: the reserved key 2^64-1 is the image of one id far above any key space here)
     wstar = planted_weight(keys, wstar_frac, wstar_std)
     row_of = torch.repeat_interleave(torch.arange(rows, device=device), counts)
     margin = torch.zeros(rows, dtype=torch.float32, device=device).index_add_(0, row_of, wstar) + bias
     y = torch.where(torch.rand(rows, generator=gen, device=device) < torch.sigmoid(margin), 1.0, -1.0)
+    if return_ids:
+        return offsets, keys, y.to(torch.float32), fid.to(torch.int32)
     return offsets, keys, y.to(torch.float32)
 
 

@@ -5,10 +5,12 @@ Role map to the reference: :class:`FTRLEngine` is worker + server of one rank ‚Ä
 ``FTRLModel`` (src/linear_method/ftrl_model.h) on the server side.  A step is
 two cooperative kernels (see ``csrc/ftrl_kernels.cu``):
 
-* pull-fused SpMV  ‚Äî dedup keys, gather weights from the owner shards over NVLink,
-  ``Xw``, logistic loss, per-row coefficient;
-* push-fused update ‚Äî ``X·µÄ¬∑coef`` + pos/neg counts per unique key, key-range
-  routing into the owners' inboxes, owner-side FTRL update on arrival.
+* pull-fused SpMV  ‚Äî dedup keys into a table laid out by owner; every owner reads its region
+  of every worker's table over NVLink, looks the keys up in its shard and stores the weights
+  into the worker's weight array; ``Xw``, logistic loss, per-row coefficient;
+* push-fused update ‚Äî ``X·µÄ¬∑coef`` + pos/neg counts per unique key into the worker's
+  accumulators; every owner reads its region of them over NVLink and applies the FTRL update
+  to the shard slots it resolved during the pull.
 
 ``impl="nccl"`` runs the same arithmetic with stand-alone kernels and
 ``all_to_all_single`` exchanges; it is the comparison baseline, not the product.
@@ -22,8 +24,10 @@ from typing import Optional
 import torch
 
 from ..ops import _native as N
-from ..parallel.peer import PeerGroup
+from ..parallel.peer import PeerGroup, SymmetricBuffer
 from ..utils.range import Range
+
+KEY_U64, KEY_U32, KEY_U32_HASHED = 0, 1, 2
 
 
 @dataclass
@@ -46,11 +50,17 @@ class FTRLHyper:
 
 @dataclass
 class DeviceMinibatch:
-    """CSR minibatch resident on the device. ``keys`` holds uint64 bit patterns in int64."""
-    offsets: torch.Tensor            # int64 [rows+1]
-    keys: torch.Tensor               # int64 [nnz]
+    """CSR minibatch resident on the device.
+
+    ``keys``: uint64 bit patterns in int64 (``key_mode`` KEY_U64), or 32-bit feature ids in int32 that the
+    kernels widen on the fly: KEY_U32 uses the id itself as the key, KEY_U32_HASHED the 64-bit mix of the id
+    (``data.synthetic.mix64``) ‚Äî half the bytes per non-zero for jobs whose feature space fits 32 bits.
+    ``offsets``: int64 or int32."""
+    offsets: torch.Tensor            # [rows+1]
+    keys: torch.Tensor               # [nnz]
     y: torch.Tensor                  # float32 [rows], ¬±1
     vals: Optional[torch.Tensor] = None  # float32 [nnz]; None = binary features
+    key_mode: int = KEY_U64
 
     @property
     def rows(self) -> int:
@@ -61,7 +71,8 @@ class DeviceMinibatch:
         return self.keys.numel()
 
     def nbytes(self) -> int:
-        n = self.offsets.numel() * 8 + self.keys.numel() * 8 + self.y.numel() * 4
+        n = (self.offsets.numel() * self.offsets.element_size() + self.keys.numel() * self.keys.element_size()
+             + self.y.numel() * 4)
         return n + (self.vals.numel() * 4 if self.vals is not None else 0)
 
 
@@ -75,13 +86,18 @@ def _pow2_at_least(n: int) -> int:
 class FTRLEngine:
     """Worker + server shard of one rank for online FTRL (see module docstring)."""
 
+    GROW_AT = 0.75    # share of the shard table's slots that may be taken after a worst-case step
+
     def __init__(self, group: PeerGroup, hyper: FTRLHyper, *, table_capacity: int, max_rows: int, max_nnz: int,
                  local_capacity: Optional[int] = None, timeout_s: float = 2.0, max_probe: int = 512,
                  key_range: Optional[Range] = None, impl: str = "fused", track_counts: Optional[bool] = None):
-        """``track_counts``: keep the per-key pos/neg row counts of FTRL::countKeys
+        """``table_capacity``: initial slots of this rank's shard table (it grows by doubling, see
+        :meth:`maybe_grow`).  ``local_capacity``: slots of the per-minibatch table over all owners; it should
+        hold about 1.5 x the unique keys of a minibatch, evenly spread over the owners' key ranges.
+        ``track_counts``: keep the per-key pos/neg row counts of FTRL::countKeys
         (src/linear_method/ftrl.cc:154-174).  The count rule needs them; the Œ£g¬≤ rule does not, and
-        without them the fused kernels use a 4-byte-per-value split layout of the minibatch table and
-        12-byte push records.  Default: on for ``rule="count"``, off for ``rule="sumsq"``."""
+        without them an accumulator is one float instead of four.  Default: on for ``rule="count"``,
+        off for ``rule="sumsq"``."""
         if group.world > N.MAX_RANKS:
             raise ValueError(f"at most {N.MAX_RANKS} ranks per box")
         needs_counts = hyper.rule == "count" or hyper.tail_feature_freq > 0
@@ -92,36 +108,30 @@ class FTRLEngine:
         self.track_counts = bool(track_counts) or impl != "fused"
         self.group, self.hyper, self.impl = group, hyper, impl
         self.dev = group.device
-        self.cap = _pow2_at_least(table_capacity)
-        self.lcap = _pow2_at_least(local_capacity or max_nnz)
-        if self.lcap >= (1 << 32) - 1:
-            raise ValueError("local table too large")
-        self.in_cap = self.lcap
-        self.max_rows, self.max_nnz = max_rows, max_nnz
-        self.epoch = 0
-        self.key_range = key_range or Range.all()
-        self.seps = self.key_range.separators(group.world)
         W = group.world
+        # one region of 2^region_log2 slots per owner
+        lcap = _pow2_at_least(local_capacity or max_nnz)
+        self.region_log2 = max((lcap // _pow2_at_least(W)).bit_length() - 1, 2)    # at least 4 slots: 16-byte rows
+        self.lcap = W << self.region_log2
+        if self.lcap >= (1 << 32) - 2:
+            raise ValueError("local table too large")
+        self.max_rows, self.max_nnz, self.max_probe = max_rows, max_nnz, max_probe
+        self.epoch = 0          # training steps taken
+        self.pull_seq = 0       # pulls launched (steps and predictions): sequence of the ready / replied flags
+        self.push_seq = 0       # pushes launched: sequence of the grads flags, parity of the accumulator buffers
+        self.key_range = key_range or Range.all()
+        self.seps = self.key_range.separators(W)
         i64, f32 = torch.int64, torch.float32
-
-        # --- server side: shard table + inbox + flags (peer-addressable)
-        # one 32-byte slot per key: [key, (w,z), (pos,neg), reserved] viewed as 4 x int64
-        self.tab = group.alloc((self.cap, 4), i64, fill=0)
-        self.tab.local[:, 0] = -1
-        self.in_keys = group.alloc((W * self.in_cap,), i64, fill=-1)
-        self.in_g = group.alloc((W * self.in_cap,), f32)
-        self.in_cnt = group.alloc((W * self.in_cap,), i64)
-        # the per-minibatch table is cut into chunks of 1024 slots; chunk c of sender s owns the fixed inbox
-        # segment [s * in_cap + c * 1024, ...) and reports its fill level in in_chunk[s * nchunks + c]
-        self.nchunks = (self.lcap + 1023) // 1024
-        self.in_chunk = group.alloc((W * self.nchunks,), torch.int32)
-        self.in_flag = group.alloc((N.MAX_RANKS,), i64)
-        self.applied = group.alloc((N.MAX_RANKS,), i64)
-
-        # --- worker side: per-minibatch scratch (local only)
         d = self.dev
-        self.lt_keys = torch.full((self.lcap,), -1, dtype=i64, device=d)
-        self.lt_val = torch.zeros((self.lcap, 4), dtype=f32, device=d)
+
+        # --- worker side, readable / writable by the owners: per-minibatch table, weights, accumulators, flags
+        self.lt_keys = group.alloc((self.lcap,), i64, fill=-1)
+        self.lt_w = group.alloc((self.lcap,), f32)
+        self.lt_acc = group.alloc((2, self.lcap, 4) if self.track_counts else (2, self.lcap), f32)
+        self.ready = group.alloc((N.MAX_RANKS,), i64)
+        self.replied = group.alloc((N.MAX_RANKS,), i64)
+        self.grads = group.alloc((N.MAX_RANKS,), i64)
+        # --- worker side, private
         self.slot_of = torch.empty((max_nnz,), dtype=torch.int32, device=d)
         self.coef = torch.empty((max_rows,), dtype=f32, device=d)
         self.xw = torch.empty((max_rows,), dtype=f32, device=d)
@@ -129,6 +139,10 @@ class FTRLEngine:
         self.recv_cnt = torch.zeros((N.MAX_RANKS,), dtype=torch.int32, device=d)
         self.stats = torch.zeros((8,), dtype=torch.float64, device=d)
         self.status = torch.zeros((8,), dtype=torch.int32, device=d)
+        self.trace = torch.zeros((16,), dtype=torch.int64, device=d)
+        # --- server side, private: shard slot of every request of the current step (and the keys, for the filter)
+        self.in_slot = torch.full((self.lcap,), -1, dtype=torch.int32, device=d)
+        self.in_keys = torch.full((self.lcap,), -1, dtype=i64, device=d) if hyper.tail_feature_freq > 0 else None
 
         self._seps = N.KeySeps()
         for i, s in enumerate(self.seps):
@@ -139,32 +153,30 @@ class FTRLEngine:
 
         P = N.FtrlPeers()
         P.seps = self._seps
-        P.rank, P.max_probe, P.tab_mask = group.rank, max_probe, self.cap - 1
+        P.rank, P.max_probe = group.rank, max_probe
         for r in range(W):
-            P.tab[r] = self.tab.ptrs[r]
-            P.in_keys[r] = self.in_keys.ptrs[r]
-            P.in_g[r] = self.in_g.ptrs[r]
-            P.in_cnt[r] = self.in_cnt.ptrs[r]
-            P.in_flag[r] = self.in_flag.ptrs[r]
-            P.in_chunk[r] = self.in_chunk.ptrs[r]
-            P.applied[r] = self.applied.ptrs[r]
+            P.lt_keys[r] = self.lt_keys.ptrs[r]
+            P.lt_w[r] = self.lt_w.ptrs[r]
+            P.lt_acc[r] = self.lt_acc.ptrs[r]
+            P.ready[r] = self.ready.ptrs[r]
+            P.replied[r] = self.replied.ptrs[r]
+            P.grads[r] = self.grads.ptrs[r]
+        P.in_slot = self.in_slot.data_ptr()
+        P.in_keys = 0 if self.in_keys is None else self.in_keys.data_ptr()
         P.timeout_ns = int(timeout_s * 1e9)
-        P.in_cap = self.in_cap
-        P.nchunks = self.nchunks
-        P.tab_shift = 64 - (self.cap.bit_length() - 1)
+        P.region_log2 = self.region_log2
         self._P = P
+        # --- server side: the shard table, one 32-byte slot per key: [key, (w,z), (pos,neg), reserved] as 4 x int64
+        self._set_table(self._empty_table(_pow2_at_least(table_capacity)))
+
         L = N.LocalScratch()
-        L.lt_keys, L.lt_val, L.lt_mask = self.lt_keys.data_ptr(), self.lt_val.data_ptr(), self.lcap - 1
-        L.lt_shift = 64 - (self.lcap.bit_length() - 1)
+        L.lt_keys, L.lt_w, L.lt_acc = self.lt_keys.local.data_ptr(), self.lt_w.local.data_ptr(), self.lt_acc.local.data_ptr()
+        L.lt_slots = self.lcap
         L.slot_of, L.coef, L.xw = self.slot_of.data_ptr(), self.coef.data_ptr(), self.xw.data_ptr()
         L.send_cnt, L.recv_cnt = self.send_cnt.data_ptr(), self.recv_cnt.data_ptr()
         L.stats, L.status = self.stats.data_ptr(), self.status.data_ptr()
-        self.trace = torch.zeros((16,), dtype=torch.int64, device=d)
         L.trace = self.trace.data_ptr()
-        if not self.track_counts:
-            self.lt_w = torch.zeros((self.lcap,), dtype=f32, device=d)
-            self.lt_g = torch.zeros((self.lcap,), dtype=f32, device=d)
-            L.lt_w, L.lt_g, L.soa = self.lt_w.data_ptr(), self.lt_g.data_ptr(), 1
+        L.soa = 0 if self.track_counts else 1
         self._L = L
         self._H = hyper.native()
         if hyper.tail_feature_freq > 0:
@@ -175,18 +187,78 @@ class FTRLEngine:
             self._H.cm_k, self._H.tail_freq = max(int(hyper.countmin_k), 1), int(hyper.tail_feature_freq)
         self._lib = N.lib()
         self.kernel_launches = 0
+        self.grown = 0
         if impl == "nccl":
             self._u_keys = torch.empty((self.lcap,), dtype=i64, device=d)
             self._u_slot = torch.empty((self.lcap,), dtype=torch.int32, device=d)
             self._counts = torch.zeros((N.MAX_RANKS,), dtype=torch.int32, device=d)
+        self.maybe_grow(0.0)      # a table too small for even one step's keys starts larger
+        self.grown = 0
         group.barrier()
+
+    # ------------------------------------------------------------- shard table
+    def _empty_table(self, cap: int) -> torch.Tensor:
+        t = torch.zeros((cap, 4), dtype=torch.int64, device=self.dev)
+        t[:, 0] = -1
+        return t
+
+    def _set_table(self, t: torch.Tensor) -> None:
+        """Make ``t`` this rank's shard table.  Only the owner ever touches its table, so no other rank has
+        to know; the shard slots remembered between the two kernels of a step do not outlive the step."""
+        cap = t.shape[0]
+        if cap & (cap - 1) or cap >= (1 << 32) - 2:
+            raise ValueError("shard table capacity must be a power of two below 2^32")
+        self.cap = cap
+        self.tab = SymmetricBuffer(t, [t.data_ptr()])
+        self._P.tab = t.data_ptr()
+        self._P.tab_mask = cap - 1
+        self._P.tab_shift = 64 - (cap.bit_length() - 1)
+
+    def maybe_grow(self, table_entries: Optional[float] = None) -> bool:
+        """Double the shard table before it can fill up (the reference's model is an ``unordered_map`` that
+        grows, src/linear_method/ftrl_model.h:57).  One step creates at most one entry per slot of the
+        per-minibatch tables' regions for this owner, so the table grows as soon as that many new keys
+        would take it beyond ``GROW_AT`` of its slots.  Call between steps; reads the entry count from the
+        device unless the caller has it.  Local to this rank."""
+        if table_entries is None:
+            table_entries = float(self.stats[6].item())
+        worst_step = min(self.lcap, self.max_nnz * self.group.world)
+        if table_entries + worst_step <= self.GROW_AT * self.cap:
+            return False
+        new_cap = self.cap
+        while table_entries + worst_step > self.GROW_AT * new_cap:
+            new_cap *= 2
+        new = self._empty_table(new_cap)
+        N.check(self._lib.psb_ftrl_rehash(N.ptr(self.tab.local), C.c_uint64(self.cap - 1), N.ptr(new),
+                                          C.c_uint64(new_cap - 1), C.c_uint32(64 - (new_cap.bit_length() - 1)),
+                                          self.max_probe, N.ptr(self.status), N.stream_ptr()), "ftrl_rehash")
+        self.kernel_launches += 1
+        torch.cuda.current_stream(self.dev).synchronize()
+        self._set_table(new)
+        self.grown += 1
+        return True
+
+    def reset_protocol(self) -> None:
+        """Bring the flag words and sequence numbers of all ranks back to zero (collective; used after a
+        checkpoint was loaded, so that fresh and used engines continue in step)."""
+        self.group.barrier()
+        for f in (self.ready, self.replied, self.grads):
+            f.local.zero_()
+        self.pull_seq = self.push_seq = 0
+        self.lt_keys.local.fill_(-1)
+        self.lt_acc.local.zero_()
+        self.group.barrier()
 
     # ----------------------------------------------------------------- helpers
     def _mb(self, mb: DeviceMinibatch) -> N.Minibatch:
         if mb.rows > self.max_rows or mb.nnz > self.max_nnz:
             raise ValueError(f"minibatch {mb.rows}x{mb.nnz} exceeds engine limits {self.max_rows}x{self.max_nnz}")
+        off32 = 1 if mb.offsets.dtype == torch.int32 else 0
+        if (mb.keys.dtype == torch.int32) != (mb.key_mode != KEY_U64):
+            raise ValueError("32-bit keys need key_mode KEY_U32 or KEY_U32_HASHED (and 64-bit keys KEY_U64)")
         return N.Minibatch(mb.offsets.data_ptr(), mb.keys.data_ptr(),
-                           0 if mb.vals is None else mb.vals.data_ptr(), mb.y.data_ptr(), mb.nnz, mb.rows, 0)
+                           0 if mb.vals is None else mb.vals.data_ptr(), mb.y.data_ptr(), mb.nnz, mb.rows, off32,
+                           int(mb.key_mode))
 
     def check_status(self) -> None:
         """Raise if a kernel recorded an error (bounded wait ran out, table full, ...)."""
@@ -195,34 +267,38 @@ class FTRLEngine:
             raise RuntimeError(f"rank {self.group.rank}: {N.STATUS_NAMES.get(st[0], st[0])} (peer/arg={st[1]}, phase={st[2]})")
 
     # -------------------------------------------------------------------- step
+    def _launch_pull(self, M, insert: bool) -> None:
+        self.pull_seq += 1
+        N.check(self._lib.psb_ftrl_pull_spmv(C.byref(self._P), C.byref(M), C.byref(self._L), C.c_uint32(self.pull_seq),
+                                             C.c_uint32(1 if insert else 0), N.stream_ptr()), "ftrl_pull_spmv")
+        self.kernel_launches += 1
+
     def step(self, mb: DeviceMinibatch) -> None:
         """Enqueue one training step on the current stream (no host synchronisation)."""
         if self.impl == "nccl":
             return self._step_nccl(mb)
         self.epoch += 1
-        M, s = self._mb(mb), N.stream_ptr()
-        N.check(self._lib.psb_ftrl_pull_spmv(C.byref(self._P), C.byref(M), C.byref(self._L), C.c_uint32(self.epoch), s),
-                "ftrl_pull_spmv")
+        M = self._mb(mb)
+        self._L.parity = (self.push_seq + 1) & 1
+        # under the tail filter a key gets its entry only when it passes the filter, in the push
+        self._launch_pull(M, insert=self.hyper.tail_feature_freq <= 0)
+        self.push_seq += 1
         N.check(self._lib.psb_ftrl_push_update(C.byref(self._P), C.byref(M), C.byref(self._L), C.byref(self._H),
-                                               C.c_uint32(self.epoch), s), "ftrl_push_update")
-        self.kernel_launches += 2
+                                               C.c_uint32(self.push_seq), N.stream_ptr()), "ftrl_push_update")
+        self.kernel_launches += 1
 
     def predict(self, mb: DeviceMinibatch) -> torch.Tensor:
         """X¬∑w for a minibatch with the current model (collective: every rank calls it between steps).
-
-        The pull runs with the next step's epoch without consuming it, so it waits for exactly the
-        updates of the last completed step and leaves the epoch protocol untouched.
-        """
+        Creates no entries in the model."""
         M, s = self._mb(mb), N.stream_ptr()
         saved = self.stats.clone()
         if self.impl == "nccl":
             self.group.barrier()   # every owner's last apply kernel has finished
             self._pull_nccl(M)
         else:
-            N.check(self._lib.psb_ftrl_pull_spmv(C.byref(self._P), C.byref(M), C.byref(self._L),
-                                                 C.c_uint32(self.epoch + 1), s), "ftrl_pull_spmv")
+            self._launch_pull(M, insert=False)
         N.check(self._lib.psb_ftrl_clear_local(C.byref(self._L), s), "clear_local")
-        self.kernel_launches += 2
+        self.kernel_launches += 1
         out = self.xw[: mb.rows].clone()
         self.stats.copy_(saved)
         return out
@@ -240,7 +316,7 @@ class FTRLEngine:
 
         lib, L, s = self._lib, self._L, N.stream_ptr()
         W = self.group.world
-        N.check(lib.psb_ftrl_localize(C.byref(M), C.byref(L), self._P.max_probe, s), "localize")
+        N.check(lib.psb_ftrl_localize(C.byref(self._P), C.byref(M), C.byref(L), s), "localize")
         self._counts.zero_()
         N.check(lib.psb_ftrl_count_owner(C.byref(self._seps), C.byref(L), N.ptr(self._counts), s), "count_owner")
         counts = self._counts[:W].tolist()
@@ -324,8 +400,8 @@ class FTRLEngine:
         """Durations (¬µs) of the phases of the last fused step, from in-kernel globaltimer marks."""
         t = self.trace.tolist()
         d = lambda a, b: (t[b] - t[a]) / 1e3
-        return {"localize": d(0, 1), "gather": d(1, 2), "spmv_loss": d(2, 3), "kernel_gap": d(3, 4), "grad": d(4, 5),
-                "route_send": d(5, 6), "wait_senders": d(6, 7), "apply": d(7, 8), "step": d(0, 8)}
+        return {"localize": d(0, 1), "lookup_reply": d(1, 2), "spmv_loss": d(2, 3), "kernel_gap": d(3, 4), "grad": d(4, 5),
+                "flag_reset": d(5, 6), "apply": d(6, 8), "step": d(0, 8)}
 
     def penalty(self, st: dict) -> float:
         """Œª‚ÇÅ‚Äñw‚Äñ‚ÇÅ + ¬ΩŒª‚ÇÇ¬∑sqrt(‚Äñw‚Äñ‚ÇÇ¬≤) exactly as FTRLModel::objv (src/linear_method/ftrl_model.h:31)."""

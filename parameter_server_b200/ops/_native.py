@@ -45,22 +45,21 @@ _P8 = C.c_void_p * MAX_RANKS
 
 class FtrlPeers(C.Structure):
     _fields_ = [("seps", KeySeps), ("rank", C.c_int), ("max_probe", C.c_int), ("tab_mask", C.c_uint64),
-                ("tab", _P8), ("in_keys", _P8), ("in_g", _P8), ("in_cnt", _P8),
-                ("in_flag", _P8), ("applied", _P8), ("timeout_ns", C.c_uint64), ("in_cap", C.c_uint32),
-                ("tab_shift", C.c_uint32), ("in_chunk", _P8), ("nchunks", C.c_uint32), ("pad", C.c_uint32)]
+                ("tab", C.c_void_p), ("lt_keys", _P8), ("lt_w", _P8), ("lt_acc", _P8),
+                ("ready", _P8), ("replied", _P8), ("grads", _P8), ("in_slot", C.c_void_p), ("in_keys", C.c_void_p),
+                ("timeout_ns", C.c_uint64), ("tab_shift", C.c_uint32), ("region_log2", C.c_uint32)]
 
 
 class Minibatch(C.Structure):
     _fields_ = [("offsets", C.c_void_p), ("keys", C.c_void_p), ("vals", C.c_void_p), ("y", C.c_void_p),
-                ("nnz", C.c_int64), ("rows", C.c_int), ("pad", C.c_int)]
+                ("nnz", C.c_int64), ("rows", C.c_int), ("off32", C.c_uint16), ("key_mode", C.c_uint16)]
 
 
 class LocalScratch(C.Structure):
-    _fields_ = [("lt_keys", C.c_void_p), ("lt_val", C.c_void_p),
-                ("lt_mask", C.c_uint64), ("lt_shift", C.c_uint64), ("slot_of", C.c_void_p), ("coef", C.c_void_p), ("xw", C.c_void_p),
+    _fields_ = [("lt_keys", C.c_void_p), ("lt_w", C.c_void_p), ("lt_acc", C.c_void_p), ("lt_slots", C.c_uint64),
+                ("slot_of", C.c_void_p), ("coef", C.c_void_p), ("xw", C.c_void_p),
                 ("send_cnt", C.c_void_p), ("recv_cnt", C.c_void_p), ("stats", C.c_void_p),
-                ("status", C.c_void_p), ("trace", C.c_void_p),
-                ("lt_w", C.c_void_p), ("lt_g", C.c_void_p), ("soa", C.c_uint32), ("pad", C.c_uint32)]
+                ("status", C.c_void_p), ("trace", C.c_void_p), ("soa", C.c_uint32), ("parity", C.c_uint32)]
 
 
 def lib() -> C.CDLL:

@@ -132,25 +132,15 @@ def load_ftrl(eng, directory: str, step: int = -1) -> int:
     if step < 0:
         return -1
     st = torch.load(_path(directory, "ftrl", eng.group.rank, step), map_location="cpu", weights_only=True)
-    if st["cap"] != eng.cap or [int(x) for x in st["seps"]] != [int(x) for x in eng.seps]:
-        raise RuntimeError("checkpoint was written with a different table capacity or key-range partition")
-    eng.tab.local.copy_(st["table"].to(eng.dev))
+    if [int(x) for x in st["seps"]] != [int(x) for x in eng.seps]:
+        raise RuntimeError("checkpoint was written with a different key-range partition")
+    eng._set_table(st["table"].to(eng.dev))      # whatever size the table had grown to
     eng.stats.copy_(st["stats"].to(eng.dev))
     if st.get("sketch") is not None and getattr(eng, "cm", None) is not None:
         if st["sketch"].numel() != eng.cm.numel():
             raise RuntimeError("checkpoint was written with a different count-min width")
         eng.cm.copy_(st["sketch"].to(eng.dev))
-    # The step protocol of the fused kernels compares flag words with the engine's epoch: every rank
-    # continues from the stored epoch with its flags saying "everything up to here has arrived and is
-    # applied", whether the engine is fresh or has run steps before the load.
-    epoch = int(st.get("epoch", 0))
-    epochs = eng.group.all_reduce_max(float(epoch))
-    if int(epochs) != epoch:
-        raise RuntimeError(f"rank {eng.group.rank}: checkpoint epoch {epoch} differs from another rank's ({int(epochs)})")
-    eng.group.barrier()           # no kernel of an earlier step is still writing flags
-    eng.epoch = epoch
-    eng.in_flag.local.fill_(epoch << 32)
-    eng.applied.local.fill_(epoch << 32)
-    torch.cuda.synchronize(eng.dev) if eng.dev.type == "cuda" else None
-    eng.group.barrier()
+    # fresh and used engines continue in step: flag words and sequence numbers restart from zero everywhere
+    eng.epoch = int(st.get("epoch", 0))
+    eng.reset_protocol()
     return st["step"]

@@ -130,3 +130,50 @@ def test_model_text_dump(tmp_path):
     for kk, ww in zip(k[:50], w[:50]):
         assert m[int(kk)] == pytest.approx(float(ww), rel=1e-5)
 
+
+
+def test_compact_inputs_give_the_same_model():
+    """32-bit feature ids hashed on the device + 32-bit row offsets == the same minibatches as uint64 keys."""
+    from parameter_server_b200.models.ftrl import KEY_U32, KEY_U32_HASHED, DeviceMinibatch
+
+    a, _ = _engine(rule="sumsq")
+    b, _ = _engine(rule="sumsq")
+    c, _ = _engine(rule="sumsq")
+    d, _ = _engine(rule="sumsq")
+    for i in range(4):
+        off, keys, y, fid = ctr_minibatch(500, seed=40 + i, device="cuda", key_space_log2=13, bias=-0.5, wstar_frac=0.2,
+                                          wstar_std=1.0, return_ids=True)
+        a.step(DeviceMinibatch(off, keys, y))
+        b.step(DeviceMinibatch(off.to(torch.int32), fid, y, None, KEY_U32_HASHED))
+        c.step(DeviceMinibatch(off, fid.to(torch.int64), y))             # the ids themselves as keys, 64 bits wide
+        d.step(DeviceMinibatch(off.to(torch.int32), fid, y, None, KEY_U32))
+    for e in (a, b, c, d):
+        e.check_status()
+    (ka, wa), (kb, wb), (kc, wc), (kd, wd) = a.dump_model(), b.dump_model(), c.dump_model(), d.dump_model()
+    assert len(ka) > 50 and np.array_equal(ka, kb) and np.array_equal(kc, kd)
+    np.testing.assert_allclose(wa, wb, rtol=1e-5, atol=1e-7)     # same arithmetic, different summation order of atomics
+    np.testing.assert_allclose(wc, wd, rtol=1e-5, atol=1e-7)
+    with pytest.raises(ValueError, match="32-bit keys"):
+        a.step(DeviceMinibatch(off, fid, y))
+
+
+@pytest.mark.parametrize("rule", ["count", "sumsq"])
+def test_shard_table_grows_instead_of_filling_up(rule):
+    """A shard that starts far too small doubles between steps; the model stays the oracle's."""
+    from parameter_server_b200.models.ftrl import DeviceMinibatch
+
+    eng, hy = _engine(rule=rule, table_capacity=1 << 11, local_capacity=1 << 13)
+    assert eng.cap == 1 << 14                       # room for one worst-case step from the start
+    ref = FTRLRef(hy.alpha, hy.beta, hy.lambda1, hy.lambda2, rule)
+    for off, keys, y in _batches(6, rows=120, log2=13):
+        eng.step(DeviceMinibatch(off, keys, y))
+        eng.check_status()
+        eng.maybe_grow()
+        ref.step([(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64), y.cpu().numpy().astype(np.float64))])
+    assert eng.grown >= 1 and eng.cap > 1 << 14
+    st = eng.read_stats(reset=False)
+    assert st["table_entries"] == len(ref.model) and st["table_entries"] + eng.lcap <= eng.GROW_AT * eng.cap
+    k, w = eng.dump_model()
+    rk, rw = ref.nonzero()
+    assert np.array_equal(k, rk)
+    np.testing.assert_allclose(w, rw, rtol=2e-3, atol=2e-5)
