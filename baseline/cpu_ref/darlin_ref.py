@@ -31,6 +31,9 @@ class DarlinConfig:
     seed: int = 0
     max_block_delay: int = 0              # tau: groups of tau+1 blocks compute all gradients before any update
     reset_nan_on_kkt_reset: bool = True   # reference leaves filtered weights NaN forever (quirk)
+    feature_group_bits: int = 0           # b > 0: a key's top b bits are its feature group (batch_solver.cc:48-66)
+    prior_fea_group: tuple = ()           # groups swept first, with zero delay, in the first pass (batch_solver.cc:88-108)
+    num_iter_for_prior_fea_group: int = 5
 
 
 def block_ranges(min_key: int, max_key_excl: int, nnz_per_row: float, ratio: float) -> List[Tuple[int, int]]:
@@ -101,8 +104,26 @@ class DarlinRef:
         self.violation = 0.0
         self.kkt_threshold = 1e20
         mn, mx = int(keys_all.min()), int(keys_all.max()) + 1
-        self.block_keys = block_ranges(mn, mx, nnz / rows, cfg.feature_block_ratio)
-        self.blocks = [(int(np.searchsorted(keys_all, b)), int(np.searchsorted(keys_all, e))) for b, e in self.block_keys]
+        if cfg.feature_group_bits > 0:
+            # per group: key range, non-zeros, examples in which the group occurs; blocks group by group
+            sh = np.uint64(64 - cfg.feature_group_bits)
+            self.block_keys, self.block_group = [], []
+            for g in np.unique(keys_all >> sh).tolist():
+                gk = keys_all[(keys_all >> sh) == np.uint64(g)]
+                ele = ex = 0
+                for off, cols, _, y in shards:
+                    m = (cols >> sh) == np.uint64(g)
+                    ele += int(m.sum())
+                    ex += len(np.unique(np.repeat(np.arange(len(y)), np.diff(off))[m]))
+                for b, e in block_ranges(int(gk.min()), int(gk.max()) + 1, ele / max(ex, 1), cfg.feature_block_ratio):
+                    if e > b:
+                        self.block_keys.append((b, e))
+                        self.block_group.append(int(g))
+        else:
+            self.block_keys = block_ranges(mn, mx, nnz / rows, cfg.feature_block_ratio)
+            self.block_group = [1] * len(self.block_keys)
+        self.blocks = [(int(np.searchsorted(keys_all, np.uint64(b))),
+                        len(keys_all) if e >= (1 << 64) else int(np.searchsorted(keys_all, np.uint64(e)))) for b, e in self.block_keys]
         self.progress: List[Progress] = []
 
     # ------------------------------------------------------------------ block step
@@ -212,7 +233,19 @@ class DarlinRef:
         fin = np.nan_to_num(self.w, nan=0.0)
         return loss + self.cfg.lambda1 * float(np.abs(fin).sum()), int((fin != 0).sum()), int(self.active.sum())
 
-    def run_pass(self, order: np.ndarray, reset: bool) -> Progress:
+    def prior_order(self) -> List[int]:
+        """Extra sweeps over the blocks of the important groups (same draw as the solvers')."""
+        rng = np.random.RandomState(self.cfg.seed + 1)
+        out: List[int] = []
+        for g in self.cfg.prior_fea_group:
+            tmp = [k for k, bg in enumerate(self.block_group) if bg == int(g)]
+            for _ in range(int(self.cfg.num_iter_for_prior_fea_group) if tmp else 0):
+                if self.cfg.random_block_order:
+                    rng.shuffle(tmp)
+                out += list(tmp)
+        return out
+
+    def run_pass(self, order: np.ndarray, reset: bool, prior: Sequence[int] = ()) -> Progress:
         self.violation = 0.0
         if reset:
             self.active[:] = True
@@ -222,6 +255,8 @@ class DarlinRef:
                 self.w[np.isnan(self.w)] = 0.0
         g = max(int(self.cfg.max_block_delay), 0) + 1
         order = [int(b) for b in order]
+        for b in prior:                       # zero delay: one block at a time
+            self.run_block(int(b))
         for i in range(0, len(order), g):
             self.run_group(order[i:i + g])
         objv, nnz_w, nnz_as = self.evaluate()
@@ -235,8 +270,9 @@ class DarlinRef:
         cfg = self.cfg
         orders = block_order(len(self.blocks), cfg.max_pass, cfg.random_block_order, cfg.seed)
         reset = False
+        prior = self.prior_order()
         for it in range(cfg.max_pass):
-            p = self.run_pass(orders[it], reset)
+            p = self.run_pass(orders[it], reset, prior if it == 0 else ())
             if 0 < p.relative_objv <= cfg.epsilon:
                 if reset:
                     break

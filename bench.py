@@ -322,6 +322,7 @@ def run_darlin(args):
                            epsilon=0.0, feature_block_ratio=4.0, random_block_order=True, seed=0,
                            max_block_delay=args.block_delay)
     impl = "nccl" if args.impl == "nccl" else "fused"
+    import dataclasses
 
     def timed(sol, with_eval):
         orders = block_order(sol.nblk, args.warmup + args.steps, True, 0)
@@ -345,33 +346,72 @@ def run_darlin(args):
         sol.check_status()
         return ms, sol.kernel_launches - l0, sol.h2d_bytes - h0, objs
 
-    sol = DarlinSolver(group, cfg, timeout_s=args.timeout_s, impl=impl)
-    sol.preprocess(off, idx, vals, y)
-    nnz_total = int(group.all_reduce_sum([idx.numel()])[0])
-    nblk = sol.nblk
-    sampler = ClockSampler(dev)
-    sampler.start()
-    ms, launches, _, _ = timed(sol, False)
-    objv, nnz_w, nnz_as, _ = sol.evaluate()
-    e2e = None
-    if not args.no_e2e and impl == "fused":
+    def arm(which, tau, ooc=False):
+        """Device-timed bare passes, then the same passes again through run_pass (KKT filter threshold updated and
+        objective read back after every pass): ms per pass and the objective after every pass."""
+        sol = DarlinSolver(group, dataclasses.replace(cfg, max_block_delay=tau), timeout_s=args.timeout_s, impl=which,
+                           out_of_core=ooc, prefetch_depth=args.prefetch_depth)
+        sol.preprocess(off, idx, vals, y)
+        out = {"nblk": sol.nblk}
+        if not ooc:
+            out["ms"], out["launches"], _, _ = timed(sol, False)
+            out["final"] = sol.evaluate()
+        out["ms_eval"], l2, out["h2d"], out["objs"] = timed(sol, True)
+        out.setdefault("launches", l2)
         del sol
         torch.cuda.empty_cache()
-        ooc = DarlinSolver(group, cfg, timeout_s=args.timeout_s, impl="fused", out_of_core=True,
-                           prefetch_depth=args.prefetch_depth)
-        ooc.preprocess(off, idx, vals, y)
-        ms2, _, h2d, objs = timed(ooc, True)
+        return out
+
+    def first_reaching(objs, target):
+        return next((i + 1 for i, o in enumerate(objs) if o <= target), None)
+
+    nnz_total = int(group.all_reduce_sum([idx.numel()])[0])
+    sampler = ClockSampler(dev)
+    sampler.start()
+    main = arm(impl, args.block_delay)
+    nblk, ms, launches = main["nblk"], main["ms"], main["launches"]
+    objv, nnz_w, nnz_as, _ = main["final"]
+    value = rows_total * args.steps / (ms / 1e3)
+    vs, variants = None, {}
+    if impl == "fused" and not args.no_baseline:
+        base = arm("nccl", args.block_delay)
+        # time to objective: passes (and device time of that many bare passes) until the objective is within 1 % of
+        # what this arm reaches after the timed passes
+        target = 1.01 * main["objs"][-1]
+        pf, pn = first_reaching(main["objs"], target), first_reaching(base["objs"], target)
+        vs = {"baseline": "NCCL-only path of the same algorithm (stand-alone kernels per block, all_reduce of the block's "
+                          "(G,U) and weights), same process group, same data, same block orders",
+              "nccl_ms_per_step": base["ms"] / args.steps, "nccl_value": rows_total * args.steps / (base["ms"] / 1e3),
+              "ratio": base["ms"] / ms, "nccl_gpu_launches": base["launches"],
+              "time_to_objective": {"target": target, "fused_passes": pf, "nccl_passes": pn,
+                                    "fused_ms": None if pf is None else pf * ms / args.steps,
+                                    "nccl_ms": None if pn is None else pn * base["ms"] / args.steps}}
+        if args.also_delay is not None and args.also_delay != args.block_delay:
+            v = arm("fused", args.also_delay)
+            pv = first_reaching(v["objs"], target)
+            variants[f"tau{args.also_delay}"] = {
+                "ms_per_step": v["ms"] / args.steps, "value": rows_total * args.steps / (v["ms"] / 1e3),
+                "objective_trace": [round(o, 2) for o in v["objs"]], "passes_to_target": pv,
+                "ms_to_target": None if pv is None else pv * v["ms"] / args.steps}
+    e2e = None
+    if not args.no_e2e and impl == "fused":
+        ooc = arm("fused", args.block_delay, ooc=True)
+        ms2 = ooc["ms_eval"]
         e2e = {"value": rows_total * args.steps / (ms2 / 1e3), "unit": "examples/s", "ms_per_step": ms2 / args.steps,
-               "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": 40, "objective_last": objs[-1] if objs else None,
+               "h2d_bytes_per_step": ooc["h2d"] // args.steps, "d2h_bytes_per_step": 40,
+               "objective_last": ooc["objs"][-1] if ooc["objs"] else None,
                # time to objective: objective after every pass; pass i completes at (i+1) * ms_per_step
-               "objective_trace": [round(o, 2) for o in objs]}
+               "objective_trace": [round(o, 2) for o in ooc["objs"]]}
+        if vs is not None:
+            vs["nccl_e2e_value"] = rows_total * args.steps / (base["ms_eval"] / 1e3)     # resident data, objective read back
+            vs["e2e_ratio"] = e2e["value"] / vs["nccl_e2e_value"]
     clocks = sampler.stop()
     group.barrier()
     return {
         "metric": "examples/sec (L1-LR, DARLIN block coordinate descent, one pass = one step)",
-        "value": rows_total * args.steps / (ms / 1e3), "unit": "examples/s",
+        "value": value, "unit": "examples/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-        "higher_is_better": True, "scaling": "weak" if ooc_shape else "strong", "vs_baseline": None, "dtype": "fp32",
+        "higher_is_better": True, "scaling": "weak" if ooc_shape else "strong", "vs_baseline": vs, "dtype": "fp32",
         "data": "synthetic",
         "impl": "nccl-baseline" if impl == "nccl" else "fused",
         "config": {"model": ("out-of-core L1 logistic regression, DARLIN over 64 feature blocks, lambda1=4, KKT ratio 10, binary "
@@ -384,7 +424,9 @@ def run_darlin(args):
                    "parallelism": f"dp{world} rows x key-range shards {world} (worker+server per GPU)",
                    "l2_policy": f"inputs larger than L2: {nnz_total * (4 if vals is None else 8) >> 20} MiB of CSC row ids"
                                 f"{'' if vals is None else ' and values'} read per pass",
-                   "objective_after_timed_passes": objv, "nnz_w": nnz_w, "active_keys": nnz_as},
+                   "objective_after_timed_passes": objv, "nnz_w": nnz_w, "active_keys": nnz_as,
+                   "objective_trace": [round(o, 2) for o in main["objs"]]},
+        "variants": variants or None,
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
     }, rank
 
@@ -398,6 +440,8 @@ def main() -> None:
     ap.add_argument("--ooc-rows", type=int, default=1000000, help="rows per GPU of the out-of-core configuration")
     ap.add_argument("--block-delay", type=int, default=0,
                     help="DARLIN bounded delay tau (max_block_delay): tau+1 blocks share their synchronisation points")
+    ap.add_argument("--also-delay", type=int, default=None,
+                    help="DARLIN: also run the fused arm with this bounded delay and report it under `variants`")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)

@@ -90,7 +90,9 @@ def validation_auc(group: PeerGroup, conf_data, flags, cache: str, mk, mw, goodn
     if files:
         off, keys, vals, y, _ = load_csr(conf_data, files, flags, cache + "valid/", group.device)
         xw = predict_csr(off, keys, vals, mk, mw)
-        auc.add(y.cpu().numpy(), xw.cpu().numpy())
+        from ..ops.evalops import auc_histogram
+
+        auc.merge_data(*auc_histogram(y, xw, int(goodness)))     # binned on the device: only the occupied bins come back
     if group.world > 1:
         import torch.distributed as dist
 
@@ -129,16 +131,17 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
                           epsilon=s.epsilon, feature_block_ratio=s.feature_block_ratio,
                           random_block_order=s.random_feature_block_order, max_block_delay=s.max_block_delay,
                           seed=int(flags.seed), tail_feature_freq=int(s.tail_feature_freq),
-                          countmin_k=int(s.countmin_k), countmin_n_ratio=float(s.countmin_n_ratio))
+                          countmin_k=int(s.countmin_k), countmin_n_ratio=float(s.countmin_n_ratio),
+                          # TERAFEA keys carry their feature group in their top 10 bits: blocks are cut group by group
+                          feature_group_bits=10 if (lm.training_data.has("text") and lm.training_data.text == "TERAFEA") else 0,
+                          prior_fea_group=tuple(int(g) for g in s.prior_fea_group),
+                          num_iter_for_prior_fea_group=int(s.num_iter_for_prior_fea_group))
         if lm.has("darling"):
             impl = flags.impl if flags.impl in ("fused", "nccl") else "fused"
             # -mmap_training_data: the column blocks stay in pinned host memory and are streamed per pass
-            # (FeatureStation's out-of-core mode, src/linear_method/feature_station.cc:70-109); one GPU per job so far
+            # (FeatureStation's out-of-core mode, src/linear_method/feature_station.cc:70-109); every rank streams
+            # the blocks of its own rows
             ooc = bool(flags.mmap_training_data) and impl == "fused" and lm.init_w.type != "FILE"
-            if ooc and group.world > 1:
-                if group.rank == 0:
-                    print("-mmap_training_data: streaming from host memory runs on one GPU; this job keeps its data resident")
-                ooc = False
             sol = DarlinSolver(group, dc, timeout_s=float(flags.timeout_s), impl=impl, out_of_core=ooc)
             from ..utils.trace import ChromeTrace, MetricsLog
 

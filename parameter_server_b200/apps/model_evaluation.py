@@ -29,8 +29,10 @@ def evaluate_model(lm, flags, group) -> dict:
     if vfiles:
         off, keys, vals, y, _ = load_csr(lm.validation_data, vfiles, flags, cache, group.device)
         xw = predict_csr(off, keys, vals, mk, mw)
+        from ..ops.evalops import auc_histogram
+
         y_all, p_all = y.cpu().numpy(), xw.cpu().numpy()
-        auc.add(y_all, p_all)
+        auc.merge_data(*auc_histogram(y, xw))                    # binned on the device (the host class's default bin width)
     if group.world > 1:
         import torch.distributed as dist
 

@@ -92,7 +92,7 @@ LMCall = Schema("LM.Call", F("cmd", LMCommand, "required"), F("key", PbRange), F
                 F("progress", Progress))   # REPORT_PROGRESS carries the worker's increment
 
 # ---------------------------------------------------------------- neural_network.proto
-LayerType = Enum("LayerConfig.Type", NONE=0, FULLY_CONNECTED=1, DATA=2, LOGISTIC_LOSS=3, AUC=4)
+LayerType = Enum("LayerConfig.Type", NONE=0, FULLY_CONNECTED=1, DATA=2, LOGISTIC_LOSS=3, AUC=4, SPARSE_FULLY_CONNECTED=5)
 ActivationType = Enum("ActivationConfig.Type", IDENTITY=0, SIGMOID=1, LOGISTIC=2, SOFTMAX=3, RELU=4, SCALED_TANH=5)
 ActivationConfig = Schema("ActivationConfig", F("type", ActivationType, "required"))
 LayerConfig = Schema("LayerConfig", F("type", LayerType, "required"), F("name", "string", "required"),

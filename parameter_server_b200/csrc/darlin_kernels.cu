@@ -9,13 +9,18 @@
 //              owner shard's (G,U) accumulators with red.add.v2.f32 over NVLink
 //      ── the rank's last CTA to finish adds 1 to each owner's arrival counter (release, system scope) ──
 //   B  server  on arrival of all workers' CTAs: KKT filter, proximal-Newton step inside the
-//              trust region δ, δ update, accumulators cleared
-//      ── the rank's last CTA to finish adds 1 to each worker's "updated" counter ──
-//   C  worker  m_i += y_i·x_ij·(w_new_j − w_j) over the block's non-zeros, w_new_j loaded from the
-//              owner (peer load); one in-GPU barrier; the worker's own copy of w, δ and the
-//              active set of these columns is brought up to date one phase later, next to the
-//              gradients of the following block (other columns), so a block costs three
-//              synchronisation points, not four
+//              trust region δ, δ update — on the authoritative copy of w in the owner's shard
+//   C  worker  in the SAME phase, on every rank: m_i += y_i·x_ij·Δw_j over the block's non-zeros, where
+//              Δw_j is recomputed from the summed (G_j,U_j) (one 8-byte peer load from the owner) and the
+//              worker's own copy of (w_j, δ_j, active_j).  The step is a pure function of those inputs and
+//              is written with explicitly rounded operations, so every worker gets bit for bit the owner's
+//              Δw: no second cross-GPU round ("weights updated") is needed.
+//      ── one in-GPU barrier ──
+//              The worker's copy of w, δ and the active set of these columns is brought up to date one
+//              phase later, next to the gradients of the following block (other columns); the accumulators
+//              rotate over three buffers and a block's slots are zeroed by the owner one block later, when
+//              every rank has read them for the last time.
+//   A block therefore costs ONE cross-GPU synchronisation and one in-GPU barrier.
 //
 // Arithmetic follows Darling::computeGradients / updateWeight / updateDual
 // (src/linear_method/darling.cc:306-356, 437-477, 358-435).  Instead of
@@ -54,9 +59,9 @@ struct DarlinPeers {
   float* w[PSB_MAX_RANKS];        // owner shard weights (NaN = filtered)
   float2* gu[PSB_MAX_RANKS];      // owner shard (G,U) accumulators
   uint64_t* arrive[PSB_MAX_RANKS];   // on owner o: +1 per worker whose CTAs all finished phase A of a group
-  uint64_t* updated[PSB_MAX_RANKS];  // on worker r: +1 per owner whose CTAs all finished phase B of a group
   int rank, world;
   uint64_t timeout_ns;
+  int64_t gu_stride;                 // float2 elements between the three accumulator buffers of a shard
 };
 
 struct DarlinServer {     // local arrays of this rank's shard
@@ -80,6 +85,10 @@ struct DarlinSched {
   // out-of-core mode: stage_base[q] = device address where the packed [row ids | values] of block
   // order[q] were copied; nullptr = the matrix is resident (Wk.row_idx / Wk.vals hold it all)
   const uint64_t* stage_base;
+  // blocks of the group that ran last before this launch (its accumulators are still to be zeroed), or nullptr
+  const int32_t* prev;
+  int nprev;
+  int pad;
 };
 
 struct DarlinHyper {
@@ -112,18 +121,8 @@ __device__ __forceinline__ void red_add_v2_f32(float2* p, float a, float b) {
 // The notifications go out from `world` threads at once: a release at system scope waits for the
 // thread's earlier remote writes, so one thread sending them one after the other would pay a
 // round trip per rank.
-template <bool kUpdated>
 __device__ __forceinline__ void cta_arrive_all(const DarlinPeers& P, uint64_t* local_ctr, uint64_t local_target,
                                                bool* s_last) {
-#ifdef PSB_DARLIN_FLAT_ARRIVE
-  // one level: every CTA notifies every rank (compile-time alternative, kept for comparisons)
-  __syncthreads();
-  if (threadIdx.x < P.world) {
-    __threadfence_system();
-    red_release_sys_add_u64(kUpdated ? P.updated[threadIdx.x] : P.arrive[threadIdx.x], 1ull);
-  }
-  return;
-#endif
   // With a single rank nothing leaves the GPU and every fence, release and poll stays at GPU scope:
   // system-scope operations issued at every synchronisation point kept host-to-device copies that
   // ran beside the kernel from overlapping with it (out-of-core pass = copy time + kernel time).
@@ -137,7 +136,7 @@ __device__ __forceinline__ void cta_arrive_all(const DarlinPeers& P, uint64_t* l
   }
   __syncthreads();
   if (*s_last && threadIdx.x < P.world) {
-    uint64_t* ctr = kUpdated ? P.updated[threadIdx.x] : P.arrive[threadIdx.x];
+    uint64_t* ctr = P.arrive[threadIdx.x];
     if (multi) {
       __threadfence_system();
       red_release_sys_add_u64(ctr, 1ull);
@@ -237,7 +236,8 @@ __device__ __forceinline__ int64_t find_col_from(const int64_t* col_ptr, int64_t
 
 // ---- phase A: block gradient (G,U) pushed into the owners' accumulators
 __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
-                                                 int64_t lc1, size_t gwarp, size_t nwarps, int lane) {
+                                                 int64_t lc1, int buf, size_t gwarp, size_t nwarps, int lane) {
+  const int64_t boff = (int64_t)buf * P.gu_stride;
   const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
   const bool binary = Wk.vals == nullptr;
   const bool shares = kRangeWalk && Wk.col_of == nullptr;
@@ -284,70 +284,102 @@ __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const D
     const int64_t pj = __shfl_up_sync(0xffffffffu, j, 1);
     const bool head = valid && j >= 0 && (lane == 0 || pj != j);
     if (head) {
-      float2* acc = P.gu[Wk.gowner[j]] + Wk.gslot[j];
+      float2* acc = P.gu[Wk.gowner[j]] + boff + Wk.gslot[j];
       if (P.world > 1) red_add_v2_f32(acc, g, u); else red_add_v2_f32_gpu(acc, g, u);
     }
   }
 }
 
-// ---- phase B: server-side proximal-Newton update of the block's slots
+// The proximal-Newton step of one coordinate inside its trust region (Darling::updateWeight,
+// src/linear_method/darling.cc:437-477): a pure function of the summed (G,U), the weight, the trust
+// region and the pass constants.  The owner applies it to its shard and every worker re-evaluates it
+// for its own copy of the column, so each operation is an explicitly rounded intrinsic: the compiler
+// may not contract or reorder them differently at the different call sites, and all ranks get the
+// same bits.
+struct DarlinStep {
+  float d;       // Δw (0 when the key is dropped)
+  float delta;   // new trust region
+  float vio;     // KKT violation of a zero weight
+  bool drop;     // the KKT filter takes the key out of the active set
+};
+__device__ __forceinline__ DarlinStep darlin_step(float g, float u_sum, float wk, float dl, const DarlinHyper& H) {
+  DarlinStep r;
+  const float u = __fadd_rn(__fdiv_rn(u_sum, H.eta), 1e-10f);
+  const float gp = __fadd_rn(g, H.lambda), gn = __fsub_rn(g, H.lambda);
+  r.d = -wk; r.vio = 0.f; r.drop = false; r.delta = dl;
+  if (wk == 0.f) {
+    if (gp < 0.f) r.vio = -gp;
+    else if (gn > 0.f) r.vio = gn;
+    else if (gp > H.kkt_threshold && gn < -H.kkt_threshold) { r.drop = true; r.d = 0.f; return r; }
+  }
+  const float uw = __fmul_rn(u, wk);
+  if (gp <= uw) r.d = __fdiv_rn(-gp, u);
+  else if (gn >= uw) r.d = __fdiv_rn(-gn, u);
+  r.d = fminf(dl, fmaxf(-dl, r.d));
+  r.delta = fminf(H.delta_max, __fmaf_rn(2.f, fabsf(r.d), 0.1f));
+  return r;
+}
+
+__device__ __forceinline__ float2 ld_gu(const float2* p, bool multi) {
+  float2 v;
+  if (multi) asm volatile("ld.relaxed.sys.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+  else asm volatile("ld.relaxed.gpu.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+// ---- phase B: server-side proximal-Newton update of the block's slots.  `clear`: zero the accumulators
+// right away (the unfused baseline); the fused pass leaves them for the workers and zeroes them a block later.
 __device__ __forceinline__ void darlin_update_weight(const DarlinPeers& P, const DarlinServer& S,
-                                                     const DarlinHyper& H, int64_t s0, int64_t s1, size_t gtid,
-                                                     size_t gsz) {
+                                                     const DarlinHyper& H, int64_t s0, int64_t s1, int buf, bool clear,
+                                                     size_t gtid, size_t gsz) {
   float* w = P.w[P.rank];
-  float2* gu = P.gu[P.rank];
+  float2* gu = P.gu[P.rank] + (int64_t)buf * P.gu_stride;
   float vmax = 0.f;
   for (int64_t k = s0 + (int64_t)gtid; k < s1; k += (int64_t)gsz) {
     const float2 a = __ldcg(gu + k);
-    gu[k] = make_float2(0.f, 0.f);
+    if (clear) gu[k] = make_float2(0.f, 0.f);
     if (!S.active[k]) continue;
-    const float g = a.x, u = a.y / H.eta + 1e-10f;
-    const float gp = g + H.lambda, gn = g - H.lambda;
-    float wk = w[k];
-    float d = -wk, vio = 0.f;
-    if (wk == 0.f) {
-      if (gp < 0.f) vio = -gp;
-      else if (gn > 0.f) vio = gn;
-      else if (gp > H.kkt_threshold && gn < -H.kkt_threshold) {
-        S.active[k] = 0;
-        w[k] = __int_as_float(0x7fffffff);  // NaN sentinel: key filtered
-        continue;
-      }
+    const DarlinStep st = darlin_step(a.x, a.y, w[k], S.delta[k], H);
+    if (st.drop) {
+      S.active[k] = 0;
+      w[k] = __int_as_float(0x7fffffff);  // NaN sentinel: key filtered
+      continue;
     }
-    vmax = fmaxf(vmax, vio);
-    if (gp <= u * wk) d = -gp / u;
-    else if (gn >= u * wk) d = -gn / u;
-    const float dl = S.delta[k];
-    d = fminf(dl, fmaxf(-dl, d));
-    S.delta[k] = fminf(H.delta_max, 2.f * fabsf(d) + 0.1f);
-    w[k] = wk + d;
+    vmax = fmaxf(vmax, st.vio);
+    S.delta[k] = st.delta;
+    w[k] = __fadd_rn(w[k], st.d);
   }
   vmax = warp_max(vmax);
   if ((threadIdx.x & 31) == 0 && vmax > 0.f) atomicMax(S.violation, __float_as_uint(vmax));
 }
 
-// ---- phase C1: pull w_new for the block's local columns, Δw, δ, active set
-__device__ __forceinline__ void darlin_pull(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H,
-                                            int64_t lc0, int64_t lc1, size_t gtid, size_t gsz) {
+// zero the accumulators of a block that every rank has finished reading
+__device__ __forceinline__ void darlin_clear_gu(const DarlinPeers& P, int64_t s0, int64_t s1, int buf, size_t gtid,
+                                                size_t gsz) {
+  float2* gu = P.gu[P.rank] + (int64_t)buf * P.gu_stride;
+  for (int64_t k = s0 + (int64_t)gtid; k < s1; k += (int64_t)gsz) gu[k] = make_float2(0.f, 0.f);
+}
+
+// ---- worker's copy of a block's columns brought up to date (w, δ, active set): the same step as the owner's,
+// from the same sums.  Runs one phase after the block's margin update, when no CTA reads these columns any more.
+__device__ __forceinline__ void darlin_commit(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H,
+                                              int64_t lc0, int64_t lc1, int buf, size_t gtid, size_t gsz) {
+  const int64_t boff = (int64_t)buf * P.gu_stride;
+  const bool multi = P.world > 1;
   for (int64_t j = lc0 + (int64_t)gtid; j < lc1; j += (int64_t)gsz) {
-    float d = 0.f;
-    if (Wk.active[j]) {
-      const float* wsrc = P.w[Wk.gowner[j]] + Wk.gslot[j];
-      const float wn = P.world > 1 ? ld_relaxed_sys_f32(wsrc) : ld_relaxed_gpu_f32(wsrc);
-      if (wn != wn) {
-        Wk.active[j] = 0;
-        Wk.w[j] = 0.f;
-      } else {
-        d = wn - Wk.w[j];
-        Wk.delta[j] = fminf(H.delta_max, 2.f * fabsf(d) + 0.1f);
-        Wk.w[j] = wn;
-      }
+    if (!Wk.active[j]) continue;
+    const float2 a = ld_gu(P.gu[Wk.gowner[j]] + boff + Wk.gslot[j], multi);
+    const DarlinStep st = darlin_step(a.x, a.y, Wk.w[j], Wk.delta[j], H);
+    if (st.drop) {
+      Wk.active[j] = 0;      // its weight is 0 here (NaN only in the owner's shard)
+    } else {
+      Wk.delta[j] = st.delta;
+      Wk.w[j] = __fadd_rn(Wk.w[j], st.d);
     }
-    Wk.dw[j] = d;
   }
 }
 
-// ---- phase C2: m_i += y_i x_ij Δw_j over the block's non-zeros
+// ---- margin update of the unfused baseline: m_i += y_i x_ij Δw_j over the block's non-zeros (Δw in Wk.dw)
 __device__ __forceinline__ void darlin_update_margin(const DarlinWorker& Wk, int64_t lc0, int64_t lc1, size_t gtid,
                                                      size_t gsz) {
   const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
@@ -362,14 +394,16 @@ __device__ __forceinline__ void darlin_update_margin(const DarlinWorker& Wk, int
   }
 }
 
-// ---- fused phase C of the persistent kernel: every non-zero fetches its column's new weight from the
-// owner and the column's old weight from the worker and updates the margin with the difference.  The
-// worker-side column state (w, δ, active) is NOT written here — other CTAs are still reading it — but
-// one phase later by darlin_pull_commit, which saves the barrier between "pull" and "margin update".
-__device__ __forceinline__ void darlin_pull_margin(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
-                                                   int64_t lc1, size_t gtid, size_t gsz) {
+// ---- fused phase C of the persistent kernel: every non-zero fetches its column's summed (G,U) from the
+// owner and the column's state from the worker, re-evaluates the step and moves the margin by y·x·Δw.  The
+// worker-side column state (w, δ, active) is NOT written here — other CTAs are still reading it — but one
+// phase later by darlin_commit.
+__device__ __forceinline__ void darlin_step_margin(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H,
+                                                   int64_t lc0, int64_t lc1, int buf, size_t gtid, size_t gsz) {
   const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
   const int lane = threadIdx.x & 31;
+  const int64_t boff = (int64_t)buf * P.gu_stride;
+  const bool multi = P.world > 1;
   // warp-uniform trip count (gsz is a multiple of 32): the column search without col_of is a warp collective
   const bool shares = kRangeWalk && Wk.col_of == nullptr;
   int64_t base = p0 + (int64_t)gtid - lane, end = p1, step = (int64_t)gsz, hint = -1;
@@ -382,13 +416,12 @@ __device__ __forceinline__ void darlin_pull_margin(const DarlinWorker& Wk, const
                                 : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
     if (shares) hint = __shfl_sync(0xffffffffu, j, 31);
     if (!valid || !Wk.active[j]) continue;
-    const float* wsrc = P.w[Wk.gowner[j]] + Wk.gslot[j];
-    const float wn = P.world > 1 ? ld_relaxed_sys_f32(wsrc) : ld_relaxed_gpu_f32(wsrc);
-    const float d = wn - Wk.w[j];
-    if (wn == wn && d != 0.f) {
+    const float2 a = ld_gu(P.gu[Wk.gowner[j]] + boff + Wk.gslot[j], multi);
+    const DarlinStep st = darlin_step(a.x, a.y, Wk.w[j], Wk.delta[j], H);
+    if (st.d != 0.f) {
       const uint32_t i = Wk.row_idx[e];
       const float v = Wk.vals ? Wk.vals[e] : 1.f;
-      atomicAdd(&Wk.ym[i].y, Wk.ym[i].x * v * d);
+      atomicAdd(&Wk.ym[i].y, Wk.ym[i].x * v * st.d);
     }
   }
 }
@@ -415,17 +448,13 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
   const size_t gsz = (size_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
   const uint64_t G = gridDim.x;
-#ifdef PSB_DARLIN_FLAT_ARRIVE
-  const uint64_t fan = G;    // increments a rank contributes to a cross-GPU counter per synchronisation point
-#else
-  const uint64_t fan = 1;
-#endif
   uint64_t bar = Q.bar0;
 
   // Blocks are processed in groups of Q.group consecutive entries of the order (group = max_block_delay + 1):
   // the gradients of all blocks of a group are computed before any of them is updated, i.e. a block may see
   // weights that are up to `group - 1` block updates old — the bounded-delay schedule of the reference
   // (wait_time = time - tau, src/linear_method/darling.cc:45-69) with one set of synchronisation points per group.
+  // Group number `seq` (counted over all launches, the same on every rank) accumulates into buffer seq % 3.
   const int group = Q.group > 0 ? Q.group : 1;
   uint64_t seq = Q.seq0;
   for (int b = 0; b < Q.nblk; b += group) {
@@ -434,38 +463,47 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
     if (s_abort) break;  // uniform over the CTA
     const int ge = min(b + group, Q.nblk);
     ++seq;
+    const int buf = (int)(seq % 3), pbuf = (int)((seq + 2) % 3);
 
-    // A: gradient + push, then announce arrival at every owner.  In the same phase: commit the pulled
-    // weights of the previous group's columns (a different set of columns; all CTAs are past its phase C).
+    // A: gradient + push, then announce arrival at every owner.  In the same phase: the worker's copy of the
+    // previous group's columns is brought up to date (a different set of columns; all CTAs are past its
+    // phase C; the previous launch did this itself for its last group).
     for (int q = max(b - group, 0); q < b; ++q) {
       const int blk = Q.order[q];
-      darlin_pull(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
+      darlin_commit(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], pbuf, gtid, gsz);
     }
     for (int q = b; q < ge; ++q) {
       const int blk = Q.order[q];
       const int64_t lc0 = Q.blk_lc[2 * blk], lc1 = Q.blk_lc[2 * blk + 1];
-      darlin_grad_push(worker_for(Wk, Q, q, lc0, lc1), P, lc0, lc1, gtid >> 5, gsz >> 5, lane);
+      darlin_grad_push(worker_for(Wk, Q, q, lc0, lc1), P, lc0, lc1, buf, gtid >> 5, gsz >> 5, lane);
     }
-    cta_arrive_all<false>(P, Q.local_bar + 1, seq * G, &s_last);
-    // B: wait for all workers, update this shard's slots of the blocks
-    if (!cta_wait_counter(P.arrive[P.rank], seq * (uint64_t)P.world * fan, P.timeout_ns, P.world > 1, &s_ok)) {
+    cta_arrive_all(P, Q.local_bar + 1, seq * G, &s_last);
+    if (!cta_wait_counter(P.arrive[P.rank], seq * (uint64_t)P.world, P.timeout_ns, P.world > 1, &s_ok)) {
       if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 11); *Q.abort_flag = 1u; }
       break;
     }
+    // B and C in one phase.  Owner: update this shard's slots of the group's blocks; zero the accumulators of
+    // the previous group, which every rank has read for the last time (its arrival above came after that).
     for (int q = b; q < ge; ++q) {
       const int blk = Q.order[q];
-      darlin_update_weight(P, S, H, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], gtid, gsz);
+      darlin_update_weight(P, S, H, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], buf, false, gtid, gsz);
     }
-    cta_arrive_all<true>(P, Q.local_bar + 2, seq * G, &s_last);
-    // C: wait for all owners, pull and apply
-    if (!cta_wait_counter(P.updated[P.rank], seq * (uint64_t)P.world * fan, P.timeout_ns, P.world > 1, &s_ok)) {
-      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 12); *Q.abort_flag = 1u; }
-      break;
+    if (b > 0) {
+      for (int q = max(b - group, 0); q < b; ++q) {
+        const int blk = Q.order[q];
+        darlin_clear_gu(P, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], pbuf, gtid, gsz);
+      }
+    } else if (Q.prev != nullptr) {
+      for (int q = 0; q < Q.nprev; ++q) {
+        const int blk = Q.prev[q];
+        darlin_clear_gu(P, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], pbuf, gtid, gsz);
+      }
     }
+    // Worker: margins of the rows that the group's columns touch.
     for (int q = b; q < ge; ++q) {
       const int blk = Q.order[q];
       const int64_t lc0 = Q.blk_lc[2 * blk], lc1 = Q.blk_lc[2 * blk + 1];
-      darlin_pull_margin(worker_for(Wk, Q, q, lc0, lc1), P, lc0, lc1, gtid, gsz);
+      darlin_step_margin(worker_for(Wk, Q, q, lc0, lc1), P, H, lc0, lc1, buf, gtid, gsz);
     }
     __syncthreads();
     if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
@@ -473,10 +511,10 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 14); *Q.abort_flag = 1u; }
       break;
     }
-    if (ge == Q.nblk) {  // last group of the launch: commit its pulled weights now
+    if (ge == Q.nblk) {  // last group of the launch: bring the worker's copy of its columns up to date now
       for (int q = b; q < ge; ++q) {
         const int blk = Q.order[q];
-        darlin_pull(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], gtid, gsz);
+        darlin_commit(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], buf, gtid, gsz);
       }
     }
   }
@@ -526,7 +564,7 @@ __global__ void k_darlin_grad_local(DarlinWorker Wk, int64_t lc0, int64_t lc1, f
   }
 }
 __global__ void k_darlin_update_weight(DarlinPeers P, DarlinServer S, DarlinHyper H, int64_t s0, int64_t s1) {
-  darlin_update_weight(P, S, H, s0, s1, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+  darlin_update_weight(P, S, H, s0, s1, 0, true, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
 }
 // Δw etc. from an explicit array of new weights (w_new[j − lc0]) instead of peer loads
 __global__ void k_darlin_apply_pull(DarlinWorker Wk, DarlinHyper H, int64_t lc0, int64_t lc1, const float* w_new) {
@@ -575,8 +613,7 @@ int psb_darlin_grid() {
     int per_sm = 0, sms = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, darlin_pass_kernel, 512, 0);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int want = 2;  // CTAs per SM (upper bound of the grid; the solver launches 1 per SM when every block synchronises): more CTAs hide gather latency, fewer make the per-block barriers cheaper
-    if (const char* e = getenv("PSB_DARLIN_CTAS_PER_SM")) want = atoi(e) > 0 ? atoi(e) : want;
+    const int want = 2;  // CTAs per SM (upper bound of the grid; the solver launches 1 per SM when every block synchronises): more CTAs hide gather latency, fewer make the per-block barriers cheaper
     g_darlin_grid[dev] = sms * (per_sm > want ? want : per_sm);  // upper bound; callers may launch fewer
   }
   return g_darlin_grid[dev];
@@ -706,6 +743,10 @@ int psb_darlin_pass_streamed(void* handle, const DarlinWorker* Wk, const DarlinP
     q.seq0 = Q0->seq0 + (uint64_t)(first / grp);
     q.bar0 = Q0->bar0 + (uint64_t)(first / grp);
     q.stage_base = stage_base_dev + first;
+    if (first > 0) {   // the group that ran last before this launch: the last `grp` blocks of the previous batch
+      q.prev = Q0->order + first - grp;
+      q.nprev = grp;
+    }
     w.vals = has_vals ? reinterpret_cast<const float*>(stage[s]) : nullptr;  // only null / non-null matters
     void* args[] = {&w, &p, &sv, &q, &hy};
     e = cudaLaunchCooperativeKernel((void*)darlin_pass_kernel, dim3(grid), dim3(512), args, 0, compute);

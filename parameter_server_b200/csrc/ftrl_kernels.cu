@@ -229,7 +229,7 @@ __device__ __forceinline__ void phase_localize(const FtrlPeers& P, const Minibat
       uint32_t slot = (uint32_t)h0;
       if (cur0 != key0) {
         bool inserted = false;
-        const uint64_t s = table_find_or_insert(L.lt_keys, ~0ull, cmask, h0, key0, P.max_probe, &inserted);
+        const uint64_t s = table_find_or_insert(L.lt_keys, ~0ull, cmask, h0, key0, P.max_probe, &inserted, &cur0);
         if (s == ~0ull) {
           set_status(L.status, kLocalTableFull, 0, 0);
           slot = kBadSlot;
@@ -242,8 +242,10 @@ __device__ __forceinline__ void phase_localize(const FtrlPeers& P, const Minibat
       key0 = key1; h0 = h1; cur0 = cur1; key1 = key2;
     }
   }
+#ifndef PSB_NO_FRESH
   fresh = __reduce_add_sync(0xffffffffu, fresh);
   if ((threadIdx.x & 31) == 0 && fresh) atomicAdd(&L.stats[5], (double)fresh);
+#endif
 }
 
 // ---- shard table probes (owner side, this GPU's own memory)
@@ -434,17 +436,18 @@ __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratc
         sls[k] = i < e ? PSB_LD_U32(L.slot_of + i, pol) : kBadSlot;
         x[k] = (M.vals != nullptr && i < e) ? PSB_LD_F32(M.vals + i, pol) : 1.f;
       }
+      // the cache tags of all the lane's non-zeros first: their shared-memory loads overlap
+      uint32_t tag[kRowBatch];
+#pragma unroll
+      for (int k = 0; k < kRowBatch; ++k)
+        tag[k] = sls[k] != kBadSlot ? hc->slot[(sls[k] * 2654435761u) >> (32 - PSB_HOT_LOG2)] : 0u;
 #pragma unroll
       for (int k = 0; k < kRowBatch; ++k) {
         const uint32_t sl = sls[k];
         if (sl == kBadSlot) continue;
         const float gv = c * x[k];
         const int h = (int)((sl * 2654435761u) >> (32 - PSB_HOT_LOG2));  // top bits
-        uint32_t cur = hc->slot[h];
-        if (cur == kBadSlot) {
-          const uint32_t prev = atomicCAS(&hc->slot[h], kBadSlot, sl);
-          cur = prev == kBadSlot ? sl : prev;
-        }
+        uint32_t cur = tag[k];
         if (cur == sl) {
           atomicAdd(&hc->g[h], gv);
           if (kCounts) atomicAdd(&hc->cnt[h], inc);
@@ -725,7 +728,9 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
   PSB_TRACE(L, gtid, 5);
   if (blockIdx.x == 0 && threadIdx.x < world && world > 1)
     st_release_sys_u64(P.grads[threadIdx.x] + P.rank, (uint64_t)seq << 32);
+#ifndef PSB_RESET_AT_END
   phase_reset_tables<kCounts>(L, gtid, gsz);
+#endif
   PSB_TRACE(L, gtid, 6);
   {
     ApplyAcc acc;
@@ -736,6 +741,9 @@ ftrl_push_update_kernel(FtrlPeers P, Minibatch M, LocalScratch L, FtrlHyper H, u
     }
     apply_flush(acc, L.stats);
   }
+#ifdef PSB_RESET_AT_END
+  phase_reset_tables<kCounts>(L, gtid, gsz);
+#endif
   PSB_TRACE(L, gtid, 8);
 }
 

@@ -27,7 +27,7 @@ extern "C" int psb_reduce_sum_static(const float* x, size_t n, int op, double* o
                  (unsigned long long)PSB_REDUCE_STATIC_MAX_ELEMS);
     return (int)cudaErrorInvalidValue;
   }
-  if (op < 0 || op > 3 || out == nullptr || (x == nullptr && n != 0)) {
+  if (op < 0 || op > 4 || out == nullptr || (x == nullptr && n != 0)) {
     std::fprintf(stderr, "psb_reduce_sum_static: invalid argument (op = %d)\n", op);
     return (int)cudaErrorInvalidValue;
   }

@@ -28,7 +28,7 @@ extern "C" {
 
 // out[0] = Σ term_op(x[i]) for i < n, accumulated in fp64 in a fixed order.
 //   x      device pointer, n floats (caller-owned input)
-//   op     0 Σlog(1+1/x)  1 Σ|x| over finite non-zero x  2 #{x != 0, not NaN}  3 Σlog(1+e^-x)
+//   op     0 Σlog(1+1/x)  1 Σ|x| over finite non-zero x  2 #{x != 0, not NaN}  3 Σlog(1+e^-x)  4 Σmax(0,1-x)²
 //   out    device pointer to one double (caller-owned output)
 //   stream stream to launch on
 // Returns 0 or a cudaError_t value.

@@ -15,7 +15,7 @@ size_t psb_reduce_scratch_bytes() { return kReduceScratchBytes; }
 
 int psb_reduce_sum(const float* x, size_t n, int op, void* scratch, size_t scratch_bytes, double* out,
                    cudaStream_t stream) {
-  if (scratch_bytes < kReduceScratchBytes || op < 0 || op > 3) return (int)cudaErrorInvalidValue;
+  if (scratch_bytes < kReduceScratchBytes || op < 0 || op > 4) return (int)cudaErrorInvalidValue;
   double* partial = reinterpret_cast<double*>(scratch);
   unsigned* ticket = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(scratch) + 8 * (size_t)kReduceMaxBlocks);
   reduce_sum_kernel<<<reduce_grid(n), kReduceThreads, 0, stream>>>(x, n, op, partial, ticket, out);

@@ -20,6 +20,7 @@ enum ReduceOp : int {
   kSumAbs = 1,        // Σ |x_i| over finite, non-zero x (λ₁ penalty; NaN = filtered key)
   kCountNonZero = 2,  // #{i : x_i != 0 and x_i is not NaN}
   kSumLogistic = 3,   // Σ log(1 + exp(-x_i))  logistic loss from margins y_i·Xw_i
+  kSumSquareHinge = 4,  // Σ max(0, 1 − x_i)²   square hinge loss from margins (src/linear_method/loss.h:97-99)
 };
 
 __device__ __forceinline__ double reduce_term(int op, float x) {
@@ -27,6 +28,7 @@ __device__ __forceinline__ double reduce_term(int op, float x) {
     case kSumLog1pInv: return log1p(1.0 / (double)x);
     case kSumAbs: return (x == x && x != 0.f) ? fabs((double)x) : 0.0;
     case kCountNonZero: return (x == x && x != 0.f) ? 1.0 : 0.0;
+    case kSumSquareHinge: { const double t = 1.0 - (double)x; return t > 0 ? t * t : 0.0; }
     default: { const double m = -(double)x; return m > 0 ? m + log1p(exp(-m)) : log1p(exp(m)); }
   }
 }

@@ -249,6 +249,36 @@ __global__ void k_set_intersect_flags(const uint64_t* __restrict__ a, size_t na,
     flag[i] = (lo < nb && b[lo] == k) ? 1u : 0u;
   }
 }
+// Sorted union of two sorted key sets without a sort (SArray::setUnion, src/base/shared_array_inl.h:146-171),
+// merge by ranking: an element of `a` lands at its own index plus the number of kept elements of `b` below it,
+// a kept element of `b` (one that `a` lacks; `b_pos` = how many kept ones precede it) at b_pos plus the number
+// of elements of `a` below it.  Every output position is written exactly once.
+__global__ void k_merge_union(const uint64_t* __restrict__ a, size_t na, const uint64_t* __restrict__ b, size_t nb,
+                              const uint32_t* __restrict__ b_dup, const unsigned long long* __restrict__ b_pos,
+                              uint64_t* __restrict__ out) {
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < na + nb; t += (size_t)gridDim.x * blockDim.x) {
+    if (t < na) {
+      const uint64_t k = a[t];
+      size_t lo = 0, hi = nb;
+      while (lo < hi) { const size_t mid = (lo + hi) >> 1; if (b[mid] < k) lo = mid + 1; else hi = mid; }
+      // kept elements of b below k = (elements of b below k) − (duplicates among them) = b_pos at lo, where
+      // b_pos counts the kept ones before an index (b_pos[nb] is not stored: all of b is below k then)
+      const size_t kept_below = lo < nb ? (size_t)b_pos[lo] : (nb ? (size_t)b_pos[nb - 1] + (b_dup[nb - 1] ? 0 : 1) : 0);
+      out[t + kept_below] = k;
+    } else {
+      const size_t j = t - na;
+      if (b_dup[j]) continue;
+      const uint64_t k = b[j];
+      size_t lo = 0, hi = na;
+      while (lo < hi) { const size_t mid = (lo + hi) >> 1; if (a[mid] < k) lo = mid + 1; else hi = mid; }
+      out[(size_t)b_pos[j] + lo] = k;
+    }
+  }
+}
+// flag[i] = 1 − in[i]  (elements of b that a lacks, from the intersection flags)
+__global__ void k_invert_flags(const uint32_t* __restrict__ in, size_t n, uint32_t* __restrict__ out) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = in[i] ? 0u : 1u;
+}
 __global__ void k_compact_u64(const uint64_t* __restrict__ in, const uint32_t* __restrict__ flag, const unsigned long long* __restrict__ pos, size_t n,
                               uint64_t* __restrict__ out) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -353,6 +383,15 @@ int psb_fill_gaussian(float* x, size_t n, float mean, float std, uint64_t seed, 
 }
 int psb_set_intersect_flags(const uint64_t* a, size_t na, const uint64_t* b, size_t nb, uint32_t* flag, cudaStream_t s) {
   k_set_intersect_flags<<<g1(na), 256, 0, s>>>(a, na, b, nb, flag);
+  return (int)cudaGetLastError();
+}
+int psb_merge_union(const uint64_t* a, size_t na, const uint64_t* b, size_t nb, const uint32_t* b_dup, const unsigned long long* b_pos,
+                    uint64_t* out, cudaStream_t s) {
+  k_merge_union<<<g1(na + nb), 256, 0, s>>>(a, na, b, nb, b_dup, b_pos, out);
+  return (int)cudaGetLastError();
+}
+int psb_invert_flags(const uint32_t* in, size_t n, uint32_t* out, cudaStream_t s) {
+  k_invert_flags<<<g1(n), 256, 0, s>>>(in, n, out);
   return (int)cudaGetLastError();
 }
 int psb_compact_u64(const uint64_t* in, const uint32_t* flag, const unsigned long long* pos, size_t n, uint64_t* out, cudaStream_t s) {

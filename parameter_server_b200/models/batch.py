@@ -7,11 +7,16 @@ gradient and the diagonal Hessian over the workers and let the learner update th
 (src/linear_method/learner/proximal_gradient.h:20-53, gradient_descent.h:19-24,
 src/linear_method/loss.h:73-104, src/linear_method/penalty.h:15-50,
 src/test/aggregated_gradient_test.cc:52-104).  Here it is implemented: rows are sharded over the
-ranks, every rank keeps the whole weight vector, and the block gradients are summed with an
-all-reduce.  The arithmetic is torch on the device; the hot, fused path of this framework is DARLIN.
+ranks, every rank keeps the whole weight vector, the per-block work runs in the kernels of
+``csrc/batch_kernels.cu`` (block gradient and curvature for the logistic and the square hinge loss,
+learner update, margin update; preprocessing with the sort / unique / remap / bucket kernels of
+``ops.sparse``), and the block's (G,U) sums of the ranks are added with an NCCL all-reduce — this
+solver is the simple replicated-weights counterpart of DARLIN, whose pass kernel carries the
+product path over peer memory.
 """
 from __future__ import annotations
 
+import ctypes as C
 import math
 import sys
 import time
@@ -20,10 +25,20 @@ from typing import List
 import numpy as np
 import torch
 
+from ..ops import _native as N
+from ..ops import sparse
+from ..ops.reduce import reduce_sum
 from ..parallel.peer import PeerGroup
 from .darlin import DarlinConfig, Progress, block_order, print_progress
 
 _SIGN = -(1 << 63)
+LOSS_KIND = {"LOGIT": 0, "SQUARE_HINGE": 1}
+LEARNER_KIND = {"PROXIMAL_GRADIENT": 0, "GRADIENT_DESCENT": 1}
+
+
+class BatchShard(C.Structure):
+    _fields_ = [("col_ptr", C.c_void_p), ("row_idx", C.c_void_p), ("vals", C.c_void_p), ("col_of", C.c_void_p),
+                ("ym", C.c_void_p)]
 
 
 # ------------------------------------------------------------------ loss / penalty families
@@ -77,79 +92,79 @@ class ProxGradientSolver:
     def __init__(self, group: PeerGroup, cfg: DarlinConfig, loss: str = "LOGIT", penalty: str = "L1",
                  learner: str = "PROXIMAL_GRADIENT"):
         self.group, self.cfg, self.dev = group, cfg, group.device
-        self.loss, self.penalty = Loss.create(loss), Penalty.create(penalty, cfg.lambda1)
+        self.loss_name, self.penalty = loss, Penalty.create(penalty, cfg.lambda1)
         self.learner = learner
         self.progress: List[Progress] = []
+        self._lib = N.lib()
+        self.kernel_launches = 0
 
     def preprocess(self, offsets, keys, vals, y) -> None:
         import torch.distributed as dist
 
         g, dev = self.group, self.dev
-        uk = torch.unique(keys ^ _SIGN)
+        lkeys, _ = sparse.count_unique(keys.contiguous())          # this rank's unique keys, unsigned order
+        uk = lkeys
         if g.world > 1:
             sizes = [None] * g.world
-            dist.all_gather_object(sizes, int(uk.numel()), group=g.group)
-            pad = torch.full((max(sizes),), (1 << 63) - 1, dtype=torch.int64, device=dev)
-            pad[: uk.numel()] = uk
+            dist.all_gather_object(sizes, int(lkeys.numel()), group=g.group)
+            pad = torch.full((max(sizes),), -1, dtype=torch.int64, device=dev)
+            pad[: lkeys.numel()] = lkeys
             parts = [torch.empty_like(pad) for _ in range(g.world)]
             dist.all_gather(parts, pad, group=g.group)
-            uk = torch.unique(torch.cat([p[:n] for p, n in zip(parts, sizes)]))
-        self.gkeys = uk                      # ordered (sign-flipped) global keys
-        col = torch.searchsorted(uk, keys ^ _SIGN)
-        rows = y.numel()
-        row_of = torch.repeat_interleave(torch.arange(rows, device=dev), offsets[1:] - offsets[:-1])
-        order = torch.sort(col, stable=True).indices
-        self.col, self.row = col[order], row_of[order]
-        self.val = torch.ones_like(self.col, dtype=torch.float32) if vals is None else vals[order]
-        P = uk.numel()
-        self.col_ptr = torch.zeros(P + 1, dtype=torch.int64, device=dev)
-        self.col_ptr[1:] = torch.bincount(self.col, minlength=P).cumsum(0)
-        self.y, self.w = y, torch.zeros(P, device=dev)
-        self.xw = torch.zeros(rows, device=dev)
+            uk = sparse.set_union_many([p[:n] for p, n in zip(parts, sizes)])                # union of all ranks' keys
+        self.gkeys = uk ^ _SIGN              # ordered (sign-flipped) global keys
+        P, rows = uk.numel(), y.numel()
+        col = sparse.remap(keys.contiguous(), uk)                  # global column of every non-zero
+        self.col_ptr, self.row_idx, self.val = sparse.csr_to_csc(offsets, col, vals, P)
+        self.col_of = torch.repeat_interleave(torch.arange(P, dtype=torch.int32, device=dev),
+                                              self.col_ptr[1:] - self.col_ptr[:-1]).contiguous()
+        self.ym = torch.stack([y.to(torch.float32), torch.zeros(rows, dtype=torch.float32, device=dev)], 1).contiguous()
+        self.margin = self.ym[:, 1]
+        self.w = torch.zeros(P, device=dev)
+        self._D = BatchShard(self.col_ptr.data_ptr(), self.row_idx.data_ptr(), 0 if self.val is None else self.val.data_ptr(),
+                             self.col_of.data_ptr(), self.ym.data_ptr())
         tot = g.all_reduce_sum([rows, keys.numel()])
         self.total_rows = int(tot[0])
         per_row = tot[1] / max(tot[0], 1)
         r = self.cfg.feature_block_ratio
         self.nblk = max(int(math.ceil(per_row * r)), 1) if (per_row > 1 + 1e-6 and r > 0) else 1
-        kmin, kmax = int(uk[0].item()) - _SIGN, int(uk[-1].item()) - _SIGN + 1
+        kmin, kmax = int(self.gkeys[0].item()) - _SIGN, int(self.gkeys[-1].item()) - _SIGN + 1
         bounds = [kmin + (kmax - kmin) * i // self.nblk for i in range(self.nblk)] + [kmax]
         b = torch.tensor([min(x, (1 << 64) - 1) + _SIGN for x in bounds], dtype=torch.int64, device=dev)
-        c = torch.searchsorted(uk, b)
+        c = torch.searchsorted(self.gkeys, b)
         c[-1] = P
         self.blk = c.tolist()
+        self.blk_nnz = self.col_ptr[c].tolist()
+        widest = max((self.blk[i + 1] - self.blk[i] for i in range(self.nblk)), default=1)
+        self._gu = torch.zeros((max(widest, 1), 2), dtype=torch.float32, device=dev)
+        self._d = torch.zeros((max(widest, 1),), dtype=torch.float32, device=dev)
 
     def run_block(self, b: int) -> None:
         c0, c1 = self.blk[b], self.blk[b + 1]
         if c1 <= c0:
             return
-        p0, p1 = int(self.col_ptr[c0]), int(self.col_ptr[c1])
-        rows, cols, v = self.row[p0:p1], self.col[p0:p1] - c0, self.val[p0:p1]
-        gcoef, hcoef = self.loss.coef(self.y, self.xw)
-        gu = torch.zeros((c1 - c0, 2), device=self.dev)
-        gu[:, 0].index_add_(0, cols, gcoef[rows] * v)
-        gu[:, 1].index_add_(0, cols, hcoef[rows] * v * v)
+        lib, s = self._lib, N.stream_ptr()
+        nnz_b = self.blk_nnz[b + 1] - self.blk_nnz[b]
+        gu = self._gu[: c1 - c0]
+        gu.zero_()
+        if nnz_b:
+            N.check(lib.psb_batch_block_grad(C.byref(self._D), LOSS_KIND[self.loss_name], C.c_int64(c0), C.c_int64(c1), N.ptr(gu),
+                                             C.c_int64(nnz_b), s), "batch_block_grad")
         if self.group.world > 1:
             import torch.distributed as dist
 
             dist.all_reduce(gu, group=self.group.group)
-        G, U = gu[:, 0], gu[:, 1]
-        w = self.w[c0:c1]
-        eta, lam = self.cfg.eta, self.cfg.lambda1
-        if self.learner == "GRADIENT_DESCENT":
-            g = G + (2 * lam * w if self.penalty.p == 2 else 0.0)
-            d = -eta * g
-        elif self.penalty.p == 1:
-            u = U / eta + 1e-10
-            gp, gn = G + lam, G - lam
-            d = torch.where(gp <= u * w, -gp / u, torch.where(gn >= u * w, -gn / u, -w)).clamp_(-5.0, 5.0)
-        else:
-            u = U / eta + 2 * lam + 1e-10
-            d = (-(G + 2 * lam * w) / u).clamp_(-5.0, 5.0)
-        self.w[c0:c1] = w + d
-        self.xw.index_add_(0, rows, v * d[cols])
+        N.check(lib.psb_batch_block_update(N.ptr(gu), N.ptr(self.w[c0:c1]), N.ptr(self._d), C.c_int64(c1 - c0),
+                                           LEARNER_KIND[self.learner], self.penalty.p, C.c_float(self.cfg.eta),
+                                           C.c_float(self.cfg.lambda1), s), "batch_block_update")
+        if nnz_b:
+            N.check(lib.psb_batch_block_margin(C.byref(self._D), C.c_int64(c0), C.c_int64(c1), N.ptr(self._d), C.c_int64(nnz_b), s),
+                    "batch_block_margin")
+        self.kernel_launches += 3 if nnz_b else 1
 
     def evaluate(self):
-        loss = self.loss.evaluate(self.y, self.xw)
+        op = "sum_logistic" if self.loss_name == "LOGIT" else "sum_square_hinge"
+        loss = reduce_sum(self.margin.contiguous(), op).clone()
         if self.group.world > 1:
             import torch.distributed as dist
 

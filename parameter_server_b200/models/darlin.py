@@ -56,6 +56,45 @@ class DarlinConfig:
     tail_feature_freq: int = 0
     countmin_k: int = 2
     countmin_n_ratio: float = 2.0
+    # Feature groups (src/linear_method/batch_solver.cc:48-66): with feature_group_bits = b > 0 the top b bits
+    # of a key are its group (TERAFEA keys: b = 10); every group is cut into ceil(its non-zeros per row x
+    # feature_block_ratio) blocks over its own key range.  0 = all keys form one group.
+    feature_group_bits: int = 0
+    # blocks of these groups are swept num_iter_for_prior_fea_group times at the start of the first pass, with
+    # zero delay (src/linear_method/batch_solver.cc:88-108, src/linear_method/darling.cc:48-50)
+    prior_fea_group: tuple = ()
+    num_iter_for_prior_fea_group: int = 5
+
+
+def group_blocks(groups, ratio: float):
+    """Feature blocks of the reference's partition rule: ``groups`` = [(id, min_key, max_key_excl, nnz_ele, nnz_ex)],
+    result = [(id, begin_key, end_key_excl)] with every group cut into n even key ranges, n = ceil(non-zeros per
+    example x ratio) when a group has more than one non-zero per example, else 1; empty ranges are left out."""
+    out = []
+    for gid, lo, hi, nnz_ele, nnz_ex in groups:
+        if hi <= lo or nnz_ex <= 0:
+            continue
+        per_row = nnz_ele / nnz_ex
+        n = max(int(math.ceil(per_row * ratio)), 1) if per_row > 1 + 1e-6 and ratio > 0 else 1
+        size = hi - lo
+        for i in range(n):
+            b, e = lo + size * i // n, lo + size * (i + 1) // n
+            if e > b:
+                out.append((gid, b, e))
+    return out
+
+
+def prior_block_order(block_groups, prior_groups, n_iter: int, random_order: bool, seed: int) -> List[int]:
+    """Order of the extra sweeps over the blocks of the important groups (first pass only)."""
+    rng = np.random.RandomState(seed + 1)
+    out: List[int] = []
+    for g in prior_groups:
+        tmp = [k for k, bg in enumerate(block_groups) if bg == int(g)]
+        for _ in range(int(n_iter) if tmp else 0):
+            if random_order:
+                rng.shuffle(tmp)
+            out += list(tmp)
+    return out
 
 
 @dataclass
@@ -177,6 +216,36 @@ class DarlinSolver:
         self.tail_filter_stats = {"features": P, "dropped": P - int(keep.sum().item()), "sketch_width": width}
         return new_off, keys[sel].contiguous(), None if vals is None else vals[sel].contiguous()
 
+    def _group_info(self, offsets: torch.Tensor, keys: torch.Tensor, lkeys: torch.Tensor):
+        """Per feature group (top ``feature_group_bits`` bits of the key): (id, min_key, max_key + 1, non-zeros,
+        examples that have the group), summed / merged over all ranks — the slot statistics of the reference's
+        ExampleInfo (src/proto/example.proto, merged in src/data/common.cc).  Collective."""
+        import torch.distributed as dist
+
+        dev, bits = self.dev, int(self.cfg.feature_group_bits)
+        G, shift = 1 << bits, 64 - bits
+        gid = (keys >> shift) & (G - 1)
+        nnz_ele = torch.bincount(gid, minlength=G).to(torch.float64)
+        rows = offsets.numel() - 1
+        row_of = torch.repeat_interleave(torch.arange(rows, device=dev), offsets[1:] - offsets[:-1])
+        pairs = torch.unique(row_of * G + gid)                    # one entry per (example, group) that occurs
+        nnz_ex = torch.bincount(pairs % G, minlength=G).to(torch.float64)
+        lg = (lkeys >> shift) & (G - 1)                           # group of every unique local key (ascending keys)
+        big = (1 << 62)
+        kmin = torch.full((G,), big, dtype=torch.int64, device=dev).scatter_reduce_(0, lg, _ukey(lkeys), "amin")
+        kmax = torch.full((G,), -big, dtype=torch.int64, device=dev).scatter_reduce_(0, lg, _ukey(lkeys), "amax")
+        if self.group.world > 1:
+            cnt = torch.stack([nnz_ele, nnz_ex])
+            dist.all_reduce(cnt, group=self.group.group)
+            nnz_ele, nnz_ex = cnt[0], cnt[1]
+            dist.all_reduce(kmin, op=dist.ReduceOp.MIN, group=self.group.group)
+            dist.all_reduce(kmax, op=dist.ReduceOp.MAX, group=self.group.group)
+        out = []
+        for g in torch.nonzero(nnz_ele > 0).flatten().tolist():
+            out.append((g, int(kmin[g].item()) - _SIGN, int(kmax[g].item()) - _SIGN + 1, float(nnz_ele[g].item()),
+                        float(nnz_ex[g].item())))
+        return out
+
     def preprocess(self, offsets: torch.Tensor, keys: torch.Tensor, vals: Optional[torch.Tensor], y: torch.Tensor):
         """Localise this rank's CSR rows shard, exchange key sets with the servers, build the CSC blocks.
 
@@ -220,7 +289,8 @@ class DarlinSolver:
             pad[:P] = uk
             allk = [torch.empty_like(pad) for _ in range(W)]
             dist.all_gather(allk, pad, group=g.group)
-            gk = torch.unique(torch.cat([a[:n] for a, n in zip(allk, sizes)]))
+            # union of the workers' sorted key sets by ranking (bit patterns: unsigned order)
+            gk = _ukey(sparse.set_union_many([_ukey(a[:n]) for a, n in zip(allk, sizes)]))
         else:
             gk = uk
         self.gkeys_sorted = gk                                     # ordered (sign-flipped) global keys
@@ -236,21 +306,25 @@ class DarlinSolver:
         gidx = torch.searchsorted(gk, uk)
         owner = (torch.searchsorted(shard_begin, gidx, right=True) - 1).clamp_(0, W - 1)
         gslot = gidx - shard_begin[owner]
-        # feature blocks: even key sub-ranges of [min_key, max_key)  (batch_solver.cc:55-65)
-        nnz_per_row = self.total_nnz / max(self.total_rows, 1)
-        nblk = max(int(math.ceil(nnz_per_row * self.cfg.feature_block_ratio)), 1) if nnz_per_row > 1 + 1e-6 else 1
-        span = self.key_max - self.key_min
-        bounds = [self.key_min + span * i // nblk for i in range(nblk)] + [self.key_max]
-        self.block_keys = [(bounds[i], bounds[i + 1]) for i in range(nblk)]
-        b_s = torch.tensor([min(b, (1 << 64) - 1) + _SIGN for b in bounds],
-                           dtype=torch.int64, device=dev)
-        lc = torch.searchsorted(uk, b_s)
-        gc = torch.searchsorted(gk, b_s)
-        lc[-1] = P
-        gc[-1] = gk.numel()
-        sl = (gc - self.shard_begin[r]).clamp_(0, self.slots)
-        self.blk_lc = torch.stack([lc[:-1], lc[1:]], 1).contiguous()
-        self.blk_sl = torch.stack([sl[:-1], sl[1:]], 1).contiguous()
+        # feature blocks (batch_solver.cc:48-66): every feature group is cut into even key sub-ranges of its own
+        # key range; without groups all keys form one group over [min_key, max_key)
+        groups = self._group_info(offsets, keys, lkeys) if self.cfg.feature_group_bits > 0 else \
+            [(1, self.key_min, self.key_max, self.total_nnz, self.total_rows)]
+        blocks = group_blocks(groups, self.cfg.feature_block_ratio)
+        if not blocks:
+            blocks = [(1, self.key_min, self.key_max)]
+        nblk = len(blocks)
+        self.block_group = [g for g, _, _ in blocks]
+        self.block_keys = [(b, e) for _, b, e in blocks]
+        to_s = lambda ks: torch.tensor([min(k, (1 << 64) - 1) + _SIGN for k in ks], dtype=torch.int64, device=dev)
+        b_lo, b_hi = to_s([b for b, _ in self.block_keys]), to_s([e for _, e in self.block_keys])
+        top = torch.tensor([e >= (1 << 64) for _, e in self.block_keys], device=dev)     # a range that ends at 2^64
+        lc0, lc1 = torch.searchsorted(uk, b_lo), torch.where(top, P, torch.searchsorted(uk, b_hi))
+        gc0, gc1 = torch.searchsorted(gk, b_lo), torch.where(top, gk.numel(), torch.searchsorted(gk, b_hi))
+        sl0 = (gc0 - self.shard_begin[r]).clamp_(0, self.slots)
+        sl1 = (gc1 - self.shard_begin[r]).clamp_(0, self.slots)
+        self.blk_lc = torch.stack([lc0, lc1], 1).contiguous()
+        self.blk_sl = torch.stack([sl0, sl1], 1).contiguous()
         self.nblk = nblk
         # ---- worker state
         f32 = torch.float32
@@ -260,12 +334,9 @@ class DarlinSolver:
         # label and margin of a row share 8 bytes: every non-zero gathers them with one access
         self.ym = torch.stack([y.to(f32), torch.zeros(rows, dtype=f32, device=dev)], 1).contiguous()
         self.margin = self.ym[:, 1]
-        # column id of every non-zero (saves a binary search per non-zero and phase); not kept in out-of-core
+        # column id of every non-zero (saves a column search per non-zero and phase); not kept in out-of-core
         # mode, where it would add 50 % to the bytes streamed from the host
-        # (PSB_DARLIN_NO_COL_OF=1 drops it for resident data too: isolates the cost of the in-kernel column search)
-        import os
-
-        self.col_of = None if self.out_of_core or os.environ.get("PSB_DARLIN_NO_COL_OF") == "1" else torch.repeat_interleave(
+        self.col_of = None if self.out_of_core else torch.repeat_interleave(
             torch.arange(P, dtype=torch.int32, device=dev), col_ptr[1:] - col_ptr[:-1]).contiguous()
         self.w = torch.zeros(P, dtype=f32, device=dev)
         self.delta = torch.full((P,), self.cfg.delta_init, dtype=f32, device=dev)
@@ -276,9 +347,12 @@ class DarlinSolver:
         # ---- server state (peer-addressable weights and accumulators)
         cap = max(max_slots, 1)
         self.srv_w = g.alloc((cap,), f32)
-        self.srv_gu = g.alloc((cap, 2), f32)
+        # (G,U) accumulators, three buffers in rotation: a group of blocks sums into one while the previous
+        # group's sums are still being read and the one before that is being zeroed
+        self.srv_gu = g.alloc((3, cap, 2), f32)
+        self._gu_stride = cap
+        self._prev_tail = None          # blocks of the group that ran last (their accumulators are zeroed next)
         self.arrive = g.alloc((1,), torch.int64)
-        self.updated = g.alloc((1,), torch.int64)
         self.srv_delta = torch.full((cap,), self.cfg.delta_init, dtype=f32, device=dev)
         self.srv_active = torch.ones(cap, dtype=torch.uint8, device=dev)
         self.violation = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -311,6 +385,14 @@ class DarlinSolver:
         if self._blocks_per_launch_arg is None and len(self.blk_nnz):
             avg_bytes = max(float((self.blk_nnz[:, 1] - self.blk_nnz[:, 0]).mean()) * 4 * words, 1.0)
             self.blocks_per_launch = self._round_launch(min(16, max(1, int(24e6 // avg_bytes))))
+        if self.group.world > 1:
+            # every launch of the pass kernel synchronises with the other ranks' launches group by group, so all
+            # ranks cut the block order into the same batches
+            import torch.distributed as dist
+
+            t = torch.tensor([self.blocks_per_launch], dtype=torch.int64, device=self.dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group.group)
+            self.blocks_per_launch = self._round_launch(int(t.item()))
         d = min(self.prefetch_depth, 16)
         # a ring slot holds one launch's worth of blocks; stage_base gets every block's address for the kernel
         self.stage = [torch.empty(cap * words * self.blocks_per_launch, dtype=torch.int32, device=self.dev)
@@ -345,8 +427,7 @@ class DarlinSolver:
         H = self._hyper()
         order_h = np.ascontiguousarray(order, dtype=np.int32)
         group = max(int(self.cfg.max_block_delay), 0) + 1
-        Q = N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), n, group, self.seq,
-                          self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr())
+        Q = self._sched(order_t, n, group)
         moved, launches = C.c_ulonglong(0), C.c_int(0)
         N.check(self._lib.psb_darlin_pass_streamed(
             self._streamer, C.byref(self._Wk), C.byref(self._P), C.byref(self._S), C.byref(Q), C.byref(H), self.grid,
@@ -360,6 +441,13 @@ class DarlinSolver:
         ngroups = sum((min(self.blocks_per_launch, n - f) + group - 1) // group for f in range(0, n, self.blocks_per_launch))
         self.seq += ngroups
         self.bar += ngroups
+        self._prev_tail = order_t[(n - 1) // group * group:]
+
+    def _sched(self, order_t: torch.Tensor, n: int, group: int) -> N.DarlinSched:
+        prev = self._prev_tail
+        return N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), n, group, self.seq,
+                             self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr(), None,
+                             None if prev is None else prev.data_ptr(), 0 if prev is None else prev.numel(), 0)
 
     def _build_structs(self):
         Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),
@@ -370,8 +458,9 @@ class DarlinSolver:
         P = N.DarlinPeers()
         for r in range(self.group.world):
             P.w[r], P.gu[r] = self.srv_w.ptrs[r], self.srv_gu.ptrs[r]
-            P.arrive[r], P.updated[r] = self.arrive.ptrs[r], self.updated.ptrs[r]
+            P.arrive[r] = self.arrive.ptrs[r]
         P.rank, P.world, P.timeout_ns = self.group.rank, self.group.world, int(self.timeout_s * 1e9)
+        P.gu_stride = self._gu_stride
         S = N.DarlinServer(self.srv_delta.data_ptr(), self.srv_active.data_ptr(), self.violation.data_ptr(), self.slots)
         self._Wk, self._P, self._S = Wk, P, S
         self._lib.psb_darlin_grid.restype = C.c_int
@@ -427,24 +516,33 @@ class DarlinSolver:
         self.active.fill_(1)
         self.srv_w.local.zero_()
         self.srv_gu.local.zero_()
+        self._prev_tail = None
         self.srv_delta.fill_(self.cfg.delta_init)
         self.srv_active.fill_(1)
         self.progress = []
         self.kkt_threshold = 1e20
         self.group.barrier()
 
-    def launch_pass(self, order: np.ndarray) -> None:
-        """Enqueue one pass over the blocks in ``order`` on the current stream."""
+    def launch_pass(self, order: np.ndarray, delay: Optional[int] = None, first: bool = True) -> None:
+        """Enqueue one pass over the blocks in ``order`` on the current stream.  ``delay``: bounded delay for
+        these blocks when it differs from the configured one; ``first``: this is the first launch of a pass
+        (the maximal KKT violation restarts)."""
+        if delay is not None and delay != self.cfg.max_block_delay:
+            saved, self.cfg.max_block_delay = self.cfg.max_block_delay, delay
+            try:
+                return self.launch_pass(order, first=first)
+            finally:
+                self.cfg.max_block_delay = saved
         order_t = torch.as_tensor(order, dtype=torch.int32).to(self.dev, non_blocking=False)
         self._order_keepalive = order_t
-        self.violation.zero_()
+        if first:
+            self.violation.zero_()
         if self.impl == "nccl":
             return self._pass_unfused(order)
         if self.out_of_core:
             return self._pass_streamed(np.asarray(order), order_t)
         group = max(int(self.cfg.max_block_delay), 0) + 1        # bounded delay: tau+1 blocks share their sync points
-        Q = N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), len(order), group, self.seq,
-                          self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr())
+        Q = self._sched(order_t, len(order), group)
         H = self._hyper()
         N.check(self._lib.psb_darlin_pass(C.byref(self._Wk), C.byref(self._P), C.byref(self._S), C.byref(Q),
                                           C.byref(H), self.grid, N.stream_ptr()), "darlin_pass")
@@ -452,6 +550,7 @@ class DarlinSolver:
         self.seq += ngroups
         self.bar += ngroups
         self.kernel_launches += 1
+        self._prev_tail = order_t[(len(order) - 1) // group * group:]
 
     def _pass_unfused(self, order: np.ndarray) -> None:
         """Baseline: per block, stand-alone kernels + all_reduce of (G,U) + broadcast-free local update."""
@@ -466,14 +565,15 @@ class DarlinSolver:
             self._gcol = (self.gslot.long() + torch.tensor(gk_begin, device=self.dev)[self.gowner.long()])
             self._gu_glob = torch.zeros((nglobal, 2), dtype=torch.float32, device=self.dev)
             self._w_glob = torch.zeros((nglobal,), dtype=torch.float32, device=self.dev)
-            gb = torch.searchsorted(self.gkeys_sorted, torch.tensor(
-                [min(b, (1 << 64) - 1) + _SIGN for b, _ in self.block_keys],
-                dtype=torch.int64, device=self.dev)).tolist() + [nglobal]
-            self._blk_g = gb
+            to_s = lambda ks: torch.tensor([min(k, (1 << 64) - 1) + _SIGN for k in ks], dtype=torch.int64, device=self.dev)
+            g0s = torch.searchsorted(self.gkeys_sorted, to_s([b for b, _ in self.block_keys])).tolist()
+            g1s = [nglobal if e >= (1 << 64) else v for (_, e), v in zip(
+                self.block_keys, torch.searchsorted(self.gkeys_sorted, to_s([e for _, e in self.block_keys])).tolist())]
+            self._blk_g = list(zip(g0s, g1s))
         r = self.group.rank
         for b in order.tolist():
             lc0, lc1 = blk_lc[b]
-            g0, g1 = self._blk_g[b], self._blk_g[b + 1]
+            g0, g1 = self._blk_g[b]
             if g1 <= g0:
                 continue
             gu_loc = torch.zeros((max(lc1 - lc0, 1), 2), dtype=torch.float32, device=self.dev)
@@ -489,7 +589,7 @@ class DarlinSolver:
                 dist.all_reduce(gu, group=self.group.group)          # push + server-side sum
             s0, s1 = blk_sl[b]
             if s1 > s0:
-                self.srv_gu.local[s0:s1].copy_(gu[gk_begin[r] + s0 - g0: gk_begin[r] + s1 - g0])
+                self.srv_gu.local[0, s0:s1].copy_(gu[gk_begin[r] + s0 - g0: gk_begin[r] + s1 - g0])
                 N.check(lib.psb_darlin_update_weight(C.byref(self._P), C.byref(self._S), C.byref(H), s0, s1, s), "update_weight")
                 self.kernel_launches += 1
             wb = self._w_glob[g0:g1]
@@ -535,7 +635,8 @@ class DarlinSolver:
         if st[0] != 0:
             raise RuntimeError(f"rank {self.group.rank}: {N.STATUS_NAMES.get(st[0], st[0])} (block={st[1]}, phase={st[2]})")
 
-    def run_pass(self, order: np.ndarray, reset: bool = False) -> Progress:
+    def run_pass(self, order: np.ndarray, reset: bool = False, prior: Optional[List[int]] = None) -> Progress:
+        """One pass; ``prior``: blocks swept before ``order`` with zero delay (first pass, important groups)."""
         from ..utils.trace import nvtx_range
 
         t0 = time.time()
@@ -545,12 +646,14 @@ class DarlinSolver:
             monitor.tick(len(self.progress))
         if reset:
             self.reset_active_sets()
+        if prior:
+            self.launch_pass(np.asarray(prior, dtype=np.int32), delay=0)
         with nvtx_range("darlin_pass"):
             if trace is not None:
                 with trace.span("darlin_pass", cat="solver", device_timed=True, blocks=len(order), it=len(self.progress)):
-                    self.launch_pass(order)
+                    self.launch_pass(order, first=not prior)
             else:
-                self.launch_pass(order)
+                self.launch_pass(order, first=not prior)
         with nvtx_range("evaluate_progress"):
             objv, nnz_w, nnz_as, vio = self.evaluate()
         self.check_status()
@@ -568,9 +671,11 @@ class DarlinSolver:
         """All passes with the reference's stopping rule (src/linear_method/darling.cc:83-99)."""
         cfg = self.cfg
         orders = block_order(self.nblk, cfg.max_pass, cfg.random_block_order, cfg.seed)
+        prior = prior_block_order(self.block_group, cfg.prior_fea_group, cfg.num_iter_for_prior_fea_group,
+                                  cfg.random_block_order, cfg.seed)
         reset = False
         for it in range(cfg.max_pass):
-            p = self.run_pass(orders[it], reset)
+            p = self.run_pass(orders[it], reset, prior if it == 0 else None)
             if verbose and self.group.rank == 0:
                 print_progress(it, p, file=sys.stderr)
             if 0 < p.relative_objv <= cfg.epsilon:

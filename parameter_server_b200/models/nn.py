@@ -96,7 +96,34 @@ class DataLayer(Layer):
         if normalize:
             dense.col_normalize(self.X)
 
+    def set_sparse_data(self, off: torch.Tensor, idx: torch.Tensor, vals: Optional[torch.Tensor], y: torch.Tensor,
+                        in_dim: int) -> None:
+        """Keep the examples as CSR rows (for a SPARSE_FULLY_CONNECTED consumer): minibatches are row subsets."""
+        d = self.net.device
+        self.X = None
+        self.csr = (off.to(d).long(), idx.to(d).int(), None if vals is None else vals.to(d).float(), int(in_dim))
+        self.y = y.to(d).float()
+
+    def _sparse_minibatch(self):
+        off, idx, vals, in_dim = self.csr
+        n, b = self.y.numel(), self.conf.minibatch_size
+        if b <= 0 or b >= n:
+            return (off, idx, vals, in_dim), self.y
+        sel = torch.randperm(n, generator=self.gen)[:b].to(self.net.device)
+        lens = off[sel + 1] - off[sel]
+        noff = torch.zeros(b + 1, dtype=torch.int64, device=off.device)
+        noff[1:] = lens.cumsum(0)
+        # position p of the new matrix comes from row sel[r] at offset p - noff[r]
+        src = torch.repeat_interleave(off[sel] - noff[:-1], lens) + torch.arange(int(noff[-1]), device=off.device)
+        return (noff, idx[src].contiguous(), None if vals is None else vals[src].contiguous(), in_dim), self.y[sel].contiguous()
+
     def forward(self) -> float:
+        if getattr(self, "csr", None) is not None and self.X is None:
+            xb, yb = self._sparse_minibatch()
+            self.outputs[0].value = xb
+            if len(self.outputs) > 1:
+                self.outputs[1].value = yb
+            return 0.0
         n = self.X.shape[0]
         b = self.conf.minibatch_size
         if b <= 0 or b >= n:
@@ -150,6 +177,42 @@ class FullyConnectedLayer(Layer):
             self.inputs[0].gradient = dense.gemm_tn(z, wt, pad_k=True)                # [batch, in] = Z · W
 
 
+class SparseFullyConnectedLayer(Layer):
+    """Y = act(X·W) for a sparse minibatch: the input edge carries a CSR triple ``(offsets int64, column ids
+    int32, values float32 | None)`` (``DataLayer.set_sparse_data``), the model is one row of ``size`` floats per
+    input feature — the per-key vectors of the reference's layer (sparse_fully_connected_layer.h:31-88, which
+    adds the vectors of an example's features; its admission rule "a feature gets a vector once it was seen
+    50 times" is left to the data pipeline's tail filter).  No gradient flows into the data."""
+
+    def init(self) -> None:
+        self.act = self.conf.activation.type if self.conf.has("activation") else "IDENTITY"
+        if self.act not in dense.ACT:
+            raise ValueError(f"activation {self.act} is not implemented")
+        self.out_dim = int(self.conf.size)
+        if self.out_dim % 4:
+            raise ValueError("the size of a sparse fully connected layer must be a multiple of 4")
+        self.model = None
+
+    def forward(self) -> float:
+        off, idx, vals, in_dim = self.inputs[0].value
+        if self.model is None:
+            shared = self.net.shared_models.get(self.name)
+            if shared is None:
+                w = init_tensor((in_dim, self.out_dim), self.conf.init if self.conf.has("init") else None, self.net.device,
+                                seed=zlib.crc32(self.name.encode()) % (1 << 30))
+                shared = Parameter(self.name, w, torch.zeros_like(w), None)
+                self.net.shared_models[self.name] = shared
+            self.model = shared
+        self.x = (off, idx, vals, in_dim)
+        self.outputs[0].value = dense.sparse_fc_forward(off, idx, vals, self.model.value, self.act)
+        return 0.0
+
+    def backward(self) -> None:
+        off, idx, vals, in_dim = self.x
+        self.model.gradient = dense.sparse_fc_backward(off, idx, vals, self.outputs[0].value, self.outputs[0].gradient, in_dim,
+                                                       self.act)
+
+
 class LogisticLossLayer(Layer):
     def forward(self) -> float:
         x, y = self.inputs[0].value, self.inputs[1].value
@@ -164,11 +227,14 @@ class LogisticLossLayer(Layer):
 class AUCLayer(Layer):
     def forward(self) -> float:
         x, y = self.inputs[0].value.reshape(-1), self.inputs[1].value
-        self.auc = host().exact_auc(y.cpu().numpy(), x.cpu().numpy())
+        from ..ops.evalops import exact_auc
+
+        self.auc = exact_auc(y, x) if x.is_cuda else host().exact_auc(y.cpu().numpy(), x.cpu().numpy())
         return self.auc
 
 
-LAYERS = {"DATA": DataLayer, "FULLY_CONNECTED": FullyConnectedLayer, "LOGISTIC_LOSS": LogisticLossLayer, "AUC": AUCLayer}
+LAYERS = {"DATA": DataLayer, "FULLY_CONNECTED": FullyConnectedLayer, "SPARSE_FULLY_CONNECTED": SparseFullyConnectedLayer,
+          "LOGISTIC_LOSS": LogisticLossLayer, "AUC": AUCLayer}
 
 
 class Edge(Parameter):

@@ -102,8 +102,8 @@ class DarlinWorker(C.Structure):
 
 
 class DarlinPeers(C.Structure):
-    _fields_ = [("w", _P8), ("gu", _P8), ("arrive", _P8), ("updated", _P8), ("rank", C.c_int), ("world", C.c_int),
-                ("timeout_ns", C.c_uint64)]
+    _fields_ = [("w", _P8), ("gu", _P8), ("arrive", _P8), ("rank", C.c_int), ("world", C.c_int),
+                ("timeout_ns", C.c_uint64), ("gu_stride", C.c_int64)]
 
 
 class DarlinServer(C.Structure):
@@ -113,7 +113,8 @@ class DarlinServer(C.Structure):
 class DarlinSched(C.Structure):
     _fields_ = [("order", C.c_void_p), ("blk_lc", C.c_void_p), ("blk_sl", C.c_void_p), ("nblk", C.c_int),
                 ("group", C.c_int), ("seq0", C.c_uint64), ("local_bar", C.c_void_p), ("bar0", C.c_uint64),
-                ("abort_flag", C.c_void_p), ("status", C.c_void_p), ("stage_base", C.c_void_p)]
+                ("abort_flag", C.c_void_p), ("status", C.c_void_p), ("stage_base", C.c_void_p),
+                ("prev", C.c_void_p), ("nprev", C.c_int), ("pad", C.c_int)]
 
 
 class DarlinHyper(C.Structure):

@@ -80,3 +80,23 @@ def sgd_update(w: torch.Tensor, g: torch.Tensor, h: Optional[torch.Tensor], alph
 def col_normalize(x: torch.Tensor) -> None:
     assert x.is_contiguous() and x.dim() == 2
     N.check(N.lib().psb_col_normalize(N.ptr(x), x.shape[0], x.shape[1], N.stream_ptr()), "col_normalize")
+
+
+def sparse_fc_forward(off: torch.Tensor, idx: torch.Tensor, vals: Optional[torch.Tensor], w: torch.Tensor, act: str = "IDENTITY") -> torch.Tensor:
+    """Y = act(X·W) for CSR X (int64 offsets, int32 column ids, float32 values or None = ones) and W [in, out]
+    (out a multiple of 4): the embedding-bag sum of the sparse fully connected layer."""
+    rows, (in_dim, out_dim) = off.numel() - 1, w.shape
+    y = torch.empty((rows, out_dim), dtype=torch.float32, device=w.device)
+    N.check(N.lib().psb_spfc_forward(N.ptr(off), N.ptr(idx), N.ptr(vals), N.ptr(w), N.ptr(y), rows, in_dim, out_dim, ACT[act],
+                                     N.ptr(_status_for(w.device)), N.stream_ptr()), "spfc_forward")
+    return y
+
+
+def sparse_fc_backward(off: torch.Tensor, idx: torch.Tensor, vals: Optional[torch.Tensor], y: torch.Tensor, gy: torch.Tensor,
+                       in_dim: int, act: str = "IDENTITY") -> torch.Tensor:
+    """Wg = Xᵀ·(dY ∘ act'(Y)) as [in, out]."""
+    rows, out_dim = y.shape
+    wg = torch.zeros((in_dim, out_dim), dtype=torch.float32, device=y.device)
+    N.check(N.lib().psb_spfc_backward(N.ptr(off), N.ptr(idx), N.ptr(vals), N.ptr(y), N.ptr(gy.contiguous()), N.ptr(wg), rows, in_dim,
+                                      out_dim, ACT[act], N.stream_ptr()), "spfc_backward")
+    return wg

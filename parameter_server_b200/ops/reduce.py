@@ -7,7 +7,7 @@ import torch
 
 from . import _native as N
 
-OPS = {"sum_log1p_inv": 0, "sum_abs": 1, "count_nonzero": 2, "sum_logistic": 3}
+OPS = {"sum_log1p_inv": 0, "sum_abs": 1, "count_nonzero": 2, "sum_logistic": 3, "sum_square_hinge": 4}
 _scratch = {}
 
 

@@ -195,8 +195,31 @@ def set_intersection(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def set_union(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """Sorted union of two key sets."""
-    return count_unique(torch.cat([a, b]))[0]
+    """Sorted union of two sorted unique key sets by ranking (no sort): ``SArray::setUnion``."""
+    lib, na, nb, dev = _lib(), a.numel(), b.numel(), a.device
+    if nb == 0:
+        return a.clone()
+    if na == 0:
+        return b.clone()
+    a, b = a.contiguous(), b.contiguous()
+    dup = torch.empty(nb, dtype=torch.int32, device=dev)           # elements of b that a holds too
+    N.check(lib.psb_set_intersect_flags(N.ptr(b), _sz(nb), N.ptr(a), _sz(na), N.ptr(dup), N.stream_ptr()), "intersect_flags")
+    keep = torch.empty(nb, dtype=torch.int32, device=dev)
+    N.check(lib.psb_invert_flags(N.ptr(dup), _sz(nb), N.ptr(keep), N.stream_ptr()), "invert_flags")
+    pos, total = exclusive_scan(keep)                              # kept elements of b before every index
+    out = torch.empty(na + int(total.item()), dtype=torch.int64, device=dev)
+    N.check(lib.psb_merge_union(N.ptr(a), _sz(na), N.ptr(b), _sz(nb), N.ptr(dup), N.ptr(pos), N.ptr(out), N.stream_ptr()), "merge_union")
+    return out
+
+
+def set_union_many(parts) -> torch.Tensor:
+    """Union of several sorted unique key sets (pairwise, smallest first)."""
+    parts = sorted((p for p in parts if p.numel()), key=lambda t: t.numel())
+    if not parts:
+        return torch.zeros(0, dtype=torch.int64)
+    while len(parts) > 1:
+        parts = sorted([set_union(parts[0], parts[1])] + parts[2:], key=lambda t: t.numel())
+    return parts[0]
 
 
 def spmv(offsets: torch.Tensor, idx: torch.Tensor, vals: Optional[torch.Tensor], w: torch.Tensor) -> torch.Tensor:

@@ -59,19 +59,32 @@ def filter_tail(shards, W, freq, k=2, ratio=2.0):
 def main():
     impl = sys.argv[1] if len(sys.argv) > 1 else "fused"
     tail = int(sys.argv[2]) if len(sys.argv) > 2 else 0
+    delay = int(sys.argv[3]) if len(sys.argv) > 3 else 0        # bounded delay tau
+    streamed = len(sys.argv) > 4 and sys.argv[4] == "ooc"       # also run with the blocks streamed from host memory
     group = PeerGroup.from_env()
     rank, W, dev = group.rank, group.world, group.device
     off, idx, vals, y, _ = zipf_sparse_matrix(2400, 3000, 14, seed=5, device=dev, zipf_s=0.8)
     keys = idx * 104729 + 11
-    kw = dict(lambda1=0.3, max_pass=5, feature_block_ratio=1.0, seed=2)
+    kw = dict(lambda1=0.3, max_pass=5, feature_block_ratio=1.0, seed=2, max_block_delay=delay)
     sol = DarlinSolver(group, DarlinConfig(tail_feature_freq=tail, **kw), impl=impl)
     sol.preprocess(*shard(off, keys, vals, y, rank, W))
     prog = sol.run()
     sol.check_status()
     k, w = sol.model()
+    same_streamed = True
+    if streamed:
+        # every rank streams the blocks of its own rows; the batches are whole synchronisation groups on all ranks
+        ooc = DarlinSolver(group, DarlinConfig(tail_feature_freq=tail, **kw), impl=impl, out_of_core=True, prefetch_depth=2,
+                           blocks_per_launch=3 + rank)      # the ranks ask for different batch sizes and must agree
+        ooc.preprocess(*shard(off, keys, vals, y, rank, W))
+        prog2 = ooc.run()
+        ooc.check_status()
+        same_streamed = len(prog2) == len(prog) and ooc.h2d_bytes > 0 and ooc.kernel_launches > len(prog2)
+        for a, b in zip(prog, prog2):
+            same_streamed &= abs(b.objv / a.objv - 1) < 1e-4 and abs(a.nnz_w - b.nnz_w) <= 2
     gathered = [None] * W
     dist.all_gather_object(gathered, (k, w), group=group.group)
-    ok = True
+    ok = bool(same_streamed)
     if rank == 0:
         shards = []
         for r in range(W):
@@ -94,7 +107,7 @@ def main():
         ok &= len(common) >= 0.95 * max(len(allk), len(rk))
         wd, rd = dict(zip(allk.tolist(), allw.tolist())), dict(zip(rk.tolist(), rw.tolist()))
         ok &= max(abs(wd[c] - rd[c]) for c in common.tolist()) < 5e-2
-        print(f"impl={impl} tail={tail} dropped={dropped} world={W} passes={len(prog)} objv={prog[-1].objv:.4f} ref={rprog[-1].objv:.4f} "
+        print(f"impl={impl} tail={tail} delay={delay} streamed={streamed} dropped={dropped} world={W} passes={len(prog)} objv={prog[-1].objv:.4f} ref={rprog[-1].objv:.4f} "
               f"shard_sizes={[len(g[0]) for g in gathered]} match={bool(ok)}", flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, 0, group=group.group)

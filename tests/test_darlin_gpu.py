@@ -114,3 +114,50 @@ def test_darlin_model_dump(tmp_path):
     k, w = sol.model()
     assert len(m) == len(k) > 0
     assert list(m.keys()) == sorted(m.keys())
+
+
+def _grouped_problem(rows=1200, seed=7):
+    """TERAFEA-style keys: the top 10 bits are the feature group.  Group 3 has one feature per example (one
+    block), group 5 about six, group 9 about twelve (several blocks each)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    per_group = {3: (1, 40), 5: (6, 300), 9: (12, 700)}       # group -> (features per example, vocabulary)
+    cols = []
+    for gid, (n, vocab) in per_group.items():
+        ids = torch.randint(0, vocab, (rows, n), generator=g, device="cuda")
+        cols.append((gid << 54) + ids * 1009 + 17)
+    keys = torch.cat(cols, 1).sort(1).values
+    keep = torch.ones_like(keys, dtype=torch.bool)
+    keep[:, 1:] = keys[:, 1:] != keys[:, :-1]                  # distinct within an example
+    off = torch.zeros(rows + 1, dtype=torch.int64, device="cuda")
+    off[1:] = keep.sum(1).cumsum(0)
+    flat = keys[keep]
+    w = torch.randn(1 << 12, generator=g, device="cuda")
+    xw = torch.zeros(rows, device="cuda").index_add_(0, torch.repeat_interleave(torch.arange(rows, device="cuda"), keep.sum(1)),
+                                                     w[(flat * 2654435761 >> 7) % (1 << 12)])
+    y = torch.where(xw + 0.3 * torch.randn(rows, generator=g, device="cuda") > 0, 1.0, -1.0)
+    return off, flat.contiguous(), None, y
+
+
+@pytest.mark.parametrize("tau", [0, 2])
+def test_feature_groups_and_prior_sweeps_match_oracle(tau):
+    """Blocks cut group by group from each group's own density and key range; the important group's blocks are
+    swept first, with zero delay, in the first pass (the schedule of the reference's CTR job file)."""
+    from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver
+    from parameter_server_b200.parallel.peer import PeerGroup
+
+    off, keys, vals, y = _grouped_problem()
+    kw = dict(lambda1=0.2, max_pass=4, feature_block_ratio=0.5, seed=3, max_block_delay=tau, feature_group_bits=10,
+              prior_fea_group=(9,), num_iter_for_prior_fea_group=2)
+    sol = DarlinSolver(PeerGroup.single(torch.device("cuda", 0)), DarlinConfig(**kw))
+    sol.preprocess(off, keys, vals, y)
+    prog = sol.run()
+    sol.check_status()
+    ref = DarlinRef([(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64), None, y.cpu().numpy())], None, RefConfig(**kw))
+    rprog = ref.run()
+    assert sol.block_group == ref.block_group and sol.block_keys == ref.block_keys
+    assert sol.block_group.count(3) == 1 and sol.block_group.count(5) == 3 and sol.block_group.count(9) == 6
+    assert len(ref.prior_order()) == 12
+    for p, r in zip(prog, rprog):
+        assert p.objv == pytest.approx(r.objv, rel=2e-3)
+        assert abs(p.nnz_w - r.nnz_w) <= max(3, 0.03 * r.nnz_w)
+        assert p.violation == pytest.approx(r.violation, rel=2e-2, abs=1e-3)

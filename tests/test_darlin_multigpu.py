@@ -9,10 +9,10 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _launch(nproc, impl, port, tail=0):
+def _launch(nproc, impl, port, tail=0, delay=0, streamed=False):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_darlin_worker.py"), impl,
-           str(tail)]
+           str(tail), str(delay), "ooc" if streamed else "resident"]
     return subprocess.run(cmd, capture_output=True, text=True, timeout=300)
 
 
@@ -27,6 +27,14 @@ def test_two_gpus_tail_filter_matches_oracle():
     r = _launch(2, "fused", 29554, tail=2)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "match=True" in r.stdout
+
+
+def test_two_gpus_bounded_delay_and_streamed_blocks():
+    """tau = 2 on two GPUs equals the oracle's grouped schedule; the same job with every rank streaming its
+    blocks from pinned host memory equals the resident one."""
+    r = _launch(2, "fused", 29555, delay=2, streamed=True)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "match=True" in r.stdout and "streamed=True" in r.stdout
 
 
 def test_all_gpus_match_oracle():
