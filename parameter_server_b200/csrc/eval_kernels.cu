@@ -24,7 +24,8 @@ __global__ void k_auc_bin_keys(const float* label, const float* pred, size_t n, 
 // scores as 64-bit keys in ascending order of the float values (NaN last)
 __global__ void k_score_keys(const float* pred, size_t n, uint64_t* keys) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const uint32_t b = __float_as_uint(pred[i]);
+    uint32_t b = __float_as_uint(pred[i]);
+    if (b == 0x80000000u) b = 0u;          // −0 and +0 are the same score
     keys[i] = (uint64_t)((b & 0x80000000u) ? ~b : (b | 0x80000000u));
   }
 }

@@ -229,7 +229,7 @@ __device__ __forceinline__ void phase_localize(const FtrlPeers& P, const Minibat
       uint32_t slot = (uint32_t)h0;
       if (cur0 != key0) {
         bool inserted = false;
-        const uint64_t s = table_find_or_insert(L.lt_keys, ~0ull, cmask, h0, key0, P.max_probe, &inserted, &cur0);
+        const uint64_t s = table_find_or_insert(L.lt_keys, ~0ull, cmask, h0, key0, P.max_probe, &inserted);
         if (s == ~0ull) {
           set_status(L.status, kLocalTableFull, 0, 0);
           slot = kBadSlot;
@@ -436,18 +436,17 @@ __device__ __forceinline__ void phase_grad(const Minibatch& M, const LocalScratc
         sls[k] = i < e ? PSB_LD_U32(L.slot_of + i, pol) : kBadSlot;
         x[k] = (M.vals != nullptr && i < e) ? PSB_LD_F32(M.vals + i, pol) : 1.f;
       }
-      // the cache tags of all the lane's non-zeros first: their shared-memory loads overlap
-      uint32_t tag[kRowBatch];
-#pragma unroll
-      for (int k = 0; k < kRowBatch; ++k)
-        tag[k] = sls[k] != kBadSlot ? hc->slot[(sls[k] * 2654435761u) >> (32 - PSB_HOT_LOG2)] : 0u;
 #pragma unroll
       for (int k = 0; k < kRowBatch; ++k) {
         const uint32_t sl = sls[k];
         if (sl == kBadSlot) continue;
         const float gv = c * x[k];
         const int h = (int)((sl * 2654435761u) >> (32 - PSB_HOT_LOG2));  // top bits
-        uint32_t cur = tag[k];
+        uint32_t cur = hc->slot[h];
+        if (cur == kBadSlot) {
+          const uint32_t prev = atomicCAS(&hc->slot[h], kBadSlot, sl);
+          cur = prev == kBadSlot ? sl : prev;
+        }
         if (cur == sl) {
           atomicAdd(&hc->g[h], gv);
           if (kCounts) atomicAdd(&hc->cnt[h], inc);

@@ -149,15 +149,14 @@ __device__ __forceinline__ float warp_max(float v) {
 // insert-or-find in a local (same GPU) table; returns slot or ~0ull when the
 // probe limit is hit.  Probing wraps inside the aligned chunk of (chunk_mask + 1) slots that
 // holds the home slot h, so a key never leaves its home chunk (chunk_mask = mask: whole table).
-// *inserted (optional) is set when this call created the entry.  `seen` (optional): the value the
-// caller has already read at the home slot, which saves the first dependent load.
+// *inserted (optional) is set when this call created the entry.
 __device__ __forceinline__ uint64_t table_find_or_insert(uint64_t* keys, uint64_t mask, uint64_t chunk_mask,
                                                         uint64_t h, uint64_t key, int max_probe,
-                                                        bool* inserted = nullptr, const uint64_t* seen = nullptr) {
+                                                        bool* inserted = nullptr) {
   uint64_t slot = h & mask;
   const uint64_t base = slot & ~chunk_mask;
   for (int i = 0; i < max_probe; ++i) {
-    const uint64_t cur = (i == 0 && seen != nullptr) ? *seen : keys[slot];
+    uint64_t cur = keys[slot];
     if (cur == key) return slot;
     if (cur == kEmptyKey) {
       unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long*>(keys + slot),

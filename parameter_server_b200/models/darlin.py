@@ -135,12 +135,17 @@ class DarlinSolver:
     """Worker + server of one rank; ``preprocess`` once, then ``run`` (or ``run_pass`` repeatedly)."""
 
     def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused",
-                 out_of_core: bool = False, prefetch_depth: int = 3, blocks_per_launch: Optional[int] = None):
+                 out_of_core: bool = False, prefetch_depth: int = 3, blocks_per_launch: Optional[int] = None,
+                 ctas_per_sm: Optional[int] = None):
         """``out_of_core``: keep the column blocks (row ids, values) in pinned host memory and stream each
         block to the GPU on a side stream ahead of its turn in the block order — the role of the
         reference's ``FeatureStation`` in ``-mmap_training_data`` mode with its task-id keyed look-ahead
         prefetch (src/linear_method/feature_station.cc:212-279, src/linear_method/darling.cc:175-201)."""
         self.group, self.cfg, self.impl = group, cfg, impl
+        # thread blocks of the pass kernel per SM (1 or 2): more blocks hide gather latency, fewer make the
+        # per-group barriers cheaper; 2 measured best with and without bounded delay (5.1 against 5.8 ms per
+        # pass on 677,399 x 47,236, one GPU)
+        self.ctas_per_sm = ctas_per_sm
         self.out_of_core, self.prefetch_depth = out_of_core, max(int(prefetch_depth), 2)
         # out-of-core mode: blocks per kernel launch, rounded up to a multiple of max_block_delay + 1.  A launch
         # costs about 28 us, so small blocks are batched (up to 16); a batch is also the unit that must be on the
@@ -231,9 +236,9 @@ class DarlinSolver:
         pairs = torch.unique(row_of * G + gid)                    # one entry per (example, group) that occurs
         nnz_ex = torch.bincount(pairs % G, minlength=G).to(torch.float64)
         lg = (lkeys >> shift) & (G - 1)                           # group of every unique local key (ascending keys)
-        big = (1 << 62)
+        big = (1 << 63) - 1
         kmin = torch.full((G,), big, dtype=torch.int64, device=dev).scatter_reduce_(0, lg, _ukey(lkeys), "amin")
-        kmax = torch.full((G,), -big, dtype=torch.int64, device=dev).scatter_reduce_(0, lg, _ukey(lkeys), "amax")
+        kmax = torch.full((G,), -big - 1, dtype=torch.int64, device=dev).scatter_reduce_(0, lg, _ukey(lkeys), "amax")
         if self.group.world > 1:
             cnt = torch.stack([nnz_ele, nnz_ex])
             dist.all_reduce(cnt, group=self.group.group)
@@ -465,10 +470,8 @@ class DarlinSolver:
         self._Wk, self._P, self._S = Wk, P, S
         self._lib.psb_darlin_grid.restype = C.c_int
         grid = self._lib.psb_darlin_grid()
-        # one CTA per SM keeps the per-block barriers cheap; with bounded delay the barriers are amortised over
-        # tau+1 blocks and a second CTA per SM hides more gather latency
         sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
-        grid = min(grid, sms * (1 if self.cfg.max_block_delay <= 0 else 2))
+        grid = min(grid, sms * (self.ctas_per_sm or 2))
         if self.group.world > 1:
             import torch.distributed as dist
 

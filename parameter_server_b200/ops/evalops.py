@@ -56,4 +56,5 @@ def exact_auc(label: torch.Tensor, pred: torch.Tensor) -> float:
     fp = n - tp
     if tp == 0 or fp == 0:
         return 0.5
-    return float(area.item()) / (tp * fp)
+    # the kernel counts, for every negative, the positives that score LOWER: the complement of the AUC
+    return 1.0 - float(area.item()) / (tp * fp)
