@@ -78,8 +78,10 @@ struct DarlinSched {
   int nblk;
   int group;                // blocks per synchronisation group (max_block_delay + 1)
   uint64_t seq0;            // groups processed before this launch (same on all ranks)
-  uint64_t* local_bar;      // in-GPU barrier counter (monotone)
-  uint64_t bar0;            // barrier rounds completed before this launch
+  uint64_t* local_bar;      // [0] in-GPU barrier counter (monotone), [1] CTAs that finished a gradient phase,
+                            // [3] barrier rounds completed so far (kept on the device: a launch runs one round
+                            // per group plus one per wide group, which only the kernel counts)
+  uint64_t bar0;            // unused (the round count lives in local_bar[3])
   uint32_t* abort_flag;
   uint32_t* status;
   // out-of-core mode: stage_base[q] = device address where the packed [row ids | values] of block
@@ -88,7 +90,7 @@ struct DarlinSched {
   // blocks of the group that ran last before this launch (its accumulators are still to be zeroed), or nullptr
   const int32_t* prev;
   int nprev;
-  int pad;
+  int wide_cols;            // groups with more local columns than this take phase C in two steps (0: kWideBlockCols)
 };
 
 struct DarlinHyper {
@@ -391,6 +393,66 @@ __device__ __forceinline__ void darlin_update_margin(const DarlinWorker& Wk, int
   }
 }
 
+// Blocks with many columns take phase C in two steps: first every column fetches its (G,U) once, steps and
+// brings the worker's copy of the column up to date (Δw kept in Wk.dw), then, after one more in-GPU barrier,
+// the non-zeros read Δw locally.  With n non-zeros per column that is n times fewer loads from the owners'
+// memory — on 8 GPUs the out-of-core configuration (485 k columns and 1.9 M non-zeros per block and GPU) spent
+// most of a pass on one 8-byte NVLink load per non-zero — and one barrier more per group, which only
+// matters for small blocks.  The choice depends on this rank's columns only (the extra barrier is local).
+constexpr int64_t kWideBlockCols = 16384;
+
+__device__ __forceinline__ bool group_is_wide(const DarlinSched& Q, int b, int ge) {
+  int64_t cols = 0;
+  for (int q = b; q < ge; ++q) cols += Q.blk_lc[2 * Q.order[q] + 1] - Q.blk_lc[2 * Q.order[q]];
+  return cols > (Q.wide_cols > 0 ? (int64_t)Q.wide_cols : kWideBlockCols);
+}
+
+// first step of a wide block: step every column, commit it, keep Δw for the margin update
+__device__ __forceinline__ void darlin_step_columns(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H,
+                                                    int64_t lc0, int64_t lc1, int buf, size_t gtid, size_t gsz) {
+  const int64_t boff = (int64_t)buf * P.gu_stride;
+  const bool multi = P.world > 1;
+  for (int64_t j = lc0 + (int64_t)gtid; j < lc1; j += (int64_t)gsz) {
+    float d = 0.f;
+    if (Wk.active[j]) {
+      const float2 a = ld_gu(P.gu[Wk.gowner[j]] + boff + Wk.gslot[j], multi);
+      const DarlinStep st = darlin_step(a.x, a.y, Wk.w[j], Wk.delta[j], H);
+      if (st.drop) {
+        Wk.active[j] = 0;
+      } else {
+        d = st.d;
+        Wk.delta[j] = st.delta;
+        Wk.w[j] = __fadd_rn(Wk.w[j], st.d);
+      }
+    }
+    Wk.dw[j] = d;
+  }
+}
+
+// second step of a wide block: m_i += y_i x_ij Δw_j with Δw from Wk.dw
+__device__ __forceinline__ void darlin_margin_from_dw(const DarlinWorker& Wk, int64_t lc0, int64_t lc1, size_t gtid, size_t gsz) {
+  const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
+  const int lane = threadIdx.x & 31;
+  const bool shares = kRangeWalk && Wk.col_of == nullptr;
+  int64_t base = p0 + (int64_t)gtid - lane, end = p1, step = (int64_t)gsz, hint = -1;
+  if (shares) { warp_share(p0, p1, gtid >> 5, gsz >> 5, &base, &end); step = 32; }
+  for (; base < end; base += step) {
+    const int64_t e = base + lane;
+    const bool valid = e < end;
+    const int64_t j = Wk.col_of ? (valid ? (int64_t)Wk.col_of[e] : -1)
+                      : shares  ? find_col_from(Wk.col_ptr, lc0, lc1, hint, e, valid)
+                                : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
+    if (shares) hint = __shfl_sync(0xffffffffu, j, 31);
+    if (!valid) continue;
+    const float d = __ldcg(Wk.dw + j);
+    if (d != 0.f) {
+      const uint32_t i = Wk.row_idx[e];
+      const float v = Wk.vals ? Wk.vals[e] : 1.f;
+      atomicAdd(&Wk.ym[i].y, Wk.ym[i].x * v * d);
+    }
+  }
+}
+
 // ---- fused phase C of the persistent kernel: every non-zero fetches its column's summed (G,U) from the
 // owner and the column's state from the worker, re-evaluates the step and moves the margin by y·x·Δw.  The
 // worker-side column state (w, δ, active) is NOT written here — other CTAs are still reading it — but one
@@ -445,7 +507,7 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
   const size_t gsz = (size_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
   const uint64_t G = gridDim.x;
-  uint64_t bar = Q.bar0;
+  uint64_t bar = *(volatile uint64_t*)(Q.local_bar + 3);   // every CTA reads it before any CTA can finish the launch
 
   // Blocks are processed in groups of Q.group consecutive entries of the order (group = max_block_delay + 1):
   // the gradients of all blocks of a group are computed before any of them is updated, i.e. a block may see
@@ -465,9 +527,11 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
     // A: gradient + push, then announce arrival at every owner.  In the same phase: the worker's copy of the
     // previous group's columns is brought up to date (a different set of columns; all CTAs are past its
     // phase C; the previous launch did this itself for its last group).
-    for (int q = max(b - group, 0); q < b; ++q) {
-      const int blk = Q.order[q];
-      darlin_commit(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], pbuf, gtid, gsz);
+    if (b > 0 && !group_is_wide(Q, max(b - group, 0), b)) {    // (a wide group committed its columns itself)
+      for (int q = max(b - group, 0); q < b; ++q) {
+        const int blk = Q.order[q];
+        darlin_commit(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], pbuf, gtid, gsz);
+      }
     }
     for (int q = b; q < ge; ++q) {
       const int blk = Q.order[q];
@@ -497,10 +561,24 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       }
     }
     // Worker: margins of the rows that the group's columns touch.
+    const bool wide = group_is_wide(Q, b, ge);
+    if (wide) {
+      for (int q = b; q < ge; ++q) {
+        const int blk = Q.order[q];
+        darlin_step_columns(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], buf, gtid, gsz);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
+      if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
+        if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 13); *Q.abort_flag = 1u; }
+        break;
+      }
+    }
     for (int q = b; q < ge; ++q) {
       const int blk = Q.order[q];
       const int64_t lc0 = Q.blk_lc[2 * blk], lc1 = Q.blk_lc[2 * blk + 1];
-      darlin_step_margin(worker_for(Wk, Q, q, lc0, lc1), P, H, lc0, lc1, buf, gtid, gsz);
+      if (wide) darlin_margin_from_dw(worker_for(Wk, Q, q, lc0, lc1), lc0, lc1, gtid, gsz);
+      else darlin_step_margin(worker_for(Wk, Q, q, lc0, lc1), P, H, lc0, lc1, buf, gtid, gsz);
     }
     __syncthreads();
     if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
@@ -508,13 +586,14 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 14); *Q.abort_flag = 1u; }
       break;
     }
-    if (ge == Q.nblk) {  // last group of the launch: bring the worker's copy of its columns up to date now
+    if (ge == Q.nblk && !wide) {  // last group of the launch: bring the worker's copy of its columns up to date now
       for (int q = b; q < ge; ++q) {
         const int blk = Q.order[q];
         darlin_commit(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], buf, gtid, gsz);
       }
     }
   }
+  if (blockIdx.x == 0 && threadIdx.x == 0) Q.local_bar[3] = bar;
 }
 
 // ---- stand-alone phase kernels (unfused NCCL baseline; gradients go to local buffers)

@@ -136,7 +136,7 @@ class DarlinSolver:
 
     def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused",
                  out_of_core: bool = False, prefetch_depth: int = 3, blocks_per_launch: Optional[int] = None,
-                 ctas_per_sm: Optional[int] = None):
+                 ctas_per_sm: Optional[int] = None, wide_block_cols: int = 0):
         """``out_of_core``: keep the column blocks (row ids, values) in pinned host memory and stream each
         block to the GPU on a side stream ahead of its turn in the block order — the role of the
         reference's ``FeatureStation`` in ``-mmap_training_data`` mode with its task-id keyed look-ahead
@@ -146,6 +146,9 @@ class DarlinSolver:
         # per-group barriers cheaper; 2 measured best with and without bounded delay (5.1 against 5.8 ms per
         # pass on 677,399 x 47,236, one GPU)
         self.ctas_per_sm = ctas_per_sm
+        # groups of blocks with more local columns than this fetch the owners' sums once per column instead of
+        # once per non-zero, at the price of one more in-GPU barrier (0: the kernel's default, 16384)
+        self.wide_block_cols = int(wide_block_cols)
         self.out_of_core, self.prefetch_depth = out_of_core, max(int(prefetch_depth), 2)
         # out-of-core mode: blocks per kernel launch, rounded up to a multiple of max_block_delay + 1.  A launch
         # costs about 28 us, so small blocks are batched (up to 16); a batch is also the unit that must be on the
@@ -452,7 +455,8 @@ class DarlinSolver:
         prev = self._prev_tail
         return N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), n, group, self.seq,
                              self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr(), None,
-                             None if prev is None else prev.data_ptr(), 0 if prev is None else prev.numel(), 0)
+                             None if prev is None else prev.data_ptr(), 0 if prev is None else prev.numel(),
+                             self.wide_block_cols)
 
     def _build_structs(self):
         Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),

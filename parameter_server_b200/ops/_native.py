@@ -114,7 +114,7 @@ class DarlinSched(C.Structure):
     _fields_ = [("order", C.c_void_p), ("blk_lc", C.c_void_p), ("blk_sl", C.c_void_p), ("nblk", C.c_int),
                 ("group", C.c_int), ("seq0", C.c_uint64), ("local_bar", C.c_void_p), ("bar0", C.c_uint64),
                 ("abort_flag", C.c_void_p), ("status", C.c_void_p), ("stage_base", C.c_void_p),
-                ("prev", C.c_void_p), ("nprev", C.c_int), ("pad", C.c_int)]
+                ("prev", C.c_void_p), ("nprev", C.c_int), ("wide_cols", C.c_int)]
 
 
 class DarlinHyper(C.Structure):

@@ -75,7 +75,8 @@ def main():
     if streamed:
         # every rank streams the blocks of its own rows; the batches are whole synchronisation groups on all ranks
         ooc = DarlinSolver(group, DarlinConfig(tail_feature_freq=tail, **kw), impl=impl, out_of_core=True, prefetch_depth=2,
-                           blocks_per_launch=3 + rank)      # the ranks ask for different batch sizes and must agree
+                           blocks_per_launch=3 + rank,      # the ranks ask for different batch sizes and must agree
+                           wide_block_cols=1 if rank == 0 else 0)   # and rank 0 takes the two-step path for every group
         ooc.preprocess(*shard(off, keys, vals, y, rank, W))
         prog2 = ooc.run()
         ooc.check_status()

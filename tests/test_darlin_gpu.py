@@ -50,6 +50,26 @@ def test_darlin_matches_oracle(binary, impl):
     sol.check_status()
 
 
+@pytest.mark.parametrize("tau", [0, 2])
+def test_wide_block_path_matches_oracle(tau):
+    """Groups with many columns fetch the owners' sums once per column and update the margins in a second step;
+    forced here for every group by a threshold of one column."""
+    from parameter_server_b200.models.darlin import DarlinConfig, DarlinSolver
+    from parameter_server_b200.parallel.peer import PeerGroup
+
+    off, keys, vals, y = _problem(False)
+    kw = dict(lambda1=0.3, max_pass=4, feature_block_ratio=1.0, seed=3, max_block_delay=tau)
+    sol = DarlinSolver(PeerGroup.single(torch.device("cuda", 0)), DarlinConfig(**kw), wide_block_cols=1)
+    sol.preprocess(off, keys, vals, y)
+    prog = sol.run()
+    sol.check_status()
+    ref = DarlinRef([(off.cpu().numpy(), keys.cpu().numpy().view(np.uint64), vals.cpu().numpy(), y.cpu().numpy())], None,
+                    RefConfig(**kw))
+    for p, r in zip(prog, ref.run()):
+        assert p.objv == pytest.approx(r.objv, rel=2e-3)
+        assert abs(p.nnz_w - r.nnz_w) <= max(3, 0.03 * r.nnz_w)
+
+
 @pytest.mark.parametrize("tau", [1, 3])
 def test_bounded_delay_groups_match_oracle(tau):
     """max_block_delay = tau: tau+1 blocks share their synchronisation points (all gradients before any update)."""
