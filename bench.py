@@ -354,7 +354,10 @@ def run_darlin(args):
         sol.preprocess(off, idx, vals, y)
         out = {"nblk": sol.nblk}
         if not ooc:
+            sol.phase_times_ms()
             out["ms"], out["launches"], _, _ = timed(sol, False)
+            if which == "fused":     # in-kernel timers of thread block 0 over warm-up + timed passes, scaled to one pass
+                out["phases"] = {k: round(v / (args.warmup + args.steps), 4) for k, v in sol.phase_times_ms().items()}
             out["final"] = sol.evaluate()
         out["ms_eval"], l2, out["h2d"], out["objs"] = timed(sol, True)
         out.setdefault("launches", l2)
@@ -426,7 +429,8 @@ def run_darlin(args):
                    "l2_policy": f"inputs larger than L2: {nnz_total * (4 if vals is None else 8) >> 20} MiB of CSC row ids"
                                 f"{'' if vals is None else ' and values'} read per pass",
                    "objective_after_timed_passes": objv, "nnz_w": nnz_w, "active_keys": nnz_as,
-                   "objective_trace": [round(o, 2) for o in main["objs"]]},
+                   "objective_trace": [round(o, 2) for o in main["objs"]],
+                   "phase_ms_per_pass_rank0_block0": main.get("phases")},
         "variants": variants or None,
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
     }, rank

@@ -53,6 +53,7 @@ struct DarlinWorker {
   int64_t cols;
   int rows;
   int pad;
+  const int64_t* gcol;      // cols: position of the column's key in the global sorted key list (all owners)
 };
 
 struct DarlinPeers {
@@ -62,6 +63,10 @@ struct DarlinPeers {
   int rank, world;
   uint64_t timeout_ns;
   int64_t gu_stride;                 // float2 elements between the three accumulator buffers of a shard
+  // small groups of blocks (see kGatherCols): rank t's inbox of partial sums, [3 buffers][world senders][kGatherCols],
+  // and this rank's own partial sums of the group in flight
+  float2* part[PSB_MAX_RANKS];
+  float2* mine;
 };
 
 struct DarlinServer {     // local arrays of this rank's shard
@@ -91,6 +96,13 @@ struct DarlinSched {
   const int32_t* prev;
   int nprev;
   int wide_cols;            // groups with more local columns than this take phase C in two steps (0: kWideBlockCols)
+  const int64_t* blk_gc;    // [nblocks_total][2] range of each block in the global sorted key list
+  int64_t shard_gbegin;     // position of this owner's first slot in that list
+  int gather;               // small groups exchange per-rank partial sums (needs part / mine / gcol / blk_gc)
+  int pad2;
+  // optional [4]: nanoseconds that thread block 0 spent, summed over the launch's groups, in
+  // [0] commit + gradients, [1] arrival + cross-GPU wait, [2] sums + update + margins, [3] the in-GPU barrier
+  uint64_t* trace;
 };
 
 struct DarlinHyper {
@@ -235,9 +247,9 @@ __device__ __forceinline__ int64_t find_col_from(const int64_t* col_ptr, int64_t
 
 // ---- phase A: block gradient (G,U) pushed into the owners' accumulators
 __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
-                                                 int64_t lc1, int buf, size_t gwarp, size_t nwarps, int lane) {
+                                                 int64_t lc1, int64_t p0, int64_t p1, int buf, float2* mine, int64_t bias,
+                                                 size_t gwarp, size_t nwarps, int lane) {
   const int64_t boff = (int64_t)buf * P.gu_stride;
-  const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
   const bool binary = Wk.vals == nullptr;
   const bool shares = kRangeWalk && Wk.col_of == nullptr;
   int64_t base = p0 + (int64_t)gwarp * 32, end = p1, step = (int64_t)nwarps * 32, hint = -1;
@@ -283,8 +295,12 @@ __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const D
     const int64_t pj = __shfl_up_sync(0xffffffffu, j, 1);
     const bool head = valid && j >= 0 && (lane == 0 || pj != j);
     if (head) {
-      float2* acc = P.gu[Wk.gowner[j]] + boff + Wk.gslot[j];
-      if (P.world > 1) red_add_v2_f32(acc, g, u); else red_add_v2_f32_gpu(acc, g, u);
+      if (mine != nullptr) {   // gather group: this rank's own partial sums
+        red_add_v2_f32_gpu(mine + bias + Wk.gcol[j], g, u);
+      } else {
+        float2* acc = P.gu[Wk.gowner[j]] + boff + Wk.gslot[j];
+        if (P.world > 1) red_add_v2_f32(acc, g, u); else red_add_v2_f32_gpu(acc, g, u);
+      }
     }
   }
 }
@@ -319,6 +335,13 @@ __device__ __forceinline__ DarlinStep darlin_step(float g, float u_sum, float wk
   return r;
 }
 
+// Where a column's summed (G,U) comes from: the owner's accumulator (smem == nullptr) or, for a gather group,
+// the group's vector in shared memory, element smem[bias + global position of the column]
+struct SumSrc {
+  const float2* smem;
+  int64_t bias;
+};
+
 __device__ __forceinline__ float2 ld_gu(const float2* p, bool multi) {
   float2 v;
   if (multi) asm volatile("ld.relaxed.sys.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
@@ -330,12 +353,12 @@ __device__ __forceinline__ float2 ld_gu(const float2* p, bool multi) {
 // right away (the unfused baseline); the fused pass leaves them for the workers and zeroes them a block later.
 __device__ __forceinline__ void darlin_update_weight(const DarlinPeers& P, const DarlinServer& S,
                                                      const DarlinHyper& H, int64_t s0, int64_t s1, int buf, bool clear,
-                                                     size_t gtid, size_t gsz) {
+                                                     size_t gtid, size_t gsz, SumSrc src = SumSrc{nullptr, 0}) {
   float* w = P.w[P.rank];
   float2* gu = P.gu[P.rank] + (int64_t)buf * P.gu_stride;
   float vmax = 0.f;
   for (int64_t k = s0 + (int64_t)gtid; k < s1; k += (int64_t)gsz) {
-    const float2 a = __ldcg(gu + k);
+    const float2 a = src.smem != nullptr ? src.smem[src.bias + k] : __ldcg(gu + k);   // (bias includes the shard's start)
     if (clear) gu[k] = make_float2(0.f, 0.f);
     if (!S.active[k]) continue;
     const DarlinStep st = darlin_step(a.x, a.y, w[k], S.delta[k], H);
@@ -362,12 +385,14 @@ __device__ __forceinline__ void darlin_clear_gu(const DarlinPeers& P, int64_t s0
 // ---- worker's copy of a block's columns brought up to date (w, δ, active set): the same step as the owner's,
 // from the same sums.  Runs one phase after the block's margin update, when no CTA reads these columns any more.
 __device__ __forceinline__ void darlin_commit(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H,
-                                              int64_t lc0, int64_t lc1, int buf, size_t gtid, size_t gsz) {
+                                              int64_t lc0, int64_t lc1, int buf, size_t gtid, size_t gsz,
+                                              SumSrc src = SumSrc{nullptr, 0}) {
   const int64_t boff = (int64_t)buf * P.gu_stride;
   const bool multi = P.world > 1;
   for (int64_t j = lc0 + (int64_t)gtid; j < lc1; j += (int64_t)gsz) {
     if (!Wk.active[j]) continue;
-    const float2 a = ld_gu(P.gu[Wk.gowner[j]] + boff + Wk.gslot[j], multi);
+    const float2 a = src.smem != nullptr ? src.smem[src.bias + Wk.gcol[j]]
+                                         : ld_gu(P.gu[Wk.gowner[j]] + boff + Wk.gslot[j], multi);
     const DarlinStep st = darlin_step(a.x, a.y, Wk.w[j], Wk.delta[j], H);
     if (st.drop) {
       Wk.active[j] = 0;      // its weight is 0 here (NaN only in the owner's shard)
@@ -401,12 +426,6 @@ __device__ __forceinline__ void darlin_update_margin(const DarlinWorker& Wk, int
 // matters for small blocks.  The choice depends on this rank's columns only (the extra barrier is local).
 constexpr int64_t kWideBlockCols = 16384;
 
-__device__ __forceinline__ bool group_is_wide(const DarlinSched& Q, int b, int ge) {
-  int64_t cols = 0;
-  for (int q = b; q < ge; ++q) cols += Q.blk_lc[2 * Q.order[q] + 1] - Q.blk_lc[2 * Q.order[q]];
-  return cols > (Q.wide_cols > 0 ? (int64_t)Q.wide_cols : kWideBlockCols);
-}
-
 // first step of a wide block: step every column, commit it, keep Δw for the margin update
 __device__ __forceinline__ void darlin_step_columns(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H,
                                                     int64_t lc0, int64_t lc1, int buf, size_t gtid, size_t gsz) {
@@ -430,8 +449,8 @@ __device__ __forceinline__ void darlin_step_columns(const DarlinWorker& Wk, cons
 }
 
 // second step of a wide block: m_i += y_i x_ij Δw_j with Δw from Wk.dw
-__device__ __forceinline__ void darlin_margin_from_dw(const DarlinWorker& Wk, int64_t lc0, int64_t lc1, size_t gtid, size_t gsz) {
-  const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
+__device__ __forceinline__ void darlin_margin_from_dw(const DarlinWorker& Wk, int64_t lc0, int64_t lc1, int64_t p0, int64_t p1,
+                                                      size_t gtid, size_t gsz) {
   const int lane = threadIdx.x & 31;
   const bool shares = kRangeWalk && Wk.col_of == nullptr;
   int64_t base = p0 + (int64_t)gtid - lane, end = p1, step = (int64_t)gsz, hint = -1;
@@ -458,8 +477,8 @@ __device__ __forceinline__ void darlin_margin_from_dw(const DarlinWorker& Wk, in
 // worker-side column state (w, δ, active) is NOT written here — other CTAs are still reading it — but one
 // phase later by darlin_commit.
 __device__ __forceinline__ void darlin_step_margin(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H,
-                                                   int64_t lc0, int64_t lc1, int buf, size_t gtid, size_t gsz) {
-  const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
+                                                   int64_t lc0, int64_t lc1, int64_t p0, int64_t p1, int buf, size_t gtid,
+                                                   size_t gsz, SumSrc src = SumSrc{nullptr, 0}) {
   const int lane = threadIdx.x & 31;
   const int64_t boff = (int64_t)buf * P.gu_stride;
   const bool multi = P.world > 1;
@@ -475,7 +494,8 @@ __device__ __forceinline__ void darlin_step_margin(const DarlinWorker& Wk, const
                                 : find_col_warp(Wk.col_ptr, lc0, lc1, e, valid);
     if (shares) hint = __shfl_sync(0xffffffffu, j, 31);
     if (!valid || !Wk.active[j]) continue;
-    const float2 a = ld_gu(P.gu[Wk.gowner[j]] + boff + Wk.gslot[j], multi);
+    const float2 a = src.smem != nullptr ? src.smem[src.bias + Wk.gcol[j]]
+                                         : ld_gu(P.gu[Wk.gowner[j]] + boff + Wk.gslot[j], multi);
     const DarlinStep st = darlin_step(a.x, a.y, Wk.w[j], Wk.delta[j], H);
     if (st.d != 0.f) {
       const uint32_t i = Wk.row_idx[e];
@@ -485,13 +505,113 @@ __device__ __forceinline__ void darlin_step_margin(const DarlinWorker& Wk, const
   }
 }
 
+// ---- small groups on several GPUs: partial sums gathered on every rank
+// A group with at most kGatherCols columns over all owners does not push into the owners' accumulators.  Every
+// rank sums its gradients into a buffer of its own (GPU-scope reductions, nothing leaves the GPU, no system-scope
+// fence per thread block); the thread block that completes the rank's count copies that buffer into every
+// rank's inbox (coalesced peer stores), fences once and raises the arrival counters.  After the one cross-GPU
+// wait each thread block adds the `world` partial vectors in rank order into shared memory — every rank gets
+// bit for bit the same sums, whatever the timing — and the owner's update, the margin update and the commit of
+// the worker's columns all read them from there: no load crosses NVLink in phase C.  With 300 blocks of ~160
+// columns and 8 GPUs this path decides the time of a pass (a block is a few microseconds of work between two
+// synchronisations).
+constexpr int kGatherCols = 2048;
+
+// Everything the pass needs to know about the block at one position of the order, fetched ahead of time
+// into shared memory: a group costs a handful of microseconds, and chasing order -> block table -> column
+// offsets through global memory at the start of every phase was a third of that.
+struct BlkMeta {
+  int64_t p0, p1;      // CSC positions of the block's non-zeros on this worker
+  int64_t gc0;         // first column of the block in the global sorted key list
+  int32_t lc0, lc1;    // local columns
+  int32_t sl0, sl1;    // slots on this owner
+  int32_t gw;          // columns of the block over all owners
+  int32_t blk;         // block id
+};
+constexpr int kMetaSlots = 512;
+
+__device__ __forceinline__ void load_meta(const DarlinWorker& Wk, const DarlinSched& Q, int first, int count, BlkMeta* m) {
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    const int blk = Q.order[first + i];
+    BlkMeta x;
+    x.blk = blk;
+    x.lc0 = (int32_t)Q.blk_lc[2 * blk]; x.lc1 = (int32_t)Q.blk_lc[2 * blk + 1];
+    x.sl0 = (int32_t)Q.blk_sl[2 * blk]; x.sl1 = (int32_t)Q.blk_sl[2 * blk + 1];
+    x.p0 = Wk.col_ptr[x.lc0]; x.p1 = Wk.col_ptr[x.lc1];
+    x.gc0 = Q.blk_gc != nullptr ? Q.blk_gc[2 * blk] : 0;
+    x.gw = Q.blk_gc != nullptr ? (int32_t)(Q.blk_gc[2 * blk + 1] - Q.blk_gc[2 * blk]) : 0x7fffffff / 4096;
+    m[i] = x;
+  }
+}
+// of the blocks m[0 .. n): local columns, columns over all owners
+__device__ __forceinline__ int64_t meta_lcols(const BlkMeta* m, int n) {
+  int64_t c = 0;
+  for (int i = 0; i < n; ++i) c += m[i].lc1 - m[i].lc0;
+  return c;
+}
+__device__ __forceinline__ int64_t meta_gcols(const BlkMeta* m, int n) {
+  int64_t c = 0;
+  for (int i = 0; i < n; ++i) c += m[i].gw;
+  return c;
+}
+// index of block m[i]'s first column inside its group's vector, minus the block's first global column:
+// adding a column's global position gives its place in the vector
+__device__ __forceinline__ int64_t meta_bias(const BlkMeta* m, int i) {
+  int64_t off = 0;
+  for (int k = 0; k < i; ++k) off += m[k].gw;
+  return off - m[i].gc0;
+}
+
+// arrival of a gather group (see cta_arrive_all for the two-level count)
+__device__ __forceinline__ void cta_arrive_gather(const DarlinPeers& P, uint64_t* local_ctr, uint64_t local_target, int n,
+                                                  int buf, bool* s_last) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    unsigned long long prev;
+    asm volatile("atom.acq_rel.gpu.global.add.u64 %0, [%1], %2;" : "=l"(prev) : "l"(local_ctr), "l"(1ull) : "memory");
+    *s_last = prev + 1ull == local_target;
+  }
+  __syncthreads();
+  if (!*s_last) return;
+  const size_t slot = ((size_t)buf * P.world + P.rank) * kGatherCols;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float2 v = __ldcg(P.mine + i);
+    P.mine[i] = make_float2(0.f, 0.f);        // ready for the next group
+    for (int t = 0; t < P.world; ++t) {
+      float2* dst = P.part[t] + slot + i;
+      if (t == P.rank) *dst = v;
+      else asm volatile("st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(dst), "f"(v.x), "f"(v.y) : "memory");
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < P.world) {
+    __threadfence_system();
+    red_release_sys_add_u64(P.arrive[threadIdx.x], 1ull);
+  }
+}
+
+// sums of a gather group in shared memory: the partial vectors of all ranks added in rank order
+__device__ __forceinline__ void gather_reduce(const DarlinPeers& P, int n, int buf, float2* s_sum) {
+  const float2* in = P.part[P.rank] + (size_t)buf * P.world * kGatherCols;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float2 a = make_float2(0.f, 0.f);
+    for (int r = 0; r < P.world; ++r) {
+      const float2 v = __ldcg(in + (size_t)r * kGatherCols + c);   // written by other GPUs: from L2
+      a.x = __fadd_rn(a.x, v.x);
+      a.y = __fadd_rn(a.y, v.y);
+    }
+    s_sum[c] = a;
+  }
+  __syncthreads();
+}
+
 // worker view for the block at position q of the order: in out-of-core mode its row ids and values sit
 // in a staging buffer; the phases index them with absolute CSC positions, so the pointers are biased by p0
-__device__ __forceinline__ DarlinWorker worker_for(const DarlinWorker& Wk, const DarlinSched& Q, int q, int64_t lc0,
-                                                   int64_t lc1) {
+__device__ __forceinline__ DarlinWorker worker_for(const DarlinWorker& Wk, const DarlinSched& Q, int q, int64_t p0,
+                                                   int64_t p1) {
   DarlinWorker W = Wk;
   if (Q.stage_base != nullptr) {
-    const int64_t p0 = Wk.col_ptr[lc0], p1 = Wk.col_ptr[lc1];
     const uint32_t* base = reinterpret_cast<const uint32_t*>(Q.stage_base[q]);
     W.row_idx = base - p0;
     W.vals = Wk.vals != nullptr ? reinterpret_cast<const float*>(base + (p1 - p0)) - p0 : nullptr;
@@ -503,6 +623,8 @@ __global__ void __launch_bounds__(512)
 darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q, DarlinHyper H) {
   __shared__ bool s_ok, s_last;
   __shared__ uint32_t s_abort;
+  __shared__ float2 s_sum[kGatherCols];     // sums of the gather group in flight (kept until the next one is reduced)
+  __shared__ BlkMeta s_meta[kMetaSlots];    // metadata of a window of the order, one group of history in front
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t gsz = (size_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
@@ -514,46 +636,67 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
   // weights that are up to `group - 1` block updates old — the bounded-delay schedule of the reference
   // (wait_time = time - tau, src/linear_method/darling.cc:45-69) with one set of synchronisation points per group.
   // Group number `seq` (counted over all launches, the same on every rank) accumulates into buffer seq % 3.
-  const int group = Q.group > 0 ? Q.group : 1;
+  const int group = min(Q.group > 0 ? Q.group : 1, kMetaSlots / 4);
+  const bool multi = P.world > 1;
+  const int64_t wide_cols = Q.wide_cols > 0 ? (int64_t)Q.wide_cols : kWideBlockCols;
   uint64_t seq = Q.seq0;
+  int wbase = 0, wend = 0;     // s_meta[q - wbase] describes position q of the order, for wbase <= q < wend
   for (int b = 0; b < Q.nblk; b += group) {
     if (threadIdx.x == 0) s_abort = *(volatile uint32_t*)Q.abort_flag;
     __syncthreads();
     if (s_abort) break;  // uniform over the CTA
     const int ge = min(b + group, Q.nblk);
+    const int pb = max(b - group, 0);
+    if (ge > wend) {     // next window: from the previous group (its commit is still to come) onwards
+      wbase = pb;
+      wend = min(Q.nblk, wbase + kMetaSlots);
+      load_meta(Wk, Q, wbase, wend - wbase, s_meta);
+      __syncthreads();
+    }
+    const BlkMeta* mp = s_meta + (pb - wbase);   // previous group (b - pb blocks)
+    const BlkMeta* mg = s_meta + (b - wbase);    // this group (ge - b blocks)
+    const int ng = ge - b, np = b - pb;
     ++seq;
     const int buf = (int)(seq % 3), pbuf = (int)((seq + 2) % 3);
+    const bool timed = Q.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+    uint64_t t0 = timed ? globaltimer_ns() : 0, t1;
 
     // A: gradient + push, then announce arrival at every owner.  In the same phase: the worker's copy of the
     // previous group's columns is brought up to date (a different set of columns; all CTAs are past its
-    // phase C; the previous launch did this itself for its last group).
-    if (b > 0 && !group_is_wide(Q, max(b - group, 0), b)) {    // (a wide group committed its columns itself)
-      for (int q = max(b - group, 0); q < b; ++q) {
-        const int blk = Q.order[q];
-        darlin_commit(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], pbuf, gtid, gsz);
-      }
+    // phase C; the previous launch did this itself for its last group; a wide group committed its columns itself).
+    const bool prev_gather = np > 0 && multi && Q.gather != 0 && Q.blk_gc != nullptr && meta_gcols(mp, np) <= kGatherCols;
+    const bool prev_commit = np > 0 && (prev_gather || meta_lcols(mp, np) <= wide_cols);
+    const bool gat = multi && Q.gather != 0 && Q.blk_gc != nullptr && meta_gcols(mg, ng) <= kGatherCols;
+    const int gcols = gat ? (int)meta_gcols(mg, ng) : 0;
+    const bool wide = !gat && meta_lcols(mg, ng) > wide_cols;
+    if (prev_commit && !prev_gather) {   // sums in the owners' accumulators: read them before this rank arrives
+      for (int i = 0; i < np; ++i) darlin_commit(Wk, P, H, mp[i].lc0, mp[i].lc1, pbuf, gtid, gsz);
     }
-    for (int q = b; q < ge; ++q) {
-      const int blk = Q.order[q];
-      const int64_t lc0 = Q.blk_lc[2 * blk], lc1 = Q.blk_lc[2 * blk + 1];
-      darlin_grad_push(worker_for(Wk, Q, q, lc0, lc1), P, lc0, lc1, buf, gtid >> 5, gsz >> 5, lane);
+    for (int i = 0; i < ng; ++i) {
+      darlin_grad_push(worker_for(Wk, Q, b + i, mg[i].p0, mg[i].p1), P, mg[i].lc0, mg[i].lc1, mg[i].p0, mg[i].p1, buf,
+                       gat ? P.mine : nullptr, gat ? meta_bias(mg, i) : 0, gtid >> 5, gsz >> 5, lane);
     }
-    cta_arrive_all(P, Q.local_bar + 1, seq * G, &s_last);
-    if (!cta_wait_counter(P.arrive[P.rank], seq * (uint64_t)P.world, P.timeout_ns, P.world > 1, &s_ok)) {
-      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 11); *Q.abort_flag = 1u; }
+    if (timed) { t1 = globaltimer_ns(); Q.trace[0] += t1 - t0; t0 = t1; }
+    if (gat) cta_arrive_gather(P, Q.local_bar + 1, seq * G, gcols, buf, &s_last);
+    else cta_arrive_all(P, Q.local_bar + 1, seq * G, &s_last);
+    if (prev_commit && prev_gather) {    // sums still in shared memory: commit while the other ranks arrive
+      for (int i = 0; i < np; ++i)
+        darlin_commit(Wk, P, H, mp[i].lc0, mp[i].lc1, pbuf, gtid, gsz, SumSrc{s_sum, meta_bias(mp, i)});
+    }
+    if (!cta_wait_counter(P.arrive[P.rank], seq * (uint64_t)P.world, P.timeout_ns, multi, &s_ok)) {
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)mg[0].blk, 11); *Q.abort_flag = 1u; }
       break;
     }
+    if (timed) { t1 = globaltimer_ns(); Q.trace[1] += t1 - t0; t0 = t1; }
+    if (gat) gather_reduce(P, gcols, buf, s_sum);
     // B and C in one phase.  Owner: update this shard's slots of the group's blocks; zero the accumulators of
     // the previous group, which every rank has read for the last time (its arrival above came after that).
-    for (int q = b; q < ge; ++q) {
-      const int blk = Q.order[q];
-      darlin_update_weight(P, S, H, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], buf, false, gtid, gsz);
+    for (int i = 0; i < ng; ++i) {
+      const SumSrc src = gat ? SumSrc{s_sum, meta_bias(mg, i) + Q.shard_gbegin} : SumSrc{nullptr, 0};
+      darlin_update_weight(P, S, H, mg[i].sl0, mg[i].sl1, buf, false, gtid, gsz, src);
     }
-    if (b > 0) {
-      for (int q = max(b - group, 0); q < b; ++q) {
-        const int blk = Q.order[q];
-        darlin_clear_gu(P, Q.blk_sl[2 * blk], Q.blk_sl[2 * blk + 1], pbuf, gtid, gsz);
-      }
+    if (np > 0) {
+      for (int i = 0; i < np && !prev_gather; ++i) darlin_clear_gu(P, mp[i].sl0, mp[i].sl1, pbuf, gtid, gsz);
     } else if (Q.prev != nullptr) {
       for (int q = 0; q < Q.nprev; ++q) {
         const int blk = Q.prev[q];
@@ -561,36 +704,32 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       }
     }
     // Worker: margins of the rows that the group's columns touch.
-    const bool wide = group_is_wide(Q, b, ge);
     if (wide) {
-      for (int q = b; q < ge; ++q) {
-        const int blk = Q.order[q];
-        darlin_step_columns(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], buf, gtid, gsz);
-      }
+      for (int i = 0; i < ng; ++i) darlin_step_columns(Wk, P, H, mg[i].lc0, mg[i].lc1, buf, gtid, gsz);
       __syncthreads();
       if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
       if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
-        if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 13); *Q.abort_flag = 1u; }
+        if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)mg[0].blk, 13); *Q.abort_flag = 1u; }
         break;
       }
     }
-    for (int q = b; q < ge; ++q) {
-      const int blk = Q.order[q];
-      const int64_t lc0 = Q.blk_lc[2 * blk], lc1 = Q.blk_lc[2 * blk + 1];
-      if (wide) darlin_margin_from_dw(worker_for(Wk, Q, q, lc0, lc1), lc0, lc1, gtid, gsz);
-      else darlin_step_margin(worker_for(Wk, Q, q, lc0, lc1), P, H, lc0, lc1, buf, gtid, gsz);
+    for (int i = 0; i < ng; ++i) {
+      const DarlinWorker W = worker_for(Wk, Q, b + i, mg[i].p0, mg[i].p1);
+      if (wide) darlin_margin_from_dw(W, mg[i].lc0, mg[i].lc1, mg[i].p0, mg[i].p1, gtid, gsz);
+      else darlin_step_margin(W, P, H, mg[i].lc0, mg[i].lc1, mg[i].p0, mg[i].p1, buf, gtid, gsz,
+                              gat ? SumSrc{s_sum, meta_bias(mg, i)} : SumSrc{nullptr, 0});
     }
     __syncthreads();
+    if (timed) { t1 = globaltimer_ns(); Q.trace[2] += t1 - t0; t0 = t1; }
     if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }
     if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {
-      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)Q.order[b], 14); *Q.abort_flag = 1u; }
+      if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)mg[0].blk, 14); *Q.abort_flag = 1u; }
       break;
     }
+    if (timed) { t1 = globaltimer_ns(); Q.trace[3] += t1 - t0; t0 = t1; }
     if (ge == Q.nblk && !wide) {  // last group of the launch: bring the worker's copy of its columns up to date now
-      for (int q = b; q < ge; ++q) {
-        const int blk = Q.order[q];
-        darlin_commit(Wk, P, H, Q.blk_lc[2 * blk], Q.blk_lc[2 * blk + 1], buf, gtid, gsz);
-      }
+      for (int i = 0; i < ng; ++i)
+        darlin_commit(Wk, P, H, mg[i].lc0, mg[i].lc1, buf, gtid, gsz, gat ? SumSrc{s_sum, meta_bias(mg, i)} : SumSrc{nullptr, 0});
     }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) Q.local_bar[3] = bar;

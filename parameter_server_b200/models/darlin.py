@@ -136,7 +136,7 @@ class DarlinSolver:
 
     def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused",
                  out_of_core: bool = False, prefetch_depth: int = 3, blocks_per_launch: Optional[int] = None,
-                 ctas_per_sm: Optional[int] = None, wide_block_cols: int = 0):
+                 ctas_per_sm: Optional[int] = None, wide_block_cols: int = 0, gather_small_groups: bool = True):
         """``out_of_core``: keep the column blocks (row ids, values) in pinned host memory and stream each
         block to the GPU on a side stream ahead of its turn in the block order — the role of the
         reference's ``FeatureStation`` in ``-mmap_training_data`` mode with its task-id keyed look-ahead
@@ -149,10 +149,15 @@ class DarlinSolver:
         # groups of blocks with more local columns than this fetch the owners' sums once per column instead of
         # once per non-zero, at the price of one more in-GPU barrier (0: the kernel's default, 16384)
         self.wide_block_cols = int(wide_block_cols)
+        # groups of blocks with at most 2048 columns over all owners: gather every rank's partial sums on every
+        # rank (one cross-GPU wait, no NVLink load in the margin update) instead of pushing into the owners
+        self.gather_small_groups = bool(gather_small_groups)
         self.out_of_core, self.prefetch_depth = out_of_core, max(int(prefetch_depth), 2)
         # out-of-core mode: blocks per kernel launch, rounded up to a multiple of max_block_delay + 1.  A launch
         # costs about 28 us, so small blocks are batched (up to 16); a batch is also the unit that must be on the
         # device before its kernel starts, so it is kept near 24 MB (chosen in _to_host_blocks when not given)
+        if cfg.max_block_delay > 127:
+            raise ValueError("max_block_delay above 127 is not supported by the pass kernel")
         self._launch_group = max(int(cfg.max_block_delay), 0) + 1
         self._blocks_per_launch_arg = blocks_per_launch
         self.blocks_per_launch = self._round_launch(16 if blocks_per_launch is None else blocks_per_launch)
@@ -333,6 +338,8 @@ class DarlinSolver:
         sl1 = (gc1 - self.shard_begin[r]).clamp_(0, self.slots)
         self.blk_lc = torch.stack([lc0, lc1], 1).contiguous()
         self.blk_sl = torch.stack([sl0, sl1], 1).contiguous()
+        self.blk_gc = torch.stack([gc0, gc1], 1).contiguous()      # every block's range in the global sorted key list
+        self.gcol = gidx.contiguous()                               # every local column's position in that list
         self.nblk = nblk
         # ---- worker state
         f32 = torch.float32
@@ -360,6 +367,11 @@ class DarlinSolver:
         self.srv_gu = g.alloc((3, cap, 2), f32)
         self._gu_stride = cap
         self._prev_tail = None          # blocks of the group that ran last (their accumulators are zeroed next)
+        # small groups of blocks on several GPUs: every rank's partial sums are gathered on every rank instead of
+        # pushed into the owners' accumulators (csrc/darlin_kernels.cu, kGatherCols = 2048)
+        self.srv_part = g.alloc((3, W, 2048, 2), f32)
+        self.part_mine = torch.zeros((2048, 2), dtype=f32, device=dev)
+        self.phase_ns = torch.zeros(4, dtype=torch.int64, device=dev)     # in-kernel phase timers (thread block 0)
         self.arrive = g.alloc((1,), torch.int64)
         self.srv_delta = torch.full((cap,), self.cfg.delta_init, dtype=f32, device=dev)
         self.srv_active = torch.ones(cap, dtype=torch.uint8, device=dev)
@@ -456,18 +468,22 @@ class DarlinSolver:
         return N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), n, group, self.seq,
                              self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr(), None,
                              None if prev is None else prev.data_ptr(), 0 if prev is None else prev.numel(),
-                             self.wide_block_cols)
+                             self.wide_block_cols, self.blk_gc.data_ptr(), int(self.shard_begin[self.group.rank]),
+                             1 if self.gather_small_groups else 0, 0, self.phase_ns.data_ptr())
 
     def _build_structs(self):
         Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),
                             0 if self.vals is None else self.vals.data_ptr(), self.ym.data_ptr(),
                             0 if self.col_of is None else self.col_of.data_ptr(), self.w.data_ptr(), self.delta.data_ptr(),
                             self.active.data_ptr(),
-                            self.gslot.data_ptr(), self.gowner.data_ptr(), self.dw.data_ptr(), self.cols, self.rows, 0)
+                            self.gslot.data_ptr(), self.gowner.data_ptr(), self.dw.data_ptr(), self.cols, self.rows, 0,
+                            self.gcol.data_ptr())
         P = N.DarlinPeers()
         for r in range(self.group.world):
             P.w[r], P.gu[r] = self.srv_w.ptrs[r], self.srv_gu.ptrs[r]
             P.arrive[r] = self.arrive.ptrs[r]
+            P.part[r] = self.srv_part.ptrs[r]
+        P.mine = self.part_mine.data_ptr()
         P.rank, P.world, P.timeout_ns = self.group.rank, self.group.world, int(self.timeout_s * 1e9)
         P.gu_stride = self._gu_stride
         S = N.DarlinServer(self.srv_delta.data_ptr(), self.srv_active.data_ptr(), self.violation.data_ptr(), self.slots)
@@ -523,6 +539,7 @@ class DarlinSolver:
         self.active.fill_(1)
         self.srv_w.local.zero_()
         self.srv_gu.local.zero_()
+        self.part_mine.zero_()
         self._prev_tail = None
         self.srv_delta.fill_(self.cfg.delta_init)
         self.srv_active.fill_(1)
@@ -616,6 +633,13 @@ class DarlinSolver:
                 if nnz_b:
                     N.check(lib.psb_darlin_update_margin(C.byref(self._Wk), lc0, lc1, nnz_b, s), "update_margin")
                 self.kernel_launches += 2
+
+    def phase_times_ms(self, reset: bool = True) -> dict:
+        """Time thread block 0 spent per phase since the last reset, from in-kernel globaltimer reads."""
+        t = (self.phase_ns.to(torch.float64) / 1e6).tolist()
+        if reset:
+            self.phase_ns.zero_()
+        return {"commit_grad": t[0], "arrive_wait": t[1], "update_margin": t[2], "gpu_barrier": t[3]}
 
     def evaluate(self) -> tuple:
         """(objective, nnz_w, nnz_active, violation) summed/maxed over ranks (Darling::evaluateProgress)."""

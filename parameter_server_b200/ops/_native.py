@@ -98,12 +98,12 @@ class DarlinWorker(C.Structure):
     _fields_ = [("col_ptr", C.c_void_p), ("row_idx", C.c_void_p), ("vals", C.c_void_p), ("ym", C.c_void_p),
                 ("col_of", C.c_void_p), ("w", C.c_void_p), ("delta", C.c_void_p), ("active", C.c_void_p),
                 ("gslot", C.c_void_p), ("gowner", C.c_void_p), ("dw", C.c_void_p), ("cols", C.c_int64),
-                ("rows", C.c_int), ("pad", C.c_int)]
+                ("rows", C.c_int), ("pad", C.c_int), ("gcol", C.c_void_p)]
 
 
 class DarlinPeers(C.Structure):
     _fields_ = [("w", _P8), ("gu", _P8), ("arrive", _P8), ("rank", C.c_int), ("world", C.c_int),
-                ("timeout_ns", C.c_uint64), ("gu_stride", C.c_int64)]
+                ("timeout_ns", C.c_uint64), ("gu_stride", C.c_int64), ("part", _P8), ("mine", C.c_void_p)]
 
 
 class DarlinServer(C.Structure):
@@ -114,7 +114,9 @@ class DarlinSched(C.Structure):
     _fields_ = [("order", C.c_void_p), ("blk_lc", C.c_void_p), ("blk_sl", C.c_void_p), ("nblk", C.c_int),
                 ("group", C.c_int), ("seq0", C.c_uint64), ("local_bar", C.c_void_p), ("bar0", C.c_uint64),
                 ("abort_flag", C.c_void_p), ("status", C.c_void_p), ("stage_base", C.c_void_p),
-                ("prev", C.c_void_p), ("nprev", C.c_int), ("wide_cols", C.c_int)]
+                ("prev", C.c_void_p), ("nprev", C.c_int), ("wide_cols", C.c_int),
+                ("blk_gc", C.c_void_p), ("shard_gbegin", C.c_int64), ("gather", C.c_int), ("pad2", C.c_int),
+                ("trace", C.c_void_p)]
 
 
 class DarlinHyper(C.Structure):
