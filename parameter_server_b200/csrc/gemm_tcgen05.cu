@@ -500,7 +500,7 @@ int psb_gemm_tn_tf32(const float* a, const float* b, float* out, int M, int N, i
   static int sms = 0;
   if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   const long tiles_p = (long)((M + kBM - 1) / kBM) * ((N + kPBN - 1) / kPBN);
-  if (tiles_p >= sms && getenv("PSB_GEMM_SIMPLE") == nullptr) {
+  if (tiles_p >= sms) {
     r = make_map(&mb, b, N, K, ldb, kPBN);
     if (r) return r;
     const size_t smem_p = sizeof(GemmSmemP) + 1024;
