@@ -67,6 +67,12 @@ struct DarlinPeers {
   // and this rank's own partial sums of the group in flight
   float2* part[PSB_MAX_RANKS];
   float2* mine;
+  // very wide groups on several GPUs (see kListCols): per LOCAL column of rank r, its partial (G,U), its slot
+  // in the owner's shard and the owner's answer Δw; and the second arrival counter of those groups
+  float2* colgu[PSB_MAX_RANKS];
+  const uint32_t* colslot[PSB_MAX_RANKS];
+  float* coldw[PSB_MAX_RANKS];
+  uint64_t* arrive2[PSB_MAX_RANKS];
 };
 
 struct DarlinServer {     // local arrays of this rank's shard
@@ -74,6 +80,7 @@ struct DarlinServer {     // local arrays of this rank's shard
   uint8_t* active;        // slots
   uint32_t* violation;    // float bits of max violation (non-negative)
   int64_t slots;
+  float* d_slot;          // slots: Δw of the group in flight (NaN: key dropped), very wide groups only
 };
 
 struct DarlinSched {
@@ -103,6 +110,12 @@ struct DarlinSched {
   // optional [4]: nanoseconds that thread block 0 spent, summed over the launch's groups, in
   // [0] commit + gradients, [1] arrival + cross-GPU wait, [2] sums + update + margins, [3] the in-GPU barrier
   uint64_t* trace;
+  // very wide groups: every rank's block table (local column range of every block) and the first local column
+  // of every owner's key range on every rank, so that an owner can address the senders' columns of its range
+  const int64_t* all_blk_lc;   // [world][nblocks_total][2]
+  const int64_t* all_cb;       // [world][world + 1]
+  int64_t nblocks_total;
+  int64_t list_cols;           // groups with more columns over all owners than this take the list path (0: kListCols)
 };
 
 struct DarlinHyper {
@@ -135,8 +148,8 @@ __device__ __forceinline__ void red_add_v2_f32(float2* p, float a, float b) {
 // The notifications go out from `world` threads at once: a release at system scope waits for the
 // thread's earlier remote writes, so one thread sending them one after the other would pay a
 // round trip per rank.
-__device__ __forceinline__ void cta_arrive_all(const DarlinPeers& P, uint64_t* local_ctr, uint64_t local_target,
-                                               bool* s_last) {
+__device__ __forceinline__ void cta_arrive_all(const DarlinPeers& P, uint64_t* const* ctrs, uint64_t* local_ctr,
+                                               uint64_t local_target, bool* s_last) {
   // With a single rank nothing leaves the GPU and every fence, release and poll stays at GPU scope:
   // system-scope operations issued at every synchronisation point kept host-to-device copies that
   // ran beside the kernel from overlapping with it (out-of-core pass = copy time + kernel time).
@@ -150,7 +163,7 @@ __device__ __forceinline__ void cta_arrive_all(const DarlinPeers& P, uint64_t* l
   }
   __syncthreads();
   if (*s_last && threadIdx.x < P.world) {
-    uint64_t* ctr = P.arrive[threadIdx.x];
+    uint64_t* ctr = ctrs[threadIdx.x];
     if (multi) {
       __threadfence_system();
       red_release_sys_add_u64(ctr, 1ull);
@@ -248,7 +261,7 @@ __device__ __forceinline__ int64_t find_col_from(const int64_t* col_ptr, int64_t
 // ---- phase A: block gradient (G,U) pushed into the owners' accumulators
 __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const DarlinPeers& P, int64_t lc0,
                                                  int64_t lc1, int64_t p0, int64_t p1, int buf, float2* mine, int64_t bias,
-                                                 size_t gwarp, size_t nwarps, int lane) {
+                                                 size_t gwarp, size_t nwarps, int lane, bool by_local_column = false) {
   const int64_t boff = (int64_t)buf * P.gu_stride;
   const bool binary = Wk.vals == nullptr;
   const bool shares = kRangeWalk && Wk.col_of == nullptr;
@@ -295,8 +308,8 @@ __device__ __forceinline__ void darlin_grad_push(const DarlinWorker& Wk, const D
     const int64_t pj = __shfl_up_sync(0xffffffffu, j, 1);
     const bool head = valid && j >= 0 && (lane == 0 || pj != j);
     if (head) {
-      if (mine != nullptr) {   // gather group: this rank's own partial sums
-        red_add_v2_f32_gpu(mine + bias + Wk.gcol[j], g, u);
+      if (mine != nullptr) {   // gather / list group: this rank's own partial sums
+        red_add_v2_f32_gpu(mine + (by_local_column ? j : bias + Wk.gcol[j]), g, u);
       } else {
         float2* acc = P.gu[Wk.gowner[j]] + boff + Wk.gslot[j];
         if (P.world > 1) red_add_v2_f32(acc, g, u); else red_add_v2_f32_gpu(acc, g, u);
@@ -353,23 +366,26 @@ __device__ __forceinline__ float2 ld_gu(const float2* p, bool multi) {
 // right away (the unfused baseline); the fused pass leaves them for the workers and zeroes them a block later.
 __device__ __forceinline__ void darlin_update_weight(const DarlinPeers& P, const DarlinServer& S,
                                                      const DarlinHyper& H, int64_t s0, int64_t s1, int buf, bool clear,
-                                                     size_t gtid, size_t gsz, SumSrc src = SumSrc{nullptr, 0}) {
+                                                     size_t gtid, size_t gsz, SumSrc src = SumSrc{nullptr, 0},
+                                                     float* d_out = nullptr) {
   float* w = P.w[P.rank];
   float2* gu = P.gu[P.rank] + (int64_t)buf * P.gu_stride;
   float vmax = 0.f;
   for (int64_t k = s0 + (int64_t)gtid; k < s1; k += (int64_t)gsz) {
     const float2 a = src.smem != nullptr ? src.smem[src.bias + k] : __ldcg(gu + k);   // (bias includes the shard's start)
     if (clear) gu[k] = make_float2(0.f, 0.f);
-    if (!S.active[k]) continue;
+    if (!S.active[k]) { if (d_out != nullptr) d_out[k] = 0.f; continue; }
     const DarlinStep st = darlin_step(a.x, a.y, w[k], S.delta[k], H);
     if (st.drop) {
       S.active[k] = 0;
       w[k] = __int_as_float(0x7fffffff);  // NaN sentinel: key filtered
+      if (d_out != nullptr) d_out[k] = __int_as_float(0x7fffffff);
       continue;
     }
     vmax = fmaxf(vmax, st.vio);
     S.delta[k] = st.delta;
     w[k] = __fadd_rn(w[k], st.d);
+    if (d_out != nullptr) d_out[k] = st.d;
   }
   vmax = warp_max(vmax);
   if ((threadIdx.x & 31) == 0 && vmax > 0.f) atomicMax(S.violation, __float_as_uint(vmax));
@@ -606,6 +622,81 @@ __device__ __forceinline__ void gather_reduce(const DarlinPeers& P, int n, int b
   __syncthreads();
 }
 
+// ---- very wide groups on several GPUs: push and pull as bulk transfers over resolved column lists
+// With hundreds of thousands of columns per block and GPU, one small NVLink operation per column (a reduction
+// into the owner's accumulator, a load of its sums) is what a pass costs on 8 GPUs: 7/8 of them leave the GPU.
+// A worker's columns of one owner are contiguous in its local (key) order, and their slots in the owner's
+// shard were resolved once — the steady state of the reference's key cache
+// (src/system/remote_node.cc:96-184).  So for these groups
+//   * a worker sums (G,U) per LOCAL column in its own memory;
+//   * after the arrival the owner reads, for every sender, the contiguous run of that sender's columns in its
+//     key range — the partial sums and their slots — with coalesced peer loads, and adds them into its
+//     accumulators with GPU-scope reductions;
+//   * the owner steps its slots, keeps Δw per slot, and writes Δw back per sender column, again contiguous;
+//   * after a second arrival the worker brings its copy of the columns up to date from Δw (δ follows from Δw by
+//     the owner's formula, NaN = dropped) and moves the margins.
+// Two cross-GPU rounds and four in-GPU barriers per group, all NVLink traffic in full lines.
+constexpr int64_t kListCols = 262144;
+
+// sender r's local columns of block `blk` that this rank owns: [a, e)
+__device__ __forceinline__ void list_range(const DarlinPeers& P, const DarlinSched& Q, int r, int blk, int64_t* a, int64_t* e) {
+  const int64_t* lc = Q.all_blk_lc + ((int64_t)r * Q.nblocks_total + blk) * 2;
+  const int64_t* cb = Q.all_cb + (int64_t)r * (P.world + 1);
+  *a = max(lc[0], cb[P.rank]);
+  *e = min(lc[1], cb[P.rank + 1]);
+}
+
+__device__ __forceinline__ void darlin_list_sum(const DarlinPeers& P, const DarlinSched& Q, int blk, int buf, size_t gtid, size_t gsz) {
+  float2* acc = P.gu[P.rank] + (int64_t)buf * P.gu_stride;
+  for (int r = 0; r < P.world; ++r) {
+    int64_t a, e;
+    list_range(P, Q, r, blk, &a, &e);
+    const bool peer = r != P.rank;
+    for (int64_t j = a + (int64_t)gtid; j < e; j += (int64_t)gsz) {
+      const float2 v = peer ? ld_gu(P.colgu[r] + j, true) : __ldcg(P.colgu[r] + j);
+      if (v.x == 0.f && v.y == 0.f) continue;     // inactive or absent on that worker
+      const uint32_t slot = peer ? ld_relaxed_sys_u32(P.colslot[r] + j) : P.colslot[r][j];
+      red_add_v2_f32_gpu(acc + slot, v.x, v.y);
+    }
+  }
+}
+
+__device__ __forceinline__ void darlin_list_reply(const DarlinPeers& P, const DarlinServer& S, const DarlinSched& Q, int blk,
+                                                  size_t gtid, size_t gsz) {
+  for (int r = 0; r < P.world; ++r) {
+    int64_t a, e;
+    list_range(P, Q, r, blk, &a, &e);
+    const bool peer = r != P.rank;
+    for (int64_t j = a + (int64_t)gtid; j < e; j += (int64_t)gsz) {
+      const uint32_t slot = peer ? ld_relaxed_sys_u32(P.colslot[r] + j) : P.colslot[r][j];
+      const float d = __ldcg(S.d_slot + slot);
+      if (peer) st_relaxed_sys_f32(P.coldw[r] + j, d); else P.coldw[r][j] = d;
+    }
+  }
+}
+
+// worker: its copy of the group's columns from the owners' answers; its partial sums zeroed for the next use
+__device__ __forceinline__ void darlin_list_apply(const DarlinWorker& Wk, const DarlinPeers& P, const DarlinHyper& H, int64_t lc0,
+                                                  int64_t lc1, size_t gtid, size_t gsz) {
+  const float* in = P.coldw[P.rank];
+  float2* mine = P.colgu[P.rank];
+  for (int64_t j = lc0 + (int64_t)gtid; j < lc1; j += (int64_t)gsz) {
+    mine[j] = make_float2(0.f, 0.f);
+    float d = 0.f;
+    if (Wk.active[j]) {
+      d = __ldcg(in + j);
+      if (d != d) {
+        Wk.active[j] = 0;
+        d = 0.f;
+      } else {
+        Wk.delta[j] = fminf(H.delta_max, __fmaf_rn(2.f, fabsf(d), 0.1f));   // the owner's rule (darlin_step)
+        Wk.w[j] = __fadd_rn(Wk.w[j], d);
+      }
+    }
+    Wk.dw[j] = d;
+  }
+}
+
 // worker view for the block at position q of the order: in out-of-core mode its row ids and values sit
 // in a staging buffer; the phases index them with absolute CSC positions, so the pointers are biased by p0
 __device__ __forceinline__ DarlinWorker worker_for(const DarlinWorker& Wk, const DarlinSched& Q, int q, int64_t p0,
@@ -639,7 +730,21 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
   const int group = min(Q.group > 0 ? Q.group : 1, kMetaSlots / 4);
   const bool multi = P.world > 1;
   const int64_t wide_cols = Q.wide_cols > 0 ? (int64_t)Q.wide_cols : kWideBlockCols;
+  const int64_t list_cols = Q.list_cols > 0 ? Q.list_cols : kListCols;
+  // by default only from four GPUs on: on two, one 8-byte peer load per column (the wide path) is cheaper than the
+  // three extra sweeps over the column lists (6.7 against 10.5 ms per pass on 2 x 10^6 rows x 120 non-zeros); on
+  // eight, 7/8 of those loads cross NVLink as small packets and the pass took 30.5 ms
+  const bool can_list = multi && Q.all_blk_lc != nullptr && Q.blk_gc != nullptr && (Q.list_cols > 0 || P.world >= 4);
   uint64_t seq = Q.seq0;
+  uint64_t seq2 = *(volatile uint64_t*)(Q.local_bar + 4);   // list groups completed so far (second arrival counter)
+// in-GPU barrier (bounded); leaves the group loop when it runs out
+#define PSB_LOCAL_BARRIER(code)                                                                            \
+  __syncthreads();                                                                                         \
+  if (threadIdx.x == 0) { __threadfence(); atomicAdd((unsigned long long*)Q.local_bar, 1ull); }            \
+  if (!cta_wait_counter(Q.local_bar, (++bar) * G, P.timeout_ns, false, &s_ok)) {                           \
+    if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)mg[0].blk, code); *Q.abort_flag = 1u; } \
+    break;                                                                                                 \
+  }
   int wbase = 0, wend = 0;     // s_meta[q - wbase] describes position q of the order, for wbase <= q < wend
   for (int b = 0; b < Q.nblk; b += group) {
     if (threadIdx.x == 0) s_abort = *(volatile uint32_t*)Q.abort_flag;
@@ -665,20 +770,23 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
     // previous group's columns is brought up to date (a different set of columns; all CTAs are past its
     // phase C; the previous launch did this itself for its last group; a wide group committed its columns itself).
     const bool prev_gather = np > 0 && multi && Q.gather != 0 && Q.blk_gc != nullptr && meta_gcols(mp, np) <= kGatherCols;
-    const bool prev_commit = np > 0 && (prev_gather || meta_lcols(mp, np) <= wide_cols);
+    const bool prev_list = np > 0 && can_list && meta_gcols(mp, np) > list_cols;
+    const bool prev_commit = np > 0 && !prev_list && (prev_gather || meta_lcols(mp, np) <= wide_cols);
     const bool gat = multi && Q.gather != 0 && Q.blk_gc != nullptr && meta_gcols(mg, ng) <= kGatherCols;
     const int gcols = gat ? (int)meta_gcols(mg, ng) : 0;
-    const bool wide = !gat && meta_lcols(mg, ng) > wide_cols;
+    const bool lst = !gat && can_list && meta_gcols(mg, ng) > list_cols;     // the same choice on every rank
+    const bool wide = !gat && !lst && meta_lcols(mg, ng) > wide_cols;
     if (prev_commit && !prev_gather) {   // sums in the owners' accumulators: read them before this rank arrives
       for (int i = 0; i < np; ++i) darlin_commit(Wk, P, H, mp[i].lc0, mp[i].lc1, pbuf, gtid, gsz);
     }
     for (int i = 0; i < ng; ++i) {
       darlin_grad_push(worker_for(Wk, Q, b + i, mg[i].p0, mg[i].p1), P, mg[i].lc0, mg[i].lc1, mg[i].p0, mg[i].p1, buf,
-                       gat ? P.mine : nullptr, gat ? meta_bias(mg, i) : 0, gtid >> 5, gsz >> 5, lane);
+                       gat ? P.mine : (lst ? P.colgu[P.rank] : nullptr), gat ? meta_bias(mg, i) : 0, gtid >> 5, gsz >> 5,
+                       lane, lst);
     }
     if (timed) { t1 = globaltimer_ns(); Q.trace[0] += t1 - t0; t0 = t1; }
     if (gat) cta_arrive_gather(P, Q.local_bar + 1, seq * G, gcols, buf, &s_last);
-    else cta_arrive_all(P, Q.local_bar + 1, seq * G, &s_last);
+    else cta_arrive_all(P, P.arrive, Q.local_bar + 1, seq * G, &s_last);
     if (prev_commit && prev_gather) {    // sums still in shared memory: commit while the other ranks arrive
       for (int i = 0; i < np; ++i)
         darlin_commit(Wk, P, H, mp[i].lc0, mp[i].lc1, pbuf, gtid, gsz, SumSrc{s_sum, meta_bias(mp, i)});
@@ -688,6 +796,30 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       break;
     }
     if (timed) { t1 = globaltimer_ns(); Q.trace[1] += t1 - t0; t0 = t1; }
+    if (lst) {
+      // owner: sum the senders' runs of columns into the accumulators, step, answer per sender column
+      for (int i = 0; i < ng; ++i) darlin_list_sum(P, Q, mg[i].blk, buf, gtid, gsz);
+      PSB_LOCAL_BARRIER(15)
+      for (int i = 0; i < ng; ++i)
+        darlin_update_weight(P, S, H, mg[i].sl0, mg[i].sl1, buf, true, gtid, gsz, SumSrc{nullptr, 0}, S.d_slot);
+      PSB_LOCAL_BARRIER(16)
+      for (int i = 0; i < ng; ++i) darlin_list_reply(P, S, Q, mg[i].blk, gtid, gsz);
+      ++seq2;
+      cta_arrive_all(P, P.arrive2, Q.local_bar + 2, seq2 * G, &s_last);
+      if (!cta_wait_counter(P.arrive2[P.rank], seq2 * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
+        if (threadIdx.x == 0) { set_status(Q.status, kWaitTimeout, (uint32_t)mg[0].blk, 12); *Q.abort_flag = 1u; }
+        break;
+      }
+      // worker: columns from the answers, then the margins
+      for (int i = 0; i < ng; ++i) darlin_list_apply(Wk, P, H, mg[i].lc0, mg[i].lc1, gtid, gsz);
+      PSB_LOCAL_BARRIER(17)
+      for (int i = 0; i < ng; ++i)
+        darlin_margin_from_dw(worker_for(Wk, Q, b + i, mg[i].p0, mg[i].p1), mg[i].lc0, mg[i].lc1, mg[i].p0, mg[i].p1, gtid, gsz);
+      if (timed) { t1 = globaltimer_ns(); Q.trace[2] += t1 - t0; t0 = t1; }
+      PSB_LOCAL_BARRIER(14)
+      if (timed) { t1 = globaltimer_ns(); Q.trace[3] += t1 - t0; t0 = t1; }
+      continue;
+    }
     if (gat) gather_reduce(P, gcols, buf, s_sum);
     // B and C in one phase.  Owner: update this shard's slots of the group's blocks; zero the accumulators of
     // the previous group, which every rank has read for the last time (its arrival above came after that).
@@ -696,7 +828,7 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
       darlin_update_weight(P, S, H, mg[i].sl0, mg[i].sl1, buf, false, gtid, gsz, src);
     }
     if (np > 0) {
-      for (int i = 0; i < np && !prev_gather; ++i) darlin_clear_gu(P, mp[i].sl0, mp[i].sl1, pbuf, gtid, gsz);
+      for (int i = 0; i < np && !prev_gather && !prev_list; ++i) darlin_clear_gu(P, mp[i].sl0, mp[i].sl1, pbuf, gtid, gsz);
     } else if (Q.prev != nullptr) {
       for (int q = 0; q < Q.nprev; ++q) {
         const int blk = Q.prev[q];
@@ -732,7 +864,8 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
         darlin_commit(Wk, P, H, mg[i].lc0, mg[i].lc1, buf, gtid, gsz, gat ? SumSrc{s_sum, meta_bias(mg, i)} : SumSrc{nullptr, 0});
     }
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0) Q.local_bar[3] = bar;
+  if (blockIdx.x == 0 && threadIdx.x == 0) { Q.local_bar[3] = bar; Q.local_bar[4] = seq2; }
+#undef PSB_LOCAL_BARRIER
 }
 
 // ---- stand-alone phase kernels (unfused NCCL baseline; gradients go to local buffers)

@@ -136,7 +136,8 @@ class DarlinSolver:
 
     def __init__(self, group: PeerGroup, cfg: DarlinConfig, timeout_s: float = 2.0, impl: str = "fused",
                  out_of_core: bool = False, prefetch_depth: int = 3, blocks_per_launch: Optional[int] = None,
-                 ctas_per_sm: Optional[int] = None, wide_block_cols: int = 0, gather_small_groups: bool = True):
+                 ctas_per_sm: Optional[int] = None, wide_block_cols: int = 0, gather_small_groups: bool = True,
+                 list_block_cols: int = 0):
         """``out_of_core``: keep the column blocks (row ids, values) in pinned host memory and stream each
         block to the GPU on a side stream ahead of its turn in the block order — the role of the
         reference's ``FeatureStation`` in ``-mmap_training_data`` mode with its task-id keyed look-ahead
@@ -152,6 +153,9 @@ class DarlinSolver:
         # groups of blocks with at most 2048 columns over all owners: gather every rank's partial sums on every
         # rank (one cross-GPU wait, no NVLink load in the margin update) instead of pushing into the owners
         self.gather_small_groups = bool(gather_small_groups)
+        # several GPUs, groups with more columns over all owners than this: push and pull as bulk transfers over
+        # the resolved column lists, two cross-GPU rounds per group (0: the kernel's default, 262144)
+        self.list_block_cols = int(list_block_cols)
         self.out_of_core, self.prefetch_depth = out_of_core, max(int(prefetch_depth), 2)
         # out-of-core mode: blocks per kernel launch, rounded up to a multiple of max_block_delay + 1.  A launch
         # costs about 28 us, so small blocks are batched (up to 16); a batch is also the unit that must be on the
@@ -371,6 +375,26 @@ class DarlinSolver:
         # pushed into the owners' accumulators (csrc/darlin_kernels.cu, kGatherCols = 2048)
         self.srv_part = g.alloc((3, W, 2048, 2), f32)
         self.part_mine = torch.zeros((2048, 2), dtype=f32, device=dev)
+        # very wide groups of blocks on several GPUs: per local column its partial (G,U), its slot in the owner's
+        # shard and the owner's answer, addressable by the owners; every rank's block table and owner boundaries
+        self._all_blk_lc = self._all_cb = self.srv_d_slot = None
+        if W > 1:
+            pmax = torch.tensor([P], dtype=torch.int64, device=dev)
+            dist.all_reduce(pmax, op=dist.ReduceOp.MAX, group=g.group)
+            pmax = max(int(pmax.item()), 1)
+            self.col_gu = g.alloc((pmax, 2), f32)
+            self.col_slot = g.alloc((pmax,), torch.int32)
+            self.col_slot.local[:P] = self.gslot
+            self.col_dw = g.alloc((pmax,), f32)
+            self.arrive2 = g.alloc((1,), torch.int64)
+            cb = torch.searchsorted(owner.contiguous(), torch.arange(W + 1, device=dev))   # first local column of every owner
+            tab = [torch.empty_like(self.blk_lc) for _ in range(W)]
+            dist.all_gather(tab, self.blk_lc, group=g.group)
+            cbs = [torch.empty_like(cb) for _ in range(W)]
+            dist.all_gather(cbs, cb, group=g.group)
+            self._all_blk_lc = torch.stack(tab).contiguous()
+            self._all_cb = torch.stack(cbs).contiguous()
+            self.srv_d_slot = torch.zeros(cap, dtype=f32, device=dev)
         self.phase_ns = torch.zeros(4, dtype=torch.int64, device=dev)     # in-kernel phase timers (thread block 0)
         self.arrive = g.alloc((1,), torch.int64)
         self.srv_delta = torch.full((cap,), self.cfg.delta_init, dtype=f32, device=dev)
@@ -378,7 +402,7 @@ class DarlinSolver:
         self.violation = torch.zeros(1, dtype=torch.int32, device=dev)
         # monotone in-GPU counters: [0] barrier after the margin update, [1]/[2] this GPU's CTAs that finished
         # the gradient / update phase (the CTA completing a count notifies the other ranks)
-        self.local_bar = torch.zeros(4, dtype=torch.int64, device=dev)
+        self.local_bar = torch.zeros(8, dtype=torch.int64, device=dev)
         self.abort = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = torch.zeros(8, dtype=torch.int32, device=dev)
         if self.out_of_core:
@@ -469,7 +493,9 @@ class DarlinSolver:
                              self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr(), None,
                              None if prev is None else prev.data_ptr(), 0 if prev is None else prev.numel(),
                              self.wide_block_cols, self.blk_gc.data_ptr(), int(self.shard_begin[self.group.rank]),
-                             1 if self.gather_small_groups else 0, 0, self.phase_ns.data_ptr())
+                             1 if self.gather_small_groups else 0, 0, self.phase_ns.data_ptr(),
+                             None if self._all_blk_lc is None else self._all_blk_lc.data_ptr(),
+                             None if self._all_cb is None else self._all_cb.data_ptr(), self.nblk, self.list_block_cols)
 
     def _build_structs(self):
         Wk = N.DarlinWorker(self.col_ptr.data_ptr(), self.row_idx.data_ptr(),
@@ -483,10 +509,14 @@ class DarlinSolver:
             P.w[r], P.gu[r] = self.srv_w.ptrs[r], self.srv_gu.ptrs[r]
             P.arrive[r] = self.arrive.ptrs[r]
             P.part[r] = self.srv_part.ptrs[r]
+            if self._all_blk_lc is not None:
+                P.colgu[r], P.colslot[r] = self.col_gu.ptrs[r], self.col_slot.ptrs[r]
+                P.coldw[r], P.arrive2[r] = self.col_dw.ptrs[r], self.arrive2.ptrs[r]
         P.mine = self.part_mine.data_ptr()
         P.rank, P.world, P.timeout_ns = self.group.rank, self.group.world, int(self.timeout_s * 1e9)
         P.gu_stride = self._gu_stride
-        S = N.DarlinServer(self.srv_delta.data_ptr(), self.srv_active.data_ptr(), self.violation.data_ptr(), self.slots)
+        S = N.DarlinServer(self.srv_delta.data_ptr(), self.srv_active.data_ptr(), self.violation.data_ptr(), self.slots,
+                           None if self.srv_d_slot is None else self.srv_d_slot.data_ptr())
         self._Wk, self._P, self._S = Wk, P, S
         self._lib.psb_darlin_grid.restype = C.c_int
         grid = self._lib.psb_darlin_grid()
@@ -540,6 +570,8 @@ class DarlinSolver:
         self.srv_w.local.zero_()
         self.srv_gu.local.zero_()
         self.part_mine.zero_()
+        if self._all_blk_lc is not None:
+            self.col_gu.local.zero_()
         self._prev_tail = None
         self.srv_delta.fill_(self.cfg.delta_init)
         self.srv_active.fill_(1)

@@ -103,11 +103,13 @@ class DarlinWorker(C.Structure):
 
 class DarlinPeers(C.Structure):
     _fields_ = [("w", _P8), ("gu", _P8), ("arrive", _P8), ("rank", C.c_int), ("world", C.c_int),
-                ("timeout_ns", C.c_uint64), ("gu_stride", C.c_int64), ("part", _P8), ("mine", C.c_void_p)]
+                ("timeout_ns", C.c_uint64), ("gu_stride", C.c_int64), ("part", _P8), ("mine", C.c_void_p),
+                ("colgu", _P8), ("colslot", _P8), ("coldw", _P8), ("arrive2", _P8)]
 
 
 class DarlinServer(C.Structure):
-    _fields_ = [("delta", C.c_void_p), ("active", C.c_void_p), ("violation", C.c_void_p), ("slots", C.c_int64)]
+    _fields_ = [("delta", C.c_void_p), ("active", C.c_void_p), ("violation", C.c_void_p), ("slots", C.c_int64),
+                ("d_slot", C.c_void_p)]
 
 
 class DarlinSched(C.Structure):
@@ -116,7 +118,8 @@ class DarlinSched(C.Structure):
                 ("abort_flag", C.c_void_p), ("status", C.c_void_p), ("stage_base", C.c_void_p),
                 ("prev", C.c_void_p), ("nprev", C.c_int), ("wide_cols", C.c_int),
                 ("blk_gc", C.c_void_p), ("shard_gbegin", C.c_int64), ("gather", C.c_int), ("pad2", C.c_int),
-                ("trace", C.c_void_p)]
+                ("trace", C.c_void_p), ("all_blk_lc", C.c_void_p), ("all_cb", C.c_void_p), ("nblocks_total", C.c_int64),
+                ("list_cols", C.c_int64)]
 
 
 class DarlinHyper(C.Structure):

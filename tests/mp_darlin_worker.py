@@ -61,12 +61,14 @@ def main():
     tail = int(sys.argv[2]) if len(sys.argv) > 2 else 0
     delay = int(sys.argv[3]) if len(sys.argv) > 3 else 0        # bounded delay tau
     streamed = len(sys.argv) > 4 and sys.argv[4] == "ooc"       # also run with the blocks streamed from host memory
+    listed = len(sys.argv) > 5 and sys.argv[5] == "list"        # force the bulk-transfer path of very wide groups
     group = PeerGroup.from_env()
     rank, W, dev = group.rank, group.world, group.device
     off, idx, vals, y, _ = zipf_sparse_matrix(2400, 3000, 14, seed=5, device=dev, zipf_s=0.8)
     keys = idx * 104729 + 11
     kw = dict(lambda1=0.3, max_pass=5, feature_block_ratio=1.0, seed=2, max_block_delay=delay)
-    sol = DarlinSolver(group, DarlinConfig(tail_feature_freq=tail, **kw), impl=impl)
+    sol = DarlinSolver(group, DarlinConfig(tail_feature_freq=tail, **kw), impl=impl,
+                       **(dict(list_block_cols=1, gather_small_groups=False) if listed else {}))
     sol.preprocess(*shard(off, keys, vals, y, rank, W))
     prog = sol.run()
     sol.check_status()
@@ -108,7 +110,7 @@ def main():
         ok &= len(common) >= 0.95 * max(len(allk), len(rk))
         wd, rd = dict(zip(allk.tolist(), allw.tolist())), dict(zip(rk.tolist(), rw.tolist()))
         ok &= max(abs(wd[c] - rd[c]) for c in common.tolist()) < 5e-2
-        print(f"impl={impl} tail={tail} delay={delay} streamed={streamed} dropped={dropped} world={W} passes={len(prog)} objv={prog[-1].objv:.4f} ref={rprog[-1].objv:.4f} "
+        print(f"impl={impl} tail={tail} delay={delay} streamed={streamed} listed={listed} dropped={dropped} world={W} passes={len(prog)} objv={prog[-1].objv:.4f} ref={rprog[-1].objv:.4f} "
               f"shard_sizes={[len(g[0]) for g in gathered]} match={bool(ok)}", flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, 0, group=group.group)

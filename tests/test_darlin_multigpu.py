@@ -9,10 +9,10 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _launch(nproc, impl, port, tail=0, delay=0, streamed=False):
+def _launch(nproc, impl, port, tail=0, delay=0, streamed=False, listed=False):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_darlin_worker.py"), impl,
-           str(tail), str(delay), "ooc" if streamed else "resident"]
+           str(tail), str(delay), "ooc" if streamed else "resident", "list" if listed else "auto"]
     return subprocess.run(cmd, capture_output=True, text=True, timeout=300)
 
 
@@ -35,6 +35,15 @@ def test_two_gpus_bounded_delay_and_streamed_blocks():
     r = _launch(2, "fused", 29555, delay=2, streamed=True)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "match=True" in r.stdout and "streamed=True" in r.stdout
+
+
+@pytest.mark.parametrize("delay", [0, 1])
+def test_two_gpus_bulk_transfer_path_matches_oracle(delay):
+    """The path of very wide groups (sums per local column, owner-side bulk reads over the resolved column lists,
+    answers written back per column, two cross-GPU rounds) forced for every group."""
+    r = _launch(2, "fused", 29556 + delay, delay=delay, listed=True)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "match=True" in r.stdout and "listed=True" in r.stdout
 
 
 def test_all_gpus_match_oracle():
