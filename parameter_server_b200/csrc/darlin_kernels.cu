@@ -652,19 +652,23 @@ __device__ __forceinline__ void list_range(const DarlinPeers& P, const DarlinSch
 struct ListRuns {
   int64_t a[PSB_MAX_RANKS];
   int64_t pre[PSB_MAX_RANKS + 1];
+  int rk[PSB_MAX_RANKS];      // sender of every run: the owners start at different senders (rank, rank + 1, ...), so
+                              // that they do not all read the same GPU's memory at the same time
 };
 __device__ __forceinline__ void list_runs(const DarlinPeers& P, const DarlinSched& Q, int blk, ListRuns* s_runs) {
   __syncthreads();
   if (threadIdx.x == 0) {
     int64_t run = 0;
-    for (int r = 0; r < P.world; ++r) {
+    for (int i = 0; i < P.world; ++i) {
+      const int r = (P.rank + i) % P.world;
       int64_t a, e;
       list_range(P, Q, r, blk, &a, &e);
-      s_runs->a[r] = a;
-      s_runs->pre[r] = run;
+      s_runs->rk[i] = r;
+      s_runs->a[i] = a;
+      s_runs->pre[i] = run;
       run += e > a ? e - a : 0;
     }
-    for (int r = P.world; r <= PSB_MAX_RANKS; ++r) s_runs->pre[r] = run;
+    for (int i = P.world; i <= PSB_MAX_RANKS; ++i) s_runs->pre[i] = run;
   }
   __syncthreads();
 }
@@ -681,8 +685,9 @@ __device__ __forceinline__ void darlin_list_sum(const DarlinPeers& P, const Darl
   list_runs(P, Q, blk, s_runs);
   const int64_t total = s_runs->pre[PSB_MAX_RANKS];
   for (int64_t g = (int64_t)gtid; g < total; g += (int64_t)gsz) {
-    const int r = list_sender(s_runs, P.world, g);
-    const int64_t j = s_runs->a[r] + (g - s_runs->pre[r]);
+    const int i = list_sender(s_runs, P.world, g);
+    const int r = s_runs->rk[i];
+    const int64_t j = s_runs->a[i] + (g - s_runs->pre[i]);
     const bool peer = r != P.rank;
     const float2 v = peer ? ld_gu(P.colgu[r] + j, true) : __ldcg(P.colgu[r] + j);
     const uint32_t slot = peer ? ld_relaxed_sys_u32(P.colslot[r] + j) : P.colslot[r][j];
@@ -696,8 +701,9 @@ __device__ __forceinline__ void darlin_list_reply(const DarlinPeers& P, const Da
   list_runs(P, Q, blk, s_runs);
   const int64_t total = s_runs->pre[PSB_MAX_RANKS];
   for (int64_t g = (int64_t)gtid; g < total; g += (int64_t)gsz) {
-    const int r = list_sender(s_runs, P.world, g);
-    const int64_t j = s_runs->a[r] + (g - s_runs->pre[r]);
+    const int i = list_sender(s_runs, P.world, g);
+    const int r = s_runs->rk[i];
+    const int64_t j = s_runs->a[i] + (g - s_runs->pre[i]);
     const bool peer = r != P.rank;
     const uint32_t slot = peer ? ld_relaxed_sys_u32(P.colslot[r] + j) : P.colslot[r][j];
     const float d = __ldcg(S.d_slot + slot);

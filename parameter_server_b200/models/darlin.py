@@ -684,10 +684,18 @@ class DarlinSolver:
         else:
             pen = nz = nact = torch.zeros(1, dtype=torch.float64, device=self.dev)
         vals = torch.stack([loss.reshape(()), pen.reshape(()), nz.reshape(()), nact.reshape(())])
-        vio = self.violation.view(torch.float32).to(torch.float64)
-        if self.group.world > 1:
+        vio = self.violation.view(torch.float32)
+        if self.group.world > 1 and self.impl == "fused":
+            # merged inside one small kernel over peer memory (in-switch reduction where the box has multicast)
+            if getattr(self, "_scalars", None) is None:
+                from ..parallel.scalar_reduce import ScalarAllReduce
+
+                self._scalars = ScalarAllReduce(self.group, timeout_s=self.timeout_s)
+            vals, vio = self._scalars(vals, vio)
+        elif self.group.world > 1:
             import torch.distributed as dist
 
+            vio = vio.to(torch.float64)
             dist.all_reduce(vals, group=self.group.group)
             dist.all_reduce(vio, op=dist.ReduceOp.MAX, group=self.group.group)
         v = vals.tolist()

@@ -46,8 +46,28 @@ def main():
             want = np.stack([total[kk] for kk in m.tolist()])
             ok &= bool(np.allclose(o, want, rtol=1e-4, atol=1e-5))
         print(f"impl={impl} k={k} world={W} shard_sizes={kv.nkeys} match={ok}", flush=True)
+    # scalar all-reduce inside a kernel (sums in fp64, maxima), with the box's multicast mapping when it has one
+    # and with plain peer loads; several calls in a row alternate the two internal buffers
+    from parameter_server_b200.parallel.scalar_reduce import ScalarAllReduce
+
+    mine_ok, used_mc = True, []
+    for use_mc in (True, False):
+        red = ScalarAllReduce(group, timeout_s=5.0, use_multicast=use_mc)
+        used_mc.append(red.multicast)
+        for call in range(3):
+            sums = torch.tensor([rank + 1.0, 0.5 * call, 1e-3 * (rank + 1), -2.0 * rank], dtype=torch.float64, device=dev)
+            maxs = torch.tensor([float(rank), 3.0 - rank, 0.25 * call], dtype=torch.float32, device=dev)
+            s_out, m_out = red(sums, maxs)
+            want_s = [W * (W + 1) / 2.0, 0.5 * call * W, 1e-3 * W * (W + 1) / 2.0, -2.0 * W * (W - 1) / 2.0]
+            want_m = [float(W - 1), 3.0, 0.25 * call]
+            mine_ok &= bool(np.allclose(s_out.cpu().numpy(), want_s, rtol=1e-12, atol=1e-12))
+            mine_ok &= bool(np.allclose(m_out.cpu().numpy(), want_m))
+        red.check_status()
+    if rank == 0:
+        print(f"scalar all-reduce: multicast used {used_mc[0]}, match={mine_ok}", flush=True)
+    ok = ok and mine_ok if rank == 0 else mine_ok
     flag = torch.tensor([1 if ok else 0], device=dev)
-    dist.broadcast(flag, 0, group=group.group)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group.group)
     dist.destroy_process_group()
     sys.exit(0 if flag.item() == 1 else 1)
 
