@@ -107,8 +107,10 @@ struct DarlinSched {
   int64_t shard_gbegin;     // position of this owner's first slot in that list
   int gather;               // small groups exchange per-rank partial sums (needs part / mine / gcol / blk_gc)
   int pad2;
-  // optional [4]: nanoseconds that thread block 0 spent, summed over the launch's groups, in
-  // [0] commit + gradients, [1] arrival + cross-GPU wait, [2] sums + update + margins, [3] the in-GPU barrier
+  // optional [12]: nanoseconds that thread block 0 spent, summed over the launch's groups, in
+  // [0] commit + gradients, [1] arrival + cross-GPU wait, [2] sums + update + margins, [3] the in-GPU barrier;
+  // of [2] for very wide groups on several GPUs: [4] owner sums the senders' columns, [5] owner update,
+  // [6] answers written back, [7] second arrival + wait, [8] worker applies the answers, [9] margins
   uint64_t* trace;
   // very wide groups: every rank's block table (local column range of every block) and the first local column
   // of every owner's key range on every rank, so that an owner can address the senders' columns of its range
@@ -835,12 +837,16 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
     if (timed) { t1 = globaltimer_ns(); Q.trace[1] += t1 - t0; t0 = t1; }
     if (lst) {
       // owner: sum the senders' runs of columns into the accumulators, step, answer per sender column
+      uint64_t u0 = timed ? globaltimer_ns() : 0, u1;
       for (int i = 0; i < ng; ++i) darlin_list_sum(P, Q, mg[i].blk, buf, gtid, gsz, &s_runs);
       PSB_LOCAL_BARRIER(15)
+      if (timed) { u1 = globaltimer_ns(); Q.trace[4] += u1 - u0; u0 = u1; }
       for (int i = 0; i < ng; ++i)
         darlin_update_weight(P, S, H, mg[i].sl0, mg[i].sl1, buf, true, gtid, gsz, SumSrc{nullptr, 0}, S.d_slot);
       PSB_LOCAL_BARRIER(16)
+      if (timed) { u1 = globaltimer_ns(); Q.trace[5] += u1 - u0; u0 = u1; }
       for (int i = 0; i < ng; ++i) darlin_list_reply(P, S, Q, mg[i].blk, gtid, gsz, &s_runs);
+      if (timed) { u1 = globaltimer_ns(); Q.trace[6] += u1 - u0; u0 = u1; }
       ++seq2;
       cta_arrive_all(P, P.arrive2, Q.local_bar + 2, seq2 * G, &s_last);
       if (!cta_wait_counter(P.arrive2[P.rank], seq2 * (uint64_t)P.world, P.timeout_ns, true, &s_ok)) {
@@ -848,11 +854,14 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
         break;
       }
       // worker: columns from the answers, then the margins
+      if (timed) { u1 = globaltimer_ns(); Q.trace[7] += u1 - u0; u0 = u1; }
       for (int i = 0; i < ng; ++i) darlin_list_apply(Wk, P, H, mg[i].lc0, mg[i].lc1, gtid, gsz);
       PSB_LOCAL_BARRIER(17)
+      if (timed) { u1 = globaltimer_ns(); Q.trace[8] += u1 - u0; u0 = u1; }
       for (int i = 0; i < ng; ++i)
         darlin_margin_from_dw(worker_for(Wk, Q, b + i, mg[i].p0, mg[i].p1), mg[i].lc0, mg[i].lc1, mg[i].p0, mg[i].p1, gtid, gsz);
-      if (timed) { t1 = globaltimer_ns(); Q.trace[2] += t1 - t0; t0 = t1; }
+      __syncthreads();
+      if (timed) { t1 = globaltimer_ns(); Q.trace[9] += t1 - u0; Q.trace[2] += t1 - t0; t0 = t1; }
       PSB_LOCAL_BARRIER(14)
       if (timed) { t1 = globaltimer_ns(); Q.trace[3] += t1 - t0; t0 = t1; }
       continue;

@@ -395,7 +395,7 @@ class DarlinSolver:
             self._all_blk_lc = torch.stack(tab).contiguous()
             self._all_cb = torch.stack(cbs).contiguous()
             self.srv_d_slot = torch.zeros(cap, dtype=f32, device=dev)
-        self.phase_ns = torch.zeros(4, dtype=torch.int64, device=dev)     # in-kernel phase timers (thread block 0)
+        self.phase_ns = torch.zeros(12, dtype=torch.int64, device=dev)     # in-kernel phase timers (thread block 0)
         self.arrive = g.alloc((1,), torch.int64)
         self.srv_delta = torch.full((cap,), self.cfg.delta_init, dtype=f32, device=dev)
         self.srv_active = torch.ones(cap, dtype=torch.uint8, device=dev)
@@ -671,7 +671,10 @@ class DarlinSolver:
         t = (self.phase_ns.to(torch.float64) / 1e6).tolist()
         if reset:
             self.phase_ns.zero_()
-        return {"commit_grad": t[0], "arrive_wait": t[1], "update_margin": t[2], "gpu_barrier": t[3]}
+        out = {"commit_grad": t[0], "arrive_wait": t[1], "update_margin": t[2], "gpu_barrier": t[3]}
+        if t[4] > 0:     # very wide groups on several GPUs: the parts of "update_margin"
+            out.update(list_sum=t[4], list_update=t[5], list_reply=t[6], list_wait=t[7], list_apply=t[8], list_margin=t[9])
+        return out
 
     def evaluate(self) -> tuple:
         """(objective, nnz_w, nnz_active, violation) summed/maxed over ranks (Darling::evaluateProgress)."""

@@ -67,9 +67,9 @@ class _Staging:
 
 
 class FTRLTrainer:
-    """Double-buffered host→device streaming around :class:`FTRLEngine`."""
+    """Host→device streaming around :class:`FTRLEngine` through a ring of ``depth`` staging buffers."""
 
-    def __init__(self, engine: FTRLEngine, with_vals: bool = False, depth: int = 2):
+    def __init__(self, engine: FTRLEngine, with_vals: bool = False, depth: int = 3):
         self.eng = engine
         self.copy_stream = torch.cuda.Stream(device=engine.dev)
         self.stages = [_Staging(engine, with_vals) for _ in range(depth)]
