@@ -104,7 +104,7 @@ struct DarlinSched {
   int nprev;
   int wide_cols;            // groups with more local columns than this take phase C in two steps (0: kWideBlockCols)
   const int64_t* blk_gc;    // [nblocks_total][2] range of each block in the global sorted key list
-  int64_t shard_gbegin;     // position of this owner's first slot in that list
+  const int64_t* blk_gs0;   // [nblocks_total] position in that list of this owner's first slot of every block
   int gather;               // small groups exchange per-rank partial sums (needs part / mine / gcol / blk_gc)
   int pad2;
   // optional [12]: nanoseconds that thread block 0 spent, summed over the launch's groups, in
@@ -112,10 +112,9 @@ struct DarlinSched {
   // of [2] for very wide groups on several GPUs: [4] owner sums the senders' columns, [5] owner update,
   // [6] answers written back, [7] second arrival + wait, [8] worker applies the answers, [9] margins
   uint64_t* trace;
-  // very wide groups: every rank's block table (local column range of every block) and the first local column
-  // of every owner's key range on every rank, so that an owner can address the senders' columns of its range
-  const int64_t* all_blk_lc;   // [world][nblocks_total][2]
-  const int64_t* all_cb;       // [world][world + 1]
+  // very wide groups: on every rank and for every block, the first local column of every owner's share of the
+  // block, so that an owner can address the senders' columns of its share
+  const int64_t* all_cb;       // [world][nblocks_total][world + 1]
   int64_t nblocks_total;
   int64_t list_cols;           // groups with more columns over all owners than this take the list path (0: kListCols)
 };
@@ -374,7 +373,7 @@ __device__ __forceinline__ void darlin_update_weight(const DarlinPeers& P, const
   float2* gu = P.gu[P.rank] + (int64_t)buf * P.gu_stride;
   float vmax = 0.f;
   for (int64_t k = s0 + (int64_t)gtid; k < s1; k += (int64_t)gsz) {
-    const float2 a = src.smem != nullptr ? src.smem[src.bias + k] : __ldcg(gu + k);   // (bias includes the shard's start)
+    const float2 a = src.smem != nullptr ? src.smem[src.bias + k] : __ldcg(gu + k);   // (bias maps the slot to its place in the group's vector)
     if (clear) gu[k] = make_float2(0.f, 0.f);
     if (!S.active[k]) { if (d_out != nullptr) d_out[k] = 0.f; continue; }
     const DarlinStep st = darlin_step(a.x, a.y, w[k], S.delta[k], H);
@@ -627,12 +626,12 @@ __device__ __forceinline__ void gather_reduce(const DarlinPeers& P, int n, int b
 // ---- very wide groups on several GPUs: push and pull as bulk transfers over resolved column lists
 // With hundreds of thousands of columns per block and GPU, one small NVLink operation per column (a reduction
 // into the owner's accumulator, a load of its sums) is what a pass costs on 8 GPUs: 7/8 of them leave the GPU.
-// A worker's columns of one owner are contiguous in its local (key) order, and their slots in the owner's
-// shard were resolved once — the steady state of the reference's key cache
+// Every owner holds one run of consecutive keys of every block, so a worker's columns of one owner and block are
+// contiguous in its local (key) order, and their slots in the owner's shard were resolved once — the steady state of the reference's key cache
 // (src/system/remote_node.cc:96-184).  So for these groups
 //   * a worker sums (G,U) per LOCAL column in its own memory;
 //   * after the arrival the owner reads, for every sender, the contiguous run of that sender's columns in its
-//     key range — the partial sums and their slots — with coalesced peer loads, and adds them into its
+//     share of the block — the partial sums and their slots — with coalesced peer loads, and adds them into its
 //     accumulators with GPU-scope reductions;
 //   * the owner steps its slots, keeps Δw per slot, and writes Δw back per sender column, again contiguous;
 //   * after a second arrival the worker brings its copy of the columns up to date from Δw (δ follows from Δw by
@@ -642,10 +641,9 @@ constexpr int64_t kListCols = 262144;
 
 // sender r's local columns of block `blk` that this rank owns: [a, e)
 __device__ __forceinline__ void list_range(const DarlinPeers& P, const DarlinSched& Q, int r, int blk, int64_t* a, int64_t* e) {
-  const int64_t* lc = Q.all_blk_lc + ((int64_t)r * Q.nblocks_total + blk) * 2;
-  const int64_t* cb = Q.all_cb + (int64_t)r * (P.world + 1);
-  *a = max(lc[0], cb[P.rank]);
-  *e = min(lc[1], cb[P.rank + 1]);
+  const int64_t* cb = Q.all_cb + ((int64_t)r * Q.nblocks_total + blk) * (P.world + 1);
+  *a = cb[P.rank];
+  *e = cb[P.rank + 1];
 }
 
 // The senders' runs of one block, laid end to end: position g of [0, total) belongs to sender r with
@@ -773,7 +771,7 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
   // by default only from four GPUs on: on two, one 8-byte peer load per column (the wide path) is cheaper than the
   // three extra sweeps over the column lists (6.7 against 10.5 ms per pass on 2 x 10^6 rows x 120 non-zeros); on
   // eight, 7/8 of those loads cross NVLink as small packets and the pass took 30.5 ms
-  const bool can_list = multi && Q.all_blk_lc != nullptr && Q.blk_gc != nullptr && (Q.list_cols > 0 || P.world >= 4);
+  const bool can_list = multi && Q.all_cb != nullptr && Q.blk_gc != nullptr && (Q.list_cols > 0 || P.world >= 4);
   uint64_t seq = Q.seq0;
   uint64_t seq2 = *(volatile uint64_t*)(Q.local_bar + 4);   // list groups completed so far (second arrival counter)
 // in-GPU barrier (bounded); leaves the group loop when it runs out
@@ -870,7 +868,7 @@ darlin_pass_kernel(DarlinWorker Wk, DarlinPeers P, DarlinServer S, DarlinSched Q
     // B and C in one phase.  Owner: update this shard's slots of the group's blocks; zero the accumulators of
     // the previous group, which every rank has read for the last time (its arrival above came after that).
     for (int i = 0; i < ng; ++i) {
-      const SumSrc src = gat ? SumSrc{s_sum, meta_bias(mg, i) + Q.shard_gbegin} : SumSrc{nullptr, 0};
+      const SumSrc src = gat ? SumSrc{s_sum, meta_bias(mg, i) + Q.blk_gs0[mg[i].blk] - mg[i].sl0} : SumSrc{nullptr, 0};
       darlin_update_weight(P, S, H, mg[i].sl0, mg[i].sl1, buf, false, gtid, gsz, src);
     }
     if (np > 0) {

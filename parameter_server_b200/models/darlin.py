@@ -50,7 +50,6 @@ class DarlinConfig:
     max_block_delay: int = 0          # tau: tau+1 consecutive blocks form a group whose gradients precede its updates
     seed: int = 0
     reset_nan_on_kkt_reset: bool = True
-    shard_by_data_range: bool = True  # servers split [min_key, max_key] instead of the whole uint64 space
     # tail-feature filter of BatchSolver::preprocessData (src/linear_method/batch_solver.cc:227-290): features
     # whose count-min estimate of occurrences is <= tail_feature_freq are dropped before training; 0 = off
     tail_feature_freq: int = 0
@@ -294,9 +293,6 @@ class DarlinSolver:
             dist.all_reduce(tmax, op=dist.ReduceOp.MAX, group=g.group)
             kmin, kmax = int(tmin.item()), int(tmax.item())
         self.key_min, self.key_max = kmin - _SIGN, kmax - _SIGN + 1   # unsigned [min, max+1)
-        # server key ranges
-        rng = Range(self.key_min, self.key_max) if self.cfg.shard_by_data_range else Range.all()
-        self.seps = rng.separators(W)
         # servers take the union of the workers' keys in their range (KVVector::setValue key-only push)
         if W > 1:
             sizes = [None] * W
@@ -311,18 +307,8 @@ class DarlinSolver:
         else:
             gk = uk
         self.gkeys_sorted = gk                                     # ordered (sign-flipped) global keys
-        sep_s = torch.tensor([min(s, (1 << 64) - 1) + _SIGN for s in self.seps[:-1]], dtype=torch.int64, device=dev)
-        shard_begin = torch.searchsorted(gk, sep_s)                # first global index of every owner
-        shard_begin = torch.cat([shard_begin, torch.tensor([gk.numel()], device=dev)])
-        self.shard_begin = shard_begin.tolist()
         r = g.rank
-        self.slots = self.shard_begin[r + 1] - self.shard_begin[r]
-        max_slots = max(self.shard_begin[i + 1] - self.shard_begin[i] for i in range(W))
-        self.skeys = _ukey(gk[self.shard_begin[r]: self.shard_begin[r + 1]])   # this shard's keys (bit patterns)
-        # resolve (owner, slot) of each local column
-        gidx = torch.searchsorted(gk, uk)
-        owner = (torch.searchsorted(shard_begin, gidx, right=True) - 1).clamp_(0, W - 1)
-        gslot = gidx - shard_begin[owner]
+        gidx = torch.searchsorted(gk, uk)                          # every local column's position in that list
         # feature blocks (batch_solver.cc:48-66): every feature group is cut into even key sub-ranges of its own
         # key range; without groups all keys form one group over [min_key, max_key)
         groups = self._group_info(offsets, keys, lkeys) if self.cfg.feature_group_bits > 0 else \
@@ -338,8 +324,35 @@ class DarlinSolver:
         top = torch.tensor([e >= (1 << 64) for _, e in self.block_keys], device=dev)     # a range that ends at 2^64
         lc0, lc1 = torch.searchsorted(uk, b_lo), torch.where(top, P, torch.searchsorted(uk, b_hi))
         gc0, gc1 = torch.searchsorted(gk, b_lo), torch.where(top, gk.numel(), torch.searchsorted(gk, b_hi))
-        sl0 = (gc0 - self.shard_begin[r]).clamp_(0, self.slots)
-        sl1 = (gc1 - self.shard_begin[r]).clamp_(0, self.slots)
+        # Ownership.  The reference gives server i the i-th even cut of the whole key range, so one feature block
+        # (a key sub-range itself) lands on one server and the servers take turns.  Here every block's keys are cut
+        # into W runs of equal key count, one per server: a server owns one key range per block, all servers work
+        # on every block, and a shard's slots follow block order (ascending keys).
+        nb = gc1 - gc0
+        if nblk > 1 and not bool((gc0[1:] >= gc1[:-1]).all()):
+            raise ValueError("feature blocks must be disjoint ascending key ranges")
+        ow = torch.arange(W + 1, device=dev)
+        own_lo = gc0[:, None] + (nb[:, None] * ow[None, :]) // W    # [nblk, W + 1] cuts in the global key list
+        cnt = own_lo[:, 1:] - own_lo[:, :-1]                        # keys of block b on owner o
+        base = torch.cumsum(cnt, 0) - cnt                           # ... and the first of their slots
+        slots_all = cnt.sum(0)
+        self.slots, max_slots = int(slots_all[r].item()), int(slots_all.max().item())
+        starts = own_lo[:, :W].reshape(-1).contiguous()
+
+        def owner_slot(pos):
+            idx = (torch.searchsorted(starts, pos, right=True) - 1).clamp_(0, nblk * W - 1)
+            b_, o_ = idx // W, idx % W
+            inside = (pos >= gc0[b_]) & (pos < gc1[b_])             # keys of no block are never touched
+            return torch.where(inside, o_, 0), torch.where(inside, base[b_, o_] + pos - own_lo[b_, o_], 0), inside
+
+        owner, gslot, _ = owner_slot(gidx)
+        all_o, _, all_in = owner_slot(torch.arange(gk.numel(), device=dev))
+        self.skeys = _ukey(gk[(all_o == r) & all_in])              # this shard's keys (bit patterns), in slot order
+        sl0 = base[:, r].contiguous()
+        sl1 = sl0 + cnt[:, r]
+        self.blk_gs0 = own_lo[:, r].contiguous()                   # global position of this shard's first slot per block
+        # first local column of every owner's share of every block
+        self._cb = torch.searchsorted(gidx.contiguous(), own_lo.reshape(-1).contiguous()).reshape(nblk, W + 1).contiguous()
         self.blk_lc = torch.stack([lc0, lc1], 1).contiguous()
         self.blk_sl = torch.stack([sl0, sl1], 1).contiguous()
         self.blk_gc = torch.stack([gc0, gc1], 1).contiguous()      # every block's range in the global sorted key list
@@ -376,8 +389,8 @@ class DarlinSolver:
         self.srv_part = g.alloc((3, W, 2048, 2), f32)
         self.part_mine = torch.zeros((2048, 2), dtype=f32, device=dev)
         # very wide groups of blocks on several GPUs: per local column its partial (G,U), its slot in the owner's
-        # shard and the owner's answer, addressable by the owners; every rank's block table and owner boundaries
-        self._all_blk_lc = self._all_cb = self.srv_d_slot = None
+        # shard and the owner's answer, addressable by the owners; every rank's owner boundaries per block
+        self._all_cb = self.srv_d_slot = None
         if W > 1:
             pmax = torch.tensor([P], dtype=torch.int64, device=dev)
             dist.all_reduce(pmax, op=dist.ReduceOp.MAX, group=g.group)
@@ -387,12 +400,8 @@ class DarlinSolver:
             self.col_slot.local[:P] = self.gslot
             self.col_dw = g.alloc((pmax,), f32)
             self.arrive2 = g.alloc((1,), torch.int64)
-            cb = torch.searchsorted(owner.contiguous(), torch.arange(W + 1, device=dev))   # first local column of every owner
-            tab = [torch.empty_like(self.blk_lc) for _ in range(W)]
-            dist.all_gather(tab, self.blk_lc, group=g.group)
-            cbs = [torch.empty_like(cb) for _ in range(W)]
-            dist.all_gather(cbs, cb, group=g.group)
-            self._all_blk_lc = torch.stack(tab).contiguous()
+            cbs = [torch.empty_like(self._cb) for _ in range(W)]
+            dist.all_gather(cbs, self._cb, group=g.group)
             self._all_cb = torch.stack(cbs).contiguous()
             self.srv_d_slot = torch.zeros(cap, dtype=f32, device=dev)
         self.phase_ns = torch.zeros(12, dtype=torch.int64, device=dev)     # in-kernel phase timers (thread block 0)
@@ -492,9 +501,8 @@ class DarlinSolver:
         return N.DarlinSched(order_t.data_ptr(), self.blk_lc.data_ptr(), self.blk_sl.data_ptr(), n, group, self.seq,
                              self.local_bar.data_ptr(), self.bar, self.abort.data_ptr(), self.status.data_ptr(), None,
                              None if prev is None else prev.data_ptr(), 0 if prev is None else prev.numel(),
-                             self.wide_block_cols, self.blk_gc.data_ptr(), int(self.shard_begin[self.group.rank]),
+                             self.wide_block_cols, self.blk_gc.data_ptr(), self.blk_gs0.data_ptr(),
                              1 if self.gather_small_groups else 0, 0, self.phase_ns.data_ptr(),
-                             None if self._all_blk_lc is None else self._all_blk_lc.data_ptr(),
                              None if self._all_cb is None else self._all_cb.data_ptr(), self.nblk, self.list_block_cols)
 
     def _build_structs(self):
@@ -509,7 +517,7 @@ class DarlinSolver:
             P.w[r], P.gu[r] = self.srv_w.ptrs[r], self.srv_gu.ptrs[r]
             P.arrive[r] = self.arrive.ptrs[r]
             P.part[r] = self.srv_part.ptrs[r]
-            if self._all_blk_lc is not None:
+            if self._all_cb is not None:
                 P.colgu[r], P.colslot[r] = self.col_gu.ptrs[r], self.col_slot.ptrs[r]
                 P.coldw[r], P.arrive2[r] = self.col_dw.ptrs[r], self.arrive2.ptrs[r]
         P.mine = self.part_mine.data_ptr()
@@ -570,7 +578,7 @@ class DarlinSolver:
         self.srv_w.local.zero_()
         self.srv_gu.local.zero_()
         self.part_mine.zero_()
-        if self._all_blk_lc is not None:
+        if self._all_cb is not None:
             self.col_gu.local.zero_()
         self._prev_tail = None
         self.srv_delta.fill_(self.cfg.delta_init)
@@ -614,11 +622,11 @@ class DarlinSolver:
 
         lib, s, H, W = self._lib, N.stream_ptr(), self._hyper(), self.group.world
         blk_lc, blk_sl = self.blk_lc.tolist(), self.blk_sl.tolist()
-        gk_begin = self.shard_begin
+        gs0 = self.blk_gs0.tolist()
         nglobal = self.gkeys_sorted.numel()
         # global column index of each local column, for dense exchange buffers
         if not hasattr(self, "_gcol"):
-            self._gcol = (self.gslot.long() + torch.tensor(gk_begin, device=self.dev)[self.gowner.long()])
+            self._gcol = self.gcol
             self._gu_glob = torch.zeros((nglobal, 2), dtype=torch.float32, device=self.dev)
             self._w_glob = torch.zeros((nglobal,), dtype=torch.float32, device=self.dev)
             to_s = lambda ks: torch.tensor([min(k, (1 << 64) - 1) + _SIGN for k in ks], dtype=torch.int64, device=self.dev)
@@ -645,13 +653,13 @@ class DarlinSolver:
                 dist.all_reduce(gu, group=self.group.group)          # push + server-side sum
             s0, s1 = blk_sl[b]
             if s1 > s0:
-                self.srv_gu.local[0, s0:s1].copy_(gu[gk_begin[r] + s0 - g0: gk_begin[r] + s1 - g0])
+                self.srv_gu.local[0, s0:s1].copy_(gu[gs0[b] - g0: gs0[b] - g0 + s1 - s0])
                 N.check(lib.psb_darlin_update_weight(C.byref(self._P), C.byref(self._S), C.byref(H), s0, s1, s), "update_weight")
                 self.kernel_launches += 1
             wb = self._w_glob[g0:g1]
             wb.zero_()
             if s1 > s0:
-                wb[gk_begin[r] + s0 - g0: gk_begin[r] + s1 - g0] = self.srv_w.local[s0:s1]
+                wb[gs0[b] - g0: gs0[b] - g0 + s1 - s0] = self.srv_w.local[s0:s1]
             if W > 1:
                 wnan = torch.isnan(wb)
                 wz = torch.nan_to_num(wb, nan=0.0)

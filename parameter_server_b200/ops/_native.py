@@ -117,8 +117,8 @@ class DarlinSched(C.Structure):
                 ("group", C.c_int), ("seq0", C.c_uint64), ("local_bar", C.c_void_p), ("bar0", C.c_uint64),
                 ("abort_flag", C.c_void_p), ("status", C.c_void_p), ("stage_base", C.c_void_p),
                 ("prev", C.c_void_p), ("nprev", C.c_int), ("wide_cols", C.c_int),
-                ("blk_gc", C.c_void_p), ("shard_gbegin", C.c_int64), ("gather", C.c_int), ("pad2", C.c_int),
-                ("trace", C.c_void_p), ("all_blk_lc", C.c_void_p), ("all_cb", C.c_void_p), ("nblocks_total", C.c_int64),
+                ("blk_gc", C.c_void_p), ("blk_gs0", C.c_void_p), ("gather", C.c_int), ("pad2", C.c_int),
+                ("trace", C.c_void_p), ("all_cb", C.c_void_p), ("nblocks_total", C.c_int64),
                 ("list_cols", C.c_int64)]
 
 

@@ -104,7 +104,8 @@ def main():
             ok &= abs(p.objv / q.objv - 1) < 2e-3 and abs(p.nnz_w - q.nnz_w) <= max(3, 0.03 * q.nnz_w)
         allk = np.concatenate([g[0] for g in gathered])
         allw = np.concatenate([g[1] for g in gathered])
-        ok &= bool(np.all(np.diff(allk.astype(np.float64)) > 0))      # shards are disjoint ascending key ranges
+        ok &= all(bool(np.all(np.diff(g[0].astype(np.float64)) > 0)) for g in gathered if len(g[0]) > 1)   # ascending per shard
+        ok &= len(np.unique(allk)) == len(allk)                         # shards are disjoint
         rk, rw = ref.model()
         common = np.intersect1d(allk, rk)
         ok &= len(common) >= 0.95 * max(len(allk), len(rk))
