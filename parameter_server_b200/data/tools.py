@@ -10,6 +10,9 @@ Counterparts of the reference's ``text2proto`` / ``proto2bin`` / ``showins`` pro
   python -m parameter_server_b200.data.tools info ADFEA 'data/ctr/part-.*'
   python -m parameter_server_b200.data.tools bin2text out/train out/train.libsvm
   python -m parameter_server_b200.data.tools split rcv1_train.binary rcv1 1000 13   # train/part-000.. + test/part-013..
+  python -m parameter_server_b200.data.tools text2proto LIBSVM data/part-000 out/part   # out/part.recordio + out/part.info
+  python -m parameter_server_b200.data.tools showins out/part.recordio 10
+  python -m parameter_server_b200.data.tools proto2bin out/part.recordio out/part_bin
 """
 from __future__ import annotations
 
@@ -130,6 +133,15 @@ def main(argv=None) -> int:
         print(info(a[1], a[2]))
     elif a[0] == "bin2text":
         print(bin2text(a[1], a[2]))
+    elif a[0] == "text2proto":
+        from .instance import text2proto
+        print(text2proto(a[1], a[2], a[3]))
+    elif a[0] == "showins":
+        from .instance import showins
+        showins(a[1], int(a[2]) if len(a) > 2 else 10)
+    elif a[0] == "proto2bin":
+        from .instance import proto2bin
+        print(proto2bin(a[1], a[2]))
     elif a[0] == "split":
         print(split_parts(a[1], a[2], int(a[3]) if len(a) > 3 else 1000, int(a[4]) if len(a) > 4 else 13))
     else:
