@@ -69,6 +69,21 @@ def test_checkpoint_resume_gives_the_same_run(tmp_path):
         assert b["objv"] == pytest.approx(a["objv"], rel=2e-4)
 
 
+def test_warm_start_from_a_model_dump(tmp_path):
+    """init_w { type: FILE }: a second job starts from the dump of the first and carries on from its objective."""
+    _data(tmp_path)
+    text = BATCH.format(d=tmp_path, darling="darling { delta_init_value: 1 delta_max_value: 5 }")
+    first = _run(tmp_path, text.replace("max_pass_of_data: 6", "max_pass_of_data: 4"))
+    a = [p["objv"] for p in first["progress"]]
+    warm = text.replace("max_pass_of_data: 6", "max_pass_of_data: 2").replace(
+        "loss {", 'init_w {{ type: FILE file_name: "{d}/model" }} loss {{'.format(d=tmp_path), 1)
+    second = _run(tmp_path, warm)
+    b = [p["objv"] for p in second["progress"]]
+    assert len(b) == 2
+    assert b[0] < a[0] and b[0] <= a[-1] * 1.002          # first pass from the dump: at the level the first job had reached
+    assert b[-1] <= b[0] * 1.0005
+
+
 def test_plain_batch_solver_job(tmp_path):
     _data(tmp_path)
     out = _run(tmp_path, BATCH.format(d=tmp_path, darling="learner { type: PROXIMAL_GRADIENT }"))
