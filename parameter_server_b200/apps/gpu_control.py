@@ -1,0 +1,240 @@
+"""A scheduler node for GPU jobs: the host control plane drives the passes of a batch job on GPU ranks.
+
+In the reference the scheduler owns the loop of a batch job (src/linear_method/batch_solver.cc:69-132,
+src/linear_method/darling.cc:30-101): it submits tasks to the workers and servers, merges their ``Progress`` replies,
+prints the table, applies the stopping rule and finally asks for the model; a monitor thread prints the heartbeat
+table of all nodes (src/system/postoffice.cc:271-374).  GPU ranks by default run that loop themselves, in lock step,
+with ``torch.distributed`` as the only control plane.  With ``-gpu_scheduler`` the loop moves to a scheduler node:
+
+* rank 0 also runs the scheduler node ``H`` (post office + TCP van on the loopback); every rank runs a worker node
+  ``W<rank>`` whose server half lives in the same process (the data plane stays inside the kernels, over NVLink);
+* a task covers a whole pass, not one block: a pass is one kernel launch here, and the block order of the pass
+  (with the zero-delay sweeps over the important groups in front) travels in the task (``block_order``,
+  ``num_prior``) — one message per block would cost more than the block;
+* every rank answers with the ``Progress`` of the pass (already merged on the device); the scheduler checks that the
+  ranks agree, prints the table, applies the reference's stopping rule and sends ``SAVE_MODEL``;
+* with ``-report_interval`` the workers' heartbeats carry the device and its memory in use, and the scheduler prints
+  the dashboard.
+
+The solver only needs ``nblk``, ``cfg``, ``block_group``, ``progress``, ``run_pass(order, reset, prior)`` and
+``save_model(prefix)``, which is what the CPU test's stand-in provides.
+"""
+from __future__ import annotations
+
+import copy
+import socket
+import sys
+import threading
+import time
+from typing import List, Optional
+
+import numpy as np
+
+from .. import config as cfg
+from ..runtime import host
+from ..runtime.node import NodeContext, dashboard, start_node
+from ..utils.pbtext import dumps, parse
+
+
+def _call(cmd: str, **kw) -> bytes:
+    m = cfg.LMCall(cmd=cmd)
+    for k, v in kw.items():
+        m.set(k, v)
+    return dumps(m, oneline=True).encode()
+
+
+ERROR_PREFIX = b"ERROR: "
+
+
+class GpuWorkerNode:
+    """Worker + server of one GPU rank: runs the scheduler's tasks on the solver, on the node's executor thread."""
+
+    def __init__(self, ctx: NodeContext, app_name: str, sol, model_prefix: str = "", device=None):
+        self.ctx, self.sol, self.model_prefix, self.device = ctx, sol, model_prefix, device
+        self.saved: Optional[str] = None
+        self.failed: Optional[str] = None
+        self.cust = host().Customer(ctx.po, app_name, self.process, False)
+
+    def _where(self) -> str:
+        if self.device is None or getattr(self.device, "type", "cpu") != "cuda":
+            return ""
+        import torch
+
+        free, total = torch.cuda.mem_get_info(self.device)
+        return f" {self.device} hbm {(total - free) / 2**30:.1f}/{total / 2**30:.0f}GB"
+
+    def process(self, msg) -> None:
+        if not msg.request:
+            return
+        t0 = time.time()
+        reply = b""
+        try:
+            if self.device is not None and getattr(self.device, "type", "cpu") == "cuda":
+                import torch
+
+                torch.cuda.set_device(self.device)           # the executor thread has no current device of its own
+            call = parse(msg.payload.decode(), cfg.LMCall)
+            if self.ctx.hb_state is not None:
+                self.ctx.hb_state["task"] = msg.time
+            if call.cmd == "UPDATE_MODEL":
+                order = np.asarray(list(call.block_order), dtype=np.int32)
+                n_prior = int(call.num_prior)
+                prior = order[:n_prior].tolist() if n_prior > 0 else None
+                p = self.sol.run_pass(order[n_prior:], bool(call.kkt_filter_reset), prior)
+                reply = dumps(cfg.Progress(objv=float(p.objv), relative_objv=float(p.relative_objv), nnz_w=int(p.nnz_w),
+                                           violation=float(p.violation), nnz_active_set=int(p.nnz_active),
+                                           total_time=float(p.seconds), kkt_threshold=float(p.kkt_threshold)),
+                               oneline=True).encode()
+            elif call.cmd == "SAVE_MODEL":
+                if self.model_prefix:
+                    self.saved = self.sol.save_model(self.model_prefix)
+                    reply = self.saved.encode()
+            # LOAD_DATA / PREPROCESS_DATA are done before the control plane starts (they are collective set-up);
+            # RECOVER does nothing, as in the reference
+            if self.ctx.hb_state is not None:
+                self.ctx.hb_state["where"] = self._where()
+        except Exception as e:  # noqa: BLE001 - the scheduler must hear about it instead of waiting forever
+            import traceback
+
+            self.failed = traceback.format_exc()
+            reply = ERROR_PREFIX + f"{type(e).__name__}: {e}".encode()
+        self.ctx.add_busy(time.time() - t0)
+        self.cust.reply(msg, payload=reply)
+
+    def stop(self) -> None:
+        self.cust.stop()
+
+
+class GpuBatchScheduler:
+    """Scheduler side of a batch job on GPU ranks: one UPDATE_MODEL task per pass."""
+
+    def __init__(self, ctx: NodeContext, app_name: str, solver_cfg, nblk: int, block_group, verbose: bool = True):
+        self.H, self.ctx = host(), ctx
+        self.cfg, self.nblk, self.block_group, self.verbose = solver_cfg, nblk, block_group, verbose
+        self.cust = self.H.Customer(ctx.po, app_name, None, False)
+        self.progress: List[dict] = []
+        self.saved: List[str] = []
+
+    def _round(self, payload: bytes) -> dict:
+        t = self.cust.submit(self.H.kWorkerGroup, payload=payload)
+        self.cust.wait_out(self.H.kWorkerGroup, t)
+        replies = self.cust.take_replies(t)
+        for nid, text in replies.items():
+            if bytes(text).startswith(ERROR_PREFIX):
+                raise RuntimeError(f"{nid}: {bytes(text)[len(ERROR_PREFIX):].decode()}")
+        return replies
+
+    def run(self) -> List[dict]:
+        from ..models.darlin import Progress, block_order, print_progress, prior_block_order
+
+        c = self.cfg
+        orders = block_order(self.nblk, c.max_pass, c.random_block_order, c.seed)
+        prior = prior_block_order(self.block_group, c.prior_fea_group, c.num_iter_for_prior_fea_group, c.random_block_order, c.seed)
+        reset = False
+        t_start = time.time()
+        for it in range(c.max_pass):
+            first = prior if it == 0 else []
+            t_it = time.time()
+            replies = self._round(_call("UPDATE_MODEL", block_order=[int(b) for b in first] + orders[it].tolist(),
+                                        num_prior=len(first), kkt_filter_reset=reset))
+            ps = {nid: parse(bytes(text).decode(), cfg.Progress) for nid, text in replies.items()}
+            p0 = next(iter(ps.values()))
+            for nid, p in ps.items():      # the ranks merged their parts on the device: they must report the same pass
+                if abs(p.objv - p0.objv) > 1e-9 * max(abs(p0.objv), 1.0) or p.nnz_w != p0.nnz_w:
+                    raise RuntimeError(f"pass {it}: {nid} reports objective {p.objv} / {p.nnz_w} non-zeros, others {p0.objv} / {p0.nnz_w}")
+            rec = dict(objv=p0.objv, relative_objv=p0.relative_objv, nnz_w=int(p0.nnz_w), violation=p0.violation,
+                       nnz_active_set=int(p0.nnz_active_set), kkt_threshold=p0.kkt_threshold, total_time=time.time() - t_start,
+                       busy_time=[p.total_time for p in ps.values()])
+            self.progress.append(rec)
+            if self.verbose:
+                print_progress(it, Progress(p0.objv, p0.relative_objv, int(p0.nnz_w), p0.violation, int(p0.nnz_active_set),
+                                            p0.kkt_threshold, time.time() - t_it), file=sys.stderr)
+            if 0 < p0.relative_objv <= c.epsilon:
+                if reset:
+                    break
+                reset = True
+            else:
+                reset = False
+        self.saved = sorted(bytes(t).decode() for t in self._round(_call("SAVE_MODEL")).values() if bytes(t))
+        return self.progress
+
+    def stop(self) -> None:
+        self.cust.stop()
+
+
+def _free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def run_scheduled(group, flags: cfg.Flags, app_name: str, sol, model_prefix: str = "", verbose: bool = True) -> dict:
+    """Run the passes of ``sol`` (already preprocessed, on every rank) under a scheduler node on rank 0.
+
+    Collective over ``group`` (``rank``, ``world``, ``group`` = the torch.distributed group, ``device``,
+    ``barrier()``).  Returns on every rank ``{"progress": solver.progress, "model": path or None}``; rank 0 adds the
+    scheduler's own records under ``"scheduler"`` and the last dashboard under ``"dashboard"``."""
+    import torch.distributed as dist
+
+    W = int(group.world)
+    port = [_free_port() if group.rank == 0 else 0]
+    if W > 1:
+        dist.broadcast_object_list(port, src=0, group=group.group)
+    f = copy.copy(flags)
+    f.num_workers, f.num_servers, f.num_unused, f.num_replicas = W, 0, 0, 0
+    f.scheduler = f"role:SCHEDULER,hostname:'127.0.0.1',port:{int(port[0])},id:'H'"
+    f.interface = ""
+    sched_ctx: dict = {}
+    th = None
+    if group.rank == 0:
+        def boot():
+            try:
+                sched_ctx["ctx"] = start_node(0, f)
+            except Exception as e:  # noqa: BLE001
+                sched_ctx["error"] = e
+
+        th = threading.Thread(target=boot, name="H-boot", daemon=True)
+        th.start()
+    ctx = start_node(group.rank + 1, f)
+    node = GpuWorkerNode(ctx, app_name, sol, model_prefix, getattr(group, "device", None))
+    out: dict = {}
+    try:
+        if th is not None:
+            th.join()
+            if "error" in sched_ctx:
+                raise sched_ctx["error"]
+        group.barrier()                                   # every rank's customer exists before the first task goes out
+        if group.rank == 0:
+            hctx = sched_ctx["ctx"]
+            sched = GpuBatchScheduler(hctx, app_name, sol.cfg, sol.nblk, sol.block_group, verbose)
+            stop_monitor = threading.Event()
+            if float(flags.report_interval) > 0:
+                def monitor():
+                    while not stop_monitor.wait(float(flags.report_interval)):
+                        print(dashboard(hctx.po), file=sys.stderr, flush=True)
+
+                threading.Thread(target=monitor, name="H-monitor", daemon=True).start()
+            try:
+                out["scheduler"] = sched.run()
+                out["saved"] = sched.saved
+                if float(flags.report_interval) > 0:
+                    # a short job can end before the first report is due: give every worker three intervals
+                    deadline = time.time() + 3.0 * float(flags.report_interval)
+                    while time.time() < deadline and not all(text for _, text in hctx.po.heartbeats().values()):
+                        time.sleep(0.01)
+                    out["dashboard"] = dashboard(hctx.po)
+            finally:
+                stop_monitor.set()
+                hctx.po.stop_all()                        # TERMINATE to every node, this process's worker included
+                sched.stop()
+        ctx.po.wait_terminate(1e9)
+    finally:
+        node.stop()
+        ctx.stop()
+        if "ctx" in sched_ctx:
+            sched_ctx["ctx"].stop()
+    if node.failed:
+        raise RuntimeError(f"rank {group.rank}: a task failed\n{node.failed}")
+    out["progress"] = sol.progress
+    out["model"] = node.saved
+    return out

@@ -166,6 +166,18 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
                 from ..utils.checkpoint import run_with_checkpoints
 
                 prog = run_with_checkpoints(sol, flags.checkpoint_dir, int(flags.checkpoint_interval) or 1, verbose=bool(flags.verbose) or True)
+            elif flags.gpu_scheduler:
+                # the passes run under a scheduler node of the host control plane (apps/gpu_control.py)
+                from .gpu_control import run_scheduled
+
+                ctl = run_scheduled(group, flags, conf.app_name or "linear_method", sol,
+                                    lm.model_output.file[0] if lm.model_output.file else "", verbose=True)
+                prog = sol.progress
+                if ctl.get("model"):
+                    out["model"] = ctl["model"]               # written by the SAVE_MODEL task
+                out["scheduler_progress"] = ctl.get("scheduler")
+                if "dashboard" in ctl:
+                    out["dashboard"] = ctl["dashboard"]
             else:
                 prog = sol.run(verbose=True)
         else:
@@ -180,7 +192,7 @@ def run_gpu_job(flags: cfg.Flags) -> dict:
         out["progress"] = [p.__dict__ for p in prog]
         if getattr(sol, "trace", None) is not None:
             out["trace"] = sol.trace.save()
-        if lm.model_output.file:
+        if lm.model_output.file and "model" not in out:
             out["model"] = sol.save_model(lm.model_output.file[0])
         if lm.has("validation_data"):
             mk, mw = _gather_model(group, *sol.model())

@@ -84,12 +84,15 @@ LMConfig = Schema(
 Progress = Schema("LM.Progress", F("objv", "double"), F("relative_objv", "double"), F("nnz_w", "uint64"),
                   F("violation", "double"), F("nnz_active_set", "uint64"), F("training_auc", "double"),
                   F("training_auc_data", AUCData), F("num_ex_trained", "uint64"), F("acc", "double"),
-                  F("total_time", "double"), F("busy_time", "double", "repeated"))
+                  F("total_time", "double"), F("busy_time", "double", "repeated"),
+                  F("kkt_threshold", "double"))      # addition of this framework: GPU ranks report the threshold they used
 LMCommand = Enum("LM.Call.Command", LOAD_DATA=1, PREPROCESS_DATA=2, UPDATE_MODEL=3, EVALUATE_PROGRESS=4, SAVE_MODEL=5,
                  RECOVER=6, COMPUTE_VALIDATION_AUC=7, REPORT_PROGRESS=8)
 LMCall = Schema("LM.Call", F("cmd", LMCommand, "required"), F("key", PbRange), F("kkt_filter_threshold", "double"),
                 F("kkt_filter_reset", "bool"), F("fea_grp", "int32", "repeated"), F("hit_cache", "bool"),
-                F("progress", Progress))   # REPORT_PROGRESS carries the worker's increment
+                F("progress", Progress),   # REPORT_PROGRESS carries the worker's increment
+                # additions of this framework: a task of a scheduled GPU job covers a whole pass
+                F("block_order", "int32", "repeated"), F("num_prior", "int32", default=0))
 
 # ---------------------------------------------------------------- neural_network.proto
 LayerType = Enum("LayerConfig.Type", NONE=0, FULLY_CONNECTED=1, DATA=2, LOGISTIC_LOSS=3, AUC=4, SPARSE_FULLY_CONNECTED=5)
@@ -188,7 +191,7 @@ FLAG_DEFAULTS: Dict[str, object] = {
     "log_instant": False,
     # additions of this framework
     "impl": "fused", "gpus": 0, "seed": 0, "timeout_s": 2.0, "checkpoint_dir": "", "checkpoint_interval": 0,
-    "trace_file": "", "metrics_file": "",
+    "trace_file": "", "metrics_file": "", "gpu_scheduler": False,
 }
 
 

@@ -48,7 +48,8 @@ def _host_stats() -> dict:
 def heartbeat_report(node_id: str, state: dict) -> str:
     """Text-format ``HeartbeatReport`` of this process (src/system/heartbeat_info.cc:37-155): CPU share of the process
     and of the machine since the previous report, memory of both, time spent in compute sections (``busy_ms``, added
-    by the application), network totals and rates."""
+    by the application), network totals and rates.  ``state["where"]`` (a GPU rank: its device and the device memory
+    in use) is appended to the host name, the table's last column."""
     import socket
 
     H = host()
@@ -61,7 +62,7 @@ def heartbeat_report(node_id: str, state: dict) -> str:
     d_busy = hs["busy"] - state.get("hbusy", hs["busy"])
     d_total = max(hs["total"] - state.get("htotal", hs["total"]), 1)
     r = cfg.HeartbeatReport(
-        task_id=int(state.get("task", 0)), hostname=f"{node_id}@{socket.gethostname()}", seconds_since_epoch=int(now), total_time_milli=int(dt * 1000),
+        task_id=int(state.get("task", 0)), hostname=f"{node_id}@{socket.gethostname()}{state.get('where', '')}", seconds_since_epoch=int(now), total_time_milli=int(dt * 1000),
         busy_time_milli=int(state.get("busy_ms", 0)), net_in_mb=int(u["net_in"] >> 20), net_out_mb=int(u["net_out"] >> 20),
         process_cpu_usage=int(100 * d_proc / d_host * (state.get("ncpu", 1))), host_cpu_usage=int(100 * d_busy / d_total),
         process_rss_mb=int(u["rss_mb"]), process_virt_mb=int(u["virt_mb"]),
@@ -171,6 +172,8 @@ def dashboard(po) -> str:
     for nid in sorted(hb, key=order):
         age, text = hb[nid]
         try:
+            if not text:                                   # registered, but no report has arrived yet
+                raise ValueError("empty")
             r = parse(text.decode(), cfg.HeartbeatReport)
             busy_pct = int(100 * r.busy_time_milli / max(r.total_time_milli, 1))
             use = f"{r.host_in_use_gb}({r.host_in_use_percentage}%)"

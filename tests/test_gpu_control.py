@@ -1,0 +1,131 @@
+"""The scheduler node for GPU jobs, on CPU: gloo ranks, a stand-in solver with the interface of the GPU solver.
+
+Checks the control flow only (tasks per pass with the block order, progress replies, the stopping rule, SAVE_MODEL,
+heartbeat table, a failing task reaching the scheduler); the GPU job test runs the same code on the real solver."""
+import multiprocessing as mp
+import os
+import socket
+import time
+
+import pytest
+
+
+def _free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, mode, tmp, q):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from parameter_server_b200 import config as cfg
+    from parameter_server_b200.apps.gpu_control import run_scheduled
+    from parameter_server_b200.models.darlin import DarlinConfig, Progress, block_order
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    class Group:
+        def __init__(self):
+            self.rank, self.world, self.group, self.device = rank, world, dist.group.WORLD, torch.device("cpu")
+
+        def barrier(self):
+            dist.barrier()
+
+    class StandIn:
+        """Objective halves every pass until it stalls; every pass is a collective, like the real one."""
+
+        def __init__(self):
+            self.cfg = DarlinConfig(lambda1=1.0, max_pass=12, epsilon=1e-3, random_block_order=True, seed=5,
+                                    prior_fea_group=(2,), num_iter_for_prior_fea_group=2)
+            self.nblk, self.block_group = 6, [1, 1, 2, 2, 3, 3]
+            self.progress, self.seen = [], []
+
+        def run_pass(self, order, reset=False, prior=None):
+            it = len(self.progress)
+            if mode == "heartbeat":
+                time.sleep(0.1)                                      # long enough for a few reports per job
+            self.seen.append((list(map(int, order)), bool(reset), None if prior is None else list(map(int, prior))))
+            part = torch.tensor([100.0 / world * max(0.5 ** it, 0.5 ** 4)], dtype=torch.float64)
+            dist.all_reduce(part)                                    # runs on the node's executor thread
+            objv = float(part.item())
+            if mode == "fail" and it == 2 and rank == 1:
+                raise ValueError("device says no")                   # after the collective: the other rank is not left in it
+            rel = 1.0 if not self.progress else self.progress[-1].objv / objv - 1.0
+            p = Progress(objv, rel, 10 + it, 0.5, 60, 0.0, 0.01)
+            self.progress.append(p)
+            return p
+
+        def save_model(self, prefix):
+            path = f"{prefix}_S{rank}"
+            open(path, "w").write("1\t0.5\n")
+            return path
+
+    sol = StandIn()
+    flags = cfg.Flags(report_interval=0.2 if mode == "heartbeat" else 0)
+    try:
+        out = run_scheduled(Group(), flags, "job", sol, os.path.join(tmp, "model"), verbose=False)
+        orders = [o.tolist() for o in block_order(6, 12, True, 5)]
+        q.put((rank, "ok", dict(passes=len(sol.progress), seen=sol.seen, orders=orders, model=out["model"],
+                                sched=out.get("scheduler"), saved=out.get("saved"), dash=out.get("dashboard"))))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, "error", f"{type(e).__name__}: {e}"))
+    dist.barrier() if mode != "fail" else time.sleep(1.0)
+    os._exit(0)
+
+
+def _run(mode, tmp, world=2):
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, mode, str(tmp), q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    deadline = time.time() + 240
+    while len(got) < world and time.time() < deadline:
+        if q.empty():
+            time.sleep(0.1)
+            continue
+        r, status, body = q.get()
+        got[r] = (status, body)
+    for p in procs:
+        p.join(20)
+        if p.is_alive():
+            p.kill()
+    assert len(got) == world, f"only {sorted(got)} reported"
+    return got
+
+
+def test_scheduler_drives_the_passes_and_stops_by_the_rule(tmp_path):
+    got = _run("plain", tmp_path)
+    assert all(s == "ok" for s, _ in got.values()), got
+    a, b = got[0][1], got[1][1]
+    # objective 100, 50, 25, 12.5, 6.25, then constant: relative change 0 is not "0 < rel <= eps", so the job runs
+    # all 12 passes; the order of every pass and the first pass's prior sweeps arrive as the scheduler made them
+    assert a["passes"] == b["passes"] == 12 and a["seen"] == b["seen"]
+    assert [s[0] for s in a["seen"]] == a["orders"]
+    assert a["seen"][0][2] is not None and sorted(set(a["seen"][0][2])) == [2, 3] and len(a["seen"][0][2]) == 4
+    assert all(s[2] is None for s in a["seen"][1:])
+    assert len(a["sched"]) == 12 and a["sched"][0]["objv"] == pytest.approx(100.0) and a["sched"][1]["relative_objv"] == pytest.approx(1.0)
+    assert a["saved"] == [str(tmp_path / "model_S0"), str(tmp_path / "model_S1")]
+    assert a["model"].endswith("_S0") and b["model"].endswith("_S1") and os.path.exists(b["model"])
+    assert b["sched"] is None
+
+
+def test_heartbeats_reach_the_scheduler(tmp_path):
+    got = _run("heartbeat", tmp_path)
+    assert all(s == "ok" for s, _ in got.values()), got
+    dash = got[0][1]["dash"]
+    assert dash.splitlines()[0].startswith("Node") and "W0@" in dash and "W1@" in dash and "no report yet" not in dash
+
+
+def test_a_failing_task_ends_the_job_with_its_error(tmp_path):
+    got = _run("fail", tmp_path)
+    assert got[0][0] == "error" and "W1" in got[0][1] and "device says no" in got[0][1]
+    assert got[1][0] == "error" and "device says no" in got[1][1]

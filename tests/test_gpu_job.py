@@ -84,6 +84,25 @@ def test_warm_start_from_a_model_dump(tmp_path):
     assert b[-1] <= b[0] * 1.0005
 
 
+def test_darlin_job_under_a_scheduler_node(tmp_path):
+    """-gpu_scheduler: the passes are tasks of a scheduler node of the host control plane; same run, same model."""
+    _data(tmp_path)
+    text = BATCH.format(d=tmp_path, darling="darling { delta_init_value: 1 delta_max_value: 5 }")
+    plain = _run(tmp_path, text)
+    model_plain = read_model_text(plain["model"])
+    ctl = _run(tmp_path, text, gpu_scheduler=True, report_interval=0.05)
+    # float atomics sum in a different order from run to run: equal within the tolerance of the resume test
+    assert [p["objv"] for p in ctl["progress"]] == pytest.approx([p["objv"] for p in plain["progress"]], rel=2e-4)
+    assert [p["objv"] for p in ctl["scheduler_progress"]] == [p["objv"] for p in ctl["progress"]]     # what the ranks replied
+    assert [p["nnz_w"] for p in ctl["scheduler_progress"]] == [p["nnz_w"] for p in ctl["progress"]]
+    model = read_model_text(ctl["model"])
+    common = set(model) & set(model_plain)
+    assert ctl["model"].endswith("model_S0") and len(common) >= 0.98 * max(len(model), len(model_plain))
+    assert max(abs(model[k] - model_plain[k]) for k in common) < 5e-3
+    assert "W0" in ctl["dashboard"] and "cuda:0" in ctl["dashboard"]
+    assert ctl["validation_auc"] == pytest.approx(plain["validation_auc"], abs=2e-3)
+
+
 def test_plain_batch_solver_job(tmp_path):
     _data(tmp_path)
     out = _run(tmp_path, BATCH.format(d=tmp_path, darling="learner { type: PROXIMAL_GRADIENT }"))
