@@ -9,6 +9,7 @@
 #include "darlin_cpu.h"
 #include "data.h"
 #include "feature_station.h"
+#include "ocean.h"
 #include "ftrl_cpu.h"
 #include "kv.h"
 #include "localizer.h"
@@ -271,6 +272,45 @@ PYBIND11_MODULE(_psb_host, m) {
     darlin_update_dual(B, y.data(), dual.mutable_data(), w.mutable_data(), delta.mutable_data(), active.mutable_data(), w_new.data(),
                        delta_max);
   });
+  // ---- general block store: arrays cut along a column partition, spilled per block, prefetched by block
+  {
+    py::class_<Ocean> oc(m, "Ocean");
+    oc.def(py::init<std::string, std::string, int, int, bool>(), py::arg("dir"), py::arg("identity"), py::arg("threads") = 2,
+           py::arg("job_limit") = 64, py::arg("less_memory") = false)
+        .def("set_partition", &Ocean::set_partition)
+        .def("num_blocks", &Ocean::num_blocks)
+        .def("dump", [](Ocean& o, int grp, int kind, py::array a) {
+          py::array c = py::array::ensure(a, py::array::c_style);
+          if (!c) return false;
+          const void* p = c.data(); const size_t n = (size_t)c.size(), elem = (size_t)c.itemsize();
+          py::gil_scoped_release rel;
+          return o.dump(grp, (Ocean::Kind)kind, p, n, elem);
+        })
+        .def("prefetch", &Ocean::prefetch)
+        .def("get", [](Ocean& o, int grp, size_t blk, int kind, const std::string& dtype) -> py::object {
+          if (kind < 0 || kind >= Ocean::NUM_KINDS) throw std::invalid_argument("unknown kind");
+          Ocean::BytesPtr b;
+          { py::gil_scoped_release rel; b = o.get(grp, blk, (Ocean::Kind)kind); }
+          if (!b) return py::none();
+          py::dtype dt = py::dtype::from_args(py::str(dtype));
+          if (b->size() % (size_t)dt.itemsize() != 0) throw std::invalid_argument("block size is not a multiple of the element size");
+          const std::vector<py::ssize_t> shape{(py::ssize_t)(b->size() / (size_t)dt.itemsize())};
+          py::array out(dt, shape);
+          if (!b->empty()) std::memcpy(out.mutable_data(), b->data(), b->size());
+          return py::object(std::move(out));
+        }, py::arg("grp"), py::arg("blk"), py::arg("kind"), py::arg("dtype"))
+        .def("drop", &Ocean::drop, py::call_guard<py::gil_scoped_release>())
+        .def("pending", &Ocean::pending)
+        .def("stats", [](Ocean& o) {
+          auto s = o.stats(); py::dict d;
+          d["bytes_written"] = s.bytes_written; d["bytes_read"] = s.bytes_read; d["prefetched"] = s.prefetched; d["hits"] = s.hits;
+          d["misses"] = s.misses; d["loaded_now"] = s.loaded_now; d["peak_loaded"] = s.peak_loaded;
+          return d;
+        });
+    oc.attr("FEATURE_KEY") = (int)Ocean::FEATURE_KEY; oc.attr("FEATURE_OFFSET") = (int)Ocean::FEATURE_OFFSET;
+    oc.attr("FEATURE_VALUE") = (int)Ocean::FEATURE_VALUE; oc.attr("PARAMETER_KEY") = (int)Ocean::PARAMETER_KEY;
+    oc.attr("PARAMETER_VALUE") = (int)Ocean::PARAMETER_VALUE; oc.attr("DELTA") = (int)Ocean::DELTA;
+  }
   // ---- worker-side feature store (memory or disk with prefetch) and the block steps on its ranges
   py::class_<FeatureStation>(m, "FeatureStation")
       .def(py::init<std::string, std::string, size_t, int, size_t, bool>(), py::arg("dir"), py::arg("name"), py::arg("mem_limit_kb") = 1048576,

@@ -21,6 +21,7 @@
 
 #include "../darlin_cpu.h"
 #include "../feature_station.h"
+#include "../ocean.h"
 #include "../data.h"
 #include "../kv.h"
 #include "../runtime.h"
@@ -394,6 +395,37 @@ int main(int argc, char** argv) {
     for (int i = 0; i < 40; ++i)
       CHECK_TRUE((G0[i] == G1[i] && U0[i] == U1[i]) || (i == 5 && G0[i] != G0[i] && G1[i] != G1[i]));
     st.drop(1000);
+
+    // the general block store under concurrent prefetchers and users
+    {
+      Ocean oc(dir + "/ocean", "T0", 3, 4, false);
+      std::vector<uint64_t> cuts;
+      for (uint64_t c = 0; c <= (uint64_t)cols; c += 20) cuts.push_back(c);
+      CHECK_TRUE(oc.set_partition(1, cuts));
+      std::vector<uint64_t> off(indptr.begin(), indptr.end());
+      CHECK_TRUE(oc.dump(1, Ocean::FEATURE_OFFSET, off.data(), off.size(), 8));
+      CHECK_TRUE(oc.dump(1, Ocean::FEATURE_KEY, indices.data(), indices.size(), 4));
+      CHECK_TRUE(oc.dump(1, Ocean::FEATURE_VALUE, values.data(), values.size(), 8));
+      CHECK_TRUE(!oc.dump(1, Ocean::FEATURE_VALUE, values.data(), values.size(), 8));
+      const size_t nb = oc.num_blocks(1);
+      std::atomic<int> wrong{0};
+      std::thread pre([&] { for (size_t b = 0; b < nb; ++b) { oc.prefetch(1, b); oc.prefetch(1, b); } });
+      auto user = [&] {
+        for (size_t b = 0; b < nb; ++b) {
+          auto k = oc.get(1, b, Ocean::FEATURE_KEY);
+          auto o = oc.get(1, b, Ocean::FEATURE_OFFSET);
+          const int64_t p0 = indptr[20 * b], p1 = indptr[20 * b + 20];
+          if (!k || !o || k->size() != (size_t)(p1 - p0) * 4 || o->size() != 21 * 8) { ++wrong; continue; }
+          if (std::memcmp(k->data(), indices.data() + p0, k->size()) != 0) ++wrong;
+          oc.drop(1, b);
+          oc.drop(1, b);
+        }
+      };
+      std::thread u0(user), u1(user);
+      pre.join(); u0.join(); u1.join();
+      CHECK_TRUE(wrong == 0);
+      CHECK_TRUE(oc.pending() == 0);
+    }
   }
 
   // shutdown with traffic possibly still queued
