@@ -139,7 +139,25 @@ class LinearMethodNode:
         v = r.value(1)
         self.binary = len(v) == 0
         self.val = np.ones(len(self.idx)) if self.binary else v.astype(np.float64)
+        if td.has("text") and td.text == "TERAFEA":
+            return self._group_info(info).encode()
         return info["text"].encode()
+
+    def _group_info(self, info: dict) -> str:
+        """TERAFEA keys carry their feature group in their top 10 bits.  The keys of all groups stay in one key space
+        (the groups' key ranges cannot overlap), but the scheduler cuts every group into blocks of its own, so it gets
+        one slot per group: id, key range, non-zeros, examples in which the group occurs (src/proto/example.proto)."""
+        gid = (self.idx >> U64(54)).astype(np.int64)
+        row_of = np.repeat(np.arange(len(self.off) - 1, dtype=np.int64), np.diff(self.off))
+        out = cfg.ExampleInfo(num_ex=int(info["num_ex"]))
+        slots = [cfg.SlotInfo(format="DENSE", id=0, min_key=0, max_key=1, nnz_ele=len(self.y), nnz_ex=len(self.y))]
+        for g in np.unique(gid).tolist():
+            m = gid == g
+            k = self.idx[m]
+            slots.append(cfg.SlotInfo(format="SPARSE_BINARY" if self.binary else "SPARSE", id=int(g), min_key=int(k.min()),
+                                      max_key=int(k.max()) + 1, nnz_ele=int(m.sum()), nnz_ex=int(len(np.unique(row_of[m])))))
+        out.slot = slots
+        return dumps(out)
 
     # ------------------------------------------------------------------ PREPROCESS_DATA
     def preprocess(self, T: int) -> None:
@@ -413,6 +431,7 @@ class BatchScheduler:
         t = self._submit(_call("LOAD_DATA"))
         num_ex = nnz = 0
         kmin, kmax = 2**64 - 1, 0
+        per_slot: dict = {}
         for text in self.cust.take_replies(t).values():
             info = parse(text.decode(), cfg.ExampleInfo)
             num_ex += info.num_ex
@@ -421,13 +440,25 @@ class BatchScheduler:
                     continue
                 nnz += s.nnz_ele
                 kmin, kmax = min(kmin, s.min_key), max(kmax, s.max_key)
+                a = per_slot.setdefault(int(s.id), [2**64 - 1, 0, 0, 0])
+                a[0], a[1], a[2], a[3] = min(a[0], s.min_key), max(a[1], s.max_key), a[2] + s.nnz_ele, a[3] + s.nnz_ex
         self.num_ex = num_ex
-        # feature blocks (batch_solver.cc:48-66)
-        per_row = nnz / max(num_ex, 1)
-        nblk = max(int(math.ceil(per_row * sol.feature_block_ratio)), 1) if per_row > 1 + 1e-6 and sol.feature_block_ratio > 0 else 1
-        span = kmax - kmin
-        bounds = [kmin + span * i // nblk for i in range(nblk)] + [kmax]
-        self.blocks = [(bounds[i], bounds[i + 1]) for i in range(nblk)]
+        # feature blocks (batch_solver.cc:48-66): every feature group (slot) is cut by its own density over its own
+        # key range; data that comes as one slot is cut as one group over [min_key, max_key)
+        if len(per_slot) > 1:
+            from ..models.darlin import group_blocks
+
+            cut = group_blocks([(g, a[0], a[1], a[2], a[3]) for g, a in sorted(per_slot.items())], sol.feature_block_ratio)
+            self.blocks = [(b, e) for _, b, e in cut]
+            self.block_group = [g for g, _, _ in cut]
+        else:
+            per_row = nnz / max(num_ex, 1)
+            nblk = max(int(math.ceil(per_row * sol.feature_block_ratio)), 1) if per_row > 1 + 1e-6 and sol.feature_block_ratio > 0 else 1
+            span = kmax - kmin
+            bounds = [kmin + span * i // nblk for i in range(nblk)] + [kmax]
+            self.blocks = [(bounds[i], bounds[i + 1]) for i in range(nblk)]
+            self.block_group = None
+        nblk = len(self.blocks)
         self._submit(_call("PREPROCESS_DATA"))
         # iterations
         tau = sol.max_block_delay
@@ -437,7 +468,12 @@ class BatchScheduler:
         # its top 10 bits, so a group's blocks are those whose key range meets the group's.
         prior: List[int] = []
         prng = np.random.RandomState(int(self.flags.seed) + 1)
-        for g in sol.prior_fea_group:
+        if self.block_group is not None:
+            from ..models.darlin import prior_block_order
+
+            prior = prior_block_order(self.block_group, [int(g) for g in sol.prior_fea_group],
+                                      int(sol.num_iter_for_prior_fea_group), bool(sol.random_feature_block_order), int(self.flags.seed))
+        for g in ([] if self.block_group is not None else sol.prior_fea_group):
             glo, ghi = int(g) << 54, (int(g) + 1) << 54
             tmp = [k for k, (b0, b1) in enumerate(self.blocks) if max(b0, glo) < min(b1, ghi)]
             for _ in range(int(sol.num_iter_for_prior_fea_group) if tmp else 0):
@@ -453,7 +489,7 @@ class BatchScheduler:
             t_it = time.time()
             order = (prior if it == 0 else []) + orders[it].tolist()
             for i, b in enumerate(order):
-                kw = dict(key=self.blocks[b], fea_grp=[1])
+                kw = dict(key=self.blocks[b], fea_grp=[1 if self.block_group is None else int(self.block_group[b])])
                 if i == 0:
                     kw["kkt_filter_threshold"] = kkt
                     if reset:

@@ -278,3 +278,71 @@ def test_many_servers_own_ranges_in_numeric_order(tmp_path):
         prev = max(m)
         seen += 1
     assert seen >= 10
+
+
+def test_terafea_groups_are_cut_group_by_group(tmp_path):
+    """TERAFEA data: every feature group (top 10 bits of a key) gets blocks of its own, by its own density over its own
+    key range, and the important group's blocks are swept first — the schedule of the reference's CTR job — and the run
+    equals the oracle's with the same groups."""
+    rows, passes, lam, ratio = 900, 3, 0.3, 1.0
+    g = torch.Generator().manual_seed(11)
+    lines, shard_rows = [], []
+    keys_per_row = []
+    w_true = {}
+    for r in range(rows):
+        ks = set()
+        ks.add((127 << 54) | int(torch.randint(0, 40, (1,), generator=g)))                     # one feature per example
+        ks.update((120 << 54) | int(v) for v in torch.randint(0, 300, (3,), generator=g))
+        ks.update((5 << 54) | int(v) for v in torch.randint(0, 500, (6,), generator=g))
+        keys_per_row.append(sorted(ks))
+    allk = sorted({k for ks in keys_per_row for k in ks})
+    wv = torch.randn(len(allk), generator=g) * (torch.rand(len(allk), generator=g) < 0.1)
+    w_true = dict(zip(allk, wv.tolist()))
+    ys = []
+    for r, ks in enumerate(keys_per_row):
+        s = sum(w_true[k] for k in ks) + 0.1 * float(torch.randn(1, generator=g))
+        ys.append(1 if s > 0 else -1)
+        lines.append(f"{1 if ys[-1] > 0 else 0} {r} | " + " ".join(str(k) for k in ks))
+    os.makedirs(tmp_path / "train")
+    h = rows // 2
+    for i, part in enumerate((lines[:h], lines[h:])):
+        (tmp_path / "train" / f"part-{i:03d}").write_text("\n".join(part) + "\n")
+    text = CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=lam, ratio=ratio, passes=passes, tail=0)
+    text = text.replace("text: LIBSVM", "text: TERAFEA").replace(
+        "random_feature_block_order: true", "random_feature_block_order: true prior_fea_group: 127 num_iter_for_prior_fea_group: 2")
+    from parameter_server_b200.apps import linear_cpu
+
+    seen = []
+    orig = linear_cpu.BatchScheduler._submit
+
+    def spy(self, payload, wait=True, wait_time=-1):
+        call = linear_cpu.parse(payload.decode(), cfg.LMCall)
+        if call.cmd == "UPDATE_MODEL":
+            seen.append((int(call.fea_grp[0]), call.key.begin, call.key.end))
+        return orig(self, payload, wait, wait_time)
+
+    linear_cpu.BatchScheduler._submit = spy
+    try:
+        prog = run_local_threads(cfg.Flags(num_workers=2, num_servers=2, seed=0), text)
+    finally:
+        linear_cpu.BatchScheduler._submit = orig
+    blocks = sorted(set(seen), key=lambda b: b[1])
+    by_group = {gid: [b for b in blocks if b[0] == gid] for gid in (5, 120, 127)}
+    # one feature per example: one block; the denser groups: ceil(non-zeros per example x ratio) blocks each
+    assert len(by_group[127]) == 1 and len(by_group[120]) == 3 and len(by_group[5]) == 6 and len(blocks) == 10
+    for gid, bs in by_group.items():
+        assert all(b[1] >> 54 == gid and (b[2] - 1) >> 54 == gid for b in bs)              # a block never crosses groups
+    assert seen[:2] == by_group[127] * 2 and len(seen) == 2 + passes * 10                   # the prior sweeps, then the passes
+
+    def shard(lo, hi):
+        off = np.concatenate([[0], np.cumsum([len(k) for k in keys_per_row[lo:hi]])]).astype(np.int64)
+        cols = np.array([k for ks in keys_per_row[lo:hi] for k in ks], dtype=np.uint64)
+        return off, cols, np.ones(len(cols)), np.array(ys[lo:hi], dtype=np.float64)
+
+    ref = DarlinRef([shard(0, h), shard(h, rows)], None,
+                    RefConfig(lambda1=lam, max_pass=passes, feature_block_ratio=ratio, epsilon=1e-6, delta_init=1, delta_max=5,
+                              kkt_ratio=10, seed=0, feature_group_bits=10, prior_fea_group=(127,), num_iter_for_prior_fea_group=2))
+    rprog = ref.run()
+    assert len(prog) == len(rprog) == passes
+    for p, r in zip(prog, rprog):
+        assert p["objv"] == pytest.approx(r.objv, rel=1e-9) and p["nnz_w"] == r.nnz_w
