@@ -10,6 +10,7 @@ Counterparts of the reference's ``text2proto`` / ``proto2bin`` / ``showins`` pro
   python -m parameter_server_b200.data.tools info ADFEA 'data/ctr/part-.*'
   python -m parameter_server_b200.data.tools bin2text out/train out/train.libsvm
   python -m parameter_server_b200.data.tools split rcv1_train.binary rcv1 1000 13   # train/part-000.. + test/part-013..
+  python -m parameter_server_b200.data.tools rcv1 rcv1                               # fetch + unpack + split (data/rcv1_binary.sh)
   python -m parameter_server_b200.data.tools text2proto LIBSVM data/part-000 out/part   # out/part.recordio + out/part.info
   python -m parameter_server_b200.data.tools showins out/part.recordio 10
   python -m parameter_server_b200.data.tools proto2bin out/part.recordio out/part_bin
@@ -120,6 +121,37 @@ def split_parts(path: str, out_dir: str, lines_per_part: int = 1000, train_parts
     return counts
 
 
+RCV1_URL = "http://www.csie.ntu.edu.tw/~cjlin/libsvmtools/datasets/binary/rcv1_train.binary.bz2"
+
+
+def rcv1(out_dir: str = "rcv1", url: str = RCV1_URL, lines_per_part: int = 1000, train_parts: int = 13) -> dict:
+    """The reference's data set script (data/rcv1_binary.sh): fetch ``rcv1_train.binary.bz2`` unless
+    ``rcv1_train.binary`` is already in the current directory, unpack it, and cut it into ``<out_dir>/train/part-000..``
+    (the first ``train_parts`` parts of ``lines_per_part`` lines) and ``<out_dir>/test/part-...`` (the rest).  Without a
+    network the download fails with the URL in the message: put the file there by hand and run the command again."""
+    import bz2
+    import os
+    import shutil
+    import urllib.request
+
+    plain = "rcv1_train.binary"
+    if not os.path.exists(plain):
+        packed = plain + ".bz2"
+        if not os.path.exists(packed):
+            try:
+                with urllib.request.urlopen(url, timeout=60) as r, open(packed + ".tmp", "wb") as f:
+                    shutil.copyfileobj(r, f)
+            except OSError as e:
+                if os.path.exists(packed + ".tmp"):
+                    os.remove(packed + ".tmp")
+                raise OSError(f"cannot fetch {url} ({e}); download it to ./{packed} by hand and run this again") from e
+            os.replace(packed + ".tmp", packed)
+        with bz2.open(packed, "rb") as src, open(plain + ".tmp", "wb") as dst:
+            shutil.copyfileobj(src, dst)
+        os.replace(plain + ".tmp", plain)
+    return split_parts(plain, out_dir, lines_per_part, train_parts)
+
+
 def main(argv=None) -> int:
     a = list(sys.argv[1:] if argv is None else argv)
     if not a:
@@ -142,6 +174,8 @@ def main(argv=None) -> int:
     elif a[0] == "proto2bin":
         from .instance import proto2bin
         print(proto2bin(a[1], a[2]))
+    elif a[0] == "rcv1":
+        print(rcv1(a[1] if len(a) > 1 else "rcv1", a[2] if len(a) > 2 else RCV1_URL))
     elif a[0] == "split":
         print(split_parts(a[1], a[2], int(a[3]) if len(a) > 3 else 1000, int(a[4]) if len(a) > 4 else 13))
     else:

@@ -5,6 +5,7 @@ like the reference's ``script/local.sh`` (rank 0 = scheduler ``H`` on 127.0.0.1)
   python -m parameter_server_b200.launch -num_servers 2 -num_workers 2 -app config/rcv1_l1lr.conf
   python -m parameter_server_b200.launch -gpus 8 -app config/ctr_ftrl.conf
   python -m parameter_server_b200.launch -mpi_hostfile hosts -num_servers 2 -num_workers 2 -app job.conf   # mpirun over machines
+  python -m parameter_server_b200.launch -mpi_conf config/mpi.conf                                         # the reference's mpi.conf
 """
 from __future__ import annotations
 
@@ -31,7 +32,8 @@ def mpi_command(args, flags, hostfile: str) -> list:
     from .runtime import host
 
     n = 1 + flags.num_workers + flags.num_servers + max(int(flags.num_unused), 0)
-    cmd = ["mpirun", "-np", str(n), "--hostfile", hostfile, sys.executable, "-m", "parameter_server_b200.ps", *args]
+    cmd = ["mpirun", "-np", str(n), *(["--hostfile", hostfile] if hostfile != "-" else []),
+           sys.executable, "-m", "parameter_server_b200.ps", *args]
     if not any(a.lstrip("-").split("=")[0] == "scheduler" for a in args):
         ip = host().local_ip(flags.interface or "")
         if not ip:
@@ -40,9 +42,60 @@ def mpi_command(args, flags, hostfile: str) -> list:
     return cmd
 
 
+def read_mpi_conf(path: str) -> tuple:
+    """The reference's ``mpi.conf`` (config/mpi.conf, read by script/mpi_root.sh and script/mpi_node.sh): shell
+    assignments ``name=value``.  Returns (node arguments, hostfile or "").  ``num_workers / num_servers / num_threads /
+    report_interval / load_limit / line_limit / prefetch_mem_limit_kb`` become ``-name value``; ``app_conf`` becomes
+    ``-app`` (relative to the conf file, like the scripts); values that are flags themselves (``verbose="-verbose"``,
+    ``parallel_match="-noparallel_match"`` ...) are passed on as they are; ``scheduler_network_interface`` becomes
+    ``-interface`` and, with ``scheduler_network_port``, fixes the scheduler's address."""
+    import os
+    import shlex
+
+    here = os.path.dirname(os.path.abspath(path))
+    vals = {}
+    with open(path) as f:
+        for line in f:
+            line = line.split("#", 1)[0].strip()
+            if "=" not in line:
+                continue
+            name, v = line.split("=", 1)
+            toks = shlex.split(v)
+            vals[name.strip()] = toks[0] if toks else ""
+    out = []
+    for name in ("num_workers", "num_servers", "num_threads", "report_interval", "load_limit", "line_limit", "prefetch_mem_limit_kb"):
+        if vals.get(name):
+            out += [f"-{name}", vals[name]]
+    if vals.get("app_conf"):
+        out += ["-app", os.path.normpath(os.path.join(here, vals["app_conf"]))]
+    for name in ("verbose", "log_to_file", "log_instant", "print_van", "shuffle_fea_id", "parallel_match", "mmap_training_data",
+                 "prefetch_detail"):
+        if vals.get(name, "").startswith("-"):
+            out.append(vals[name])
+    iface, port = vals.get("scheduler_network_interface", ""), vals.get("scheduler_network_port", "")
+    if iface:
+        out += ["-interface", iface]
+    if port:
+        from .runtime import host
+
+        ip = host().local_ip(iface)
+        if not ip:
+            raise RuntimeError(f"mpi.conf: no IPv4 address on interface '{iface}'")
+        out += ["-scheduler", f"role:SCHEDULER,hostname:'{ip}',port:{int(port)},id:'H'"]
+    hostfile = vals.get("hostfile", "")
+    return out, (os.path.normpath(os.path.join(here, hostfile)) if hostfile else "")
+
+
 def main(argv=None) -> int:
     args = list(sys.argv[1:] if argv is None else argv)
     hostfile = ""
+    for i, a in enumerate(args):                      # -mpi_conf FILE: the reference's mpi.conf; later arguments win
+        if a.lstrip("-") == "mpi_conf" and i + 1 < len(args):
+            conf_args, hostfile = read_mpi_conf(args[i + 1])
+            args = conf_args + args[:i] + args[i + 2:]
+            if not hostfile:
+                hostfile = "-"                         # an MPI job on this machine only: mpirun without a host file
+            break
     for i, a in enumerate(args):                      # -mpi_hostfile FILE belongs to the launcher, not to the nodes
         if a.lstrip("-") == "mpi_hostfile" and i + 1 < len(args):
             hostfile = args[i + 1]

@@ -1,6 +1,7 @@
 """Addresses of CPU nodes: a job whose scheduler is not on the loopback makes every node advertise the address of a
 real interface (-interface, or the first one that is up), so that nodes on other machines can reach it."""
 import os
+import socket
 import subprocess
 import sys
 
@@ -92,6 +93,54 @@ def test_mpirun_launch(tmp_path):
     assert hostfile == str(tmp_path / "hosts")
     assert "parameter_server_b200.ps" in line and "-my_rank" not in line and f"hostname:'{ip}'" in line and "mpi_hostfile" not in line
     assert len(read_model_text(str(tmp_path / "model_S0"))) > 10
+
+
+def test_mpi_conf_of_the_reference_launch_scripts(tmp_path):
+    """-mpi_conf: the shell-assignment file that the reference's mpi_root.sh / mpi_node.sh read gives the node flags, the
+    job file (relative to the conf), the scheduler's port and the host file."""
+    from parameter_server_b200.launch import read_mpi_conf
+
+    ip = host().local_ip("")
+    bindir = tmp_path / "bin"
+    bindir.mkdir()
+    exe = bindir / "mpirun"
+    exe.write_text(FAKE_MPIRUN)
+    exe.chmod(0o755)
+    (tmp_path / "hosts").write_text("localhost slots=8\n")
+    off, idx, vals, y = planted(500, 512, 8, 4, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    (tmp_path / "job.conf").write_text(CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.5,
+                                                   ratio=0.5, passes=2, tail=0))
+    port = socket.socket()
+    port.bind(("127.0.0.1", 0))
+    pnum = port.getsockname()[1]
+    port.close()
+    (tmp_path / "mpi.conf").write_text(f"""#!/bin/bash
+num_workers=2
+num_servers=1
+num_threads=3     # per node
+scheduler_network_interface=""
+scheduler_network_port={pnum}
+app_conf=job.conf
+report_interval=0
+verbose=""
+print_van="-print_van"
+parallel_match="-noparallel_match"
+load_limit=0
+hostfile=hosts
+""")
+    args, hostfile = read_mpi_conf(str(tmp_path / "mpi.conf"))
+    assert hostfile == str(tmp_path / "hosts") and args[:6] == ["-num_workers", "2", "-num_servers", "1", "-num_threads", "3"]
+    assert "-print_van" in args and "-noparallel_match" in args and "-verbose" not in args
+    assert args[args.index("-app") + 1] == str(tmp_path / "job.conf") and f"port:{pnum}" in args[args.index("-scheduler") + 1]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root, PATH=str(bindir) + os.pathsep + os.environ["PATH"], FAKE_MPI_LOG=str(tmp_path / "mpi.log"))
+    r = subprocess.run([sys.executable, "-m", "parameter_server_b200.launch", "-mpi_conf", str(tmp_path / "mpi.conf")],
+                       cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    hostfile, line = open(tmp_path / "mpi.log").read().splitlines()[:2]
+    assert hostfile == str(tmp_path / "hosts") and f"hostname:'{ip}',port:{pnum}" in line and "-mpi_conf" not in line
+    assert len(read_model_text(str(tmp_path / "model_S0"))) > 10 and os.path.exists(tmp_path / "van_W0")
 
 
 def test_stand_by_node_joins_and_leaves_with_the_job(tmp_path):

@@ -51,3 +51,30 @@ def test_split_into_train_and_test_parts(tmp_path):
     back = "".join((tmp_path / "out" / d / n).read_text() for d, names in (("train", tr), ("test", te)) for n in names)
     assert back == "".join(lines)
     assert len((tmp_path / "out" / "test" / "part-004").read_text().splitlines()) == 7
+
+
+def test_rcv1_fetch_unpack_split(tmp_path, monkeypatch):
+    """The data set script end to end, with a file:// URL in place of the download; then the failure without a network."""
+    import bz2
+
+    import pytest
+
+    lines = [f"{'1' if i % 2 else '-1'} {i % 9 + 1}:0.5\n" for i in range(35)]
+    served = tmp_path / "served.bz2"
+    with bz2.open(served, "wt") as f:
+        f.writelines(lines)
+    work = tmp_path / "work"
+    work.mkdir()
+    monkeypatch.chdir(work)
+    got = tools.rcv1("rcv1", served.as_uri(), lines_per_part=10, train_parts=2)
+    assert got == {"train": 2, "test": 2, "lines": 35}
+    assert (work / "rcv1_train.binary").read_text() == "".join(lines)
+    assert sorted(p.name for p in (work / "rcv1" / "test").iterdir()) == ["part-002", "part-003"]
+    # a second run finds the unpacked file and does not fetch
+    assert tools.rcv1("again", "file:///nonexistent", lines_per_part=10, train_parts=2)["lines"] == 35
+    other = tmp_path / "offline"
+    other.mkdir()
+    monkeypatch.chdir(other)
+    with pytest.raises(OSError, match="by hand"):
+        tools.rcv1("rcv1", "file:///nonexistent/rcv1_train.binary.bz2")
+    assert list(other.iterdir()) == []
