@@ -98,3 +98,27 @@ def test_text2proto_showins_proto2bin(tmp_path, capsys):
     assert m["offset"].tolist() == [0, 3, 5, 6] and m["index"].tolist() == [3, 7, 10, 1, 7, 2]
     assert np.allclose(m["value"], [0.5, 1.5, 2, 1, 0.25, 3])
     assert np.fromfile(str(tmp_path / "bin") + ".label", np.float32).tolist() == [1, -1, 1]
+
+
+def test_codec_roundtrip_property():
+    hyp = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+
+    u64 = st.integers(min_value=0, max_value=(1 << 64) - 1)
+    f32 = st.floats(width=32, allow_nan=False, allow_infinity=True)
+    group = st.tuples(st.integers(0, 4095), st.lists(u64, max_size=12), st.booleans()).flatmap(
+        lambda t: st.tuples(st.just(t[0]), st.just(t[1]), st.lists(f32, min_size=len(t[1]), max_size=len(t[1])) if t[2] else st.just([])))
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.one_of(st.none(), f32), st.lists(group, max_size=5), st.one_of(st.none(), st.integers(-(1 << 63), (1 << 63) - 1)))
+    def check(label, groups, ins_id):
+        ins = I.Instance(label=label, ins_id=ins_id, fea_grp=[
+            I.FeatureGroup(g, np.asarray(ids, np.uint64), np.asarray(vals, np.float32)) for g, ids, vals in groups])
+        back = I.Instance.decode(ins.encode())
+        assert (back.label is None) == (label is None) and (label is None or np.float32(back.label) == np.float32(label))
+        assert back.ins_id == ins_id and len(back.fea_grp) == len(groups)
+        for b, (g, ids, vals) in zip(back.fea_grp, groups):
+            assert b.grp_id == g and b.fea_id.tolist() == ids
+            assert np.array_equal(b.fea_val, np.asarray(vals, np.float32))
+
+    check()
