@@ -134,6 +134,7 @@ class Ocean {
   BytesPtr get(int grp, size_t blk, Kind kind) {
     std::unique_lock<std::mutex> l(mu_);
     auto& e = entry(grp, blk);
+    ++e.users;            // counted before any wait: the block cannot leave memory under a thread that waits for it
     if (e.state == Entry::LOADED || e.state == Entry::LOADING) ++stats_.hits; else ++stats_.misses;
     if (e.state == Entry::ABSENT || e.state == Entry::QUEUED) {
       // not loaded and no loader has it: the caller loads it itself instead of waiting for a free job slot
@@ -150,11 +151,10 @@ class Ocean {
       e2.data = std::move(data);
       e2.state = Entry::LOADED;
       cv_.notify_all();
+    } else {
+      cv_.wait(l, [&] { return entry(grp, blk).state == Entry::LOADED; });
     }
-    cv_.wait(l, [&] { return entry(grp, blk).state == Entry::LOADED; });
-    auto& e3 = entry(grp, blk);
-    ++e3.users;
-    return e3.data[kind];
+    return entry(grp, blk).data[kind];
   }
 
   // One user less; the block leaves memory when nobody uses it and no prefetch is still to be consumed
