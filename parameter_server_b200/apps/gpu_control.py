@@ -148,7 +148,7 @@ class GpuBatchScheduler:
             self.progress.append(rec)
             if self.verbose:
                 print_progress(it, Progress(p0.objv, p0.relative_objv, int(p0.nnz_w), p0.violation, int(p0.nnz_active_set),
-                                            p0.kkt_threshold, time.time() - t_it), file=sys.stderr)
+                                            p0.kkt_threshold, time.time() - t_it), file=sys.stderr, busy=rec["busy_time"] or None)
             if 0 < p0.relative_objv <= c.epsilon:
                 if reset:
                     break

@@ -516,7 +516,7 @@ class BatchScheduler:
                        kkt_threshold=kkt, total_time=time.time() - t_start, busy_time=busy)
             self.progress.append(rec)
             if verbose:
-                print_progress(it, Progress(objv, rel, nnz_w, vio, nnz_as, kkt, time.time() - t_it), file=sys.stderr)
+                print_progress(it, Progress(objv, rel, nnz_w, vio, nnz_as, kkt, time.time() - t_it), file=sys.stderr, busy=busy or None)
             kkt = vio / max(num_ex, 1) * conf.darling.kkt_filter_threshold_ratio
             if 0 < rel <= sol.epsilon:
                 if reset:

@@ -785,14 +785,15 @@ class DarlinSolver:
         return path
 
 
-def print_progress(it: int, p: Progress, file=sys.stderr) -> None:
-    """Progress table in the reference's layout (linear_method.cc:181-231, darling.cc:480-501)."""
+def print_progress(it: int, p: Progress, file=sys.stderr, busy=None) -> None:
+    """Progress table in the reference's layout (linear_method.cc:181-231, darling.cc:480-501).  ``busy``: the nodes'
+    compute seconds of this pass; a scheduler that has them prints the reference's "(app:min max) total" columns."""
     if it == 0:
-        print("  iter |  objective    relative     |w|_0 |      KKT filter      |  time", file=file)
-        print("       |                                  | threshold  #active   |  (sec)", file=file)
-        print(" ------+----------------------------------+----------------------+-------", file=file)
-    print(f" {it:5d} | {p.objv:.5e}  {p.relative_objv:.3e} {p.nnz_w:8d} | {p.kkt_threshold:.1e} {p.nnz_active:11d} | {p.seconds:6.2f}",
-          file=file)
+        print("     |        training        |  sparsity |      KKT filter     |" + ("    time (sec.)" if busy else "  time"), file=file)
+        print("iter |  objective    relative |     |w|_0 | threshold  #activet |" + ("(app:min max) total" if busy else " (sec)"), file=file)
+        print(" ----+------------------------+-----------+---------------------+" + ("-----------------" if busy else "-------"), file=file)
+    tail = f"{min(busy):6.1f}{max(busy):6.1f}{p.seconds:6.1f}" if busy else f"{p.seconds:6.2f}"
+    print(f"{it:4d} | {p.objv:.5e}  {p.relative_objv:.3e} |{p.nnz_w:10d} | {p.kkt_threshold:.1e} {p.nnz_active:11d} |{tail}", file=file)
 
 
 def smoke(dev) -> None:
