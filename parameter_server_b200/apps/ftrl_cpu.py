@@ -49,6 +49,7 @@ class FTRLNode:
         self.store = self.param
         self.cust = H.Customer(ctx.po, app_conf.app_name, self.process, False)
         self.examples, self.loss_sum, self.steps = 0, 0.0, 0
+        self._reporting = threading.Event()       # set when the periodic server reports must end
 
     def _take(self, t: int):
         """The replies of pull ``t`` concatenated in server (= key) order: (keys, values)."""
@@ -63,11 +64,33 @@ class FTRLNode:
         if call.cmd == "UPDATE_MODEL":
             if self.ctx.is_worker:
                 self.update_model()
+            else:
+                self._start_server_reports()
         elif call.cmd == "EVALUATE_PROGRESS":
+            self._reporting.set()                 # training is over: the periodic reports end
             reply = self.progress()
         elif call.cmd == "SAVE_MODEL":
             self.save_model()
         self.cust.reply(msg, payload=reply)
+
+    def _penalty(self):
+        n1, n2, nnz = self.store.stats()
+        lam = list(self.conf.penalty.get("lambda")) + [0.0, 0.0]
+        return lam[0] * n1 + 0.5 * lam[1] * math.sqrt(max(n2, 0.0)), nnz
+
+    def _start_server_reports(self) -> None:
+        """A server returns from UPDATE_MODEL at once and keeps reporting the penalty and the non-zeros of its shard
+        every ``eval_interval`` seconds while the workers train (FTRL::updateModel / evalProgress, ftrl.cc:61-69,184-197)."""
+        every = float(self.conf.solver.eval_interval)
+        if every <= 0:
+            return
+
+        def loop():
+            while not self._reporting.wait(every):
+                pen, nnz = self._penalty()
+                self.cust.submit("H", payload=_call("REPORT_PROGRESS", progress=cfg.Progress(objv=pen, nnz_w=int(nnz))))
+
+        threading.Thread(target=loop, name=f"{self.ctx.node_id}-progress", daemon=True).start()
 
     def update_model(self) -> None:
         """FTRL::updateModel: one pass over this worker's files in minibatches."""
@@ -154,10 +177,8 @@ class FTRLNode:
             P.wait_out(H.kServerGroup, last_push)
 
     def progress(self) -> bytes:
-        n1, n2, nnz = self.store.stats() if self.ctx.is_server else (0.0, 0.0, 0)
-        lam = list(self.conf.penalty.get("lambda")) + [0.0, 0.0]
-        p = cfg.Progress(objv=self.loss_sum + lam[0] * n1 + 0.5 * lam[1] * math.sqrt(max(n2, 0.0)), nnz_w=nnz,
-                         num_ex_trained=self.examples)
+        pen, nnz = self._penalty() if self.ctx.is_server else (0.0, 0)
+        p = cfg.Progress(objv=self.loss_sum + pen, nnz_w=nnz, num_ex_trained=self.examples)
         return dumps(p, oneline=True).encode()
 
     def save_model(self) -> None:
@@ -167,6 +188,7 @@ class FTRLNode:
             write_model_text(f"{mo.file[0]}_{self.ctx.node_id}", k, v)
 
     def stop(self) -> None:
+        self._reporting.set()
         self.cust.stop()
         self.param.stop()
 
@@ -181,6 +203,10 @@ class FTRLScheduler:
         self.verbose = True
         self.reports: List[dict] = []          # periodic worker reports, in arrival order
         self._seen, self._loss = 0, 0.0
+        self._mu = threading.Lock()
+        self._window = [0.0, 0]                # workers' loss sum and examples since the last printed line
+        self._servers: Dict[str, tuple] = {}   # server id -> its latest (penalty, non-zeros)
+        self.lines: List[str] = []             # the progress lines printed so far
         self.cust = H.Customer(ctx.po, app_conf.app_name, self.process, False)
         self.progress: List[dict] = []
 
@@ -192,19 +218,47 @@ class FTRLScheduler:
         if call.cmd != "REPORT_PROGRESS":
             return
         p = call.progress
-        self._seen += p.num_ex_trained
-        self._loss += p.objv
-        rec = dict(worker=msg.sender, examples=self._seen, mean_loss=p.objv / max(p.num_ex_trained, 1))
-        self.reports.append(rec)
+        with self._mu:
+            if not p.has("num_ex_trained"):        # a server: penalty and non-zeros of its shard
+                self._servers[msg.sender] = (p.objv, int(p.nnz_w))
+                return
+            self._seen += p.num_ex_trained
+            self._loss += p.objv
+            self._window[0] += p.objv
+            self._window[1] += p.num_ex_trained
+            rec = dict(worker=msg.sender, examples=self._seen, mean_loss=p.objv / max(p.num_ex_trained, 1))
+            self.reports.append(rec)
+        if float(self.app_conf.linear_method.solver.eval_interval) <= 0:
+            self.show_progress()                   # every report is shown when there is no interval
+
+    def show_progress(self) -> None:
+        """FTRL::showProgress (ftrl.cc:203-219): examples so far, the workers' mean loss since the last line, the servers'
+        penalty and non-zeros as last reported."""
+        with self._mu:
+            loss, n = self._window
+            self._window = [0.0, 0]
+            pen = sum(v[0] for v in self._servers.values())
+            nnz = sum(v[1] for v in self._servers.values())
+            line = "%10d examples, loss %.5e, penalty %.5e, |w|_0 %8d" % (self._seen, loss / max(n, 1), pen, nnz)
+            self.lines.append(line)
         if self.verbose:
-            print("%10d examples, loss %.5e (%s)" % (rec["examples"], rec["mean_loss"], rec["worker"]), file=sys.stderr)
+            print(line, file=sys.stderr)
 
     def run(self, verbose: bool = True) -> List[dict]:
         H = self.H
         self.verbose = verbose
         t0 = time.time()
-        t = self.cust.submit(H.kWorkerGroup, payload=_call("UPDATE_MODEL"))
-        self.cust.wait_out(H.kWorkerGroup, t)            # workers return when their data is exhausted and applied
+        every = float(self.app_conf.linear_method.solver.eval_interval)
+        done = threading.Event()
+        if every > 0:                                    # the thread that shows the merged progress (ftrl.cc:41-48)
+            def shower():
+                while not done.wait(every):
+                    self.show_progress()
+
+            threading.Thread(target=shower, name="H-progress", daemon=True).start()
+        t = self.cust.submit(H.kActiveGroup, payload=_call("UPDATE_MODEL"))
+        self.cust.wait_out(H.kActiveGroup, t)            # workers return when their data is exhausted and applied;
+        done.set()                                       # servers return at once and report while the workers train
         t = self.cust.submit(H.kActiveGroup, payload=_call("EVALUATE_PROGRESS"))
         self.cust.wait_out(H.kActiveGroup, t)
         objv, nnz_w, examples = 0.0, 0, 0
@@ -213,7 +267,7 @@ class FTRLScheduler:
             objv += p.objv
             nnz_w += p.nnz_w
             examples += p.num_ex_trained
-        rec = dict(objv=objv, nnz_w=nnz_w, examples=examples, seconds=time.time() - t0, reports=list(self.reports))
+        rec = dict(objv=objv, nnz_w=nnz_w, examples=examples, seconds=time.time() - t0, reports=list(self.reports), lines=list(self.lines))
         self.progress.append(rec)
         if verbose:
             print("%10d examples, objective %.5e, |w|_0 %8d, %.2f s" % (examples, objv, nnz_w, rec["seconds"]), file=sys.stderr)

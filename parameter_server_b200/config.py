@@ -67,7 +67,7 @@ LMSolverConfig = Schema(
     F("tail_feature_filter_k", "int32", default=2), F("countmin_k", "int32", default=2),
     F("countmin_n_ratio", "double", default=2.0), F("countmin_n", "double", default=1e8),
     F("max_num_parallel_groups_in_preprocessing", "int32", default=1000),
-    F("max_data_buf_size_in_mb", "int32", default=1000), F("eval_interval", "int32", default=5))
+    F("max_data_buf_size_in_mb", "int32", default=1000), F("eval_interval", "double", default=5))
 DarlingConfig = Schema("LM.DarlingConfig", F("delta_init_value", "double", default=1.0),
                        F("delta_max_value", "double", default=5.0),
                        F("kkt_filter_threshold_ratio", "double", default=10.0))

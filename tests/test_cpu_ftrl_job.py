@@ -84,6 +84,29 @@ def test_two_workers_learn(tmp_path):
     assert np.mean(np.logaddexp(0.0, -yy * xw)) < 0.66      # log 2 = 0.693 for the constant predictor
 
 
+def test_progress_lines_merge_worker_and_server_reports(tmp_path):
+    """eval_interval > 0: workers report loss and examples, servers their penalty and non-zeros, every interval; the
+    scheduler shows one merged line per interval in the reference's format."""
+    import re
+
+    rows, cols = 60000, 4096
+    off, idx, vals, y = planted(rows, cols, 8, 5, False)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    text = CONF.format(train=tmp_path / "train", out=tmp_path, mb=50, tail=0).replace("eval_interval: 0", "eval_interval: 0.05")
+    prog = run_local_threads(cfg.Flags(num_workers=2, num_servers=2, seed=0), text)
+    assert prog[0]["examples"] == rows
+    lines = prog[0]["lines"]
+    if not lines:
+        pytest.skip("the job ended within one interval on this machine")
+    pat = re.compile(r"^\s*(\d+) examples, loss (\S+), penalty (\S+), \|w\|_0\s+(\d+)$")
+    got = [pat.match(l) for l in lines]
+    assert all(got)
+    seen = [int(m.group(1)) for m in got]
+    assert seen == sorted(seen) and 0 < seen[-1] <= rows
+    assert any(float(m.group(3)) > 0 and int(m.group(4)) > 0 for m in got) or len(lines) < 2    # the servers' reports arrived
+    assert 0.0 < float(got[-1].group(2)) < 1.5
+
+
 def test_processes_over_tcp(tmp_path):
     """The same job as five real processes (1 + 2 + 2) over the TCP van, started by the launcher."""
     import os
