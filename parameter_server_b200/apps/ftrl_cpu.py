@@ -199,7 +199,7 @@ class FTRLScheduler:
     def __init__(self, ctx: NodeContext, app_conf, flags: cfg.Flags):
         H = host()
         self.H, self.ctx, self.flags, self.app_conf = H, ctx, flags, app_conf
-        self.param = H.Customer(ctx.po, app_conf.parameter_name[0], None, True)
+        self.param = H.Customer(ctx.po, (list(app_conf.parameter_name) or [app_conf.app_name + "_w"])[0], None, True)
         self.verbose = True
         self.reports: List[dict] = []          # periodic worker reports, in arrival order
         self._seen, self._loss = 0, 0.0
@@ -259,6 +259,9 @@ class FTRLScheduler:
         t = self.cust.submit(H.kActiveGroup, payload=_call("UPDATE_MODEL"))
         self.cust.wait_out(H.kActiveGroup, t)            # workers return when their data is exhausted and applied;
         done.set()                                       # servers return at once and report while the workers train
+        for nid, text in self.cust.take_replies(t).items():
+            if bytes(text).startswith(b"ERROR: "):       # a GPU rank's training loop failed (apps/gpu_control.py)
+                raise RuntimeError(f"{nid}: {bytes(text)[7:].decode()}")
         t = self.cust.submit(H.kActiveGroup, payload=_call("EVALUATE_PROGRESS"))
         self.cust.wait_out(H.kActiveGroup, t)
         objv, nnz_w, examples = 0.0, 0, 0

@@ -18,6 +18,11 @@ with ``torch.distributed`` as the only control plane.  With ``-gpu_scheduler`` t
 
 The solver only needs ``nblk``, ``cfg``, ``block_group``, ``progress``, ``run_pass(order, reset, prior)`` and
 ``save_model(prefix)``, which is what the CPU test's stand-in provides.
+
+Online (FTRL) jobs follow ``FTRL::run`` (src/linear_method/ftrl.cc:38-59) the same way: one UPDATE_MODEL task runs a
+rank's whole training loop, the ranks send the reference's worker and server progress reports while they train, and
+the scheduler (the one of the CPU-node job, ``apps/ftrl_cpu.py::FTRLScheduler``) shows the merged line every
+``eval_interval``, collects the final progress and sends SAVE_MODEL (:func:`run_scheduled_online`).
 """
 from __future__ import annotations
 
@@ -236,5 +241,120 @@ def run_scheduled(group, flags: cfg.Flags, app_name: str, sol, model_prefix: str
     if node.failed:
         raise RuntimeError(f"rank {group.rank}: a task failed\n{node.failed}")
     out["progress"] = sol.progress
+    out["model"] = node.saved
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# online jobs: one UPDATE_MODEL task for the whole stream, periodic progress reports to the scheduler
+class GpuOnlineWorkerNode:
+    """Worker + server of one GPU rank of an online (FTRL) job.  The scheduler's single UPDATE_MODEL task runs the
+    rank's whole training loop on the node's executor thread; the loop calls :meth:`report` now and then, which
+    sends the reference's two kinds of REPORT_PROGRESS to the scheduler: the worker's (loss and examples since its
+    last report) and the server's (penalty and non-zeros of its shard) — src/linear_method/ftrl.cc:184-201."""
+
+    def __init__(self, ctx: NodeContext, app_name: str, run_training, final_progress, save_model, device=None):
+        self.ctx, self.device = ctx, device
+        self.run_training, self.final_progress, self.save_model = run_training, final_progress, save_model
+        self.result = None
+        self.saved: Optional[str] = None
+        self.failed: Optional[str] = None
+        self.cust = host().Customer(ctx.po, app_name, self.process, False)
+
+    def report(self, loss_sum: float, examples: int, penalty: float, nnz_w: int) -> None:
+        self.cust.submit("H", payload=_call("REPORT_PROGRESS", progress=cfg.Progress(objv=float(loss_sum), num_ex_trained=int(examples))))
+        self.cust.submit("H", payload=_call("REPORT_PROGRESS", progress=cfg.Progress(objv=float(penalty), nnz_w=int(nnz_w))))
+
+    def process(self, msg) -> None:
+        if not msg.request:
+            return
+        t0 = time.time()
+        reply = b""
+        try:
+            if self.device is not None and getattr(self.device, "type", "cpu") == "cuda":
+                import torch
+
+                torch.cuda.set_device(self.device)
+            call = parse(msg.payload.decode(), cfg.LMCall)
+            if self.ctx.hb_state is not None:
+                self.ctx.hb_state["task"] = msg.time
+            if call.cmd == "UPDATE_MODEL":
+                self.result = self.run_training(self.report)
+            elif call.cmd == "EVALUATE_PROGRESS":
+                objv, nnz_w, examples = self.final_progress()
+                reply = dumps(cfg.Progress(objv=float(objv), nnz_w=int(nnz_w), num_ex_trained=int(examples)), oneline=True).encode()
+            elif call.cmd == "SAVE_MODEL":
+                self.saved = self.save_model()
+                reply = (self.saved or "").encode()
+        except Exception as e:  # noqa: BLE001 - the scheduler must hear about it instead of waiting forever
+            import traceback
+
+            self.failed = traceback.format_exc()
+            reply = ERROR_PREFIX + f"{type(e).__name__}: {e}".encode()
+        self.ctx.add_busy(time.time() - t0)
+        self.cust.reply(msg, payload=reply)
+
+    def stop(self) -> None:
+        self.cust.stop()
+
+
+def run_scheduled_online(group, flags: cfg.Flags, app_conf, run_training, final_progress, save_model, verbose: bool = True) -> dict:
+    """An online job under a scheduler node on rank 0 (``FTRL::run``, src/linear_method/ftrl.cc:38-59): UPDATE_MODEL to
+    every rank, the merged progress line every ``eval_interval`` while the ranks train, EVALUATE_PROGRESS, SAVE_MODEL.
+
+    ``run_training(report)`` is the rank's whole training loop (``report(loss_sum, examples, penalty, nnz_w)`` at its
+    own pace), ``final_progress()`` returns ``(objective part, non-zeros, examples)`` of this rank, ``save_model()``
+    the path it wrote.  Collective over ``group``.  Returns ``{"result": run_training's value, "model": path}``; rank 0
+    adds ``"scheduler"`` (the scheduler's record: totals, worker reports, printed lines)."""
+    import torch.distributed as dist
+
+    from .ftrl_cpu import FTRLScheduler
+
+    W = int(group.world)
+    port = [_free_port() if group.rank == 0 else 0]
+    if W > 1:
+        dist.broadcast_object_list(port, src=0, group=group.group)
+    f = copy.copy(flags)
+    f.num_workers, f.num_servers, f.num_unused, f.num_replicas = W, 0, 0, 0
+    f.scheduler = f"role:SCHEDULER,hostname:'127.0.0.1',port:{int(port[0])},id:'H'"
+    f.interface = ""
+    sched_ctx: dict = {}
+    th = None
+    if group.rank == 0:
+        def boot():
+            try:
+                sched_ctx["ctx"] = start_node(0, f)
+            except Exception as e:  # noqa: BLE001
+                sched_ctx["error"] = e
+
+        th = threading.Thread(target=boot, name="H-boot", daemon=True)
+        th.start()
+    ctx = start_node(group.rank + 1, f)
+    node = GpuOnlineWorkerNode(ctx, app_conf.app_name or "linear_method", run_training, final_progress, save_model,
+                               getattr(group, "device", None))
+    out: dict = {}
+    try:
+        if th is not None:
+            th.join()
+            if "error" in sched_ctx:
+                raise sched_ctx["error"]
+        group.barrier()
+        if group.rank == 0:
+            hctx = sched_ctx["ctx"]
+            sched = FTRLScheduler(hctx, app_conf, flags)
+            try:
+                out["scheduler"] = sched.run(verbose=verbose)
+            finally:
+                hctx.po.stop_all()
+                sched.stop()
+        ctx.po.wait_terminate(1e9)
+    finally:
+        node.stop()
+        ctx.stop()
+        if "ctx" in sched_ctx:
+            sched_ctx["ctx"].stop()
+    if node.failed:
+        raise RuntimeError(f"rank {group.rank}: a task failed\n{node.failed}")
+    out["result"] = node.result
     out["model"] = node.saved
     return out

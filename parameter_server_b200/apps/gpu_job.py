@@ -271,6 +271,8 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
 
         mon = RankMonitor(group.rank, group.world, deadline_s=max(10.0, 5.0 * float(flags.report_interval)))
 
+    rows_of: list = []
+
     def stream():
         # minibatches that a checkpoint already covers are read and skipped; the rest go to the trainer, which
         # uploads minibatch i+1 while step i computes
@@ -281,6 +283,7 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
                 mon.tick(step, float(flags.report_interval))
             seen += hb.y.numel()
             if step > start_step:
+                rows_of.append(int(hb.y.numel()))       # rows of the trainer's step len(rows_of) - 1
                 yield hb
 
     def after_step(i):
@@ -296,14 +299,49 @@ def run_ftrl_job(lm, flags: cfg.Flags, group: PeerGroup, cache: str) -> dict:
             print("%10d examples, loss %.5e, penalty %.5e, |w|_0 %8d" % (seen * group.world, loss, eng.penalty(st), int(st["nnz_w"])))
             last = time.time()
 
-    losses = trainer.train(stream(), after_step=after_step, on_loss=on_loss)
+    ctl = None
+    if flags.gpu_scheduler:
+        # the stream runs as the one UPDATE_MODEL task of a scheduler node (apps/gpu_control.py); every rank reports
+        # its loss and examples, and the penalty and non-zeros of its shard, every eval_interval
+        from .gpu_control import run_scheduled_online
+
+        total = {"loss": 0.0}                                    # sum of the steps' loss sums (the trainer gives means)
+
+        def run_training(report):
+            mark = {"t": time.time(), "seen": 0, "loss": 0.0}
+
+            def on_loss_report(i, loss):
+                n = rows_of[i]                                    # the step's mean loss times its rows = its loss sum
+                mark["loss"] += loss * n
+                mark["seen"] += n
+                total["loss"] += loss * n
+                if time.time() - mark["t"] >= s.eval_interval:
+                    st_ = eng.read_stats(reset=False)
+                    report(mark["loss"], mark["seen"], eng.penalty(st_), int(st_["nnz_w"]))
+                    mark.update(t=time.time(), seen=0, loss=0.0)
+
+            return trainer.train(stream(), after_step=after_step, on_loss=on_loss_report)
+
+        def final_progress():
+            st_ = eng.read_stats(reset=False)
+            return total["loss"] + eng.penalty(st_), int(st_["nnz_w"]), seen
+
+        ctl = run_scheduled_online(group, flags, cfg.load_app_config(flags.app), run_training, final_progress,
+                                   lambda: eng.save_model(lm.model_output.file[0]) if lm.model_output.file else None)
+        losses = ctl["result"] or []
+    else:
+        losses = trainer.train(stream(), after_step=after_step, on_loss=on_loss)
     st = eng.read_stats(reset=False)
     out = {"seconds": time.time() - t0, "examples": seen, "mean_logloss_last": losses[-1] if losses else None,
            "nnz_w": st["nnz_w"], "penalty": eng.penalty(st)}
     if group.rank == 0:
         print("%10d examples, loss %.5e, penalty %.5e, |w|_0 %8d" % (seen * group.world, out["mean_logloss_last"] or 0.0,
                                                                    out["penalty"], int(st["nnz_w"])))
-    if lm.model_output.file:
+    if ctl is not None:
+        out["scheduler_progress"] = ctl.get("scheduler")
+        if ctl.get("model"):
+            out["model"] = ctl["model"]                   # written by the SAVE_MODEL task
+    if lm.model_output.file and "model" not in out:
         out["model"] = eng.save_model(lm.model_output.file[0])
     group.barrier()
     return out

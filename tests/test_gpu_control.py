@@ -129,3 +129,100 @@ def test_a_failing_task_ends_the_job_with_its_error(tmp_path):
     got = _run("fail", tmp_path)
     assert got[0][0] == "error" and "W1" in got[0][1] and "device says no" in got[0][1]
     assert got[1][0] == "error" and "device says no" in got[1][1]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def _online_main(rank, world, port, mode, tmp, q):
+    import torch
+    import torch.distributed as dist
+
+    from parameter_server_b200 import config as cfg
+    from parameter_server_b200.apps.gpu_control import run_scheduled_online
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    class Group:
+        def __init__(self):
+            self.rank, self.world, self.group, self.device = rank, world, dist.group.WORLD, torch.device("cpu")
+
+        def barrier(self):
+            dist.barrier()
+
+    conf = cfg.parse_app_config('''app_name: "ctr" parameter_name: "ctr_w"
+        linear_method { loss { type: LOGIT } penalty { type: L1 lambda: 0.1 }
+          solver { minibatch_size: 100 eval_interval: 0.05 } ftrl { } }''')
+    state = {"examples": 0, "loss": 0.0}
+
+    def run_training(report):
+        losses = []
+        for step in range(12):
+            t = torch.tensor([1.0])
+            dist.all_reduce(t)                            # every step is a collective, like the real one
+            if mode == "fail" and step == 5:                # rank 1 fails; rank 0 sees it as a wait that ran out
+                raise ValueError("table full") if rank == 1 else TimeoutError("peer 1 silent")
+            loss = 0.6 - 0.02 * step
+            losses.append(loss)
+            state["examples"] += 100
+            state["loss"] += loss * 100
+            report(loss * 100, 100, 0.5 + rank, 10 * (rank + 1))
+            time.sleep(0.03)
+        return losses
+
+    try:
+        out = run_scheduled_online(Group(), cfg.Flags(), conf, run_training,
+                                   lambda: (state["loss"] + 0.5 + rank, 10 * (rank + 1), state["examples"]),
+                                   lambda: os.path.join(tmp, f"ftrl_S{rank}"), verbose=False)
+        q.put((rank, "ok", dict(result=out["result"], model=out["model"], sched=out.get("scheduler"))))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, "error", f"{type(e).__name__}: {e}"))
+    dist.barrier() if mode != "fail" else time.sleep(1.0)
+    os._exit(0)
+
+
+def _run_online(mode, tmp, world=2):
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_online_main, args=(r, world, port, mode, str(tmp), q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    deadline = time.time() + 240
+    while len(got) < world and time.time() < deadline:
+        if q.empty():
+            time.sleep(0.1)
+            continue
+        r, status, body = q.get()
+        got[r] = (status, body)
+    for p in procs:
+        p.join(20)
+        if p.is_alive():
+            p.kill()
+    assert len(got) == world, f"only {sorted(got)} reported"
+    return got
+
+
+def test_online_job_under_the_scheduler(tmp_path):
+    import re
+
+    got = _run_online("plain", tmp_path)
+    assert all(s == "ok" for s, _ in got.values()), got
+    a, b = got[0][1], got[1][1]
+    assert len(a["result"]) == len(b["result"]) == 12 and a["model"].endswith("ftrl_S0") and b["model"].endswith("ftrl_S1")
+    rec = a["sched"][0]
+    assert b["sched"] is None and rec["examples"] == 2400 and rec["nnz_w"] == 30
+    want = 2 * sum((0.6 - 0.02 * s) * 100 for s in range(12)) + 0.5 + 1.5
+    assert rec["objv"] == pytest.approx(want, rel=1e-9)
+    assert len(rec["reports"]) == 24 and {r["worker"] for r in rec["reports"]} == {"W0", "W1"}
+    pat = re.compile(r"^\s*(\d+) examples, loss (\S+), penalty (\S+), \|w\|_0\s+(\d+)$")
+    got_lines = [pat.match(l) for l in rec["lines"]]
+    assert got_lines and all(got_lines)
+    last = got_lines[-1]
+    assert float(last.group(3)) == pytest.approx(2.0) and int(last.group(4)) == 30 and 0.3 < float(last.group(2)) < 0.7
+
+
+def test_online_job_failure_reaches_the_scheduler(tmp_path):
+    got = _run_online("fail", tmp_path)
+    assert got[0][0] == "error" and ("table full" in got[0][1] or "peer 1 silent" in got[0][1])   # the scheduler's rank
+    assert got[1][0] == "error" and "table full" in got[1][1]
