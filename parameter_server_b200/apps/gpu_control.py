@@ -173,12 +173,10 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def run_scheduled(group, flags: cfg.Flags, app_name: str, sol, model_prefix: str = "", verbose: bool = True) -> dict:
-    """Run the passes of ``sol`` (already preprocessed, on every rank) under a scheduler node on rank 0.
-
-    Collective over ``group`` (``rank``, ``world``, ``group`` = the torch.distributed group, ``device``,
-    ``barrier()``).  Returns on every rank ``{"progress": solver.progress, "model": path or None}``; rank 0 adds the
-    scheduler's own records under ``"scheduler"`` and the last dashboard under ``"dashboard"``."""
+def _start_nodes(group, flags: cfg.Flags):
+    """The nodes of a scheduled GPU job: every rank starts its worker node ``W<rank>``; rank 0 also starts the scheduler
+    ``H`` (in a thread of its own: it waits for all workers to register) on a free loopback port that the ranks
+    learn over the process group.  Returns (worker context, {"ctx": scheduler context} on rank 0, the boot thread)."""
     import torch.distributed as dist
 
     W = int(group.world)
@@ -201,6 +199,16 @@ def run_scheduled(group, flags: cfg.Flags, app_name: str, sol, model_prefix: str
         th = threading.Thread(target=boot, name="H-boot", daemon=True)
         th.start()
     ctx = start_node(group.rank + 1, f)
+    return ctx, sched_ctx, th
+
+
+def run_scheduled(group, flags: cfg.Flags, app_name: str, sol, model_prefix: str = "", verbose: bool = True) -> dict:
+    """Run the passes of ``sol`` (already preprocessed, on every rank) under a scheduler node on rank 0.
+
+    Collective over ``group`` (``rank``, ``world``, ``group`` = the torch.distributed group, ``device``,
+    ``barrier()``).  Returns on every rank ``{"progress": solver.progress, "model": path or None}``; rank 0 adds the
+    scheduler's own records under ``"scheduler"`` and the last dashboard under ``"dashboard"``."""
+    ctx, sched_ctx, th = _start_nodes(group, flags)
     node = GpuWorkerNode(ctx, app_name, sol, model_prefix, getattr(group, "device", None))
     out: dict = {}
     try:
@@ -306,30 +314,9 @@ def run_scheduled_online(group, flags: cfg.Flags, app_conf, run_training, final_
     own pace), ``final_progress()`` returns ``(objective part, non-zeros, examples)`` of this rank, ``save_model()``
     the path it wrote.  Collective over ``group``.  Returns ``{"result": run_training's value, "model": path}``; rank 0
     adds ``"scheduler"`` (the scheduler's record: totals, worker reports, printed lines)."""
-    import torch.distributed as dist
-
     from .ftrl_cpu import FTRLScheduler
 
-    W = int(group.world)
-    port = [_free_port() if group.rank == 0 else 0]
-    if W > 1:
-        dist.broadcast_object_list(port, src=0, group=group.group)
-    f = copy.copy(flags)
-    f.num_workers, f.num_servers, f.num_unused, f.num_replicas = W, 0, 0, 0
-    f.scheduler = f"role:SCHEDULER,hostname:'127.0.0.1',port:{int(port[0])},id:'H'"
-    f.interface = ""
-    sched_ctx: dict = {}
-    th = None
-    if group.rank == 0:
-        def boot():
-            try:
-                sched_ctx["ctx"] = start_node(0, f)
-            except Exception as e:  # noqa: BLE001
-                sched_ctx["error"] = e
-
-        th = threading.Thread(target=boot, name="H-boot", daemon=True)
-        th.start()
-    ctx = start_node(group.rank + 1, f)
+    ctx, sched_ctx, th = _start_nodes(group, flags)
     node = GpuOnlineWorkerNode(ctx, app_conf.app_name or "linear_method", run_training, final_progress, save_model,
                                getattr(group, "device", None))
     out: dict = {}
