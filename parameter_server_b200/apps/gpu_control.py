@@ -58,6 +58,8 @@ class GpuWorkerNode:
         self.ctx, self.sol, self.model_prefix, self.device = ctx, sol, model_prefix, device
         self.saved: Optional[str] = None
         self.failed: Optional[str] = None
+        if ctx.hb_state is not None:
+            ctx.hb_state["where"] = self._where()        # the first heartbeat already names the device
         self.cust = host().Customer(ctx.po, app_name, self.process, False)
 
     def _where(self) -> str:
@@ -231,8 +233,8 @@ def run_scheduled(group, flags: cfg.Flags, app_name: str, sol, model_prefix: str
                 out["scheduler"] = sched.run()
                 out["saved"] = sched.saved
                 if float(flags.report_interval) > 0:
-                    # a short job can end before the first report is due: give every worker three intervals
-                    deadline = time.time() + 3.0 * float(flags.report_interval)
+                    # a short job can end before the first report is due: wait for every worker's first one (bounded)
+                    deadline = time.time() + 3.0 * float(flags.report_interval) + 1.0
                     while time.time() < deadline and not all(text for _, text in hctx.po.heartbeats().values()):
                         time.sleep(0.01)
                     out["dashboard"] = dashboard(hctx.po)
