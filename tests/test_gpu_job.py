@@ -80,8 +80,8 @@ def test_warm_start_from_a_model_dump(tmp_path):
     second = _run(tmp_path, warm)
     b = [p["objv"] for p in second["progress"]]
     assert len(b) == 2
-    assert b[0] < a[0] and b[0] <= a[-1] * 1.002          # first pass from the dump: at the level the first job had reached
-    assert b[-1] <= b[0] * 1.0005
+    assert b[0] < a[1] and b[0] <= a[-1] * 1.01           # first pass from the dump: at the level the first job had reached
+    assert b[-1] <= b[0] * 1.001
 
 
 def test_darlin_job_under_a_scheduler_node(tmp_path):
