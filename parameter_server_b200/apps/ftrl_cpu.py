@@ -257,11 +257,27 @@ class FTRLScheduler:
 
             threading.Thread(target=shower, name="H-progress", daemon=True).start()
         t = self.cust.submit(H.kActiveGroup, payload=_call("UPDATE_MODEL"))
-        self.cust.wait_out(H.kActiveGroup, t)            # workers return when their data is exhausted and applied;
-        done.set()                                       # servers return at once and report while the workers train
-        for nid, text in self.cust.take_replies(t).items():
-            if bytes(text).startswith(b"ERROR: "):       # a GPU rank's training loop failed (apps/gpu_control.py)
-                raise RuntimeError(f"{nid}: {bytes(text)[7:].decode()}")
+        # workers return when their data is exhausted and applied; servers return at once and report while the workers
+        # train.  The wait is not for ever: a node's error reply (a GPU rank's training loop that failed,
+        # apps/gpu_control.py) ends it at once, and with heartbeats on so does a node that stopped reporting.
+        hb = float(self.flags.report_interval)
+        deadline_s = max(10.0 * hb, 2.0) if hb > 0 else 0.0
+        replies: dict = {}
+        try:
+            while True:
+                finished = self.cust.wait_out(H.kActiveGroup, t, 0.2)
+                replies.update(self.cust.take_replies(t))
+                for nid, text in replies.items():
+                    if bytes(text).startswith(b"ERROR: "):
+                        raise RuntimeError(f"{nid}: {bytes(text)[7:].decode()}")
+                if finished:
+                    break
+                if deadline_s > 0:
+                    dead = self.ctx.po.dead_nodes(deadline_s)
+                    if dead:
+                        raise RuntimeError(f"no heartbeat from {', '.join(dead)} for {deadline_s:g} s")
+        finally:
+            done.set()
         t = self.cust.submit(H.kActiveGroup, payload=_call("EVALUATE_PROGRESS"))
         self.cust.wait_out(H.kActiveGroup, t)
         objv, nnz_w, examples = 0.0, 0, 0

@@ -115,20 +115,33 @@ class GpuWorkerNode:
 class GpuBatchScheduler:
     """Scheduler side of a batch job on GPU ranks: one UPDATE_MODEL task per pass."""
 
-    def __init__(self, ctx: NodeContext, app_name: str, solver_cfg, nblk: int, block_group, verbose: bool = True):
-        self.H, self.ctx = host(), ctx
+    def __init__(self, ctx: NodeContext, app_name: str, solver_cfg, nblk: int, block_group, verbose: bool = True,
+                 deadline_s: float = 0.0):
+        self.H, self.ctx, self.deadline_s = host(), ctx, float(deadline_s)
         self.cfg, self.nblk, self.block_group, self.verbose = solver_cfg, nblk, block_group, verbose
         self.cust = self.H.Customer(ctx.po, app_name, None, False)
         self.progress: List[dict] = []
         self.saved: List[str] = []
 
     def _round(self, payload: bytes) -> dict:
+        """One task to every rank; returns their replies.  Does not wait for ever: a rank's error reply ends the round
+        at once, and with heartbeats on (``-report_interval``) so does a rank that stopped reporting."""
         t = self.cust.submit(self.H.kWorkerGroup, payload=payload)
-        self.cust.wait_out(self.H.kWorkerGroup, t)
-        replies = self.cust.take_replies(t)
-        for nid, text in replies.items():
-            if bytes(text).startswith(ERROR_PREFIX):
-                raise RuntimeError(f"{nid}: {bytes(text)[len(ERROR_PREFIX):].decode()}")
+        replies: dict = {}
+
+        def check():
+            replies.update(self.cust.take_replies(t))
+            for nid, text in replies.items():
+                if bytes(text).startswith(ERROR_PREFIX):
+                    raise RuntimeError(f"{nid}: {bytes(text)[len(ERROR_PREFIX):].decode()}")
+
+        while not self.cust.wait_out(self.H.kWorkerGroup, t, 0.2):
+            check()
+            if self.deadline_s > 0:
+                dead = self.ctx.po.dead_nodes(self.deadline_s)
+                if dead:
+                    raise RuntimeError(f"no heartbeat from {', '.join(dead)} for {self.deadline_s:g} s")
+        check()
         return replies
 
     def run(self) -> List[dict]:
@@ -221,7 +234,9 @@ def run_scheduled(group, flags: cfg.Flags, app_name: str, sol, model_prefix: str
         group.barrier()                                   # every rank's customer exists before the first task goes out
         if group.rank == 0:
             hctx = sched_ctx["ctx"]
-            sched = GpuBatchScheduler(hctx, app_name, sol.cfg, sol.nblk, sol.block_group, verbose)
+            every = float(flags.report_interval)
+            sched = GpuBatchScheduler(hctx, app_name, sol.cfg, sol.nblk, sol.block_group, verbose,
+                                      deadline_s=max(10.0 * every, 2.0) if every > 0 else 0.0)
             stop_monitor = threading.Event()
             if float(flags.report_interval) > 0:
                 def monitor():

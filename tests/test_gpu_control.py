@@ -27,8 +27,11 @@ def _rank_main(rank, world, port, mode, tmp, q):
     from parameter_server_b200.apps.gpu_control import run_scheduled
     from parameter_server_b200.models.darlin import DarlinConfig, Progress, block_order
 
+    import datetime
+
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # like the kernels' bounded waits: a collective whose peer is gone gives up instead of waiting for ever
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
 
     class Group:
         def __init__(self):
@@ -51,6 +54,8 @@ def _rank_main(rank, world, port, mode, tmp, q):
             if mode == "heartbeat":
                 time.sleep(0.1)                                      # long enough for a few reports per job
             self.seen.append((list(map(int, order)), bool(reset), None if prior is None else list(map(int, prior))))
+            if mode == "vanish" and it == 2 and rank == 1:
+                os._exit(0)                                          # between passes, nothing in flight, no goodbye
             part = torch.tensor([100.0 / world * max(0.5 ** it, 0.5 ** 4)], dtype=torch.float64)
             dist.all_reduce(part)                                    # runs on the node's executor thread
             objv = float(part.item())
@@ -67,7 +72,7 @@ def _rank_main(rank, world, port, mode, tmp, q):
             return path
 
     sol = StandIn()
-    flags = cfg.Flags(report_interval=0.2 if mode == "heartbeat" else 0)
+    flags = cfg.Flags(report_interval=0.2 if mode in ("heartbeat", "vanish") else 0)
     try:
         out = run_scheduled(Group(), flags, "job", sol, os.path.join(tmp, "model"), verbose=False)
         orders = [o.tolist() for o in block_order(6, 12, True, 5)]
@@ -75,20 +80,21 @@ def _rank_main(rank, world, port, mode, tmp, q):
                                 sched=out.get("scheduler"), saved=out.get("saved"), dash=out.get("dashboard"))))
     except Exception as e:  # noqa: BLE001
         q.put((rank, "error", f"{type(e).__name__}: {e}"))
-    dist.barrier() if mode != "fail" else time.sleep(1.0)
+    dist.barrier() if mode not in ("fail", "vanish") else time.sleep(1.0)
     os._exit(0)
 
 
-def _run(mode, tmp, world=2):
+def _run(mode, tmp, world=2, expect=None):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
     port = _free_port()
     procs = [ctx.Process(target=_rank_main, args=(r, world, port, mode, str(tmp), q)) for r in range(world)]
     for p in procs:
         p.start()
+    expect = world if expect is None else expect
     got = {}
     deadline = time.time() + 240
-    while len(got) < world and time.time() < deadline:
+    while len(got) < expect and time.time() < deadline:
         if q.empty():
             time.sleep(0.1)
             continue
@@ -98,7 +104,7 @@ def _run(mode, tmp, world=2):
         p.join(20)
         if p.is_alive():
             p.kill()
-    assert len(got) == world, f"only {sorted(got)} reported"
+    assert len(got) == expect, f"only {sorted(got)} reported"
     return got
 
 
@@ -131,6 +137,16 @@ def test_a_failing_task_ends_the_job_with_its_error(tmp_path):
     assert got[1][0] == "error" and "device says no" in got[1][1]
 
 
+def test_a_rank_that_vanishes_does_not_hang_the_job(tmp_path):
+    """Rank 1 exits between passes.  Rank 0's pass gives up in its bounded collective and says so, or the scheduler
+    misses W1's heartbeats first; either way the job ends with an error that names the cause instead of waiting."""
+    t0 = time.time()
+    got = _run("vanish", tmp_path, expect=1)
+    assert got[0][0] == "error", got
+    msg = got[0][1]
+    assert "no heartbeat from W1" in msg or "W0:" in msg or "task failed" in msg, msg
+    assert time.time() - t0 < 120
+
 # ---------------------------------------------------------------------------------------------------------------
 def _online_main(rank, world, port, mode, tmp, q):
     import torch
@@ -139,8 +155,10 @@ def _online_main(rank, world, port, mode, tmp, q):
     from parameter_server_b200 import config as cfg
     from parameter_server_b200.apps.gpu_control import run_scheduled_online
 
+    import datetime
+
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
 
     class Group:
         def __init__(self):
@@ -157,6 +175,8 @@ def _online_main(rank, world, port, mode, tmp, q):
     def run_training(report):
         losses = []
         for step in range(12):
+            if mode == "vanish" and step == 5 and rank == 1:
+                os._exit(0)
             t = torch.tensor([1.0])
             dist.all_reduce(t)                            # every step is a collective, like the real one
             if mode == "fail" and step == 5:                # rank 1 fails; rank 0 sees it as a wait that ran out
@@ -176,20 +196,21 @@ def _online_main(rank, world, port, mode, tmp, q):
         q.put((rank, "ok", dict(result=out["result"], model=out["model"], sched=out.get("scheduler"))))
     except Exception as e:  # noqa: BLE001
         q.put((rank, "error", f"{type(e).__name__}: {e}"))
-    dist.barrier() if mode != "fail" else time.sleep(1.0)
+    dist.barrier() if mode not in ("fail", "vanish") else time.sleep(1.0)
     os._exit(0)
 
 
-def _run_online(mode, tmp, world=2):
+def _run_online(mode, tmp, world=2, expect=None):
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
     port = _free_port()
     procs = [ctx.Process(target=_online_main, args=(r, world, port, mode, str(tmp), q)) for r in range(world)]
     for p in procs:
         p.start()
+    expect = world if expect is None else expect
     got = {}
     deadline = time.time() + 240
-    while len(got) < world and time.time() < deadline:
+    while len(got) < expect and time.time() < deadline:
         if q.empty():
             time.sleep(0.1)
             continue
@@ -199,7 +220,7 @@ def _run_online(mode, tmp, world=2):
         p.join(20)
         if p.is_alive():
             p.kill()
-    assert len(got) == world, f"only {sorted(got)} reported"
+    assert len(got) == expect, f"only {sorted(got)} reported"
     return got
 
 
@@ -226,3 +247,8 @@ def test_online_job_failure_reaches_the_scheduler(tmp_path):
     got = _run_online("fail", tmp_path)
     assert got[0][0] == "error" and ("table full" in got[0][1] or "peer 1 silent" in got[0][1])   # the scheduler's rank
     assert got[1][0] == "error" and "table full" in got[1][1]
+
+
+def test_online_job_does_not_hang_when_a_rank_vanishes(tmp_path):
+    got = _run_online("vanish", tmp_path, expect=1)
+    assert got[0][0] == "error" and ("W0:" in got[0][1] or "no heartbeat" in got[0][1] or "task failed" in got[0][1]), got
