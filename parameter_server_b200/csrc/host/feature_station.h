@@ -10,9 +10,10 @@
 //
 // Counterpart in the reference: FeatureStation (src/linear_method/feature_station.{h,cc}: addFeatureGrp
 // :70-109, prefetch :212-230, prefetchThreadFunc :232-279, getFeature :374-431, dropFeature :433-465) and
-// the unused generic block store Ocean (src/system/ocean.{h,cc}).  Differences: ranges are read with
-// pread() into plain buffers instead of through SArray file reads, a task that was not prefetched is
-// loaded by the caller itself (counted as a miss) instead of waiting forever, and a range larger than the
+// the generic block store Ocean (src/system/ocean.{h,cc}; here csrc/host/ocean.h).  Differences: ranges are read with
+// pread() into plain buffers instead of through SArray file reads, a task that was not prefetched, or whose
+// read-ahead is still queued while the readers wait for room under the limit, is loaded by the caller itself
+// (counted as a miss) instead of waiting, and a range larger than the
 // whole limit is admitted when nothing else is resident so that it cannot block the queue.
 #pragma once
 #include <fcntl.h>
@@ -153,8 +154,23 @@ class FeatureStation {
       return b;
     }
     if (used_.count(task)) {
-      // queued, being read, or resident; a failed prefetch takes the task out of used_ again
-      cv_.wait(l, [&] { return ready_.count(task) > 0 || !used_.count(task) || done_; });
+      // queued, being read, or resident; a failed prefetch takes the task out of used_ again.  While the readers are
+      // held back by the memory limit (the job at the head of the queue does not fit beside what is resident) a job
+      // that is still queued is taken over by the caller: what fills the limit may be ranges that only the caller's
+      // progress releases, so the solver must not wait behind it.
+      while (!ready_.count(task) && used_.count(task) && !done_) {
+        if (limit_waiters_ > 0 && !jobs_.empty() && !fits_nolock(jobs_.front())) {
+          auto it = jobs_.begin();
+          while (it != jobs_.end() && it->task != task) ++it;
+          if (it != jobs_.end()) {
+            jobs_.erase(it);
+            used_.erase(task);
+            cv_.notify_all();
+            break;
+          }
+        }
+        cv_.wait(l);
+      }
       auto it = ready_.find(task);
       if (it != ready_.end()) {
         FeatureBlockPtr b = it->second;
@@ -174,6 +190,7 @@ class FeatureStation {
     resident_ += cost;
     stats_.peak_resident = std::max<uint64_t>(stats_.peak_resident, resident_);
     ready_[task] = b;
+    cv_.notify_all();              // what is resident changed: callers that wait behind the limit look again
     return b;
   }
 
@@ -202,6 +219,12 @@ class FeatureStation {
     std::string base;
   };
   struct Job { int task, grp; int64_t c0, c1; };
+
+  // whether a queued job could be read now under the memory limit (an oversized one may when nothing is resident)
+  bool fits_nolock(const Job& j) const {
+    const size_t cost = range_bytes_nolock(groups_.at(j.grp), j.c0, j.c1);
+    return resident_ + reserved_ == 0 || resident_ + reserved_ + cost <= limit_;
+  }
 
   static void make_dirs(const std::string& d) {
     for (size_t i = 1; i <= d.size(); ++i)
@@ -273,7 +296,10 @@ class FeatureStation {
         // the memory limit: wait until the range fits, or nothing else is resident (an oversized range must not block)
         if (resident_ + reserved_ != 0 && resident_ + reserved_ + cost > limit_) {
           ++stats_.limit_waits;
+          ++limit_waiters_;
+          cv_.notify_all();          // callers that wait for a queued job look again
           cv_.wait(l, [&] { return done_ || resident_ + reserved_ == 0 || resident_ + reserved_ + cost <= limit_; });
+          --limit_waiters_;
           if (done_) return;
           if (jobs_.empty() || jobs_.front().task != j.task) continue;   // another thread took it meanwhile
         }
@@ -314,7 +340,7 @@ class FeatureStation {
   std::map<int, FeatureBlockPtr> ready_;
   std::set<int> used_;
   std::vector<std::thread> pool_;
-  size_t resident_ = 0, reserved_ = 0, in_flight_ = 0;
+  size_t resident_ = 0, reserved_ = 0, in_flight_ = 0, limit_waiters_ = 0;
   uint64_t total_bytes_ = 0;
   int max_task_ = -1;
   bool done_ = false;

@@ -253,6 +253,10 @@ class Ocean {
       auto& e2 = entry(job.first, job.second);
       e2.data = std::move(data);
       e2.state = Entry::LOADED;
+      if (e2.users == 0 && e2.expected == 0) {     // dropped while it was queued or loading: nobody will come for it
+        blocks_.erase({job.first, job.second});
+        note_loaded(-1);
+      }
       cv_.notify_all();
     }
   }

@@ -261,7 +261,13 @@ class Postoffice {
     c->exec()->start();
     for (auto& m : backlog) c->exec()->accept(m);
   }
-  void remove_customer(Customer* c) { std::lock_guard<std::mutex> l(mu_); customers_.erase(c->name()); }
+  // A customer that goes away is first taken out of the table, then waits until no message is being handed to
+  // it: dispatch() calls into the customer's executor after it let go of the table's lock.
+  void remove_customer(Customer* c) {
+    std::unique_lock<std::mutex> l(mu_);
+    customers_.erase(c->name());
+    deliver_cv_.wait(l, [&] { return delivering_.count(c) == 0; });
+  }
 
   // ---- membership (src/system/postoffice.cc:185-243)
   // non-scheduler: announce myself to the scheduler
@@ -528,8 +534,14 @@ class Postoffice {
         return;
       }
       c = it->second;
+      ++delivering_[c];
     }
     c->exec()->accept(m);
+    {
+      std::lock_guard<std::mutex> l(mu_);
+      if (--delivering_[c] == 0) delivering_.erase(c);
+    }
+    deliver_cv_.notify_all();
   }
 
   std::shared_ptr<Van> van_;
@@ -541,6 +553,8 @@ class Postoffice {
   std::mutex mu_, hb_mu_;
   std::condition_variable nodes_cv_, term_cv_, hb_cv_;
   std::map<std::string, Customer*> customers_;
+  std::map<Customer*, int> delivering_;      // customers whose executor is being handed a message right now
+  std::condition_variable deliver_cv_;
   std::map<std::string, std::vector<MessagePtr>> orphan_;
   std::vector<Node> nodes_, pending_nodes_;
   bool nodes_ready_ = false, table_sent_ = false, terminated_ = false, key_cache_ = true;

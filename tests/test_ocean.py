@@ -117,3 +117,19 @@ def test_less_memory_and_concurrent_users(tmp_path):
     for t in ts:
         t.join(30)
     assert not errs and oc.stats()["loaded_now"] == 0
+
+
+def test_a_block_dropped_before_it_was_loaded_does_not_stay(tmp_path):
+    H, oc = _store(tmp_path, threads=1, job_limit=1)
+    O = H.Ocean
+    oc.set_partition(0, [0, 4, 8, 12])
+    oc.dump(0, O.DELTA, np.arange(12.0))
+    for b in range(3):
+        oc.prefetch(0, b)
+        oc.drop(0, b)                      # the caller changed its mind: no get will follow
+    deadline = time.time() + 5
+    while (oc.pending() or oc.stats()["loaded_now"]) and time.time() < deadline:
+        time.sleep(0.01)
+    assert oc.pending() == 0 and oc.stats()["loaded_now"] == 0      # nothing is left holding the single job slot
+    assert oc.get(0, 1, O.DELTA, "float64").tolist() == [4.0, 5.0, 6.0, 7.0]
+    oc.drop(0, 1)
