@@ -217,12 +217,28 @@ int main(int argc, char** argv) {
         if (!c->wait_out(kServerGroup, 10, 20.0)) ++bad;
         for (int r = 0; r < kR; ++r) {
           const int t = 20 + 10 * r;
-          auto push = mk(1, t, -1);
+          // the first values wait for the servers' time 11 (all workers' keys merged, values initialised): nothing else
+          // keeps a fast worker's values from reaching a server before a slow worker's keys
+          auto push = mk(1, t, r == 0 ? 11 : -1);
           std::vector<double> v(wk[w].size(), (double)(w + 1));     // every key of worker w carries w + 1
           push->value.push_back(bytes_of(v));
           c->submit(push);
           c->submit(mk(2, t + 2, t + 1));
-          if (!c->wait_out(kServerGroup, t + 2, 20.0)) { ++bad; continue; }
+          if (!c->wait_out(kServerGroup, t + 2, 20.0)) {
+            std::fprintf(stderr, "selftest: worker %d round %d: no reply to the pull at %d (S0 %d, S1 %d)\n", w, r, t + 2,
+                         (int)c->try_wait_out("S0", t + 2), (int)c->try_wait_out("S1", t + 2));
+            for (const char* sid : {"S0", "S1"}) {                   // what the servers hold for this worker
+              auto* sc = sp[sid].get();
+              auto me = sc->exec()->rnode("W" + std::to_string(w));
+              std::fprintf(stderr, "selftest:   %s: time %d of W%d finished: %d, started %d; waiting requests:", sid, t + 1, w,
+                           me ? (int)me->incoming.try_wait(t + 1) : -1, me ? (int)me->incoming.try_wait(t) : -1);
+              for (auto& q : sc->exec()->pending_requests())
+                std::fprintf(stderr, " [%s cmd %d t %d wait %d]", q->sender.c_str(), q->task.cmd, q->task.time, q->task.wait_time);
+              std::fprintf(stderr, " processed %d\n", (int)sc->exec()->processed);
+            }
+            ++bad;
+            break;                                                   // the later rounds would only time out as well
+          }
           auto got = c->take_pulled(t + 2, {"S0", "S1"});
           const double* x = reinterpret_cast<const double*>(got.second.data());     // values only: a value reply carries no keys
           if (got.second.size() != wk[w].size() * 8) { ++bad; continue; }
@@ -241,10 +257,19 @@ int main(int argc, char** argv) {
         c->finish_in(kWorkerGroup, 11);
         for (int r = 0; r < kR; ++r) {
           const int t = 20 + 10 * r;
-          if (!c->wait_in(kWorkerGroup, t, 20.0)) { ++bad; continue; }
+          if (!c->wait_in(kWorkerGroup, t, 20.0)) {
+            std::fprintf(stderr, "selftest: server %d round %d: the pushes at %d did not both arrive\n", sv, r, t);
+            ++bad;
+            break;
+          }
           auto agg = c->received(t);
           auto w = c->values(0);
-          if (agg.nval != 1 || agg.hi - agg.lo != w.size()) { ++bad; continue; }
+          if (agg.nval != 1 || agg.hi - agg.lo != w.size()) {
+            std::fprintf(stderr, "selftest: server %d round %d: aggregate of %d values per key over [%zu, %zu), %zu values, %zu keys here\n",
+                         sv, r, agg.nval, agg.lo, agg.hi, w.size(), c->keys(0).size());
+            ++bad;
+            break;
+          }
           for (size_t i = 0; i < w.size(); ++i) w[i] += agg.vals[i];
           c->set_values_range(0, agg.lo, w.data(), w.size());
           c->finish_in(kWorkerGroup, t + 1);
