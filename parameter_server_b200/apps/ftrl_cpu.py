@@ -189,6 +189,8 @@ class FTRLNode:
 
     def stop(self) -> None:
         self._reporting.set()
+        self.param.abort_waits()          # a handler may still wait for a node that is gone
+        self.cust.abort_waits()
         self.cust.stop()
         self.param.stop()
 
@@ -261,7 +263,7 @@ class FTRLScheduler:
         # train.  The wait is not for ever: a node's error reply (a GPU rank's training loop that failed,
         # apps/gpu_control.py) ends it at once, and with heartbeats on so does a node that stopped reporting.
         hb = float(self.flags.report_interval)
-        deadline_s = max(10.0 * hb, 2.0) if hb > 0 else 0.0
+        deadline_s = max(5.0 * hb, 2.0) if hb > 0 else 0.0
         replies: dict = {}
         try:
             while True:

@@ -236,7 +236,7 @@ def run_scheduled(group, flags: cfg.Flags, app_name: str, sol, model_prefix: str
             hctx = sched_ctx["ctx"]
             every = float(flags.report_interval)
             sched = GpuBatchScheduler(hctx, app_name, sol.cfg, sol.nblk, sol.block_group, verbose,
-                                      deadline_s=max(10.0 * every, 2.0) if every > 0 else 0.0)
+                                      deadline_s=max(5.0 * every, 2.0) if every > 0 else 0.0)
             stop_monitor = threading.Event()
             if float(flags.report_interval) > 0:
                 def monitor():

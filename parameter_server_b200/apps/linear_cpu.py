@@ -397,6 +397,10 @@ class LinearMethodNode:
         write_model_text(f"{self.conf.model_output.file[0]}_{self.ctx.node_id}", keys, w)
 
     def stop(self) -> None:
+        # the job is over; a handler may still wait for a node that is gone (a worker that died): call the waits off
+        # first, so that the executor threads can be joined
+        self.param.cust.abort_waits()
+        self.cust.abort_waits()
         self.cust.stop()
         self.param.cust.stop()
         if self.station is not None:
@@ -420,8 +424,19 @@ class BatchScheduler:
     def _submit(self, payload: bytes, wait: bool = True, wait_time: int = -1) -> int:
         t = self.cust.submit(self.H.kActiveGroup, payload=payload, wait_time=wait_time)
         if wait:
-            self.cust.wait_out(self.H.kActiveGroup, t)
+            self._wait(t)
         return t
+
+    def _wait(self, t: int) -> None:
+        """Wait for every node's reply to task ``t``; with heartbeats on (``-report_interval``) a node that stopped
+        reporting ends the job with an error instead of holding the scheduler for ever."""
+        hb = float(self.flags.report_interval)
+        deadline_s = max(5.0 * hb, 2.0) if hb > 0 else 0.0
+        while not self.cust.wait_out(self.H.kActiveGroup, t, 0.2):
+            if deadline_s > 0:
+                dead = self.ctx.po.dead_nodes(deadline_s)
+                if dead:
+                    raise RuntimeError(f"no heartbeat from {', '.join(dead)} for {deadline_s:g} s")
 
     def run(self, verbose: bool = True) -> List[dict]:
         from ..models.darlin import Progress, block_order, print_progress

@@ -590,6 +590,7 @@ PYBIND11_MODULE(_psb_host, m) {
       .def("partition", [](PyCustomer& c, const std::string& id) { return c.exec()->partition(id); })
       .def("processed", [](PyCustomer& c) { return (uint64_t)c.exec()->processed; })
       .def("pending_requests", [](PyCustomer& c) { return c.exec()->pending_requests(); })
+      .def("abort_waits", [](PyCustomer& c) { c.exec()->abort_waits(); }, "calls off every wait_in / wait_out on this customer (the job is over)")
       .def("stop", [](PyCustomer& c) {
         c.exec()->stop();
         // the callback usually is a bound method of the object that owns this customer: dropping it breaks that cycle,

@@ -26,14 +26,19 @@ class TaskTracker {
   void start(int t) { std::lock_guard<std::mutex> l(mu_); task_.emplace(t, false); }
   void finish(int t) { { std::lock_guard<std::mutex> l(mu_); task_[t] = true; } cv_.notify_all(); }
   bool try_wait(int t) const { std::lock_guard<std::mutex> l(mu_); auto it = task_.find(t); return it != task_.end() && it->second; }
+  // false: the time ran out, or the waits were called off (abort) before t finished
   bool wait(int t, double timeout_s = 1e9) {
     std::unique_lock<std::mutex> l(mu_);
-    return cv_.wait_for(l, std::chrono::duration<double>(timeout_s), [&] { auto it = task_.find(t); return it != task_.end() && it->second; });
+    auto done = [&] { auto it = task_.find(t); return it != task_.end() && it->second; };
+    cv_.wait_for(l, std::chrono::duration<double>(timeout_s), [&] { return aborted_ || done(); });
+    return done();
   }
   bool has_started(int t) const { std::lock_guard<std::mutex> l(mu_); return task_.count(t) > 0; }
+  // The job is over (TERMINATE while a node still waits for a peer that is gone): every wait, now and later, returns.
+  void abort() { { std::lock_guard<std::mutex> l(mu_); aborted_ = true; } cv_.notify_all(); }
 
  private:
-  mutable std::mutex mu_; std::condition_variable cv_; std::map<int, bool> task_;
+  mutable std::mutex mu_; std::condition_variable cv_; std::map<int, bool> task_; bool aborted_ = false;
 };
 
 class Postoffice;
@@ -153,6 +158,12 @@ class Executor {
     cv_.notify_all();
   }
   void notify() { cv_.notify_all(); }
+  // calls off every wait on this customer's nodes (wait_in / wait_out of application threads and handlers)
+  void abort_waits() {
+    std::vector<RNodePtr> all;
+    { std::lock_guard<std::mutex> l(mu_); for (auto& kv : nodes_) all.push_back(kv.second); }
+    for (auto& n : all) { n->incoming.abort(); n->outgoing.abort(); }
+  }
   RNodePtr rnode(const std::string& id) { std::lock_guard<std::mutex> l(mu_); return rnode_nolock(id); }
   std::vector<RNodePtr> group(const std::string& id) {
     std::lock_guard<std::mutex> l(mu_);

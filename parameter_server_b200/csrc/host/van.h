@@ -181,7 +181,13 @@ class TcpVan : public Van {
       hints.ai_socktype = SOCK_STREAM;
       if (getaddrinfo(host.c_str(), std::to_string(peer.port).c_str(), &hints, &res) != 0 || res == nullptr)
         return Status::NetError("cannot resolve " + host + " (node " + to + ")");
-      for (int attempt = 0; attempt < retries_ && fd < 0; ++attempt) {
+      // The long retry schedule is for the start of a job, when a peer may not be listening yet.  A peer that was
+      // reached before and is gone now (its process ended) is given three quick attempts: senders must not sit
+      // for most of a minute on every message to a dead node.
+      bool reached_before;
+      { std::lock_guard<std::mutex> l2(mu_); reached_before = reached_.count(to) > 0; }
+      const int attempts = reached_before ? std::min(retries_, 3) : retries_;
+      for (int attempt = 0; attempt < attempts && fd < 0; ++attempt) {
         fd = ::socket(AF_INET, SOCK_STREAM, 0);
         if (fd < 0 || ::connect(fd, res->ai_addr, res->ai_addrlen) != 0) {
           if (fd >= 0) ::close(fd);
@@ -196,6 +202,7 @@ class TcpVan : public Van {
       std::lock_guard<std::mutex> l2(mu_);
       if (closed_) { ::close(fd); return Status::NetError("van closed"); }
       out_fd_[to] = fd;
+      reached_.insert(to);
     }
     const uint64_t n = frame.size();
     if (!write_all(fd, &n, 8) || !write_all(fd, frame.data(), n)) {
@@ -271,6 +278,7 @@ class TcpVan : public Van {
     }
   }
   int listen_fd_ = -1, retries_ = 3;
+  std::set<std::string> reached_;      // peers that a connection was made to at least once (guarded by mu_)
   std::atomic<bool> closed_{false};
   std::mutex mu_;
   std::map<std::string, Node> peers_;

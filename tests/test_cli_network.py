@@ -157,3 +157,41 @@ def test_stand_by_node_joins_and_leaves_with_the_job(tmp_path):
     assert (tmp_path / "model_S0").exists()
     log = open(tmp_path / "van_U0").read()                    # it talked to the scheduler: registration, node table, termination
     assert "U0=>H" in log and "H=>U0" in log
+
+
+def test_a_worker_process_that_dies_ends_the_job(tmp_path):
+    """Failure detection on the host: five processes (1 + 2 + 2) over TCP with heartbeats on; one worker is ended by the
+    test in the middle of the job.  The scheduler misses its reports, gives up with an error that names the node, and
+    tells the others to terminate: nothing waits for ever."""
+    import time
+
+    off, idx, vals, y = planted(4000, 4096, 12, 9, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 2)
+    conf = tmp_path / "job.conf"
+    conf.write_text(CONF.format(train=tmp_path / "train", cache=tmp_path / "cache", out=tmp_path, lam=0.01, ratio=8.0, passes=100000, tail=0)
+                    .replace("epsilon: 1e-6", "epsilon: 1e-30"))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sched = f"role:SCHEDULER,hostname:'127.0.0.1',port:{_free_port()},id:'H'"
+    env = dict(os.environ, PYTHONPATH=root)
+    procs = []
+    for r in range(5):                                                    # ranks: H, W0, W1, S0, S1
+        procs.append(subprocess.Popen([sys.executable, "-m", "parameter_server_b200.ps", "-num_servers", "2", "-num_workers", "2",
+                                       "-app", str(conf), "-scheduler", sched, "-my_rank", str(r), "-report_interval", "1"],
+                                      cwd=tmp_path, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE, text=True))
+    try:
+        time.sleep(6.0)                                                   # start-up, load, a few passes
+        assert all(p.poll() is None for p in procs), "the job ended before the failure was injected"
+        procs[2].kill()                                                   # W1: this child, by its own handle
+        t0 = time.time()
+        try:
+            _, err = procs[0].communicate(timeout=60)
+        except subprocess.TimeoutExpired:
+            pytest.fail("the scheduler kept waiting for the dead worker")
+        assert procs[0].returncode != 0 and "no heartbeat from W1" in err, err[-2000:]
+        assert time.time() - t0 < 30
+        for i in (1, 3, 4):                                               # the survivors were told to terminate
+            procs[i].wait(timeout=30)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
