@@ -50,6 +50,7 @@ class FTRLNode:
         self.cust = H.Customer(ctx.po, app_conf.app_name, self.process, False)
         self.examples, self.loss_sum, self.steps = 0, 0.0, 0
         self._reporting = threading.Event()       # set when the periodic server reports must end
+        self._stopping = threading.Event()        # set when the job is over: a stream still running is abandoned
 
     def _take(self, t: int):
         """The replies of pull ``t`` concatenated in server (= key) order: (keys, values)."""
@@ -122,7 +123,7 @@ class FTRLNode:
                 ahead.put(e)
 
         threading.Thread(target=read_ahead, name=f"{self.ctx.node_id}-reader", daemon=True).start()
-        while True:
+        while not self._stopping.is_set():
             out = ahead.get()
             if isinstance(out, BaseException):
                 raise out
@@ -189,6 +190,7 @@ class FTRLNode:
 
     def stop(self) -> None:
         self._reporting.set()
+        self._stopping.set()
         self.param.abort_waits()          # a handler may still wait for a node that is gone
         self.cust.abort_waits()
         self.cust.stop()

@@ -195,3 +195,40 @@ def test_a_worker_process_that_dies_ends_the_job(tmp_path):
         for p in procs:
             if p.poll() is None:
                 p.kill()
+
+
+def test_a_worker_process_that_dies_ends_the_online_job(tmp_path):
+    """The same for the online (FTRL) job: the scheduler's one long wait for UPDATE_MODEL notices the missing reports."""
+    import shutil
+    import time
+
+    from test_cpu_ftrl_job import CONF as FTRL_CONF
+
+    off, idx, vals, y = planted(10000, 4096, 10, 3, True)
+    write_libsvm_parts(str(tmp_path / "train"), off, idx, vals, y, 1)
+    for i in range(1, 200):                                               # a long stream out of one small file
+        shutil.copy(tmp_path / "train" / "part-000", tmp_path / "train" / f"part-{i:03d}")
+    conf = tmp_path / "job.conf"
+    conf.write_text(FTRL_CONF.format(train=tmp_path / "train", out=tmp_path, mb=100, tail=0).replace("eval_interval: 0", "eval_interval: 1"))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sched = f"role:SCHEDULER,hostname:'127.0.0.1',port:{_free_port()},id:'H'"
+    env = dict(os.environ, PYTHONPATH=root)
+    procs = [subprocess.Popen([sys.executable, "-m", "parameter_server_b200.ps", "-num_servers", "2", "-num_workers", "2",
+                               "-app", str(conf), "-scheduler", sched, "-my_rank", str(r), "-report_interval", "1"],
+                              cwd=tmp_path, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE, text=True) for r in range(5)]
+    try:
+        time.sleep(6.0)
+        if any(p.poll() is not None for p in procs):
+            pytest.skip("the stream was over before the failure could be injected")
+        procs[2].kill()                                                   # W1
+        try:
+            _, err = procs[0].communicate(timeout=60)
+        except subprocess.TimeoutExpired:
+            pytest.fail("the scheduler kept waiting for the dead worker")
+        assert procs[0].returncode != 0 and "no heartbeat from W1" in err, err[-2000:]
+        for i in (1, 3, 4):
+            procs[i].wait(timeout=60)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
