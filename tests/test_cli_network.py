@@ -159,6 +159,31 @@ def test_stand_by_node_joins_and_leaves_with_the_job(tmp_path):
     assert "U0=>H" in log and "H=>U0" in log
 
 
+def _start_five(tmp_path, conf, sched, env):
+    """1 scheduler + 2 workers + 2 servers as child processes with heartbeats on; the scheduler's stderr goes to H.err."""
+    procs = []
+    for r in range(5):
+        err = open(tmp_path / "H.err", "w") if r == 0 else subprocess.DEVNULL
+        procs.append(subprocess.Popen([sys.executable, "-m", "parameter_server_b200.ps", "-num_servers", "2", "-num_workers", "2",
+                                       "-app", str(conf), "-scheduler", sched, "-my_rank", str(r), "-report_interval", "1"],
+                                      cwd=tmp_path, env=env, stdout=subprocess.DEVNULL, stderr=err))
+    return procs
+
+
+def _wait_for_line(path, needle, procs, timeout_s=120.0):
+    """Until the scheduler has printed a line with ``needle`` (the job is demonstrably running) or a process ended."""
+    import time
+
+    deadline = time.time() + timeout_s
+    while time.time() < deadline:
+        if needle in path.read_text():
+            return
+        if any(p.poll() is not None for p in procs):
+            return
+        time.sleep(0.2)
+    raise AssertionError(f"no line with {needle!r} within {timeout_s:g} s:\n" + path.read_text()[-2000:])
+
+
 def test_a_worker_process_that_dies_ends_the_job(tmp_path):
     """Failure detection on the host: five processes (1 + 2 + 2) over TCP with heartbeats on; one worker is ended by the
     test in the middle of the job.  The scheduler misses its reports, gives up with an error that names the node, and
@@ -173,20 +198,16 @@ def test_a_worker_process_that_dies_ends_the_job(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     sched = f"role:SCHEDULER,hostname:'127.0.0.1',port:{_free_port()},id:'H'"
     env = dict(os.environ, PYTHONPATH=root)
-    procs = []
-    for r in range(5):                                                    # ranks: H, W0, W1, S0, S1
-        procs.append(subprocess.Popen([sys.executable, "-m", "parameter_server_b200.ps", "-num_servers", "2", "-num_workers", "2",
-                                       "-app", str(conf), "-scheduler", sched, "-my_rank", str(r), "-report_interval", "1"],
-                                      cwd=tmp_path, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE, text=True))
+    procs = _start_five(tmp_path, conf, sched, env)                       # ranks: H, W0, W1, S0, S1
     try:
-        time.sleep(6.0)                                                   # start-up, load, a few passes
-        assert all(p.poll() is None for p in procs), "the job ended before the failure was injected"
+        _wait_for_line(tmp_path / "H.err", " 1 | ", procs)                # the passes are under way
         procs[2].kill()                                                   # W1: this child, by its own handle
         t0 = time.time()
         try:
-            _, err = procs[0].communicate(timeout=60)
+            procs[0].wait(timeout=60)
         except subprocess.TimeoutExpired:
             pytest.fail("the scheduler kept waiting for the dead worker")
+        err = (tmp_path / "H.err").read_text()
         assert procs[0].returncode != 0 and "no heartbeat from W1" in err, err[-2000:]
         assert time.time() - t0 < 30
         for i in (1, 3, 4):                                               # the survivors were told to terminate
@@ -213,18 +234,17 @@ def test_a_worker_process_that_dies_ends_the_online_job(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     sched = f"role:SCHEDULER,hostname:'127.0.0.1',port:{_free_port()},id:'H'"
     env = dict(os.environ, PYTHONPATH=root)
-    procs = [subprocess.Popen([sys.executable, "-m", "parameter_server_b200.ps", "-num_servers", "2", "-num_workers", "2",
-                               "-app", str(conf), "-scheduler", sched, "-my_rank", str(r), "-report_interval", "1"],
-                              cwd=tmp_path, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE, text=True) for r in range(5)]
+    procs = _start_five(tmp_path, conf, sched, env)
     try:
-        time.sleep(6.0)
+        _wait_for_line(tmp_path / "H.err", " examples, loss ", procs)     # the workers are streaming
         if any(p.poll() is not None for p in procs):
             pytest.skip("the stream was over before the failure could be injected")
         procs[2].kill()                                                   # W1
         try:
-            _, err = procs[0].communicate(timeout=60)
+            procs[0].wait(timeout=60)
         except subprocess.TimeoutExpired:
             pytest.fail("the scheduler kept waiting for the dead worker")
+        err = (tmp_path / "H.err").read_text()
         assert procs[0].returncode != 0 and "no heartbeat from W1" in err, err[-2000:]
         for i in (1, 3, 4):
             procs[i].wait(timeout=60)
